@@ -1,0 +1,106 @@
+// Host launcher for the tcgen05 GEMM: builds TMA descriptors, picks the tile width and launches
+// the persistent kernel.  C ABI so Python reaches it through ctypes without a torch build step.
+#include <mutex>
+
+#include "../common/host_utils.cuh"
+#include "gemm_sm100.cuh"
+
+using namespace mcb;
+
+namespace {
+
+template <int BN, bool A_MN, bool B_MN>
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  auto kern = gemm_bf16_sm100_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;  // per template instantiation
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+template <int BN>
+cudaError_t launch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                         int grid, cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch<BN, false, false>(ta, tb, p, grid, s);
+  if (!a_mn && b_mn) return launch<BN, false, true>(ta, tb, p, grid, s);
+  if (a_mn && b_mn) return launch<BN, true, true>(ta, tb, p, grid, s);
+  return launch<BN, true, false>(ta, tb, p, grid, s);
+}
+
+int pick_bn(int M, int N, int groups, int sms) {
+  const int cand[3] = {256, 128, 64};
+  const float penalty[3] = {1.0f, 1.12f, 1.45f};  // narrower tiles re-read A more often per flop
+  int best = 256;
+  float best_cost = 1e30f;
+  for (int i = 0; i < 3; ++i) {
+    long long tiles = (long long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + cand[i] - 1) / cand[i]) * groups;
+    long long waves = (tiles + sms - 1) / sms;
+    float cost = waves * cand[i] * penalty[i];
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = cand[i];
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Returns 0 on success, a negative code for bad arguments, or a positive cudaError_t.
+//   A: K-major  -> [a_outer rows, a_inner = contraction] with leading dimension lda
+//      MN-major -> [a_outer = contraction rows, a_inner = M] with leading dimension lda
+//   B likewise (rows of a K-major B are the N index).
+int mcb_gemm_bf16(const void* A, long long a_inner, long long a_outer, long long lda, int a_mn,  //
+                  const void* B, long long b_inner, long long b_outer, long long ldb, int b_mn,  //
+                  void* C, long long ldc, long long c_group_stride, int c_fp32, int accumulate,  //
+                  int M, int N, int K, float alpha, const void* bias,                            //
+                  int mode, int num_groups, const int* offsets, int b_group_rows,               //
+                  int* status, int max_sms, int force_bn, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (mode != GEMM_DENSE && (num_groups <= 0 || num_groups > GEMM_MAX_GROUPS || offsets == nullptr)) return -2;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -3;  // TMA needs 16-byte aligned bases and strides
+  int sms = device_sm_count();
+  if (max_sms > 0 && max_sms < sms) sms = max_sms;
+  int groups = (mode == GEMM_GROUPED_K) ? num_groups : 1;
+  int bn = force_bn > 0 ? force_bn : pick_bn(M, N, groups, sms);
+  if (bn != 256 && bn != 128 && bn != 64) return -4;
+
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn)
+    rc = make_tmap_2d_bf16(&ta, A, a_inner, a_outer, lda, GEMM_BK, GEMM_BM);
+  else
+    rc = make_tmap_2d_bf16(&ta, A, a_inner, a_outer, lda, 64, GEMM_BK);
+  if (rc) return rc;
+  if (!b_mn)
+    rc = make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, GEMM_BK, bn);
+  else
+    rc = make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, 64, GEMM_BK);
+  if (rc) return rc;
+
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.c_group_stride = c_group_stride;
+  p.bias = bias; p.c_fp32 = c_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  p.mode = mode; p.num_groups = num_groups; p.offsets = offsets; p.b_group_rows = b_group_rows;
+  p.epilogue = EPI_NONE; p.aux = nullptr; p.ld_aux = 0;
+  p.status = status;
+
+  long long tiles = (long long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + bn - 1) / bn) * groups;
+  int grid = (int)(tiles < sms ? tiles : sms);
+  cudaError_t e;
+  if (bn == 256) e = launch_major<256>(a_mn, b_mn, ta, tb, p, grid, stream);
+  else if (bn == 128) e = launch_major<128>(a_mn, b_mn, ta, tb, p, grid, stream);
+  else e = launch_major<64>(a_mn, b_mn, ta, tb, p, grid, stream);
+  return (int)e;
+}
+
+}  // extern "C"
