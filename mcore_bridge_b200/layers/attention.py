@@ -1,0 +1,106 @@
+"""Self-attention block: fused-norm QKV projection, per-head q/k norm + rope, core attention, output projection.
+
+Covers standard GQA attention and the gated variant (``attention_output_gate``: the query projection is
+doubled, every query head is followed by a gate head and the attention output is multiplied by
+``sigmoid(gate)`` — reference ``src/mcore_bridge/model/modules/gated_self_attention.py:55-83``).
+Parameter names: ``linear_qkv.{weight,bias,layer_norm_weight}``, ``q_layernorm.weight``,
+``k_layernorm.weight``, ``linear_proj.weight`` and, for learnable softmax sinks, ``core_attention.softmax_offset``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ..ops.attention import attention
+from ..ops.rope import qkv_split_norm_rope
+from ..parallel import state as ps
+from .context import ForwardContext
+from .linear import ColumnParallelLinear, LayerNormColumnParallelLinear, RowParallelLinear
+from .norm import Norm
+
+
+class CoreAttention(nn.Module):
+
+    def __init__(self, config, layer_number: int, num_heads_local: int, window=None, scale: Optional[float] = None):
+        super().__init__()
+        self.config = config
+        self.window = window
+        self.scale = scale
+        if config.softmax_type == 'learnable':
+            self.softmax_offset = nn.Parameter(torch.zeros(num_heads_local, dtype=config.params_dtype))
+            self.softmax_offset.tensor_model_parallel = ps.get_world_size('tp') > 1
+            self.softmax_offset.partition_dim = 0
+        else:
+            self.register_parameter('softmax_offset', None)
+        self.off_by_one = config.softmax_type == 'off-by-one'
+
+    def forward(self, q, k, v, ctx: ForwardContext):
+        sinks = self.softmax_offset
+        if self.off_by_one:
+            sinks = torch.zeros(q.shape[1], device=q.device, dtype=torch.float32)
+        cp = ps.get_world_size('cp')
+        if cp > 1:
+            from ..parallel.context_parallel import ring_attention
+            return ring_attention(q, k, v, ctx, scale=self.scale, window=self.window, sinks=sinks)
+        return attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, causal=True, scale=self.scale, window=self.window,
+                         sinks=sinks)
+
+
+class SelfAttention(nn.Module):
+
+    def __init__(self, config, layer_number: int, fuse_input_norm: bool = True, use_rope: bool = True,
+                 window=None, rope_key: Optional[str] = None, kv_channels: Optional[int] = None,
+                 num_query_groups: Optional[int] = None):
+        super().__init__()
+        self.config = config
+        self.layer_number = layer_number
+        tp = ps.get_world_size('tp')
+        self.d = kv_channels or config.kv_channels
+        self.nq = config.num_attention_heads
+        self.ng = num_query_groups or config.num_query_groups
+        assert self.nq % tp == 0
+        if self.ng % tp != 0:
+            raise NotImplementedError(f'num_query_groups ({self.ng}) must be divisible by TP ({tp})')
+        self.nq_local, self.ng_local = self.nq // tp, self.ng // tp
+        self.qpg = self.nq // self.ng
+        self.gate = bool(config.attention_output_gate)
+        qkv_out = (self.nq * (2 if self.gate else 1) + 2 * self.ng) * self.d
+        cls = LayerNormColumnParallelLinear if fuse_input_norm else ColumnParallelLinear
+        self.linear_qkv = cls(config.hidden_size, qkv_out, config, bias=config.add_qkv_bias or config.add_bias_linear)
+        if config.qk_layernorm:
+            self.q_layernorm = Norm(config, self.d, sequence_parallel_grad=False)
+            self.k_layernorm = Norm(config, self.d, sequence_parallel_grad=False)
+        else:
+            self.q_layernorm = self.k_layernorm = None
+        self.qk_l2_norm = bool(config.qk_l2_norm)
+        scale = config.softmax_scale
+        self.core_attention = CoreAttention(config, layer_number, self.nq_local, window=window, scale=scale)
+        self.linear_proj = RowParallelLinear(self.nq * self.d, config.hidden_size, config, bias=config.add_bias_linear)
+        self.use_rope = use_rope and config.position_embedding_type in ('rope', 'mrope')
+        self.rope_key = rope_key
+
+    def forward(self, x: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
+        cfg = self.config
+        qkv = self.linear_qkv(x)                                  # [T, local packed qkv]
+        cos = sin = None
+        if self.use_rope:
+            if self.rope_key is not None and self.rope_key in ctx.rope_tables:
+                cos, sin = ctx.rope_tables[self.rope_key]
+            else:
+                cos, sin = ctx.cos, ctx.sin
+        wq = self.q_layernorm.weight if self.q_layernorm is not None else None
+        wk = self.k_layernorm.weight if self.k_layernorm is not None else None
+        q, k, v, gate = qkv_split_norm_rope(qkv, wq, wk, cos, sin, self.ng_local, self.qpg, self.d, self.gate,
+                                            cfg.rotary_interleaved, cfg.layernorm_epsilon,
+                                            cfg.layernorm_zero_centered_gamma)
+        if self.qk_l2_norm:
+            from ..ops.norm import l2norm
+            q, k = l2norm(q), l2norm(k)
+        o = self.core_attention(q, k, v, ctx)                     # [T, nq_local, d]
+        o = o.reshape(o.shape[0], -1)
+        if gate is not None:
+            o = o * torch.sigmoid(gate.reshape(o.shape[0], -1).float()).to(o.dtype)
+        return self.linear_proj(o)

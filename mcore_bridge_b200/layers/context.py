@@ -1,0 +1,35 @@
+"""Per-batch tensors shared by every layer of a forward pass (rope tables, packing, masks)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, Optional
+
+import torch
+
+
+@dataclass
+class PackedSeqParams:
+    """Packed ("thd") batch description; field names follow Megatron's ``PackedSeqParams`` so user code
+    written for the reference passes the same object (reference ``src/mcore_bridge/model/gpt_model.py:238``)."""
+    qkv_format: str = 'thd'
+    cu_seqlens_q: Optional[torch.Tensor] = None
+    cu_seqlens_kv: Optional[torch.Tensor] = None
+    cu_seqlens_q_padded: Optional[torch.Tensor] = None
+    cu_seqlens_kv_padded: Optional[torch.Tensor] = None
+    max_seqlen_q: Optional[int] = None
+    max_seqlen_kv: Optional[int] = None
+
+
+@dataclass
+class ForwardContext:
+    cu_seqlens: Optional[torch.Tensor] = None      # int32 [B+1], boundaries in the *full* (pre-CP) token stream
+    max_seqlen: Optional[int] = None
+    cos: Optional[torch.Tensor] = None             # [T_local_cp, rot/2]
+    sin: Optional[torch.Tensor] = None
+    position_ids: Optional[torch.Tensor] = None    # [T] positions of the tokens this CP rank holds
+    padding_mask: Optional[torch.Tensor] = None    # [T_local] True where the token is padding
+    seg_ids: Optional[torch.Tensor] = None         # [T_local] packed-sequence index per token
+    num_seqs: Optional[int] = None
+    input_ids: Optional[torch.Tensor] = None       # hash-routed MoE layers look at the ids
+    extra: Dict[str, Any] = field(default_factory=dict)
+    rope_tables: Dict[str, Any] = field(default_factory=dict)  # alternative tables (sliding / compressed / indexer)

@@ -1,0 +1,335 @@
+"""Mixture-of-experts layer: router, token dispatcher, grouped experts, shared expert.
+
+Dispatch is "alltoall" (the reference pins ``moe_token_dispatcher_type='alltoall'`` and
+``moe_grouped_gemm=True``, ``src/mcore_bridge/config/model_config.py:233-234``): every rank routes its own
+tokens, copies travel to the rank owning the expert, experts run as one grouped GEMM over an
+expert-sorted buffer, results travel back and are summed per token.
+
+Module / parameter names (``router.weight``, ``router.expert_bias``, ``experts.linear_fc1``,
+``shared_experts.gate_weight`` ...) match what the weight bridge addresses.  Expert weights are stored
+stacked, ``[E_local, out, in]``, the layout the grouped tcgen05 GEMM consumes; ``weight{i}`` resolves to
+a view of expert ``i``.
+"""
+from __future__ import annotations
+
+import re
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..ops import gemm
+from ..ops import moe as moe_ops
+from ..ops.activation import glu
+from ..ops.linear import LinearSpec, linear
+from ..parallel import mappings as M
+from ..parallel import state as ps
+from .linear import ColumnParallelLinear, RowParallelLinear, _set_tp_attrs
+from .norm import mark_sequence_parallel
+
+_AUX_TRACKER = {}
+
+
+def get_moe_aux_losses() -> dict:
+    """Per-step tracker ``{name: (sum, count)}`` the trainer logs and clears."""
+    return _AUX_TRACKER
+
+
+def _track(name: str, value: torch.Tensor):
+    s, c = _AUX_TRACKER.get(name, (0.0, 0))
+    _AUX_TRACKER[name] = (s + value.detach().float(), c + 1)
+
+
+class TopKRouter(nn.Module):
+    """Gate ``[E, H]`` in fp32 math + top-k selection + load-balancing losses + expert-bias bookkeeping.
+
+    The expert-bias token count ignores padded tokens and is only updated while gradients are enabled, so
+    evaluation and activation recomputation do not double count (reference
+    ``src/mcore_bridge/model/modules/topk_router.py:7-21``).
+    """
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.num_experts = config.num_moe_experts
+        self.topk = config.moe_router_topk
+        self.weight = nn.Parameter(torch.empty(self.num_experts, config.hidden_size, dtype=config.params_dtype))
+        _set_tp_attrs(self.weight, False, -1)
+        mark_sequence_parallel(self.weight, config)
+        self.enable_expert_bias = bool(config.moe_router_enable_expert_bias)
+        if self.enable_expert_bias:
+            self.register_buffer('expert_bias', torch.zeros(self.num_experts, dtype=torch.float32))
+            self.register_buffer('local_tokens_per_expert', torch.zeros(self.num_experts, dtype=torch.float32),
+                                 persistent=False)
+        else:
+            self.expert_bias = None
+
+    def gating(self, x: torch.Tensor) -> torch.Tensor:
+        dt = {None: x.dtype, 'fp32': torch.float32, 'fp64': torch.float64}[self.config.moe_router_dtype]
+        return torch.nn.functional.linear(x.to(dt), self.weight.to(dt))
+
+    def _apply_expert_bias(self, indices: torch.Tensor, padding_mask: Optional[torch.Tensor]):
+        if self.enable_expert_bias and torch.is_grad_enabled():
+            with torch.no_grad():
+                valid = None if padding_mask is None else ~padding_mask.reshape(-1)
+                self.local_tokens_per_expert += moe_ops.tokens_per_expert(indices, self.num_experts, valid)
+
+    @torch.no_grad()
+    def update_expert_bias(self, group=None):
+        """Aux-loss-free balancing: ``bias += rate * sign(mean_load - load)`` from the accumulated counts."""
+        if not self.enable_expert_bias:
+            return
+        load = self.local_tokens_per_expert.clone()
+        if group is not None:
+            dist.all_reduce(load, group=group)
+        self.expert_bias += self.config.moe_router_bias_update_rate * torch.sign(load.mean() - load)
+        self.local_tokens_per_expert.zero_()
+
+    def forward(self, x: torch.Tensor, padding_mask: Optional[torch.Tensor] = None, seg_ids=None, num_seqs=None):
+        cfg = self.config
+        logits = self.gating(x)
+        if cfg.moe_z_loss_coeff:
+            z = moe_ops.z_loss(logits, cfg.moe_z_loss_coeff)
+            logits = moe_ops.MoEAuxLossAutoScaler.apply(logits, z)
+            _track('z_loss', z / cfg.moe_z_loss_coeff)
+        probs, idx, scores = moe_ops.topk_routing(
+            logits, self.topk, cfg.moe_router_score_function, cfg.moe_router_pre_softmax, cfg.moe_router_num_groups,
+            cfg.moe_router_group_topk, cfg.moe_router_topk_scaling_factor, self.expert_bias)
+        self._apply_expert_bias(idx, padding_mask)
+        lb = cfg.moe_router_load_balancing_type
+        coeff = cfg.moe_aux_loss_coeff
+        if self.training and coeff and lb in ('aux_loss', 'global_aux_loss', 'seq_aux_loss'):
+            valid = None if padding_mask is None else ~padding_mask.reshape(-1)
+            if lb == 'seq_aux_loss' and seg_ids is not None:
+                aux = moe_ops.seq_aux_loss(scores, idx, seg_ids, num_seqs, self.topk, coeff)
+            else:
+                sc = scores if valid is None else scores * valid[:, None]
+                counts = moe_ops.tokens_per_expert(idx, self.num_experts, valid)
+                ntok = torch.tensor(float(scores.shape[0]), device=x.device) if valid is None else valid.sum().float()
+                group = 'tp_dp_cp' if lb == 'global_aux_loss' else ('tp_cp' if cfg.sequence_parallel or
+                                                                    cfg.context_parallel_size > 1 else None)
+                if group is not None and ps.get_world_size(group) > 1:
+                    # f_e uses the counts of the whole (sub)sequence group; P_e stays local (its gradient is local)
+                    packed = torch.cat([counts, ntok.view(1)])
+                    dist.all_reduce(packed, group=ps.get_group(group))
+                    n = ps.get_world_size(group)
+                    counts, ntok_all = packed[:-1], packed[-1]
+                    aux = coeff * self.num_experts * ((counts / (ntok_all * self.topk)) * (sc.sum(0) / ntok)).sum()
+                else:
+                    aux = moe_ops.aux_loss(sc, counts, self.topk, coeff, ntok)
+            probs = moe_ops.MoEAuxLossAutoScaler.apply(probs, aux)
+            _track('load_balancing_loss', aux / coeff)
+        return probs, idx
+
+
+class GroupedLinear(nn.Module):
+    """``E_local`` linears as one stacked parameter; forward over an expert-sorted, padded row buffer."""
+
+    def __init__(self, num_local_experts: int, input_size: int, output_size: int, config, parallel_mode: str):
+        super().__init__()
+        n = ps.get_world_size('etp')
+        self.parallel_mode = parallel_mode
+        if parallel_mode == 'column':
+            output_size //= n
+            pdim = 1
+        else:
+            input_size //= n
+            pdim = 2
+        self.num_local_experts = num_local_experts
+        self.weight = nn.Parameter(torch.empty(num_local_experts, output_size, input_size, dtype=config.params_dtype))
+        _set_tp_attrs(self.weight, n > 1, pdim, is_expert=True)
+
+    def __getattr__(self, name):
+        m = re.fullmatch(r'weight(\d+)', name)
+        if m is not None:
+            return super().__getattr__('weight')[int(m.group(1))]
+        return super().__getattr__(name)
+
+    def forward(self, x, offsets):
+        return _GroupedLinearFn.apply(x, self.weight, offsets)
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, weight, offsets):
+        ctx.save_for_backward(x, weight, offsets)
+        return gemm.grouped_mm_nt(x, weight, offsets)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, offsets = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = gemm.grouped_mm_nn(dy, weight, offsets) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(weight, 'main_grad', None)
+            if mg is not None:
+                gemm.grouped_mm_tn(dy, x, offsets, out=mg, accumulate=True)
+                hook = getattr(weight, 'grad_ready_hook', None)
+                if hook is not None:
+                    hook()
+            else:
+                dw = gemm.grouped_mm_tn(dy, x, offsets, out_dtype=weight.dtype)
+        return dx, dw, None
+
+
+class GroupedMLP(nn.Module):
+    """All local experts: grouped fc1 -> gated activation (weighted by the routing prob) -> grouped fc2."""
+
+    def __init__(self, config, num_local_experts: int):
+        super().__init__()
+        self.config = config
+        f = config.moe_ffn_hidden_size
+        mult = 2 if config.gated_linear_unit else 1
+        self.linear_fc1 = GroupedLinear(num_local_experts, config.hidden_size, f * mult, config, 'column')
+        self.linear_fc2 = GroupedLinear(num_local_experts, f, config.hidden_size, config, 'row')
+        self.kind = 'swiglu' if config.swiglu else ('quick_geglu' if config.quick_geglu else 'geglu_tanh')
+
+    def forward(self, x, offsets, row_probs=None):
+        cfg = self.config
+        h = self.linear_fc1(x, offsets)
+        if cfg.gated_linear_unit:
+            h = glu(h, self.kind, row_probs, cfg.activation_func_clamp_value or 0.0, cfg.glu_linear_offset)
+        else:
+            h = cfg.activation_func(h)
+            if row_probs is not None:
+                h = h * row_probs[:, None].to(h.dtype)
+        return self.linear_fc2(h, offsets)
+
+
+class SharedExpertMLP(nn.Module):
+    """Always-on expert beside the routed ones, optionally gated by ``sigmoid(x . gate_weight)``."""
+
+    def __init__(self, config, intermediate_size: int):
+        super().__init__()
+        self.config = config
+        mult = 2 if config.gated_linear_unit else 1
+        self.linear_fc1 = ColumnParallelLinear(config.hidden_size, intermediate_size * mult, config,
+                                               bias=config.add_bias_linear)
+        self.linear_fc2 = RowParallelLinear(intermediate_size, config.hidden_size, config, bias=config.add_bias_linear)
+        if config.moe_shared_expert_gate:
+            self.gate_weight = nn.Parameter(torch.empty(1, config.hidden_size, dtype=config.params_dtype))
+            mark_sequence_parallel(self.gate_weight, config)
+        else:
+            self.register_parameter('gate_weight', None)
+        self.kind = 'swiglu' if config.swiglu else ('quick_geglu' if config.quick_geglu else 'geglu_tanh')
+
+    def forward(self, x):
+        cfg = self.config
+        h = self.linear_fc1(x)
+        if cfg.gated_linear_unit:
+            h = glu(h, self.kind, None, cfg.activation_func_clamp_value or 0.0, cfg.glu_linear_offset)
+        else:
+            h = cfg.activation_func(h)
+        y = self.linear_fc2(h)
+        if self.gate_weight is not None:
+            g = torch.sigmoid(torch.nn.functional.linear(x.float(), self.gate_weight.float()))
+            y = (y.float() * g).to(y.dtype)
+        return y
+
+
+class MoELayer(nn.Module):
+
+    def __init__(self, config, layer_number: int = 1):
+        super().__init__()
+        self.config = config
+        self.layer_number = layer_number
+        self.ep = ps.get_world_size('ep')
+        self.ep_rank = ps.get_rank_in('ep') if self.ep > 1 else 0
+        self.num_experts = config.num_moe_experts
+        assert self.num_experts % self.ep == 0
+        self.num_local_experts = self.num_experts // self.ep
+        self.router = TopKRouter(config)
+        self.experts = GroupedMLP(config, self.num_local_experts)
+        if config.moe_shared_expert_intermediate_size:
+            self.shared_experts = SharedExpertMLP(config, config.moe_shared_expert_intermediate_size)
+        else:
+            self.shared_experts = None
+        self.apply_probs_on_input = bool(config.moe_apply_probs_on_input)
+
+    # -- dispatch over the EP group with torch.distributed (baseline; host-synchronised split sizes)
+    def _dispatch_nccl(self, x, probs, idx):
+        T, k = idx.shape
+        E, El, ep = self.num_experts, self.num_local_experts, self.ep
+        flat_e = idx.reshape(-1)
+        src_token = torch.arange(T, device=x.device).repeat_interleave(k)
+        order = torch.argsort(flat_e, stable=True)              # copies sorted by global expert = by dest rank
+        send = x.index_select(0, src_token[order])
+        send_e = flat_e[order]
+        send_p = probs.reshape(-1)[order]
+        counts = torch.bincount(flat_e, minlength=E)
+        all_counts = torch.empty(ep, E, dtype=counts.dtype, device=x.device)
+        dist.all_gather_into_tensor(all_counts, counts.contiguous(), group=ps.get_group('ep'))
+        in_splits = counts.view(ep, El).sum(1).tolist()                                   # host sync
+        out_splits = all_counts[:, self.ep_rank * El:(self.ep_rank + 1) * El].sum(1).tolist()
+        recv = M.all_to_all(send, out_splits, in_splits, 'ep')
+        recv_e = M.all_to_all_single(send_e.contiguous(), out_splits, in_splits, 'ep') - self.ep_rank * El
+        recv_p = M.all_to_all(send_p.contiguous().view(-1, 1), out_splits, in_splits, 'ep').view(-1)
+        return recv, recv_e, recv_p, (order, src_token, in_splits, out_splits)
+
+    def forward(self, x: torch.Tensor, padding_mask: Optional[torch.Tensor] = None, seg_ids=None, num_seqs=None):
+        """``x [T_local, H]`` -> ``[T_local, H]``."""
+        cfg = self.config
+        T, H = x.shape
+        probs, idx = self.router(x, padding_mask, seg_ids, num_seqs)
+        k = idx.shape[1]
+        etp = ps.get_world_size('etp')
+        if self.ep == 1:
+            src_token = torch.arange(T, device=x.device).repeat_interleave(k)
+            dest, offsets, cap = moe_ops.permute_plan(idx.reshape(-1), self.num_local_experts)
+            xp = moe_ops.permute(x, src_token, dest, cap)
+            pflat = probs.reshape(-1)
+            if self.apply_probs_on_input:
+                xp = _scale_rows(xp, dest, pflat, cap)
+                row_probs = None
+            else:
+                row_probs = _scatter_rows(pflat, dest, cap)
+            if etp > 1:
+                raise NotImplementedError('expert tensor parallelism > 1')
+            yp = self.experts(xp, offsets, row_probs)
+            y = moe_ops.unpermute(yp, src_token, dest, T, None)
+        else:
+            recv, recv_e, recv_p, (order, src_token, in_splits, out_splits) = self._dispatch_nccl(x, probs, idx)
+            R = recv.shape[0]
+            dest, offsets, cap = moe_ops.permute_plan(recv_e, self.num_local_experts)
+            ar = torch.arange(R, device=x.device)
+            xp = moe_ops.permute(recv, ar, dest, cap)
+            if self.apply_probs_on_input:
+                xp = _scale_rows(xp, dest, recv_p, cap)
+                row_probs = None
+            else:
+                row_probs = _scatter_rows(recv_p, dest, cap)
+            yp = self.experts(xp, offsets, row_probs)
+            back = moe_ops.unpermute(yp, ar, dest, R, None)          # rows back in arrival order
+            ret = M.all_to_all(back, in_splits, out_splits, 'ep')    # rows in `order`
+            y = moe_ops.unpermute(ret, src_token[order], torch.arange(ret.shape[0], device=x.device), T, None)
+        if self.shared_experts is not None:
+            y = y + self.shared_experts(x)
+        return y
+
+
+class _ScatterRows(torch.autograd.Function):
+    """``out[dest[i]] = v[i]`` into a zero vector of length ``cap`` (per-row routing probabilities)."""
+
+    @staticmethod
+    def forward(ctx, v, dest, cap):
+        out = torch.zeros(cap, dtype=torch.float32, device=v.device)
+        out.index_copy_(0, dest, v.float())
+        ctx.save_for_backward(dest)
+        ctx.dtype = v.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (dest,) = ctx.saved_tensors
+        return g.index_select(0, dest).to(ctx.dtype), None, None
+
+
+def _scatter_rows(v, dest, cap):
+    return _ScatterRows.apply(v, dest, cap)
+
+
+def _scale_rows(xp, dest, v, cap):
+    return (xp.float() * _scatter_rows(v, dest, cap)[:, None]).to(xp.dtype)

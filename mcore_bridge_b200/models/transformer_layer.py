@@ -1,0 +1,113 @@
+"""One decoder layer: attention variant + residual, then dense MLP or MoE + residual.
+
+Which sub-modules a layer gets is decided by its (1-based) ``layer_number`` and the config patterns:
+MoE vs dense (``moe_layer_freq``), gated-DeltaNet vs full attention (``linear_attention_freq``), sliding
+window (``window_attn_skip_freq``), rope skipping (``no_rope_freq``), MLA / DSA
+(``multi_latent_attention`` / ``experimental_attention_variant``).  Norms are folded into the following
+linear where that linear is column-parallel (``linear_qkv.layer_norm_weight``,
+``mlp.linear_fc1.layer_norm_weight``); MoE layers and MLA keep stand-alone ``pre_mlp_layernorm`` /
+``input_layernorm`` modules — the naming the weight bridge relies on (reference
+``src/mcore_bridge/bridge/gpt_bridge.py:1619-1651``).
+
+``mlp_padding_free`` drops padding tokens before the MLP/MoE and restores them afterwards (reference
+``src/mcore_bridge/model/modules/transformer_layer.py:343-375``).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ..layers.attention import SelfAttention
+from ..layers.context import ForwardContext
+from ..layers.mlp import MLP
+from ..layers.moe import MoELayer
+from ..layers.norm import Norm
+from ..parallel import mappings as M
+from ..parallel import state as ps
+
+
+def _identity(x):
+    return x
+
+
+class TransformerLayer(nn.Module):
+
+    def __init__(self, config, layer_number: int, is_mtp_layer: bool = False):
+        super().__init__()
+        self.config = config
+        self.layer_number = layer_number
+        idx = min(layer_number - 1, config.num_layers - 1)  # MTP layers reuse the last layer's pattern entry
+        self.is_moe = bool(config.moe_layer_pattern()[idx]) if config.num_moe_experts else False
+        self.is_linear_attention = bool(config.linear_attention_pattern()[idx]) and not is_mtp_layer
+        use_rope = not bool(config.no_rope_pattern()[idx])
+        window = config.window_size if config.window_pattern()[idx] else None
+        variant = config.experimental_attention_variant
+        self.input_layernorm = None
+        if self.is_linear_attention and variant == 'gated_delta_net':
+            from ..layers.gated_delta_net import GatedDeltaNet
+            self.self_attention = GatedDeltaNet(config, layer_number)
+        elif config.multi_latent_attention:
+            from ..layers.mla import MLASelfAttention
+            self.input_layernorm = Norm(config, config.hidden_size)
+            self.self_attention = MLASelfAttention(config, layer_number)
+        else:
+            self.self_attention = SelfAttention(config, layer_number, fuse_input_norm=True, use_rope=use_rope,
+                                                window=window)
+        if self.is_moe:
+            self.pre_mlp_layernorm = Norm(config, config.hidden_size)
+            self.mlp = MoELayer(config, layer_number)
+        else:
+            self.pre_mlp_layernorm = None
+            self.mlp = MLP(config, fuse_input_norm=True)
+
+    def _attention(self, hidden, ctx):
+        x = hidden if self.input_layernorm is None else self.input_layernorm(hidden)
+        return hidden + self.self_attention(x, ctx)
+
+    def _mlp(self, hidden, ctx: ForwardContext):
+        cfg = self.config
+        x = hidden if self.pre_mlp_layernorm is None else self.pre_mlp_layernorm(hidden)
+        if self.is_moe:
+            out = self.mlp(x, ctx.padding_mask, ctx.seg_ids, ctx.num_seqs)
+        else:
+            out = self.mlp(x)
+        return hidden + out
+
+    def _mlp_padding_free(self, hidden, ctx: ForwardContext):
+        """Run the MLP on non-padding tokens only.  Under sequence parallelism the tokens are gathered,
+        filtered, padded to a multiple of TP and scattered again, and the inverse afterwards."""
+        cfg = self.config
+        sp = cfg.sequence_parallel and ps.get_world_size('tp') > 1
+        x = hidden if self.pre_mlp_layernorm is None else None
+        h = hidden
+        if sp:
+            h = M.gather_from_sequence_parallel_region(h, tensor_parallel_output_grad=False)
+        keep = ~ctx.extra['full_padding_mask']
+        sel = keep.nonzero(as_tuple=True)[0]
+        hs = h.index_select(0, sel)
+        pad = 0
+        if sp:
+            tp = ps.get_world_size('tp')
+            pad = (-hs.shape[0]) % tp
+            if pad:
+                hs = torch.nn.functional.pad(hs, (0, 0, 0, pad))
+            hs = M.scatter_to_sequence_parallel_region(hs)
+        sub = ForwardContext(**{**ctx.__dict__, 'padding_mask': None, 'seg_ids': None})
+        xs = hs if self.pre_mlp_layernorm is None else self.pre_mlp_layernorm(hs)
+        out = self.mlp(xs, None, None, None) if self.is_moe else self.mlp(xs)
+        if sp:
+            out = M.gather_from_sequence_parallel_region(out, tensor_parallel_output_grad=False)
+            if pad:
+                out = out[:-pad]
+        full = torch.zeros_like(h).index_copy(0, sel, out)
+        if sp:
+            full = M.scatter_to_sequence_parallel_region(full)
+        return hidden + full
+
+    def forward(self, hidden: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
+        hidden = self._attention(hidden, ctx)
+        if self.config.mlp_padding_free and ctx.extra.get('full_padding_mask') is not None:
+            return self._mlp_padding_free(hidden, ctx)
+        return self._mlp(hidden, ctx)

@@ -1,0 +1,108 @@
+"""Dequantisers for quantised Hugging Face checkpoints: block-scaled fp8, MXFP4, fp4(e2m1)->fp8, packed int4/int8.
+
+Semantics as in reference ``src/mcore_bridge/utils/dequantizer.py:6-152``; formulas written out here.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+# e2m1 code -> value (sign bit is bit 3)
+_FP4_VALUES = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+
+
+class Fp8Dequantizer:
+    """``w = q * scale_inv`` with one scale per ``block_m x block_n`` block (ragged edges allowed)."""
+
+    def __init__(self, block_size: Tuple[Optional[int], Optional[int]] = (None, None)):
+        self.block_size = block_size
+
+    def convert(self, quantized: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+        if not isinstance(quantized, torch.Tensor) or not isinstance(scales, torch.Tensor):
+            raise TypeError('Fp8Dequantizer expects tensors')
+        if quantized.dtype == torch.uint8:
+            quantized = quantized.view(torch.float8_e4m3fn)
+        q = quantized.to(torch.float32)
+        rows, cols = q.shape[-2:]
+        srows, scols = scales.shape[-2:]
+        bm, bn = self.block_size
+        bm = bm or -(-rows // srows)
+        bn = bn or -(-cols // scols)
+        s = scales.to(torch.float32)
+        s = s.repeat_interleave(bm, dim=-2)[..., :rows, :].repeat_interleave(bn, dim=-1)[..., :, :cols]
+        return q * s
+
+
+def quantize_fp8_blockwise(w: torch.Tensor, block: Tuple[int, int] = (128, 128)):
+    """Inverse of :class:`Fp8Dequantizer`: returns ``(fp8 e4m3 tensor, scale_inv)``."""
+    bm, bn = block
+    rows, cols = w.shape[-2:]
+    pr, pc = (-rows) % bm, (-cols) % bn
+    wf = torch.nn.functional.pad(w.float(), (0, pc, 0, pr))
+    R, C = wf.shape[-2:]
+    blocks = wf.reshape(*wf.shape[:-2], R // bm, bm, C // bn, bn)
+    amax = blocks.abs().amax(dim=(-3, -1), keepdim=True).clamp(min=1e-12)
+    scale_inv = amax / 448.0
+    q = (blocks / scale_inv).reshape(*wf.shape[:-2], R, C)[..., :rows, :cols].to(torch.float8_e4m3fn)
+    return q, scale_inv.squeeze(-1).squeeze(-2)
+
+
+class MxFp4Dequantizer:
+    """MXFP4: two e2m1 values per byte (low nibble first), one e8m0 scale per 32 values."""
+
+    def convert(self, blocks: torch.Tensor, scales: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        lut = torch.tensor(_FP4_VALUES, dtype=torch.float32, device=blocks.device)
+        b = blocks.to(torch.uint8)
+        lo, hi = (b & 0x0F).long(), (b >> 4).long()
+        vals = torch.stack((lut[lo], lut[hi]), dim=-1).flatten(-2)         # [..., G, 32]
+        exp = scales.to(torch.int32) - 127
+        out = torch.ldexp(vals, exp.unsqueeze(-1))
+        return out.flatten(-2).to(dtype)
+
+
+def fp4_to_fp8(packed: torch.Tensor) -> torch.Tensor:
+    """Unpacks e2m1 nibbles (low first) into ``float8_e4m3fn`` values; output last dim doubles."""
+    lut = torch.tensor(_FP4_VALUES, dtype=torch.float32, device=packed.device)
+    b = packed.view(torch.uint8)
+    lo, hi = (b & 0x0F).long(), (b >> 4).long()
+    return torch.stack((lut[lo], lut[hi]), dim=-1).flatten(-2).to(torch.float8_e4m3fn)
+
+
+class PackedDequantizer:
+    """compressed-tensors style packed int4 / int8 weights: ``weight_packed`` (int32 words holding
+    ``32/bits`` values, offset-binary), ``weight_scale`` per group, optional ``weight_zero_point``."""
+
+    def __init__(self, quantization_config: dict):
+        cfg = quantization_config or {}
+        groups = cfg.get('config_groups') or {}
+        w = {}
+        for g in groups.values():
+            w = g.get('weights') or {}
+            break
+        self.num_bits = int(w.get('num_bits', cfg.get('bits', 4)))
+        self.group_size = w.get('group_size', cfg.get('group_size', 128))
+        self.symmetric = bool(w.get('symmetric', True))
+
+    def unpack(self, packed: torch.Tensor, shape) -> torch.Tensor:
+        bits = self.num_bits
+        per = 32 // bits
+        p = packed.to(torch.int32)
+        shifts = torch.arange(per, device=p.device, dtype=torch.int32) * bits
+        vals = (p.unsqueeze(-1) >> shifts) & ((1 << bits) - 1)
+        vals = vals.flatten(-2)[..., :shape[-1]]
+        return vals - (1 << (bits - 1))  # offset binary -> signed
+
+    def convert(self, weight_packed: torch.Tensor, weight_scale: torch.Tensor, weight_shape,
+                weight_zero_point: Optional[torch.Tensor] = None, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        shape = [int(x) for x in (weight_shape.tolist() if isinstance(weight_shape, torch.Tensor) else weight_shape)]
+        q = self.unpack(weight_packed, shape).to(torch.float32)
+        rows, cols = shape[-2], shape[-1]
+        scale = weight_scale.to(torch.float32)
+        gs = self.group_size if self.group_size and self.group_size > 0 else cols
+        s = scale.repeat_interleave(gs, dim=-1)[..., :cols] if scale.shape[-1] != cols else scale
+        if weight_zero_point is not None and not self.symmetric:
+            zp = self.unpack(weight_zero_point, [rows, scale.shape[-1]]).float() if weight_zero_point.dtype == torch.int32 \
+                else weight_zero_point.float()
+            q = q - zp.repeat_interleave(gs, dim=-1)[..., :cols]
+        return (q * s).to(dtype)
