@@ -17,6 +17,7 @@ _LIB_PATH = Path(__file__).resolve().parent.parent / 'lib' / 'libmcb200.so'
 _lib = None
 _lock = threading.Lock()
 _status_words: dict[int, torch.Tensor] = {}
+LAUNCHES = 0  # kernel launches issued through this library (every op reports exactly one per launch)
 
 STATUS_NAMES = {
     0: 'ok', 1: 'timeout waiting for a filled smem stage', 2: 'timeout waiting for a free smem stage',
@@ -85,5 +86,7 @@ def check_status(device=None, clear: bool = True) -> None:
 
 
 def check_rc(rc: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if rc != 0:
         raise KernelError(f'{what} failed with code {rc}' + (' (CUDA error)' if rc > 0 else ' (bad argument)'))

@@ -1,0 +1,364 @@
+"""Data-parallel gradient buffers and the sharded ("distributed") AdamW optimizer.
+
+Layout.  Parameters are regrouped into a few flat buffers keyed by (expert / dense, weight-decay / none):
+a bf16 parameter buffer (the model's parameters become views into it) and an fp32 gradient buffer
+(``param.main_grad`` views; the weight-gradient GEMMs accumulate straight into it).  Each buffer is cut into
+buckets; a bucket is reduce-scattered over the data-parallel group as soon as every gradient in it is
+final — on a side stream, overlapping with the rest of backward — and each rank keeps fp32 master weights
+and Adam moments only for its 1/dp slice of every bucket.  After the fused Adam kernel has updated the slice
+and written the bf16 values, the parameter buffer is all-gathered bucket by bucket.
+
+Dense parameters shard over the ``dp_cp`` group, expert parameters over ``edp``.  Parameters flagged
+``sequence_parallel`` (norm weights, router ...) have their gradients summed over the tensor-parallel group
+first.  With a data-parallel size of one the collectives vanish and the optimizer still runs the same
+fused kernel on the whole buffer.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..ops import _lib
+from ..parallel import state as ps
+from ..utils.logger import get_logger
+
+logger = get_logger()
+_ll, _int, _f = ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+ALIGN = 128  # elements; keeps every shard 16-byte aligned for vector access in any dtype
+
+
+class Bucket:
+
+    def __init__(self, start: int, end: int):
+        self.start, self.end = start, end
+        self.params: List[nn.Parameter] = []
+        self.pending = 0
+        self.work = None
+
+
+class ParamAndGradBuffer:
+
+    def __init__(self, params: List[nn.Parameter], group_name: str, bucket_bytes: int, device, param_dtype,
+                 grad_dtype=torch.float32):
+        self.group_name = group_name
+        self.dp = ps.get_world_size(group_name)
+        self.dp_rank = ps.get_rank_in(group_name) if self.dp > 1 else 0
+        self.group = ps.get_group(group_name) if self.dp > 1 else None
+        self.params = params
+        unit = ALIGN * self.dp
+        bucket_elems = max(unit, bucket_bytes // 4 // unit * unit)
+        self.buckets: List[Bucket] = []
+        self.param_range: Dict[nn.Parameter, Tuple[int, int]] = {}
+        offset, bstart = 0, 0
+        cur: List[nn.Parameter] = []
+        for p in params:
+            n = p.numel()
+            start = (offset + 7) // 8 * 8
+            self.param_range[p] = (start, start + n)
+            offset = start + n
+            cur.append(p)
+            if offset - bstart >= bucket_elems:
+                end = (offset + unit - 1) // unit * unit
+                b = Bucket(bstart, end)
+                b.params = cur
+                self.buckets.append(b)
+                cur, bstart, offset = [], end, end
+        if cur:
+            end = (offset + unit - 1) // unit * unit
+            b = Bucket(bstart, end)
+            b.params = cur
+            self.buckets.append(b)
+            offset = end
+        self.numel = offset
+        self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=device)
+        self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=device)
+        self.param_to_bucket: Dict[nn.Parameter, Bucket] = {}
+        for b in self.buckets:
+            for p in b.params:
+                self.param_to_bucket[p] = b
+        for p in params:
+            s, e = self.param_range[p]
+            view = self.param_data[s:e].view(p.shape)
+            view.copy_(p.data)
+            p.data = view
+            p.main_grad = self.grad_data[s:e].view(p.shape)
+
+    def shard_range(self, b: Bucket) -> Tuple[int, int]:
+        n = (b.end - b.start) // self.dp
+        return b.start + self.dp_rank * n, b.start + (self.dp_rank + 1) * n
+
+
+class DistributedDataParallel(nn.Module):
+    """Owns the flat buffers of a model chunk and overlaps gradient reduce-scatter with backward."""
+
+    def __init__(self, module: nn.Module, bucket_mb: float = 256.0, overlap_grad_reduce: bool = True,
+                 grad_dtype=torch.float32):
+        super().__init__()
+        self.module = module
+        self.overlap = overlap_grad_reduce
+        groups: Dict[Tuple[bool, bool], List[nn.Parameter]] = {}
+        seen = set()
+        plist = [p for p in module.parameters() if p.requires_grad]
+        for p in reversed(plist):  # backward produces gradients roughly in reverse registration order
+            if id(p) in seen:
+                continue
+            seen.add(id(p))
+            is_expert = bool(getattr(p, 'is_expert', False))
+            decay = p.dim() >= 2 and not getattr(p, 'no_weight_decay', False)
+            groups.setdefault((is_expert, decay), []).append(p)
+        self.buffers: Dict[Tuple[bool, bool], ParamAndGradBuffer] = {}
+        for key, params in groups.items():
+            dev, dt = params[0].device, params[0].dtype
+            same = [p for p in params if p.dtype == dt]
+            assert len(same) == len(params), 'all parameters of a buffer must share a dtype'
+            self.buffers[key] = ParamAndGradBuffer(params, 'edp' if key[0] else 'dp_cp', int(bucket_mb * 2**20), dev, dt,
+                                                   grad_dtype)
+        self.is_last_microbatch = True
+        self._comm_stream = torch.cuda.Stream() if torch.cuda.is_available() else None
+        self._hooks = []
+        for buf in self.buffers.values():
+            for p in buf.params:
+                p.grad_ready_hook = self._make_ready_hook(buf, p)
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_accum_hook(buf, p)))
+        self._reset_pending()
+
+    # ------------------------------------------------------------------ hooks
+    def _make_accum_hook(self, buf, p):
+        def hook(param):
+            if param.grad is not None:
+                param.main_grad.add_(param.grad.to(param.main_grad.dtype))
+                param.grad = None
+            param.grad_ready_hook()
+        return hook
+
+    def _make_ready_hook(self, buf: ParamAndGradBuffer, p):
+        def ready():
+            if not (self.overlap and self.is_last_microbatch and buf.dp > 1):
+                return
+            b = buf.param_to_bucket[p]
+            b.pending -= 1
+            if b.pending == 0:
+                self._launch_reduce(buf, b)
+        return ready
+
+    def _reset_pending(self):
+        for buf in self.buffers.values():
+            for b in buf.buckets:
+                b.pending = len(b.params)
+                b.work = None
+
+    def _needs_tp_reduce(self, b: Bucket) -> bool:
+        return ps.get_world_size('tp') > 1 and any(getattr(p, 'sequence_parallel', False) for p in b.params)
+
+    def _launch_reduce(self, buf: ParamAndGradBuffer, b: Bucket):
+        if buf.dp == 1 or b.work is not None:
+            return
+        if self._needs_tp_reduce(b):
+            return  # reduced in finish_grad_sync after the tensor-parallel all-reduce of flagged grads
+        g = buf.grad_data[b.start:b.end]
+        s, e = buf.shard_range(b)
+        out = buf.grad_data[s:e]
+        if g.is_cuda:
+            self._comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._comm_stream):
+                b.work = dist.reduce_scatter_tensor(out, g, group=buf.group, async_op=True)
+        else:
+            tmp = g.clone()
+            dist.all_reduce(tmp, group=buf.group)
+            out.copy_(tmp[s - b.start:e - b.start])
+            b.work = True
+
+    # ------------------------------------------------------------------ API
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+    def zero_grad_buffer(self):
+        for buf in self.buffers.values():
+            buf.grad_data.zero_()
+        self._reset_pending()
+
+    def _allreduce_sequence_parallel_grads(self):
+        if ps.get_world_size('tp') == 1:
+            return
+        ps_list = [p for buf in self.buffers.values() for p in buf.params if getattr(p, 'sequence_parallel', False)]
+        if not ps_list:
+            return
+        flat = torch.cat([p.main_grad.reshape(-1) for p in ps_list])
+        dist.all_reduce(flat, group=ps.get_group('tp'))
+        off = 0
+        for p in ps_list:
+            n = p.numel()
+            p.main_grad.copy_(flat[off:off + n].view(p.shape))
+            off += n
+
+    def finish_grad_sync(self):
+        """Blocks until every bucket's gradient shard is reduced (launching the ones not started yet)."""
+        self._allreduce_sequence_parallel_grads()
+        for buf in self.buffers.values():
+            if buf.dp == 1:
+                continue
+            for b in buf.buckets:
+                if b.work is None:
+                    g = buf.grad_data[b.start:b.end]
+                    s, e = buf.shard_range(b)
+                    if g.is_cuda:
+                        dist.reduce_scatter_tensor(buf.grad_data[s:e], g, group=buf.group)
+                    else:
+                        tmp = g.clone()
+                        dist.all_reduce(tmp, group=buf.group)
+                        buf.grad_data[s:e].copy_(tmp[s - b.start:e - b.start])
+                elif b.work is not True:
+                    b.work.wait()
+        if self._comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+
+    def state_dict(self, *a, **k):
+        return self.module.state_dict(*a, **k)
+
+    def load_state_dict(self, *a, **k):
+        return self.module.load_state_dict(*a, **k)
+
+
+class DistributedOptimizer:
+    """AdamW on the rank's slice of every bucket; fp32 master weights + moments are allocated only for it."""
+
+    def __init__(self, ddp_models: Iterable[DistributedDataParallel], lr: float = 1e-4, betas=(0.9, 0.95),
+                 eps: float = 1e-8, weight_decay: float = 0.1, clip_grad: float = 1.0):
+        self.models = list(ddp_models)
+        self.lr, self.betas, self.eps, self.weight_decay, self.clip_grad = lr, betas, eps, weight_decay, clip_grad
+        self.step_count = 0
+        self.shards = []  # (buf, bucket, decay, main, m, v)
+        for model in self.models:
+            for (is_expert, decay), buf in model.buffers.items():
+                for b in buf.buckets:
+                    s, e = buf.shard_range(b)
+                    main = buf.param_data[s:e].float().clone()
+                    self.shards.append((buf, b, decay, main, torch.zeros_like(main), torch.zeros_like(main)))
+        dev = self.shards[0][3].device if self.shards else torch.device('cpu')
+        self.device = dev
+        self._scalars = {True: torch.zeros(8, dtype=torch.float32, device=dev),
+                         False: torch.zeros(8, dtype=torch.float32, device=dev)}
+        self._sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._coef = torch.ones(1, dtype=torch.float32, device=dev)
+        self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.grad_norm = self._norm
+        self.grad_scale = 1.0
+
+    def zero_grad(self):
+        for m in self.models:
+            m.zero_grad_buffer()
+
+    def _use_cuda(self):
+        return self.device.type == 'cuda' and _lib.available()
+
+    def _grad_norm(self):
+        """Global L2 norm over every distinct gradient element (dp-sharded, tp-sharded, pp-sharded)."""
+        self._sq.zero_()
+        tp_rank0 = ps.get_rank_in('tp') == 0 if ps.get_world_size('tp') > 1 else True
+        for buf, b, decay, main, m, v in self.shards:
+            s, e = buf.shard_range(b)
+            g = buf.grad_data[s:e]
+            # replicated (non tensor-parallel) parameters are counted once per TP group
+            if not tp_rank0 and ps.get_world_size('tp') > 1:
+                dup = self._replicated_mask(buf, b, s, e)
+                if dup is not None:
+                    g = g * dup
+            if self._use_cuda() and g.dtype == torch.float32:
+                _lib.check_rc(_lib.lib().mcb_sqnorm_accum(_lib.ptr(g), _ll(g.numel()), _lib.ptr(self._sq),
+                                                          _lib.stream_ptr()), 'mcb_sqnorm_accum')
+            else:
+                self._sq += g.float().pow(2).sum()
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(self._sq)  # shards are disjoint across all ranks except the masked replicas
+        if self._use_cuda():
+            _lib.check_rc(_lib.lib().mcb_clip_coef(_lib.ptr(self._sq), _f(float(self.clip_grad or 0.0)),
+                                                   _lib.ptr(self._coef), _lib.ptr(self._norm), _lib.stream_ptr()),
+                          'mcb_clip_coef')
+        else:
+            self._norm.copy_(self._sq.sqrt())
+            if self.clip_grad and self.clip_grad > 0:
+                self._coef.copy_(torch.clamp(self.clip_grad / (self._norm + 1e-6), max=1.0))
+            else:
+                self._coef.fill_(1.0)
+
+    def _replicated_mask(self, buf, b, s, e):
+        mask = None
+        for p in b.params:
+            if getattr(p, 'tensor_model_parallel', False) or getattr(p, 'is_expert', False):
+                continue
+            ps_, pe = buf.param_range[p]
+            lo, hi = max(ps_, s), min(pe, e)
+            if lo < hi:
+                if mask is None:
+                    mask = torch.ones(e - s, dtype=torch.float32, device=buf.grad_data.device)
+                mask[lo - s:hi - s] = 0
+        return mask
+
+    @torch.no_grad()
+    def step(self):
+        for m in self.models:
+            m.finish_grad_sync()
+        self.step_count += 1
+        t = self.step_count
+        b1, b2 = self.betas
+        self._grad_norm()
+        for decay in (True, False):
+            # data-parallel averaging is folded into the gradient scale
+            self._scalars[decay].copy_(torch.tensor(
+                [self.lr, b1, b2, self.eps, self.weight_decay if decay else 0.0, 1 - b1**t, 1 - b2**t, self.grad_scale],
+                dtype=torch.float32), non_blocking=True)
+        for buf, b, decay, main, m, v in self.shards:
+            s, e = buf.shard_range(b)
+            g = buf.grad_data[s:e]
+            pshard = buf.param_data[s:e]
+            scale_dp = 1.0 / buf.dp
+            if self._use_cuda() and g.dtype == torch.float32 and pshard.dtype in (torch.bfloat16, torch.float32):
+                sc = self._scalars[decay]
+                if buf.dp > 1:
+                    sc = sc.clone()
+                    sc[7] *= scale_dp
+                rc = _lib.lib().mcb_adam_step(_lib.ptr(g), _lib.ptr(main), _lib.ptr(m), _lib.ptr(v), _lib.ptr(pshard),
+                                              _int(int(pshard.dtype == torch.bfloat16)), _ll(main.numel()),
+                                              _lib.ptr(sc), _lib.ptr(self._coef), None, _lib.stream_ptr())
+                _lib.check_rc(rc, 'mcb_adam_step')
+            else:
+                gf = g.float() * (self.grad_scale * scale_dp) * self._coef
+                m.mul_(b1).add_(gf, alpha=1 - b1)
+                v.mul_(b2).addcmul_(gf, gf, value=1 - b2)
+                denom = (v / (1 - b2**t)).sqrt_().add_(self.eps)
+                main.mul_(1 - self.lr * (self.weight_decay if decay else 0.0))
+                main.addcdiv_(m / (1 - b1**t), denom, value=-self.lr)
+                pshard.copy_(main.to(pshard.dtype))
+        # parameter all-gather, bucket by bucket (in place: every rank's slice sits at its final position)
+        for buf, b, *_ in self.shards:
+            if buf.dp > 1:
+                full = buf.param_data[b.start:b.end]
+                s, e = buf.shard_range(b)
+                if full.is_cuda:
+                    dist.all_gather_into_tensor(full, buf.param_data[s:e], group=buf.group)
+                else:
+                    parts = [torch.empty_like(buf.param_data[s:e]) for _ in range(buf.dp)]
+                    dist.all_gather(parts, buf.param_data[s:e].clone(), group=buf.group)
+                    full.copy_(torch.cat(parts))
+        return self._norm
+
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self) -> dict:
+        return {
+            'step': self.step_count,
+            'shards': [{'main': main, 'exp_avg': m, 'exp_avg_sq': v} for (_, _, _, main, m, v) in self.shards],
+            'hyper': {'lr': self.lr, 'betas': self.betas, 'eps': self.eps, 'weight_decay': self.weight_decay},
+        }
+
+    def load_state_dict(self, sd: dict):
+        self.step_count = int(sd['step'])
+        assert len(sd['shards']) == len(self.shards), 'optimizer shard layout changed'
+        for (_, _, _, main, m, v), s in zip(self.shards, sd['shards']):
+            main.copy_(s['main'])
+            m.copy_(s['exp_avg'])
+            v.copy_(s['exp_avg_sq'])

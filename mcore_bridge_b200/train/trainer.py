@@ -1,0 +1,176 @@
+"""Training entry point: build model + optimizer, run steps.  ``Trainer.train_step`` is the call a user makes.
+
+A step = ``num_microbatches`` forward/backward passes (activation recompute per config) with gradient
+accumulation in the fp32 buffers, then gradient reduce-scatter, clipping, fused AdamW on the local shards
+and parameter all-gather.  Inputs arrive as host tensors (pinned when possible) and are copied to the device
+inside the step; the loss comes back to the host at the end of the step.  Pipeline parallel runs go through
+``train/schedules.py``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..layers.context import PackedSeqParams
+from ..layers.moe import get_moe_aux_losses
+from ..models.register import get_mcore_model
+from ..ops.moe import MoEAuxLossAutoScaler
+from ..parallel import state as ps
+from ..utils.logger import get_logger
+from ..utils.megatron_utils import split_cp_inputs
+from .distributed_optimizer import DistributedDataParallel, DistributedOptimizer
+
+logger = get_logger()
+
+
+@dataclass
+class TrainConfig:
+    lr: float = 1e-4
+    betas: tuple = (0.9, 0.95)
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+    clip_grad: float = 1.0
+    bucket_mb: float = 256.0
+    overlap_grad_reduce: bool = True
+    init_seed: Optional[int] = 1234
+    init_std: float = 0.02
+
+
+@torch.no_grad()
+def init_weights(model: torch.nn.Module, std: float = 0.02, seed: Optional[int] = None):
+    """Random init: N(0, std) for matrices (tensor-parallel shards draw from the TP stream, replicated tensors
+    from the shared stream), norms at their identity value, biases zero."""
+    from ..parallel.random import get_rng_tracker, model_parallel_manual_seed
+    if seed is not None:
+        model_parallel_manual_seed(seed)
+    tracker = get_rng_tracker()
+    for name, p in model.named_parameters():
+        is_norm = ('layernorm' in name or 'layer_norm' in name or name.endswith('norm.weight') or
+                   'q_norm' in name or 'k_norm' in name)
+        if p.dim() < 2 and (is_norm or name.endswith('bias')):
+            if is_norm and name.endswith('weight'):
+                zero_centered = getattr(model, 'config', None) is not None and model.config.layernorm_zero_centered_gamma
+                p.fill_(0.0 if zero_centered else 1.0)
+            else:
+                p.zero_()
+            continue
+        if p.dim() < 2:
+            continue  # family-specific 1-D parameters (A_log, dt_bias ...) keep their constructor values
+        stream = 'expert-parallel-rng' if getattr(p, 'is_expert', False) else (
+            'model-parallel-rng' if getattr(p, 'tensor_model_parallel', False) else None)
+        if stream is not None and stream in tracker.states:
+            with tracker.fork(stream):
+                p.normal_(0.0, std)
+        else:
+            p.normal_(0.0, std)
+
+
+class Trainer:
+
+    def __init__(self, config, train_config: Optional[TrainConfig] = None, models: Optional[List] = None):
+        self.config = config
+        self.tc = train_config or TrainConfig()
+        self.models = models if models is not None else get_mcore_model(config)
+        if models is None and self.tc.init_seed is not None:
+            for i, m in enumerate(self.models):
+                init_weights(m, self.tc.init_std, self.tc.init_seed + i)
+        self.ddp = [DistributedDataParallel(m, self.tc.bucket_mb, self.tc.overlap_grad_reduce) for m in self.models]
+        self.optimizer = DistributedOptimizer(self.ddp, self.tc.lr, self.tc.betas, self.tc.eps, self.tc.weight_decay,
+                                              self.tc.clip_grad)
+        self.device = next(self.models[0].parameters()).device
+        self._copy_stream = torch.cuda.Stream() if self.device.type == 'cuda' else None
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.last_metrics: Dict[str, float] = {}
+
+    # ------------------------------------------------------------------ data movement
+    def _to_device(self, mb: Dict) -> Dict:
+        out = {}
+        for k, v in mb.items():
+            if isinstance(v, torch.Tensor):
+                self.h2d_bytes += v.numel() * v.element_size() if v.device.type == 'cpu' else 0
+                out[k] = v.to(self.device, non_blocking=True)
+            else:
+                out[k] = v
+        return out
+
+    def _prepare(self, mb: Dict) -> Dict:
+        """Device copy + context-parallel selection of this rank's zig-zag chunks."""
+        d = self._to_device(mb)
+        cp = ps.get_world_size('cp')
+        if cp > 1:
+            cu = d.get('cu_seqlens')
+            for k in ('input_ids', 'labels', 'position_ids', 'loss_mask'):
+                if d.get(k) is not None:
+                    d[k] = split_cp_inputs(d[k], cu, -1)
+        return d
+
+    # ------------------------------------------------------------------ one micro-batch
+    def forward_backward_microbatch(self, d: Dict, num_microbatches: int) -> torch.Tensor:
+        model = self.ddp[0]
+        psp = None
+        if d.get('cu_seqlens') is not None:
+            psp = PackedSeqParams(cu_seqlens_q=d['cu_seqlens'], cu_seqlens_kv=d['cu_seqlens'],
+                                  max_seqlen_q=d.get('max_seqlen'), max_seqlen_kv=d.get('max_seqlen'))
+        loss_tok = model(input_ids=d['input_ids'], position_ids=d.get('position_ids'),
+                         attention_mask=d.get('attention_mask'), labels=d['labels'], packed_seq_params=psp,
+                         loss_mask=d.get('loss_mask'))
+        mask = d.get('loss_mask')
+        if mask is None:
+            mask = torch.ones_like(loss_tok)
+        ntok = mask.sum()
+        cpn = ps.get_world_size('cp')
+        if cpn > 1:
+            ntok = ntok.clone()
+            dist.all_reduce(ntok, group=ps.get_group('cp'))
+        loss = (loss_tok * mask).sum() / ntok.clamp(min=1.0) / num_microbatches
+        MoEAuxLossAutoScaler.set_loss_scale(1.0 / num_microbatches)
+        loss.backward()
+        return loss.detach()
+
+    # ------------------------------------------------------------------ the public step
+    def train_step(self, microbatches: Iterable[Dict]) -> float:
+        """Runs one optimizer step over the given host micro-batches and returns the mean loss (host float)."""
+        mbs = list(microbatches)
+        n = len(mbs)
+        if ps.get_world_size('pp') > 1:
+            from .schedules import forward_backward_pipelining
+            total = forward_backward_pipelining(self, mbs)
+        else:
+            self.optimizer.zero_grad()
+            total = torch.zeros((), dtype=torch.float32, device=self.device)
+            nxt = self._prepare(mbs[0])
+            for i in range(n):
+                cur = nxt
+                for m in self.ddp:
+                    m.is_last_microbatch = (i == n - 1)
+                if i + 1 < n:
+                    nxt = self._prepare(mbs[i + 1])  # async H2D of the next micro-batch overlaps this one's compute
+                total += self.forward_backward_microbatch(cur, n)
+        grad_norm = self.optimizer.step()
+        self._after_step()
+        # loss summed over CP happens inside; average over data-parallel ranks for reporting
+        if ps.get_world_size('dp') > 1:
+            dist.all_reduce(total, group=ps.get_group('dp'))
+            total = total / ps.get_world_size('dp')
+        out = torch.stack([total.float(), grad_norm.float().reshape(())])
+        host = out.cpu()                       # the step's device->host read
+        self.d2h_bytes += out.numel() * out.element_size()
+        self.last_metrics = {'loss': float(host[0]), 'grad_norm': float(host[1])}
+        aux = get_moe_aux_losses()
+        for k, (s, c) in list(aux.items()):
+            self.last_metrics[k] = float(s) / max(c, 1)
+        aux.clear()
+        return self.last_metrics['loss']
+
+    def _after_step(self):
+        if self.config.moe_router_enable_expert_bias:
+            from ..layers.moe import TopKRouter
+            group = ps.get_group('tp_dp_cp') if ps.get_world_size('tp_dp_cp') > 1 else None
+            for m in self.models:
+                for mod in m.modules():
+                    if isinstance(mod, TopKRouter):
+                        mod.update_expert_bias(group)
