@@ -1,0 +1,78 @@
+"""TP=2 (+sequence parallel) on two gloo ranks equals the single-process model; export gathers shards."""
+import torch
+
+from dist_utils import run_ranks
+
+
+def _worker(rank, world, ckpt_dir, sp):
+    from mcore_bridge_b200 import ModelConfig, get_mcore_model, hf_to_mcore_config
+    from mcore_bridge_b200.parallel import state as ps
+    from mcore_bridge_b200.train.presets import hf_config
+    ps.initialize_model_parallel(tensor_model_parallel_size=2)
+    cfg = ModelConfig(**hf_to_mcore_config(hf_config('qwen3_tiny')), params_dtype=torch.float32,
+                      tensor_model_parallel_size=2, sequence_parallel=sp)
+    model = get_mcore_model(cfg)[0]
+    cfg.bridge.load_weights([model], ckpt_dir)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 1024, (2, 128), generator=g)
+    labels = torch.randint(0, 1024, (2, 128), generator=g)
+    loss = model(ids, labels=labels)
+    loss.mean().backward()
+    logits = model(ids, runtime_gather_output=True).detach()
+    exported = {k: v.clone() for k, v in cfg.bridge.export_weights([model])}
+    gq = model.decoder.layers[0].self_attention.linear_qkv.weight.grad.clone()
+    gn = model.decoder.layers[0].self_attention.linear_qkv.layer_norm_weight.grad.clone()
+    return loss.detach(), logits, exported, gq, gn
+
+
+def _setup(tmp):
+    from transformers import Qwen3ForCausalLM
+
+    from mcore_bridge_b200.train.presets import hf_config
+    torch.manual_seed(0)
+    hf = Qwen3ForCausalLM(hf_config('qwen3_tiny')).float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.normal_(0, 0.02) if p.dim() >= 2 else p.normal_(1.0, 0.1)
+    hf.save_pretrained(tmp)
+    return hf
+
+
+def _check(tmp_path, sp):
+    import torch.distributed as dist
+    d = str(tmp_path / 'ckpt')
+    hf = _setup(d)
+    res = run_ranks(_worker, 2, d, sp)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 1024, (2, 128), generator=g)
+    labels = torch.randint(0, 1024, (2, 128), generator=g)
+    ref_logits = hf(ids).logits
+    ref_loss = torch.nn.functional.cross_entropy(ref_logits.view(-1, 1024), labels.view(-1), reduction='none').view(2, 128)
+    ref_loss.mean().backward()
+    for r in range(2):
+        loss, logits, exported, gq, gn = res[r]
+        assert torch.allclose(loss, ref_loss.detach(), atol=1e-5)
+        assert torch.allclose(logits, ref_logits.detach(), atol=1e-5)
+        sd = hf.state_dict()
+        for k, v in exported.items():
+            assert torch.equal(v, sd[k]), k
+    # gradient of the TP-sharded qkv weight: rank shards concatenate to the interleaved full gradient
+    from mcore_bridge_b200.bridge.gpt_bridge import qkv_to_mcore
+    a = hf.model.layers[0].self_attn
+    full = qkv_to_mcore(a.q_proj.weight.grad, a.k_proj.weight.grad, a.v_proj.weight.grad, 2)
+    got = torch.cat([res[0][3], res[1][3]], dim=0)
+    assert torch.allclose(got, full, atol=1e-6)
+    # replicated norm weight: with SP each rank has a partial gradient that sums to the full one
+    gn_ref = hf.model.layers[0].input_layernorm.weight.grad
+    if sp:
+        assert torch.allclose(res[0][4] + res[1][4], gn_ref, atol=1e-6)
+    else:
+        assert torch.allclose(res[0][4], gn_ref, atol=1e-6)
+
+
+def test_tp2(tmp_path):
+    _check(tmp_path, sp=False)
+
+
+def test_tp2_sequence_parallel(tmp_path):
+    _check(tmp_path, sp=True)
