@@ -1,0 +1,725 @@
+// Tensor-parallel GEMMs fused with their collective over NVLink peer memory (one kernel each):
+//
+//   all-gather -> GEMM   C[M,N] = gather(A_shards)[M,K] . B^T       (column-parallel fwd, row-parallel dgrad)
+//       A few "copy CTAs" pull the peers' shards with bulk (TMA) copies through shared memory into a local
+//       gathered buffer and publish a flag per 128-row block; the GEMM CTAs start on the local shard and
+//       consume remote blocks in arrival order, so the transfer hides behind the math tile by tile.
+//
+//   GEMM -> reduce-scatter   out[M/w, N] = sum_ranks (A . B^T)[rows of this rank]   (row-parallel fwd, column dgrad)
+//       Each epilogue stores its bf16 partial tile straight into the staging buffer of the rank that owns the
+//       rows (peer stores over NVLink) and bumps a counter there; when a CTA runs out of tiles it turns to
+//       reducing the rows this rank owns as their counters fill.
+//
+// No TMA multicast anywhere; remote data is only touched by plain bulk copies, ld/st and red.
+// Every cross-rank wait is bounded and reports through the status word.
+#include <cstdlib>
+
+#include "../common/host_utils.cuh"
+#include "../gemm/gemm_sm100.cuh"
+
+using namespace mcb;
+
+namespace {
+
+constexpr int MAX_WORLD = 8;
+// flag-region layout (uint32 indices)
+constexpr int F_READY = 0;        // [world]   AG: shard of rank i is ready (epoch)
+constexpr int F_BLOCK = 64;       // [<=4096]  AG: gathered 128-row block landed (epoch)
+constexpr int F_DONE = 0;         // [world]   RS: rank i finished reducing (epoch)
+constexpr int F_TICKET = 32;      // RS: CTA completion ticket
+constexpr int F_CNT = 64;         // [2][2048] RS: tiles pushed per row block, per epoch parity
+constexpr int F_CNT_STRIDE = 2048;
+
+constexpr int COPY_STAGES = 12;
+constexpr int COPY_CHUNK = 16384;
+constexpr int COPY_STORES_IN_FLIGHT = 3;
+
+struct CommGemmParams {
+  int M, N, K;
+  int world, rank, epoch;
+  int rows_per_rank;
+  int copy_ctas;
+  const void* peer_shard[MAX_WORLD];
+  void* gathered;
+  uint32_t* peer_flags[MAX_WORLD];
+  void* C;
+  long long ldc;
+  const void* bias;
+  void* peer_stage[MAX_WORLD];
+  void* out;
+  long long ld_out;
+  int* status;
+  int debug;  // timing experiments only (MCB200_RS_DEBUG): 1 skip reduce phase, 2 push to self, 4 skip stores
+};
+
+// GEMM -> reduce-scatter: one TMA store descriptor per destination rank's staging buffer, viewed as
+// [world * rows_per_rank, N] bf16 with 128-byte swizzled 64-column boxes
+struct RsMaps {
+  CUtensorMap stage[MAX_WORLD];
+};
+constexpr int RS_SLAB_COLS = 64;
+constexpr int RS_SLAB_BYTES = GEMM_BM * RS_SLAB_COLS * 2;  // 16 KiB
+
+struct CommSched {
+  int tiles_m, tiles_n, total, bps, BN, world, rank, first_step;
+  __device__ CommSched(const CommGemmParams& p, int bn, int first) : BN(bn), world(p.world), rank(p.rank), first_step(first) {
+    tiles_m = p.M / GEMM_BM;
+    tiles_n = (p.N + bn - 1) / bn;
+    total = tiles_m * tiles_n;
+    bps = p.rows_per_rank / GEMM_BM;
+  }
+  // logical m index j -> (owning shard, block inside the shard); step 0 is `first_step` ranks after our own
+  __device__ void get(int t, int& shard, int& blk, int& n0, int& step) const {
+    const int G = bps < 8 ? bps : 8;
+    const int per_sg = G * tiles_n;
+    const int sg = t / per_sg;
+    const int first_m = sg * G;
+    const int gsize = min(tiles_m - first_m, G);
+    const int r = t - sg * per_sg;
+    const int j = first_m + r % gsize;
+    n0 = (r / gsize) * BN;
+    step = j / bps;
+    blk = j - step * bps;
+    shard = (rank + first_step + step) % world;
+  }
+};
+
+// ----------------------------------------------------------------------------------------------------------
+// shared mainloop pieces
+// ----------------------------------------------------------------------------------------------------------
+template <int BN>
+struct Pipe {
+  using L = GemmSmem<BN>;
+  uint8_t* smem;
+  uint64_t *full_bar, *empty_bar, *tfull_bar, *tempty_bar;
+  uint32_t* tmem_slot;
+  volatile int* abort_flag;
+  __device__ Pipe(uint8_t* raw) {
+    smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::STAGES * L::STAGE_BYTES);
+    full_bar = bars;
+    empty_bar = bars + L::STAGES;
+    tfull_bar = bars + 2 * L::STAGES;
+    tempty_bar = bars + 2 * L::STAGES + 2;
+    tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * L::STAGES + 4);
+    abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  }
+  __device__ void init() {
+    *abort_flag = 0;
+    for (int s = 0; s < L::STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tfull_bar[a]), 1);
+      mbar_init(smem_u32(&tempty_bar[a]), 4);
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+};
+
+template <int BN, bool B_MN>
+__device__ __forceinline__ void issue_mma_tile(Pipe<BN>& P, uint32_t d_tmem, int K, uint32_t& it, int* status, bool& ok) {
+  using L = GemmSmem<BN>;
+  constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, false, B_MN);
+  bool first = true;
+  for (int k = 0; k < K; k += GEMM_BK, ++it) {
+    const uint32_t s = it % L::STAGES, ph = (it / L::STAGES) & 1;
+    if (!mbar_wait(smem_u32(&P.full_bar[s]), ph, P.abort_flag, status, ST_TIMEOUT_FULL)) {
+      ok = false;
+      return;
+    }
+    tc_fence_after();
+    const uint32_t sa = smem_u32(P.smem + s * L::STAGE_BYTES);
+    const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+    for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+      uint64_t ad = make_smem_desc_sw128(sa + kk * 32, 16, 1024);
+      uint64_t bd = B_MN ? make_smem_desc_sw128(sb + kk * 2048, 8192, 1024) : make_smem_desc_sw128(sb + kk * 32, 16, 1024);
+      umma_f16(d_tmem, ad, bd, idesc, first ? 0u : 1u);
+      first = false;
+    }
+    umma_commit(smem_u32(&P.empty_bar[s]));
+  }
+}
+
+template <int BN, bool B_MN>
+__device__ __forceinline__ bool load_tile(Pipe<BN>& P, const CUtensorMap* ta, const CUtensorMap* tb, int a_row, int n0,
+                                          int K, uint32_t& it, int* status) {
+  using L = GemmSmem<BN>;
+  for (int k = 0; k < K; k += GEMM_BK, ++it) {
+    const uint32_t s = it % L::STAGES, ph = (it / L::STAGES) & 1;
+    if (!mbar_wait(smem_u32(&P.empty_bar[s]), ph ^ 1, P.abort_flag, status, ST_TIMEOUT_EMPTY)) return false;
+    const uint32_t fb = smem_u32(&P.full_bar[s]);
+    mbar_expect_tx(fb, L::STAGE_BYTES);
+    const uint32_t sa = smem_u32(P.smem + s * L::STAGE_BYTES);
+    const uint32_t sb = sa + L::A_BYTES;
+    tma_load_2d(sa, ta, k, a_row, fb);
+    if (!B_MN) {
+      tma_load_2d(sb, tb, k, n0, fb);
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, tb, n0 + j * 64, k, fb);
+    }
+  }
+  return true;
+}
+
+template <int BN>
+__device__ __forceinline__ void drain_loads(Pipe<BN>& P, uint32_t it) {
+  using L = GemmSmem<BN>;
+  uint32_t first = it > L::STAGES ? it - L::STAGES : 0;
+  for (uint32_t j = first; j < it; ++j) {
+    const uint32_t s = j % L::STAGES, ph = (j / L::STAGES) & 1;
+    uint64_t t0 = globaltimer_ns();
+    while (!mbar_try_wait(smem_u32(&P.full_bar[s]), ph)) {
+      if (globaltimer_ns() - t0 > 200000000ull) break;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------------
+// all-gather -> GEMM
+// ----------------------------------------------------------------------------------------------------------
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_constant__ CUtensorMap tmap_a_gath,
+               const __grid_constant__ CUtensorMap tmap_b, const CommGemmParams p) {
+  using L = GemmSmem<BN>;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t* lflags = p.peer_flags[p.rank];
+  const uint32_t epoch = (uint32_t)p.epoch;
+  const int bps = p.rows_per_rank / GEMM_BM;
+
+  if ((int)blockIdx.x < p.copy_ctas) {
+    // =================================================================== copy CTA
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + COPY_STAGES * COPY_CHUNK);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + COPY_STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * COPY_STAGES);
+    if (threadIdx.x == 0) {
+      *abort_flag = 0;
+      for (int s = 0; s < COPY_STAGES; ++s) {
+        mbar_init(smem_u32(&full[s]), 1);
+        mbar_init(smem_u32(&empty[s]), 1);
+      }
+      fence_barrier_init();
+      fence_proxy_async_smem();
+    }
+    __syncthreads();
+    // announce that this rank's shard (written by the preceding kernel in stream order) may be read
+    if (blockIdx.x == 0 && (int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
+      fence_acq_rel_sys();
+      st_release_sys(p.peer_flags[threadIdx.x] + F_READY + p.rank, epoch);
+    }
+    const long long block_bytes = (long long)GEMM_BM * p.K * 2;
+    const int chunks_per_block = (int)((block_bytes + COPY_CHUNK - 1) / COPY_CHUNK);
+    const int nblocks = p.world * bps;  // remote shards in ring order, then the local shard
+    if (warp == 0 && lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int i = blockIdx.x; i < nblocks && ok; i += p.copy_ctas) {
+        const int step = i / bps, blk = i - step * bps;
+        const int s = step < p.world - 1 ? (p.rank + 1 + step) % p.world : p.rank;
+        if (s != p.rank && !wait_flag<SCOPE_SYS>(lflags + F_READY + s, epoch, false, abort_flag, p.status)) break;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.peer_shard[s]) + (long long)blk * block_bytes;
+        for (int c = 0; c < chunks_per_block; ++c, ++it) {
+          const uint32_t st = it % COPY_STAGES, ph = (it / COPY_STAGES) & 1;
+          if (!mbar_wait(smem_u32(&empty[st]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const long long off = (long long)c * COPY_CHUNK;
+          const uint32_t bytes = (uint32_t)min((long long)COPY_CHUNK, block_bytes - off);
+          mbar_expect_tx(smem_u32(&full[st]), bytes);
+          bulk_load_1d(smem_u32(ring + st * COPY_CHUNK), src + off, bytes, smem_u32(&full[st]));
+        }
+      }
+      // drain: loads this thread issued must land before the CTA exits
+      uint32_t first = it > COPY_STAGES ? it - COPY_STAGES : 0;
+      for (uint32_t j = first; j < it; ++j) {
+        const uint32_t st = j % COPY_STAGES, ph = (j / COPY_STAGES) & 1;
+        uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(smem_u32(&full[st]), ph)) {
+          if (globaltimer_ns() - t0 > 200000000ull) break;
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int i = blockIdx.x; i < nblocks && ok; i += p.copy_ctas) {
+        const int step = i / bps, blk = i - step * bps;
+        const int s = step < p.world - 1 ? (p.rank + 1 + step) % p.world : p.rank;
+        const int gblock = s * bps + blk;
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.gathered) + (long long)gblock * block_bytes;
+        const uint32_t block_first = it;
+        for (int c = 0; c < chunks_per_block; ++c, ++it) {
+          const uint32_t st = it % COPY_STAGES, ph = (it / COPY_STAGES) & 1;
+          if (!mbar_wait(smem_u32(&full[st]), ph, abort_flag, p.status, ST_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          const long long off = (long long)c * COPY_CHUNK;
+          const uint32_t bytes = (uint32_t)min((long long)COPY_CHUNK, block_bytes - off);
+          bulk_store_1d(dst + off, smem_u32(ring + st * COPY_CHUNK), bytes);
+          tma_store_commit();
+          // stores older than the most recent few have finished reading their stage: hand it back
+          tma_store_wait_read<COPY_STORES_IN_FLIGHT>();
+          if (it >= block_first + COPY_STORES_IN_FLIGHT)
+            mbar_arrive(smem_u32(&empty[(it - COPY_STORES_IN_FLIGHT) % COPY_STAGES]));
+        }
+        tma_store_wait<0>();  // the whole block is in global memory
+        if (ok) {
+          const uint32_t done = it;
+          const uint32_t from = done >= block_first + COPY_STORES_IN_FLIGHT ? done - COPY_STORES_IN_FLIGHT : block_first;
+          for (uint32_t j = from; j < done; ++j) mbar_arrive(smem_u32(&empty[j % COPY_STAGES]));
+          fence_proxy_async_all();
+          st_release_gpu(lflags + F_BLOCK + gblock, epoch);
+        }
+      }
+      tma_store_wait<0>();
+    }
+    return;
+  }
+
+  // ===================================================================== GEMM CTA
+  Pipe<BN> P(smem_raw);
+  if (threadIdx.x == 0) {
+    P.init();
+    prefetch_tensormap(&tmap_a_local);
+    prefetch_tensormap(&tmap_a_gath);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(P.tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *P.tmem_slot;
+  CommSched sched(p, BN, 0);
+  const int g0 = blockIdx.x - p.copy_ctas, gs = gridDim.x - p.copy_ctas;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      int seen_block = -1;
+      for (int t = g0; t < sched.total; t += gs) {
+        int shard, blk, n0, step;
+        sched.get(t, shard, blk, n0, step);
+        const int gblock = shard * bps + blk;
+        const CUtensorMap* ta = &tmap_a_local;
+        int a_row = blk * GEMM_BM;
+        if (shard != p.rank) {
+          if (gblock != seen_block) {
+            if (!wait_flag<SCOPE_GPU>(lflags + F_BLOCK + gblock, epoch, false, P.abort_flag, p.status)) break;
+            fence_proxy_async_all();
+            seen_block = gblock;
+          }
+          ta = &tmap_a_gath;
+          a_row = gblock * GEMM_BM;
+        }
+        if (!load_tile<BN, B_MN>(P, ta, &tmap_b, a_row, n0, p.K, it, p.status)) break;
+      }
+      drain_loads<BN>(P, it);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int t = g0; t < sched.total && ok; t += gs, ++lt) {
+        const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+        if (!mbar_wait(smem_u32(&P.tempty_bar[acc]), aph ^ 1, P.abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        issue_mma_tile<BN, B_MN>(P, tmem_base + acc * BN, p.K, it, p.status, ok);
+        if (ok) umma_commit(smem_u32(&P.tfull_bar[acc]));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t lt = 0;
+    for (int t = g0; t < sched.total; t += gs, ++lt) {
+      int shard, blk, n0, step;
+      sched.get(t, shard, blk, n0, step);
+      const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+      if (!mbar_wait(smem_u32(&P.tfull_bar[acc]), aph, P.abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      const long long row = (long long)(shard * bps + blk) * GEMM_BM + q * 32 + lane;
+      __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc;
+      const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+#pragma unroll 1
+      for (int cc = 0; cc < BN; cc += 32) {
+        if (n0 + cc >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + cc, r);
+        tmem_ld_wait();
+        const int col0 = n0 + cc;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += __bfloat162float(bias[col0 + j]);
+        }
+        if (col0 + 32 <= p.N) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(v[j], v[j + 1]);
+            o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+            o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+            o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+            *reinterpret_cast<uint4*>(crow + col0 + j) = o;
+          }
+        } else {
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) crow[col0 + j] = __float2bfloat16(v[j]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&P.tempty_bar[acc]));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------------
+// GEMM -> reduce-scatter
+// ----------------------------------------------------------------------------------------------------------
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ RsMaps maps, const CommGemmParams p) {
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t* lflags = p.peer_flags[p.rank];
+  const uint32_t epoch = (uint32_t)p.epoch;
+  const int bps = p.rows_per_rank / GEMM_BM;
+  const int parity = p.epoch & 1;
+  Pipe<BN> P(smem_raw);
+  if (threadIdx.x == 0) {
+    P.init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(P.tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *P.tmem_slot;
+  CommSched sched(p, BN, 1);  // start with the rows of rank+1, finish with our own
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < sched.total; t += gridDim.x) {
+        int shard, blk, n0, step;
+        sched.get(t, shard, blk, n0, step);
+        if (!load_tile<BN, B_MN>(P, &tmap_a, &tmap_b, (shard * bps + blk) * GEMM_BM, n0, p.K, it, p.status)) break;
+      }
+      drain_loads<BN>(P, it);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x, ++lt) {
+        const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+        if (!mbar_wait(smem_u32(&P.tempty_bar[acc]), aph ^ 1, P.abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        issue_mma_tile<BN, B_MN>(P, tmem_base + acc * BN, p.K, it, p.status, ok);
+        if (ok) umma_commit(smem_u32(&P.tfull_bar[acc]));
+      }
+    }
+  } else {
+    // Epilogue: TMEM -> registers -> bf16 -> 128B-swizzled shared slab -> TMA store into the owner's staging
+    // buffer (coalesced NVLink writes).  A tile's counter is bumped one tile late, after the bulk stores that
+    // carried it are known to be complete, so the completion latency hides behind the next tile.
+    const int q = warp & 3;
+    const bool issuer = (warp == 2 && lane == 0);
+    uint8_t* slab_base = P.smem + GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + 1024;
+    uint32_t lt = 0;
+    uint32_t verified = 0;  // bit s: rank s has released the staging half we are about to write
+    int pend_shard = -1, pend_blk = 0;  // tile whose counter increment is still owed
+    uint32_t slab_ctr = 0;
+    for (int t = blockIdx.x; t < sched.total; t += gridDim.x, ++lt) {
+      int shard, blk, n0, step;
+      sched.get(t, shard, blk, n0, step);
+      const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+      if (!mbar_wait(smem_u32(&P.tfull_bar[acc]), aph, P.abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      if (!(verified & (1u << shard))) {
+        // the owner must have finished reducing the call that last used this staging half (two calls ago)
+        if (p.epoch > 2 && shard != p.rank) {
+          if (!wait_flag<SCOPE_SYS>(lflags + F_DONE + shard, epoch - 2, false, P.abort_flag, p.status)) break;
+        }
+        verified |= 1u << shard;
+      }
+      const int srow0 = p.rank * p.rows_per_rank + blk * GEMM_BM;  // row of this tile in the owner's staging view
+      const int r_local = q * 32 + lane;
+      int slabs_issued = 0;
+#pragma unroll 1
+      for (int cc = 0; cc < BN; cc += RS_SLAB_COLS, ++slab_ctr) {
+        if (n0 + cc >= p.N) break;
+        uint8_t* slab = slab_base + (slab_ctr & 1) * RS_SLAB_BYTES;
+        if (issuer) tma_store_wait_read<1>();  // the store that last used this slab has finished reading it
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int h = 0; h < RS_SLAB_COLS / 32; ++h) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + cc + h * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+            const int chunk = (h * 32 + j) >> 3;                 // 16-byte chunk inside the 128-byte row
+            const int sw = chunk ^ (r_local & 7);                // 128-byte swizzle
+            *reinterpret_cast<uint4*>(slab + r_local * 128 + sw * 16) = o;
+          }
+        }
+        if (cc + RS_SLAB_COLS >= BN || n0 + cc + RS_SLAB_COLS >= p.N) {
+          // last slab of the tile: the accumulator can go back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&P.tempty_bar[acc]));
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer) {
+          if (!(p.debug & 4)) tma_store_2d(&maps.stage[(p.debug & 2) ? p.rank : shard], smem_u32(slab), n0 + cc, srow0);
+          tma_store_commit();
+        }
+        ++slabs_issued;
+      }
+      if (issuer) {
+        if (pend_shard >= 0) {
+          // everything but this tile's stores is complete -> the previous tile may be published
+          if (slabs_issued >= 4) tma_store_wait<4>();
+          else if (slabs_issued == 3) tma_store_wait<3>();
+          else if (slabs_issued == 2) tma_store_wait<2>();
+          else tma_store_wait<1>();
+          fence_proxy_async_all();
+          fence_acq_rel_sys();
+          red_release_sys_add(p.peer_flags[pend_shard] + F_CNT + parity * F_CNT_STRIDE + pend_blk, 1u);
+        }
+        pend_shard = shard;
+        pend_blk = blk;
+      }
+    }
+    if (issuer) {
+      tma_store_wait<0>();
+      if (pend_shard >= 0) {
+        fence_proxy_async_all();
+        fence_acq_rel_sys();
+        red_release_sys_add(p.peer_flags[pend_shard] + F_CNT + parity * F_CNT_STRIDE + pend_blk, 1u);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+
+  // ------------------------------------------------------------------ reduce the rows this rank owns
+  if (!*P.abort_flag && !(p.debug & 1)) {
+    const uint32_t want = (uint32_t)(p.world * sched.tiles_n);
+    const int nwarps = GEMM_THREADS / 32;
+    const int segs = (p.N + 1023) / 1024;               // a warp iteration covers one row x 1024 columns
+    const long long units = (long long)p.rows_per_rank * segs;
+    const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.peer_stage[p.rank]);
+    int ready_blk = -1;
+    bool ok = true;
+    // blocks are walked in order, so early blocks (pushed first by every peer) are reduced while late ones land
+    for (long long u = (long long)blockIdx.x * nwarps + warp; u < units && ok; u += (long long)gridDim.x * nwarps) {
+      const long long row = u / segs;
+      const int seg = (int)(u - row * segs);
+      const int blk = (int)(row / GEMM_BM);
+      if (blk != ready_blk) {
+        int good = 1;
+        if (lane == 0)
+          good = wait_flag<SCOPE_SYS>(lflags + F_CNT + parity * F_CNT_STRIDE + blk, want, true, P.abort_flag, p.status);
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) {
+          ok = false;
+          break;
+        }
+        ready_blk = blk;
+      }
+      float acc[4][8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
+      const int c0 = seg * 1024 + lane * 8;
+      for (int s0 = 0; s0 < p.world; s0 += 4) {
+        uint4 raw[4][4];
+#pragma unroll
+        for (int ss = 0; ss < 4; ++ss) {
+          const int src = s0 + ss;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int c = c0 + k * 256;
+            if (src < p.world && c < p.N)
+              raw[ss][k] = __ldcs(reinterpret_cast<const uint4*>(stage + ((long long)src * p.rows_per_rank + row) * p.N + c));
+            else
+              raw[ss][k] = make_uint4(0, 0, 0, 0);
+          }
+        }
+#pragma unroll
+        for (int ss = 0; ss < 4; ++ss)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[ss][k]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float2 f = __bfloat1622float2(h[e]);
+              acc[k][2 * e] += f.x;
+              acc[k][2 * e + 1] += f.y;
+            }
+          }
+      }
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ld_out;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k * 256;
+        if (c < p.N) {
+          uint4 o;
+          o.x = pack_bf16x2(acc[k][0], acc[k][1]);
+          o.y = pack_bf16x2(acc[k][2], acc[k][3]);
+          o.z = pack_bf16x2(acc[k][4], acc[k][5]);
+          o.w = pack_bf16x2(acc[k][6], acc[k][7]);
+          *reinterpret_cast<uint4*>(orow + c) = o;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // the last CTA to get here resets the counters of this parity and tells every peer we are done
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t ticket = atomicAdd(lflags + F_TICKET, 1u);
+    if (ticket == gridDim.x - 1) {
+      for (int b = 0; b < bps; ++b) lflags[F_CNT + parity * F_CNT_STRIDE + b] = 0;
+      lflags[F_TICKET] = 0;
+      fence_acq_rel_sys();
+      for (int s = 0; s < p.world; ++s)
+        if (s != p.rank) st_release_sys(p.peer_flags[s] + F_DONE + p.rank, epoch);
+    }
+  }
+}
+
+template <typename Kern>
+cudaError_t set_smem(Kern k, int bytes) {
+  return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+}  // namespace
+
+extern "C" {
+
+// flags_ptrs / shard_ptrs / stage_ptrs: host arrays of `world` device pointers (index = group rank)
+int mcb_ag_gemm_bf16(const void* const* shard_ptrs, void* const* flag_ptrs, void* gathered, const void* B, long long b_inner,
+                     long long b_outer, long long ldb, int b_mn, void* C, long long ldc, const void* bias, int M, int N,
+                     int K, int world, int rank, int epoch, int copy_ctas, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (world < 2 || world > MAX_WORLD || M % (world * GEMM_BM) || K % 8 || N % 8) return -2;
+  const int rows = M / world;
+  if (M / GEMM_BM > 4096 - F_BLOCK) return -3;
+  constexpr int BN = 256;
+  int sms = device_sm_count();
+  if (copy_ctas <= 0) copy_ctas = 12;
+  if (copy_ctas >= sms) return -4;
+  CUtensorMap ta_l, ta_g, tb;
+  int rc = make_tmap_2d_bf16(&ta_l, shard_ptrs[rank], K, rows, K, GEMM_BK, GEMM_BM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&ta_g, gathered, K, M, K, GEMM_BK, GEMM_BM);
+  if (rc) return rc;
+  rc = b_mn ? make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, 64, GEMM_BK)
+            : make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, GEMM_BK, BN);
+  if (rc) return rc;
+  CommGemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.world = world; p.rank = rank; p.epoch = epoch; p.rows_per_rank = rows;
+  p.copy_ctas = copy_ctas;
+  for (int i = 0; i < world; ++i) {
+    p.peer_shard[i] = shard_ptrs[i];
+    p.peer_flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  p.gathered = gathered; p.C = C; p.ldc = ldc; p.bias = bias; p.status = status;
+  const int smem = GemmSmem<BN>::TOTAL;
+  static bool cfg[2] = {false, false};
+  cudaError_t e;
+  if (b_mn) {
+    if (!cfg[1]) { if ((e = set_smem(ag_gemm_kernel<BN, true>, smem)) != cudaSuccess) return (int)e; cfg[1] = true; }
+    ag_gemm_kernel<BN, true><<<sms, GEMM_THREADS, smem, stream>>>(ta_l, ta_g, tb, p);
+  } else {
+    if (!cfg[0]) { if ((e = set_smem(ag_gemm_kernel<BN, false>, smem)) != cudaSuccess) return (int)e; cfg[0] = true; }
+    ag_gemm_kernel<BN, false><<<sms, GEMM_THREADS, smem, stream>>>(ta_l, ta_g, tb, p);
+  }
+  return (int)cudaGetLastError();
+}
+
+int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_inner, long long b_outer, long long ldb,
+                     int b_mn, void* const* stage_ptrs, void* const* flag_ptrs, void* out, long long ld_out, int M, int N,
+                     int K, int world, int rank, int epoch, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (world < 2 || world > MAX_WORLD || M % (world * GEMM_BM) || K % 8 || N % 8 || lda % 8) return -2;
+  const int rows = M / world;
+  if (rows / GEMM_BM > F_CNT_STRIDE) return -3;
+  constexpr int BN = 256;
+  int sms = device_sm_count();
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, GEMM_BK, GEMM_BM);
+  if (rc) return rc;
+  rc = b_mn ? make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, 64, GEMM_BK)
+            : make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, GEMM_BK, BN);
+  if (rc) return rc;
+  CommGemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.world = world; p.rank = rank; p.epoch = epoch; p.rows_per_rank = rows;
+  RsMaps maps;
+  for (int i = 0; i < world; ++i) {
+    p.peer_stage[i] = stage_ptrs[i];
+    p.peer_flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
+    rc = make_tmap_2d_bf16(&maps.stage[i], stage_ptrs[i], N, (long long)M, N, RS_SLAB_COLS, GEMM_BM);
+    if (rc) return rc;
+  }
+  for (int i = world; i < MAX_WORLD; ++i) maps.stage[i] = maps.stage[0];
+  p.out = out; p.ld_out = ld_out; p.status = status;
+  { const char* d = getenv("MCB200_RS_DEBUG"); p.debug = d ? atoi(d) : 0; }
+  const int smem = GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + 1024 + 2 * RS_SLAB_BYTES + 1024;
+  long long tiles = (long long)(M / GEMM_BM) * ((N + BN - 1) / BN);
+  int grid = (int)(tiles < sms ? tiles : sms);
+  static bool cfg[2] = {false, false};
+  cudaError_t e;
+  if (b_mn) {
+    if (!cfg[1]) { if ((e = set_smem(gemm_rs_kernel<BN, true>, smem)) != cudaSuccess) return (int)e; cfg[1] = true; }
+    gemm_rs_kernel<BN, true><<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, maps, p);
+  } else {
+    if (!cfg[0]) { if ((e = set_smem(gemm_rs_kernel<BN, false>, smem)) != cudaSuccess) return (int)e; cfg[0] = true; }
+    gemm_rs_kernel<BN, false><<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, maps, p);
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

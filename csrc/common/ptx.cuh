@@ -215,3 +215,65 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 }  // namespace mcb
+
+// ---------------------------------------------------------------- cross-CTA / cross-GPU flags and bulk copies
+namespace mcb {
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+// orders generic-proxy and async-proxy (TMA) accesses to the same memory
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// 1-D bulk copy global -> shared (source may be a peer GPU's memory; never multicast)
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+
+enum FlagScope { SCOPE_GPU = 0, SCOPE_SYS = 1 };
+
+// Bounded wait until *p >= want (flags are monotonically increasing epochs) or, with `exact`, *p == want.
+template <int SCOPE>
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, bool exact, volatile int* abort_flag,
+                                          int* status) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0; it < 0x7fffffffu; ++it) {
+    const uint32_t v = SCOPE == SCOPE_SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+    if (exact ? (v == want) : (int32_t(v - want) >= 0)) return true;
+    if ((it & 0x3fu) == 0x3fu) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > MCB_WAIT_LIMIT_NS) break;
+    }
+    __nanosleep(64);
+  }
+  *abort_flag = 1;
+  if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+  return false;
+}
+
+}  // namespace mcb

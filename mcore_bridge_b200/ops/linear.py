@@ -66,27 +66,27 @@ class _LinearFn(torch.autograd.Function):
         ctx.has_bias = bias is not None
         if spec.mode == 'column' and spec.sequence_parallel and n > 1:
             fc = _fused()
-            if fc.enabled(x2, weight, spec.group):
-                y, x_full = fc.all_gather_gemm(x2, weight, bias, spec.group)
+            res = fc.all_gather_gemm(x2, weight, bias, spec.group) if fc.enabled(x2, weight, spec.group) else None
+            if res is not None:
+                y, x_full = res
             else:
                 x_full = M.all_gather_dim0(x2, spec.group)
                 y = gemm.mm_nt(x_full, weight, bias=bias)
-            ctx.save_for_backward(x2, weight)  # re-gather in backward rather than hold [T, K]
-            del x_full
+            # the gathered input feeds the weight gradient; under per-layer recompute it lives only briefly
+            ctx.save_for_backward(x_full, weight)
             return y
         if spec.mode == 'row' and n > 1:
             if spec.sequence_parallel:
                 fc = _fused()
-                if fc.enabled(x2, weight, spec.group):
-                    y = fc.gemm_reduce_scatter(x2, weight, spec.group)
-                else:
+                y = fc.gemm_reduce_scatter(x2, weight, spec.group) if fc.enabled(x2, weight, spec.group) else None
+                if y is None:
                     y = M.reduce_scatter_dim0(gemm.mm_nt(x2, weight), spec.group)
             else:
                 y = M.all_reduce(gemm.mm_nt(x2, weight), spec.group)
             if bias is not None:
                 y = y + bias
             ctx.save_for_backward(x2, weight)
-            return y if not spec.sequence_parallel else y
+            return y
         y = gemm.mm_nt(x2, weight, bias=bias)
         ctx.save_for_backward(x2, weight)
         return y.view(*x.shape[:-1], weight.shape[0])
@@ -103,13 +103,11 @@ class _LinearFn(torch.autograd.Function):
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1] and not spec.skip_weight_grad
         dx = dw = db = None
         if spec.mode == 'column' and spec.sequence_parallel and n > 1:
-            fc = _fused()
-            fused = fc.enabled(x2, weight, spec.group)
-            x_full = fc.all_gather(x2, spec.group) if fused else M.all_gather_dim0(x2, spec.group)
+            x_full = x2  # saved gathered input
             if need_dx:
-                if fused:
-                    dx = fc.gemm_reduce_scatter_nn(dy2, weight, spec.group)
-                else:
+                fc = _fused()
+                dx = fc.gemm_reduce_scatter_nn(dy2, weight, spec.group) if fc.enabled(dy2, weight, spec.group) else None
+                if dx is None:
                     dx = M.reduce_scatter_dim0(gemm.mm_nn(dy2, weight), spec.group)
             if need_dw:
                 dw = _weight_grad(weight, dy2, x_full)
@@ -119,8 +117,11 @@ class _LinearFn(torch.autograd.Function):
         if spec.mode == 'row' and n > 1:
             if spec.sequence_parallel:
                 fc = _fused()
-                if fc.enabled(x2, weight, spec.group) and need_dx:
-                    dx, dy_full = fc.all_gather_gemm_nn(dy2, weight, spec.group)
+                res = None
+                if need_dx and fc.enabled(dy2, weight, spec.group):
+                    res = fc.all_gather_gemm_nn(dy2, weight, spec.group)
+                if res is not None:
+                    dx, dy_full = res
                 else:
                     dy_full = M.all_gather_dim0(dy2, spec.group)
                     if need_dx:
