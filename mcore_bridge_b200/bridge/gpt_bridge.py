@@ -552,7 +552,25 @@ class GPTBridge:
             yield from flush()
 
     def _language_model(self, m):
+        while hasattr(m, 'base_model') or (hasattr(m, 'model') and not hasattr(m, 'decoder')):
+            m = m.base_model if hasattr(m, 'base_model') else m.model   # strip PEFT wrappers
         return getattr(m, 'language_model', m)
+
+    def _convert_modules_to_save(self, model, adapter_name: str):
+        """Trainable copies made by ``modules_to_save`` (embedding / head / final norm), under their HF keys."""
+        from ..tuners.peft_model import ModulesToSaveWrapper
+        out: Dict[str, torch.Tensor] = {}
+        rows, actual = self._vocab_rows(), self.config.padded_vocab_size
+        emb = getattr(getattr(model, 'embedding', None), 'word_embeddings', None)
+        if isinstance(emb, ModulesToSaveWrapper):
+            self._direct(emb, 'weight', out, self.hf_embed_key, False, tp_dim=0, to_hf=lambda w: w[:actual])
+        if isinstance(getattr(model, 'output_layer', None), ModulesToSaveWrapper):
+            self._direct(model.output_layer, 'weight', out, self.hf_lm_head_key, False, tp_dim=0,
+                         to_hf=lambda w: w[:actual])
+        dec = getattr(model, 'decoder', None)
+        if dec is not None and isinstance(getattr(dec, 'final_layernorm', None), ModulesToSaveWrapper):
+            self._direct(dec.final_layernorm, 'weight', out, self.hf_final_layernorm_key, False)
+        yield from out.items()
 
     def _convert_mtp(self, model, hf_sd, to_mcore: bool):
         """Multi-token-prediction layers are stored after the decoder layers (``model.layers.{L + k}``) with
