@@ -137,8 +137,11 @@ def main():
     hf_over = {}
     if args.layers is not None:
         hf_over['num_hidden_layers'] = args.layers
+    # one GPU holds all parameters, gradients and optimizer state (~148 GB): activations are recomputed per layer.
+    # With TP >= 2 the state is sharded and every activation fits, so nothing is recomputed.
+    recompute = dict(recompute_granularity='full', recompute_method='uniform', recompute_num_layers=1) if tp == 1 else {}
     cfg = model_config(args.model, hf_over, bf16=True, tensor_model_parallel_size=tp, sequence_parallel=tp > 1,
-                       recompute_granularity='full', recompute_method='uniform', recompute_num_layers=1)
+                       **recompute)
     trainer = Trainer(cfg, TrainConfig())
     dp = ps.get_world_size('dp')
     n_micro = args.seqs_per_gpu * world // dp          # micro-batches this rank runs per step
@@ -213,7 +216,8 @@ def main():
             'config': {'model': args.model + ('' if args.layers is None else f'[layers={args.layers}: INVALID debug run]'),
                        'global_batch': global_batch, 'seq_len': args.seq_len,
                        'parallelism': f'tp{tp}' + ('+sp' if tp > 1 else '') + (f' dp{dp}' if dp > 1 else ''),
-                       'micro_batches_per_step': n_micro, 'recompute': 'full, per layer',
+                       'micro_batches_per_step': n_micro, 'recompute': 'full, per layer' if recompute else 'none',
+                       'tp_collectives': 'fused in-kernel (NVLink peer memory)' if (tp > 1 and os.environ.get('MCB200_FUSED_COMM', '1') != '0') else ('nccl' if tp > 1 else 'none'),
                        'optimizer': 'AdamW, fp32 master weights and moments, fp32 gradient accumulation',
                        'l2': 'working set per step (parameters, gradients, optimizer state: > 100 GB) exceeds the 126 MB L2; no flush needed',
                        'loss': trainer.last_metrics.get('loss')},

@@ -189,6 +189,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_co
   using L = GemmSmem<BN>;
   constexpr uint32_t TMEM_COLS = 2 * BN;
   extern __shared__ uint8_t smem_raw[];
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;  // an earlier wait gave up: do not pile up
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint32_t* lflags = p.peer_flags[p.rank];
   const uint32_t epoch = (uint32_t)p.epoch;
@@ -404,6 +405,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                const __grid_constant__ RsMaps maps, const CommGemmParams p) {
   constexpr uint32_t TMEM_COLS = 2 * BN;
   extern __shared__ uint8_t smem_raw[];
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;  // an earlier wait gave up: do not pile up
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint32_t* lflags = p.peer_flags[p.rank];
   const uint32_t epoch = (uint32_t)p.epoch;

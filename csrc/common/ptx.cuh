@@ -66,8 +66,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 #ifndef MCB_WAIT_LIMIT_NS
-#define MCB_WAIT_LIMIT_NS 2000000000ull  // 2 s
+#define MCB_WAIT_LIMIT_NS 10000000000ull  // default 10 s
 #endif
+
+// The status buffer is int32[16]: [0] first failure code, [1] wait limit in milliseconds (0 = default).
+__device__ __forceinline__ uint64_t wait_limit_ns(const int* status) {
+  if (status) {
+    const int ms = status[1];
+    if (ms > 0) return static_cast<uint64_t>(ms) * 1000000ull;
+  }
+  return MCB_WAIT_LIMIT_NS;
+}
 
 // Bounded wait on an mbarrier phase.  `abort_flag` lives in shared memory and is
 // shared by every role of the CTA; `status` is the kernel's global status word.
@@ -80,7 +89,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > MCB_WAIT_LIMIT_NS) break;
+      if (now - t0 > wait_limit_ns(status)) break;
     }
   }
   *abort_flag = 1;
@@ -267,7 +276,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, bool
       if (*abort_flag) return false;
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > MCB_WAIT_LIMIT_NS) break;
+      if (now - t0 > wait_limit_ns(status)) break;
     }
     __nanosleep(64);
   }

@@ -133,6 +133,7 @@ class ModelConfig:
     qk_head_dim: int = 128
     qk_pos_emb_head_dim: int = 64
     v_head_dim: int = 128
+    mla_rope_interleaved: Optional[bool] = None  # None -> True (DeepSeek); GLM-5 checkpoints use rotate-half
 
     # qwen3_next / qwen3_5
     linear_attention_freq: Optional[Union[str, int, List[int]]] = None
@@ -278,6 +279,8 @@ class ModelConfig:
             self.mtp_unroll_steps = self.mtp_num_layers
         if self.csa_compress_ratios is not None and self.mtp_num_layers is not None:
             self.csa_compress_ratios = list(self.csa_compress_ratios) + [0] * self.mtp_num_layers
+        if self.mla_rope_interleaved is None:
+            self.mla_rope_interleaved = True
         if self.multi_latent_attention:
             # MLA always rotates interleaved pairs of the rope sub-dimension; the flag only applies to the
             # (non-MLA) indexer, see dsa_indexer_rotary_interleaved

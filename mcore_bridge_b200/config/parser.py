@@ -228,6 +228,7 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
             res.pop('num_query_groups', None)
         if llm == 'glm_moe_dsa':
             res['experimental_attention_variant'] = 'dsa'
+            res['mla_rope_interleaved'] = bool(res.pop('rotary_interleaved', False))
     elif llm == 'qwen3_next' or hf_type in {'qwen3_5', 'qwen3_5_moe'}:
         res['layernorm_zero_centered_gamma'] = True
         res['attention_output_gate'] = True
@@ -268,6 +269,10 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
             and rope_scaling.get('rope_type', rope_scaling.get('type', 'default')) == 'default':
         res.pop('rope_scaling', None)  # nothing to scale: a plain table
 
+    if first_k_dense is None and isinstance(hash_layers, (list, tuple)) and set(hash_layers) <= {'dense', 'sparse'} \
+            and res.get('num_moe_experts'):
+        # newer configs list the MLP type of every layer instead of `first_k_dense_replace`
+        res['moe_layer_freq'] = '[' + ','.join('1' if t == 'sparse' else '0' for t in hash_layers) + ']'
     if first_k_dense is not None:
         res['moe_layer_freq'] = f'[0]*{first_k_dense}+[1]*{res["num_layers"] - first_k_dense}'
     if res.get('moe_router_score_function', 'softmax') == 'sigmoid' and 'moe_router_enable_expert_bias' not in res:

@@ -71,6 +71,7 @@ def status_word(device=None) -> torch.Tensor:
     w = _status_words.get(dev)
     if w is None:
         w = torch.zeros(16, dtype=torch.int32, device=f'cuda:{dev}')
+        w[1] = int(os.environ.get('MCB200_WAIT_LIMIT_MS', '10000'))  # bound of every in-kernel wait
         _status_words[dev] = w
     return w
 
@@ -81,7 +82,7 @@ def check_status(device=None, clear: bool = True) -> None:
     code = int(w[0].item())
     if code != 0:
         if clear:
-            w.zero_()
+            w[0] = 0
         raise KernelError(f'kernel status {code}: {STATUS_NAMES.get(code, "unknown")}')
 
 

@@ -56,7 +56,8 @@ def is_supported() -> bool:
     if not torch.cuda.is_available() or not dist.is_available() or not dist.is_initialized():
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import importlib
+        importlib.import_module('torch.distributed._symmetric_memory')
         return dist.get_backend() == 'nccl'
     except Exception:
         return False

@@ -160,6 +160,10 @@ class Trainer:
         host = out.cpu()                       # the step's device->host read
         self.d2h_bytes += out.numel() * out.element_size()
         self.last_metrics = {'loss': float(host[0]), 'grad_norm': float(host[1])}
+        if self.device.type == 'cuda':
+            from ..ops import _lib
+            if _lib.cuda_enabled():
+                _lib.check_status(self.device)  # a bounded in-kernel wait that gave up surfaces here, every step
         aux = get_moe_aux_losses()
         for k, (s, c) in list(aux.items()):
             self.last_metrics[k] = float(s) / max(c, 1)

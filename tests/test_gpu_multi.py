@@ -1,0 +1,24 @@
+"""Fused compute+collective kernels against the torch.distributed path, on 2 GPUs (skipped on a 1-GPU box)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason='needs 2 GPUs')
+def test_fused_tp_kernels_two_ranks():
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0')
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', '2', '--master-addr',
+           '127.0.0.1', '--master-port', '29533', os.path.join(HERE, 'multi_gpu_fused_worker.py')]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert 'ALL OK' in res.stdout
