@@ -326,6 +326,9 @@ class GPTBridge:
         if cfg.multi_latent_attention:
             self._set_mla(layer, attn, hf_sd, prefix, ap, to_mcore)
             return
+        if self._layer_is_linear_attention(prefix):
+            self._set_gdn(attn, hf_sd, prefix, to_mcore)
+            return
         self._set_qkv(attn, hf_sd, ap, to_mcore)
         self._direct(attn, 'linear_proj.weight', hf_sd, ap + self.hf_o_proj_key, to_mcore, tp_dim=1)
         self._direct(attn, 'linear_proj.bias', hf_sd, ap + self.hf_o_proj_key.replace('weight', 'bias'), to_mcore,
@@ -336,6 +339,62 @@ class GPTBridge:
         if cfg.softmax_type == 'learnable':
             self._direct(attn, 'core_attention.softmax_offset', hf_sd, ap + 'sinks', to_mcore, tp_dim=0)
         self._direct(attn, 'linear_qkv.layer_norm_weight', hf_sd, prefix + self.hf_input_layernorm_key, to_mcore)
+
+    hf_linear_attn_prefix = 'linear_attn'
+
+    def _layer_is_linear_attention(self, prefix: str) -> bool:
+        cfg = self.config
+        if cfg.linear_attention_freq is None or cfg.experimental_attention_variant != 'gated_delta_net':
+            return False
+        m = re.search(r'\.(\d+)\.$', prefix)
+        idx = int(m.group(1)) if m else 0
+        pat = cfg.linear_attention_pattern()
+        return idx < len(pat) and bool(pat[idx])
+
+    def _set_gdn(self, attn, hf_sd, prefix: str, to_mcore: bool):
+        """Gated DeltaNet.  HF keeps ``in_proj_qkvz`` / ``in_proj_ba`` (each grouped per key head) and a conv whose
+        channels run ``[all q | all k | all v]``; the model fuses the two projections per key-head group and orders
+        the conv channels per group ``[q | k | v]`` so tensor parallelism can shard whole groups."""
+        cfg = self.config
+        nk, nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        ratio = nv // nk
+        gq, gba = 2 * dk + 2 * ratio * dv, 2 * ratio
+        lp = f'{prefix}{self.hf_linear_attn_prefix}.'
+
+        def conv_to_mg(w):      # [C, 1, K]: [Q | K | V] -> per group [q | k | v]
+            q, k, v = w[:nk * dk], w[nk * dk:2 * nk * dk], w[2 * nk * dk:]
+            tail = w.shape[1:]
+            return torch.cat([q.reshape(nk, dk, *tail), k.reshape(nk, dk, *tail), v.reshape(nk, ratio * dv, *tail)],
+                             dim=1).reshape(-1, *tail)
+
+        def conv_to_hf(w):
+            tail = w.shape[1:]
+            g = w.reshape(nk, 2 * dk + ratio * dv, *tail)
+            return torch.cat([g[:, :dk].reshape(-1, *tail), g[:, dk:2 * dk].reshape(-1, *tail),
+                              g[:, 2 * dk:].reshape(-1, *tail)], dim=0)
+
+        param = attn.in_proj.weight if attn is not None else None
+        if to_mcore:
+            if param is not None:
+                qkvz = self._load_hf(hf_sd, lp + 'in_proj_qkvz.weight')
+                ba = self._load_hf(hf_sd, lp + 'in_proj_ba.weight')
+                H = qkvz.shape[-1]
+                full = torch.cat([qkvz.reshape(nk, gq, H), ba.reshape(nk, gba, H)], dim=1).reshape(-1, H)
+                self._put(param, full, 0)
+        elif self._agree(param is not None, self._device):
+            full = self._get(param, 0)
+            if full is not None:
+                g = full.reshape(nk, gq + gba, full.shape[-1])
+                self._emit(hf_sd, lp + 'in_proj_qkvz.weight', g[:, :gq].reshape(-1, full.shape[-1]))
+                self._emit(hf_sd, lp + 'in_proj_ba.weight', g[:, gq:].reshape(-1, full.shape[-1]))
+        self._direct(attn, 'conv1d.weight', hf_sd, lp + 'conv1d.weight', to_mcore, tp_dim=0, to_mg=conv_to_mg,
+                     to_hf=conv_to_hf)
+        self._direct(attn, 'A_log', hf_sd, lp + 'A_log', to_mcore, tp_dim=0)
+        self._direct(attn, 'dt_bias', hf_sd, lp + 'dt_bias', to_mcore, tp_dim=0)
+        self._direct(attn, 'out_norm.weight', hf_sd, lp + 'norm.weight', to_mcore)
+        self._direct(attn, 'out_proj.weight', hf_sd, lp + 'out_proj.weight', to_mcore, tp_dim=1)
+        self._direct(attn, 'in_proj.layer_norm_weight', hf_sd, prefix + self.hf_input_layernorm_key, to_mcore)
 
     def _set_mla(self, layer, attn, hf_sd, prefix, ap, to_mcore):
         cfg = self.config

@@ -1,0 +1,83 @@
+"""DeepSeek-V3 (MLA, sigmoid group-limited routing, shared expert) and GLM-5 style DSA sparse attention against
+the Transformers implementations; bridge round-trip for both."""
+import os
+
+import torch
+from safetensors.torch import load_file
+
+from mcore_bridge_b200 import ModelConfig, get_mcore_model, hf_to_mcore_config
+
+
+def _init(hf):
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            p.normal_(0, 0.06) if p.dim() >= 2 else p.normal_(1.0, 0.1)
+        for n, b in hf.named_buffers():
+            if 'e_score_correction_bias' in n:
+                b.normal_(0, 0.1)
+
+
+def _roundtrip(hf, c, tmp_path, ids, atol):
+    d1, d2 = str(tmp_path / 'a'), str(tmp_path / 'b')
+    hf.save_pretrained(d1)
+    cfg = ModelConfig(**hf_to_mcore_config(c), params_dtype=torch.float32)
+    model = get_mcore_model(cfg)[0].eval()
+    cfg.bridge.load_weights([model], d1)
+    with torch.no_grad():
+        ref, out = hf(ids).logits, model(ids)
+    assert (ref - out).abs().max().item() < atol
+    cfg.bridge.save_weights([model], d2)
+    a, b = load_file(os.path.join(d1, 'model.safetensors')), load_file(os.path.join(d2, 'model.safetensors'))
+    assert sorted(a) == sorted(b) and all(torch.equal(a[k], b[k]) for k in a)
+    return cfg, model
+
+
+def test_deepseek_v3(tmp_path):
+    from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+    torch.manual_seed(0)
+    c = DeepseekV3Config(num_hidden_layers=3, hidden_size=128, num_attention_heads=4, num_key_value_heads=4,
+                         q_lora_rank=32, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                         n_routed_experts=8, num_experts_per_tok=2, n_group=2, topk_group=1, moe_intermediate_size=32,
+                         intermediate_size=64, first_k_dense_replace=1, n_shared_experts=1, vocab_size=256,
+                         scoring_func='sigmoid', routed_scaling_factor=2.5, norm_topk_prob=True,
+                         max_position_embeddings=512, rope_interleave=True, tie_word_embeddings=False)
+    hf = DeepseekV3ForCausalLM(c).float().eval()
+    _init(hf)
+    ids = torch.randint(0, 256, (2, 48), generator=torch.Generator().manual_seed(0))
+    cfg, model = _roundtrip(hf, c, tmp_path, ids, 2e-5)
+    assert cfg.multi_latent_attention and cfg.moe_layer_pattern() == [0, 1, 1]
+
+
+def test_glm_moe_dsa_sparse_attention(tmp_path):
+    from transformers import GlmMoeDsaConfig, GlmMoeDsaForCausalLM
+    torch.manual_seed(0)
+    c = GlmMoeDsaConfig(num_hidden_layers=3, hidden_size=128, num_attention_heads=4, num_key_value_heads=4,
+                        q_lora_rank=32, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                        n_routed_experts=8, num_experts_per_tok=2, n_group=1, topk_group=1, moe_intermediate_size=32,
+                        intermediate_size=64, mlp_layer_types=['dense', 'sparse', 'sparse'], n_shared_experts=1,
+                        vocab_size=256, routed_scaling_factor=2.5, norm_topk_prob=True, max_position_embeddings=512,
+                        tie_word_embeddings=False, index_n_heads=4, index_head_dim=16, index_topk=8)
+    c._attn_implementation = 'eager'   # the sdpa path of the HF model drops the causal mask from the indexer
+    hf = GlmMoeDsaForCausalLM(c).float().eval()
+    _init(hf)
+    ids = torch.randint(0, 256, (1, 40), generator=torch.Generator().manual_seed(0))
+    cfg, model = _roundtrip(hf, c, tmp_path, ids, 2e-4)
+    assert cfg.experimental_attention_variant == 'dsa' and cfg.dsa_indexer_topk == 8
+
+
+def test_dsa_indexer_loss_trains_indexer():
+    from mcore_bridge_b200.train.trainer import init_weights
+    from transformers import GlmMoeDsaConfig
+    c = GlmMoeDsaConfig(num_hidden_layers=1, hidden_size=64, num_attention_heads=2, num_key_value_heads=2,
+                        q_lora_rank=16, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                        n_routed_experts=4, num_experts_per_tok=2, n_group=1, topk_group=1, moe_intermediate_size=16,
+                        intermediate_size=32, mlp_layer_types=['dense'], n_shared_experts=1, vocab_size=64,
+                        max_position_embeddings=128, index_n_heads=2, index_head_dim=16, index_topk=4)
+    cfg = ModelConfig(**hf_to_mcore_config(c), params_dtype=torch.float32, dsa_indexer_loss_coeff=0.1)
+    model = get_mcore_model(cfg)[0].train()
+    init_weights(model, 0.1, 3)
+    ids = torch.randint(0, 64, (1, 32))
+    model(ids, labels=ids).mean().backward()
+    idx = model.decoder.layers[0].self_attention.indexer
+    assert idx.linear_wk.weight.grad is not None and idx.linear_wk.weight.grad.abs().sum() > 0
+    assert model.decoder.layers[0].self_attention.indexer_loss is not None
