@@ -37,6 +37,8 @@ def parse_args():
     ap.add_argument('--layers', type=int, default=None, help='debug only: override the layer count (marks the run invalid)')
     ap.add_argument('--parallelism', default='tp', choices=['tp', 'dp'])
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--micro-batch-size', type=int, default=0,
+                    help='packed sequences per micro-batch (0: min(4, GPUs); one GPU keeps 1 to fit memory)')
     return ap.parse_args()
 
 
@@ -144,10 +146,12 @@ def main():
                        **recompute)
     trainer = Trainer(cfg, TrainConfig())
     dp = ps.get_world_size('dp')
-    n_micro = args.seqs_per_gpu * world // dp          # micro-batches this rank runs per step
+    mbs = args.micro_batch_size or min(4, world)
     global_batch = args.seqs_per_gpu * world
-    ds = SyntheticPackedDataset(cfg.padded_vocab_size, args.seq_len, seed=1234 + ps.get_rank_in('dp'),
-                                segment_multiple=max(1, tp))
+    n_micro = global_batch // dp // mbs                # micro-batches this rank runs per step
+    assert n_micro * mbs * dp == global_batch
+    ds = SyntheticPackedDataset(cfg.padded_vocab_size, args.seq_len, micro_batch_size=mbs,
+                                seed=1234 + ps.get_rank_in('dp'), segment_multiple=max(1, tp))
     tokens_per_step = global_batch * args.seq_len
 
     def host_batches():
@@ -216,7 +220,7 @@ def main():
             'config': {'model': args.model + ('' if args.layers is None else f'[layers={args.layers}: INVALID debug run]'),
                        'global_batch': global_batch, 'seq_len': args.seq_len,
                        'parallelism': f'tp{tp}' + ('+sp' if tp > 1 else '') + (f' dp{dp}' if dp > 1 else ''),
-                       'micro_batches_per_step': n_micro, 'recompute': 'full, per layer' if recompute else 'none',
+                       'micro_batches_per_step': n_micro, 'micro_batch_size': mbs, 'recompute': 'full, per layer' if recompute else 'none',
                        'tp_collectives': 'fused in-kernel (NVLink peer memory)' if (tp > 1 and os.environ.get('MCB200_FUSED_COMM', '1') != '0') else ('nccl' if tp > 1 else 'none'),
                        'optimizer': 'AdamW, fp32 master weights and moments, fp32 gradient accumulation',
                        'l2': 'working set per step (parameters, gradients, optimizer state: > 100 GB) exceeds the 126 MB L2; no flush needed',

@@ -25,7 +25,7 @@ from . import symm
 FLAG_BYTES = 65536
 _c_ll, _c_int = ctypes.c_longlong, ctypes.c_int
 _ptr_cache: Dict[Tuple, ctypes.Array] = {}
-COPY_CTAS = int(os.environ.get('MCB200_AG_COPY_CTAS', '12'))
+COPY_CTAS = int(os.environ.get('MCB200_AG_COPY_CTAS', '0'))  # 0: the launcher balances copy vs GEMM CTAs
 
 
 def _on() -> bool:

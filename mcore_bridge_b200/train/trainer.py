@@ -128,6 +128,8 @@ class Trainer:
             dist.all_reduce(ntok, group=ps.get_group('cp'))
         loss = (loss_tok * mask).sum() / ntok.clamp(min=1.0) / num_microbatches
         MoEAuxLossAutoScaler.set_loss_scale(1.0 / num_microbatches)
+        from ..layers.mtp import MTPLossAutoScaler
+        MTPLossAutoScaler.set_loss_scale(1.0 / num_microbatches)
         loss.backward()
         return loss.detach()
 
@@ -164,6 +166,10 @@ class Trainer:
             from ..ops import _lib
             if _lib.cuda_enabled():
                 _lib.check_status(self.device)  # a bounded in-kernel wait that gave up surfaces here, every step
+        from ..layers.mtp import get_mtp_losses
+        for k, (sm, c) in list(get_mtp_losses().items()):
+            self.last_metrics[f'mtp_{k + 1}_loss'] = float(sm) / max(c, 1)
+        get_mtp_losses().clear()
         aux = get_moe_aux_losses()
         for k, (s, c) in list(aux.items()):
             self.last_metrics[k] = float(s) / max(c, 1)
