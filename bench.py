@@ -37,6 +37,8 @@ def parse_args():
     ap.add_argument('--layers', type=int, default=None, help='debug only: override the layer count (marks the run invalid)')
     ap.add_argument('--parallelism', default='tp', choices=['tp', 'dp'])
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--recompute-layers', type=int, default=-1,
+                    help='one GPU only: how many leading layers recompute their activations (-1: the tuned default)')
     ap.add_argument('--micro-batch-size', type=int, default=0,
                     help='packed sequences per micro-batch (0: min(4, GPUs); one GPU keeps 1 to fit memory)')
     return ap.parse_args()
@@ -117,6 +119,7 @@ def main():
     args = parse_args()
     if args.impl == 'reference':
         return reference_arm()
+    os.environ.setdefault('PYTORCH_CUDA_ALLOC_CONF', 'expandable_segments:True')
     import torch
     import torch.distributed as dist
 
@@ -141,7 +144,10 @@ def main():
         hf_over['num_hidden_layers'] = args.layers
     # one GPU holds all parameters, gradients and optimizer state (~148 GB): activations are recomputed per layer.
     # With TP >= 2 the state is sharded and every activation fits, so nothing is recomputed.
-    recompute = dict(recompute_granularity='full', recompute_method='uniform', recompute_num_layers=1) if tp == 1 else {}
+    recompute = {}
+    if tp == 1:
+        n_rec = args.recompute_layers if args.recompute_layers >= 0 else 24
+        recompute = dict(recompute_granularity='full', recompute_method='block', recompute_num_layers=n_rec)
     cfg = model_config(args.model, hf_over, bf16=True, tensor_model_parallel_size=tp, sequence_parallel=tp > 1,
                        **recompute)
     trainer = Trainer(cfg, TrainConfig())
@@ -220,7 +226,8 @@ def main():
             'config': {'model': args.model + ('' if args.layers is None else f'[layers={args.layers}: INVALID debug run]'),
                        'global_batch': global_batch, 'seq_len': args.seq_len,
                        'parallelism': f'tp{tp}' + ('+sp' if tp > 1 else '') + (f' dp{dp}' if dp > 1 else ''),
-                       'micro_batches_per_step': n_micro, 'micro_batch_size': mbs, 'recompute': 'full, per layer' if recompute else 'none',
+                       'micro_batches_per_step': n_micro, 'micro_batch_size': mbs, 'recompute': (f"full, first {recompute['recompute_num_layers']} layers" if recompute else 'none'),
+                       'peak_memory_gb': round(torch.cuda.max_memory_allocated() / 2**30, 1),
                        'tp_collectives': 'fused in-kernel (NVLink peer memory)' if (tp > 1 and os.environ.get('MCB200_FUSED_COMM', '1') != '0') else ('nccl' if tp > 1 else 'none'),
                        'optimizer': 'AdamW, fp32 master weights and moments, fp32 gradient accumulation',
                        'l2': 'working set per step (parameters, gradients, optimizer state: > 100 GB) exceeds the 126 MB L2; no flush needed',

@@ -1,0 +1,110 @@
+"""Kernel micro-benchmarks: ``python -m mcore_bridge_b200.bench_ops <op> [--m ..] [--n ..] [--k ..]``.
+
+Times one in-tree kernel with CUDA events after warm-up (inputs larger than L2 where the op is memory-bound, or an
+L2 flush between iterations) and prints achieved TFLOP/s or GB/s next to the measured peaks in
+``MEASURED_PEAKS.json`` when that file is present.  The same command line (small sizes, few iterations) is what
+the profiler captures in ``profiles/`` were taken with.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 'MEASURED_PEAKS.json')
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get('bf16_tflops', 1590.0), d.get('bf16_tflops_sustained', 1400.0), d.get('hbm_gbs', 6650.0), 'measured'
+    return 1590.0, 1400.0, 6650.0, 'fallback'
+
+
+def _time(fn, iters, flush=None):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters * 1e-3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('op', choices=['gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention'])
+    ap.add_argument('--m', type=int, default=8192)
+    ap.add_argument('--n', type=int, default=4096)
+    ap.add_argument('--k', type=int, default=4096)
+    ap.add_argument('--iters', type=int, default=10)
+    ap.add_argument('--bn', type=int, default=0)
+    ap.add_argument('--no-flush', action='store_true')
+    a = ap.parse_args()
+    from .ops import _lib, activation, cross_entropy, gemm, norm, rope
+    dev = 'cuda'
+    burst, sustained, hbm, src = _peaks()
+    flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    M, N, K = a.m, a.n, a.k
+    res = {'op': a.op, 'm': M, 'n': N, 'k': K}
+    if a.op.startswith('gemm'):
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+        dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+        fn = {'gemm': lambda: gemm.mm_nt(x, w, force_bn=a.bn), 'gemm_nn': lambda: gemm.mm_nn(dy, w, force_bn=a.bn),
+              'gemm_tn': lambda: gemm.mm_tn(dy, x, force_bn=a.bn)}[a.op]
+        t = _time(fn, a.iters, flush)
+        tf = 2.0 * M * N * K / t / 1e12
+        res.update(seconds=t, tflops=tf, frac_of_burst_peak=tf / burst, peak_source=src)
+    elif a.op == 'rmsnorm':
+        x = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+        w = torch.ones(N, device=dev, dtype=torch.bfloat16)
+        t = _time(lambda: norm.rmsnorm(x, w, 1e-6), a.iters, flush)
+        gbs = 2 * x.numel() * 2 / t / 1e9
+        res.update(seconds=t, gbs=gbs, frac_of_hbm_peak=gbs / hbm, peak_source=src)
+    elif a.op == 'swiglu':
+        x = torch.randn(M, 2 * N, device=dev, dtype=torch.bfloat16)
+        t = _time(lambda: activation.swiglu(x), a.iters, flush)
+        gbs = 3 * M * N * 2 / t / 1e9
+        res.update(seconds=t, gbs=gbs, frac_of_hbm_peak=gbs / hbm, peak_source=src)
+    elif a.op == 'qkv_rope':
+        ng, qpg, d = 8, 4, 128
+        x = torch.randn(M, ng * (qpg + 2) * d, device=dev, dtype=torch.bfloat16)
+        wq = torch.ones(d, device=dev, dtype=torch.bfloat16)
+        ang = torch.rand(M, d // 2, device=dev)
+        cos, sin = ang.cos(), ang.sin()
+        t = _time(lambda: rope.qkv_split_norm_rope(x, wq, wq, cos, sin, ng, qpg, d), a.iters, flush)
+        gbs = 2 * x.numel() * 2 / t / 1e9
+        res.update(seconds=t, gbs=gbs, frac_of_hbm_peak=gbs / hbm, peak_source=src)
+    elif a.op == 'ce':
+        h = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        lab = torch.randint(0, N, (M,), device=dev)
+        t = _time(lambda: cross_entropy.fused_linear_cross_entropy(h, w, lab, 'tp'), a.iters, flush)
+        tf = 2.0 * M * N * K / t / 1e12
+        res.update(seconds=t, tflops_forward=tf, frac_of_burst_peak=tf / burst, peak_source=src)
+    elif a.op == 'attention':
+        from .ops import attention as A
+        nq, nkv, d = a.n // 128 if a.n >= 128 else 32, 8, 128
+        q = torch.randn(M, nq, d, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(M, nkv, d, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(M, nkv, d, device=dev, dtype=torch.bfloat16)
+        cu = torch.tensor([0, M], dtype=torch.int32, device=dev)
+        t = _time(lambda: A.attention(q, k, v, cu, M), a.iters, flush)
+        tf = 4.0 * M * M * nq * d / 2 / t / 1e12
+        res.update(seconds=t, tflops_causal=tf, frac_of_burst_peak=tf / burst, heads=nq, peak_source=src)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    print(json.dumps(res))
+
+
+if __name__ == '__main__':
+    main()

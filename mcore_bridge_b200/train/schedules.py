@@ -1,0 +1,192 @@
+"""Pipeline-parallel micro-batch schedules over ``torch.distributed`` point-to-point (NCCL on GPUs).
+
+* no pipelining — handled directly by ``Trainer.train_step``.
+* 1F1B (one model chunk per rank): ``pp - rank - 1`` warm-up forwards, then one-forward-one-backward, then the
+  cool-down backwards.  Sends are asynchronous (``isend``) and complete in the background while the next
+  forward/backward runs (``overlap_p2p_comm``); receives are posted before the compute they are needed after.
+* virtual pipeline (several model chunks per rank, ``virtual_pipeline_model_parallel_size``): chunks are walked
+  in order for all micro-batches forward, then in reverse order backward.  Activations of all micro-batches stay
+  alive (GPipe-like memory); the interleaved 1F1B ordering is a scheduling refinement of the same data flow.
+
+Activations travel as ``[T_local, H]`` in ``pipeline_dtype``.  With ``variable_seq_lengths`` the shape is sent
+first (two int64).  The last stage computes the loss; every stage accumulates gradients into the fp32 buffers of
+the distributed optimizer exactly as in the non-pipelined path.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..layers.context import PackedSeqParams
+from ..parallel import state as ps
+
+
+class _P2P:
+
+    def __init__(self, config, device):
+        self.cfg, self.device = config, device
+        self.prev, self.next = ps.get_pipeline_model_parallel_prev_rank(), ps.get_pipeline_model_parallel_next_rank()
+        self.group = ps.get_group('pp')
+        self.pending: List = []
+
+    def _shape(self, t: Optional[torch.Tensor], peer: int, send: bool, hidden: int, default_rows: int):
+        if not self.cfg.variable_seq_lengths:
+            return (default_rows, hidden)
+        meta = torch.zeros(2, dtype=torch.int64, device=self.device)
+        if send:
+            meta[0], meta[1] = t.shape[0], t.shape[1]
+            self.pending.append((dist.isend(meta, peer, group=self.group), meta))  # never block the sender
+            return tuple(t.shape)
+        dist.recv(meta, peer, group=self.group)
+        return (int(meta[0]), int(meta[1]))
+
+    def send(self, t: torch.Tensor, peer: int):
+        t = t.detach().to(self.cfg.pipeline_dtype).contiguous()
+        self._shape(t, peer, True, t.shape[1], t.shape[0])
+        self.pending.append((dist.isend(t, peer, group=self.group), t))
+
+    def recv(self, peer: int, rows: int, hidden: int) -> torch.Tensor:
+        shape = self._shape(None, peer, False, hidden, rows)
+        buf = torch.empty(shape, dtype=self.cfg.pipeline_dtype, device=self.device)
+        dist.recv(buf, peer, group=self.group)
+        return buf
+
+    def drain(self):
+        for w, _ in self.pending:
+            w.wait()
+        self.pending.clear()
+
+
+def _psp(d: Dict):
+    if d.get('cu_seqlens') is None:
+        return None
+    return PackedSeqParams(cu_seqlens_q=d['cu_seqlens'], cu_seqlens_kv=d['cu_seqlens'], max_seqlen_q=d.get('max_seqlen'),
+                           max_seqlen_kv=d.get('max_seqlen'))
+
+
+def _local_rows(d: Dict, cfg) -> int:
+    rows = d['input_ids'].numel()
+    if cfg.sequence_parallel and ps.get_world_size('tp') > 1:
+        rows //= ps.get_world_size('tp')
+    return rows
+
+
+def _forward(trainer, model, d: Dict, input_tensor: Optional[torch.Tensor], n_micro: int, is_last: bool):
+    cfg = trainer.config
+    if input_tensor is not None:
+        input_tensor.requires_grad_(True)
+        inner = model.module if hasattr(model, 'module') else model
+        inner.set_input_tensor(input_tensor)
+    out = model(input_ids=d['input_ids'], position_ids=d.get('position_ids'), attention_mask=d.get('attention_mask'),
+                labels=d['labels'] if is_last else None, packed_seq_params=_psp(d), loss_mask=d.get('loss_mask'))
+    if is_last:
+        mask = d.get('loss_mask')
+        if mask is None:
+            mask = torch.ones_like(out)
+        ntok = mask.sum()
+        if ps.get_world_size('cp') > 1:
+            ntok = ntok.clone()
+            dist.all_reduce(ntok, group=ps.get_group('cp'))
+        out = (out * mask).sum() / ntok.clamp(min=1.0) / n_micro
+    return out
+
+
+def _backward(output: torch.Tensor, grad: Optional[torch.Tensor], input_tensor: Optional[torch.Tensor]):
+    if grad is None:
+        output.backward()
+    else:
+        torch.autograd.backward(output, grad.to(output.dtype))
+    return None if input_tensor is None else input_tensor.grad
+
+
+def forward_backward_pipelining(trainer, microbatches: List[Dict]) -> torch.Tensor:
+    """Runs all micro-batches through the pipeline; returns the summed (already averaged) loss on the last stage,
+    zero elsewhere."""
+    cfg = trainer.config
+    pp, rank = ps.get_pipeline_model_parallel_world_size(), ps.get_pipeline_model_parallel_rank()
+    n = len(microbatches)
+    dev = trainer.device
+    p2p = _P2P(cfg, dev)
+    H = cfg.hidden_size
+    trainer.optimizer.zero_grad()
+    from ..layers.mtp import MTPLossAutoScaler
+    from ..ops.moe import MoEAuxLossAutoScaler
+    MoEAuxLossAutoScaler.set_loss_scale(1.0 / n)
+    MTPLossAutoScaler.set_loss_scale(1.0 / n)
+    total = torch.zeros((), dtype=torch.float32, device=dev)
+    data = [trainer._prepare(mb) for mb in microbatches]
+    chunks = trainer.ddp
+    for m in chunks:
+        m.is_last_microbatch = False
+
+    if len(chunks) > 1:
+        return _chunked_schedule(trainer, data, p2p, total)
+
+    model = chunks[0]
+    first, last = rank == 0, rank == pp - 1
+    warm = min(pp - rank - 1, n)
+    inputs: List[Optional[torch.Tensor]] = []
+    outputs: List[torch.Tensor] = []
+
+    def fwd(i):
+        nonlocal total
+        x = None if first else p2p.recv(p2p.prev, _local_rows(data[i], cfg), H)
+        out = _forward(trainer, model, data[i], x, n, last)
+        if last:
+            total += out.detach().float()
+        else:
+            p2p.send(out, p2p.next)
+        inputs.append(x)
+        outputs.append(out)
+
+    def bwd(j):
+        g = None if last else p2p.recv(p2p.next, outputs[j].shape[0], H)
+        model.is_last_microbatch = (j == n - 1)
+        gi = _backward(outputs[j], g, inputs[j])
+        if not first:
+            p2p.send(gi, p2p.prev)
+        inputs[j] = outputs[j] = None
+
+    for i in range(warm):
+        fwd(i)
+    for k in range(n - warm):
+        fwd(warm + k)
+        bwd(k)
+    for j in range(n - warm, n):
+        bwd(j)
+    p2p.drain()
+    return total
+
+
+def _chunked_schedule(trainer, data, p2p: _P2P, total: torch.Tensor) -> torch.Tensor:
+    """Virtual pipeline: virtual stage ``v = chunk * pp + rank``; data flows v -> v+1."""
+    cfg = trainer.config
+    pp, rank = ps.get_pipeline_model_parallel_world_size(), ps.get_pipeline_model_parallel_rank()
+    n, V, H = len(data), len(trainer.ddp), cfg.hidden_size
+    saved = {}
+    for c in range(V):
+        model = trainer.ddp[c]
+        very_first, very_last = (c == 0 and rank == 0), (c == V - 1 and rank == pp - 1)
+        for i in range(n):
+            x = None if very_first else p2p.recv(p2p.prev, _local_rows(data[i], cfg), H)
+            out = _forward(trainer, model, data[i], x, n, very_last)
+            if very_last:
+                total += out.detach().float()
+            else:
+                p2p.send(out, p2p.next)
+            saved[(c, i)] = (x, out)
+        p2p.drain()
+    for c in reversed(range(V)):
+        model = trainer.ddp[c]
+        very_first, very_last = (c == 0 and rank == 0), (c == V - 1 and rank == pp - 1)
+        for i in range(n):
+            x, out = saved.pop((c, i))
+            g = None if very_last else p2p.recv(p2p.next, out.shape[0], H)
+            model.is_last_microbatch = (i == n - 1)
+            gi = _backward(out, g, x)
+            if not very_first:
+                p2p.send(gi, p2p.prev)
+        p2p.drain()
+    return total
