@@ -46,7 +46,7 @@ class CoreAttention(nn.Module):
             from ..parallel.context_parallel import ring_attention
             return ring_attention(q, k, v, ctx, scale=self.scale, window=self.window, sinks=sinks)
         return attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, causal=True, scale=self.scale, window=self.window,
-                         sinks=sinks)
+                         sinks=sinks, seq_start=ctx.seq_start)
 
 
 class SelfAttention(nn.Module):

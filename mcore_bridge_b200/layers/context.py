@@ -29,6 +29,7 @@ class ForwardContext:
     position_ids: Optional[torch.Tensor] = None    # [T] positions of the tokens this CP rank holds
     padding_mask: Optional[torch.Tensor] = None    # [T_local] True where the token is padding
     seg_ids: Optional[torch.Tensor] = None         # [T_local] packed-sequence index per token
+    seq_start: Optional[torch.Tensor] = None       # [T] int32 first token of each token's sequence (attention kernels)
     num_seqs: Optional[int] = None
     input_ids: Optional[torch.Tensor] = None       # hash-routed MoE layers look at the ids
     extra: Dict[str, Any] = field(default_factory=dict)

@@ -111,6 +111,9 @@ class GPTModel(nn.Module):
         else:
             pos = position_ids.reshape(-1)
         ctx = ForwardContext(cu_seqlens=cu, max_seqlen=max_len, position_ids=pos, input_ids=input_ids)
+        if device.type == 'cuda' and cp == 1:
+            from ..ops.attention_cuda import seq_start_from_cu
+            ctx.seq_start = seq_start_from_cu(cu, T, device)
         if self.rotary_pos_emb is not None:
             seq_len_hint = int(max_len) if max_len is not None else None
             ctx.cos, ctx.sin = self.rotary_pos_emb(pos.to(device), seq_len_hint)

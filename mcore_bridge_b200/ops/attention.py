@@ -85,14 +85,15 @@ _BACKEND_ENV = 'MCB200_ATTENTION_BACKEND'  # auto | mcb | flash_attn | torch
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: Optional[torch.Tensor] = None,
               max_seqlen: Optional[int] = None, causal: bool = True, scale: Optional[float] = None,
               window: Optional[Tuple[int, int]] = None, sinks: Optional[torch.Tensor] = None,
-              softcap: Optional[float] = None) -> torch.Tensor:
-    """Self-attention over packed sequences; returns ``[T, nq, dv]``."""
+              softcap: Optional[float] = None, seq_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Self-attention over packed sequences; returns ``[T, nq, dv]``.  ``seq_start`` (``[T]`` int32, first token
+    of each token's sequence) can be passed to avoid recomputing it in every layer."""
     backend = os.environ.get(_BACKEND_ENV, 'auto')
     T, nq, d = q.shape
     if q.is_cuda and backend in ('auto', 'mcb'):
         from . import attention_cuda
         if attention_cuda.supported(q, k, v, causal, window, sinks, softcap):
-            return attention_cuda.attention(q, k, v, cu_seqlens, max_seqlen, scale)
+            return attention_cuda.attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start)
         if backend == 'mcb':
             raise RuntimeError('in-tree attention kernel does not support this configuration')
     if q.is_cuda and backend in ('auto', 'flash_attn') and sinks is None and q.dtype in (torch.bfloat16, torch.float16) \

@@ -1,12 +1,92 @@
-"""Binding of the in-tree sm_100a attention kernels (filled in as the kernels land)."""
+"""Binding of the in-tree sm_100a attention kernels (``csrc/attention``).
+
+Forward: ``attn_fwd_sm100.cu`` (tcgen05 / TMEM, two-pass softmax).  Backward: the in-tree kernels when
+available, else the ``flash_attn`` library backward fed with this forward's output and log-sum-exp (the layouts
+agree: ``lse [heads, T]`` in natural log).
+"""
 from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import Optional
 
 import torch
 
+from . import _lib
+
+_ll, _int, _f = ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+
 
 def supported(q, k, v, causal, window, sinks, softcap) -> bool:
-    return False
+    if os.environ.get('MCB200_ATTENTION_KERNEL', '1') == '0':
+        return False
+    if not (causal and window is None and sinks is None and not softcap):
+        return False
+    if q.dtype != torch.bfloat16 or q.shape[-1] not in (64, 128) or v.shape[-1] != q.shape[-1]:
+        return False
+    if q.shape[1] % k.shape[1] != 0 or q.shape[0] != k.shape[0]:
+        return False
+    return _lib.available()
 
 
-def attention(q, k, v, cu_seqlens, max_seqlen, scale):
-    raise NotImplementedError
+def seq_start_from_cu(cu_seqlens: Optional[torch.Tensor], T: int, device) -> torch.Tensor:
+    """``[T]`` int32: index of the first token of the packed sequence each token belongs to."""
+    if cu_seqlens is None:
+        return torch.zeros(T, dtype=torch.int32, device=device)
+    cu = cu_seqlens.to(device=device, dtype=torch.int64)
+    seg = torch.searchsorted(cu[1:].contiguous(), torch.arange(T, device=device), right=True)
+    return cu[:-1][seg.clamp(max=cu.numel() - 2)].to(torch.int32)
+
+
+class _AttnFn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, seq_start, cu_seqlens, max_seqlen, scale):
+        T, nq, d = q.shape
+        nkv = k.shape[1]
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o = torch.empty_like(q)
+        lse = torch.empty((nq, T), dtype=torch.float32, device=q.device)
+        rc = _lib.lib().mcb_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(seq_start), _lib.ptr(o),
+                                     _lib.ptr(lse), _int(T), _int(nq), _int(nkv), _int(d), _f(scale),
+                                     _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_attn_fwd')
+        ctx.save_for_backward(q, k, v, o, lse, seq_start, cu_seqlens)
+        ctx.scale, ctx.max_seqlen = scale, max_seqlen
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, seq_start, cu = ctx.saved_tensors
+        do = do.contiguous()
+        T, nq, d = q.shape
+        lib = _lib.lib()
+        if hasattr(lib, 'mcb_attn_bwd') and os.environ.get('MCB200_ATTENTION_BWD_KERNEL', '1') != '0':
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            delta = torch.empty((nq, T), dtype=torch.float32, device=q.device)
+            rc = lib.mcb_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse),
+                                  _lib.ptr(delta), _lib.ptr(seq_start), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+                                  _int(T), _int(nq), _int(k.shape[1]), _int(d), _f(ctx.scale),
+                                  _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+            _lib.check_rc(rc, 'mcb_attn_bwd')
+            return dq, dk, dv, None, None, None, None
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        if cu is None:
+            cu = torch.tensor([0, T], dtype=torch.int32, device=q.device)
+        ms = ctx.max_seqlen or T
+        _flash_attn_varlen_backward(do, q, k, v, o, lse, dq, dk, dv, cu, cu, ms, ms, 0.0, ctx.scale, True, -1, -1, 0.0,
+                                    None, False, None)
+        return dq, dk, dv, None, None, None, None
+
+
+def attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start: Optional[torch.Tensor] = None):
+    T, nq, d = q.shape
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    if seq_start is None:
+        seq_start = seq_start_from_cu(cu_seqlens, T, q.device)
+    if max_seqlen is None and cu_seqlens is not None:
+        max_seqlen = T  # only the library backward needs it; the bound is safe
+    return _AttnFn.apply(q, k, v, seq_start, cu_seqlens, max_seqlen, float(scale))
