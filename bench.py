@@ -146,7 +146,7 @@ def main():
     # With TP >= 2 the state is sharded and every activation fits, so nothing is recomputed.
     recompute = {}
     if tp == 1:
-        n_rec = args.recompute_layers if args.recompute_layers >= 0 else 24
+        n_rec = args.recompute_layers if args.recompute_layers >= 0 else 12   # peak ~167 GB of 180
         recompute = dict(recompute_granularity='full', recompute_method='block', recompute_num_layers=n_rec)
     cfg = model_config(args.model, hf_over, bf16=True, tensor_model_parallel_size=tp, sequence_parallel=tp > 1,
                        **recompute)

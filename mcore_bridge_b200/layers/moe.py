@@ -248,6 +248,7 @@ class MoELayer(nn.Module):
         else:
             self.shared_experts = None
         self.apply_probs_on_input = bool(config.moe_apply_probs_on_input)
+        self._fused = None
 
     # -- dispatch over the EP group with torch.distributed (baseline; host-synchronised split sizes)
     def _dispatch_nccl(self, x, probs, idx):
@@ -269,10 +270,66 @@ class MoELayer(nn.Module):
         recv_p = M.all_to_all(send_p.contiguous().view(-1, 1), out_splits, in_splits, 'ep').view(-1)
         return recv, recv_e, recv_p, (order, src_token, in_splits, out_splits)
 
+    def _forward_fused(self, x, padding_mask, seg_ids, num_seqs):
+        """Router, exchange and combine on the in-tree kernels (``layers/moe_fused.py``)."""
+        from . import moe_fused as F
+        cfg = self.config
+        r = self.router
+        T, H = x.shape
+        if self._fused is None:
+            self._fused = F.FusedMoEDispatcher(cfg, self.num_local_experts)
+        st = self._fused.begin(T, H, x.device)
+        lb = cfg.moe_router_load_balancing_type
+        kernel_router = (F.router_supported(self.num_experts, r.topk, cfg.moe_router_num_groups)
+                         and not (self.training and cfg.moe_aux_loss_coeff and lb == 'seq_aux_loss')
+                         and not cfg.moe_z_loss_coeff)
+        if kernel_router:
+            logits = r.gating(x).float()
+            valid = None if padding_mask is None else ~padding_mask.reshape(-1)
+            sigmoid = cfg.moe_router_score_function == 'sigmoid'
+            renorm = (not cfg.moe_router_pre_softmax) if not sigmoid else r.topk > 1
+            bias = r.expert_bias if (sigmoid and r.expert_bias is not None) else None
+            probs, idx, score_sum, counts = self._fused.route(st, logits, bias, valid, sigmoid, renorm,
+                                                              cfg.moe_router_num_groups, cfg.moe_router_group_topk,
+                                                              cfg.moe_router_topk_scaling_factor)
+            if r.enable_expert_bias and torch.is_grad_enabled():
+                with torch.no_grad():
+                    r.local_tokens_per_expert += counts.float()
+            coeff = cfg.moe_aux_loss_coeff
+            if self.training and coeff and lb in ('aux_loss', 'global_aux_loss'):
+                ntok = torch.tensor(float(T), device=x.device) if valid is None else valid.sum().float()
+                cnt = counts.float()
+                group = 'tp_dp_cp' if lb == 'global_aux_loss' else ('tp_cp' if cfg.sequence_parallel or
+                                                                    cfg.context_parallel_size > 1 else None)
+                ntok_all = ntok
+                if group is not None and ps.get_world_size(group) > 1:
+                    packed = torch.cat([cnt, ntok.view(1)])
+                    dist.all_reduce(packed, group=ps.get_group(group))
+                    cnt, ntok_all = packed[:-1], packed[-1]
+                aux = coeff * self.num_experts * ((cnt / (ntok_all * r.topk)) * (score_sum / ntok)).sum()
+                probs = moe_ops.MoEAuxLossAutoScaler.apply(probs, aux)
+                _track('load_balancing_loss', aux / coeff)
+        else:
+            probs, idx = r(x, padding_mask, seg_ids, num_seqs)
+            self._fused.publish_routing(st, idx)
+            idx = idx.to(torch.int32)
+        xp, row_probs = self._fused.dispatch(st, x, probs, idx)
+        if self.apply_probs_on_input:
+            xp = (xp.float() * row_probs[:, None]).to(xp.dtype)
+            row_probs = None
+        yp = self.experts(xp, st.seg_off, row_probs)
+        y = self._fused.combine(st, yp)
+        if self.shared_experts is not None:
+            y = y + self.shared_experts(x)
+        return y
+
     def forward(self, x: torch.Tensor, padding_mask: Optional[torch.Tensor] = None, seg_ids=None, num_seqs=None):
         """``x [T_local, H]`` -> ``[T_local, H]``."""
         cfg = self.config
         T, H = x.shape
+        from . import moe_fused
+        if moe_fused.available(x) and ps.get_world_size('etp') == 1 and H % 8 == 0:
+            return self._forward_fused(x, padding_mask, seg_ids, num_seqs)
         probs, idx = self.router(x, padding_mask, seg_ids, num_seqs)
         k = idx.shape[1]
         etp = ps.get_world_size('etp')

@@ -1,0 +1,374 @@
+"""Fused MoE token exchange on the in-tree kernels (``csrc/moe/moe_kernels.cu``).
+
+Forward of one MoE layer on a rank:
+
+1. router kernel -> probabilities, expert indices, per-expert counts, written straight into this rank's *published*
+   region of a symmetric workspace together with a copy of the activations;
+2. ``READY`` flag to all ranks of the expert-parallel group; wait for everybody's;
+3. layout kernel (padded segment offsets from all ranks' counts), then the pull-dispatch kernel: the owner of an
+   expert reads the routed rows out of the sources' published activations over NVLink into its expert-sorted GEMM
+   input (ordinary local memory, so it can be kept for backward) and records where every copy went;
+4. grouped expert GEMMs; the second one writes into the symmetric output buffer;
+5. ``DONE`` flag; each source pulls and sums its ``k`` result rows (combine kernel).
+
+Backward runs the same kernels with the saved row maps: gradient rows are pulled by the owners, expert backward
+runs, input-gradient rows and the gradients of the routing probabilities are pulled back by the sources.
+
+Workspaces are double buffered by call parity (see ``parallel/symm.py`` for the argument why that is sufficient).
+With an expert-parallel size of one everything is local and no flags are exchanged.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..ops import _lib
+from ..parallel import state as ps
+from ..parallel import symm
+
+_int, _f, _u = ctypes.c_int, ctypes.c_float, ctypes.c_uint
+FLAG_BYTES = 65536
+F_READY, F_DONE = 0, 16
+PAD = 128
+
+
+def available(x: torch.Tensor) -> bool:
+    if os.environ.get('MCB200_FUSED_MOE', '1') == '0':
+        return False
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and _lib.available()):
+        return False
+    ep = ps.get_world_size('ep')
+    return ep == 1 or (ep <= 8 and symm.is_supported())
+
+
+def _arr(ptrs: List[int]):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+@dataclass
+class _Region:
+    """Offsets of one parity half of a workspace."""
+    x: int
+    idx: int
+    probs: int
+    counts: int
+    sent: int
+    out: int
+    scalar: int
+    size: int
+
+
+class ExchangeBuffers:
+    """Published/received buffers of one direction (forward or backward) for a fixed problem size."""
+
+    def __init__(self, tag: str, T: int, H: int, k: int, E: int, capacity: int, device):
+        self.tag, self.T, self.H, self.k, self.E, self.cap = tag, T, H, k, E, capacity
+        self.world = ps.get_world_size('ep')
+        self.rank = ps.get_rank_in('ep') if self.world > 1 else 0
+        self.device = device
+
+        def al(n):
+            return (n + 1023) // 1024 * 1024
+
+        o = 0
+        offs = {}
+        for name, nbytes in (('x', T * H * 2), ('idx', T * k * 4), ('probs', T * k * 4), ('counts', E * 4),
+                             ('sent', T * k * 4), ('out', capacity * H * 2), ('scalar', capacity * 4)):
+            offs[name] = o
+            o += al(nbytes)
+        self.half = o
+        self.offs = offs
+        total = FLAG_BYTES + 2 * self.half
+        if self.world > 1:
+            self.ws = symm.get_workspace('ep', total, f'moe_{tag}_{T}_{H}_{k}_{E}_{capacity}')
+            self.base_ptrs = self.ws.peer_ptrs
+            self.buf = self.ws.buffer
+        else:
+            self.ws = None
+            self.buf = torch.zeros(total, dtype=torch.uint8, device=device)
+            self.base_ptrs = [self.buf.data_ptr()]
+        self.epoch = 0
+        self._ptr_cache: Dict[Tuple[str, int], ctypes.Array] = {}
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def off(self, name: str, parity: int) -> int:
+        return FLAG_BYTES + parity * self.half + self.offs[name]
+
+    def view(self, name: str, parity: int, shape, dtype) -> torch.Tensor:
+        o = self.off(name, parity)
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.buf[o:o + nbytes].view(dtype).view(*shape)
+
+    def ptrs(self, name: str, parity: int):
+        key = (name, parity)
+        a = self._ptr_cache.get(key)
+        if a is None:
+            a = _arr([p + self.off(name, parity) for p in self.base_ptrs])
+            self._ptr_cache[key] = a
+        return a
+
+    def flag_ptrs(self):
+        key = ('flags', 0)
+        a = self._ptr_cache.get(key)
+        if a is None:
+            a = _arr(list(self.base_ptrs))
+            self._ptr_cache[key] = a
+        return a
+
+    def signal(self, base: int, value: int):
+        if self.world == 1:
+            return
+        _lib.check_rc(_lib.lib().mcb_flag_signal(self.flag_ptrs(), _int(self.world), _int(self.rank), _int(base),
+                                                 _u(value), _lib.stream_ptr()), 'mcb_flag_signal')
+
+    def wait(self, base: int, value: int):
+        if self.world == 1:
+            return
+        _lib.check_rc(_lib.lib().mcb_flag_wait(self.flag_ptrs(), _int(self.world), _int(self.rank), _int(base),
+                                               _u(value), _lib.ptr(_lib.status_word(self.device)),
+                                               _lib.stream_ptr()), 'mcb_flag_wait')
+
+
+_BUFFERS: Dict[Tuple, ExchangeBuffers] = {}
+
+
+def _buffers(tag, T, H, k, E, cap, device) -> ExchangeBuffers:
+    key = (tag, T, H, k, E, cap, device.index)
+    b = _BUFFERS.get(key)
+    if b is None:
+        b = ExchangeBuffers(tag, T, H, k, E, cap, device)
+        _BUFFERS[key] = b
+    return b
+
+
+def capacity_rows(T: int, k: int, El: int, world: int, factor: Optional[float]) -> int:
+    """Rows of the receive buffer: ``factor`` x the balanced load plus worst-case padding, capped by the true worst
+    case (every copy of every rank lands here)."""
+    f = float(os.environ.get('MCB200_MOE_CAPACITY_FACTOR', factor or 2.0))
+    worst = world * T * k
+    rows = min(worst, int(f * T * k)) + El * PAD
+    return (rows + PAD - 1) // PAD * PAD
+
+
+# ---------------------------------------------------------------------------------------------------------------
+class _RouterFn(torch.autograd.Function):
+    """logits -> (probs [T,k], idx [T,k] int32, score_sum [E]); counts [E] int32 are written into ``counts_out``."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, valid, k, sigmoid, renorm, groups, group_topk, scaling, probs_out, idx_out,
+                counts_out):
+        T, E = logits.shape
+        logits = logits.contiguous()
+        scores = torch.empty((T, E), dtype=torch.float32, device=logits.device)
+        score_sum = torch.zeros(E, dtype=torch.float32, device=logits.device)
+        counts_out.zero_()
+        rc = _lib.lib().mcb_router_fwd(_lib.ptr(logits), _lib.ptr(bias), _lib.ptr(valid), _lib.ptr(probs_out),
+                                       _lib.ptr(idx_out), _lib.ptr(scores), _lib.ptr(counts_out), _lib.ptr(score_sum),
+                                       _int(T), _int(E), _int(k), _int(int(sigmoid)), _int(int(renorm)),
+                                       _int(groups or 0), _int(group_topk or 0), _f(scaling), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_router_fwd')
+        idx_saved = idx_out.clone()
+        ctx.save_for_backward(scores, idx_saved, valid)
+        ctx.meta = (k, sigmoid, renorm, scaling)
+        ctx.mark_non_differentiable(idx_saved)
+        return probs_out.clone(), idx_saved, score_sum
+
+    @staticmethod
+    def backward(ctx, dprobs, _didx, dscore_sum):
+        scores, idx, valid = ctx.saved_tensors
+        k, sigmoid, renorm, scaling = ctx.meta
+        T, E = scores.shape
+        dlogits = torch.empty_like(scores)
+        dprobs = dprobs.float().contiguous() if dprobs is not None else torch.zeros((T, k), device=scores.device)
+        dvec = dscore_sum.float().contiguous() if dscore_sum is not None else None
+        rc = _lib.lib().mcb_router_bwd(_lib.ptr(dprobs), _lib.ptr(idx), _lib.ptr(scores), _lib.ptr(dvec),
+                                       _lib.ptr(valid), _lib.ptr(dlogits), _int(T), _int(E), _int(k),
+                                       _int(int(sigmoid)), _int(int(renorm)), _f(scaling), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_router_bwd')
+        return (dlogits,) + (None,) * 11
+
+
+def router_supported(E: int, k: int, groups: Optional[int]) -> bool:
+    if E % 32 or E > 512 or k > 16:
+        return False
+    if groups and groups > 1:
+        epl = E // 32
+        if E % groups or (E // groups) % epl:
+            return False
+        lpg = (E // groups) // epl
+        if lpg < 1 or lpg & (lpg - 1):
+            return False
+    return True
+
+
+@dataclass
+class DispatchState:
+    fwd: ExchangeBuffers
+    bwd: ExchangeBuffers
+    parity: int
+    seg_off: torch.Tensor      # [El+1] int32 (the grouped GEMM offsets)
+    row_src: torch.Tensor      # [cap] int32
+    sent_row: Optional[torch.Tensor] = None   # [T,k] int32, saved copy
+    idx: Optional[torch.Tensor] = None
+
+
+class _DispatchFn(torch.autograd.Function):
+    """(x [T,H], probs [T,k]) -> (xp [cap,H], row_probs [cap]) on the expert owners."""
+
+    @staticmethod
+    def forward(ctx, x, probs, idx, st: DispatchState, El: int):
+        b = st.fwd
+        T, H, k, E = b.T, b.H, b.k, b.E
+        par = st.parity
+        epoch = b.epoch
+        b.view('x', par, (T, H), torch.bfloat16).copy_(x)
+        b.view('probs', par, (T, k), torch.float32).copy_(probs.float())
+        # idx and counts were written into the published region by the router kernel
+        b.signal(F_READY, epoch)
+        b.wait(F_READY, epoch)
+        dev = x.device
+        src_off = torch.empty(b.world * El, dtype=torch.int32, device=dev)
+        rc = _lib.lib().mcb_moe_layout(b.ptrs('counts', par), _int(b.world), _int(b.rank), _int(E), _int(El),
+                                       _lib.ptr(st.seg_off), _lib.ptr(src_off), _int(b.cap),
+                                       _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_moe_layout')
+        xp = torch.zeros((b.cap, H), dtype=torch.bfloat16, device=dev)
+        row_probs = torch.zeros(b.cap, dtype=torch.float32, device=dev)
+        st.row_src.fill_(-1)
+        cursor = torch.zeros(b.world * El, dtype=torch.int32, device=dev)
+        rc = _lib.lib().mcb_moe_pull_dispatch(b.ptrs('x', par), b.ptrs('idx', par), b.ptrs('probs', par),
+                                              b.ptrs('sent', par), _int(b.world), _int(b.rank), _int(T), _int(k),
+                                              _int(E), _int(El), _int(H), _int(b.cap), _lib.ptr(st.seg_off),
+                                              _lib.ptr(src_off), _lib.ptr(cursor), _lib.ptr(xp), _lib.ptr(row_probs),
+                                              _lib.ptr(st.row_src), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_moe_pull_dispatch')
+        ctx.st = st
+        ctx.meta = (T, H, k, E, El)
+        ctx.pdtype = probs.dtype
+        return xp, row_probs
+
+    @staticmethod
+    def backward(ctx, dxp, drow_probs):
+        st: DispatchState = ctx.st
+        T, H, k, E, El = ctx.meta
+        b = st.bwd
+        par = b.epoch & 1   # same call whose first half ran in _CombineFn.backward
+        epoch = b.epoch
+        # owners publish their input-gradient rows and probability gradients, sources pull them back
+        b.view('out', par, (b.cap, H), torch.bfloat16).copy_(dxp)
+        sc = b.view('scalar', par, (b.cap,), torch.float32)
+        if drow_probs is not None:
+            sc.copy_(drow_probs.float())
+        else:
+            sc.zero_()
+        b.signal(F_DONE, epoch)
+        b.wait(F_DONE, epoch)
+        dx = torch.empty((T, H), dtype=torch.bfloat16, device=dxp.device)
+        dprobs = torch.empty((T, k), dtype=torch.float32, device=dxp.device)
+        rc = _lib.lib().mcb_moe_combine(b.ptrs('out', par), b.ptrs('scalar', par), _int(b.world), _int(T), _int(k),
+                                        _int(El), _int(H), _lib.ptr(st.idx), _lib.ptr(st.sent_row), _lib.ptr(dx),
+                                        _lib.ptr(dprobs), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_moe_combine')
+        return dx, dprobs.to(ctx.pdtype), None, None, None
+
+
+class _CombineFn(torch.autograd.Function):
+    """y rows on the owners (already in the symmetric output buffer) -> out [T,H] on the sources."""
+
+    @staticmethod
+    def forward(ctx, y, st: DispatchState, El: int):
+        b = st.fwd
+        T, H, k = b.T, b.H, b.k
+        par = st.parity
+        epoch = b.epoch
+        out_buf = b.view('out', par, (b.cap, H), torch.bfloat16)
+        if y.data_ptr() != out_buf.data_ptr():
+            out_buf.copy_(y)
+        b.signal(F_DONE, epoch)
+        b.wait(F_DONE, epoch)
+        idx = b.view('idx', par, (T, k), torch.int32)
+        sent = b.view('sent', par, (T, k), torch.int32)
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=y.device)
+        rc = _lib.lib().mcb_moe_combine(b.ptrs('out', par), None, _int(b.world), _int(T), _int(k), _int(El), _int(H),
+                                        _lib.ptr(idx), _lib.ptr(sent), _lib.ptr(out), None, _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_moe_combine')
+        st.sent_row = sent.clone()   # the published tables are reused two calls later
+        st.idx = idx.clone()
+        ctx.st = st
+        ctx.meta = (T, H, k, El)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        st: DispatchState = ctx.st
+        T, H, k, El = ctx.meta
+        b = st.bwd
+        epoch = b.next_epoch()
+        par = epoch & 1
+        b.view('x', par, (T, H), torch.bfloat16).copy_(dout)
+        b.signal(F_READY, epoch)
+        b.wait(F_READY, epoch)
+        dy = torch.empty((b.cap, H), dtype=torch.bfloat16, device=dout.device)
+        rc = _lib.lib().mcb_moe_pull_rows(b.ptrs('x', par), _int(b.world), _int(T), _int(k), _int(H),
+                                          _lib.ptr(st.row_src), _int(b.cap), _lib.ptr(dy), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_moe_pull_rows')
+        return dy, None, None
+
+
+class FusedMoEDispatcher:
+    """Per-layer helper owned by ``MoELayer``; holds no parameters."""
+
+    def __init__(self, config, num_local_experts: int):
+        self.config = config
+        self.El = num_local_experts
+        self.E = config.num_moe_experts
+        self.k = config.moe_router_topk
+
+    def begin(self, T: int, H: int, device) -> DispatchState:
+        world = ps.get_world_size('ep')
+        cap = capacity_rows(T, self.k, self.El, world, self.config.moe_expert_capacity_factor)
+        fwd = _buffers('f', T, H, self.k, self.E, cap, device)
+        bwd = _buffers('b', T, H, self.k, self.E, cap, device)
+        epoch = fwd.next_epoch()
+        return DispatchState(fwd=fwd, bwd=bwd, parity=epoch & 1,
+                             seg_off=torch.empty(self.El + 1, dtype=torch.int32, device=device),
+                             row_src=torch.empty(cap, dtype=torch.int32, device=device))
+
+    def route(self, st: DispatchState, logits: torch.Tensor, bias, valid, sigmoid, renorm, groups, group_topk, scaling):
+        b = st.fwd
+        probs_out = torch.empty((b.T, b.k), dtype=torch.float32, device=logits.device)
+        idx_out = b.view('idx', st.parity, (b.T, b.k), torch.int32)
+        counts_out = b.view('counts', st.parity, (b.E,), torch.int32)
+        v8 = None if valid is None else valid.to(torch.uint8).contiguous()
+        probs, idx, score_sum = _RouterFn.apply(logits, bias, v8, b.k, sigmoid, renorm, groups, group_topk,
+                                                float(scaling or 1.0), probs_out, idx_out, counts_out)
+        return probs, idx, score_sum, counts_out
+
+    def publish_routing(self, st: DispatchState, idx: torch.Tensor):
+        """Routing decided elsewhere (torch router): publish indices and per-expert counts for the exchange."""
+        b = st.fwd
+        b.view('idx', st.parity, (b.T, b.k), torch.int32).copy_(idx.to(torch.int32))
+        counts = torch.bincount(idx.reshape(-1), minlength=b.E).to(torch.int32)
+        b.view('counts', st.parity, (b.E,), torch.int32).copy_(counts)
+        return counts
+
+    def dispatch(self, st: DispatchState, x, probs, idx):
+        return _DispatchFn.apply(x, probs, idx, st, self.El)
+
+    def out_buffer(self, st: DispatchState) -> torch.Tensor:
+        """Where the last expert GEMM should write so that the combine needs no copy."""
+        b = st.fwd
+        return b.view('out', st.parity, (b.cap, b.H), torch.bfloat16)
+
+    def combine(self, st: DispatchState, y):
+        return _CombineFn.apply(y, st, self.El)
