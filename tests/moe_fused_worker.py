@@ -1,0 +1,62 @@
+"""Worker (single process or torchrun): the fused MoE layer path (router kernel, pull dispatch over peer memory, combine)
+against the torch.distributed path of the same layer, forward and backward, expert parallel over all ranks."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch.distributed as dist
+from mcore_bridge_b200.parallel import state as ps
+from mcore_bridge_b200.ops import _lib, moe as moe_ops
+ps.init_distributed()
+world = dist.get_world_size() if dist.is_initialized() else 1
+rank = dist.get_rank() if dist.is_initialized() else 0
+ps.initialize_model_parallel(expert_model_parallel_size=world)
+dev = torch.device('cuda', torch.cuda.current_device())
+from mcore_bridge_b200 import ModelConfig
+from mcore_bridge_b200.train.presets import hf_config
+from mcore_bridge_b200.config import hf_to_mcore_config
+from mcore_bridge_b200.layers.moe import MoELayer
+def rel(a,b): return ((a.float()-b.float()).norm()/(b.float().norm()+1e-9)).item()
+ok = True
+for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None),(64,6,1024,256,True,8)]:
+    kw = hf_to_mcore_config(hf_config('qwen3_moe_tiny', num_experts=E, num_experts_per_tok=k, hidden_size=H, moe_intermediate_size=F))
+    if sig: kw.update(moe_router_score_function='sigmoid', moe_router_enable_expert_bias=True, moe_router_num_groups=groups, moe_router_group_topk=4, moe_router_topk_scaling_factor=2.5)
+    cfg = ModelConfig(**kw, bf16=True, expert_model_parallel_size=world, moe_aux_loss_coeff=1e-2)
+    torch.manual_seed(5)
+    with torch.device(dev):
+        layer = MoELayer(cfg).train()
+    # same router on every rank; experts differ per rank (global expert e = rank*El + local)
+    g = torch.Generator(device=dev).manual_seed(11)
+    with torch.no_grad():
+        layer.router.weight.copy_(torch.randn(layer.router.weight.shape, device=dev, generator=g)*0.3)
+        if sig: layer.router.expert_bias.copy_(torch.randn(E, device=dev, generator=g)*0.05)
+        full1 = torch.randn(E, layer.experts.linear_fc1.weight.shape[1], H, device=dev, generator=g)*0.05
+        full2 = torch.randn(E, H, layer.experts.linear_fc2.weight.shape[2], device=dev, generator=g)*0.05
+        El = E // world
+        layer.experts.linear_fc1.weight.copy_(full1[rank*El:(rank+1)*El]); layer.experts.linear_fc2.weight.copy_(full2[rank*El:(rank+1)*El])
+    T = 1024
+    gx = torch.Generator(device=dev).manual_seed(100+rank)
+    x = (torch.randn(T, H, device=dev, generator=gx)).to(torch.bfloat16)
+    outs = {}
+    for fused in ('1','0'):
+        os.environ['MCB200_FUSED_MOE'] = fused
+        layer.zero_grad()
+        xx = x.clone().requires_grad_()
+        y = layer(xx)
+        gy = torch.Generator(device=dev).manual_seed(200+rank)
+        dy = torch.randn(y.shape, device=dev, generator=gy).to(torch.bfloat16)
+        y.backward(dy)
+        outs[fused] = (y.detach().clone(), xx.grad.clone(), layer.router.weight.grad.clone(), layer.experts.linear_fc1.weight.grad.clone(), layer.experts.linear_fc2.weight.grad.clone())
+        torch.cuda.synchronize(); _lib.check_status()
+    names = ['y','dx','drouter','dfc1','dfc2']
+    for n_, a_, b_ in zip(names, outs['1'], outs['0']):
+        r = rel(a_, b_); good = r < 3e-2
+        t = torch.tensor([0 if good else 1], device=dev)
+        if world>1: dist.all_reduce(t)
+        ok &= t.item()==0
+        if rank==0: print(f'E{E} k{k} H{H} sig{sig}: {n_} rel={r:.3e} {"OK" if t.item()==0 else "FAIL"}', flush=True)
+if rank==0: print('ALL OK' if ok else 'SOME FAILED', flush=True)
+if world>1:
+    dist.barrier(); dist.destroy_process_group()

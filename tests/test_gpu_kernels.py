@@ -217,3 +217,56 @@ def test_bf16_model_matches_fp32_reference_model():
     loss_ref.backward()
     g, gr = model.decoder.layers[0].mlp.linear_fc1.weight.grad, ref.decoder.layers[0].mlp.linear_fc1.weight.grad
     assert rel(g, gr) < 5e-2
+
+
+@pytest.mark.parametrize('T,nq,nkv,d,segs', [(256, 2, 1, 128, [256]), (300, 4, 2, 128, [100, 200]),
+                                             (1000, 4, 4, 64, [77, 500, 423]), (1536, 4, 1, 128, [512, 1, 1023])])
+def test_attention_forward_kernel(T, nq, nkv, d, segs):
+    from mcore_bridge_b200.ops import attention as A
+    from mcore_bridge_b200.ops import attention_cuda as AC
+    torch.manual_seed(8)
+    q = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(segs).cumsum(0)), dtype=torch.int32, device=DEV)
+    assert AC.supported(q, k, v, True, None, None, None)
+    q2, k2, v2 = (t.clone().requires_grad_() for t in (q, k, v))
+    o = AC.attention(q2, k2, v2, cu, max(segs), None)
+    g = torch.randn_like(o)
+    o.backward(g)
+    qr, kr, vr = (t.float().clone().requires_grad_() for t in (q, k, v))
+    ref = A.attention_ref(qr, kr, vr, cu, cu)
+    ref.backward(g.float())
+    assert rel(o, ref) < 1e-2
+    assert rel(q2.grad, qr.grad) < 2e-2 and rel(k2.grad, kr.grad) < 2e-2 and rel(v2.grad, vr.grad) < 2e-2
+
+
+@pytest.mark.parametrize('E,k,sig,groups', [(8 * 4, 2, False, None), (128, 8, False, None), (64, 6, True, 8), (256, 8, True, 8)])
+def test_router_kernel_matches_torch(E, k, sig, groups):
+    from mcore_bridge_b200.layers import moe_fused as F
+    from mcore_bridge_b200.ops import moe as moe_ops
+    torch.manual_seed(9)
+    T = 777
+    logits = torch.randn(T, E, device=DEV) * 2
+    bias = torch.randn(E, device=DEV) * 0.1 if sig else None
+    gt = 4 if groups else None
+    assert F.router_supported(E, k, groups)
+    lg = logits.clone().requires_grad_()
+    probs_out = torch.empty(T, k, device=DEV)
+    idx_out = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    counts = torch.empty(E, dtype=torch.int32, device=DEV)
+    renorm = True
+    probs, idx, ssum = F._RouterFn.apply(lg, bias, None, k, sig, renorm, groups, gt, 2.5, probs_out, idx_out, counts)
+    lr = logits.clone().requires_grad_()
+    p_ref, i_ref, s_ref = moe_ops.topk_routing(lr, k, 'sigmoid' if sig else 'softmax', False, groups, gt, 2.5, bias)
+    # same experts (order inside the k may differ on ties: compare as sets through a scatter)
+    dense = torch.zeros(T, E, device=DEV).scatter_(1, idx.long(), probs)
+    dense_ref = torch.zeros(T, E, device=DEV).scatter_(1, i_ref, p_ref)
+    assert rel(dense, dense_ref) < 1e-4
+    assert torch.equal(counts.long(), torch.bincount(i_ref.reshape(-1), minlength=E))
+    assert rel(ssum, s_ref.sum(0)) < 1e-4
+    w = torch.randn(T, E, device=DEV)
+    v = torch.randn(E, device=DEV)
+    ((dense * w).sum() + (ssum * v).sum()).backward()
+    ((dense_ref * w).sum() + (s_ref.sum(0) * v).sum()).backward()
+    assert rel(lg.grad, lr.grad) < 1e-3
