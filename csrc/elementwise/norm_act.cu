@@ -388,3 +388,63 @@ int mcb_glu_bwd(const void* in, const float* probs, const void* dout, void* din,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate (declaration and contract: norm_noalloc.h).
+// The weight-gradient accumulator that mcb_rmsnorm_bwd receives from its caller lives here in a fixed device array.
+// ---------------------------------------------------------------------------------------------------------------
+#define MCB_NOALLOC_MAX_H 16384
+
+static __device__ __align__(256) float g_rmsnorm_dw_scratch[MCB_NOALLOC_MAX_H];
+
+namespace {
+
+__global__ void dw_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int H) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < H) dst[i] = __float2bfloat16(src[i]);
+}
+
+// Device address of the scratch array on the current device; resolved once per device.
+// In host code `g_rmsnorm_dw_scratch` itself is only a handle for the runtime, never a pointer a kernel may use.
+int noalloc_scratch_ptr(float** out) {
+  static float* per_device[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return -5;
+  if (per_device[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rmsnorm_dw_scratch);
+    if (e != cudaSuccess) return (int)e;
+    per_device[dev] = p;
+  }
+  *out = per_device[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int mcb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, void* dx, void* dw_bf16,
+                                       long long rows, int H, long long ldx, float eps, int zero_centered,
+                                       void* stream_) {
+  if (H <= 0 || H > MCB_NOALLOC_MAX_H) return -20;  // beyond the fixed scratch: use mcb_rmsnorm_bwd instead
+  if (H % 8 || ldx % 8) return -1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  float* scratch = nullptr;
+  int rc = noalloc_scratch_ptr(&scratch);
+  if (rc) return rc;
+  // the array keeps the previous call's sums: clear the part this call uses
+  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(float) * H, s);
+  if (e != cudaSuccess) return (int)e;
+  if (rows > 0) {
+    rc = mcb_rmsnorm_bwd(dy, x, w, nullptr, nullptr, dx, dw_bf16 ? scratch : nullptr, rows, H, ldx, eps,
+                         zero_centered, stream_);
+    if (rc) return rc;
+  }
+  if (dw_bf16) {
+    dw_to_bf16_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, reinterpret_cast<__nv_bfloat16*>(dw_bf16), H);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
