@@ -92,6 +92,10 @@ class GPTBridge:
     hf_final_layernorm_key = 'model.norm.weight'
     hf_lm_head_key = 'lm_head.weight'
     hf_score_key = 'score.weight'
+    # published checkpoint key prefixes -> the in-memory layout (applied to the key index on load, inverted on export)
+    hf_state_dict_mapping: Dict[str, str] = {}
+    hf_load_aliases: Dict[str, str] = {}     # further prefixes accepted on load only (older published layouts)
+    split_gdn_projections = False            # gated-DeltaNet input projection stored as qkv / z / b / a tensors
     hf_attn_prefix = 'self_attn'
     hf_mlp_prefix = 'mlp'
     hf_q_norm_key = 'q_norm.weight'
@@ -104,6 +108,9 @@ class GPTBridge:
     hf_shared_expert_prefix = None           # resolved per family ('shared_expert' / 'shared_experts')
     hf_shared_expert_gate_key = 'shared_expert_gate.weight'
     hf_experts_prefix = 'experts'
+    hf_expert_proj_names = ('gate_proj', 'up_proj', 'down_proj')     # per-expert linear names (MiniMax: w1 / w3 / w2)
+    hf_fused_gate_up = False                 # dense MLP exported as one ``gate_up_proj`` tensor (GLM-4)
+    hf_fused_qkv_key = None                  # e.g. 'query_key_value': one tensor laid out [all q | all k | all v]
     fp8_block_size = 128
 
     def __init__(self, config):
@@ -305,16 +312,29 @@ class GPTBridge:
             if to_mcore:
                 if param is None:
                     continue
-                keys = [f'{prefix}{n}.{suffix}' for n in names]
-                if suffix == 'bias' and keys[0] not in hf_sd:
-                    continue
-                full = qkv_to_mcore(*[self._load_hf(hf_sd, k) for k in keys], ng)
+                if self.hf_fused_qkv_key is not None:
+                    fk = f'{prefix}{self.hf_fused_qkv_key}.{suffix}'
+                    if suffix == 'bias' and fk not in hf_sd:
+                        continue
+                    w = self._load_hf(hf_sd, fk)
+                    nq_rows, kv_rows = q_rows * ng, d * ng
+                    parts = [w[:nq_rows], w[nq_rows:nq_rows + kv_rows], w[nq_rows + kv_rows:]]
+                else:
+                    keys = [f'{prefix}{n}.{suffix}' for n in names]
+                    if suffix == 'bias' and keys[0] not in hf_sd:
+                        continue
+                    parts = [self._load_hf(hf_sd, k) for k in keys]
+                full = qkv_to_mcore(*parts, ng)
                 self._put(param, full, 0)
             else:
                 if not self._agree(param is not None, self._device):
                     continue
                 full = self._get(param, 0)
                 if full is None:
+                    continue
+                if self.hf_fused_qkv_key is not None:
+                    self._emit(hf_sd, f'{prefix}{self.hf_fused_qkv_key}.{suffix}',
+                               torch.cat(list(qkv_to_hf(full, ng, q_rows, d)), dim=0))
                     continue
                 for n, t in zip(names, qkv_to_hf(full, ng, q_rows, d)):
                     self._emit(hf_sd, f'{prefix}{n}.{suffix}', t)
@@ -333,9 +353,17 @@ class GPTBridge:
         self._direct(attn, 'linear_proj.weight', hf_sd, ap + self.hf_o_proj_key, to_mcore, tp_dim=1)
         self._direct(attn, 'linear_proj.bias', hf_sd, ap + self.hf_o_proj_key.replace('weight', 'bias'), to_mcore,
                      optional=True)
-        if cfg.qk_layernorm:
+        if cfg.qk_layernorm and cfg.qk_layernorm_full:
+            self._direct(attn, 'q_norm.weight', hf_sd, ap + self.hf_q_norm_key, to_mcore, tp_dim=0)
+            self._direct(attn, 'k_norm.weight', hf_sd, ap + self.hf_k_norm_key, to_mcore, tp_dim=0)
+        elif cfg.qk_layernorm:
             self._direct(attn, 'q_layernorm.weight', hf_sd, ap + self.hf_q_norm_key, to_mcore)
             self._direct(attn, 'k_layernorm.weight', hf_sd, ap + self.hf_k_norm_key, to_mcore)
+        if cfg.post_sublayer_layernorm:
+            self._direct(attn, 'post_self_attn_layernorm.weight', hf_sd, prefix + 'post_self_attn_layernorm.weight',
+                         to_mcore)
+            self._direct(layer.mlp if layer is not None else None, 'post_mlp_layernorm.weight', hf_sd,
+                         prefix + 'post_mlp_layernorm.weight', to_mcore)
         if cfg.softmax_type == 'learnable':
             self._direct(attn, 'core_attention.softmax_offset', hf_sd, ap + 'sinks', to_mcore, tp_dim=0)
         self._direct(attn, 'linear_qkv.layer_norm_weight', hf_sd, prefix + self.hf_input_layernorm_key, to_mcore)
@@ -375,19 +403,40 @@ class GPTBridge:
                               g[:, 2 * dk:].reshape(-1, *tail)], dim=0)
 
         param = attn.in_proj.weight if attn is not None else None
+        split = self.split_gdn_projections
         if to_mcore:
-            if param is not None:
+            if param is not None and not split:
                 qkvz = self._load_hf(hf_sd, lp + 'in_proj_qkvz.weight')
                 ba = self._load_hf(hf_sd, lp + 'in_proj_ba.weight')
                 H = qkvz.shape[-1]
                 full = torch.cat([qkvz.reshape(nk, gq, H), ba.reshape(nk, gba, H)], dim=1).reshape(-1, H)
                 self._put(param, full, 0)
+            elif param is not None:
+                # Qwen3.5 stores four flat projections: qkv = [all q | all k | all v], z, b, a
+                qkv = self._load_hf(hf_sd, lp + 'in_proj_qkv.weight')
+                H = qkv.shape[-1]
+                parts = [qkv[:nk * dk].reshape(nk, dk, H), qkv[nk * dk:2 * nk * dk].reshape(nk, dk, H),
+                         qkv[2 * nk * dk:].reshape(nk, ratio * dv, H),
+                         self._load_hf(hf_sd, lp + 'in_proj_z.weight').reshape(nk, ratio * dv, H),
+                         self._load_hf(hf_sd, lp + 'in_proj_b.weight').reshape(nk, ratio, H),
+                         self._load_hf(hf_sd, lp + 'in_proj_a.weight').reshape(nk, ratio, H)]
+                self._put(param, torch.cat(parts, dim=1).reshape(-1, H), 0)
         elif self._agree(param is not None, self._device):
             full = self._get(param, 0)
-            if full is not None:
+            if full is not None and not split:
                 g = full.reshape(nk, gq + gba, full.shape[-1])
                 self._emit(hf_sd, lp + 'in_proj_qkvz.weight', g[:, :gq].reshape(-1, full.shape[-1]))
                 self._emit(hf_sd, lp + 'in_proj_ba.weight', g[:, gq:].reshape(-1, full.shape[-1]))
+            elif full is not None:
+                H = full.shape[-1]
+                g = full.reshape(nk, gq + gba, H)
+                q, k, v = g[:, :dk], g[:, dk:2 * dk], g[:, 2 * dk:2 * dk + ratio * dv]
+                z = g[:, 2 * dk + ratio * dv:gq]
+                self._emit(hf_sd, lp + 'in_proj_qkv.weight',
+                           torch.cat([q.reshape(-1, H), k.reshape(-1, H), v.reshape(-1, H)], 0))
+                self._emit(hf_sd, lp + 'in_proj_z.weight', z.reshape(-1, H))
+                self._emit(hf_sd, lp + 'in_proj_b.weight', g[:, gq:gq + ratio].reshape(-1, H))
+                self._emit(hf_sd, lp + 'in_proj_a.weight', g[:, gq + ratio:].reshape(-1, H))
         self._direct(attn, 'conv1d.weight', hf_sd, lp + 'conv1d.weight', to_mcore, tp_dim=0, to_mg=conv_to_mg,
                      to_hf=conv_to_hf)
         self._direct(attn, 'A_log', hf_sd, lp + 'A_log', to_mcore, tp_dim=0)
@@ -446,6 +495,9 @@ class GPTBridge:
                 full = self._get(p, tp_dim, is_expert)
                 if full is None:
                     continue
+                if self.hf_fused_gate_up:
+                    self._emit(hf_sd, fused, full)
+                    continue
                 g, u = full.chunk(2, dim=0)
                 self._emit(hf_sd, gk, g)
                 self._emit(hf_sd, uk, u)
@@ -475,6 +527,7 @@ class GPTBridge:
         fc2 = experts.linear_fc2.weight if experts is not None else None
         glu = cfg.gated_linear_unit
         _, etp, etp_rank = self._group_info(True)
+        n_gate, n_up, n_down = self.hf_expert_proj_names
         if to_mcore:
             if experts is None:
                 return
@@ -492,11 +545,11 @@ class GPTBridge:
                 for e in range(ep_rank * El, (ep_rank + 1) * El):
                     p = f'{ep_prefix}{e}.'
                     if glu:
-                        l1.append(torch.cat([self._load_hf(hf_sd, p + 'gate_proj.weight'),
-                                             self._load_hf(hf_sd, p + 'up_proj.weight')], dim=0))
+                        l1.append(torch.cat([self._load_hf(hf_sd, p + n_gate + '.weight'),
+                                             self._load_hf(hf_sd, p + n_up + '.weight')], dim=0))
                     else:
-                        l1.append(self._load_hf(hf_sd, p + 'up_proj.weight'))
-                    l2.append(self._load_hf(hf_sd, p + 'down_proj.weight'))
+                        l1.append(self._load_hf(hf_sd, p + n_up + '.weight'))
+                    l2.append(self._load_hf(hf_sd, p + n_down + '.weight'))
                 w1, w2 = torch.stack(l1), torch.stack(l2)
             w1s = torch.stack([shard(w1[i], 'glu' if glu else 0, etp_rank, etp) for i in range(El)])
             w2s = torch.stack([shard(w2[i], 1, etp_rank, etp) for i in range(El)])
@@ -523,11 +576,11 @@ class GPTBridge:
                 p = f'{ep_prefix}{e}.'
                 if glu:
                     g, u = w1[e].chunk(2, dim=0)
-                    self._emit(hf_sd, p + 'gate_proj.weight', g)
-                    self._emit(hf_sd, p + 'up_proj.weight', u)
+                    self._emit(hf_sd, p + n_gate + '.weight', g)
+                    self._emit(hf_sd, p + n_up + '.weight', u)
                 else:
-                    self._emit(hf_sd, p + 'up_proj.weight', w1[e])
-                self._emit(hf_sd, p + 'down_proj.weight', w2[e])
+                    self._emit(hf_sd, p + n_up + '.weight', w1[e])
+                self._emit(hf_sd, p + n_down + '.weight', w2[e])
 
     def _set_moe(self, mlp, hf_sd, prefix: str, to_mcore: bool):
         cfg = self.config
@@ -574,7 +627,8 @@ class GPTBridge:
     def _convert(self, mg_models: List[nn.Module], hf_sd: Dict[str, Any], to_mcore: bool, tqdm_desc: str = ''):
         """Drives all slots.  Load: fills the model, yields nothing.  Export: yields ``(hf_key, tensor)``."""
         from ..utils.megatron_utils import unwrap_model
-        mg_models = [self._language_model(m) for m in unwrap_model(list(mg_models))]
+        wrappers = unwrap_model(list(mg_models))
+        mg_models = [self._language_model(m) for m in wrappers]
         cfg = self.config
         first = next((m for m in mg_models if getattr(m, 'pre_process', False)), None)
         last = next((m for m in mg_models if getattr(m, 'post_process', False)), None)
@@ -586,6 +640,9 @@ class GPTBridge:
             return items
 
         self._convert_pre_process(first, out, to_mcore)
+        if not to_mcore:
+            yield from flush()
+        self._convert_hf_modules(wrappers, out, to_mcore)
         if not to_mcore:
             yield from flush()
         layer_iter: Iterable[int] = range(cfg.num_layers)
@@ -609,6 +666,57 @@ class GPTBridge:
         self._convert_post_process(last, out, to_mcore)
         if not to_mcore:
             yield from flush()
+
+    def _find_tower(self, wrappers):
+        for m in wrappers:
+            while hasattr(m, 'base_model') or (hasattr(m, 'model') and not hasattr(m, 'language_model')
+                                               and not hasattr(m, 'decoder')):
+                m = m.base_model if hasattr(m, 'base_model') else m.model
+            tower = getattr(m, 'visual', None)
+            if tower is not None:
+                return tower
+        return None
+
+    def _convert_hf_modules(self, wrappers, hf_sd, to_mcore: bool):
+        """Media towers keep their Hugging Face parameter names: each ``module_mapping`` entry (HF prefix ->
+        attribute of the tower wrapper) is copied tensor by tensor.  Towers are replicated over TP and live on
+        the first pipeline stage; on export that stage's ranks publish the key list so the others can take part
+        in the broadcasts.  Parity: reference ``src/mcore_bridge/bridge/gpt_bridge.py:2009-2042``."""
+        meta = self.config.model_meta
+        if getattr(meta, 'visual_cls', None) is None or self.config.language_model_only:
+            return
+        tower = self._find_tower(wrappers)
+        mapping = dict(meta.visual_cls.module_mapping)
+        if to_mcore:
+            if tower is None:
+                return
+            for hf_prefix, attr in mapping.items():
+                sub = deep_getattr(tower, attr)
+                state = sub.state_dict(keep_vars=True)
+                for name, t in state.items():
+                    key = f'{hf_prefix}.{name}'
+                    if key not in hf_sd:
+                        if isinstance(t, nn.Parameter):
+                            raise KeyError(f'{key} is missing from the checkpoint')
+                        continue              # non-persistent-like buffers recomputed at construction
+                    with torch.no_grad():
+                        t.copy_(self._load_hf(hf_sd, key).to(dtype=t.dtype, device=t.device))
+            return
+        names = None
+        if tower is not None:
+            names = []
+            for hf_prefix, attr in mapping.items():
+                sub = deep_getattr(tower, attr)
+                names += [(f'{hf_prefix}.{n}', attr, n) for n in sub.state_dict().keys()]
+        if ps.get_world_size('pp') > 1:
+            box = [None] * ps.get_world_size('pp')
+            dist.all_gather_object(box, names, group=ps.get_group('pp'))
+            names = next((b for b in box if b is not None), None)
+        for key, attr, n in names or []:
+            t = None
+            if tower is not None:
+                t = deep_getattr(tower, attr).state_dict(keep_vars=True)[n].detach()
+            self._emit(hf_sd, key, self._broadcast_pp(t, self._device))
 
     def _language_model(self, m):
         while hasattr(m, 'base_model') or (hasattr(m, 'model') and not hasattr(m, 'decoder')):
@@ -660,6 +768,8 @@ class GPTBridge:
             sd = loader.get_state_dict()
             if converter is not None:
                 sd = {k2: v2 for k, v in sd.items() for k2, v2 in self._apply_converter(converter, k, v)}
+            if (self.hf_state_dict_mapping or self.hf_load_aliases) and not peft_format:
+                sd = {self._modernise_key(k): v for k, v in sd.items()}
             if peft_format:
                 from .peft_bridge import load_adapter
                 load_adapter(self, mg_models, sd, adapter_name)
@@ -667,6 +777,19 @@ class GPTBridge:
                 for _ in self._convert(mg_models, sd, True, tqdm_desc='Loading: '):
                     pass
         self._peft_format = False
+
+    def _legacy_key(self, key: str) -> str:
+        """Inverse of ``_modernise_key``: such checkpoints are written in the layout they are published in."""
+        for old, new in self.hf_state_dict_mapping.items():
+            if key.startswith(new + '.'):
+                return old + key[len(new):]
+        return key
+
+    def _modernise_key(self, key: str) -> str:
+        for old, new in {**self.hf_state_dict_mapping, **self.hf_load_aliases}.items():
+            if key.startswith(old + '.') and not key.startswith(new + '.'):
+                return new + key[len(old):]
+        return key
 
     @staticmethod
     def _apply_converter(converter, key, value):
@@ -691,6 +814,8 @@ class GPTBridge:
                 gen = self._convert(mg_models, {}, False, tqdm_desc=tqdm_desc)
             with torch.no_grad():
                 for k, v in gen:
+                    if self.hf_state_dict_mapping and not peft_format:
+                        k = self._legacy_key(k)
                     if converter is not None:
                         for k2, v2 in self._apply_converter(converter, k, v):
                             yield k2, v2

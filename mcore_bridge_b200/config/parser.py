@@ -208,6 +208,8 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
         n_shared = res.pop('n_shared_experts')
     elif llm in {'ernie4_5', 'ernie4_5_moe', 'glm4'}:
         res['rotary_interleaved'] = True
+        if llm == 'glm4':
+            res['post_sublayer_layernorm'] = True
     elif hf_type in {'gemma4', 'gemma4_unified'}:
         res['qk_layernorm'] = True
         res['window_size'] = f'{window - 1},0'
@@ -237,8 +239,14 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
         res.setdefault('linear_attention_freq', 4)
     elif llm == 'minimax_m2':
         res['add_qkv_bias'] = False
+        res['qk_layernorm_full'] = True
+        # the architecture always routes with sigmoid scores plus a correction bias, whether or not the config
+        # spells it out
+        res.setdefault('moe_router_score_function', 'sigmoid')
+        res['moe_router_enable_expert_bias'] = True
     elif llm == 'olmoe':
         res['qk_layernorm'] = True
+        res['qk_layernorm_full'] = True
     elif hf_type == 'llama4':
         if res.pop('qk_layernorm', False):
             res['qk_l2_norm'] = True
@@ -252,6 +260,7 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
             res['moe_layer_freq'] = '[' + ','.join(pat) + ']'
     elif hf_type == 'glm4v':
         res['rotary_interleaved'] = True
+        res['post_sublayer_layernorm'] = True
     elif llm == 'bailing_hybrid':
         res.update(qk_layernorm=True, add_qkv_bias=False, moe_router_score_function='sigmoid',
                    moe_router_load_balancing_type='seq_aux_loss')

@@ -49,6 +49,28 @@ class CoreAttention(nn.Module):
                          sinks=sinks, seq_start=ctx.seq_start)
 
 
+class _ShardedChannelNorm(nn.Module):
+    """RMSNorm over ``full`` channels of which this TP rank holds ``local`` (whole heads): the mean square is summed
+    over the TP group in forward and backward, the weight shard scales the local channels.  Equivalent to
+    gathering the heads, normalising and re-scattering (reference ``src/mcore_bridge/model/gpts/olmoe.py:55-72``)
+    at a fraction of the traffic (one float per token instead of the activations)."""
+
+    def __init__(self, config, local: int, full: int):
+        super().__init__()
+        from .linear import _set_tp_attrs
+        self.eps, self.full = config.layernorm_epsilon, full
+        self.weight = nn.Parameter(torch.ones(local, dtype=config.params_dtype))
+        _set_tp_attrs(self.weight, local != full, 0)
+
+    def forward(self, x):                      # [T, heads_local, d]
+        from ..parallel import mappings as M
+        xf = x.float()
+        ss = M.all_reduce_both(xf.pow(2).sum(dim=(-1, -2)), 'tp')
+        inv = torch.rsqrt(ss / self.full + self.eps)
+        y = xf * inv[:, None, None] * self.weight.float().view(x.shape[1], x.shape[2])
+        return y.to(x.dtype)
+
+
 class SelfAttention(nn.Module):
 
     def __init__(self, config, layer_number: int, fuse_input_norm: bool = True, use_rope: bool = True,
@@ -70,7 +92,13 @@ class SelfAttention(nn.Module):
         qkv_out = (self.nq * (2 if self.gate else 1) + 2 * self.ng) * self.d
         cls = LayerNormColumnParallelLinear if fuse_input_norm else ColumnParallelLinear
         self.linear_qkv = cls(config.hidden_size, qkv_out, config, bias=config.add_qkv_bias or config.add_bias_linear)
-        if config.qk_layernorm:
+        self.q_norm = self.k_norm = None
+        if config.qk_layernorm and config.qk_layernorm_full:
+            # one RMSNorm over all heads' channels; the weight is sharded by head, the mean square is reduced over TP
+            self.q_layernorm = self.k_layernorm = None
+            self.q_norm = _ShardedChannelNorm(config, self.nq_local * self.d, self.nq * self.d)
+            self.k_norm = _ShardedChannelNorm(config, self.ng_local * self.d, self.ng * self.d)
+        elif config.qk_layernorm:
             self.q_layernorm = Norm(config, self.d, sequence_parallel_grad=False)
             self.k_layernorm = Norm(config, self.d, sequence_parallel_grad=False)
         else:
@@ -93,9 +121,17 @@ class SelfAttention(nn.Module):
                 cos, sin = ctx.cos, ctx.sin
         wq = self.q_layernorm.weight if self.q_layernorm is not None else None
         wk = self.k_layernorm.weight if self.k_layernorm is not None else None
-        q, k, v, gate = qkv_split_norm_rope(qkv, wq, wk, cos, sin, self.ng_local, self.qpg, self.d, self.gate,
-                                            cfg.rotary_interleaved, cfg.layernorm_epsilon,
-                                            cfg.layernorm_zero_centered_gamma)
+        if self.q_norm is not None:
+            q, k, v, gate = qkv_split_norm_rope(qkv, None, None, None, None, self.ng_local, self.qpg, self.d,
+                                                self.gate, cfg.rotary_interleaved, cfg.layernorm_epsilon, False)
+            q, k = self.q_norm(q), self.k_norm(k)
+            if cos is not None:
+                from ..ops.rope import apply_rope
+                q, k = apply_rope(q, cos, sin, cfg.rotary_interleaved), apply_rope(k, cos, sin, cfg.rotary_interleaved)
+        else:
+            q, k, v, gate = qkv_split_norm_rope(qkv, wq, wk, cos, sin, self.ng_local, self.qpg, self.d, self.gate,
+                                                cfg.rotary_interleaved, cfg.layernorm_epsilon,
+                                                cfg.layernorm_zero_centered_gamma)
         if self.qk_l2_norm:
             from ..ops.norm import l2norm
             q, k = l2norm(q), l2norm(k)

@@ -40,6 +40,8 @@ def padded_vocab(vocab_size: int, tp: int) -> int:
 
 
 class GPTModel(nn.Module):
+    # names of extra keyword inputs a multimodal wrapper forwards to the decoder blocks untouched
+    extra_forward_keys = []
 
     def __init__(self, config, pre_process: bool = True, post_process: bool = True, vp_stage: Optional[int] = None):
         super().__init__()
@@ -79,6 +81,9 @@ class GPTModel(nn.Module):
         if isinstance(input_tensor, (list, tuple)):
             input_tensor = input_tensor[0]
         self.decoder.set_input_tensor(input_tensor)
+
+    def get_input_tensor(self):
+        return self.decoder.input_tensor
 
     def shared_embedding_or_output_weight(self):
         if self.pre_process:

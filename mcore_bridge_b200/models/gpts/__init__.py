@@ -1,1 +1,1 @@
-from . import llm, qwen3_next  # noqa: F401
+from . import families, llm, qwen3_next  # noqa: F401

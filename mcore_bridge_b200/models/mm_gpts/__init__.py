@@ -1,0 +1,1 @@
+from . import qwen, vision_families  # noqa: F401

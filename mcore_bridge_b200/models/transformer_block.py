@@ -90,10 +90,28 @@ class TransformerBlock(nn.Module):
     def set_input_tensor(self, t):
         self.input_tensor = t
 
+    def _after_layer(self, h: torch.Tensor, ctx: ForwardContext, index: int) -> torch.Tensor:
+        """Deepstack (Qwen3-VL): intermediate vision features are added to the media-token rows after each of the
+        first ``L`` decoder layers.  ``ctx.extra['deepstack_visual_embeds']`` is ``[L, n_media_local, H]`` and
+        ``ctx.extra['visual_pos_masks']`` ``[T_local]`` (already restricted to this rank's tokens); a text-only
+        batch passes no mask and contributes a zero-valued term so the tower still receives gradients.  Parity:
+        reference ``src/mcore_bridge/model/mm_gpts/qwen3_vl.py:14-47``."""
+        ds = ctx.extra.get('deepstack_visual_embeds')
+        if ds is None:
+            return h
+        layer_index = self.layer_offset + index
+        if layer_index >= ds.shape[0]:
+            return h
+        mask = ctx.extra.get('visual_pos_masks')
+        if mask is None:
+            return h + ds[layer_index].mean().to(h.dtype) * 0
+        rows = mask.reshape(-1).nonzero(as_tuple=True)[0].to(h.device)
+        return h.index_add(0, rows, ds[layer_index].to(device=h.device, dtype=h.dtype))
+
     def _run(self, start: int, end: int):
         def fn(h, ctx):
             for i in range(start, end):
-                h = self.layers[i](h, ctx)
+                h = self._after_layer(self.layers[i](h, ctx), ctx, i)
             return h
         return fn
 
@@ -119,7 +137,7 @@ class TransformerBlock(nn.Module):
                 hidden = checkpoint(self._run(i, j), hidden, ctx, use_reentrant=False)
             else:
                 j = i + 1
-                hidden = self.layers[i](hidden, ctx)
+                hidden = self._after_layer(self.layers[i](hidden, ctx), ctx, i)
             for g in range(i, j):
                 if (self.layer_offset + g) in want:
                     taps.append(hidden)

@@ -61,10 +61,17 @@ class TransformerLayer(nn.Module):
         else:
             self.pre_mlp_layernorm = None
             self.mlp = MLP(config, fuse_input_norm=True)
+        if config.post_sublayer_layernorm:
+            # sandwich norms live on the sub-modules so their names match the checkpoint layout
+            self.self_attention.post_self_attn_layernorm = Norm(config, config.hidden_size)
+            self.mlp.post_mlp_layernorm = Norm(config, config.hidden_size)
 
     def _attention(self, hidden, ctx):
         x = hidden if self.input_layernorm is None else self.input_layernorm(hidden)
-        return hidden + self.self_attention(x, ctx)
+        out = self.self_attention(x, ctx)
+        if self.config.post_sublayer_layernorm:
+            out = self.self_attention.post_self_attn_layernorm(out)
+        return hidden + out
 
     def _mlp(self, hidden, ctx: ForwardContext):
         cfg = self.config
@@ -73,6 +80,8 @@ class TransformerLayer(nn.Module):
             out = self.mlp(x, ctx.padding_mask, ctx.seg_ids, ctx.num_seqs)
         else:
             out = self.mlp(x)
+        if cfg.post_sublayer_layernorm:
+            out = self.mlp.post_mlp_layernorm(out)
         return hidden + out
 
     def _mlp_padding_free(self, hidden, ctx: ForwardContext):

@@ -166,6 +166,26 @@ class _ScatterLastDim(torch.autograd.Function):
         return all_gather_last_dim(g, ctx.group_name), None
 
 
+class _AllReduceBoth(torch.autograd.Function):
+    """Sum over the group in forward *and* backward: for statistics shared by ranks whose downstream computation
+    differs (each rank's loss term depends on every rank's contribution to the statistic)."""
+
+    @staticmethod
+    def forward(ctx, x, group_name):
+        ctx.group_name = group_name
+        return all_reduce(x.clone(), group_name)
+
+    @staticmethod
+    def backward(ctx, g):
+        return all_reduce(g.clone(), ctx.group_name), None
+
+
+def all_reduce_both(x, group_name: str = 'tp'):
+    if _size(group_name) == 1:
+        return x
+    return _AllReduceBoth.apply(x, group_name)
+
+
 def copy_to_tensor_model_parallel_region(x, group_name: str = 'tp'):
     return x if _size(group_name) == 1 else _CopyToRegion.apply(x, group_name)
 
