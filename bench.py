@@ -35,7 +35,8 @@ def parse_args():
     ap.add_argument('--seq-len', type=int, default=8192)
     ap.add_argument('--seqs-per-gpu', type=int, default=8, help='packed sequences per GPU per step (weak scaling)')
     ap.add_argument('--layers', type=int, default=None, help='debug only: override the layer count (marks the run invalid)')
-    ap.add_argument('--parallelism', default='tp', choices=['tp', 'dp'])
+    ap.add_argument('--parallelism', default='tp', choices=['tp', 'dp', 'ep'],
+                    help="'ep': expert parallel over all GPUs with data parallel dense parameters (MoE models)")
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--recompute-layers', type=int, default=-1,
                     help='one GPU only: how many leading layers recompute their activations (-1: the tuned default)')
@@ -138,7 +139,8 @@ def main():
     torch.cuda.set_device(local_rank)
     ps.init_distributed()
     tp = world if args.parallelism == 'tp' else 1
-    ps.initialize_model_parallel(tensor_model_parallel_size=tp)
+    ep = world if args.parallelism == 'ep' else 1
+    ps.initialize_model_parallel(tensor_model_parallel_size=tp, expert_model_parallel_size=ep)
     hf_over = {}
     if args.layers is not None:
         hf_over['num_hidden_layers'] = args.layers
@@ -148,8 +150,15 @@ def main():
     if tp == 1:
         n_rec = args.recompute_layers if args.recompute_layers >= 0 else 12   # peak ~167 GB of 180
         recompute = dict(recompute_granularity='full', recompute_method='block', recompute_num_layers=n_rec)
+    extra = {}
+    if ep > 1 or args.parallelism == 'ep':
+        extra = dict(expert_model_parallel_size=ep, moe_aux_loss_coeff=1e-3, moe_router_load_balancing_type='aux_loss')
+        recompute = {}
+        if args.recompute_layers > 0:
+            recompute = dict(recompute_granularity='full', recompute_method='block',
+                             recompute_num_layers=args.recompute_layers)
     cfg = model_config(args.model, hf_over, bf16=True, tensor_model_parallel_size=tp, sequence_parallel=tp > 1,
-                       **recompute)
+                       **recompute, **extra)
     trainer = Trainer(cfg, TrainConfig())
     dp = ps.get_world_size('dp')
     mbs = args.micro_batch_size or min(4, world)
@@ -225,7 +234,8 @@ def main():
             'impl': 'ours',
             'config': {'model': args.model + ('' if args.layers is None else f'[layers={args.layers}: INVALID debug run]'),
                        'global_batch': global_batch, 'seq_len': args.seq_len,
-                       'parallelism': f'tp{tp}' + ('+sp' if tp > 1 else '') + (f' dp{dp}' if dp > 1 else ''),
+                       'parallelism': (f'ep{ep} dp{dp}' if args.parallelism == 'ep' else
+                                       f'tp{tp}' + ('+sp' if tp > 1 else '') + (f' dp{dp}' if dp > 1 else '')),
                        'micro_batches_per_step': n_micro, 'micro_batch_size': mbs, 'recompute': (f"full, first {recompute['recompute_num_layers']} layers" if recompute else 'none'),
                        'peak_memory_gb': round(torch.cuda.max_memory_allocated() / 2**30, 1),
                        'tp_collectives': 'fused in-kernel (NVLink peer memory)' if (tp > 1 and os.environ.get('MCB200_FUSED_COMM', '1') != '0') else ('nccl' if tp > 1 else 'none'),

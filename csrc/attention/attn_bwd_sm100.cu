@@ -11,9 +11,11 @@
 // the 128-byte swizzle, consumed K-major or MN-major), P is recomputed from the forward's log-sum-exp so nothing
 // but O and lse is kept from the forward.  Packed sequences are described by the same per-token `seq_start` array.
 //
-// Warp roles in dq and dk/dv (192 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..5
-// element-wise (thread = TMEM lane = query row in dq, key row in dk/dv).  Every wait is bounded and reports through
-// the status buffer.
+// Warp roles in dq and dk/dv (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9
+// element-wise in two groups of four (thread = TMEM lane = query row in dq, key row in dk/dv); group g takes the
+// blocks j = g, g+2, ... and owns TMEM / shared-memory buffer g, so every scheduler has two element-wise warps to
+// interleave and the exponentials of one block overlap the TMEM reads of the next.  Every wait is bounded and
+// reports through the status buffer.
 #include <climits>
 
 #include "../common/host_utils.cuh"
@@ -25,7 +27,7 @@ namespace {
 
 constexpr int TM = 128;   // rows of the CTA's resident tile (TMEM lanes)
 constexpr int BLK = 64;   // rows of the streamed blocks (MMA N for the score GEMMs, K for the gradient GEMMs)
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
@@ -70,10 +72,10 @@ __device__ __forceinline__ void store_row_chunk(uint8_t* tile, int r, int c, con
 }
 
 // one TMEM lane's D accumulator columns -> a bf16 row in global memory
-template <int D>
+template <int COLS>
 __device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst, bool ok) {
 #pragma unroll 1
-  for (int c = 0; c < D; c += 32) {
+  for (int c = 0; c < COLS; c += 32) {
     uint32_t v[32];
     tmem_ld_32x32(taddr + c, v);
     tmem_ld_wait();
@@ -261,6 +263,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else {
     const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;
     const int r = q * 32 + lane;
     const int i = m0 + r;
     const bool row_ok = i < p.T;
@@ -268,9 +271,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float lse2 = row_ok ? p.lse[(long long)head * p.T + i] * LOG2E : 0.f;
     const float dl = row_ok ? p.delta[(long long)head * p.T + i] : 0.f;
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    const uint32_t st = grp;
     bool ok = true;
-    for (int j = 0; j < nblk && ok; ++j) {
-      const uint32_t st = j & 1, ph = (j >> 1) & 1;
+    for (int j = grp; j < nblk && ok; j += 2) {
+      const uint32_t ph = (j >> 1) & 1;
       if (!mbar_wait(smem_u32(&s_full[st]), ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       if (!mbar_wait(smem_u32(&ds_empty[st]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
       tc_fence_after();
@@ -284,12 +288,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tmem_ld_32x32(tmem + lane_addr + COL_DP + st * BLK + c, dp);
         tmem_ld_wait();
         float ds[32];
+        if (full) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int key = n0 + c + e;
-          const bool vis = full || (key >= lo && key <= hi);
-          const float pr = exp2f(__uint_as_float(s[e]) * p.scale_log2 - lse2);
-          ds[e] = vis ? pr * (__uint_as_float(dp[e]) - dl) * p.scale : 0.f;
+          for (int e = 0; e < 32; ++e) {
+            const float pr = exp2f(__uint_as_float(s[e]) * p.scale_log2 - lse2);
+            ds[e] = pr * (__uint_as_float(dp[e]) - dl) * p.scale;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int key = n0 + c + e;
+            const float pr = exp2f(__uint_as_float(s[e]) * p.scale_log2 - lse2);
+            ds[e] = (key >= lo && key <= hi) ? pr * (__uint_as_float(dp[e]) - dl) * p.scale : 0.f;
+          }
         }
         store_row_chunk(tile, r, c, ds);
       }
@@ -301,7 +312,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
     if (ok && mbar_wait(smem_u32(dq_full), 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
-      store_acc_row<D>(tmem + lane_addr + COL_DQ, p.dq + ((long long)i * p.nq + head) * D, row_ok);
+      // each group writes half of the row
+      store_acc_row<D / 2>(tmem + lane_addr + COL_DQ + grp * (D / 2),
+                           p.dq + ((long long)i * p.nq + head) * D + grp * (D / 2), row_ok);
     }
   }
   tc_fence_before();
@@ -324,9 +337,9 @@ struct DkvSmem {
   static constexpr int OFF_DO = OFF_Q + 2 * BLOCK;      // 2 stages
   static constexpr int OFF_P = OFF_DO + 2 * BLOCK;      // 2 buffers
   static constexpr int OFF_DS = OFF_P + 2 * PT;         // 2 buffers
-  static constexpr int OFF_COL = OFF_DS + 2 * PT;       // per-column lse / delta / seq_start, 2 buffers
+  static constexpr int OFF_COL = OFF_DS + 2 * PT;       // per-column lse / delta / seq_start, 2 buffers per group
   static constexpr int COL_BYTES = 3 * BLK * 4;
-  static constexpr int OFF_BAR = OFF_COL + 2 * COL_BYTES;
+  static constexpr int OFF_BAR = OFF_COL + 4 * COL_BYTES;
   static constexpr int TOTAL = OFF_BAR + 1024 + 1024;
 };
 
@@ -350,8 +363,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   uint64_t* pds_full = bars + 9;       // 2
   uint64_t* pds_empty = bars + 11;     // 2
   uint64_t* out_full = bars + 13;      // 1
-  uint64_t* col_full = bars + 14;      // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* col_full = bars + 14;      // 4
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* i_end_slot = reinterpret_cast<int*>(tmem_slot + 2);
 
@@ -371,6 +384,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       mbar_init(smem_u32(&pds_full[i]), 128);
       mbar_init(smem_u32(&pds_empty[i]), 1);
       mbar_init(smem_u32(&col_full[i]), 128);
+      mbar_init(smem_u32(&col_full[2 + i]), 128);
     }
     mbar_init(smem_u32(out_full), 1);
     fence_barrier_init();
@@ -474,17 +488,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     }
   } else {
     const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;
     const int r = q * 32 + lane;            // key row of this thread
     const int n = n0 + r;
     const bool row_ok = n < p.T;
-    const int t = threadIdx.x - 64;         // 0..127 among the element-wise threads
+    const int t = (threadIdx.x - 64) & 127; // 0..127 inside the group
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    const uint32_t st = grp;
     bool ok = true;
-    for (int it = 0; it < iters && ok; ++it) {
-      const uint32_t st = it & 1, ph = (it >> 1) & 1;
+    for (int it = grp; it < iters && ok; it += 2) {
+      const uint32_t ph = (it >> 1) & 1;
       const int h = kvh * qpg + it / nqb;
       const int i0 = (qb0 + it % nqb) * BLK;
-      float* col_lse = reinterpret_cast<float*>(smem + L::OFF_COL + st * L::COL_BYTES);
+      // per-column values of this query block; two buffers per group: a thread can run at most one of the group's
+      // iterations ahead of the slowest reader, because passing col_full needs every thread's arrival
+      const uint32_t cb = st * 2 + ph;
+      float* col_lse = reinterpret_cast<float*>(smem + L::OFF_COL + cb * L::COL_BYTES);
       float* col_delta = col_lse + BLK;
       int* col_start = reinterpret_cast<int*>(col_delta + BLK);
       {
@@ -497,10 +516,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           col_delta[c] = i < p.T ? p.delta[(long long)h * p.T + i] : 0.f;
         }
       }
-      // per-column values are shared through an mbarrier (bounded wait) rather than a named barrier: with two
-      // buffers a thread can run at most one iteration ahead of the slowest reader
-      mbar_arrive(smem_u32(&col_full[st]));
-      if (!mbar_wait(smem_u32(&col_full[st]), ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+      mbar_arrive(smem_u32(&col_full[cb]));
+      if (!mbar_wait(smem_u32(&col_full[cb]), (it >> 2) & 1, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
       if (!mbar_wait(smem_u32(&s_full[st]), ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       if (!mbar_wait(smem_u32(&pds_empty[st]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
       tc_fence_after();
@@ -515,12 +532,29 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         tmem_ld_wait();
         float pr[32], ds[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int i = i0 + c + e;
-          const bool vis = full || (row_ok && i >= n && col_start[c + e] <= n);
-          const float x = exp2f(__uint_as_float(s[e]) * p.scale_log2 - col_lse[c + e]);
-          pr[e] = vis ? x : 0.f;
-          ds[e] = vis ? x * (__uint_as_float(dp[e]) - col_delta[c + e]) * p.scale : 0.f;
+        for (int e = 0; e < 32; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(col_lse + c + e);
+          const float4 d4 = *reinterpret_cast<const float4*>(col_delta + c + e);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+          if (full) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float x = exp2f(__uint_as_float(s[e + u]) * p.scale_log2 - ls[u]);
+              pr[e + u] = x;
+              ds[e + u] = x * (__uint_as_float(dp[e + u]) - dd[u]) * p.scale;
+            }
+          } else {
+            const int4 s4 = *reinterpret_cast<const int4*>(col_start + c + e);
+            const int ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i = i0 + c + e + u;
+              const bool vis = row_ok && i >= n && ss[u] <= n;
+              const float x = exp2f(__uint_as_float(s[e + u]) * p.scale_log2 - ls[u]);
+              pr[e + u] = vis ? x : 0.f;
+              ds[e + u] = vis ? x * (__uint_as_float(dp[e + u]) - dd[u]) * p.scale : 0.f;
+            }
+          }
         }
         store_row_chunk(tile_p, r, c, pr);
         store_row_chunk(tile_ds, r, c, ds);
@@ -533,8 +567,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     }
     if (ok && mbar_wait(smem_u32(out_full), 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
-      store_acc_row<D>(tmem + lane_addr + COL_DV, p.dv + ((long long)n * p.nkv + kvh) * D, row_ok);
-      store_acc_row<D>(tmem + lane_addr + COL_DK, p.dk + ((long long)n * p.nkv + kvh) * D, row_ok);
+      // group 0 writes dV, group 1 writes dK
+      if (grp == 0)
+        store_acc_row<D>(tmem + lane_addr + COL_DV, p.dv + ((long long)n * p.nkv + kvh) * D, row_ok);
+      else
+        store_acc_row<D>(tmem + lane_addr + COL_DK, p.dk + ((long long)n * p.nkv + kvh) * D, row_ok);
     }
   }
   tc_fence_before();

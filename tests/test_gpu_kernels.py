@@ -220,8 +220,10 @@ def test_bf16_model_matches_fp32_reference_model():
 
 
 @pytest.mark.parametrize('T,nq,nkv,d,segs', [(256, 2, 1, 128, [256]), (300, 4, 2, 128, [100, 200]),
-                                             (1000, 4, 4, 64, [77, 500, 423]), (1536, 4, 1, 128, [512, 1, 1023])])
-def test_attention_forward_kernel(T, nq, nkv, d, segs):
+                                             (1000, 4, 4, 64, [77, 500, 423]), (1536, 4, 1, 128, [512, 1, 1023]),
+                                             (2048, 8, 2, 128, [700, 1348])])
+def test_attention_kernels(T, nq, nkv, d, segs):
+    """Forward (two-pass softmax) and backward (delta, dQ, dK/dV kernels) against fp32 masked-softmax attention."""
     from mcore_bridge_b200.ops import attention as A
     from mcore_bridge_b200.ops import attention_cuda as AC
     torch.manual_seed(8)
@@ -230,6 +232,8 @@ def test_attention_forward_kernel(T, nq, nkv, d, segs):
     v = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16)
     cu = torch.tensor([0] + list(torch.tensor(segs).cumsum(0)), dtype=torch.int32, device=DEV)
     assert AC.supported(q, k, v, True, None, None, None)
+    from mcore_bridge_b200.ops import _lib
+    assert hasattr(_lib.lib(), 'mcb_attn_bwd')
     q2, k2, v2 = (t.clone().requires_grad_() for t in (q, k, v))
     o = AC.attention(q2, k2, v2, cu, max(segs), None)
     g = torch.randn_like(o)
