@@ -227,7 +227,9 @@ def main():
     _lib.check_status()
     if rank == 0:
         out = {
-            'metric': 'train tokens/s (device-timed, max over ranks) Qwen3-8B TP=N + SP, packed 8192',
+            'metric': ('train tokens/s (device-timed, max over ranks) Qwen3-30B-A3B EP=N, DP=N dense, seq 4096'
+                       if args.parallelism == 'ep' else
+                       'train tokens/s (device-timed, max over ranks) Qwen3-8B TP=N + SP, packed 8192'),
             'value': value, 'unit': 'tokens/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
             'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
             'dtype': 'bf16', 'data': 'synthetic (uniform-random token ids, packed segments 256-4096, random-init weights)',

@@ -41,7 +41,8 @@ def _time(fn, iters, flush=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('op', choices=['gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention'])
+    ap.add_argument('op', choices=['gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention', 'attention_bwd',
+                                  'gemm_fp8', 'quant_fp8'])
     ap.add_argument('--m', type=int, default=8192)
     ap.add_argument('--n', type=int, default=4096)
     ap.add_argument('--k', type=int, default=4096)
@@ -55,7 +56,7 @@ def main():
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     M, N, K = a.m, a.n, a.k
     res = {'op': a.op, 'm': M, 'n': N, 'k': K}
-    if a.op.startswith('gemm'):
+    if a.op in ('gemm', 'gemm_nn', 'gemm_tn'):
         x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         w = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
         dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
@@ -101,6 +102,31 @@ def main():
         t = _time(lambda: A.attention(q, k, v, cu, M), a.iters, flush)
         tf = 4.0 * M * M * nq * d / 2 / t / 1e12
         res.update(seconds=t, tflops_causal=tf, frac_of_burst_peak=tf / burst, heads=nq, peak_source=src)
+    elif a.op == 'attention_bwd':
+        from .ops import attention_cuda as AC
+        nq, nkv, d = a.n // 128 if a.n >= 128 else 32, 8, 128
+        seg = a.k if a.k <= M else M          # packed segments of --k tokens
+        q, k, v = (torch.randn(M, h, d, device=dev, dtype=torch.bfloat16, requires_grad=True) for h in (nq, nkv, nkv))
+        cu = torch.arange(0, M + 1, seg, dtype=torch.int32, device=dev)
+        o = AC.attention(q, k, v, cu, seg, None)
+        g = torch.randn_like(o)
+        t = _time(lambda: o.backward(g, retain_graph=True), a.iters, flush)
+        tf = 2.5 * 4.0 * M * seg * nq * d / 2 / t / 1e12
+        res.update(seconds=t, tflops_causal=tf, frac_of_burst_peak=tf / burst, heads=nq, segment=seg, peak_source=src)
+    elif a.op in ('gemm_fp8', 'quant_fp8'):
+        from .ops import fp8
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+        x8, sx = fp8.quantize_1x128(x)
+        w8, sw = fp8.quantize_128x128(w)
+        if a.op == 'gemm_fp8':
+            t = _time(lambda: fp8.gemm_blockscaled(x8, sx, w8, sw), a.iters, flush)
+            tf = 2.0 * M * N * K / t / 1e12
+            res.update(seconds=t, tflops=tf, frac_of_bf16_burst_peak=tf / burst, peak_source=src)
+        else:
+            t = _time(lambda: fp8.quantize_1x128(x), a.iters, flush)
+            gbs = x.numel() * 3 / t / 1e9
+            res.update(seconds=t, gbs=gbs, frac_of_hbm_peak=gbs / hbm, peak_source=src)
     torch.cuda.synchronize()
     _lib.check_status()
     print(json.dumps(res))

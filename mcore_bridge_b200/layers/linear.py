@@ -32,12 +32,18 @@ class _LinearBase(nn.Module):
         return 'etp' if is_expert else 'tp'
 
 
+def _fp8_default(config) -> bool:
+    """Block-scaled fp8 GEMMs for the decoder's linear layers when the config asks for fp8 training with the
+    blockwise recipe (128 x 128 weight blocks, 1 x 128 activation blocks)."""
+    return getattr(config, 'fp8', None) is not None and getattr(config, 'fp8_recipe', None) in (None, 'blockwise')
+
+
 class ColumnParallelLinear(_LinearBase):
     """``y = x W^T + b`` with ``W [out/tp, in]``."""
 
     def __init__(self, input_size: int, output_size: int, config, bias: bool = False, gather_output: bool = False,
                  is_expert: bool = False, skip_bias_add: bool = False, tp_group: Optional[str] = None,
-                 sequence_parallel: Optional[bool] = None, params_dtype=None):
+                 sequence_parallel: Optional[bool] = None, params_dtype=None, fp8: Optional[bool] = None):
         super().__init__()
         self.config = config
         self.group = tp_group or self._group(is_expert)
@@ -59,7 +65,7 @@ class ColumnParallelLinear(_LinearBase):
         else:
             self.register_parameter('bias', None)
         self.spec = LinearSpec(mode='column', sequence_parallel=self.sequence_parallel, group=self.group,
-                               gather_output=gather_output)
+                               gather_output=gather_output, fp8=_fp8_default(config) if fp8 is None else fp8)
 
     def forward(self, x):
         return linear(x, self.weight, self.bias, self.spec)
@@ -111,7 +117,7 @@ class RowParallelLinear(_LinearBase):
 
     def __init__(self, input_size: int, output_size: int, config, bias: bool = False, input_is_parallel: bool = True,
                  is_expert: bool = False, tp_group: Optional[str] = None, sequence_parallel: Optional[bool] = None,
-                 params_dtype=None):
+                 params_dtype=None, fp8: Optional[bool] = None):
         super().__init__()
         self.config = config
         self.group = tp_group or self._group(is_expert)
@@ -132,7 +138,8 @@ class RowParallelLinear(_LinearBase):
             mark_sequence_parallel(self.bias, config)
         else:
             self.register_parameter('bias', None)
-        self.spec = LinearSpec(mode='row', sequence_parallel=self.sequence_parallel, group=self.group)
+        self.spec = LinearSpec(mode='row', sequence_parallel=self.sequence_parallel, group=self.group,
+                               fp8=_fp8_default(config) if fp8 is None else fp8)
 
     def forward(self, x):
         return linear(x, self.weight, self.bias, self.spec)

@@ -68,7 +68,7 @@ class GPTModel(nn.Module):
             task = config.task_type
             if task == 'causal_lm' or task == 'generative_reranker':
                 self.output_layer = ColumnParallelLinear(config.hidden_size, self.vocab_size, config, bias=False,
-                                                         sequence_parallel=False)
+                                                         sequence_parallel=False, fp8=False)
                 if self.share_embeddings_and_output_weights and pre_process:
                     self.output_layer.weight = self.embedding.word_embeddings.weight
             elif task == 'seq_cls':

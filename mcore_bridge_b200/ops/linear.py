@@ -34,6 +34,7 @@ class LinearSpec:
     input_is_parallel: bool = True    # row: input already sharded on its last dim
     skip_weight_grad: bool = False
     allreduce_dgrad: bool = True      # column without SP: all-reduce dx (False when the caller does it later)
+    fp8: bool = False                 # block-scaled fp8 forward and data-gradient GEMMs (weight gradient stays bf16)
 
 
 def _weight_grad(weight: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor):
@@ -53,6 +54,27 @@ def _fused():
     return fused_comm
 
 
+def _use_fp8(spec: 'LinearSpec', x2: torch.Tensor, weight: torch.Tensor) -> bool:
+    if not spec.fp8:
+        return False
+    from . import fp8
+    return fp8.eligible(x2, weight)
+
+
+def _mm_nt(x2, weight, bias, use_fp8: bool):
+    if use_fp8:
+        from . import fp8
+        return fp8.mm_nt(x2, weight, bias)
+    return gemm.mm_nt(x2, weight, bias=bias)
+
+
+def _mm_nn(dy2, weight, use_fp8: bool):
+    if use_fp8:
+        from . import fp8
+        return fp8.mm_nn(dy2, weight)
+    return gemm.mm_nn(dy2, weight)
+
+
 class _LinearFn(torch.autograd.Function):
 
     @staticmethod
@@ -64,30 +86,33 @@ class _LinearFn(torch.autograd.Function):
         n = ps.get_world_size(spec.group) if spec.mode else 1
         ctx.n = n
         ctx.has_bias = bias is not None
+        f8 = ctx.fp8 = _use_fp8(spec, x2, weight)
         if spec.mode == 'column' and spec.sequence_parallel and n > 1:
             fc = _fused()
-            res = fc.all_gather_gemm(x2, weight, bias, spec.group) if fc.enabled(x2, weight, spec.group) else None
+            res = fc.all_gather_gemm(x2, weight, bias, spec.group) if (not f8 and fc.enabled(x2, weight, spec.group)) \
+                else None
             if res is not None:
                 y, x_full = res
             else:
                 x_full = M.all_gather_dim0(x2, spec.group)
-                y = gemm.mm_nt(x_full, weight, bias=bias)
+                y = _mm_nt(x_full, weight, bias, f8)
             # the gathered input feeds the weight gradient; under per-layer recompute it lives only briefly
             ctx.save_for_backward(x_full, weight)
             return y
         if spec.mode == 'row' and n > 1:
             if spec.sequence_parallel:
                 fc = _fused()
-                y = fc.gemm_reduce_scatter(x2, weight, spec.group) if fc.enabled(x2, weight, spec.group) else None
+                y = fc.gemm_reduce_scatter(x2, weight, spec.group) if (not f8 and fc.enabled(x2, weight, spec.group)) \
+                    else None
                 if y is None:
-                    y = M.reduce_scatter_dim0(gemm.mm_nt(x2, weight), spec.group)
+                    y = M.reduce_scatter_dim0(_mm_nt(x2, weight, None, f8), spec.group)
             else:
-                y = M.all_reduce(gemm.mm_nt(x2, weight), spec.group)
+                y = M.all_reduce(_mm_nt(x2, weight, None, f8), spec.group)
             if bias is not None:
                 y = y + bias
             ctx.save_for_backward(x2, weight)
             return y
-        y = gemm.mm_nt(x2, weight, bias=bias)
+        y = _mm_nt(x2, weight, bias, f8)
         ctx.save_for_backward(x2, weight)
         return y.view(*x.shape[:-1], weight.shape[0])
 
@@ -102,13 +127,15 @@ class _LinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1] and not spec.skip_weight_grad
         dx = dw = db = None
+        f8 = ctx.fp8
         if spec.mode == 'column' and spec.sequence_parallel and n > 1:
             x_full = x2  # saved gathered input
             if need_dx:
                 fc = _fused()
-                dx = fc.gemm_reduce_scatter_nn(dy2, weight, spec.group) if fc.enabled(dy2, weight, spec.group) else None
+                dx = fc.gemm_reduce_scatter_nn(dy2, weight, spec.group) if (not f8 and fc.enabled(dy2, weight, spec.group)) \
+                    else None
                 if dx is None:
-                    dx = M.reduce_scatter_dim0(gemm.mm_nn(dy2, weight), spec.group)
+                    dx = M.reduce_scatter_dim0(_mm_nn(dy2, weight, f8), spec.group)
             if need_dw:
                 dw = _weight_grad(weight, dy2, x_full)
             if ctx.has_bias:
@@ -118,25 +145,25 @@ class _LinearFn(torch.autograd.Function):
             if spec.sequence_parallel:
                 fc = _fused()
                 res = None
-                if need_dx and fc.enabled(dy2, weight, spec.group):
+                if need_dx and not f8 and fc.enabled(dy2, weight, spec.group):
                     res = fc.all_gather_gemm_nn(dy2, weight, spec.group)
                 if res is not None:
                     dx, dy_full = res
                 else:
                     dy_full = M.all_gather_dim0(dy2, spec.group)
                     if need_dx:
-                        dx = gemm.mm_nn(dy_full, weight)
+                        dx = _mm_nn(dy_full, weight, f8)
             else:
                 dy_full = dy2
                 if need_dx:
-                    dx = gemm.mm_nn(dy_full, weight)
+                    dx = _mm_nn(dy_full, weight, f8)
             if need_dw:
                 dw = _weight_grad(weight, dy_full, x2)
             if ctx.has_bias:
                 db = dy2.float().sum(0).to(dy.dtype)
             return (dx.view(ctx.x_shape) if dx is not None else None), dw, db, None
         if need_dx:
-            dx = gemm.mm_nn(dy2, weight)
+            dx = _mm_nn(dy2, weight, f8)
             if spec.mode == 'column' and n > 1 and spec.allreduce_dgrad:
                 dx = M.all_reduce(dx, spec.group)
             dx = dx.view(ctx.x_shape)

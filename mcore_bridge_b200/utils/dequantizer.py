@@ -27,8 +27,9 @@ class Fp8Dequantizer:
         rows, cols = q.shape[-2:]
         srows, scols = scales.shape[-2:]
         bm, bn = self.block_size
-        bm = bm or -(-rows // srows)
-        bn = bn or -(-cols // scols)
+        # the usual checkpoints use 128 x 128 blocks; anything else is inferred from the scale grid
+        bm = bm or (128 if -(-rows // 128) == srows else -(-rows // srows))
+        bn = bn or (128 if -(-cols // 128) == scols else -(-cols // scols))
         s = scales.to(torch.float32)
         s = s.repeat_interleave(bm, dim=-2)[..., :rows, :].repeat_interleave(bn, dim=-1)[..., :, :cols]
         return q * s

@@ -274,3 +274,41 @@ def test_router_kernel_matches_torch(E, k, sig, groups):
     ((dense * w).sum() + (ssum * v).sum()).backward()
     ((dense_ref * w).sum() + (s_ref.sum(0) * v).sum()).backward()
     assert rel(lg.grad, lr.grad) < 1e-3
+
+
+@pytest.mark.parametrize('M,N,K', [(256, 256, 512), (1000, 384, 1024), (4096, 2048, 7168)])
+def test_fp8_blockscaled_gemm_and_quant(M, N, K):
+    """Quantisation kernels equal the torch restatement bit for bit; the GEMM equals the fp32 product of the
+    dequantised operands."""
+    from mcore_bridge_b200.ops import fp8
+    torch.manual_seed(11)
+    x = (torch.randn(M, K, device=DEV) * torch.rand(M, 1, device=DEV) * 3).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    x8, sx = fp8.quantize_1x128(x)
+    x8r, sxr = fp8.quantize_1x128_ref(x)
+    assert torch.equal(sx, sxr)
+    assert (x8.float() - x8r.float()).abs().max().item() == 0
+    w8, sw, w8t, swt = fp8.quantize_128x128(w, with_transpose=True)
+    w8r, swr = fp8.quantize_128x128_ref(w)
+    assert torch.equal(sw, swr) and torch.equal(swt, swr.t())
+    assert (w8.float() - w8r.float()).abs().max().item() == 0
+    assert torch.equal(w8t.view(torch.uint8), w8.view(torch.uint8).t())
+    c = fp8.gemm_blockscaled(x8, sx, w8, sw)
+    ref = fp8.gemm_blockscaled_ref(x8, sx, w8, sw, out_dtype=torch.float32)
+    assert rel(c, ref) < 5e-3
+    # against the unquantised product: fp8 rounding only
+    assert rel(c, x.float() @ w.float().t()) < 6e-2
+
+
+def test_fp8_linear_forward_backward():
+    from mcore_bridge_b200.ops.linear import LinearSpec, linear
+    torch.manual_seed(12)
+    x = torch.randn(512, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(768, 1024, device=DEV) * 0.03).to(torch.bfloat16).requires_grad_()
+    y = linear(x, w, None, LinearSpec(fp8=True))
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(g.float())
+    assert rel(y, yr) < 6e-2 and rel(x.grad, xr.grad) < 6e-2 and rel(w.grad, wr.grad) < 2e-2
