@@ -343,6 +343,9 @@ class GPTBridge:
         cfg = self.config
         attn = layer.self_attention if layer is not None else None
         ap = f'{prefix}{self.hf_attn_prefix}.'
+        if self._layer_is_linear_attention(prefix, 'lightning'):
+            self._set_lightning(layer, attn, hf_sd, prefix, ap, to_mcore)
+            return
         if cfg.multi_latent_attention:
             self._set_mla(layer, attn, hf_sd, prefix, ap, to_mcore)
             return
@@ -370,9 +373,23 @@ class GPTBridge:
 
     hf_linear_attn_prefix = 'linear_attn'
 
-    def _layer_is_linear_attention(self, prefix: str) -> bool:
+    def _set_lightning(self, layer, attn, hf_sd, prefix: str, ap: str, to_mcore: bool):
+        """Lightning-attention layers of the Ling / Ring hybrids: ordinary fused QKV, per-head q/k norms, the output
+        gate projection ``g_proj`` (column parallel) and the group norm ``g_norm`` (sharded with the heads)
+        (reference ``src/mcore_bridge/model/gpts/bailing_hybrid.py:27-45``)."""
         cfg = self.config
-        if cfg.linear_attention_freq is None or cfg.experimental_attention_variant != 'gated_delta_net':
+        self._direct(layer, 'input_layernorm.weight', hf_sd, prefix + self.hf_input_layernorm_key, to_mcore)
+        self._set_qkv(attn, hf_sd, ap, to_mcore)
+        self._direct(attn, 'linear_proj.weight', hf_sd, ap + self.hf_o_proj_key, to_mcore, tp_dim=1)
+        if cfg.qk_layernorm:
+            self._direct(attn, 'q_layernorm.weight', hf_sd, ap + self.hf_q_norm_key, to_mcore)
+            self._direct(attn, 'k_layernorm.weight', hf_sd, ap + self.hf_k_norm_key, to_mcore)
+        self._direct(attn, 'g_proj.weight', hf_sd, ap + 'g_proj.weight', to_mcore, tp_dim=0)
+        self._direct(attn, 'g_norm.weight', hf_sd, ap + 'g_norm.weight', to_mcore, tp_dim=0)
+
+    def _layer_is_linear_attention(self, prefix: str, variant: str = 'gated_delta_net') -> bool:
+        cfg = self.config
+        if cfg.linear_attention_freq is None or cfg.experimental_attention_variant != variant:
             return False
         m = re.search(r'\.(\d+)\.$', prefix)
         idx = int(m.group(1)) if m else 0

@@ -263,7 +263,14 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
         res['post_sublayer_layernorm'] = True
     elif llm == 'bailing_hybrid':
         res.update(qk_layernorm=True, add_qkv_bias=False, moe_router_score_function='sigmoid',
-                   moe_router_load_balancing_type='seq_aux_loss')
+                   moe_router_load_balancing_type='seq_aux_loss', experimental_attention_variant='lightning')
+        # every `layer_group_size`-th layer and the tail that does not fill a group use full (MLA) attention
+        group = getattr(hf_config, 'layer_group_size', None) if not isinstance(hf_config, dict) else \
+            hf_config.get('layer_group_size')
+        if group:
+            n = res['num_layers']
+            tail = n // group * group
+            res['linear_attention_freq'] = [0 if ((i + 1) % group == 0 or i >= tail) else 1 for i in range(n)]
 
     if 'partial_rotary_factor' not in res and 'partial_rotary_factor' in rope_scaling:
         res['partial_rotary_factor'] = rope_scaling['partial_rotary_factor']

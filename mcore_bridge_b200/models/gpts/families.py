@@ -44,6 +44,10 @@ class BailingMoeBridge(GPTBridge):
     hf_mtp_final_layernorm_key = 'final_layernorm.weight'
 
 
+class BailingHybridBridge(BailingMoeBridge):
+    """Ling-2.5 / Ring-linear: groups of lightning-attention layers closed by an MLA layer."""
+
+
 class Qwen3EmbBridge(GPTBridge):
     """Qwen3-Embedding checkpoints are a bare ``Qwen3Model``: keys lack the ``model.`` prefix."""
     hf_layers_prefix = 'layers'
@@ -56,4 +60,5 @@ register_model(ModelMeta(ModelType.olmoe, ['olmoe'], bridge_cls=OLMoEBridge))
 register_model(ModelMeta(ModelType.minimax_m2, ['minimax_m2'], bridge_cls=MinimaxM2Bridge))
 register_model(ModelMeta(ModelType.hy_v3, ['hy_v3'], bridge_cls=HyV3Bridge))
 register_model(ModelMeta(ModelType.bailing_moe, ['bailing_moe'], bridge_cls=BailingMoeBridge))
+register_model(ModelMeta(ModelType.bailing_hybrid, ['bailing_hybrid'], bridge_cls=BailingHybridBridge))
 register_model(ModelMeta(ModelType.qwen3_emb, [], bridge_cls=Qwen3EmbBridge))

@@ -48,6 +48,10 @@ class TransformerLayer(nn.Module):
         if self.is_linear_attention and variant == 'gated_delta_net':
             from ..layers.gated_delta_net import GatedDeltaNet
             self.self_attention = GatedDeltaNet(config, layer_number)
+        elif self.is_linear_attention and variant == 'lightning':
+            from ..layers.lightning_attention import LightningAttention
+            self.input_layernorm = Norm(config, config.hidden_size)
+            self.self_attention = LightningAttention(config, layer_number)
         elif config.multi_latent_attention:
             from ..layers.mla import MLASelfAttention
             self.input_layernorm = Norm(config, config.hidden_size)

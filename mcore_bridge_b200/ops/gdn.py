@@ -118,3 +118,175 @@ def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     y = weight.float() * y.to(x.dtype).float()
     return (y * F.silu(gate.float())).to(x.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ simple GLA
+def simple_gla_ref(q, k, v, decay, cu_seqlens=None, scale: Optional[float] = None) -> torch.Tensor:
+    """Linear attention with a constant per-head log-decay ``decay [h] <= 0``::
+
+        S_t = exp(decay_h) * S_{t-1} + k_t v_t^T,      o_t = scale * S_t^T q_t
+
+    evaluated per sequence as ``(Q K^T * D) V`` with ``D[i, j] = exp(decay * (i - j))`` for ``j <= i`` (fp32).  The
+    recurrence the reference runs through fla's ``fused_recurrent_simple_gla``
+    (``src/mcore_bridge/model/gpts/bailing_hybrid.py:180-193``)."""
+    T, h, dk = q.shape
+    scale = dk**-0.5 if scale is None else scale
+    out = torch.empty(T, h, v.shape[-1], dtype=torch.float32, device=q.device)
+    for s, e in _bounds(cu_seqlens, T):
+        L = e - s
+        pos = torch.arange(L, device=q.device, dtype=torch.float32)
+        diff = pos[:, None] - pos[None, :]
+        D = torch.exp(decay.float()[:, None, None] * diff.clamp(min=0)[None]) * (diff >= 0)[None]
+        att = torch.einsum('ihd,jhd->hij', q[s:e].float() * scale, k[s:e].float()) * D
+        out[s:e] = torch.einsum('hij,jhd->ihd', att, v[s:e].float())
+    return out.to(v.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ CUDA dispatch
+def _cuda_ok(*ts) -> bool:
+    from . import _lib
+    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts) and _lib.available()
+
+
+def _seq_start(cu_seqlens, T, device):
+    from .attention_cuda import seq_start_from_cu
+    return seq_start_from_cu(cu_seqlens, T, device)
+
+
+class _ConvFn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, weight, seq_start, act):
+        import ctypes
+
+        from . import _lib
+        T, C = x.shape
+        x, w = x.contiguous(), weight.contiguous()
+        y = torch.empty_like(x)
+        rc = _lib.lib().mcb_conv1d_silu_fwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(seq_start), _lib.ptr(y), ctypes.c_int(T),
+                                            ctypes.c_int(C), ctypes.c_int(w.shape[1]), ctypes.c_int(int(act)),
+                                            _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_conv1d_silu_fwd')
+        ctx.save_for_backward(x, w, seq_start)
+        ctx.act = act
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        import ctypes
+
+        from . import _lib
+        x, w, seq_start = ctx.saved_tensors
+        T, C = x.shape
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=x.device)
+        rc = _lib.lib().mcb_conv1d_silu_bwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(dy), _lib.ptr(seq_start), _lib.ptr(dx),
+                                            _lib.ptr(dw), ctypes.c_int(T), ctypes.c_int(C), ctypes.c_int(w.shape[1]),
+                                            ctypes.c_int(int(ctx.act)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_conv1d_silu_bwd')
+        return dx, dw.to(w.dtype), None, None
+
+
+class _GatedNormFn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, gate, weight, eps):
+        import ctypes
+
+        from . import _lib
+        D = x.shape[-1]
+        x2, z2, w = x.reshape(-1, D).contiguous(), gate.reshape(-1, D).contiguous(), weight.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rc = _lib.lib().mcb_gated_rmsnorm_fwd(_lib.ptr(x2), _lib.ptr(z2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(rstd),
+                                              ctypes.c_longlong(rows), ctypes.c_int(D), ctypes.c_float(eps),
+                                              _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_gated_rmsnorm_fwd')
+        ctx.save_for_backward(x2, z2, w, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        import ctypes
+
+        from . import _lib
+        x2, z2, w, rstd = ctx.saved_tensors
+        rows, D = x2.shape
+        dy2 = dy.reshape(rows, D).contiguous()
+        dx, dz = torch.empty_like(x2), torch.empty_like(z2)
+        dw = torch.zeros(D, dtype=torch.float32, device=x2.device)
+        rc = _lib.lib().mcb_gated_rmsnorm_bwd(_lib.ptr(x2), _lib.ptr(z2), _lib.ptr(w), _lib.ptr(dy2), _lib.ptr(rstd),
+                                              _lib.ptr(dx), _lib.ptr(dz), _lib.ptr(dw), ctypes.c_longlong(rows),
+                                              ctypes.c_int(D), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_gated_rmsnorm_bwd')
+        return dx.view(ctx.shape), dz.view(ctx.shape), dw.to(w.dtype), None
+
+
+class _SimpleGlaFn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, decay, cu_seqlens, scale):
+        import ctypes
+
+        from . import _lib
+        T, h, dk = q.shape
+        dv = v.shape[-1]
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        decay = decay.float().contiguous()
+        o = torch.empty_like(v)
+        n_seq = cu_seqlens.numel() - 1
+        rc = _lib.lib().mcb_simple_gla_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(decay), _lib.ptr(cu_seqlens),
+                                           _lib.ptr(o), ctypes.c_int(n_seq), ctypes.c_int(h), ctypes.c_int(dk),
+                                           ctypes.c_int(dv), ctypes.c_float(scale), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_simple_gla_fwd')
+        ctx.save_for_backward(q, k, v, decay, cu_seqlens)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        import ctypes
+
+        from . import _lib
+        q, k, v, decay, cu = ctx.saved_tensors
+        T, h, dk = q.shape
+        dv_ = v.shape[-1]
+        do = do.contiguous()
+        dq, dk_, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        rc = _lib.lib().mcb_simple_gla_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(do), _lib.ptr(decay),
+                                           _lib.ptr(cu), _lib.ptr(dq), _lib.ptr(dk_), _lib.ptr(dv),
+                                           ctypes.c_int(cu.numel() - 1), ctypes.c_int(h), ctypes.c_int(dk),
+                                           ctypes.c_int(dv_), ctypes.c_float(ctx.scale), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_simple_gla_bwd')
+        return dq, dk_, dv, None, None, None
+
+
+def simple_gla(q, k, v, decay, cu_seqlens=None, scale: Optional[float] = None) -> torch.Tensor:
+    """Dispatches to the recurrent CUDA kernels (bf16, square 64 / 128 state) or the torch restatement."""
+    T, h, dk = q.shape
+    scale = dk**-0.5 if scale is None else scale
+    if _cuda_ok(q, k, v) and dk == v.shape[-1] and dk in (64, 128):
+        cu = cu_seqlens if cu_seqlens is not None else torch.tensor([0, T], dtype=torch.int32, device=q.device)
+        return _SimpleGlaFn.apply(q, k, v, decay, cu.to(device=q.device, dtype=torch.int32), float(scale))
+    return simple_gla_ref(q, k, v, decay, cu_seqlens, scale)
+
+
+_causal_conv1d_silu_torch = causal_conv1d_silu
+_gated_rmsnorm_torch = gated_rmsnorm
+
+
+def causal_conv1d_silu(x, weight, bias=None, cu_seqlens=None, activation: bool = True, seq_start=None):  # noqa: F811
+    if bias is None and _cuda_ok(x, weight) and x.shape[1] % 8 == 0 and weight.shape[-1] in (2, 3, 4):
+        if seq_start is None:
+            seq_start = _seq_start(cu_seqlens, x.shape[0], x.device)
+        return _ConvFn.apply(x, weight, seq_start, bool(activation))
+    return _causal_conv1d_silu_torch(x, weight, bias, cu_seqlens, activation)
+
+
+def gated_rmsnorm(x, gate, weight, eps):  # noqa: F811
+    if _cuda_ok(x, gate, weight) and x.shape[-1] in (64, 128, 256):
+        return _GatedNormFn.apply(x, gate, weight, float(eps))
+    return _gated_rmsnorm_torch(x, gate, weight, eps)

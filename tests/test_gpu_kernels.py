@@ -312,3 +312,54 @@ def test_fp8_linear_forward_backward():
     yr = xr @ wr.t()
     yr.backward(g.float())
     assert rel(y, yr) < 6e-2 and rel(x.grad, xr.grad) < 6e-2 and rel(w.grad, wr.grad) < 2e-2
+
+
+def test_linear_attention_elementwise_kernels():
+    """Causal conv1d+SiLU and gated RMSNorm kernels (forward and backward) against the torch restatements."""
+    from mcore_bridge_b200.ops import gdn as G
+    torch.manual_seed(13)
+    T, C, K = 700, 256, 4
+    cu = torch.tensor([0, 100, 101, 450, 700], dtype=torch.int32, device=DEV)
+    x = torch.randn(T, C, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(C, K, device=DEV) * 0.5).to(torch.bfloat16)
+    g = torch.randn(T, C, device=DEV, dtype=torch.bfloat16)
+    x1, w1 = x.clone().requires_grad_(), w.clone().requires_grad_()
+    y = G.causal_conv1d_silu(x1, w1, None, cu)
+    y.backward(g)
+    x2, w2 = x.float().requires_grad_(), w.float().requires_grad_()
+    yr = G._causal_conv1d_silu_torch(x2, w2, None, cu)
+    yr.backward(g.float())
+    assert rel(y, yr) < 1e-2 and rel(x1.grad, x2.grad) < 1e-2 and rel(w1.grad, w2.grad) < 1e-2
+    rows, D = 3000, 128
+    a = torch.randn(rows, D, device=DEV, dtype=torch.bfloat16)
+    z = torch.randn(rows, D, device=DEV, dtype=torch.bfloat16)
+    wn = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16)
+    gg = torch.randn(rows, D, device=DEV, dtype=torch.bfloat16)
+    a1, z1, n1 = a.clone().requires_grad_(), z.clone().requires_grad_(), wn.clone().requires_grad_()
+    o = G.gated_rmsnorm(a1, z1, n1, 1e-6)
+    o.backward(gg)
+    a2, z2, n2 = a.float().requires_grad_(), z.float().requires_grad_(), wn.float().requires_grad_()
+    orf = G._gated_rmsnorm_torch(a2, z2, n2, 1e-6)
+    orf.backward(gg.float())
+    assert rel(o, orf) < 1e-2 and rel(a1.grad, a2.grad) < 1.5e-2 and rel(z1.grad, z2.grad) < 1e-2
+    assert rel(n1.grad, n2.grad) < 1e-2
+
+
+@pytest.mark.parametrize('d', [64, 128])
+def test_simple_gla_kernels(d):
+    """Recurrent lightning-attention kernels against the masked-decay matmul form, packed sequences."""
+    from mcore_bridge_b200.ops import gdn as G
+    torch.manual_seed(14)
+    T, h = 600, 4
+    cu = torch.tensor([0, 256, 257, 600], dtype=torch.int32, device=DEV)
+    q, k, v = (torch.randn(T, h, d, device=DEV, dtype=torch.bfloat16) * 0.5 for _ in range(3))
+    decay = -torch.rand(h, device=DEV) * 0.2 - 0.01
+    g = torch.randn(T, h, d, device=DEV, dtype=torch.bfloat16)
+    q1, k1, v1 = (t.clone().requires_grad_() for t in (q, k, v))
+    o = G.simple_gla(q1, k1, v1, decay, cu)
+    o.backward(g)
+    q2, k2, v2 = (t.float().requires_grad_() for t in (q, k, v))
+    orf = G.simple_gla_ref(q2, k2, v2, decay, cu)
+    orf.backward(g.float())
+    assert rel(o, orf) < 1e-2
+    assert rel(q1.grad, q2.grad) < 1e-2 and rel(k1.grad, k2.grad) < 1e-2 and rel(v1.grad, v2.grad) < 1e-2
