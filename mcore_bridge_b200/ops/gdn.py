@@ -84,16 +84,67 @@ def _chunk_one_sequence(q, k, v, g, beta, chunk: int):
 
 
 def chunk_gated_delta_rule(q, k, v, g, beta, cu_seqlens=None, scale: Optional[float] = None, chunk: int = 64):
-    """Chunked evaluation; same signature and result as :func:`recurrent_gated_delta_rule`."""
+    """Chunked evaluation; same signature and result as :func:`recurrent_gated_delta_rule`.
+
+    All sequences are processed together: every sequence is padded to a whole number of chunks, the intra-chunk
+    quantities (decay matrix, WY solve, intra-chunk attention) are one batched computation over all chunks, and the
+    state recurrence runs over the chunk *position inside its sequence*, i.e. ``max_len / chunk`` steps of batched
+    matmuls over the sequences still alive, rather than one step per chunk of the packed stream."""
     T, h, dk = q.shape
+    dv = v.shape[-1]
+    dev = q.device
     scale = dk**-0.5 if scale is None else scale
-    qf = (q.float() * scale).transpose(0, 1)
-    kf, vf = k.float().transpose(0, 1), v.float().transpose(0, 1)
-    gf, bf = g.float().transpose(0, 1), beta.float().transpose(0, 1)
-    outs = []
-    for s, e in _bounds(cu_seqlens, T):
-        outs.append(_chunk_one_sequence(qf[:, s:e], kf[:, s:e], vf[:, s:e], gf[:, s:e], bf[:, s:e], chunk))
-    return torch.cat(outs, dim=1).transpose(0, 1).to(v.dtype)
+    bounds = _bounds(cu_seqlens, T)
+    n_chunks = [-(-(e - s) // chunk) for s, e in bounds]
+    total = sum(n_chunks)
+    # token -> slot in the chunk-padded layout
+    slot = torch.empty(T, dtype=torch.int64, device=dev)
+    first_chunk, off = [], 0
+    for (s, e), n in zip(bounds, n_chunks):
+        slot[s:e] = torch.arange(off * chunk, off * chunk + (e - s), device=dev)
+        first_chunk.append(off)
+        off += n
+    covered = torch.zeros(T, dtype=torch.bool, device=dev)
+    for s, e in bounds:
+        covered[s:e] = True
+
+    def pad(x, fill=0.0):
+        out = x.new_full((total * chunk, *x.shape[1:]), fill, dtype=torch.float32)
+        out[slot[covered]] = x[covered].float()
+        return out
+
+    qp = (pad(q) * scale).view(total, chunk, h, dk).permute(0, 2, 1, 3)          # [N, h, C, dk]
+    kp = pad(k).view(total, chunk, h, dk).permute(0, 2, 1, 3)
+    vp = pad(v).view(total, chunk, h, dv).permute(0, 2, 1, 3)
+    gp = pad(g).view(total, chunk, h).permute(0, 2, 1)                            # [N, h, C]
+    bp = pad(beta).view(total, chunk, h).permute(0, 2, 1)
+    gc = gp.cumsum(-1)
+    decay = (gc[..., :, None] - gc[..., None, :]).tril().exp().tril()
+    kb, vb = kp * bp[..., None], vp * bp[..., None]
+    eye = torch.eye(chunk, dtype=torch.float32, device=dev)
+    A = eye + ((kb @ kp.transpose(-1, -2)) * decay).tril(-1)
+    u = torch.linalg.solve_triangular(A, vb, upper=False, unitriangular=True)
+    w = torch.linalg.solve_triangular(A, kb * gc.exp()[..., None], upper=False, unitriangular=True)
+    qk = (qp @ kp.transpose(-1, -2)) * decay
+    q_dec = qp * gc.exp()[..., None]
+    g_last = gc[..., -1]                                                          # [N, h]
+    k_dec = kp * (g_last[..., None] - gc).exp()[..., None]
+    out = torch.empty(total, h, chunk, dv, dtype=torch.float32, device=dev)
+    n_seq = len(bounds)
+    S = torch.zeros(n_seq, h, dk, dv, dtype=torch.float32, device=dev)
+    first = torch.tensor(first_chunk, dtype=torch.int64, device=dev)
+    counts = torch.tensor(n_chunks, dtype=torch.int64, device=dev)
+    for i in range(max(n_chunks) if n_chunks else 0):
+        alive = (counts > i).nonzero(as_tuple=True)[0]
+        ci = first[alive] + i                                                     # chunk ids processed this step
+        Si = S[alive]
+        v_new = u[ci] - w[ci] @ Si
+        out[ci] = q_dec[ci] @ Si + qk[ci] @ v_new
+        S = S.index_copy(0, alive, Si * g_last[ci].exp()[..., None, None] + k_dec[ci].transpose(-1, -2) @ v_new)
+    o_flat = out.permute(0, 2, 1, 3).reshape(total * chunk, h, dv)
+    res = torch.zeros(T, h, dv, dtype=torch.float32, device=dev)
+    res[covered] = o_flat[slot[covered]]
+    return res.to(v.dtype)
 
 
 def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
