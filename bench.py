@@ -38,6 +38,8 @@ def parse_args():
     ap.add_argument('--parallelism', default='tp', choices=['tp', 'dp', 'ep'],
                     help="'ep': expert parallel over all GPUs with data parallel dense parameters (MoE models)")
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--lora-rank', type=int, default=0,
+                    help='train LoRA adapters (alpha = 2 * rank) on all linear layers with the base weights frozen')
     ap.add_argument('--recompute-layers', type=int, default=-1,
                     help='one GPU only: how many leading layers recompute their activations (-1: the tuned default)')
     ap.add_argument('--micro-batch-size', type=int, default=0,
@@ -157,9 +159,23 @@ def main():
         if args.recompute_layers > 0:
             recompute = dict(recompute_granularity='full', recompute_method='block',
                              recompute_num_layers=args.recompute_layers)
+    if args.lora_rank > 0:
+        recompute = {}          # frozen base weights carry no gradient or optimizer state: everything fits
     cfg = model_config(args.model, hf_over, bf16=True, tensor_model_parallel_size=tp, sequence_parallel=tp > 1,
                        **recompute, **extra)
-    trainer = Trainer(cfg, TrainConfig())
+    models = None
+    if args.lora_rank > 0:
+        from mcore_bridge_b200 import get_mcore_model
+        from mcore_bridge_b200.train.trainer import init_weights
+        from mcore_bridge_b200.tuners import LoraConfig, get_peft_model
+        tc0 = TrainConfig()
+        models = get_mcore_model(cfg)
+        for i, m in enumerate(models):
+            init_weights(m, tc0.init_std, (tc0.init_seed or 0) + i)
+        lc = LoraConfig(r=args.lora_rank, lora_alpha=2 * args.lora_rank,
+                        target_modules=['linear_qkv', 'linear_proj', 'linear_fc1', 'linear_fc2'])
+        models = [get_peft_model(m, lc) for m in models]
+    trainer = Trainer(cfg, TrainConfig(), models=models)
     dp = ps.get_world_size('dp')
     mbs = args.micro_batch_size or min(4, world)
     global_batch = args.seqs_per_gpu * world
@@ -242,6 +258,8 @@ def main():
                        'peak_memory_gb': round(torch.cuda.max_memory_allocated() / 2**30, 1),
                        'tp_collectives': 'fused in-kernel (NVLink peer memory)' if (tp > 1 and os.environ.get('MCB200_FUSED_COMM', '1') != '0') else ('nccl' if tp > 1 else 'none'),
                        'optimizer': 'AdamW, fp32 master weights and moments, fp32 gradient accumulation',
+                       'lora': (f'rank {args.lora_rank}, alpha {2 * args.lora_rank}, all linear layers'
+                                if args.lora_rank > 0 else None),
                        'l2': 'working set per step (parameters, gradients, optimizer state: > 100 GB) exceeds the 126 MB L2; no flush needed',
                        'loss': trainer.last_metrics.get('loss')},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': launches,
