@@ -10,7 +10,10 @@
 // The extra Q K^T is cheap next to the exponentials, which bound attention on this architecture, and the kernel
 // needs no accumulator rescaling traffic.
 //
-// Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..5 softmax (thread = row).
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 softmax in two groups of
+// four (thread = query row).  Group g owns score buffer g in TMEM, i.e. every other key block of both passes, so each
+// scheduler has two softmax warps to interleave (exponentials of one block overlap the TMEM reads of the next); the
+// groups exchange their partial row maxima after pass 1 and their partial row sums after pass 2 through shared memory.
 #include "../common/host_utils.cuh"
 #include "../common/ptx.cuh"
 
@@ -20,7 +23,7 @@ namespace {
 
 constexpr int BM = 128;  // queries per CTA
 constexpr int BNK = 128; // keys per block
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;
 
 struct AttnParams {
   int T, nq, nkv, d;
@@ -75,7 +78,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* p_full = bars + 13;       // 2
   uint64_t* p_empty = bars + 15;      // 2
   uint64_t* o_full = bars + 17;       // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* xchg = bars + 18;         // 2: row maxima / row sums exchanged between the softmax groups
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -100,6 +104,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(smem_u32(&p_empty[i]), 1);
     }
     mbar_init(smem_u32(o_full), 1);
+    mbar_init(smem_u32(&xchg[0]), 256);
+    mbar_init(smem_u32(&xchg[1]), 256);
     fence_barrier_init();
     fence_proxy_async_smem();
     prefetch_tensormap(&tm_q);
@@ -209,16 +215,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ softmax warps: thread = query row
     const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;
     const int r = q * 32 + lane;
     const int i = m0 + r;
     const bool row_ok = i < p.T;
     const int lo = row_ok ? p.seq_start[i] : 1, hi = row_ok ? i : 0;
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    const uint32_t sb = grp;                         // this group's score buffer
     float mx = -INFINITY;
-    uint32_t sit = 0;
     bool ok = true;
-    for (int j = 0; j < nblk && ok; ++j, ++sit) {
-      const uint32_t sb = sit & 1, sph = (sit >> 1) & 1;
+    // pass 1: score iterations sit = j (this group takes sit & 1 == grp)
+    for (int j = grp; j < nblk && ok; j += 2) {
+      const uint32_t sph = (uint32_t(j) >> 1) & 1;
       if (!mbar_wait(smem_u32(&s_full[sb]), sph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int n0 = (kb0 + j) * BNK;
@@ -243,10 +251,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_empty[sb]));
     }
+    // The row maximum is over both groups' blocks.  The partial maxima travel through the P buffers, which nothing
+    // has written yet: a group leaves its value in the buffer the *other* group owns in pass 2, so the value is
+    // overwritten only by its reader, after it has been read.
+    {
+      const int pb_mine = (grp + nblk) & 1;
+      reinterpret_cast<float*>(smem + L::OFF_P + (pb_mine ^ 1) * L::P_BYTES)[r] = mx;
+      mbar_arrive(smem_u32(&xchg[0]));
+      if (ok && !mbar_wait(smem_u32(&xchg[0]), 0, abort_flag, p.status, ST_TIMEOUT_FULL)) ok = false;
+      if (ok) mx = fmaxf(mx, reinterpret_cast<const float*>(smem + L::OFF_P + pb_mine * L::P_BYTES)[r]);
+    }
     const float m2 = (mx == -INFINITY) ? 0.f : mx * p.scale_log2;
     float sum = 0.f;
-    for (int j = 0; j < nblk && ok; ++j, ++sit) {
-      const uint32_t sb = sit & 1, sph = (sit >> 1) & 1, pb = j & 1, pph = (j >> 1) & 1;
+    // pass 2: score iterations sit = nblk + j; this group takes the j with (nblk + j) & 1 == grp, which all share
+    // one P buffer
+    const int j0 = (grp + nblk) & 1;
+    for (int j = j0; j < nblk && ok; j += 2) {
+      const uint32_t sit = uint32_t(nblk + j);
+      const uint32_t sph = (sit >> 1) & 1, pb = j & 1, pph = (uint32_t(j) >> 1) & 1;
       if (!mbar_wait(smem_u32(&s_full[sb]), sph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       if (!mbar_wait(smem_u32(&p_empty[pb]), pph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
       tc_fence_after();
@@ -259,13 +281,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_32x32(tmem + lane_addr + COL_S + sb * BNK + c, v);
         tmem_ld_wait();
         float pv[32];
+        if (full) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int key = n0 + c + e;
-          const bool vis = full || (key >= lo && key <= hi);
-          const float x = exp2f(__uint_as_float(v[e]) * p.scale_log2 - m2);
-          pv[e] = vis ? x : 0.f;
-          sum += pv[e];
+          for (int e = 0; e < 32; ++e) {
+            pv[e] = exp2f(__uint_as_float(v[e]) * p.scale_log2 - m2);
+            sum += pv[e];
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int key = n0 + c + e;
+            const float x = exp2f(__uint_as_float(v[e]) * p.scale_log2 - m2);
+            pv[e] = (key >= lo && key <= hi) ? x : 0.f;
+            sum += pv[e];
+          }
         }
         uint8_t* box = prow + (c >> 6) * (BM * 128);
 #pragma unroll
@@ -285,14 +314,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_proxy_async_smem();   // P stores -> visible to the tensor core's shared-memory reads
       mbar_arrive(smem_u32(&p_full[pb]));
     }
-    if (ok && mbar_wait(smem_u32(o_full), 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
+    // once every MMA has completed the Q tile is free: the partial row sums are exchanged through it
+    const bool done = ok && mbar_wait(smem_u32(o_full), 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    float* sbuf = reinterpret_cast<float*>(smem + L::OFF_Q);
+    if (done) sbuf[grp * BM + r] = sum;
+    mbar_arrive(smem_u32(&xchg[1]));
+    if (done && mbar_wait(smem_u32(&xchg[1]), 0, abort_flag, p.status, ST_TIMEOUT_FULL)) {
+      sum += sbuf[(grp ^ 1) * BM + r];
       tc_fence_after();
       const float inv = sum > 0.f ? 1.f / sum : 0.f;
-      __nv_bfloat16* orow = p.o + ((long long)i * p.nq + head) * D;
+      // each group writes half of the head dimension
+      __nv_bfloat16* orow = p.o + ((long long)i * p.nq + head) * D + grp * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
+      for (int c = 0; c < D / 2; c += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_addr + COL_O + c, v);
+        tmem_ld_32x32(tmem + lane_addr + COL_O + grp * (D / 2) + c, v);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
@@ -306,7 +342,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
-      if (row_ok) p.lse[(long long)head * p.T + i] = (sum > 0.f) ? (m2 + log2f(sum)) * 0.6931471805599453f : -INFINITY;
+      if (row_ok && grp == 0)
+        p.lse[(long long)head * p.T + i] = (sum > 0.f) ? (m2 + log2f(sum)) * 0.6931471805599453f : -INFINITY;
     }
   }
   tc_fence_before();
