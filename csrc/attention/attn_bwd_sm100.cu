@@ -40,6 +40,8 @@ struct BwdParams {
   __nv_bfloat16* dk;        // [T, nkv, d]
   __nv_bfloat16* dv;        // [T, nkv, d]
   int* status;
+  float* partial;           // head-split mode: [2 (dv, dk), splits, T, nkv, d] fp32 partial sums, else null
+  int splits;               // CTAs per (key tile, kv head); each takes qpg / splits query heads
 };
 
 // K-major operand: tile of `rows` x D stored as D/64 boxes of [rows x 64]; kk-th 16-wide slice of the reduction dim
@@ -89,6 +91,22 @@ __device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst
         o.w = pack_bf16x2(__uint_as_float(v[e + 6]), __uint_as_float(v[e + 7]));
         *reinterpret_cast<uint4*>(dst + c + e) = o;
       }
+    }
+  }
+}
+
+// one TMEM lane's accumulator columns -> an fp32 row in global memory
+template <int COLS>
+__device__ __forceinline__ void store_acc_row_f32(uint32_t taddr, float* dst, bool ok) {
+#pragma unroll 1
+  for (int c = 0; c < COLS; c += 32) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + c, v);
+    tmem_ld_wait();
+    if (ok) {
+#pragma unroll
+      for (int e = 0; e < 32; e += 4)
+        *reinterpret_cast<uint4*>(dst + c + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
     }
   }
 }
@@ -412,7 +430,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   const uint32_t tmem = *tmem_slot;
   const int qb0 = n0 / BLK;
   const int nqb = *i_end_slot / BLK - qb0 + 1;
-  const int iters = qpg * nqb;
+  const int hps = qpg / p.splits;                 // query heads handled by this CTA
+  const int h_first = kvh * qpg + blockIdx.z * hps;
+  const int iters = hps * nqb;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -425,7 +445,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       int it = 0;
       for (; it < iters; ++it) {
         const uint32_t st = it & 1, ph = (it >> 1) & 1;
-        const int h = kvh * qpg + it / nqb;
+        const int h = h_first + it / nqb;
         const int i0 = (qb0 + it % nqb) * BLK;
         if (!mbar_wait(smem_u32(&qdo_empty[st]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
         mbar_expect_tx(smem_u32(&qdo_full[st]), 2 * L::BLOCK);
@@ -498,7 +518,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     bool ok = true;
     for (int it = grp; it < iters && ok; it += 2) {
       const uint32_t ph = (it >> 1) & 1;
-      const int h = kvh * qpg + it / nqb;
+      const int h = h_first + it / nqb;
       const int i0 = (qb0 + it % nqb) * BLK;
       // per-column values of this query block; two buffers per group: a thread can run at most one of the group's
       // iterations ahead of the slowest reader, because passing col_full needs every thread's arrival
@@ -568,10 +588,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     if (ok && mbar_wait(smem_u32(out_full), 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       // group 0 writes dV, group 1 writes dK
-      if (grp == 0)
-        store_acc_row<D>(tmem + lane_addr + COL_DV, p.dv + ((long long)n * p.nkv + kvh) * D, row_ok);
-      else
-        store_acc_row<D>(tmem + lane_addr + COL_DK, p.dk + ((long long)n * p.nkv + kvh) * D, row_ok);
+      const long long row_off = ((long long)n * p.nkv + kvh) * D;
+      if (p.partial == nullptr) {
+        if (grp == 0) store_acc_row<D>(tmem + lane_addr + COL_DV, p.dv + row_off, row_ok);
+        else store_acc_row<D>(tmem + lane_addr + COL_DK, p.dk + row_off, row_ok);
+      } else {
+        const long long plane = (long long)p.T * p.nkv * D;
+        float* dst = p.partial + ((long long)grp * p.splits + blockIdx.z) * plane + row_off;
+        store_acc_row_f32<D>(tmem + lane_addr + (grp == 0 ? COL_DV : COL_DK), dst, row_ok);
+      }
     }
   }
   tc_fence_before();
@@ -579,6 +604,29 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// sums the head-split partials: out[i] = sum_s partial[s][i] (fp32 -> bf16), 8 elements per thread
+__global__ void attn_bwd_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dv,
+                                       __nv_bfloat16* __restrict__ dk, long long plane, int splits) {
+  const long long i8 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i8 >= plane) return;
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s2 = 0; s2 < splits; ++s2) {
+      const float* src = partial + ((long long)which * splits + s2) * plane + i8;
+      const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>((which == 0 ? dv : dk) + i8) = o;
   }
 }
 
@@ -613,7 +661,13 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* o, const
   attn_bwd_dq_kernel<D><<<dim3(tiles, p.nq), BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(tq128, tdo128, tk64, tv64, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  attn_bwd_dkv_kernel<D><<<dim3(tiles, p.nkv), BWD_THREADS, DkvSmem<D>::TOTAL, stream>>>(tk128, tv128, tq64, tdo64, p);
+  attn_bwd_dkv_kernel<D><<<dim3(tiles, p.nkv, p.splits), BWD_THREADS, DkvSmem<D>::TOTAL, stream>>>(tk128, tv128, tq64,
+                                                                                                    tdo64, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess || p.partial == nullptr) return (int)e;
+  const long long plane = (long long)p.T * p.nkv * D;
+  attn_bwd_reduce_kernel<<<(unsigned)((plane / 8 + 255) / 256), 256, 0, stream>>>(p.partial, p.dv, p.dk, plane,
+                                                                                  p.splits);
   return (int)cudaGetLastError();
 }
 
@@ -623,13 +677,33 @@ extern "C" {
 
 // q/o/dout/dq [T, nq, d], k/v/dk/dv [T, nkv, d] bf16 contiguous; lse, delta [nq, T] fp32 (delta is scratch filled
 // here); seq_start [T] int32.  `scale` is the softmax scale the forward used.
+//
+// Head split: with few kv heads and few key tiles the dK/dV grid (tiles x nkv CTAs) cannot fill the GPU.  Passing
+// `splits` > 1 (a divisor of nq / nkv) and `partial` (fp32, 2 * splits * T * nkv * d elements) lets `splits` CTAs share
+// a (tile, kv head) pair, each over nq / nkv / splits query heads; a reduction kernel sums their partial results.
+int mcb_attn_bwd_split(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                       float* delta, const int* seq_start, void* dq, void* dk, void* dv, int T, int nq, int nkv, int d,
+                       float scale, float* partial, int splits, int* status, void* stream_) {
+  if (T == 0) return 0;
+  if (nq % nkv) return -2;
+  if (splits < 1 || (nq / nkv) % splits) return -4;
+  if (splits == 1) partial = nullptr;
+  else if (partial == nullptr) return -5;
+  BwdParams p{T, nq, nkv, d, scale, scale * LOG2E, seq_start, lse, delta,
+              (__nv_bfloat16*)dq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, status, partial, splits};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  if (d == 128) return launch_bwd<128>(q, k, v, o, dout, delta, p, s);
+  if (d == 64) return launch_bwd<64>(q, k, v, o, dout, delta, p, s);
+  return -3;
+}
+
 int mcb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
                  float* delta, const int* seq_start, void* dq, void* dk, void* dv, int T, int nq, int nkv, int d,
                  float scale, int* status, void* stream_) {
   if (T == 0) return 0;
   if (nq % nkv) return -2;
   BwdParams p{T, nq, nkv, d, scale, scale * LOG2E, seq_start, lse, delta,
-              (__nv_bfloat16*)dq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, status};
+              (__nv_bfloat16*)dq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, status, nullptr, 1};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   if (d == 128) return launch_bwd<128>(q, k, v, o, dout, delta, p, s);
   if (d == 64) return launch_bwd<64>(q, k, v, o, dout, delta, p, s);

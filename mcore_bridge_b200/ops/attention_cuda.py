@@ -39,6 +39,22 @@ def seq_start_from_cu(cu_seqlens: Optional[torch.Tensor], T: int, device) -> tor
     return cu[:-1][seg.clamp(max=cu.numel() - 2)].to(torch.int32)
 
 
+def _dkv_splits(T: int, nq: int, nkv: int, device) -> int:
+    """How many CTAs share one (key tile, kv head) pair in the dK/dV kernel: enough to put at least about three
+    CTAs on every SM, limited to divisors of the GQA ratio.  ``MCB200_ATTN_DKV_SPLITS`` overrides it."""
+    env = os.environ.get('MCB200_ATTN_DKV_SPLITS')
+    qpg = nq // nkv
+    if env:
+        s = int(env)
+        return s if s >= 1 and qpg % s == 0 else 1
+    ctas = ((T + 127) // 128) * nkv
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    s = 1
+    while ctas * s < 3 * sms and s * 2 <= qpg and qpg % (s * 2) == 0:
+        s *= 2
+    return s
+
+
 class _AttnFn(torch.autograd.Function):
 
     @staticmethod
@@ -65,11 +81,17 @@ class _AttnFn(torch.autograd.Function):
         if hasattr(lib, 'mcb_attn_bwd') and os.environ.get('MCB200_ATTENTION_BWD_KERNEL', '1') != '0':
             dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
             delta = torch.empty((nq, T), dtype=torch.float32, device=q.device)
-            rc = lib.mcb_attn_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse),
-                                  _lib.ptr(delta), _lib.ptr(seq_start), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
-                                  _int(T), _int(nq), _int(k.shape[1]), _int(d), _f(ctx.scale),
-                                  _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
-            _lib.check_rc(rc, 'mcb_attn_bwd')
+            nkv = k.shape[1]
+            splits = _dkv_splits(T, nq, nkv, q.device)
+            partial = None
+            if splits > 1:
+                partial = torch.empty((2, splits, T, nkv, d), dtype=torch.float32, device=q.device)
+            rc = lib.mcb_attn_bwd_split(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do),
+                                        _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(seq_start), _lib.ptr(dq),
+                                        _lib.ptr(dk), _lib.ptr(dv), _int(T), _int(nq), _int(nkv), _int(d),
+                                        _f(ctx.scale), _lib.ptr(partial) if partial is not None else None,
+                                        _int(splits), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+            _lib.check_rc(rc, 'mcb_attn_bwd_split')
             return dq, dk, dv, None, None, None, None
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
