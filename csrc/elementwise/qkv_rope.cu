@@ -65,11 +65,9 @@ qkv_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __res
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slots = L.ng * (L.qpg * (1 + L.gate) + 2);
   const int nq = L.ng * L.qpg, d = L.d, half = L.rot / 2;
-  const long long total = T * slots;
-  const long long nwarps = (long long)gridDim.x * WARPS;
-  for (long long w = (long long)blockIdx.x * WARPS + warp; w < total; w += nwarps) {
-    const long long t = w / slots;
-    const int slot = (int)(w - t * slots);
+  // a block walks tokens, its warps walk the heads of the token: no 64-bit division on the hot path
+  for (long long t = blockIdx.x; t < T; t += gridDim.x)
+  for (int slot = warp; slot < slots; slot += WARPS) {
     int kind, head;
     decode_slot(L, slot, kind, head);
     const __nv_bfloat16* src = qkv + t * L.ld + (long long)slot * d;
@@ -142,11 +140,16 @@ qkv_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __res
   const int nq = L.ng * L.qpg, d = L.d, half = L.rot / 2;
   for (int i = threadIdx.x; i < 2 * MAX_D; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
   __syncthreads();
-  const long long total = T * slots;
-  const long long nwarps = (long long)gridDim.x * WARPS;
-  for (long long w = (long long)blockIdx.x * WARPS + warp; w < total; w += nwarps) {
-    const long long t = w / slots;
-    const int slot = (int)(w - t * slots);
+  // every lane always touches the same head positions, so the norm-weight gradients are summed in registers over all
+  // the heads a warp visits and meet in shared memory once, after the loop
+  float dw_acc[2][MAX_D / 32];
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int b = 0; b < MAX_D / 32; ++b) dw_acc[a][b] = 0.f;
+  // a block walks tokens, its warps walk the heads of the token: no 64-bit division on the hot path
+  for (long long t = blockIdx.x; t < T; t += gridDim.x)
+  for (int slot = warp; slot < slots; slot += WARPS) {
     int kind, head;
     decode_slot(L, slot, kind, head);
     const __nv_bfloat16* src = qkv + t * L.ld + (long long)slot * d;
@@ -228,7 +231,8 @@ qkv_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __res
           if (L.norm) {
             const float wv = (L.zero_centered ? 1.f : 0.f) + __bfloat162float(wn[idx]);
             o[e] = g * wv * rstd - sx[warp][idx] * c3;
-            atomicAdd(&sdw[kind == 0 ? 0 : 1][idx], g * sx[warp][idx] * rstd);
+            const float contrib = g * sx[warp][idx] * rstd;
+            if (kind == 0) dw_acc[0][2 * j + e] += contrib; else dw_acc[1][2 * j + e] += contrib;
           } else {
             o[e] = g;
           }
@@ -237,6 +241,18 @@ qkv_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __res
       }
     }
     __syncwarp();
+  }
+  if (L.norm) {
+#pragma unroll
+    for (int j = 0; j < MAX_D / 64; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int idx = lane * 2 + j * 64 + e;
+        if (idx < d) {
+          atomicAdd(&sdw[0][idx], dw_acc[0][2 * j + e]);
+          atomicAdd(&sdw[1][idx], dw_acc[1][2 * j + e]);
+        }
+      }
   }
   __syncthreads();
   if (L.norm) {
@@ -258,8 +274,7 @@ int mcb_qkv_split_norm_rope_fwd(const void* qkv, const void* wq, const void* wk,
   if (T == 0) return 0;
   if (d > MAX_D || d % 8 || rot > d || (rot & 1) || ld % 8) return -1;
   QkvLayout L{ng, qpg, d, has_gate, rot, interleaved, norm, zero_centered, eps, ld};
-  long long total = T * (long long)(ng * (qpg * (1 + has_gate) + 2));
-  long long blocks = (total + WARPS - 1) / WARPS;
+  long long blocks = T;
   long long cap = (long long)device_sm_count() * 16;
   qkv_fwd_kernel<<<(int)(blocks < cap ? blocks : cap), WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cosb, sinb, (__nv_bfloat16*)q,
@@ -275,8 +290,7 @@ int mcb_qkv_split_norm_rope_bwd(const void* qkv, const void* wq, const void* wk,
   if (T == 0) return 0;
   if (d > MAX_D || d % 8 || rot > d || (rot & 1) || ld % 8) return -1;
   QkvLayout L{ng, qpg, d, has_gate, rot, interleaved, norm, zero_centered, eps, ld};
-  long long total = T * (long long)(ng * (qpg * (1 + has_gate) + 2));
-  long long blocks = (total + WARPS - 1) / WARPS;
+  long long blocks = T;
   long long cap = (long long)device_sm_count() * 8;
   qkv_bwd_kernel<<<(int)(blocks < cap ? blocks : cap), WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cosb, sinb,
