@@ -263,6 +263,137 @@ qkv_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __res
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Fast path for head size 128 with rotate-half RoPE over the whole head (the Qwen3 / Llama layout): a lane holds
+// elements {2l, 2l+1} and their rotation partners {64+2l, 65+2l}, so the head never leaves registers.
+__device__ __forceinline__ float2 ld_bf2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+__global__ void __launch_bounds__(WARPS * 32)
+qkv_fwd_fast_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq,
+                    const __nv_bfloat16* __restrict__ wk, const float* __restrict__ cosb,
+                    const float* __restrict__ sinb, __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k,
+                    __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ gate, long long T, QkvLayout L) {
+  constexpr int D = 128;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slots = L.ng * (L.qpg * (1 + L.gate) + 2);
+  const int nq = L.ng * L.qpg;
+  const float wbase = L.zero_centered ? 1.f : 0.f;
+  float2 wqa = make_float2(1.f, 1.f), wqb = wqa, wka = wqa, wkb = wqa;
+  if (L.norm) {
+    wqa = ld_bf2(wq + 2 * lane); wqb = ld_bf2(wq + 64 + 2 * lane);
+    wka = ld_bf2(wk + 2 * lane); wkb = ld_bf2(wk + 64 + 2 * lane);
+    wqa.x += wbase; wqa.y += wbase; wqb.x += wbase; wqb.y += wbase;
+    wka.x += wbase; wka.y += wbase; wkb.x += wbase; wkb.y += wbase;
+  }
+  for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+    const float2 c = *reinterpret_cast<const float2*>(cosb + t * 64 + 2 * lane);
+    const float2 sn = *reinterpret_cast<const float2*>(sinb + t * 64 + 2 * lane);
+    for (int slot = warp; slot < slots; slot += WARPS) {
+      int kind, head;
+      decode_slot(L, slot, kind, head);
+      const __nv_bfloat16* src = qkv + t * L.ld + (long long)slot * D;
+      __nv_bfloat16* dst = kind == 0 ? q + (t * nq + head) * D
+                           : kind == 1 ? gate + (t * nq + head) * D
+                           : kind == 2 ? k + (t * L.ng + head) * D
+                                       : v + (t * L.ng + head) * D;
+      if (kind == 1 || kind == 3) {
+        *reinterpret_cast<uint2*>(dst + 4 * lane) = *reinterpret_cast<const uint2*>(src + 4 * lane);
+        continue;
+      }
+      float2 a = ld_bf2(src + 2 * lane), b = ld_bf2(src + 64 + 2 * lane);
+      if (L.norm) {
+        const float ss = warp_sum(a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y);
+        const float rstd = rsqrtf(ss * (1.f / D) + L.eps);
+        const float2 wa = kind == 0 ? wqa : wka, wb = kind == 0 ? wqb : wkb;
+        a.x *= rstd * wa.x; a.y *= rstd * wa.y; b.x *= rstd * wb.x; b.y *= rstd * wb.y;
+      }
+      *reinterpret_cast<uint32_t*>(dst + 2 * lane) = pack_bf16x2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+      *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = pack_bf16x2(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(WARPS * 32)
+qkv_bwd_fast_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq,
+                    const __nv_bfloat16* __restrict__ wk, const float* __restrict__ cosb,
+                    const float* __restrict__ sinb, const __nv_bfloat16* __restrict__ dq,
+                    const __nv_bfloat16* __restrict__ dk, const __nv_bfloat16* __restrict__ dv,
+                    const __nv_bfloat16* __restrict__ dgate, __nv_bfloat16* __restrict__ dqkv,
+                    float* __restrict__ dwq, float* __restrict__ dwk, long long T, QkvLayout L) {
+  constexpr int D = 128;
+  __shared__ float sdw[2][D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slots = L.ng * (L.qpg * (1 + L.gate) + 2);
+  const int nq = L.ng * L.qpg;
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
+  __syncthreads();
+  const float wbase = L.zero_centered ? 1.f : 0.f;
+  float2 wqa = make_float2(1.f, 1.f), wqb = wqa, wka = wqa, wkb = wqa;
+  if (L.norm) {
+    wqa = ld_bf2(wq + 2 * lane); wqb = ld_bf2(wq + 64 + 2 * lane);
+    wka = ld_bf2(wk + 2 * lane); wkb = ld_bf2(wk + 64 + 2 * lane);
+    wqa.x += wbase; wqa.y += wbase; wqb.x += wbase; wqb.y += wbase;
+    wka.x += wbase; wka.y += wbase; wkb.x += wbase; wkb.y += wbase;
+  }
+  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+    const float2 c = *reinterpret_cast<const float2*>(cosb + t * 64 + 2 * lane);
+    const float2 sn = *reinterpret_cast<const float2*>(sinb + t * 64 + 2 * lane);
+    for (int slot = warp; slot < slots; slot += WARPS) {
+      int kind, head;
+      decode_slot(L, slot, kind, head);
+      const __nv_bfloat16* src = qkv + t * L.ld + (long long)slot * D;
+      __nv_bfloat16* dst = dqkv + t * L.ld + (long long)slot * D;
+      const __nv_bfloat16* gsrc = kind == 0 ? dq + (t * nq + head) * D
+                                  : kind == 1 ? (dgate ? dgate + (t * nq + head) * D : nullptr)
+                                  : kind == 2 ? dk + (t * L.ng + head) * D
+                                              : dv + (t * L.ng + head) * D;
+      if (kind == 1 || kind == 3) {
+        *reinterpret_cast<uint2*>(dst + 4 * lane) =
+            gsrc ? *reinterpret_cast<const uint2*>(gsrc + 4 * lane) : make_uint2(0, 0);
+        continue;
+      }
+      const float2 ga = ld_bf2(gsrc + 2 * lane), gb = ld_bf2(gsrc + 64 + 2 * lane);
+      // transpose of the rotation
+      float2 na = make_float2(ga.x * c.x + gb.x * sn.x, ga.y * c.y + gb.y * sn.y);
+      float2 nb = make_float2(gb.x * c.x - ga.x * sn.x, gb.y * c.y - ga.y * sn.y);
+      if (L.norm) {
+        const float2 xa = ld_bf2(src + 2 * lane), xb = ld_bf2(src + 64 + 2 * lane);
+        const float2 wa = kind == 0 ? wqa : wka, wb = kind == 0 ? wqb : wkb;
+        float ss = xa.x * xa.x + xa.y * xa.y + xb.x * xb.x + xb.y * xb.y;
+        float dot = na.x * wa.x * xa.x + na.y * wa.y * xa.y + nb.x * wb.x * xb.x + nb.y * wb.y * xb.y;
+        ss = warp_sum(ss);
+        dot = warp_sum(dot);
+        const float rstd = rsqrtf(ss * (1.f / D) + L.eps);
+        const float c3 = dot * rstd * rstd * rstd * (1.f / D);
+        const float d0 = na.x * xa.x * rstd, d1 = na.y * xa.y * rstd, d2 = nb.x * xb.x * rstd, d3 = nb.y * xb.y * rstd;
+        if (kind == 0) { acc[0][0] += d0; acc[0][1] += d1; acc[0][2] += d2; acc[0][3] += d3; }
+        else { acc[1][0] += d0; acc[1][1] += d1; acc[1][2] += d2; acc[1][3] += d3; }
+        na.x = na.x * wa.x * rstd - xa.x * c3; na.y = na.y * wa.y * rstd - xa.y * c3;
+        nb.x = nb.x * wb.x * rstd - xb.x * c3; nb.y = nb.y * wb.y * rstd - xb.y * c3;
+      }
+      *reinterpret_cast<uint32_t*>(dst + 2 * lane) = pack_bf16x2(na.x, na.y);
+      *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = pack_bf16x2(nb.x, nb.y);
+    }
+  }
+  if (L.norm) {
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      atomicAdd(&sdw[a][2 * lane], acc[a][0]);
+      atomicAdd(&sdw[a][2 * lane + 1], acc[a][1]);
+      atomicAdd(&sdw[a][64 + 2 * lane], acc[a][2]);
+      atomicAdd(&sdw[a][65 + 2 * lane], acc[a][3]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      if (dwq) atomicAdd(dwq + i, sdw[0][i]);
+      if (dwk) atomicAdd(dwk + i, sdw[1][i]);
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -276,6 +407,12 @@ int mcb_qkv_split_norm_rope_fwd(const void* qkv, const void* wq, const void* wk,
   QkvLayout L{ng, qpg, d, has_gate, rot, interleaved, norm, zero_centered, eps, ld};
   long long blocks = T;
   long long cap = (long long)device_sm_count() * 16;
+  if (d == 128 && rot == 128 && !interleaved) {
+    qkv_fwd_fast_kernel<<<(int)(blocks < cap ? blocks : cap), WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+        (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cosb, sinb, (__nv_bfloat16*)q,
+        (__nv_bfloat16*)k, (__nv_bfloat16*)v, (__nv_bfloat16*)gate, T, L);
+    return (int)cudaGetLastError();
+  }
   qkv_fwd_kernel<<<(int)(blocks < cap ? blocks : cap), WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cosb, sinb, (__nv_bfloat16*)q,
       (__nv_bfloat16*)k, (__nv_bfloat16*)v, (__nv_bfloat16*)gate, T, L);
@@ -292,6 +429,13 @@ int mcb_qkv_split_norm_rope_bwd(const void* qkv, const void* wq, const void* wk,
   QkvLayout L{ng, qpg, d, has_gate, rot, interleaved, norm, zero_centered, eps, ld};
   long long blocks = T;
   long long cap = (long long)device_sm_count() * 8;
+  if (d == 128 && rot == 128 && !interleaved) {
+    qkv_bwd_fast_kernel<<<(int)(blocks < cap ? blocks : cap), WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+        (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cosb, sinb,
+        (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv, (const __nv_bfloat16*)dgate,
+        (__nv_bfloat16*)dqkv, dwq, dwk, T, L);
+    return (int)cudaGetLastError();
+  }
   qkv_bwd_kernel<<<(int)(blocks < cap ? blocks : cap), WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cosb, sinb,
       (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv, (const __nv_bfloat16*)dgate,

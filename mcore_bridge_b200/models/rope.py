@@ -98,10 +98,10 @@ def compute_inv_freq(rope_type: str, base: float, dim: int, rope_scaling: Option
     if rope_type == 'longrope':
         orig = original_max_position_embeddings or rs.get('original_max_position_embeddings')
         factor = rs.get('factor')
-        if orig:
-            factor = max_position_embeddings / orig
-        else:
+        if not orig:
             orig = max_position_embeddings
+        if factor is None:     # Phi-3 style configs give only the two lengths
+            factor = max_position_embeddings / orig
         attention_factor = rs.get('attention_factor')
         if attention_factor is None:
             attention_factor = 1.0 if factor <= 1.0 else math.sqrt(1 + math.log(factor) / math.log(orig))
