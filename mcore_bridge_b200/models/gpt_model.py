@@ -74,6 +74,13 @@ class GPTModel(nn.Module):
             elif task == 'seq_cls':
                 self.output_layer = ReplicatedLinear(config.hidden_size, config.num_labels, config, bias=False,
                                                      sequence_parallel_grad=False)
+        if self.share_embeddings_and_output_weights and ps.get_pipeline_model_parallel_world_size() > 1:
+            # the stages at the two ends of the pipeline each hold a copy of the tied matrix
+            if pre_process and self.embedding is not None:
+                self.embedding.word_embeddings.weight.shared_embedding = True
+            if post_process and not pre_process and self.output_layer is not None and \
+                    config.task_type in ('causal_lm', 'generative_reranker'):
+                self.output_layer.weight.shared_embedding = True
         self._extra_tables: Dict[str, RotaryEmbedding] = {}
 
     # ------------------------------------------------------------------ pipeline plumbing

@@ -155,6 +155,16 @@ def initialize_model_parallel(tensor_model_parallel_size: int = 1, pipeline_mode
                 mine, handle = ranks, g
         st.group_ranks[name] = mine
         st.groups[name] = handle
+    # embedding group: first and last pipeline stage of every pipeline (tied input / output embeddings keep one
+    # copy on each and sum their gradients); ranks in between are not members
+    mine, handle = None, None
+    for ranks in groups_for(world, st.dense_names, st.dense_sizes, ('pp',)):
+        ends = [ranks[0], ranks[-1]] if len(ranks) > 1 else [ranks[0]]
+        g = dist.new_group(ends, backend=backend, **kw) if (world > 1 and len(ends) > 1) else None
+        if rank in ends:
+            mine, handle = ends, g
+    st.group_ranks['embd'] = mine
+    st.groups['embd'] = handle
     _STATE = st
     return st
 
@@ -174,7 +184,7 @@ def get_state() -> ParallelState:
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             raise RuntimeError('call initialize_model_parallel() first')
         _STATE = ParallelState()
-        for name in _GROUP_DEFS:
+        for name in list(_GROUP_DEFS) + ['embd']:
             _STATE.groups[name] = None
             _STATE.group_ranks[name] = [0]
     return _STATE

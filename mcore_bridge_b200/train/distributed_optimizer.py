@@ -153,7 +153,10 @@ class DistributedDataParallel(nn.Module):
                 b.work = None
 
     def _needs_tp_reduce(self, b: Bucket) -> bool:
-        return ps.get_world_size('tp') > 1 and any(getattr(p, 'sequence_parallel', False) for p in b.params)
+        if ps.get_world_size('tp') > 1 and any(getattr(p, 'sequence_parallel', False) for p in b.params):
+            return True
+        # copies of a tied embedding on the first and last pipeline stage sum their gradients first
+        return ps.get_world_size('embd') > 1 and any(getattr(p, 'shared_embedding', False) for p in b.params)
 
     def _launch_reduce(self, buf: ParamAndGradBuffer, b: Bucket):
         if buf.dp == 1 or b.work is not None:
@@ -196,9 +199,21 @@ class DistributedDataParallel(nn.Module):
             p.main_grad.copy_(flat[off:off + n].view(p.shape))
             off += n
 
+    def _allreduce_shared_embedding_grads(self):
+        """Tied input / output embeddings under pipeline parallelism: the first stage's embedding and the last
+        stage's head are two copies of one weight, so their gradients are summed over the two-rank embedding group
+        (before the data-parallel reduction, while every rank still holds full gradients)."""
+        if ps.get_world_size('embd') == 1:
+            return
+        for buf in self.buffers.values():
+            for p in buf.params:
+                if getattr(p, 'shared_embedding', False):
+                    dist.all_reduce(p.main_grad, group=ps.get_group('embd'))
+
     def finish_grad_sync(self):
         """Blocks until every bucket's gradient shard is reduced (launching the ones not started yet)."""
         self._allreduce_sequence_parallel_grads()
+        self._allreduce_shared_embedding_grads()
         for buf in self.buffers.values():
             if buf.dp == 1:
                 continue

@@ -68,6 +68,18 @@ def init_weights(model: torch.nn.Module, std: float = 0.02, seed: Optional[int] 
             p.normal_(0.0, std)
 
 
+def sync_shared_embeddings(models) -> None:
+    """Makes the last pipeline stage's copy of a tied embedding equal to the first stage's (after random init; a
+    checkpoint load fills both from the same tensor anyway)."""
+    if ps.get_world_size('embd') == 1:
+        return
+    src = ps.get_group_ranks('embd')[0]
+    for m in models:
+        for p in m.parameters():
+            if getattr(p, 'shared_embedding', False):
+                dist.broadcast(p.data, src=src, group=ps.get_group('embd'))
+
+
 class Trainer:
 
     def __init__(self, config, train_config: Optional[TrainConfig] = None, models: Optional[List] = None):
@@ -77,6 +89,7 @@ class Trainer:
         if models is None and self.tc.init_seed is not None:
             for i, m in enumerate(self.models):
                 init_weights(m, self.tc.init_std, self.tc.init_seed + i)
+        sync_shared_embeddings(self.models)
         self.ddp = [DistributedDataParallel(m, self.tc.bucket_mb, self.tc.overlap_grad_reduce) for m in self.models]
         self.optimizer = DistributedOptimizer(self.ddp, self.tc.lr, self.tc.betas, self.tc.eps, self.tc.weight_decay,
                                               self.tc.clip_grad)

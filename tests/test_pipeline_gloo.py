@@ -4,14 +4,15 @@ import torch
 from dist_utils import run_ranks
 
 
-def _run(rank, world, pp, vpp, tp):
+def _run(rank, world, pp, vpp, tp, tied=False):
     from mcore_bridge_b200.parallel import state as ps
     from mcore_bridge_b200.train.data import SyntheticPackedDataset
     from mcore_bridge_b200.train.presets import model_config
     from mcore_bridge_b200.train.trainer import TrainConfig, Trainer
     ps.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
                                  virtual_pipeline_model_parallel_size=vpp)
-    cfg = model_config('qwen3_tiny', params_dtype=torch.float32, tensor_model_parallel_size=tp,
+    cfg = model_config('qwen3_tiny', {'tie_word_embeddings': True} if tied else None, params_dtype=torch.float32,
+                       tensor_model_parallel_size=tp,
                        pipeline_model_parallel_size=pp, virtual_pipeline_model_parallel_size=vpp)
     tr = Trainer(cfg, TrainConfig(lr=1e-3, init_seed=None, clip_grad=0.0))
     # identical weights on every layout: fill each parameter from a generator seeded by its global name
@@ -27,8 +28,8 @@ def _run(rank, world, pp, vpp, tp):
             full_shape = list(p.shape)
             with torch.no_grad():
                 p.copy_(torch.randn(full_shape, generator=g) * 0.05 + (1.0 if p.dim() == 1 else 0.0))
-    for ddp in tr.ddp:       # master weights were cloned before the fill above
-        pass
+    from mcore_bridge_b200.train.trainer import sync_shared_embeddings
+    sync_shared_embeddings(tr.models)     # tied embeddings: the last stage's copy follows the first stage's
     tr.optimizer = type(tr.optimizer)(tr.ddp, 1e-3, clip_grad=0.0)
     ds = SyntheticPackedDataset(1024, 256, seg_lo=32, seg_hi=128, seed=3)
     mbs = [ds.next_microbatch() for _ in range(4)]
@@ -75,3 +76,18 @@ def test_pp2_vpp2_matches_single():
         merged.update(r[1])
     for k, v in base[1].items():
         assert abs(merged[k] - v) < 1e-6 * max(1.0, abs(v)), k
+
+
+def test_pp2_tied_embeddings_match_single():
+    """With tied input / output embeddings the two pipeline ends keep one copy each; their gradients are summed, so
+    both copies end up equal to the single-process weight after the step."""
+    _hashseed_env()
+    base = run_ranks(_run, 1, 1, None, 1, True)[0]
+    res = run_ranks(_run, 2, 2, None, 1, True)
+    last = [r for r in res if r[2]][0]
+    first = [r for r in res if not r[2]][0]
+    assert abs(last[0] - base[0]) < 1e-5
+    want = base[1]['embedding.word_embeddings.weight']
+    assert 'output_layer.weight' not in base[1]
+    assert abs(first[1]['embedding.word_embeddings.weight'] - want) < 1e-6 * max(1.0, abs(want))
+    assert abs(last[1]['output_layer.weight'] - want) < 1e-6 * max(1.0, abs(want))
