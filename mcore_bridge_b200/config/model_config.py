@@ -101,6 +101,7 @@ class ModelConfig:
     kv_channels: Optional[int] = None
     qk_layernorm: bool = False
     qk_l2_norm: bool = False
+    lean_activations: bool = True            # single-rank dense path: recompute norm / gated activation in backward instead of storing them
     qk_layernorm_full: bool = False          # q/k RMSNorm over all heads' channels at once (OLMoE, MiniMax-M2)
     post_sublayer_layernorm: bool = False    # sandwich norms after attention and MLP outputs (GLM-4)
     no_rope_freq: Optional[Union[int, str, List[int]]] = None

@@ -104,7 +104,21 @@ class LayerNormColumnParallelLinear(ColumnParallelLinear):
             return layernorm_ref(x, w, self.layer_norm_bias, self.eps)
         return rmsnorm(x, self.layer_norm_weight, self.eps, self.zero_centered)
 
+    def _lean(self, x) -> bool:
+        """Single-rank RMSNorm path that does not keep the normalised activation (``ops/fused_mlp.py``)."""
+        if self.return_layernorm_output or self.bias is not None or self.spec.fp8 or self.gather_output:
+            return False
+        if self.normalization == 'LayerNorm' or ps.get_world_size(self.group) > 1:
+            return False
+        if not getattr(self.config, 'lean_activations', True):
+            return False
+        from ..ops import fused_mlp
+        return fused_mlp.usable(x, self.weight) and self.layer_norm_weight.dtype == torch.bfloat16
+
     def forward(self, x):
+        if self._lean(x):
+            from ..ops import fused_mlp
+            return fused_mlp.norm_linear(x, self.layer_norm_weight, self.weight, self.eps, self.zero_centered)
         xn = self.norm(x)
         y = linear(xn, self.weight, self.bias, self.spec)
         if self.return_layernorm_output:

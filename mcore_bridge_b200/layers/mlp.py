@@ -23,6 +23,15 @@ class MLP(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         cfg = self.config
         h = self.linear_fc1(x)
+        fc2 = self.linear_fc2
+        if cfg.gated_linear_unit and type(fc2) is RowParallelLinear and fc2.bias is None and not fc2.spec.fp8 \
+                and getattr(cfg, 'lean_activations', True):
+            from ..parallel import state as ps
+            from ..ops import fused_mlp
+            if ps.get_world_size(fc2.group) == 1 and fused_mlp.usable(h, fc2.weight) and (h.shape[-1] // 2) % 8 == 0:
+                from ..ops.activation import KINDS
+                return fused_mlp.glu_linear(h, fc2.weight, KINDS[self.kind], cfg.activation_func_clamp_value or 0.0,
+                                            cfg.glu_linear_offset)
         if cfg.gated_linear_unit:
             h = glu(h, self.kind, None, cfg.activation_func_clamp_value or 0.0, cfg.glu_linear_offset)
         else:

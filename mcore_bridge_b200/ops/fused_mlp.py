@@ -1,0 +1,125 @@
+"""Activation-lean fused blocks for the single-rank (no tensor parallel) dense path.
+
+``norm_linear``:  ``y = rmsnorm(x) @ W^T`` that keeps ``x`` and the per-row ``rstd`` for backward instead of the
+normalised activation, and re-runs the (memory-bound, ~30 us) norm in backward for the weight gradient.
+``glu_linear``:   ``y = glu(h) @ W^T`` that keeps ``h`` only and re-runs the gated activation in backward.
+
+Per Qwen3-8B layer and 8192 tokens this drops 2 x 67 MB (normalised inputs of QKV and FC1) and 201 MB (SwiGLU output)
+from what autograd holds, about 30 % of a layer's activations, which is what lets a single 180 GB GPU keep almost all
+layers' activations instead of recomputing a third of the forward pass.  Results are bit-identical to the unfused
+sequence (the recomputed tensors come from the same kernels on the same inputs).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib, gemm
+from .linear import _weight_grad
+
+_ll, _int, _f = ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+
+
+def _rmsnorm_raw(x2, w, eps, zc, rstd=None):
+    rows, H = x2.shape
+    y = torch.empty((rows, H), dtype=x2.dtype, device=x2.device)
+    if rstd is None:
+        rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
+    rc = _lib.lib().mcb_rmsnorm_fwd(_lib.ptr(x2), None, _lib.ptr(w), _lib.ptr(y), None, _lib.ptr(rstd), _ll(rows),
+                                    _int(H), _ll(x2.stride(0)), _f(eps), _int(int(zc)), _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_rmsnorm_fwd')
+    return y, rstd
+
+
+def _glu_raw(h2, kind, clamp, offset):
+    rows, F2 = h2.shape
+    out = torch.empty((rows, F2 // 2), dtype=h2.dtype, device=h2.device)
+    rc = _lib.lib().mcb_glu_fwd(_lib.ptr(h2), None, _lib.ptr(out), _ll(rows), _int(F2 // 2), _ll(h2.stride(0)),
+                                _int(kind), _f(clamp), _f(offset), _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_glu_fwd')
+    return out
+
+
+class _NormLinearFn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, ln_w, weight, eps, zc):
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        xn, rstd = _rmsnorm_raw(x2, ln_w, eps, zc)
+        y = gemm.mm_nt(xn, weight)
+        ctx.save_for_backward(x2, ln_w, rstd, weight)
+        ctx.eps, ctx.zc, ctx.shape = eps, zc, x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, ln_w, rstd, weight = ctx.saved_tensors
+        rows, H = x2.shape
+        dy2 = dy.reshape(rows, weight.shape[0])
+        if dy2.stride(-1) != 1:
+            dy2 = dy2.contiguous()
+        dw = None
+        if ctx.needs_input_grad[2]:
+            xn, _ = _rmsnorm_raw(x2, ln_w, ctx.eps, ctx.zc, rstd)
+            dw = _weight_grad(weight, dy2, xn)
+            del xn
+        dxn = gemm.mm_nn(dy2, weight)
+        dx = torch.empty((rows, H), dtype=x2.dtype, device=x2.device)
+        dlw = torch.zeros(H, dtype=torch.float32, device=x2.device)
+        rc = _lib.lib().mcb_rmsnorm_bwd(_lib.ptr(dxn), _lib.ptr(x2), _lib.ptr(ln_w), _lib.ptr(rstd), None, _lib.ptr(dx),
+                                        _lib.ptr(dlw), _ll(rows), _int(H), _ll(x2.stride(0)), _f(ctx.eps),
+                                        _int(int(ctx.zc)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_rmsnorm_bwd')
+        return dx.view(ctx.shape), dlw.to(ln_w.dtype), dw, None, None
+
+
+class _GluLinearFn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, h, weight, kind, clamp, offset):
+        F2 = h.shape[-1]
+        h2 = h.reshape(-1, F2)
+        if h2.stride(-1) != 1:
+            h2 = h2.contiguous()
+        a = _glu_raw(h2, kind, clamp, offset)
+        y = gemm.mm_nt(a, weight)
+        ctx.save_for_backward(h2, weight)
+        ctx.args = (kind, clamp, offset, h.shape)
+        return y.view(*h.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        h2, weight = ctx.saved_tensors
+        kind, clamp, offset, shape = ctx.args
+        rows, F2 = h2.shape
+        dy2 = dy.reshape(rows, weight.shape[0])
+        if dy2.stride(-1) != 1:
+            dy2 = dy2.contiguous()
+        dw = None
+        if ctx.needs_input_grad[1]:
+            a = _glu_raw(h2, kind, clamp, offset)
+            dw = _weight_grad(weight, dy2, a)
+            del a
+        da = gemm.mm_nn(dy2, weight)
+        dh = torch.empty((rows, F2), dtype=h2.dtype, device=h2.device)
+        rc = _lib.lib().mcb_glu_bwd(_lib.ptr(h2), None, _lib.ptr(da), _lib.ptr(dh), None, _ll(rows), _int(F2 // 2),
+                                    _ll(h2.stride(0)), _int(kind), _f(clamp), _f(offset), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_glu_bwd')
+        return dh.view(shape), dw, None, None, None
+
+
+def usable(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _lib.available()
+            and x.shape[-1] % 8 == 0 and torch.is_grad_enabled())
+
+
+def norm_linear(x, ln_w, weight, eps, zero_centered):
+    return _NormLinearFn.apply(x, ln_w, weight, float(eps), bool(zero_centered))
+
+
+def glu_linear(h, weight, kind: int, clamp: float, offset: float):
+    return _GluLinearFn.apply(h, weight, int(kind), float(clamp or 0.0), float(offset))

@@ -363,3 +363,27 @@ def test_simple_gla_kernels(d):
     orf.backward(g.float())
     assert rel(o, orf) < 1e-2
     assert rel(q1.grad, q2.grad) < 1e-2 and rel(k1.grad, k2.grad) < 1e-2 and rel(v1.grad, v2.grad) < 1e-2
+
+
+def test_lean_activation_blocks_match_unfused():
+    """norm_linear / glu_linear (recompute in backward) give the same loss and gradients as the unfused layers."""
+    from mcore_bridge_b200 import get_mcore_model
+    from mcore_bridge_b200.train.presets import model_config
+    from mcore_bridge_b200.train.trainer import init_weights
+    ids = torch.randint(0, 1024, (2, 256), device=DEV, generator=torch.Generator(device=DEV).manual_seed(3))
+    labels = torch.randint(0, 1024, (2, 256), device=DEV, generator=torch.Generator(device=DEV).manual_seed(4))
+    out = {}
+    for lean in (True, False):
+        cfg = model_config('qwen3_tiny', bf16=True, lean_activations=lean)
+        model = get_mcore_model(cfg)[0]
+        init_weights(model, 0.02, 7)
+        loss = model(ids, labels=labels).mean()
+        loss.backward()
+        layer = model.decoder.layers[1]
+        out[lean] = (loss.detach(), layer.mlp.linear_fc1.weight.grad.clone(), layer.mlp.linear_fc2.weight.grad.clone(),
+                     layer.mlp.linear_fc1.layer_norm_weight.grad.clone(),
+                     layer.self_attention.linear_qkv.weight.grad.clone(),
+                     model.embedding.word_embeddings.weight.grad.clone())
+    assert torch.equal(out[True][0], out[False][0])
+    for a, b in zip(out[True][1:], out[False][1:]):
+        assert rel(a, b) < 1e-3
