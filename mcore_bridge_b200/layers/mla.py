@@ -86,9 +86,19 @@ class DSAIndexer(nn.Module):
         return dsa.index_scores(q, k, w, mask)
 
     def forward(self, x, qr, ctx: ForwardContext, mask: torch.Tensor):
+        from ..ops import dsa
         q, k, w = self.forward_before_topk(x, qr, ctx)
+        T = q.shape[0]
+        topk = min(self.topk, T)
+        if not torch.is_grad_enabled() and dsa.cuda_indexer_supported(q, k) and ps.get_world_size('cp') == 1:
+            # selection only (the indexer is not being trained through this call): tcgen05 scores + radix select
+            seq_start = ctx.seq_start
+            if seq_start is None:
+                from ..ops.attention_cuda import seq_start_from_cu
+                seq_start = seq_start_from_cu(ctx.cu_seqlens, T, q.device)
+            scores = dsa.index_scores_cuda(q, k, w, seq_start)
+            return dsa.topk_indices(scores, topk), scores
         scores = self.index_scores(q, k, w, mask)
-        topk = min(self.topk, scores.shape[-1])
         idx = scores.topk(topk, dim=-1).indices
         return idx, scores
 

@@ -61,3 +61,42 @@ def indexer_kl_loss(scores: torch.Tensor, attn_probs: torch.Tensor, mask: torch.
     logp = torch.where(keep, logp, torch.zeros_like(logp))
     kl = (target * (torch.log(target.clamp(min=1e-20)) - logp)).sum(-1)
     return kl.mean()
+
+
+# ------------------------------------------------------------------------------------------------ CUDA kernels
+def cuda_indexer_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
+    from . import _lib
+    return (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q.shape[-1] == 128
+            and q.shape[0] == k.shape[0] and q.shape[0] % 4 == 0 and _lib.available())
+
+
+def index_scores_cuda(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, seq_start: torch.Tensor) -> torch.Tensor:
+    """Lightning-indexer scores on the tcgen05 kernel (``csrc/dsa/dsa_indexer_sm100.cu``): ``[T, T]`` fp32 with
+    ``-inf`` outside the causal, same-sequence region described by ``seq_start``.  No gradient."""
+    import ctypes
+
+    from . import _lib
+    T, H, D = q.shape
+    out = torch.full((T, T), float('-inf'), dtype=torch.float32, device=q.device)
+    rc = _lib.lib().mcb_dsa_index_scores(_lib.ptr(q.contiguous()), _lib.ptr(k.contiguous()),
+                                         _lib.ptr(w.float().contiguous()), _lib.ptr(seq_start), _lib.ptr(out),
+                                         ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(D),
+                                         _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_dsa_index_scores')
+    return out
+
+
+def topk_indices(scores: torch.Tensor, k: int) -> torch.Tensor:
+    """Positions of the ``k`` largest entries of every row (unordered), radix-select kernel on CUDA."""
+    import ctypes
+
+    from . import _lib
+    if not (scores.is_cuda and scores.dtype == torch.float32 and scores.dim() == 2 and _lib.available()):
+        return scores.topk(k, dim=-1).indices
+    rows, n = scores.shape
+    s = scores if scores.stride(1) == 1 else scores.contiguous()
+    idx = torch.empty((rows, k), dtype=torch.int64, device=scores.device)
+    rc = _lib.lib().mcb_topk_select(_lib.ptr(s), ctypes.c_longlong(s.stride(0)), ctypes.c_int(rows), ctypes.c_int(n),
+                                    ctypes.c_int(k), _lib.ptr(idx), _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_topk_select')
+    return idx

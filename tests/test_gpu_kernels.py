@@ -387,3 +387,31 @@ def test_lean_activation_blocks_match_unfused():
     assert torch.equal(out[True][0], out[False][0])
     for a, b in zip(out[True][1:], out[False][1:]):
         assert rel(a, b) < 1e-3
+
+
+@pytest.mark.parametrize('T,H,segs,k', [(512, 4, [512], 64), (1000, 8, [300, 700], 128), (2048, 64, [2048], 512)])
+def test_dsa_indexer_scores_and_topk(T, H, segs, k):
+    """tcgen05 lightning-indexer scores against the fp32 einsum; radix-select top-k against torch.topk (as sets, and
+    by the selected values since ties may resolve differently)."""
+    from mcore_bridge_b200.ops import dsa
+    from mcore_bridge_b200.ops.attention_cuda import seq_start_from_cu
+    torch.manual_seed(21)
+    q = torch.randn(T, H, 128, device=DEV, dtype=torch.bfloat16)
+    kk = torch.randn(T, 128, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(T, H, device=DEV) * 0.1
+    cu = torch.tensor([0] + list(torch.tensor(segs).cumsum(0)), dtype=torch.int32, device=DEV)
+    ss = seq_start_from_cu(cu, T, q.device)
+    pos = torch.arange(T, device=DEV)
+    mask = (ss[:, None] <= pos[None, :]) & (pos[None, :] <= pos[:, None])
+    ref = dsa.index_scores(q, kk, w, mask)
+    got = dsa.index_scores_cuda(q, kk, w, ss)
+    assert torch.equal(torch.isinf(got), torch.isinf(ref))
+    fin = ~torch.isinf(ref)
+    assert ((got[fin] - ref[fin]).abs().max() / ref[fin].abs().max()).item() < 2e-2
+    idx = dsa.topk_indices(got, k)
+    assert idx.shape == (T, k)
+    vals = got.gather(1, idx).sort(dim=1, descending=True).values
+    want = got.topk(k, dim=1).values
+    assert torch.equal(vals, want)
+    # no position is selected twice
+    assert (idx.sort(dim=1).values[:, 1:] != idx.sort(dim=1).values[:, :-1]).all()
