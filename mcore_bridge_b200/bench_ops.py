@@ -42,7 +42,7 @@ def _time(fn, iters, flush=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('op', choices=['gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention', 'attention_bwd',
-                                  'gemm_fp8', 'quant_fp8'])
+                                  'gemm_fp8', 'quant_fp8', 'dsa_index', 'topk', 'simple_gla', 'conv1d'])
     ap.add_argument('--m', type=int, default=8192)
     ap.add_argument('--n', type=int, default=4096)
     ap.add_argument('--k', type=int, default=4096)
@@ -127,6 +127,45 @@ def main():
             t = _time(lambda: fp8.quantize_1x128(x), a.iters, flush)
             gbs = x.numel() * 3 / t / 1e9
             res.update(seconds=t, gbs=gbs, frac_of_hbm_peak=gbs / hbm, peak_source=src)
+    elif a.op in ('dsa_index', 'topk'):
+        from .ops import dsa
+        from .ops.attention_cuda import seq_start_from_cu
+        H = 64
+        q = torch.randn(M, H, 128, device=dev, dtype=torch.bfloat16)
+        kk = torch.randn(M, 128, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(M, H, device=dev) * 0.1
+        ss = seq_start_from_cu(None, M, q.device)
+        if a.op == 'dsa_index':
+            t = _time(lambda: dsa.index_scores_cuda(q, kk, w, ss), a.iters, flush)
+            tf = 2.0 * M * M / 2 * H * 128 / t / 1e12
+            res.update(seconds=t, tflops_causal=tf, frac_of_burst_peak=tf / burst, heads=H, peak_source=src,
+                       note='time includes the -inf fill of the [T, T] output')
+        else:
+            sc = dsa.index_scores_cuda(q, kk, w, ss)
+            kq = min(2048, M)
+            t = _time(lambda: dsa.topk_indices(sc, kq), a.iters, flush)
+            t_ref = _time(lambda: sc.topk(kq, dim=-1), max(2, a.iters // 3), flush)
+            res.update(seconds=t, torch_topk_seconds=t_ref, k=kq, gbs=sc.numel() * 4 / t / 1e9)
+    elif a.op == 'simple_gla':
+        from .ops import gdn
+        h, d = 32, 128
+        seg = a.k if a.k <= M else M
+        q, k, v = (torch.randn(M, h, d, device=dev, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+        decay = -torch.rand(h, device=dev) * 0.1
+        cu = torch.arange(0, M + 1, seg, dtype=torch.int32, device=dev)
+        t = _time(lambda: gdn.simple_gla(q, k, v, decay, cu), a.iters, flush)
+        o = gdn.simple_gla(q, k, v, decay, cu)
+        g = torch.randn_like(o)
+        tb = _time(lambda: o.backward(g, retain_graph=True), a.iters, flush)
+        res.update(seconds_fwd=t, seconds_bwd=tb, heads=h, segment=seg, tokens_per_s_fwd=M / t)
+    elif a.op == 'conv1d':
+        from .ops import gdn
+        C = N
+        x = torch.randn(M, C, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        wc = torch.randn(C, 4, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        t = _time(lambda: gdn.causal_conv1d_silu(x, wc, None, None), a.iters, flush)
+        gbs = 2 * x.numel() * 2 / t / 1e9
+        res.update(seconds=t, gbs=gbs, frac_of_hbm_peak=gbs / hbm, peak_source=src)
     torch.cuda.synchronize()
     _lib.check_status()
     print(json.dumps(res))
