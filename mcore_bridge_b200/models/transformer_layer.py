@@ -119,8 +119,24 @@ class TransformerLayer(nn.Module):
             full = M.scatter_to_sequence_parallel_region(full)
         return hidden + full
 
+    def _selective(self, name: str) -> bool:
+        """Selective recompute: ``recompute_modules`` names the sub-blocks whose activations are dropped and recomputed
+        in backward.  ``mlp`` / ``moe`` cover the feed-forward block (norm included), ``self_attn`` the whole attention
+        block; ``core_attn`` needs nothing here because the attention kernels keep only their output and
+        log-sum-exp, and ``layernorm`` nothing because the fused norm-linear blocks already recompute the norm
+        (reference ``src/mcore_bridge/model/modules/transformer_layer.py:144-196``)."""
+        cfg = self.config
+        return (self.training and cfg.recompute_granularity == 'selective' and name in (cfg.recompute_modules or ())
+                and torch.is_grad_enabled())
+
     def forward(self, hidden: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
-        hidden = self._attention(hidden, ctx)
+        from torch.utils.checkpoint import checkpoint
+        if self._selective('self_attn'):
+            hidden = checkpoint(self._attention, hidden, ctx, use_reentrant=False)
+        else:
+            hidden = self._attention(hidden, ctx)
         if self.config.mlp_padding_free and ctx.extra.get('full_padding_mask') is not None:
             return self._mlp_padding_free(hidden, ctx)
+        if self._selective('moe' if self.is_moe else 'mlp'):
+            return checkpoint(self._mlp, hidden, ctx, use_reentrant=False)
         return self._mlp(hidden, ctx)

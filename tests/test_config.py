@@ -56,3 +56,24 @@ def test_deepcopy_shares_bridge():
 def test_linear_attention_freq():
     cfg = ModelConfig(**{**hf_to_mcore_config(hf_config('qwen3_tiny')), 'num_layers': 8, 'linear_attention_freq': 4})
     assert cfg.linear_attention_pattern() == [1, 1, 1, 0, 1, 1, 1, 0]
+
+
+def test_selective_recompute_matches_plain():
+    """``recompute_granularity='selective'`` with the mlp / self_attn modules gives the same loss and gradients."""
+    import torch
+    from mcore_bridge_b200 import get_mcore_model
+    from mcore_bridge_b200.train.presets import model_config
+    from mcore_bridge_b200.train.trainer import init_weights
+    ids = torch.randint(0, 1024, (2, 64), generator=torch.Generator().manual_seed(0))
+    labels = torch.randint(0, 1024, (2, 64), generator=torch.Generator().manual_seed(1))
+    res = []
+    for kw in ({}, dict(recompute_granularity='selective', recompute_modules=['mlp', 'self_attn'])):
+        cfg = model_config('qwen3_tiny', params_dtype=torch.float32, **kw)
+        m = get_mcore_model(cfg)[0].train()
+        init_weights(m, 0.02, 5)
+        loss = m(ids, labels=labels).mean()
+        loss.backward()
+        res.append((loss.detach(), m.decoder.layers[0].mlp.linear_fc1.weight.grad.clone(),
+                    m.decoder.layers[1].self_attention.linear_qkv.weight.grad.clone()))
+    assert torch.equal(res[0][0], res[1][0])
+    assert torch.allclose(res[0][1], res[1][1], atol=1e-7) and torch.allclose(res[0][2], res[1][2], atol=1e-7)
