@@ -110,13 +110,39 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
 // ------------------------------------------------------------------ RMSNorm backward
 // dx = rstd * (g - xh * mean(g * xh)),  g = dy * w_eff, xh = x * rstd;  dw += sum_rows dy * xh.
 // Persistent blocks: each thread owns fixed columns, accumulates dw over its rows, one atomic per column at the end.
+// Two rows are processed per iteration: their loads are in flight together and their row reductions share one
+// round of barriers, which is what bounds a one-row-at-a-time block.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  __syncthreads();
+  if (lane == 0) {
+    red[warp] = a;
+    red[33 + warp] = b;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f, u = lane < nw ? red[33 + lane] : 0.f;
+    t = warp_sum(t);
+    u = warp_sum(u);
+    if (lane == 0) {
+      red[32] = t;
+      red[65] = u;
+    }
+  }
+  __syncthreads();
+  a = red[32];
+  b = red[65];
+}
+
 template <int VPT>
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                                    float* __restrict__ dw, long long rows, int H, long long ldx, float eps,
                                    int zero_centered) {
-  __shared__ float red[33];
+  __shared__ float red[66];
   const int nvec = H / 8;
   float dwacc[VPT][8];
   float wf[VPT][8];
@@ -135,57 +161,83 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
       }
     }
   }
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
-    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * (long long)H);
-    float xv[VPT][8], gv[VPT][8];
-    float ss = 0.f, dot = 0.f;
+  for (long long row0 = 2LL * blockIdx.x; row0 < rows; row0 += 2LL * gridDim.x) {
+    const bool two = row0 + 1 < rows;
+    uint4 xr[2][VPT], gr[2][VPT];
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = threadIdx.x + i * blockDim.x;
-      if (vi < nvec) {
-        bf16x8 a, b;
-        a.raw = xr[vi];
-        b.raw = gr[vi];
-        a.unpack(xv[i]);
-        b.unpack(gv[i]);
+    for (int r = 0; r < 2; ++r) {
+      const long long row = row0 + ((r == 1 && two) ? 1 : 0);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          ss += xv[i][j] * xv[i][j];
-          dot += gv[i][j] * wf[i][j] * xv[i][j];
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = threadIdx.x + i * blockDim.x;
+        if (vi < nvec) {
+          xr[r][i] = reinterpret_cast<const uint4*>(x + row * ldx)[vi];
+          gr[r][i] = reinterpret_cast<const uint4*>(dy + row * (long long)H)[vi];
         }
       }
     }
-    float rstd;
+    float ss[2] = {0.f, 0.f}, dot[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = threadIdx.x + i * blockDim.x;
+        if (vi < nvec) {
+          float xv[8], gv[8];
+          bf16x8 a, b;
+          a.raw = xr[r][i];
+          b.raw = gr[r][i];
+          a.unpack(xv);
+          b.unpack(gv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            ss[r] += xv[j] * xv[j];
+            dot[r] += gv[j] * wf[i][j] * xv[j];
+          }
+        }
+      }
+    float rstd[2];
     if (rstd_in) {
-      rstd = rstd_in[row];
+      rstd[0] = rstd_in[row0];
+      rstd[1] = two ? rstd_in[row0 + 1] : 0.f;
     } else {
-      ss = block_sum(ss, red);
-      rstd = rsqrtf(ss / H + eps);
+      block_sum2(ss[0], ss[1], red);
+      rstd[0] = rsqrtf(ss[0] / H + eps);
+      rstd[1] = rsqrtf(ss[1] / H + eps);
     }
-    dot = block_sum(dot, red);
-    const float c = dot * rstd * rstd * rstd / H;  // mean(g*xh) * rstd, with xh = x*rstd folded in
+    block_sum2(dot[0], dot[1], red);
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = threadIdx.x + i * blockDim.x;
-      if (vi < nvec) {
-        float o[8];
-        if (dres) {
-          bf16x8 r;
-          r.raw = reinterpret_cast<const uint4*>(dres + row * (long long)H)[vi];
-          r.unpack(o);
-        } else {
+    for (int r = 0; r < 2; ++r) {
+      if (r == 1 && !two) break;
+      const long long row = row0 + r;
+      const float c = dot[r] * rstd[r] * rstd[r] * rstd[r] / H;  // mean(g*xh) * rstd, with xh = x*rstd folded in
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = 0.f;
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = threadIdx.x + i * blockDim.x;
+        if (vi < nvec) {
+          float xv[8], gv[8], o[8];
+          bf16x8 a, b;
+          a.raw = xr[r][i];
+          b.raw = gr[r][i];
+          a.unpack(xv);
+          b.unpack(gv);
+          if (dres) {
+            bf16x8 rr;
+            rr.raw = reinterpret_cast<const uint4*>(dres + row * (long long)H)[vi];
+            rr.unpack(o);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            o[j] += gv[j] * wf[i][j] * rstd[r] - xv[j] * c;
+            dwacc[i][j] += gv[j] * xv[j] * rstd[r];
+          }
+          bf16x8 ov;
+          ov.pack(o);
+          reinterpret_cast<uint4*>(dx + row * (long long)H)[vi] = ov.raw;
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          o[j] += gv[i][j] * wf[i][j] * rstd - xv[i][j] * c;
-          dwacc[i][j] += gv[i][j] * xv[i][j] * rstd;
-        }
-        bf16x8 ov;
-        ov.pack(o);
-        reinterpret_cast<uint4*>(dx + row * (long long)H)[vi] = ov.raw;
       }
     }
   }
@@ -346,7 +398,8 @@ int mcb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   int vpt, threads = pick_threads(H, &vpt);
   long long cap = (long long)device_sm_count() * (threads <= 256 ? 4 : 2);
-  long long grid = rows < cap ? rows : cap;
+  long long pairs = (rows + 1) / 2;
+  long long grid = pairs < cap ? pairs : cap;
 #define LAUNCH(V)                                                                                                    \
   rmsnorm_bwd_kernel<V><<<(int)grid, threads, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,              \
                                                       (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,      \

@@ -41,7 +41,7 @@ def _time(fn, iters, flush=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('op', choices=['gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention', 'attention_bwd',
+    ap.add_argument('op', choices=['gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'rmsnorm_bwd', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention', 'attention_bwd',
                                   'gemm_fp8', 'quant_fp8', 'dsa_index', 'topk', 'simple_gla', 'conv1d'])
     ap.add_argument('--m', type=int, default=8192)
     ap.add_argument('--n', type=int, default=4096)
@@ -71,6 +71,15 @@ def main():
         t = _time(lambda: norm.rmsnorm(x, w, 1e-6), a.iters, flush)
         gbs = 2 * x.numel() * 2 / t / 1e9
         res.update(seconds=t, gbs=gbs, frac_of_hbm_peak=gbs / hbm, peak_source=src)
+    elif a.op == 'rmsnorm_bwd':
+        x = torch.randn(M, N, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        w = torch.ones(N, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        y = norm.rmsnorm(x, w, 1e-6)
+        g = torch.randn_like(y)
+        t = _time(lambda: y.backward(g, retain_graph=True), a.iters, flush)
+        gbs = 3 * x.numel() * 2 / t / 1e9
+        res.update(seconds=t, gbs=gbs, frac_of_hbm_peak=gbs / hbm, peak_source=src,
+                   note='includes autograd overhead and the gradient accumulation into x.grad')
     elif a.op == 'swiglu':
         x = torch.randn(M, 2 * N, device=dev, dtype=torch.bfloat16)
         t = _time(lambda: activation.swiglu(x), a.iters, flush)
