@@ -1,8 +1,9 @@
 """Binding of the in-tree sm_100a attention kernels (``csrc/attention``).
 
-Forward: ``attn_fwd_sm100.cu`` (tcgen05 / TMEM, two-pass softmax).  Backward: the in-tree kernels when
-available, else the ``flash_attn`` library backward fed with this forward's output and log-sum-exp (the layouts
-agree: ``lse [heads, T]`` in natural log).
+Forward: ``attn_fwd_sm100.cu`` (tcgen05 / TMEM, two-pass softmax, two softmax warp groups).  Backward:
+``attn_bwd_sm100.cu`` (delta, dQ and dK/dV kernels; the dK/dV kernel can split the query heads of a GQA group over
+several CTAs when the grid would not fill the GPU).  ``MCB200_ATTENTION_BWD_KERNEL=0`` routes the backward through the
+``flash_attn`` library instead (same ``lse [heads, T]`` layout in natural log) for A/B comparisons.
 """
 from __future__ import annotations
 
