@@ -90,6 +90,11 @@ class DSAIndexer(nn.Module):
         q, k, w = self.forward_before_topk(x, qr, ctx)
         T = q.shape[0]
         topk = min(self.topk, T)
+        if mask is None and not (not torch.is_grad_enabled() and dsa.cuda_indexer_supported(q, k)
+                                 and ps.get_world_size('cp') == 1):
+            seg = segment_ids(ctx.cu_seqlens, T)
+            pos = torch.arange(T, device=q.device)
+            mask = (seg[:, None] == seg[None, :]) & (pos[None, :] <= pos[:, None])
         if not torch.is_grad_enabled() and dsa.cuda_indexer_supported(q, k) and ps.get_world_size('cp') == 1:
             # selection only (the indexer is not being trained through this call): tcgen05 scores + radix select
             seq_start = ctx.seq_start
@@ -161,8 +166,10 @@ class MLASelfAttention(nn.Module):
         kv_lat, k_pe = kv_c[:, :self.kv_lora], kv_c[:, self.kv_lora:]
         if tp > 1:  # k_pe feeds every local head: its gradient is a per-rank partial sum
             k_pe = M.copy_to_tensor_model_parallel_region(k_pe.contiguous(), 'tp')
-        kv = self.linear_kv_up_proj(kv_lat.contiguous())          # [T, nh_local * (nope + v)]
         T = q.shape[0]
+        if self.indexer is not None and self._use_gather_path(T):
+            return self.linear_proj(self._sparse_attention_absorbed(x, qr, q, kv_lat, k_pe, ctx, sp).reshape(T, -1))
+        kv = self.linear_kv_up_proj(kv_lat.contiguous())          # [T, nh_local * (nope + v)]
         q = q.view(T, self.nh_local, self.q_dim)
         kv = kv.view(T, self.nh_local, self.qk_nope + self.v_dim)
         q_nope, q_pe = q[..., :self.qk_nope], q[..., self.qk_nope:]
@@ -179,6 +186,43 @@ class MLASelfAttention(nn.Module):
             o = attention(q.contiguous(), k.contiguous(), v, ctx.cu_seqlens, ctx.max_seqlen, causal=True,
                           scale=self.scale)
         return self.linear_proj(o.reshape(T, -1))
+
+    def _use_gather_path(self, T: int) -> bool:
+        """Long inputs take the weight-absorbed, gather-based sparse attention (memory ``O(T * topk)``); short ones the
+        dense-masked form, which also serves the KL-trained indexer.  ``MCB200_DSA_GATHER_MIN_T`` moves the switch."""
+        import os
+        cfg = self.config
+        if self.training and cfg.dsa_indexer_loss_coeff > 0:
+            return False
+        if ps.get_world_size('cp') > 1:
+            return False
+        return T >= int(os.environ.get('MCB200_DSA_GATHER_MIN_T', '4096'))
+
+    def _sparse_attention_absorbed(self, x, qr, q, kv_lat, k_pe, ctx: ForwardContext, sp: bool):
+        cfg = self.config
+        from ..ops import dsa
+        T = q.shape[0]
+        up = self.linear_kv_up_proj
+        lat_n = up.norm(kv_lat.contiguous())                                    # normalised latent [T, kv_lora]
+        if ps.get_world_size('tp') > 1:       # feeds this rank's heads only: the gradient is a per-rank partial sum
+            lat_n = M.copy_to_tensor_model_parallel_region(lat_n, 'tp')
+        W = up.weight.view(self.nh_local, self.qk_nope + self.v_dim, self.kv_lora)
+        q = q.view(T, self.nh_local, self.q_dim)
+        q_nope, q_pe = q[..., :self.qk_nope], q[..., self.qk_nope:]
+        rope = rope_interleaved_to_half if cfg.mla_rope_interleaved else apply_rope_ref
+        q_pe = rope(q_pe, ctx.cos, ctx.sin)
+        k_pe = rope(k_pe.reshape(T, 1, self.qk_rope), ctx.cos, ctx.sin).reshape(T, self.qk_rope)
+        xg = M.gather_from_sequence_parallel_region(x, 'tp', tensor_parallel_output_grad=False) if sp else x
+        with torch.no_grad():
+            idx, _ = self.indexer(xg.detach(), qr.detach(), ctx, None)
+        seq_start = ctx.seq_start
+        if seq_start is None:
+            seg = segment_ids(ctx.cu_seqlens, T)
+            starts = ctx.cu_seqlens[:-1].to(torch.int64) if ctx.cu_seqlens is not None else \
+                torch.zeros(1, dtype=torch.int64, device=q.device)
+            seq_start = starts.to(q.device)[seg]
+        return dsa.sparse_mla_attention_absorbed(q_nope, q_pe, lat_n, k_pe, W[:, :self.qk_nope], W[:, self.qk_nope:],
+                                                 idx, seq_start, self.scale)
 
     def _sparse_attention(self, x, qr, q, k, v, ctx: ForwardContext, sp: bool):
         """Top-k sparse attention.  The indexer runs without gradient for the main loss (as in the Hugging Face

@@ -100,3 +100,47 @@ def topk_indices(scores: torch.Tensor, k: int) -> torch.Tensor:
                                     ctypes.c_int(k), _lib.ptr(idx), _lib.stream_ptr())
     _lib.check_rc(rc, 'mcb_topk_select')
     return idx
+
+
+# ------------------------------------------------------------------------------------------------ scalable path
+def sparse_mla_attention_absorbed(q_nope: torch.Tensor, q_pe: torch.Tensor, kv_lat: torch.Tensor, k_pe: torch.Tensor,
+                                  w_uk: torch.Tensor, w_uv: torch.Tensor, idx: torch.Tensor, seq_start: torch.Tensor,
+                                  scale: float, chunk: int = 512) -> torch.Tensor:
+    """Top-k sparse MLA attention in the weight-absorbed (latent, multi-query) form, one block of queries at a time.
+
+    ``q_nope [T, h, dn]``, ``q_pe [T, h, dr]`` (rotated), ``kv_lat [T, dl]`` (normalised latent), ``k_pe [T, dr]``
+    (rotated, shared by the heads), ``w_uk [h, dn, dl]`` / ``w_uv [h, dv, dl]`` (the two halves of the kv up-projection),
+    ``idx [T, topk]`` selected key positions, ``seq_start [T]``.  Scores are ``(q_nope W_uk) . c_kv + q_pe . k_pe`` over
+    the selected keys only, so memory is ``O(chunk * topk)`` instead of ``O(T^2)`` and the work is the sparse work.  A
+    selected position that the query may not see (later than the query or in another sequence: rows with fewer than
+    top-k visible keys) is masked.  Each block runs under activation checkpointing: its gathered keys are rebuilt in
+    backward, not stored.  Equal to :func:`sparse_attention` on the explicit per-head keys / values.
+    """
+    from torch.utils.checkpoint import checkpoint
+    T, h, dn = q_nope.shape
+    dv = w_uv.shape[1]
+    q_abs = torch.einsum('thn,hnl->thl', q_nope, w_uk.to(q_nope.dtype))                     # [T, h, dl]
+
+    def block(qa, qp, ids, lo, pos, lat, kpe):
+        sel = lat[ids]                                                                      # [C, K, dl]
+        pe = kpe[ids]                                                                       # [C, K, dr]
+        s = torch.einsum('chl,ckl->chk', qa, sel).float() + torch.einsum('chr,ckr->chk', qp, pe).float()
+        s = s * scale
+        vis = (ids <= pos[:, None]) & (ids >= lo[:, None])                                  # [C, K]
+        s = s.masked_fill(~vis[:, None, :], float('-inf'))
+        p = torch.softmax(s, dim=-1)
+        p = torch.nan_to_num(p, nan=0.0).to(sel.dtype)
+        return torch.einsum('chk,ckl->chl', p, sel)                                         # [C, h, dl]
+
+    outs = []
+    pos_all = torch.arange(T, device=q_nope.device)
+    lo_all = seq_start.to(torch.int64)
+    for c0 in range(0, T, chunk):
+        c1 = min(T, c0 + chunk)
+        args = (q_abs[c0:c1], q_pe[c0:c1], idx[c0:c1], lo_all[c0:c1], pos_all[c0:c1], kv_lat, k_pe)
+        if torch.is_grad_enabled() and (q_nope.requires_grad or kv_lat.requires_grad):
+            outs.append(checkpoint(block, *args, use_reentrant=False))
+        else:
+            outs.append(block(*args))
+    o_lat = torch.cat(outs, dim=0)
+    return torch.einsum('thl,hvl->thv', o_lat, w_uv.to(o_lat.dtype)).contiguous()

@@ -81,3 +81,37 @@ def test_dsa_indexer_loss_trains_indexer():
     idx = model.decoder.layers[0].self_attention.indexer
     assert idx.linear_wk.weight.grad is not None and idx.linear_wk.weight.grad.abs().sum() > 0
     assert model.decoder.layers[0].self_attention.indexer_loss is not None
+
+
+def test_dsa_gather_path_equals_dense_path(monkeypatch):
+    """The weight-absorbed, gather-based sparse attention (the long-sequence path) gives the same logits and
+    gradients as the dense-masked formulation, on a packed batch."""
+    from transformers import GlmMoeDsaConfig
+
+    from mcore_bridge_b200.layers.context import PackedSeqParams
+    from mcore_bridge_b200.train.trainer import init_weights
+    c = GlmMoeDsaConfig(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=4,
+                        q_lora_rank=16, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                        n_routed_experts=4, num_experts_per_tok=2, n_group=1, topk_group=1, moe_intermediate_size=16,
+                        intermediate_size=32, mlp_layer_types=['dense', 'dense'], n_shared_experts=1, vocab_size=64,
+                        max_position_embeddings=128, index_n_heads=2, index_head_dim=16, index_topk=6)
+    ids = torch.randint(0, 64, (1, 48), generator=torch.Generator().manual_seed(2))
+    cu = torch.tensor([0, 20, 48], dtype=torch.int32)
+    pos = torch.cat([torch.arange(20), torch.arange(28)]).reshape(1, -1)
+    psp = PackedSeqParams(cu_seqlens_q=cu, cu_seqlens_kv=cu, max_seqlen_q=28, max_seqlen_kv=28)
+    res = []
+    for min_t in ('100000', '0'):
+        monkeypatch.setenv('MCB200_DSA_GATHER_MIN_T', min_t)
+        cfg = ModelConfig(**hf_to_mcore_config(c), params_dtype=torch.float32)
+        model = get_mcore_model(cfg)[0].train()
+        init_weights(model, 0.1, 3)
+        attn = model.decoder.layers[0].self_attention
+        assert attn._use_gather_path(48) == (min_t == '0')
+        loss = model(ids, position_ids=pos, labels=ids, packed_seq_params=psp).mean()
+        loss.backward()
+        res.append((loss.detach(), attn.linear_kv_up_proj.weight.grad.clone(),
+                    attn.linear_kv_down_proj.weight.grad.clone(), attn.linear_q_up_proj.weight.grad.clone(),
+                    attn.linear_kv_up_proj.layer_norm_weight.grad.clone()))
+    assert abs(res[0][0].item() - res[1][0].item()) < 1e-5
+    for a, b in zip(res[0][1:], res[1][1:]):
+        assert torch.allclose(a, b, atol=2e-5), (a - b).abs().max()
