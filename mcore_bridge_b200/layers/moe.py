@@ -261,8 +261,9 @@ class MoELayer(nn.Module):
         send_e = flat_e[order]
         send_p = probs.reshape(-1)[order]
         counts = torch.bincount(flat_e, minlength=E)
-        all_counts = torch.empty(ep, E, dtype=counts.dtype, device=x.device)
+        all_counts = torch.empty(ep * E, dtype=counts.dtype, device=x.device)     # flat: gloo wants 1-D buffers here
         dist.all_gather_into_tensor(all_counts, counts.contiguous(), group=ps.get_group('ep'))
+        all_counts = all_counts.view(ep, E)
         in_splits = counts.view(ep, El).sum(1).tolist()                                   # host sync
         out_splits = all_counts[:, self.ep_rank * El:(self.ep_rank + 1) * El].sum(1).tolist()
         recv = M.all_to_all(send, out_splits, in_splits, 'ep')
