@@ -107,6 +107,8 @@ _GROUP_DEFS = {
     'tp_cp': ('dense', ('tp', 'cp')),
     'tp_dp_cp': ('dense', ('tp', 'cp', 'dp')),
     'pp': ('dense', ('pp',)),
+    'pp_bwd': ('dense', ('pp',)),     # second communicator over the same ranks: gradients travel on it, so a rank
+                                      # pair's activation and gradient messages never share an ordered channel
     'mp': ('dense', ('tp', 'pp')),
     'etp': ('expert', ('etp',)),
     'ep': ('expert', ('ep',)),

@@ -4,9 +4,12 @@
 * 1F1B (one model chunk per rank): ``pp - rank - 1`` warm-up forwards, then one-forward-one-backward, then the
   cool-down backwards.  Sends are asynchronous (``isend``) and complete in the background while the next
   forward/backward runs (``overlap_p2p_comm``); receives are posted before the compute they are needed after.
-* virtual pipeline (several model chunks per rank, ``virtual_pipeline_model_parallel_size``): chunks are walked
-  in order for all micro-batches forward, then in reverse order backward.  Activations of all micro-batches stay
-  alive (GPipe-like memory); the interleaved 1F1B ordering is a scheduling refinement of the same data flow.
+* virtual pipeline (several model chunks per rank, ``virtual_pipeline_model_parallel_size``): interleaved 1F1B
+  when the number of micro-batches is a multiple of the pipeline size — virtual micro-batches are walked in groups
+  of ``pp`` per chunk, ``(pp - rank - 1) * 2 + (V - 1) * pp`` warm-up forwards, then one-forward-one-backward,
+  then the cool-down backwards, the ordering Megatron uses — otherwise chunk by chunk (all forwards, then all
+  backwards; same data flow, GPipe-like memory).  Activations and gradients travel on two communicators so that a
+  pair of ranks that exchanges both (``pp = 2`` with virtual stages) never mixes them in one ordered channel.
 
 Activations travel as ``[T_local, H]`` in ``pipeline_dtype``.  With ``variable_seq_lengths`` the shape is sent
 first (two int64).  The last stage computes the loss; every stage accumulates gradients into the fp32 buffers of
@@ -29,6 +32,7 @@ class _P2P:
         self.cfg, self.device = config, device
         self.prev, self.next = ps.get_pipeline_model_parallel_prev_rank(), ps.get_pipeline_model_parallel_next_rank()
         self.group = ps.get_group('pp')
+        self.group_bwd = ps.get_group('pp_bwd')
         self.pending: List = []
 
     def _shape(self, t: Optional[torch.Tensor], peer: int, send: bool, hidden: int, default_rows: int):
@@ -42,15 +46,16 @@ class _P2P:
         dist.recv(meta, peer, group=self.group)
         return (int(meta[0]), int(meta[1]))
 
-    def send(self, t: torch.Tensor, peer: int):
+    def send(self, t: torch.Tensor, peer: int, grad: bool = False):
         t = t.detach().to(self.cfg.pipeline_dtype).contiguous()
-        self._shape(t, peer, True, t.shape[1], t.shape[0])
-        self.pending.append((dist.isend(t, peer, group=self.group), t))
+        if not grad:
+            self._shape(t, peer, True, t.shape[1], t.shape[0])
+        self.pending.append((dist.isend(t, peer, group=self.group_bwd if grad else self.group), t))
 
-    def recv(self, peer: int, rows: int, hidden: int) -> torch.Tensor:
-        shape = self._shape(None, peer, False, hidden, rows)
+    def recv(self, peer: int, rows: int, hidden: int, grad: bool = False) -> torch.Tensor:
+        shape = (rows, hidden) if grad else self._shape(None, peer, False, hidden, rows)
         buf = torch.empty(shape, dtype=self.cfg.pipeline_dtype, device=self.device)
-        dist.recv(buf, peer, group=self.group)
+        dist.recv(buf, peer, group=self.group_bwd if grad else self.group)
         return buf
 
     def drain(self):
@@ -122,6 +127,8 @@ def forward_backward_pipelining(trainer, microbatches: List[Dict]) -> torch.Tens
         m.is_last_microbatch = False
 
     if len(chunks) > 1:
+        if n % pp == 0:
+            return _interleaved_schedule(trainer, data, p2p, total)
         return _chunked_schedule(trainer, data, p2p, total)
 
     model = chunks[0]
@@ -142,11 +149,11 @@ def forward_backward_pipelining(trainer, microbatches: List[Dict]) -> torch.Tens
         outputs.append(out)
 
     def bwd(j):
-        g = None if last else p2p.recv(p2p.next, outputs[j].shape[0], H)
+        g = None if last else p2p.recv(p2p.next, outputs[j].shape[0], H, grad=True)
         model.is_last_microbatch = (j == n - 1)
         gi = _backward(outputs[j], g, inputs[j])
         if not first:
-            p2p.send(gi, p2p.prev)
+            p2p.send(gi, p2p.prev, grad=True)
         inputs[j] = outputs[j] = None
 
     for i in range(warm):
@@ -183,10 +190,64 @@ def _chunked_schedule(trainer, data, p2p: _P2P, total: torch.Tensor) -> torch.Te
         very_first, very_last = (c == 0 and rank == 0), (c == V - 1 and rank == pp - 1)
         for i in range(n):
             x, out = saved.pop((c, i))
-            g = None if very_last else p2p.recv(p2p.next, out.shape[0], H)
+            g = None if very_last else p2p.recv(p2p.next, out.shape[0], H, grad=True)
             model.is_last_microbatch = (i == n - 1)
             gi = _backward(out, g, x)
             if not very_first:
-                p2p.send(gi, p2p.prev)
+                p2p.send(gi, p2p.prev, grad=True)
         p2p.drain()
+    return total
+
+
+def _interleaved_schedule(trainer, data, p2p: _P2P, total: torch.Tensor) -> torch.Tensor:
+    """Interleaved 1F1B over ``V`` model chunks per rank (virtual stage ``v = chunk * pp + rank``).  Step ``k`` of the
+    forward (backward) sequence works on chunk ``(k % (pp * V)) // pp`` (mirrored for backward) and micro-batch
+    ``(k // (pp * V)) * pp + k % pp``."""
+    cfg = trainer.config
+    pp, rank = ps.get_pipeline_model_parallel_world_size(), ps.get_pipeline_model_parallel_rank()
+    n, V, H = len(data), len(trainer.ddp), cfg.hidden_size
+    steps = n * V
+    warm = min((pp - rank - 1) * 2 + (V - 1) * pp, steps)
+    saved = {}
+    done_bwd = [0] * V
+
+    def where(k: int, forward: bool):
+        c = (k % (pp * V)) // pp
+        if not forward:
+            c = V - 1 - c
+        return c, (k // (pp * V)) * pp + k % pp
+
+    def fwd(k):
+        nonlocal total
+        c, i = where(k, True)
+        model = trainer.ddp[c]
+        very_first, very_last = (c == 0 and rank == 0), (c == V - 1 and rank == pp - 1)
+        x = None if very_first else p2p.recv(p2p.prev, _local_rows(data[i], cfg), H)
+        out = _forward(trainer, model, data[i], x, n, very_last)
+        if very_last:
+            total += out.detach().float()
+        else:
+            p2p.send(out, p2p.next)
+        saved[(c, i)] = (x, out)
+
+    def bwd(k):
+        c, i = where(k, False)
+        model = trainer.ddp[c]
+        very_first, very_last = (c == 0 and rank == 0), (c == V - 1 and rank == pp - 1)
+        x, out = saved.pop((c, i))
+        g = None if very_last else p2p.recv(p2p.next, out.shape[0], H, grad=True)
+        done_bwd[c] += 1
+        model.is_last_microbatch = (done_bwd[c] == n)     # this chunk's gradients are complete after this backward
+        gi = _backward(out, g, x)
+        if not very_first:
+            p2p.send(gi, p2p.prev, grad=True)
+
+    for k in range(warm):
+        fwd(k)
+    for k in range(steps - warm):
+        fwd(warm + k)
+        bwd(k)
+    for k in range(steps - warm, steps):
+        bwd(k)
+    p2p.drain()
     return total
