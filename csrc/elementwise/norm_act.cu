@@ -137,7 +137,7 @@ __device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
 }
 
 template <int VPT>
-__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                                    float* __restrict__ dw, long long rows, int H, long long ldx, float eps,
@@ -396,8 +396,12 @@ int mcb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   if (rows == 0) return 0;
   if (H % 8 || ldx % 8) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
-  int vpt, threads = pick_threads(H, &vpt);
-  long long cap = (long long)device_sm_count() * (threads <= 256 ? 4 : 2);
+  // the two-rows-per-iteration kernel needs up to ~160 registers: blocks stay at <= 256 threads
+  const int nvec = H / 8;
+  int threads = nvec <= 128 ? 128 : 256;
+  int vpt = (nvec + threads - 1) / threads;
+  if (vpt > 8) return -2;                      // H > 16384
+  long long cap = (long long)device_sm_count() * (vpt <= 2 ? 2 : 1);
   long long pairs = (rows + 1) / 2;
   long long grid = pairs < cap ? pairs : cap;
 #define LAUNCH(V)                                                                                                    \

@@ -40,6 +40,36 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
   *reinterpret_cast<uint4*>(p) = o;
 }
 
+// the KW taps of 8 consecutive channels are 8 * KW contiguous bf16 (w is [C, KW]): fetched with 16-byte loads when the
+// span is a multiple of 16 bytes, which it is for KW = 2 and 4
+template <int KW>
+__device__ __forceinline__ void load_taps(const __nv_bfloat16* __restrict__ w, int c0, float (&wt)[8][KW]) {
+  if constexpr ((8 * KW * 2) % 16 == 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(w + (long long)c0 * KW);
+    float flat[8 * KW];
+#pragma unroll
+    for (int v = 0; v < 8 * KW / 8; ++v) {
+      const uint4 raw = src[v];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(h[i]);
+        flat[v * 8 + 2 * i] = t.x;
+        flat[v * 8 + 2 * i + 1] = t.y;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+      for (int j = 0; j < KW; ++j) wt[c][j] = flat[c * KW + j];
+  } else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+      for (int j = 0; j < KW; ++j) wt[c][j] = __bfloat162float(w[(c0 + c) * KW + j]);
+  }
+}
+
 // ------------------------------------------------------------------------------------------ causal conv1d + SiLU
 // x, y [T, C] bf16; w [C, KW] bf16 (KW <= 4); thread = (token, 8 channels)
 template <int KW>
@@ -52,10 +82,7 @@ __global__ void conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, cons
   const int t = int(id / cv), c0 = int(id % cv) * 8;
   const int s0 = seq_start[t];
   float wt[8][KW];
-#pragma unroll
-  for (int c = 0; c < 8; ++c)
-#pragma unroll
-    for (int j = 0; j < KW; ++j) wt[c][j] = __bfloat162float(w[(c0 + c) * KW + j]);
+  load_taps<KW>(w, c0, wt);
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int j = 0; j < KW; ++j) {
@@ -88,13 +115,11 @@ __global__ void conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, cons
   const int chunk = int(id / cv), c0 = int(id % cv) * 8;
   const int t_lo = chunk * TOK, t_hi = min(T, t_lo + TOK);
   float wt[8][KW], dwa[8][KW];
+  load_taps<KW>(w, c0, wt);
 #pragma unroll
   for (int c = 0; c < 8; ++c)
 #pragma unroll
-    for (int j = 0; j < KW; ++j) {
-      wt[c][j] = __bfloat162float(w[(c0 + c) * KW + j]);
-      dwa[c][j] = 0.f;
-    }
+    for (int j = 0; j < KW; ++j) dwa[c][j] = 0.f;
   // dpre of tokens t .. t+KW-1 is needed for dx[t]; walk tokens and keep a window of dpre values
   // dpre[u] = dy[u] * d silu(pre[u]),  pre[u] = sum_j w[j] x[u-(KW-1)+j]
   auto dpre_at = [&](int u, bool own, float (&out)[8]) {

@@ -9,6 +9,35 @@ from ..parallel import state as ps
 from .linear import _set_tp_attrs
 
 
+class _EmbeddingFn(torch.autograd.Function):
+    """Row gather whose backward scatter-adds the token gradients straight into the fp32 ``main_grad`` of the
+    weight (when the distributed optimizer provides one) instead of materialising a dense ``[vocab, H]`` gradient,
+    converting it to fp32 and adding it: for a 152k x 4096 table that is ~10 GB of traffic per micro-batch saved."""
+
+    @staticmethod
+    def forward(ctx, ids, weight, mask):
+        ctx.save_for_backward(ids, mask if mask is not None else torch.empty(0))
+        ctx.weight, ctx.has_mask = weight, mask is not None
+        out = torch.nn.functional.embedding(ids, weight)
+        if mask is not None:
+            out = out.masked_fill(mask[..., None], 0.0)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        ids, mask = ctx.saved_tensors
+        w = ctx.weight
+        g2 = g.reshape(-1, g.shape[-1])
+        flat = ids.reshape(-1)
+        if ctx.has_mask:
+            g2 = g2.masked_fill(mask.reshape(-1)[:, None], 0.0)
+        w.main_grad.index_add_(0, flat, g2.to(w.main_grad.dtype))
+        hook = getattr(w, 'grad_ready_hook', None)
+        if hook is not None:
+            hook()
+        return None, None, None
+
+
 class VocabParallelEmbedding(nn.Module):
 
     def __init__(self, num_embeddings: int, embedding_dim: int, config):
@@ -25,14 +54,21 @@ class VocabParallelEmbedding(nn.Module):
 
     def forward(self, input_ids: torch.Tensor, scatter_to_sequence_parallel: bool = False) -> torch.Tensor:
         """``input_ids [T]`` -> ``[T, H]`` (or ``[T/tp, H]`` reduce-scattered for sequence parallelism)."""
+        fused_grad = getattr(self.weight, 'main_grad', None) is not None and torch.is_grad_enabled() \
+            and self.weight.requires_grad
         if self.tp > 1:
             local = input_ids - self.vocab_start
             mask = (local < 0) | (local >= self.per_partition)
-            out = torch.nn.functional.embedding(local.masked_fill(mask, 0), self.weight)
-            out = out.masked_fill(mask[..., None], 0.0)
+            if fused_grad:
+                out = _EmbeddingFn.apply(local.masked_fill(mask, 0), self.weight, mask)
+            else:
+                out = torch.nn.functional.embedding(local.masked_fill(mask, 0), self.weight)
+                out = out.masked_fill(mask[..., None], 0.0)
             if scatter_to_sequence_parallel:
                 return M.reduce_scatter_to_sequence_parallel_region(out)
             return M.reduce_from_tensor_model_parallel_region(out)
+        if fused_grad:
+            return _EmbeddingFn.apply(input_ids, self.weight, None)
         return torch.nn.functional.embedding(input_ids, self.weight)
 
 

@@ -108,7 +108,7 @@ class LayerNormColumnParallelLinear(ColumnParallelLinear):
         """Single-rank RMSNorm path that does not keep the normalised activation (``ops/fused_mlp.py``)."""
         if self.return_layernorm_output or self.bias is not None or self.spec.fp8 or self.gather_output:
             return False
-        if self.normalization == 'LayerNorm' or ps.get_world_size(self.group) > 1:
+        if self.normalization == 'LayerNorm' or ps.get_world_size(self.group) > 1 or self.input_size > 16384:
             return False
         if not getattr(self.config, 'lean_activations', True):
             return False

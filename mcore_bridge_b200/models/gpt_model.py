@@ -71,6 +71,9 @@ class GPTModel(nn.Module):
                                                          sequence_parallel=False, fp8=False)
                 if self.share_embeddings_and_output_weights and pre_process:
                     self.output_layer.weight = self.embedding.word_embeddings.weight
+                    # embedding lookup and head (and, per MTP depth, one more of each) produce a gradient for this
+                    # tensor in every backward pass; the bucket waits for all of them
+                    self.output_layer.weight.grad_contributions = 2 + 2 * int(config.mtp_num_layers or 0)
             elif task == 'seq_cls':
                 self.output_layer = ReplicatedLinear(config.hidden_size, config.num_labels, config, bias=False,
                                                      sequence_parallel_grad=False)

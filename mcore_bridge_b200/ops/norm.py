@@ -60,7 +60,7 @@ class _RMSNormCuda(torch.autograd.Function):
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, zero_centered: bool = False) -> torch.Tensor:
     """Normalises the last dimension.  ``x`` may be ``[..., H]`` (per-head norm: pass ``[..., heads, d]``)."""
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 \
-            and x.shape[-1] <= 65536 and _lib.available():
+            and x.shape[-1] <= 16384 and _lib.available():
         return _RMSNormCuda.apply(x, w, eps, zero_centered)
     return rmsnorm_ref(x, w, eps, zero_centered)
 

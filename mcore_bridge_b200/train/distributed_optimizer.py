@@ -149,7 +149,8 @@ class DistributedDataParallel(nn.Module):
     def _reset_pending(self):
         for buf in self.buffers.values():
             for b in buf.buckets:
-                b.pending = len(b.params)
+                # a parameter used twice in the graph (tied embedding / head) reports twice
+                b.pending = sum(int(getattr(p, 'grad_contributions', 1)) for p in b.params)
                 b.work = None
 
     def _needs_tp_reduce(self, b: Bucket) -> bool:
