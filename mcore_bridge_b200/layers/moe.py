@@ -271,6 +271,37 @@ class MoELayer(nn.Module):
         recv_p = M.all_to_all(send_p.contiguous().view(-1, 1), out_splits, in_splits, 'ep').view(-1)
         return recv, recv_e, recv_p, (order, src_token, in_splits, out_splits)
 
+    def _experts_nccl(self, x: torch.Tensor, probs: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        """Permute / exchange / grouped experts / combine through torch and NCCL (baseline and CPU path)."""
+        T = x.shape[0]
+        k = idx.shape[1]
+        if self.ep == 1:
+            src_token = torch.arange(T, device=x.device).repeat_interleave(k)
+            dest, offsets, cap = moe_ops.permute_plan(idx.reshape(-1), self.num_local_experts)
+            xp = moe_ops.permute(x, src_token, dest, cap)
+            pflat = probs.reshape(-1)
+            if self.apply_probs_on_input:
+                xp = _scale_rows(xp, dest, pflat, cap)
+                row_probs = None
+            else:
+                row_probs = _scatter_rows(pflat, dest, cap)
+            yp = self.experts(xp, offsets, row_probs)
+            return moe_ops.unpermute(yp, src_token, dest, T, None)
+        recv, recv_e, recv_p, (order, src_token, in_splits, out_splits) = self._dispatch_nccl(x, probs, idx)
+        R = recv.shape[0]
+        dest, offsets, cap = moe_ops.permute_plan(recv_e, self.num_local_experts)
+        ar = torch.arange(R, device=x.device)
+        xp = moe_ops.permute(recv, ar, dest, cap)
+        if self.apply_probs_on_input:
+            xp = _scale_rows(xp, dest, recv_p, cap)
+            row_probs = None
+        else:
+            row_probs = _scatter_rows(recv_p, dest, cap)
+        yp = self.experts(xp, offsets, row_probs)
+        back = moe_ops.unpermute(yp, ar, dest, R, None)          # rows back in arrival order
+        ret = M.all_to_all(back, in_splits, out_splits, 'ep')    # rows in `order`
+        return moe_ops.unpermute(ret, src_token[order], torch.arange(ret.shape[0], device=x.device), T, None)
+
     def _forward_fused(self, x, padding_mask, seg_ids, num_seqs):
         """Router, exchange and combine on the in-tree kernels (``layers/moe_fused.py``)."""
         from . import moe_fused as F
@@ -332,37 +363,24 @@ class MoELayer(nn.Module):
         if moe_fused.available(x) and ps.get_world_size('etp') == 1 and H % 8 == 0:
             return self._forward_fused(x, padding_mask, seg_ids, num_seqs)
         probs, idx = self.router(x, padding_mask, seg_ids, num_seqs)
-        k = idx.shape[1]
         etp = ps.get_world_size('etp')
-        if self.ep == 1:
-            src_token = torch.arange(T, device=x.device).repeat_interleave(k)
-            dest, offsets, cap = moe_ops.permute_plan(idx.reshape(-1), self.num_local_experts)
-            xp = moe_ops.permute(x, src_token, dest, cap)
-            pflat = probs.reshape(-1)
-            if self.apply_probs_on_input:
-                xp = _scale_rows(xp, dest, pflat, cap)
-                row_probs = None
-            else:
-                row_probs = _scatter_rows(pflat, dest, cap)
-            if etp > 1:
-                raise NotImplementedError('expert tensor parallelism > 1')
-            yp = self.experts(xp, offsets, row_probs)
-            y = moe_ops.unpermute(yp, src_token, dest, T, None)
-        else:
-            recv, recv_e, recv_p, (order, src_token, in_splits, out_splits) = self._dispatch_nccl(x, probs, idx)
-            R = recv.shape[0]
-            dest, offsets, cap = moe_ops.permute_plan(recv_e, self.num_local_experts)
-            ar = torch.arange(R, device=x.device)
-            xp = moe_ops.permute(recv, ar, dest, cap)
-            if self.apply_probs_on_input:
-                xp = _scale_rows(xp, dest, recv_p, cap)
-                row_probs = None
-            else:
-                row_probs = _scatter_rows(recv_p, dest, cap)
-            yp = self.experts(xp, offsets, row_probs)
-            back = moe_ops.unpermute(yp, ar, dest, R, None)          # rows back in arrival order
-            ret = M.all_to_all(back, in_splits, out_splits, 'ep')    # rows in `order`
-            y = moe_ops.unpermute(ret, src_token[order], torch.arange(ret.shape[0], device=x.device), T, None)
+        x_in = x
+        if etp > 1:
+            # Expert tensor parallelism: every rank of the group holds a slice of each local expert's FFN, so all of
+            # them process the group's tokens and their partial outputs are summed.  Routing is computed once per
+            # token (on the rank that owns it) and shared.
+            sp = cfg.sequence_parallel and ps.get_world_size('tp') > 1
+            if sp:      # tokens are sharded over the group: gather them (gradient: reduce-scatter of the partials)
+                x_in = M.gather_from_sequence_parallel_region(x, 'etp', tensor_parallel_output_grad=True)
+                probs = M.gather_from_sequence_parallel_region(probs, 'etp', tensor_parallel_output_grad=True)
+                idx = M.all_gather_dim0(idx.contiguous(), 'etp')
+            else:       # tokens are replicated: identity forward, gradients of the partial paths are summed
+                x_in = M.copy_to_tensor_model_parallel_region(x, 'etp')
+                probs = M.copy_to_tensor_model_parallel_region(probs, 'etp')
+        y = self._experts_nccl(x_in, probs, idx)
+        if etp > 1:
+            y = M.reduce_scatter_to_sequence_parallel_region(y, 'etp') if sp else \
+                M.reduce_from_tensor_model_parallel_region(y, 'etp')
         if self.shared_experts is not None:
             y = y + self.shared_experts(x)
         return y
