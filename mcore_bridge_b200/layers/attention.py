@@ -101,6 +101,10 @@ class SelfAttention(nn.Module):
         elif config.qk_layernorm:
             self.q_layernorm = Norm(config, self.d, sequence_parallel_grad=False)
             self.k_layernorm = Norm(config, self.d, sequence_parallel_grad=False)
+            # replicated weights applied to this rank's heads only: every rank holds a partial gradient, summed over
+            # the TP group by the optimizer (the flag it looks at is `sequence_parallel`), with or without SP
+            for p_ in (self.q_layernorm.weight, self.k_layernorm.weight):
+                p_.sequence_parallel = ps.get_world_size('tp') > 1
         else:
             self.q_layernorm = self.k_layernorm = None
         self.qk_l2_norm = bool(config.qk_l2_norm)

@@ -45,6 +45,9 @@ class GatedDeltaNet(nn.Module):
         self.dt_bias = nn.Parameter(torch.ones(self.nv_local, dtype=dt))
         self.out_norm = nn.Module()
         self.out_norm.weight = nn.Parameter(torch.ones(self.dv, dtype=dt))
+        # shared by all heads but applied to this rank's heads (and, under CP, this rank's head slice) only: the
+        # partial gradients are summed over the TP group by the optimizer
+        self.out_norm.weight.sequence_parallel = tp > 1
         for p in (self.conv1d.weight, self.A_log, self.dt_bias):
             p.tensor_model_parallel = tp > 1
             p.partition_dim = 0

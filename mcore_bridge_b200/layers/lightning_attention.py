@@ -74,6 +74,8 @@ class LightningAttention(nn.Module):
         if config.qk_layernorm:
             self.q_layernorm = Norm(config, self.d, sequence_parallel_grad=False)
             self.k_layernorm = Norm(config, self.d, sequence_parallel_grad=False)
+            for p_ in (self.q_layernorm.weight, self.k_layernorm.weight):     # partial gradient per TP rank
+                p_.sequence_parallel = tp > 1
         else:
             self.q_layernorm = self.k_layernorm = None
         self.g_proj = ColumnParallelLinear(config.hidden_size, proj, config, bias=False)

@@ -22,7 +22,8 @@ def _worker(rank, world, ckpt_dir, sp):
     exported = {k: v.clone() for k, v in cfg.bridge.export_weights([model])}
     gq = model.decoder.layers[0].self_attention.linear_qkv.weight.grad.clone()
     gn = model.decoder.layers[0].self_attention.linear_qkv.layer_norm_weight.grad.clone()
-    return loss.detach(), logits, exported, gq, gn
+    gqn = model.decoder.layers[0].self_attention.q_layernorm.weight.grad.clone()
+    return loss.detach(), logits, exported, gq, gn, gqn
 
 
 def _setup(tmp):
@@ -50,7 +51,7 @@ def _check(tmp_path, sp):
     ref_loss = torch.nn.functional.cross_entropy(ref_logits.view(-1, 1024), labels.view(-1), reduction='none').view(2, 128)
     ref_loss.mean().backward()
     for r in range(2):
-        loss, logits, exported, gq, gn = res[r]
+        loss, logits, exported, gq, gn, _ = res[r]
         assert torch.allclose(loss, ref_loss.detach(), atol=1e-5)
         assert torch.allclose(logits, ref_logits.detach(), atol=1e-5)
         sd = hf.state_dict()
@@ -62,6 +63,8 @@ def _check(tmp_path, sp):
     full = qkv_to_mcore(a.q_proj.weight.grad, a.k_proj.weight.grad, a.v_proj.weight.grad, 2)
     got = torch.cat([res[0][3], res[1][3]], dim=0)
     assert torch.allclose(got, full, atol=1e-6)
+    # per-head q norm: replicated weight, each rank covers its own heads, the partial gradients sum to the full one
+    assert torch.allclose(res[0][5] + res[1][5], hf.model.layers[0].self_attn.q_norm.weight.grad, atol=1e-6)
     # replicated norm weight: with SP each rank has a partial gradient that sums to the full one
     gn_ref = hf.model.layers[0].input_layernorm.weight.grad
     if sp:
