@@ -84,9 +84,16 @@ class SelfAttention(nn.Module):
         self.nq = config.num_attention_heads
         self.ng = num_query_groups or config.num_query_groups
         assert self.nq % tp == 0
+        # More TP ranks than KV heads: the packed QKV matrix is still split evenly by rows, so a rank's slice cuts
+        # through a group [q heads | k | v].  At run time the projection output is all-gathered on the last dim, the
+        # rank takes its group and, inside it, its share of the query heads; every `kv_rep` ranks share one KV head
+        # (reference ``src/mcore_bridge/model/modules/gated_self_attention.py:23-38,66-72``).
+        self.kv_rep = 1
         if self.ng % tp != 0:
-            raise NotImplementedError(f'num_query_groups ({self.ng}) must be divisible by TP ({tp})')
-        self.nq_local, self.ng_local = self.nq // tp, self.ng // tp
+            if tp % self.ng != 0:
+                raise NotImplementedError(f'TP ({tp}) must divide or be a multiple of num_query_groups ({self.ng})')
+            self.kv_rep = tp // self.ng
+        self.nq_local, self.ng_local = self.nq // tp, max(1, self.ng // tp)
         self.qpg = self.nq // self.ng
         self.gate = bool(config.attention_output_gate)
         qkv_out = (self.nq * (2 if self.gate else 1) + 2 * self.ng) * self.d
@@ -117,6 +124,17 @@ class SelfAttention(nn.Module):
     def forward(self, x: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
         cfg = self.config
         qkv = self.linear_qkv(x)                                  # [T, local packed qkv]
+        qpg = self.qpg
+        if self.kv_rep > 1:
+            from ..parallel import mappings as M
+            full = M.all_gather_last_dim_sum_grad(qkv, 'tp')      # [T, ng * group]
+            r = ps.get_rank_in('tp')
+            mult = 2 if self.gate else 1
+            gsize = (self.qpg * mult + 2) * self.d
+            grp = full[:, (r // self.kv_rep) * gsize:(r // self.kv_rep + 1) * gsize]
+            qpg = self.qpg // self.kv_rep                         # query heads of the group handled here
+            q0 = (r % self.kv_rep) * qpg * mult * self.d
+            qkv = torch.cat([grp[:, q0:q0 + qpg * mult * self.d], grp[:, self.qpg * mult * self.d:]], dim=-1)
         cos = sin = None
         if self.use_rope:
             if self.rope_key is not None and self.rope_key in ctx.rope_tables:
@@ -126,14 +144,14 @@ class SelfAttention(nn.Module):
         wq = self.q_layernorm.weight if self.q_layernorm is not None else None
         wk = self.k_layernorm.weight if self.k_layernorm is not None else None
         if self.q_norm is not None:
-            q, k, v, gate = qkv_split_norm_rope(qkv, None, None, None, None, self.ng_local, self.qpg, self.d,
+            q, k, v, gate = qkv_split_norm_rope(qkv, None, None, None, None, self.ng_local, qpg, self.d,
                                                 self.gate, cfg.rotary_interleaved, cfg.layernorm_epsilon, False)
             q, k = self.q_norm(q), self.k_norm(k)
             if cos is not None:
                 from ..ops.rope import apply_rope
                 q, k = apply_rope(q, cos, sin, cfg.rotary_interleaved), apply_rope(k, cos, sin, cfg.rotary_interleaved)
         else:
-            q, k, v, gate = qkv_split_norm_rope(qkv, wq, wk, cos, sin, self.ng_local, self.qpg, self.d, self.gate,
+            q, k, v, gate = qkv_split_norm_rope(qkv, wq, wk, cos, sin, self.ng_local, qpg, self.d, self.gate,
                                                 cfg.rotary_interleaved, cfg.layernorm_epsilon,
                                                 cfg.layernorm_zero_centered_gamma)
         if self.qk_l2_norm:

@@ -166,6 +166,24 @@ class _ScatterLastDim(torch.autograd.Function):
         return all_gather_last_dim(g, ctx.group_name), None
 
 
+class _GatherLastDimSum(torch.autograd.Function):
+    """All-gather on the last dim whose consumers differ per rank: the gradients of the gathered tensor are summed over
+    the group and each rank keeps the slice it produced (reduce-scatter on the last dim)."""
+
+    @staticmethod
+    def forward(ctx, x, group_name):
+        ctx.group_name = group_name
+        return all_gather_last_dim(x, group_name)
+
+    @staticmethod
+    def backward(ctx, g):
+        return split_last_dim(all_reduce(g.contiguous().clone(), ctx.group_name), ctx.group_name), None
+
+
+def all_gather_last_dim_sum_grad(x, group_name: str = 'tp'):
+    return x if _size(group_name) == 1 else _GatherLastDimSum.apply(x, group_name)
+
+
 class _AllReduceBoth(torch.autograd.Function):
     """Sum over the group in forward *and* backward: for statistics shared by ranks whose downstream computation
     differs (each rank's loss term depends on every rank's contribution to the statistic)."""

@@ -4,13 +4,13 @@ import torch
 from dist_utils import run_ranks
 
 
-def _worker(rank, world, ckpt_dir, sp):
+def _worker(rank, world, ckpt_dir, sp, tp=2):
     from mcore_bridge_b200 import ModelConfig, get_mcore_model, hf_to_mcore_config
     from mcore_bridge_b200.parallel import state as ps
     from mcore_bridge_b200.train.presets import hf_config
-    ps.initialize_model_parallel(tensor_model_parallel_size=2)
+    ps.initialize_model_parallel(tensor_model_parallel_size=tp)
     cfg = ModelConfig(**hf_to_mcore_config(hf_config('qwen3_tiny')), params_dtype=torch.float32,
-                      tensor_model_parallel_size=2, sequence_parallel=sp)
+                      tensor_model_parallel_size=tp, sequence_parallel=sp)
     model = get_mcore_model(cfg)[0]
     cfg.bridge.load_weights([model], ckpt_dir)
     g = torch.Generator().manual_seed(1)
@@ -79,3 +79,30 @@ def test_tp2(tmp_path):
 
 def test_tp2_sequence_parallel(tmp_path):
     _check(tmp_path, sp=True)
+
+
+def test_tp4_more_ranks_than_kv_heads(tmp_path):
+    """4 query heads / 2 KV heads on TP=4: two ranks share each KV head (the projection output is gathered on the
+    last dim and re-sliced); loss, logits, export and the packed QKV weight gradient equal the dense model."""
+    d = str(tmp_path / 'ckpt')
+    hf = _setup(d)
+    res = run_ranks(_worker, 4, d, True, 4)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 1024, (2, 128), generator=g)
+    labels = torch.randint(0, 1024, (2, 128), generator=g)
+    ref_logits = hf(ids).logits
+    ref_loss = torch.nn.functional.cross_entropy(ref_logits.view(-1, 1024), labels.view(-1), reduction='none').view(2, 128)
+    ref_loss.mean().backward()
+    sd = hf.state_dict()
+    for r in range(4):
+        loss, logits, exported, gq, gn, gqn = res[r]
+        assert torch.allclose(loss, ref_loss.detach(), atol=1e-5)
+        assert torch.allclose(logits, ref_logits.detach(), atol=1e-5)
+        for k, v in exported.items():
+            assert torch.equal(v, sd[k]), k
+    from mcore_bridge_b200.bridge.gpt_bridge import qkv_to_mcore
+    a = hf.model.layers[0].self_attn
+    full = qkv_to_mcore(a.q_proj.weight.grad, a.k_proj.weight.grad, a.v_proj.weight.grad, 2)
+    got = torch.cat([res[r][3] for r in range(4)], dim=0)
+    assert torch.allclose(got, full, atol=1e-6)
+    assert torch.allclose(sum(res[r][5] for r in range(4)), a.q_norm.weight.grad, atol=1e-6)
