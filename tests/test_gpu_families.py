@@ -1,0 +1,74 @@
+"""Hybrid / sparse-attention families on the GPU in bf16: the CUDA kernels they route through (causal conv1d, gated
+RMSNorm, per-head norms, DSA indexer scores + top-k, attention, grouped GEMMs) against the same model in fp32 on the CPU
+reference paths."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda'
+
+
+def _build(hf_cfg, dtype, device, seed=5, **kw):
+    from mcore_bridge_b200 import ModelConfig, hf_to_mcore_config
+    from mcore_bridge_b200.models.gpt_model import GPTModel
+    from mcore_bridge_b200.train.trainer import init_weights
+    cfg = ModelConfig(**hf_to_mcore_config(hf_cfg), params_dtype=dtype, **kw)
+    with torch.device(device):
+        model = GPTModel(cfg)
+    init_weights(model, 0.05, seed)
+    return cfg, model
+
+
+def _compare(hf_cfg, vocab, T=192, tol=6e-2, **kw):
+    _, ref = _build(hf_cfg, torch.float32, 'cpu', **kw)
+    _, gpu = _build(hf_cfg, torch.bfloat16, 'cuda', **kw)
+    with torch.no_grad():       # identical weights: the bf16 model gets the rounded fp32 values
+        for (n1, p1), (n2, p2) in zip(ref.named_parameters(), gpu.named_parameters()):
+            assert n1 == n2
+            p2.copy_(p1.to(torch.bfloat16))
+            p1.copy_(p2.float().cpu())
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, vocab, (1, T), generator=g)
+    labels = torch.randint(0, vocab, (1, T), generator=g)
+    ref.train(), gpu.train()
+    l_ref = ref(ids, labels=labels).mean()
+    l_gpu = gpu(ids.to(DEV), labels=labels.to(DEV)).mean()
+    l_ref.backward()
+    l_gpu.backward()
+    torch.cuda.synchronize()
+    from mcore_bridge_b200.ops import _lib
+    _lib.check_status()
+    assert abs(l_ref.item() - l_gpu.item()) < 3e-2, (l_ref.item(), l_gpu.item())
+    worst = 0.0
+    for (n, p1), (_, p2) in zip(ref.named_parameters(), gpu.named_parameters()):
+        if p1.grad is None or p1.grad.abs().max() == 0:
+            continue
+        r = ((p2.grad.float().cpu() - p1.grad).norm() / p1.grad.norm()).item()
+        worst = max(worst, r)
+        assert r < tol * 3, (n, r)
+    return worst
+
+
+def test_qwen3_next_hybrid_gpu_matches_cpu_reference():
+    from transformers import Qwen3NextConfig
+    c = Qwen3NextConfig(num_hidden_layers=4, hidden_size=128, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                        intermediate_size=256, moe_intermediate_size=64, shared_expert_intermediate_size=64,
+                        num_experts=8, num_experts_per_tok=2, linear_num_key_heads=2, linear_num_value_heads=4,
+                        linear_key_head_dim=64, linear_value_head_dim=64, linear_conv_kernel_dim=4, vocab_size=256,
+                        max_position_embeddings=512, full_attention_interval=4, partial_rotary_factor=0.25,
+                        tie_word_embeddings=False, decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True)
+    _compare(c, 256)
+
+
+def test_glm_dsa_gpu_matches_cpu_reference(monkeypatch):
+    from transformers import GlmMoeDsaConfig
+    c = GlmMoeDsaConfig(num_hidden_layers=2, hidden_size=128, num_attention_heads=4, num_key_value_heads=4,
+                        q_lora_rank=32, kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                        n_routed_experts=4, num_experts_per_tok=2, n_group=1, topk_group=1, moe_intermediate_size=32,
+                        intermediate_size=128, mlp_layer_types=['dense', 'sparse'], n_shared_experts=1, vocab_size=256,
+                        max_position_embeddings=512, index_n_heads=4, index_head_dim=128, index_topk=64,
+                        tie_word_embeddings=False)
+    # both the dense-masked and the gather-based sparse attention, each with the CUDA indexer + top-k for selection
+    for min_t in ('100000', '0'):
+        monkeypatch.setenv('MCB200_DSA_GATHER_MIN_T', min_t)
+        _compare(c, 256, T=256, tol=8e-2)
