@@ -178,7 +178,7 @@ def main():
         models = [get_peft_model(m, lc) for m in models]
     trainer = Trainer(cfg, TrainConfig(), models=models)
     dp = ps.get_world_size('dp')
-    mbs = args.micro_batch_size or min(4, world)
+    mbs = args.micro_batch_size or (8 if world >= 8 else min(4, world))
     global_batch = args.seqs_per_gpu * world
     n_micro = global_batch // dp // mbs                # micro-batches this rank runs per step
     assert n_micro * mbs * dp == global_batch

@@ -14,6 +14,7 @@
 // four (thread = query row).  Group g owns score buffer g in TMEM, i.e. every other key block of both passes, so each
 // scheduler has two softmax warps to interleave (exponentials of one block overlap the TMEM reads of the next); the
 // groups exchange their partial row maxima after pass 1 and their partial row sums after pass 2 through shared memory.
+#include <type_traits>
 #include "../common/host_utils.cuh"
 #include "../common/ptx.cuh"
 
@@ -231,25 +232,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_after();
       const int n0 = (kb0 + j) * BNK;
       const bool full = (lo <= n0) && (n0 + BNK - 1 <= hi);
-#pragma unroll 1
-      for (int c = 0; c < BNK; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_addr + COL_S + sb * BNK + c, v);
-        tmem_ld_wait();
-        if (full) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = n0 + c + e;
-            if (key >= lo && key <= hi) mx = fmaxf(mx, __uint_as_float(v[e]));
-          }
-        }
-      }
+      // the whole 128-column row in one TMEM round trip; the score buffer is released as soon as the values are in
+      // registers, so the next QK^T of this group overlaps the arithmetic below
+      uint32_t v0[64], v1[64];
+      tmem_ld_32x32_x64(tmem + lane_addr + COL_S + sb * BNK, v0);
+      tmem_ld_32x32_x64(tmem + lane_addr + COL_S + sb * BNK + 64, v1);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_empty[sb]));
+      if (full) {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[e]), __uint_as_float(v1[e])));
+      } else {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) {
+          const int key = n0 + e;
+          if (key >= lo && key <= hi) mx = fmaxf(mx, __uint_as_float(v0[e]));
+          if (key + 64 >= lo && key + 64 <= hi) mx = fmaxf(mx, __uint_as_float(v1[e]));
+        }
+      }
     }
     // The row maximum is over both groups' blocks.  The partial maxima travel through the P buffers, which nothing
     // has written yet: a group leaves its value in the buffer the *other* group owns in pass 2, so the value is
@@ -270,47 +272,46 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t sit = uint32_t(nblk + j);
       const uint32_t sph = (sit >> 1) & 1, pb = j & 1, pph = (uint32_t(j) >> 1) & 1;
       if (!mbar_wait(smem_u32(&s_full[sb]), sph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      if (!mbar_wait(smem_u32(&p_empty[pb]), pph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
       tc_fence_after();
+      uint32_t v0[64], v1[64];
+      tmem_ld_32x32_x64(tmem + lane_addr + COL_S + sb * BNK, v0);
+      tmem_ld_32x32_x64(tmem + lane_addr + COL_S + sb * BNK + 64, v1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_empty[sb]));   // scores are in registers: the next QK^T may start
+      if (!mbar_wait(smem_u32(&p_empty[pb]), pph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
       const int n0 = (kb0 + j) * BNK;
       const bool full = (lo <= n0) && (n0 + BNK - 1 <= hi);
       uint8_t* prow = smem + L::OFF_P + pb * L::P_BYTES + r * 128;
-#pragma unroll 1
-      for (int c = 0; c < BNK; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_addr + COL_S + sb * BNK + c, v);
-        tmem_ld_wait();
-        float pv[32];
-        if (full) {
+      auto half = [&](const uint32_t (&v)[64], int c0, auto fullc) {
+        constexpr bool FULL = decltype(fullc)::value;
+        uint8_t* box = prow + (c0 >> 6) * (BM * 128);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            pv[e] = exp2f(__uint_as_float(v[e]) * p.scale_log2 - m2);
-            sum += pv[e];
+        for (int e = 0; e < 64; e += 8) {
+          float pv[8];
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const float x = exp2f(__uint_as_float(v[e + t]) * p.scale_log2 - m2);
+            const int key = n0 + c0 + e + t;
+            pv[t] = (FULL || (key >= lo && key <= hi)) ? x : 0.f;
+            sum += pv[t];
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = n0 + c + e;
-            const float x = exp2f(__uint_as_float(v[e]) * p.scale_log2 - m2);
-            pv[e] = (key >= lo && key <= hi) ? x : 0.f;
-            sum += pv[e];
-          }
-        }
-        uint8_t* box = prow + (c >> 6) * (BM * 128);
-#pragma unroll
-        for (int e = 0; e < 32; e += 8) {
           uint4 o;
-          o.x = pack_bf16x2(pv[e], pv[e + 1]);
-          o.y = pack_bf16x2(pv[e + 2], pv[e + 3]);
-          o.z = pack_bf16x2(pv[e + 4], pv[e + 5]);
-          o.w = pack_bf16x2(pv[e + 6], pv[e + 7]);
-          const int chunk = ((c & 63) + e) >> 3;
-          *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = o;
+          o.x = pack_bf16x2(pv[0], pv[1]);
+          o.y = pack_bf16x2(pv[2], pv[3]);
+          o.z = pack_bf16x2(pv[4], pv[5]);
+          o.w = pack_bf16x2(pv[6], pv[7]);
+          *reinterpret_cast<uint4*>(box + (((e >> 3) ^ (r & 7)) << 4)) = o;
         }
+      };
+      if (full) {
+        half(v0, 0, std::true_type{});
+        half(v1, 64, std::true_type{});
+      } else {
+        half(v0, 0, std::false_type{});
+        half(v1, 64, std::false_type{});
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_empty[sb]));
       fence_proxy_async_smem();   // P stores -> visible to the tensor core's shared-memory reads
       mbar_arrive(smem_u32(&p_full[pb]));
     }
@@ -325,14 +326,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const float inv = sum > 0.f ? 1.f / sum : 0.f;
       // each group writes half of the head dimension
       __nv_bfloat16* orow = p.o + ((long long)i * p.nq + head) * D + grp * (D / 2);
+      constexpr int OW = (D / 2 >= 64) ? 64 : 32;   // columns per TMEM load
 #pragma unroll 1
-      for (int c = 0; c < D / 2; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_addr + COL_O + grp * (D / 2) + c, v);
+      for (int c = 0; c < D / 2; c += OW) {
+        uint32_t v[OW];
+        if constexpr (OW == 64) tmem_ld_32x32_x64(tmem + lane_addr + COL_O + grp * (D / 2) + c, v);
+        else tmem_ld_32x32(tmem + lane_addr + COL_O + grp * (D / 2) + c, v);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 8) {
+          for (int e = 0; e < OW; e += 8) {
             uint4 o;
             o.x = pack_bf16x2(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
             o.y = pack_bf16x2(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
