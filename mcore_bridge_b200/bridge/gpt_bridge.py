@@ -110,6 +110,7 @@ class GPTBridge:
     hf_experts_prefix = 'experts'
     hf_expert_proj_names = ('gate_proj', 'up_proj', 'down_proj')     # per-expert linear names (MiniMax: w1 / w3 / w2)
     hf_fused_gate_up = False                 # dense MLP exported as one ``gate_up_proj`` tensor (GLM-4)
+    hf_fused_experts = False                 # routed experts exported as ``experts.gate_up_proj`` / ``experts.down_proj``
     hf_fused_qkv_key = None                  # e.g. 'query_key_value': one tensor laid out [all q | all k | all v]
     fp8_block_size = 128
 
@@ -589,6 +590,10 @@ class GPTBridge:
             w1, w2 = gather(fc1, 'glu' if glu else 0), gather(fc2, 1)
             if w1 is None:
                 return
+            if self.hf_fused_experts:
+                self._emit(hf_sd, ep_prefix + 'gate_up_proj', w1)
+                self._emit(hf_sd, ep_prefix + 'down_proj', w2)
+                return
             for e in range(E):
                 p = f'{ep_prefix}{e}.'
                 if glu:
@@ -709,6 +714,8 @@ class GPTBridge:
                 return
             for hf_prefix, attr in mapping.items():
                 sub = deep_getattr(tower, attr)
+                if sub is None:               # optional tower the config leaves out (e.g. no audio encoder)
+                    continue
                 state = sub.state_dict(keep_vars=True)
                 for name, t in state.items():
                     key = f'{hf_prefix}.{name}'
@@ -724,6 +731,8 @@ class GPTBridge:
             names = []
             for hf_prefix, attr in mapping.items():
                 sub = deep_getattr(tower, attr)
+                if sub is None:
+                    continue
                 names += [(f'{hf_prefix}.{n}', attr, n) for n in sub.state_dict().keys()]
         if ps.get_world_size('pp') > 1:
             box = [None] * ps.get_world_size('pp')

@@ -210,7 +210,7 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
         res['rotary_interleaved'] = True
         if llm == 'glm4':
             res['post_sublayer_layernorm'] = True
-    elif hf_type in {'gemma4', 'gemma4_unified'}:
+    elif hf_type in {'gemma4', 'gemma4_unified'} or llm == 'gemma4_text':
         res['qk_layernorm'] = True
         res['window_size'] = f'{window - 1},0'
         res['window_attn_skip_freq'] = _window_pattern(layer_types)

@@ -250,6 +250,13 @@ class MoELayer(nn.Module):
         self.apply_probs_on_input = bool(config.moe_apply_probs_on_input)
         self._fused = None
 
+    # -- hooks for families whose router does not look at the expert input itself
+    def _router_input(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def _post_route(self, probs: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        return probs
+
     # -- dispatch over the EP group with torch.distributed (baseline; host-synchronised split sizes)
     def _dispatch_nccl(self, x, probs, idx):
         T, k = idx.shape
@@ -316,7 +323,7 @@ class MoELayer(nn.Module):
                          and not (self.training and cfg.moe_aux_loss_coeff and lb == 'seq_aux_loss')
                          and not cfg.moe_z_loss_coeff)
         if kernel_router:
-            logits = r.gating(x).float()
+            logits = r.gating(self._router_input(x)).float()
             valid = None if padding_mask is None else ~padding_mask.reshape(-1)
             sigmoid = cfg.moe_router_score_function == 'sigmoid'
             renorm = (not cfg.moe_router_pre_softmax) if not sigmoid else r.topk > 1
@@ -342,9 +349,10 @@ class MoELayer(nn.Module):
                 probs = moe_ops.MoEAuxLossAutoScaler.apply(probs, aux)
                 _track('load_balancing_loss', aux / coeff)
         else:
-            probs, idx = r(x, padding_mask, seg_ids, num_seqs)
+            probs, idx = r(self._router_input(x), padding_mask, seg_ids, num_seqs)
             self._fused.publish_routing(st, idx)
             idx = idx.to(torch.int32)
+        probs = self._post_route(probs, idx)
         xp, row_probs = self._fused.dispatch(st, x, probs, idx)
         if self.apply_probs_on_input:
             xp = (xp.float() * row_probs[:, None]).to(xp.dtype)
@@ -362,7 +370,8 @@ class MoELayer(nn.Module):
         from . import moe_fused
         if moe_fused.available(x) and ps.get_world_size('etp') == 1 and H % 8 == 0:
             return self._forward_fused(x, padding_mask, seg_ids, num_seqs)
-        probs, idx = self.router(x, padding_mask, seg_ids, num_seqs)
+        probs, idx = self.router(self._router_input(x), padding_mask, seg_ids, num_seqs)
+        probs = self._post_route(probs, idx)
         etp = ps.get_world_size('etp')
         x_in = x
         if etp > 1:

@@ -42,6 +42,7 @@ def padded_vocab(vocab_size: int, tp: int) -> int:
 class GPTModel(nn.Module):
     # names of extra keyword inputs a multimodal wrapper forwards to the decoder blocks untouched
     extra_forward_keys = []
+    block_cls = TransformerBlock          # families with their own decoder stack replace this
 
     def __init__(self, config, pre_process: bool = True, post_process: bool = True, vp_stage: Optional[int] = None):
         super().__init__()
@@ -58,7 +59,7 @@ class GPTModel(nn.Module):
             self.rotary_pos_emb = RotaryEmbedding(config)
         else:
             self.rotary_pos_emb = None
-        self.decoder = TransformerBlock(config, pre_process, post_process, vp_stage)
+        self.decoder = self.block_cls(config, pre_process, post_process, vp_stage)
         self.mtp = None
         if post_process and config.mtp_num_layers:
             from ..layers.mtp import MultiTokenPredictionBlock
@@ -175,7 +176,7 @@ class GPTModel(nn.Module):
         hidden = None
         if self.pre_process:
             if decoder_input is not None:
-                hidden = decoder_input.reshape(batch * seq, -1)
+                hidden = self.on_decoder_input(decoder_input.reshape(batch * seq, -1), ctx)
                 if sp:
                     hidden = M.scatter_to_sequence_parallel_region(hidden)
             else:
@@ -190,6 +191,15 @@ class GPTModel(nn.Module):
         if taps is not None:
             return result, taps
         return result
+
+    def on_decoder_input(self, hidden_full: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
+        """Hook for embeddings computed by the caller (multimodal wrappers): sees the full token stream ``[T, H]``
+        before the sequence-parallel scatter."""
+        return hidden_full
+
+    def finalize_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        """Hook applied to the (vocab-parallel) logits before they are returned."""
+        return logits
 
     def embed(self, flat_ids: torch.Tensor, ctx: ForwardContext, sp: bool) -> torch.Tensor:
         return self.embedding(flat_ids.clamp(min=0), scatter_to_sequence_parallel=sp)
@@ -232,7 +242,7 @@ class GPTModel(nn.Module):
             return self._reranker(hidden, batch, seq, sp)
         h = self._gather_for_head(hidden, sp)
         if labels is None:
-            logits = linear(h, self._head_weight(), None, LinearSpec())
+            logits = self.finalize_logits(linear(h, self._head_weight(), None, LinearSpec()))
             if runtime_gather_output:
                 logits = M.gather_from_tensor_model_parallel_region(logits, 'tp')
             return logits.view(batch, seq, -1)

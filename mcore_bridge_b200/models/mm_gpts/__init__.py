@@ -1,1 +1,1 @@
-from . import qwen, vision_families  # noqa: F401
+from . import gemma4, qwen, vision_families  # noqa: F401

@@ -76,6 +76,7 @@ def get_transformer_layer_offset(config, vp_stage: Optional[int] = None) -> int:
 
 
 class TransformerBlock(nn.Module):
+    layer_cls = TransformerLayer          # families with their own decoder layer replace this
 
     def __init__(self, config, pre_process: bool = True, post_process: bool = True, vp_stage: Optional[int] = None):
         super().__init__()
@@ -83,7 +84,7 @@ class TransformerBlock(nn.Module):
         self.pre_process, self.post_process, self.vp_stage = pre_process, post_process, vp_stage
         n = get_num_layers_to_build(config, vp_stage)
         self.layer_offset = get_transformer_layer_offset(config, vp_stage)
-        self.layers = nn.ModuleList([TransformerLayer(config, self.layer_offset + i + 1) for i in range(n)])
+        self.layers = nn.ModuleList([self.layer_cls(config, self.layer_offset + i + 1) for i in range(n)])
         self.final_layernorm = Norm(config, config.hidden_size) if post_process else None
         self.input_tensor = None
 
