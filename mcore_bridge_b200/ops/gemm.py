@@ -75,7 +75,7 @@ def mm_nt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
             else:
                 out.copy_(y.view(out.shape))
             return out
-        return y.view(*lead, N)
+        return y if len(lead) == 1 else y.view(*lead, N)
     x2, w2 = _row_major_2d(x), _row_major_2d(w)
     M = x2.shape[0]
     c = _out(out.view(M, N) if out is not None else None, (M, N), out_dtype or torch.bfloat16, x.device, accumulate)
@@ -83,7 +83,9 @@ def mm_nt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
         bias = bias.to(torch.bfloat16).contiguous()
     _launch(x2, K, M, x2.stride(0), False, w2, K, N, w2.stride(0), False, c, c.stride(0), 0, M, N, K, alpha, bias,
             accumulate, max_sms=max_sms, force_bn=force_bn)
-    return c.view(*lead, N) if out is None else out
+    if out is not None:
+        return out
+    return c if len(lead) == 1 else c.view(*lead, N)      # no alias for the common 2-D case: callers may add in place
 
 
 def mm_nn(dy: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -102,14 +104,16 @@ def mm_nn(dy: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
             else:
                 out.copy_(y.view(out.shape))
             return out
-        return y.view(*lead, K)
+        return y if len(lead) == 1 else y.view(*lead, K)
     d2, w2 = _row_major_2d(dy), _row_major_2d(w)
     M = d2.shape[0]
     c = _out(out.view(M, K) if out is not None else None, (M, K), out_dtype or torch.bfloat16, dy.device, accumulate)
     # A = dy (K-major over the contraction N); B[k_out, n] = w[n, k_out] is MN-major as stored
     _launch(d2, N, M, d2.stride(0), False, w2, K, N, w2.stride(0), True, c, c.stride(0), 0, M, K, N, alpha, None,
             accumulate, max_sms=max_sms, force_bn=force_bn)
-    return c.view(*lead, K) if out is None else out
+    if out is not None:
+        return out
+    return c if len(lead) == 1 else c.view(*lead, K)
 
 
 def mm_tn(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None,

@@ -114,7 +114,7 @@ class _LinearFn(torch.autograd.Function):
             return y
         y = _mm_nt(x2, weight, bias, f8)
         ctx.save_for_backward(x2, weight)
-        return y.view(*x.shape[:-1], weight.shape[0])
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, dy):

@@ -32,6 +32,35 @@ from ..parallel import state as ps
 from ..parallel.random import get_rng_tracker
 
 
+class _AccumulateLoraB(torch.autograd.Function):
+    """``result += scaling * h @ B^T`` written by the second adapter GEMM straight into the base layer's output
+    (the GEMM epilogue reads and adds the tile it is about to store), instead of materialising the adapter output
+    and adding it in a separate pass over ``[T, N]``."""
+
+    @staticmethod
+    def forward(ctx, result, h, b, scaling):
+        from ..ops import gemm
+        ctx.save_for_backward(h, b)
+        ctx.scaling = scaling
+        gemm.mm_nt(h, b, out=result, accumulate=True, alpha=scaling)
+        ctx.mark_dirty(result)
+        return result
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..ops import gemm
+        h, b = ctx.saved_tensors
+        g2 = g.reshape(-1, g.shape[-1])
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        dh = db = None
+        if ctx.needs_input_grad[1]:
+            dh = gemm.mm_nn(g2, b, alpha=ctx.scaling).view(*g.shape[:-1], b.shape[1])
+        if ctx.needs_input_grad[2]:
+            db = gemm.mm_tn(g2, h.reshape(-1, h.shape[-1]), alpha=ctx.scaling, out_dtype=b.dtype)
+        return g, dh, db, None
+
+
 def is_expert_layer(layer) -> bool:
     return bool(getattr(layer, 'is_expert', False)) or isinstance(layer, GroupedLinear)
 
@@ -191,23 +220,30 @@ class LoraParallelLinear(nn.Module):
         b.weight.zero_()
 
     # ------------------------------------------------------------------ adapter math
-    def _lora_dense(self, x: torch.Tensor, name: str) -> torch.Tensor:
-        a, b = self.lora_A[name].weight, self.lora_B[name].weight
+    def _lora_dense_a(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        """First adapter GEMM and the collective the base layer's parallel mode calls for; returns ``h [.., r]``."""
+        a = self.lora_A[name].weight
         x = self.lora_dropout[name](x).to(a.dtype)
         tp, sp = self.tp_size, self.sequence_parallel
-        if self.is_parallel_a:
-            h = linear(x, a, None, LinearSpec())                   # partial sums over the input shards
-            if tp > 1:
-                h = M.reduce_scatter_to_sequence_parallel_region(h, self.group) if sp else \
-                    M.reduce_from_tensor_model_parallel_region(h, self.group)
-            return linear(h, b, None, LinearSpec())
         h = linear(x, a, None, LinearSpec())
+        if tp > 1 and self.is_parallel_a:                          # partial sums over the input shards
+            return M.reduce_scatter_to_sequence_parallel_region(h, self.group) if sp else \
+                M.reduce_from_tensor_model_parallel_region(h, self.group)
         if tp > 1:
-            if sp:
-                h = M.gather_from_sequence_parallel_region(h, self.group, tensor_parallel_output_grad=True)
-            else:
-                h = M.copy_to_tensor_model_parallel_region(h, self.group)
-        return linear(h, b, None, LinearSpec())
+            return M.gather_from_sequence_parallel_region(h, self.group, tensor_parallel_output_grad=True) if sp \
+                else M.copy_to_tensor_model_parallel_region(h, self.group)
+        return h
+
+    def _lora_dense(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        return linear(self._lora_dense_a(x, name), self.lora_B[name].weight, None, LinearSpec())
+
+    @staticmethod
+    def _can_accumulate(result: torch.Tensor, h: torch.Tensor, b: torch.Tensor) -> bool:
+        # an alias of another tensor cannot be updated in place under autograd: those cases add out of place
+        return (torch.is_tensor(result) and result._base is None and result.dtype == h.dtype == b.dtype
+                and result.is_contiguous()
+                and result.shape[:-1] == h.shape[:-1] and result.shape[-1] == b.shape[0]
+                and (not result.is_cuda or result.dtype == torch.bfloat16))
 
     def _lora_grouped(self, x: torch.Tensor, offsets: torch.Tensor, name: str) -> torch.Tensor:
         a, b = self.lora_A[name].weight, self.lora_B[name].weight
@@ -247,7 +283,11 @@ class LoraParallelLinear(nn.Module):
             if self.is_grouped:
                 delta = self._lora_grouped(x, args[0] if args else kwargs['offsets'], name)
             else:
-                delta = self._lora_dense(x, name)
+                h, b = self._lora_dense_a(x, name), self.lora_B[name].weight
+                if self._can_accumulate(result, h, b):
+                    result = _AccumulateLoraB.apply(result, h, b, float(self.scaling[name]))
+                    continue
+                delta = linear(h, b, None, LinearSpec())
             result = result + delta * self.scaling[name]
         return result.to(x.dtype) if result.dtype != x.dtype and x.is_floating_point() else result
 
