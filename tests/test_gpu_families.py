@@ -10,11 +10,10 @@ DEV = 'cuda'
 
 def _build(hf_cfg, dtype, device, seed=5, **kw):
     from mcore_bridge_b200 import ModelConfig, hf_to_mcore_config
-    from mcore_bridge_b200.models.gpt_model import GPTModel
     from mcore_bridge_b200.train.trainer import init_weights
     cfg = ModelConfig(**hf_to_mcore_config(hf_cfg), params_dtype=dtype, **kw)
     with torch.device(device):
-        model = GPTModel(cfg)
+        model = cfg.model_meta.loader(cfg).get_model_cls()(cfg)
     init_weights(model, 0.05, seed)
     return cfg, model
 
@@ -75,3 +74,18 @@ def test_glm_dsa_gpu_matches_cpu_reference(monkeypatch):
     for min_t in ('100000', '0'):
         monkeypatch.setenv('MCB200_DSA_GATHER_MIN_T', min_t)
         _compare(c, 256, T=256, tol=8e-2)
+
+
+def test_gemma4_gpu_matches_cpu_reference():
+    """Sliding layers (windowed attention), global layers with their own head size on the tcgen05 attention kernel,
+    shared-KV tail layers, the MoE branch on the grouped GEMMs and the per-layer input path."""
+    from transformers import Gemma4TextConfig
+    c = Gemma4TextConfig(vocab_size=256, hidden_size=128, intermediate_size=256, num_hidden_layers=6,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=64, global_head_dim=128,
+                         num_global_key_value_heads=2, attention_k_eq_v=True,
+                         layer_types=['sliding_attention', 'sliding_attention', 'full_attention'] * 2,
+                         sliding_window=64, num_kv_shared_layers=2, use_double_wide_mlp=True,
+                         hidden_size_per_layer_input=64, vocab_size_per_layer_input=256, enable_moe_block=True,
+                         num_experts=4, top_k_experts=2, moe_intermediate_size=64, final_logit_softcapping=30.0,
+                         max_position_embeddings=512, tie_word_embeddings=True, pad_token_id=0)
+    _compare(c, 256, T=256, tol=8e-2)
