@@ -75,8 +75,16 @@ class ParamAndGradBuffer:
             self.buckets.append(b)
             offset = end
         self.numel = offset
-        self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=device)
-        self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=device)
+        # With 2..8 ranks of one node the two flat buffers live in peer-mapped memory and the reduce-scatter /
+        # all-gather below are in-tree kernels that read the other ranks' buffers over NVLink
+        from ..parallel import dp_comm
+        self.fused = self.dp > 1 and grad_dtype == torch.float32 and dp_comm.usable(group_name, device)
+        if self.fused:
+            self.param_ws, self.param_data = dp_comm.allocate(group_name, self.numel, param_dtype)
+            self.grad_ws, self.grad_data = dp_comm.allocate(group_name, self.numel, grad_dtype)
+        else:
+            self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=device)
+            self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=device)
         self.param_to_bucket: Dict[nn.Parameter, Bucket] = {}
         for b in self.buckets:
             for p in b.params:
@@ -170,7 +178,12 @@ class DistributedDataParallel(nn.Module):
         if g.is_cuda:
             self._comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self._comm_stream):
-                b.work = dist.reduce_scatter_tensor(out, g, group=buf.group, async_op=True)
+                if buf.fused:
+                    from ..parallel import dp_comm
+                    dp_comm.reduce_scatter_(buf.grad_ws, buf.grad_data, b.start, b.end)
+                    b.work = True       # ordered on the side stream; finish_grad_sync joins the streams
+                else:
+                    b.work = dist.reduce_scatter_tensor(out, g, group=buf.group, async_op=True)
         else:
             tmp = g.clone()
             dist.all_reduce(tmp, group=buf.group)
@@ -222,7 +235,13 @@ class DistributedDataParallel(nn.Module):
                 if b.work is None:
                     g = buf.grad_data[b.start:b.end]
                     s, e = buf.shard_range(b)
-                    if g.is_cuda:
+                    if g.is_cuda and buf.fused:
+                        # same side stream as the overlapped buckets: the kernels of one buffer never run concurrently
+                        from ..parallel import dp_comm
+                        self._comm_stream.wait_stream(torch.cuda.current_stream())
+                        with torch.cuda.stream(self._comm_stream):
+                            dp_comm.reduce_scatter_(buf.grad_ws, buf.grad_data, b.start, b.end)
+                    elif g.is_cuda:
                         dist.reduce_scatter_tensor(buf.grad_data[s:e], g, group=buf.group)
                     else:
                         tmp = g.clone()
@@ -355,7 +374,10 @@ class DistributedOptimizer:
             if buf.dp > 1:
                 full = buf.param_data[b.start:b.end]
                 s, e = buf.shard_range(b)
-                if full.is_cuda:
+                if full.is_cuda and buf.fused:
+                    from ..parallel import dp_comm
+                    dp_comm.all_gather_(buf.param_ws, buf.param_data, b.start, b.end)
+                elif full.is_cuda:
                     dist.all_gather_into_tensor(full, buf.param_data[s:e], group=buf.group)
                 else:
                     parts = [torch.empty_like(buf.param_data[s:e]) for _ in range(buf.dp)]

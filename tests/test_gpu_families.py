@@ -18,9 +18,11 @@ def _build(hf_cfg, dtype, device, seed=5, **kw):
     return cfg, model
 
 
-def _compare(hf_cfg, vocab, T=192, tol=6e-2, **kw):
+def _compare(hf_cfg, vocab, T=192, tol=6e-2, prep=None, **kw):
     _, ref = _build(hf_cfg, torch.float32, 'cpu', **kw)
     _, gpu = _build(hf_cfg, torch.bfloat16, 'cuda', **kw)
+    if prep is not None:
+        prep(ref)
     with torch.no_grad():       # identical weights: the bf16 model gets the rounded fp32 values
         for (n1, p1), (n2, p2) in zip(ref.named_parameters(), gpu.named_parameters()):
             assert n1 == n2
@@ -38,16 +40,18 @@ def _compare(hf_cfg, vocab, T=192, tol=6e-2, **kw):
     from mcore_bridge_b200.ops import _lib
     _lib.check_status()
     assert abs(l_ref.item() - l_gpu.item()) < 3e-2, (l_ref.item(), l_gpu.item())
-    worst = 0.0
+    worst, bad = 0.0, []
     for (n, p1), (_, p2) in zip(ref.named_parameters(), gpu.named_parameters()):
         if p1.grad is None or p1.grad.abs().max() == 0:
             continue
         r = ((p2.grad.float().cpu() - p1.grad).norm() / p1.grad.norm()).item()
         worst = max(worst, r)
-        # a router or indexer weight feeds a discrete top-k: one selection that flips under bf16 rounding moves its
-        # gradient by a whole token's contribution, so those only get a sanity bound
-        bound = 0.75 if ('router' in n or 'indexer' in n) else tol * 3
-        assert r < bound, (n, r)
+        # a router or indexer weight (and the scales in front of a router) feeds a discrete top-k: one selection that
+        # flips under bf16 rounding moves its gradient by a whole token's contribution, so those only get a sanity bound
+        discrete = any(k in n for k in ('router', 'indexer', 'experts_mlp.scale', 'per_expert_scale'))
+        if r >= (0.75 if discrete else tol * 3):
+            bad.append((n, round(r, 4)))
+    assert not bad, bad
     return worst
 
 
@@ -88,4 +92,18 @@ def test_gemma4_gpu_matches_cpu_reference():
                          hidden_size_per_layer_input=64, vocab_size_per_layer_input=256, enable_moe_block=True,
                          num_experts=4, top_k_experts=2, moe_intermediate_size=64, final_logit_softcapping=30.0,
                          max_position_embeddings=512, tie_word_embeddings=True, pad_token_id=0)
-    _compare(c, 256, T=256, tol=8e-2)
+
+    def condition(model):
+        with torch.no_grad():
+            for layer in model.decoder.layers:
+                # the router sees a unit-norm vector: with the generic small initialisation all four experts would
+                # score within bf16 rounding of each other and the top-2 choice would be noise
+                layer.experts_mlp.router.weight.mul_(60.0)
+                # softmax scale is 1 and q / k are RMS-normalised: unit norm weights would give logits of the order
+                # of sqrt(d) ~ 8-11, where bf16 rounding of q and k alone moves the probabilities by several percent
+                attn = layer.self_attention
+                attn.q_layernorm.weight.mul_(0.35)
+                if attn.k_layernorm is not None:
+                    attn.k_layernorm.weight.mul_(0.35)
+
+    _compare(c, 256, T=256, tol=8e-2, prep=condition)

@@ -34,6 +34,16 @@ def test_fused_moe_expert_parallel_two_ranks():
     assert 'ALL OK' in res.stdout
 
 
+@pytest.mark.skipif(_ngpu() < 2, reason='needs 2 GPUs')
+def test_peer_memory_dp_collectives_two_ranks():
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0')
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', '2', '--master-addr',
+           '127.0.0.1', '--master-port', '29535', os.path.join(HERE, 'dp_comm_worker.py')]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert 'ALL OK' in res.stdout, res.stdout[-3000:]
+
+
 def test_fused_moe_single_gpu():
     res = subprocess.run([sys.executable, os.path.join(HERE, 'moe_fused_worker.py')], capture_output=True, text=True,
                          timeout=600)
