@@ -138,9 +138,13 @@ class DistributedDataParallel(nn.Module):
     # ------------------------------------------------------------------ hooks
     def _make_accum_hook(self, buf, p):
         def hook(param):
-            if param.grad is not None:
-                param.main_grad.add_(param.grad.to(param.main_grad.dtype))
-                param.grad = None
+            # The accumulate node also runs for a weight whose backward wrote straight into ``main_grad`` and returned
+            # no gradient; that backward has already reported the weight, and a second report would start the bucket's
+            # reduction while later gradients are still missing.
+            if param.grad is None:
+                return
+            param.main_grad.add_(param.grad.to(param.main_grad.dtype))
+            param.grad = None
             param.grad_ready_hook()
         return hook
 

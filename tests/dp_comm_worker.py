@@ -109,13 +109,13 @@ from mcore_bridge_b200.train.data import SyntheticPackedDataset
 from mcore_bridge_b200.train.presets import model_config
 from mcore_bridge_b200.train.trainer import TrainConfig, Trainer
 
-def run_steps(flag: str):
+def run_steps(flag: str, overlap: bool = True):
     """Two optimizer steps; returns the losses, the flat parameters after each step and whether the peer-memory
     buffers were in use."""
     os.environ['MCB200_FUSED_DP'] = flag
     torch.manual_seed(0)
     cfg = model_config('qwen3_tiny', bf16=True)
-    trainer = Trainer(cfg, TrainConfig(lr=1e-3))
+    trainer = Trainer(cfg, TrainConfig(lr=1e-3, overlap_grad_reduce=overlap))
     used = any(buf.fused for m in trainer.ddp for buf in m.buffers.values())
     ds = SyntheticPackedDataset(cfg.padded_vocab_size, 1024, seg_lo=128, seg_hi=512, seed=11 + rank)
     losses, flats = [], []
@@ -124,15 +124,14 @@ def run_steps(flag: str):
         flats.append(torch.cat([p.detach().float().reshape(-1) for m in trainer.models for p in m.parameters()]))
     torch.cuda.synchronize()
     _lib.check_status()
-    return losses, flats, used
+    names = [(n, p.numel()) for m in trainer.models for n, p in m.named_parameters()]
+    return losses, flats, used, names
 
 
 # The library path twice gives the run-to-run noise of the step itself (atomics in a few gradient kernels plus Adam's
 # first steps, which turn a rounding-level difference of a near-zero gradient into a full +-lr update); the
 # peer-memory path has to stay within it.
 fused, lib_a, lib_b = run_steps('1'), run_steps('0'), run_steps('0')
-
-
 def dist_of(x, y):
     return [(p - q).abs().max().item() for p, q in zip(x[1], y[1])], [abs(p - q) for p, q in zip(x[0], y[0])]
 
