@@ -2,12 +2,13 @@
 result of reducing after backward, and every parameter must report its gradient exactly once per backward pass (a
 weight whose backward writes straight into ``main_grad`` is also visited by autograd's accumulate node, which must
 not report it a second time: the bucket would be reduced before the gradients produced later exist)."""
+import pytest
 import torch
 
 from dist_utils import run_ranks
 
 
-def _worker(rank, world):
+def _worker(rank, world, tied):
     from mcore_bridge_b200.parallel import state as ps
     from mcore_bridge_b200.train.data import SyntheticPackedDataset
     from mcore_bridge_b200.train.presets import model_config
@@ -16,7 +17,7 @@ def _worker(rank, world):
     out = {}
     for overlap in (True, False):
         torch.manual_seed(0)
-        cfg = model_config('qwen3_tiny')
+        cfg = model_config('qwen3_tiny', untie_embeddings_and_output_weights=not tied)
         tr = Trainer(cfg, TrainConfig(lr=1e-3, overlap_grad_reduce=overlap))
         calls = {}
         for m in tr.ddp:
@@ -37,8 +38,9 @@ def _worker(rank, world):
     return out[True][0], out[False][0], torch.equal(out[True][1], out[False][1]), out[True][2], out[True][1]
 
 
-def test_overlapped_reduction_equals_reduction_after_backward():
-    res = run_ranks(_worker, 2)
+@pytest.mark.parametrize('tied', [False, True])
+def test_overlapped_reduction_equals_reduction_after_backward(tied):
+    res = run_ranks(_worker, 2, tied)
     for loss_a, loss_b, same, wrong, _ in res:
         assert not wrong, f'parameters reporting a wrong number of times (got, expected): {wrong}'
         assert loss_a == loss_b
