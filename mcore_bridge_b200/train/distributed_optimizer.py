@@ -49,6 +49,10 @@ class ParamAndGradBuffer:
         self.dp = ps.get_world_size(group_name)
         self.dp_rank = ps.get_rank_in(group_name) if self.dp > 1 else 0
         self.group = ps.get_group(group_name) if self.dp > 1 else None
+        # Number of ranks whose losses are averaged into one step.  An expert's gradient already sums the tokens that
+        # the ranks of its expert-parallel group sent to it, and is then summed over the expert data-parallel group, so
+        # its divisor is the dense data-parallel size as well, not the size of the group it is reduced over.
+        self.grad_divisor = max(1, ps.get_world_size('dp_cp'))
         self.params = params
         unit = ALIGN * self.dp
         bucket_elems = max(unit, bucket_bytes // 4 // unit * unit)
@@ -299,7 +303,21 @@ class DistributedOptimizer:
         """Global L2 norm over every distinct gradient element (dp-sharded, tp-sharded, pp-sharded)."""
         self._sq.zero_()
         tp_rank0 = ps.get_rank_in('tp') == 0 if ps.get_world_size('tp') > 1 else True
+        # A shard holds the *sum* of the data-parallel ranks' gradients; the averaging (and any loss scale) is folded
+        # into the optimizer kernel's gradient scale.  The norm is that of the gradient the update uses, so every
+        # buffer's sum of squares is scaled accordingly (buffers can have different data-parallel sizes: dense vs expert).
+        part = torch.zeros_like(self._sq)
+        cur = None
+
+        def flush():
+            if cur is not None:
+                self._sq.add_(part * (self.grad_scale / cur.grad_divisor) ** 2)
+                part.zero_()
+
         for buf, b, decay, main, m, v in self.shards:
+            if buf is not cur:
+                flush()
+                cur = buf
             s, e = buf.shard_range(b)
             g = buf.grad_data[s:e]
             # replicated (non tensor-parallel) parameters are counted once per TP group
@@ -308,10 +326,11 @@ class DistributedOptimizer:
                 if dup is not None:
                     g = g * dup
             if self._use_cuda() and g.dtype == torch.float32:
-                _lib.check_rc(_lib.lib().mcb_sqnorm_accum(_lib.ptr(g), _ll(g.numel()), _lib.ptr(self._sq),
+                _lib.check_rc(_lib.lib().mcb_sqnorm_accum(_lib.ptr(g), _ll(g.numel()), _lib.ptr(part),
                                                           _lib.stream_ptr()), 'mcb_sqnorm_accum')
             else:
-                self._sq += g.float().pow(2).sum()
+                part += g.float().pow(2).sum()
+        flush()
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(self._sq)  # shards are disjoint across all ranks except the masked replicas
         if self._use_cuda():
@@ -355,10 +374,10 @@ class DistributedOptimizer:
             s, e = buf.shard_range(b)
             g = buf.grad_data[s:e]
             pshard = buf.param_data[s:e]
-            scale_dp = 1.0 / buf.dp
+            scale_dp = 1.0 / buf.grad_divisor
             if self._use_cuda() and g.dtype == torch.float32 and pshard.dtype in (torch.bfloat16, torch.float32):
                 sc = self._scalars[decay]
-                if buf.dp > 1:
+                if scale_dp != 1.0:
                     sc = sc.clone()
                     sc[7] *= scale_dp
                 rc = _lib.lib().mcb_adam_step(_lib.ptr(g), _lib.ptr(main), _lib.ptr(m), _lib.ptr(v), _lib.ptr(pshard),
