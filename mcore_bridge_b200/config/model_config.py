@@ -342,6 +342,11 @@ class ModelConfig:
             raise ValueError(f'num_attention_heads ({self.num_attention_heads}) must be divisible by TP ({tp})')
         if self.num_moe_experts is not None and self.num_moe_experts % self.expert_model_parallel_size != 0:
             raise ValueError('num_moe_experts must be divisible by expert_model_parallel_size')
+        if self.num_moe_experts and self.expert_model_parallel_size > 1 and self.tensor_model_parallel_size > 1 \
+                and not self.sequence_parallel:
+            # without sequence parallelism every tensor-parallel rank holds all tokens and would send each of them to
+            # the experts once more: outputs would still be right, expert gradients would count every token tp times
+            raise ValueError('expert parallelism together with tensor parallelism requires sequence_parallel=True')
 
     # pattern accessors (1-based semantics as in the reference's pattern language)
     def moe_layer_pattern(self) -> List[int]:

@@ -36,6 +36,17 @@ def get_moe_aux_losses() -> dict:
     return _AUX_TRACKER
 
 
+def _micro_batch_tokens(cfg, ntok_local, ntok_group, group: str):
+    """Tokens of the micro-batch this rank holds a slice of.  Under sequence / context parallelism every rank of the
+    ``tp_cp`` group sees part of the same micro-batch, and the load-balancing term is linear in the mean probability
+    ``P_e``: each rank contributes ``sum of its scores / tokens of the whole micro-batch``, so that the ranks' terms add
+    up to the loss of the micro-batch (and each rank's gradient is exactly its share of it)."""
+    if group == 'tp_cp':
+        return ntok_group
+    parts = ps.get_world_size('tp_cp') if (cfg.sequence_parallel or cfg.context_parallel_size > 1) else 1
+    return ntok_local * parts
+
+
 def _track(name: str, value: torch.Tensor):
     s, c = _AUX_TRACKER.get(name, (0.0, 0))
     _AUX_TRACKER[name] = (s + value.detach().float(), c + 1)
@@ -115,7 +126,8 @@ class TopKRouter(nn.Module):
                     dist.all_reduce(packed, group=ps.get_group(group))
                     n = ps.get_world_size(group)
                     counts, ntok_all = packed[:-1], packed[-1]
-                    aux = coeff * self.num_experts * ((counts / (ntok_all * self.topk)) * (sc.sum(0) / ntok)).sum()
+                    aux = coeff * self.num_experts * ((counts / (ntok_all * self.topk)) *
+                                                      (sc.sum(0) / _micro_batch_tokens(cfg, ntok, ntok_all, group))).sum()
                 else:
                     aux = moe_ops.aux_loss(sc, counts, self.topk, coeff, ntok)
             probs = moe_ops.MoEAuxLossAutoScaler.apply(probs, aux)
@@ -345,7 +357,9 @@ class MoELayer(nn.Module):
                     packed = torch.cat([cnt, ntok.view(1)])
                     dist.all_reduce(packed, group=ps.get_group(group))
                     cnt, ntok_all = packed[:-1], packed[-1]
-                aux = coeff * self.num_experts * ((cnt / (ntok_all * r.topk)) * (score_sum / ntok)).sum()
+                ntok_p = _micro_batch_tokens(cfg, ntok, ntok_all, group) if group is not None and \
+                    ps.get_world_size(group) > 1 else ntok
+                aux = coeff * self.num_experts * ((cnt / (ntok_all * r.topk)) * (score_sum / ntok_p)).sum()
                 probs = moe_ops.MoEAuxLossAutoScaler.apply(probs, aux)
                 _track('load_balancing_loss', aux / coeff)
         else:

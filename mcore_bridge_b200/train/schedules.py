@@ -94,7 +94,8 @@ def _forward(trainer, model, d: Dict, input_tensor: Optional[torch.Tensor], n_mi
         if ps.get_world_size('cp') > 1:
             ntok = ntok.clone()
             dist.all_reduce(ntok, group=ps.get_group('cp'))
-        out = (out * mask).sum() / ntok.clamp(min=1.0) / n_micro
+        # a context-parallel rank's share of the micro-batch loss, scaled by cp (see Trainer.forward_backward_microbatch)
+        out = (out * mask).sum() / ntok.clamp(min=1.0) * (float(ps.get_world_size('cp')) / n_micro)
     return out
 
 
@@ -118,7 +119,7 @@ def forward_backward_pipelining(trainer, microbatches: List[Dict]) -> torch.Tens
     trainer.optimizer.zero_grad()
     from ..layers.mtp import MTPLossAutoScaler
     from ..ops.moe import MoEAuxLossAutoScaler
-    MoEAuxLossAutoScaler.set_loss_scale(1.0 / n)
+    MoEAuxLossAutoScaler.set_loss_scale(float(ps.get_world_size('cp')) / n)
     MTPLossAutoScaler.set_loss_scale(1.0 / n)
     total = torch.zeros((), dtype=torch.float32, device=dev)
     data = [trainer._prepare(mb) for mb in microbatches]

@@ -139,8 +139,12 @@ class Trainer:
         if cpn > 1:
             ntok = ntok.clone()
             dist.all_reduce(ntok, group=ps.get_group('cp'))
-        loss = (loss_tok * mask).sum() / ntok.clamp(min=1.0) / num_microbatches
-        MoEAuxLossAutoScaler.set_loss_scale(1.0 / num_microbatches)
+        # Under context parallelism every rank holds part of each sequence and the sum above is normalised by the
+        # micro-batch's token count, i.e. it is this rank's *share* of the micro-batch loss.  Gradients are averaged
+        # over the dp x cp group, so the share is scaled by cp: the average over the cp ranks is then the micro-batch
+        # gradient.  The load-balancing loss is a share in the same sense; the MTP loss is a local mean and is not.
+        loss = (loss_tok * mask).sum() / ntok.clamp(min=1.0) * (float(cpn) / num_microbatches)
+        MoEAuxLossAutoScaler.set_loss_scale(float(cpn) / num_microbatches)
         from ..layers.mtp import MTPLossAutoScaler
         MTPLossAutoScaler.set_loss_scale(1.0 / num_microbatches)
         loss.backward()
@@ -167,10 +171,10 @@ class Trainer:
                 total += self.forward_backward_microbatch(cur, n)
         grad_norm = self.optimizer.step()
         self._after_step()
-        # loss summed over CP happens inside; average over data-parallel ranks for reporting
-        if ps.get_world_size('dp') > 1:
-            dist.all_reduce(total, group=ps.get_group('dp'))
-            total = total / ps.get_world_size('dp')
+        # every rank holds cp x its share of its micro-batches' loss: the mean over the dp x cp group is the step's loss
+        if ps.get_world_size('dp_cp') > 1:
+            dist.all_reduce(total, group=ps.get_group('dp_cp'))
+            total = total / ps.get_world_size('dp_cp')
         out = torch.stack([total.float(), grad_norm.float().reshape(())])
         host = out.cpu()                       # the step's device->host read
         self.d2h_bytes += out.numel() * out.element_size()
