@@ -113,7 +113,9 @@ class TopKRouter(nn.Module):
         if self.training and coeff and lb in ('aux_loss', 'global_aux_loss', 'seq_aux_loss'):
             valid = None if padding_mask is None else ~padding_mask.reshape(-1)
             if lb == 'seq_aux_loss' and seg_ids is not None:
-                aux = moe_ops.seq_aux_loss(scores, idx, seg_ids, num_seqs, self.topk, coeff)
+                split = (cfg.sequence_parallel or cfg.context_parallel_size > 1) and ps.get_world_size('tp_cp') > 1
+                aux = moe_ops.seq_aux_loss(scores, idx, seg_ids, num_seqs, self.topk, coeff,
+                                           ps.get_group('tp_cp') if split else None)
             else:
                 sc = scores if valid is None else scores * valid[:, None]
                 counts = moe_ops.tokens_per_expert(idx, self.num_experts, valid)

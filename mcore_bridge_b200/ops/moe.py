@@ -83,15 +83,24 @@ def aux_loss(scores: torch.Tensor, counts: torch.Tensor, topk: int, coeff: float
 
 
 def seq_aux_loss(scores: torch.Tensor, indices: torch.Tensor, seg_ids: torch.Tensor, num_seqs: int, topk: int,
-                 coeff: float) -> torch.Tensor:
+                 coeff: float, group=None) -> torch.Tensor:
     """Per-sequence load-balancing loss (DeepSeek): the loss above computed inside each packed sequence,
-    averaged over sequences.  Scores are normalised over experts first."""
+    averaged over sequences.  Scores are normalised over experts first.
+
+    ``group``: process group whose ranks each hold part of every sequence (sequence / context parallelism).  The
+    selection counts and sequence lengths are then summed over it and this rank's term uses its own share of the
+    mean probability, so the ranks' values add up to the loss of the whole sequences."""
     T, E = scores.shape
     sn = scores / (scores.sum(-1, keepdim=True) + 1e-20)
     onehot = torch.zeros(T, E, device=scores.device, dtype=torch.float32).scatter_add_(
         1, indices, torch.ones_like(indices, dtype=torch.float32))
-    lens = torch.bincount(seg_ids, minlength=num_seqs).clamp(min=1).float()
+    lens = torch.bincount(seg_ids, minlength=num_seqs).float()
     cnt = torch.zeros(num_seqs, E, device=scores.device).index_add_(0, seg_ids, onehot)
+    if group is not None:
+        packed = torch.cat([cnt, lens[:, None]], dim=1)
+        torch.distributed.all_reduce(packed, group=group)
+        cnt, lens = packed[:, :E], packed[:, E]
+    lens = lens.clamp(min=1)
     sm = torch.zeros(num_seqs, E, device=scores.device).index_add_(0, seg_ids, sn)
     f = cnt * E / (topk * lens[:, None])
     p = sm / lens[:, None]

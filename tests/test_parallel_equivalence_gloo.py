@@ -10,17 +10,18 @@ from dist_utils import run_ranks
 STEPS, GLOBAL_MB = 2, 4
 
 
-def _worker(rank, world, name, ckpt, tp, ep, aux, pp=1, cp=1):
+def _worker(rank, world, name, ckpt, tp, ep, aux, pp=1, cp=1, etp=1, hf_over=None, over=None):
     from mcore_bridge_b200.parallel import state as ps
     from mcore_bridge_b200.train.data import SyntheticPackedDataset
     from mcore_bridge_b200.train.presets import model_config
     from mcore_bridge_b200.train.trainer import TrainConfig, Trainer
     ps.initialize_model_parallel(tensor_model_parallel_size=tp, expert_model_parallel_size=ep,
-                                 expert_tensor_parallel_size=1, pipeline_model_parallel_size=pp,
+                                 expert_tensor_parallel_size=etp, pipeline_model_parallel_size=pp,
                                  context_parallel_size=cp)
     extra = dict(moe_aux_loss_coeff=aux) if aux else {}
-    cfg = model_config(name, params_dtype=torch.float32, tensor_model_parallel_size=tp,
-                       expert_model_parallel_size=ep, expert_tensor_parallel_size=1,
+    extra.update(over or {})
+    cfg = model_config(name, hf_over, params_dtype=torch.float32, tensor_model_parallel_size=tp,
+                       expert_model_parallel_size=ep, expert_tensor_parallel_size=etp,
                        pipeline_model_parallel_size=pp, context_parallel_size=cp,
                        sequence_parallel=tp > 1, **extra)
     tr = Trainer(cfg, TrainConfig(lr=1e-3, init_seed=None, clip_grad=1.0))
@@ -39,17 +40,17 @@ def _worker(rank, world, name, ckpt, tp, ep, aux, pp=1, cp=1):
     return losses, weights, ps.is_pipeline_last_stage()
 
 
-def _check(tmp_path, name, hf_cls, tp, ep, aux=0.0, pp=1, cp=1):
+def _check(tmp_path, name, hf_cls, tp, ep, aux=0.0, pp=1, cp=1, etp=1, hf_over=None, over=None):
     from mcore_bridge_b200.train.presets import hf_config
     torch.manual_seed(0)
-    hf = hf_cls(hf_config(name)).float()
+    hf = hf_cls(hf_config(name, **(hf_over or {}))).float()
     with torch.no_grad():
         for p in hf.parameters():
             p.normal_(0, 0.05) if p.dim() >= 2 else p.normal_(1.0, 0.05)
     d = str(tmp_path / 'ckpt')
     hf.save_pretrained(d)
-    base_losses, base_w, _ = run_ranks(_worker, 1, name, d, 1, 1, aux)[0]
-    res = run_ranks(_worker, 4, name, d, tp, ep, aux, pp, cp)
+    base_losses, base_w, _ = run_ranks(_worker, 1, name, d, 1, 1, aux, 1, 1, 1, hf_over, over)[0]
+    res = run_ranks(_worker, 4, name, d, tp, ep, aux, pp, cp, etp, hf_over, over)
     for losses, weights, last_stage in res:
         if last_stage:                      # only the last pipeline stage sees the loss
             for a, b in zip(losses, base_losses):
@@ -83,3 +84,29 @@ def test_dense_cp2_dp2_matches_single_process(tmp_path):
 def test_moe_tp2_ep2_matches_single_process(tmp_path):
     from transformers import Qwen3MoeForCausalLM
     _check(tmp_path, 'qwen3_moe_tiny', Qwen3MoeForCausalLM, tp=2, ep=2, aux=1e-2)
+
+
+def test_dense_tp2_pp2_matches_single_process(tmp_path):
+    from transformers import Qwen3ForCausalLM
+    _check(tmp_path, 'qwen3_tiny', Qwen3ForCausalLM, tp=2, ep=1, pp=2)
+
+
+def test_dense_tied_embeddings_tp2_dp2_matches_single_process(tmp_path):
+    from transformers import Qwen3ForCausalLM
+    _check(tmp_path, 'qwen3_tiny', Qwen3ForCausalLM, tp=2, ep=1, hf_over={'tie_word_embeddings': True})
+
+
+def test_moe_expert_tensor_parallel_dp2_matches_single_process(tmp_path):
+    from transformers import Qwen3MoeForCausalLM
+    _check(tmp_path, 'qwen3_moe_tiny', Qwen3MoeForCausalLM, tp=2, ep=1, etp=2, aux=1e-2)
+
+
+def test_moe_ep2_pp2_matches_single_process(tmp_path):
+    from transformers import Qwen3MoeForCausalLM
+    _check(tmp_path, 'qwen3_moe_tiny', Qwen3MoeForCausalLM, tp=1, ep=2, pp=2, aux=1e-2)
+
+
+def test_moe_seq_aux_loss_tp2_ep2_matches_single_process(tmp_path):
+    from transformers import Qwen3MoeForCausalLM
+    _check(tmp_path, 'qwen3_moe_tiny', Qwen3MoeForCausalLM, tp=2, ep=2, aux=1e-2,
+           over={'moe_router_load_balancing_type': 'seq_aux_loss'})
