@@ -23,18 +23,15 @@ device of the parameters.
 """
 from __future__ import annotations
 
-import math
-import os
 import re
-from contextlib import contextmanager
-from typing import Any, Callable, Dict, Iterable, List, Optional, Tuple
+from typing import Any, Callable, Dict, Iterable, List, Optional
 
 import torch
 import torch.distributed as dist
 from torch import nn
 
 from ..parallel import state as ps
-from ..utils.dequantizer import Fp8Dequantizer, MxFp4Dequantizer, quantize_fp8_blockwise
+from ..utils.dequantizer import Fp8Dequantizer
 from ..utils.env import is_master
 from ..utils.logger import get_logger
 from ..utils.safetensors import LazyTensor, SafetensorLazyLoader, StreamingSafetensorSaver

@@ -24,7 +24,7 @@ from torch import nn
 from ..parallel import state as ps
 from ..utils.safetensors import LazyTensor
 from ..utils.utils import deep_getattr
-from .gpt_bridge import qkv_to_hf, qkv_to_mcore, shard, unshard
+from .gpt_bridge import qkv_to_hf, qkv_to_mcore, shard
 
 PREFIX = 'base_model.model.'
 

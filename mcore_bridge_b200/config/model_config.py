@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import copy
 import re
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable, List, Literal, Optional, Tuple, Union
 
 import torch

@@ -7,7 +7,7 @@ recurses into nested text configs, then a list of small family rules applied in 
 from __future__ import annotations
 
 from functools import partial
-from typing import Any, Callable, Dict, List, Tuple
+from typing import Any, Dict, Tuple
 
 import torch.nn.functional as F
 

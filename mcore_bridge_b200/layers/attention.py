@@ -8,7 +8,6 @@ Parameter names: ``linear_qkv.{weight,bias,layer_norm_weight}``, ``q_layernorm.w
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

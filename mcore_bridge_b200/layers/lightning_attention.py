@@ -15,7 +15,6 @@ from torch import nn
 
 from ..ops import gdn as G
 from ..ops.rope import qkv_split_norm_rope
-from ..parallel import mappings as M
 from ..parallel import state as ps
 from .context import ForwardContext
 from .linear import ColumnParallelLinear, RowParallelLinear, _set_tp_attrs

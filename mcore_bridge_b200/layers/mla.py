@@ -18,12 +18,11 @@ quantisation of the indexer operands and is applied there.
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 from torch import nn
 
-from ..ops.attention import attention, attention_ref, segment_ids
+from ..ops.attention import attention, segment_ids
 from ..ops.norm import layernorm_ref
 from ..ops.rope import apply_rope_ref
 from ..parallel import mappings as M

@@ -22,7 +22,7 @@ from torch import nn
 from ..ops import gemm
 from ..ops import moe as moe_ops
 from ..ops.activation import glu
-from ..ops.linear import LinearSpec, linear
+from ..ops.linear import linear
 from ..parallel import mappings as M
 from ..parallel import state as ps
 from .linear import ColumnParallelLinear, RowParallelLinear, _set_tp_attrs

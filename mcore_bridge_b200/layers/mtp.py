@@ -11,7 +11,7 @@ gradient into the embedding.
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 from torch import nn

@@ -15,7 +15,7 @@ Task heads: ``causal_lm`` (vocab-parallel head, fused linear + cross-entropy), `
 from __future__ import annotations
 
 import os
-from typing import Any, Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 from torch import nn

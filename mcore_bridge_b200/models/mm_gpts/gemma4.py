@@ -26,7 +26,7 @@ from typing import Optional
 import torch
 from torch import nn
 
-from ...bridge.gpt_bridge import GPTBridge, MultimodalGPTBridge
+from ...bridge.gpt_bridge import MultimodalGPTBridge
 from ...layers.context import ForwardContext
 from ...layers.embedding import VocabParallelEmbedding
 from ...layers.linear import ColumnParallelLinear, LayerNormColumnParallelLinear, RowParallelLinear

@@ -8,7 +8,7 @@ pipeline rank owns — one per virtual stage under interleaved pipelining, with 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import TYPE_CHECKING, Dict, List, Optional, Type
+from typing import Dict, List, Optional, Type
 
 import torch
 from torch import nn

@@ -11,7 +11,7 @@ attention scaling folded in), including MRoPE (3-axis positions, sectioned or in
 from __future__ import annotations
 
 import math
-from typing import List, Optional, Tuple
+from typing import Optional, Tuple
 
 import torch
 

@@ -14,7 +14,6 @@ linear where that linear is column-parallel (``linear_qkv.layer_norm_weight``,
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 from torch import nn

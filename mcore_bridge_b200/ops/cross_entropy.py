@@ -13,7 +13,6 @@ Both return the per-token loss ``[T]`` in fp32 (the caller masks and averages).
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -7,7 +7,6 @@ zero-centred definition the reference spells out in ``src/mcore_bridge/model/gpt
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
 
 import torch
 

@@ -15,8 +15,7 @@ Protocol state kept here:
 """
 from __future__ import annotations
 
-import ctypes
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 import torch

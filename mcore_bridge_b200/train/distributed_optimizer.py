@@ -16,8 +16,7 @@ fused kernel on the whole buffer.
 from __future__ import annotations
 
 import ctypes
-import math
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Dict, Iterable, List, Tuple
 
 import torch
 import torch.distributed as dist

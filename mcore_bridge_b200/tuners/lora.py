@@ -23,8 +23,7 @@ from typing import Any, Dict, List, Optional
 import torch
 from torch import nn
 
-from ..layers.linear import (ColumnParallelLinear, LayerNormColumnParallelLinear, ReplicatedLinear, RowParallelLinear,
-                             _set_tp_attrs)
+from ..layers.linear import LayerNormColumnParallelLinear, RowParallelLinear, _set_tp_attrs
 from ..layers.moe import GroupedLinear, TopKRouter, _GroupedLinearFn
 from ..ops.linear import LinearSpec, linear
 from ..parallel import mappings as M

@@ -12,10 +12,9 @@ import copy
 import json
 import os
 import re
-from dataclasses import asdict, dataclass, field
-from typing import Dict, List, Optional, Union
+from dataclasses import asdict, dataclass
+from typing import List, Optional, Union
 
-import torch
 from torch import nn
 
 from ..layers.linear import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear

@@ -3,7 +3,6 @@ from __future__ import annotations
 
 from typing import Dict
 
-import torch
 from torch import nn
 
 

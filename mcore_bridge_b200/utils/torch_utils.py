@@ -5,7 +5,6 @@ import gc
 import hashlib
 import os
 import time
-import uuid
 from contextlib import contextmanager
 from typing import Any, Mapping, Optional, Union
 

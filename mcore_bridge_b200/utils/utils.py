@@ -1,11 +1,10 @@
 """Small generic helpers (parity: reference ``src/mcore_bridge/utils/utils.py:15-106``)."""
 from __future__ import annotations
 
-import copy
 import json
 import os
 from contextlib import contextmanager
-from typing import Any, Callable, Dict, Optional, TypeVar, Union
+from typing import Callable, Dict, Optional, TypeVar, Union
 
 _T = TypeVar('_T')
 
