@@ -15,8 +15,8 @@ What differs from the generic decoder, all of it read from the Hugging Face text
 * word embeddings scaled by ``sqrt(hidden)``, logits soft-capped with ``tanh``.
 
 Parity: reference ``src/mcore_bridge/model/mm_gpts/gemma4.py`` (attention 139-361, MLP / MoE 364-418, bridge
-421-509, model 512-711, layer 714-819, tower 58-136).  Limits: pipeline parallelism is refused when per-layer inputs or
-KV sharing are configured (both would have to travel between stages); global
+421-509, model 512-711, layer 714-819, tower 58-136).  Under pipeline parallelism the per-layer inputs and the shared
+keys / values are packed behind the hidden states sent to the next stage (reference 656-703).  Limits: global
 layers with a head size above 256 use the masked-softmax attention path.
 """
 from __future__ import annotations
@@ -254,12 +254,7 @@ class Gemma4Layer(nn.Module):
                 self.experts_mlp(residual, ctx.padding_mask, ctx.seg_ids, ctx.num_seqs))
         hidden = residual + self.post_feedforward_layernorm(out)
         if self.per_layer_dim:
-            pli = ctx.extra[PER_LAYER][:, self.layer_number - 1]           # [T, P]
-            tp = ps.get_world_size('tp')
-            if tp > 1:
-                w = self.per_layer_dim // tp
-                r = ps.get_rank_in('tp')
-                pli = pli[:, r * w:(r + 1) * w]
+            pli = ctx.extra[PER_LAYER][:, self.layer_number - 1]           # [T, P / tp]: this rank's columns
             g = self._activation(self.per_layer_input_gate(hidden)) * pli.to(hidden.dtype)
             hidden = hidden + self.post_per_layer_input_norm(self.per_layer_projection(g))
         return hidden * self.layer_scalar.to(hidden.dtype)
@@ -276,15 +271,13 @@ class Gemma4TextModel(GPTModel):
     def __init__(self, config, pre_process: bool = True, post_process: bool = True, vp_stage: Optional[int] = None):
         tc = text_config_of(config)
         self.per_layer_dim = int(getattr(tc, 'hidden_size_per_layer_input', 0) or 0)
-        shared = int(getattr(tc, 'num_kv_shared_layers', 0) or 0)
-        if ps.get_pipeline_model_parallel_world_size() > 1 and (self.per_layer_dim or shared):
-            raise NotImplementedError('Gemma-4 with per-layer inputs or shared KV layers does not run under pipeline '
-                                      'parallelism: both would have to be sent along with the hidden states')
+        self.kv_shared_layers = int(getattr(tc, 'num_kv_shared_layers', 0) or 0)
         if getattr(tc, 'use_bidirectional_attention', None) == 'vision':
             # image tokens would attend to each other in both directions; the attention kernels here are causal
             logger.warning('use_bidirectional_attention="vision" is not supported: image tokens attend causally')
         super().__init__(config, pre_process, post_process, vp_stage)
         self.rotary_pos_emb = None
+        self._received, self._ctx = None, None
         self.ropes = nn.ModuleDict({lt: Gemma4Rope(tc, lt) for lt in sorted(set(tc.layer_types))})
         self.embed_scale = float(config.hidden_size) ** 0.5
         self.final_logit_softcapping = getattr(tc, 'final_logit_softcapping', None)
@@ -295,14 +288,95 @@ class Gemma4TextModel(GPTModel):
             self.embed_tokens_per_layer = VocabParallelEmbedding(rows, total, config)
             self.per_layer_model_projection = ColumnParallelLinear(config.hidden_size, total, config, bias=False,
                                                                    gather_output=True, sequence_parallel=False)
-            self.per_layer_projection_norm = Norm(config, self.per_layer_dim)
+            # applied to values that are replicated over the tensor-parallel ranks and receives the full gradient on
+            # each of them (see _per_layer_inputs): its weight gradient must not be summed over the group
+            self.per_layer_projection_norm = Norm(config, self.per_layer_dim, sequence_parallel_grad=False)
 
     def build_context(self, input_ids, position_ids, attention_mask, packed_seq_params, batch, seq, device):
         ctx = super().build_context(input_ids, position_ids, attention_mask, packed_seq_params, batch, seq, device)
         pos = ctx.position_ids
         for lt, rope in self.ropes.items():
             ctx.rope_tables[lt] = rope(pos.to(device))
+        if self._received is not None:          # what the previous pipeline stage sent along with the hidden states
+            ctx.extra.update(self._received)
+            self._received = None
+        self._ctx = ctx
         return ctx
+
+    # ---- pipeline parallelism: per-layer inputs and shared keys / values travel behind the hidden states
+    def _kv_slots(self):
+        """(layer type, local kv heads, head dim) of every layer type whose keys / values later layers reuse."""
+        if not self.kv_shared_layers:
+            return []
+        tc, tp = text_config_of(self.config), ps.get_world_size('tp')
+        slots = {}
+        for lt, d, ng, _, _, stores in layer_kinds(tc, self.config.num_layers):
+            if stores:
+                slots[lt] = (lt, max(1, ng // tp), d)
+        return [slots[k] for k in sorted(slots)]
+
+    def _extra_columns(self) -> int:
+        """Columns per *token* that ride along (this rank's share under tensor parallelism)."""
+        tp = ps.get_world_size('tp')
+        cols = self.config.num_layers * (self.per_layer_dim // tp) if self.per_layer_dim else 0
+        return cols + sum(2 * h * d for _, h, d in self._kv_slots())
+
+    def pipeline_width(self) -> int:
+        """Width of the tensor exchanged between stages.  Its rows are this rank's hidden-state rows (a 1/tp slice
+        of the tokens under sequence parallelism) while the extras cover all tokens, so they take tp times their
+        per-token width."""
+        return self.config.hidden_size + self._extra_columns() * self._tokens_per_row()
+
+    def _tokens_per_row(self) -> int:
+        sp = self.config.sequence_parallel and ps.get_world_size('tp') > 1
+        return ps.get_world_size('tp') if sp else 1
+
+    def _pack(self, hidden: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
+        rows = hidden.shape[0]
+        parts = [hidden]
+        if self.per_layer_dim:
+            parts.append(ctx.extra[PER_LAYER].reshape(rows, -1).to(hidden.dtype))
+        shared = ctx.extra.get(SHARED_KV, {})
+        for lt, h, d in self._kv_slots():
+            if lt in shared:
+                k, v = shared[lt]
+                parts += [k.reshape(rows, -1).to(hidden.dtype), v.reshape(rows, -1).to(hidden.dtype)]
+            else:       # produced by a later stage: placeholders keep the width static
+                parts += [hidden.new_zeros(rows, self._tokens_per_row() * h * d)] * 2
+        return torch.cat(parts, dim=-1)
+
+    def set_input_tensor(self, input_tensor):
+        if isinstance(input_tensor, (list, tuple)):
+            input_tensor = input_tensor[0]
+        H = self.config.hidden_size
+        if input_tensor is None or input_tensor.shape[-1] == H:
+            return super().set_input_tensor(input_tensor)
+        rows = input_tensor.shape[0]
+        tokens = rows * self._tokens_per_row()
+        tp = ps.get_world_size('tp')
+        assert input_tensor.shape[-1] == self.pipeline_width(), (input_tensor.shape, self.pipeline_width())
+        got, at = {}, H
+        if self.per_layer_dim:
+            w = tokens * self.config.num_layers * (self.per_layer_dim // tp) // rows
+            got[PER_LAYER] = input_tensor[:, at:at + w].reshape(tokens, self.config.num_layers, self.per_layer_dim // tp)
+            at += w
+        kv = {}
+        for lt, h, d in self._kv_slots():
+            w = tokens * h * d // rows
+            kv[lt] = (input_tensor[:, at:at + w].reshape(tokens, h, d),
+                      input_tensor[:, at + w:at + 2 * w].reshape(tokens, h, d))
+            at += 2 * w
+        if kv:
+            got[SHARED_KV] = kv
+        self._received = got
+        super().set_input_tensor(input_tensor[:, :H])
+
+    def forward(self, *args, **kwargs):
+        out = super().forward(*args, **kwargs)
+        if not self.post_process and self._extra_columns():
+            out = self._pack(out, self._ctx)
+        self._ctx = None
+        return out
 
     # ---- embeddings
     def _per_layer_inputs(self, embeds_full: torch.Tensor, ids: Optional[torch.Tensor], ctx: ForwardContext):
@@ -311,12 +385,15 @@ class Gemma4TextModel(GPTModel):
         L, P = self.config.num_layers, self.per_layer_dim
         proj = self.per_layer_model_projection(embeds_full)
         proj = self.per_layer_projection_norm((proj * float(self.config.hidden_size) ** -0.5).view(-1, L, P))
-        if ids is None:
-            ctx.extra[PER_LAYER] = proj
-            return
-        tab = self.embed_tokens_per_layer(ids.reshape(-1).clamp(min=0))
-        tab = (tab * torch.tensor(float(P) ** 0.5, dtype=tab.dtype)).view(-1, L, P)
-        ctx.extra[PER_LAYER] = (proj + tab) * (2.0 ** -0.5)
+        if ids is not None:
+            tab = self.embed_tokens_per_layer(ids.reshape(-1).clamp(min=0))
+            tab = (tab * torch.tensor(float(P) ** 0.5, dtype=tab.dtype)).view(-1, L, P)
+            proj = (proj + tab) * (2.0 ** -0.5)
+        if ps.get_world_size('tp') > 1:
+            # Every layer's gate is column-parallel over P: keep this rank's columns only.  The values were computed
+            # identically on every rank, so the backward gathers the ranks' column gradients into the full gradient.
+            proj = M.scatter_to_tensor_model_parallel_region(proj, 'tp')
+        ctx.extra[PER_LAYER] = proj
 
     def embed(self, flat_ids, ctx, sp):
         e = self.embedding(flat_ids.clamp(min=0), scatter_to_sequence_parallel=False)

@@ -307,6 +307,7 @@ class DistributedOptimizer:
         # buffer's sum of squares is scaled accordingly (buffers can have different data-parallel sizes: dense vs expert).
         part = torch.zeros_like(self._sq)
         cur = None
+        tied_copy = ps.get_world_size('embd') > 1 and not ps.is_pipeline_first_stage()
 
         def flush():
             if cur is not None:
@@ -322,6 +323,12 @@ class DistributedOptimizer:
             # replicated (non tensor-parallel) parameters are counted once per TP group
             if not tp_rank0 and ps.get_world_size('tp') > 1:
                 dup = self._replicated_mask(buf, b, s, e)
+                if dup is not None:
+                    g = g * dup
+            # a tied embedding lives on the first and on the last pipeline stage (both hold the summed gradient):
+            # the first stage's copy is the one that counts
+            if tied_copy:
+                dup = self._replicated_mask(buf, b, s, e, lambda p: getattr(p, 'shared_embedding', False))
                 if dup is not None:
                     g = g * dup
             if self._use_cuda() and g.dtype == torch.float32:
@@ -343,10 +350,15 @@ class DistributedOptimizer:
             else:
                 self._coef.fill_(1.0)
 
-    def _replicated_mask(self, buf, b, s, e):
+    def _replicated_mask(self, buf, b, s, e, duplicate=None):
+        """0 over the part of the shard ``[s, e)`` that belongs to parameters another rank already counts (by default
+        the parameters replicated over the tensor-parallel group), 1 elsewhere; ``None`` when nothing is masked."""
+        if duplicate is None:
+            def duplicate(p):
+                return not (getattr(p, 'tensor_model_parallel', False) or getattr(p, 'is_expert', False))
         mask = None
         for p in b.params:
-            if getattr(p, 'tensor_model_parallel', False) or getattr(p, 'is_expert', False):
+            if not duplicate(p):
                 continue
             ps_, pe = buf.param_range[p]
             lo, hi = max(ps_, s), min(pe, e)

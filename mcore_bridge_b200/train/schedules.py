@@ -99,6 +99,15 @@ def _forward(trainer, model, d: Dict, input_tensor: Optional[torch.Tensor], n_mi
     return out
 
 
+def _pipeline_width(trainer) -> int:
+    """Columns of the tensor sent between stages: the hidden size, or what the model declares when it sends more than
+    the hidden states (Gemma-4 packs its per-layer inputs and shared keys / values behind them)."""
+    m = trainer.models[0]
+    m = getattr(m, 'language_model', m)
+    fn = getattr(m, 'pipeline_width', None)
+    return int(fn()) if fn is not None else trainer.config.hidden_size
+
+
 def _backward(output: torch.Tensor, grad: Optional[torch.Tensor], input_tensor: Optional[torch.Tensor]):
     if grad is None:
         output.backward()
@@ -115,7 +124,7 @@ def forward_backward_pipelining(trainer, microbatches: List[Dict]) -> torch.Tens
     n = len(microbatches)
     dev = trainer.device
     p2p = _P2P(cfg, dev)
-    H = cfg.hidden_size
+    H = _pipeline_width(trainer)
     trainer.optimizer.zero_grad()
     from ..layers.mtp import MTPLossAutoScaler
     from ..ops.moe import MoEAuxLossAutoScaler
@@ -172,7 +181,7 @@ def _chunked_schedule(trainer, data, p2p: _P2P, total: torch.Tensor) -> torch.Te
     """Virtual pipeline: virtual stage ``v = chunk * pp + rank``; data flows v -> v+1."""
     cfg = trainer.config
     pp, rank = ps.get_pipeline_model_parallel_world_size(), ps.get_pipeline_model_parallel_rank()
-    n, V, H = len(data), len(trainer.ddp), cfg.hidden_size
+    n, V, H = len(data), len(trainer.ddp), _pipeline_width(trainer)
     saved = {}
     for c in range(V):
         model = trainer.ddp[c]
@@ -206,7 +215,7 @@ def _interleaved_schedule(trainer, data, p2p: _P2P, total: torch.Tensor) -> torc
     ``(k // (pp * V)) * pp + k % pp``."""
     cfg = trainer.config
     pp, rank = ps.get_pipeline_model_parallel_world_size(), ps.get_pipeline_model_parallel_rank()
-    n, V, H = len(data), len(trainer.ddp), cfg.hidden_size
+    n, V, H = len(data), len(trainer.ddp), _pipeline_width(trainer)
     steps = n * V
     warm = min((pp - rank - 1) * 2 + (V - 1) * pp, steps)
     saved = {}

@@ -88,3 +88,32 @@ def test_deepseek_v3_tp2_ep2_matches_single_process(tmp_path):
 
 def test_deepseek_v3_pp2_ep2_matches_single_process(tmp_path):
     _check(tmp_path, _deepseek_v3(), pp=2, ep=2, over={'moe_aux_loss_coeff': 1e-2})
+
+
+def _gemma4():
+    from transformers import Gemma4ForCausalLM, Gemma4TextConfig
+    c = Gemma4TextConfig(vocab_size=256, hidden_size=64, intermediate_size=96, num_hidden_layers=6,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=16, global_head_dim=32,
+                         num_global_key_value_heads=2, attention_k_eq_v=True,
+                         layer_types=['sliding_attention', 'sliding_attention', 'full_attention'] * 2,
+                         sliding_window=32, num_kv_shared_layers=2, use_double_wide_mlp=True,
+                         hidden_size_per_layer_input=8, vocab_size_per_layer_input=256, enable_moe_block=True,
+                         num_experts=4, top_k_experts=2, moe_intermediate_size=32, final_logit_softcapping=30.0,
+                         max_position_embeddings=512, tie_word_embeddings=True, pad_token_id=0)
+    return Gemma4ForCausalLM(c).float()
+
+
+def test_gemma4_pp2_dp2_matches_single_process(tmp_path):
+    """Per-layer inputs and the shared keys / values of the full-attention type cross the stage boundary (the sliding
+    type's are produced on the second stage), gradients come back through the packed tensor."""
+    _check(tmp_path, _gemma4(), pp=2)
+
+
+def test_gemma4_tp2_pp2_matches_single_process(tmp_path):
+    _check(tmp_path, _gemma4(), tp=2, pp=2)
+
+
+def test_gemma4_tp2_dp2_matches_single_process(tmp_path):
+    """The per-layer inputs are computed identically on both tensor-parallel ranks and consumed column by column: the
+    gradients of the table, the projection and its norm need the other rank's columns too."""
+    _check(tmp_path, _gemma4(), tp=2)

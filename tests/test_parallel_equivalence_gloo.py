@@ -110,3 +110,10 @@ def test_moe_seq_aux_loss_tp2_ep2_matches_single_process(tmp_path):
     from transformers import Qwen3MoeForCausalLM
     _check(tmp_path, 'qwen3_moe_tiny', Qwen3MoeForCausalLM, tp=2, ep=2, aux=1e-2,
            over={'moe_router_load_balancing_type': 'seq_aux_loss'})
+
+
+def test_dense_tied_embeddings_pp2_dp2_matches_single_process(tmp_path):
+    """The tied matrix lives on both pipeline ends; its gradient is summed over the two copies and must enter the
+    clipping norm once."""
+    from transformers import Qwen3ForCausalLM
+    _check(tmp_path, 'qwen3_tiny', Qwen3ForCausalLM, tp=1, ep=1, pp=2, hf_over={'tie_word_embeddings': True})
