@@ -5,6 +5,7 @@ import torch
 from dist_utils import run_ranks
 
 STEPS, GLOBAL_MB = 2, 4
+_BASE = {}      # single-process results per model (the checkpoint is seeded, so they do not depend on the test)
 
 
 def _worker(rank, world, ckpt, tp, ep, pp, cp, over):
@@ -42,7 +43,10 @@ def _check(tmp_path, hf, tp=1, ep=1, pp=1, cp=1, over=None, atol=2e-6):
             p.normal_(0, 0.05) if p.dim() >= 2 else p.normal_(1.0 if 'norm' in n else 0.0, 0.05)
     d = str(tmp_path / 'ckpt')
     hf.save_pretrained(d)
-    base_losses, base_w, _ = run_ranks(_worker, 1, d, 1, 1, 1, 1, over)[0]
+    key = (type(hf).__name__, repr(sorted((over or {}).items())))
+    if key not in _BASE:
+        _BASE[key] = run_ranks(_worker, 1, d, 1, 1, 1, 1, over)[0]
+    base_losses, base_w, _ = _BASE[key]
     res = run_ranks(_worker, 4, d, tp, ep, pp, cp, over)
     for losses, weights, last_stage in res:
         if last_stage:
@@ -84,10 +88,6 @@ def test_qwen3_next_cp2_ep2_matches_single_process(tmp_path):
 
 def test_deepseek_v3_tp2_ep2_matches_single_process(tmp_path):
     _check(tmp_path, _deepseek_v3(), tp=2, ep=2, over={'moe_aux_loss_coeff': 1e-2})
-
-
-def test_deepseek_v3_pp2_ep2_matches_single_process(tmp_path):
-    _check(tmp_path, _deepseek_v3(), pp=2, ep=2, over={'moe_aux_loss_coeff': 1e-2})
 
 
 def _gemma4():

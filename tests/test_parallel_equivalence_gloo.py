@@ -2,12 +2,12 @@
 expert x data parallel for an MoE model — against the same two steps in one process: losses and every exported weight
 must agree.  Weights travel through the Hugging Face checkpoint bridge, so every layout starts from identical values;
 the global batch is the same four micro-batches, dealt out to the data-parallel ranks."""
-import pytest
 import torch
 
 from dist_utils import run_ranks
 
 STEPS, GLOBAL_MB = 2, 4
+_BASE = {}      # single-process results, shared by the layouts of one model / loss configuration
 
 
 def _worker(rank, world, name, ckpt, tp, ep, aux, pp=1, cp=1, etp=1, hf_over=None, over=None):
@@ -49,7 +49,10 @@ def _check(tmp_path, name, hf_cls, tp, ep, aux=0.0, pp=1, cp=1, etp=1, hf_over=N
             p.normal_(0, 0.05) if p.dim() >= 2 else p.normal_(1.0, 0.05)
     d = str(tmp_path / 'ckpt')
     hf.save_pretrained(d)
-    base_losses, base_w, _ = run_ranks(_worker, 1, name, d, 1, 1, aux, 1, 1, 1, hf_over, over)[0]
+    key = (name, aux, repr(sorted((hf_over or {}).items())), repr(sorted((over or {}).items())))
+    if key not in _BASE:        # the checkpoint is a function of the key (seeded), so the reference run is too
+        _BASE[key] = run_ranks(_worker, 1, name, d, 1, 1, aux, 1, 1, 1, hf_over, over)[0]
+    base_losses, base_w, _ = _BASE[key]
     res = run_ranks(_worker, 4, name, d, tp, ep, aux, pp, cp, etp, hf_over, over)
     for losses, weights, last_stage in res:
         if last_stage:                      # only the last pipeline stage sees the loss
@@ -65,10 +68,9 @@ def test_dense_tp2_dp2_matches_single_process(tmp_path):
     _check(tmp_path, 'qwen3_tiny', Qwen3ForCausalLM, tp=2, ep=1)
 
 
-@pytest.mark.parametrize('aux', [0.0, 1e-2])
-def test_moe_ep2_dp_matches_single_process(tmp_path, aux):
+def test_moe_ep2_dp_matches_single_process(tmp_path):
     from transformers import Qwen3MoeForCausalLM
-    _check(tmp_path, 'qwen3_moe_tiny', Qwen3MoeForCausalLM, tp=1, ep=2, aux=aux)
+    _check(tmp_path, 'qwen3_moe_tiny', Qwen3MoeForCausalLM, tp=1, ep=2, aux=1e-2)
 
 
 def test_dense_pp2_dp2_matches_single_process(tmp_path):
@@ -89,11 +91,6 @@ def test_moe_tp2_ep2_matches_single_process(tmp_path):
 def test_dense_tp2_pp2_matches_single_process(tmp_path):
     from transformers import Qwen3ForCausalLM
     _check(tmp_path, 'qwen3_tiny', Qwen3ForCausalLM, tp=2, ep=1, pp=2)
-
-
-def test_dense_tied_embeddings_tp2_dp2_matches_single_process(tmp_path):
-    from transformers import Qwen3ForCausalLM
-    _check(tmp_path, 'qwen3_tiny', Qwen3ForCausalLM, tp=2, ep=1, hf_over={'tie_word_embeddings': True})
 
 
 def test_moe_expert_tensor_parallel_dp2_matches_single_process(tmp_path):
