@@ -70,6 +70,11 @@ def shard_token_aligned(mask_full: torch.Tensor, values: torch.Tensor, cu_seqlen
     order = torch.cumsum(mask_full.to(torch.int64), 0) - 1          # rank of each media token among media tokens
     local_mask = mask_full[idx]
     sel = order[idx][local_mask]
+    if config.sequence_parallel and ps.get_world_size('tp') > 1:
+        # every tensor-parallel rank computed the same ``values`` and now keeps the rows of its token slice: the
+        # gradient of the (replicated) tower is the sum of the ranks' row gradients
+        from ...parallel import mappings as M
+        values = M.copy_to_tensor_model_parallel_region(values, 'tp')
     return local_mask, values[:, sel]
 
 
