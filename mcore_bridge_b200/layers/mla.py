@@ -84,11 +84,14 @@ class DSAIndexer(nn.Module):
         from ..ops import dsa
         return dsa.index_scores(q, k, w, mask)
 
-    def forward(self, x, qr, ctx: ForwardContext, mask: torch.Tensor):
+    def forward(self, x, qr, ctx: ForwardContext, mask: torch.Tensor, gather_keys=None):
+        """``gather_keys``: under context parallelism, maps this rank's keys to the keys of the whole stream."""
         from ..ops import dsa
         q, k, w = self.forward_before_topk(x, qr, ctx)
+        if gather_keys is not None:
+            k = gather_keys(k)
         T = q.shape[0]
-        topk = min(self.topk, T)
+        topk = min(self.topk, k.shape[0])
         if mask is None and not (not torch.is_grad_enabled() and dsa.cuda_indexer_supported(q, k)
                                  and ps.get_world_size('cp') == 1):
             seg = segment_ids(ctx.cu_seqlens, T)
@@ -181,6 +184,10 @@ class MLASelfAttention(nn.Module):
         v = v.contiguous()
         if self.indexer is not None:
             o = self._sparse_attention(x, qr, q, k, v, ctx, sp)
+        elif ps.get_world_size('cp') > 1:
+            # this rank holds two zig-zag chunks of every sequence: keys / values are exchanged over the group
+            from ..parallel.context_parallel import ring_attention
+            o = ring_attention(q.contiguous(), k.contiguous(), v, ctx, scale=self.scale)
         else:
             o = attention(q.contiguous(), k.contiguous(), v, ctx.cu_seqlens, ctx.max_seqlen, causal=True,
                           scale=self.scale)
@@ -229,13 +236,27 @@ class MLASelfAttention(nn.Module):
         cfg = self.config
         T = q.shape[0]
         xg = M.gather_from_sequence_parallel_region(x, 'tp', tensor_parallel_output_grad=False) if sp else x
-        seg = segment_ids(ctx.cu_seqlens, T)
-        pos = torch.arange(T, device=q.device)
-        mask = (seg[:, None] == seg[None, :]) & (pos[None, :] <= pos[:, None])
+        gather_keys = None
+        if ps.get_world_size('cp') > 1:
+            # queries are this rank's zig-zag chunks, keys / values (and the indexer's keys) those of the whole stream
+            from ..parallel.context_parallel import gather_to_stream_order, stream_index_of_local_tokens
+
+            def gather_keys(t):
+                return gather_to_stream_order(t, ctx)
+
+            k, v = gather_keys(k.contiguous()), gather_keys(v)
+            qpos = stream_index_of_local_tokens(ctx, q.device)
+            seg = segment_ids(ctx.cu_seqlens, k.shape[0])
+            mask = (seg[qpos][:, None] == seg[None, :]) & (torch.arange(k.shape[0], device=q.device)[None, :]
+                                                            <= qpos[:, None])
+        else:
+            seg = segment_ids(ctx.cu_seqlens, T)
+            pos = torch.arange(T, device=q.device)
+            mask = (seg[:, None] == seg[None, :]) & (pos[None, :] <= pos[:, None])
         train_indexer = self.training and cfg.dsa_indexer_loss_coeff > 0
         with torch.set_grad_enabled(train_indexer):
             idx, scores = self.indexer(xg.detach() if not train_indexer else xg.detach(),
-                                       qr.detach(), ctx, mask)
+                                       qr.detach(), ctx, mask, gather_keys)
         from ..ops import dsa
         o, attn_probs = dsa.sparse_attention(q, k, v, idx, mask, self.scale, need_probs=train_indexer)
         if train_indexer:

@@ -109,6 +109,12 @@ class MultiTokenPredictionBlock(nn.Module):
                 s[0] = s[0] + (mtp_loss.sum() / n.clamp(min=1)).detach()
                 s[1] += 1
             scale = cfg.mtp_loss_scaling_factor / steps
+            if cp_group is not None:
+                # the mean is over the tokens of the whole sequences: this rank adds its share of it, times cp because
+                # gradients are averaged over the dp x cp group afterwards (as for the main loss)
+                n = n.clone()
+                torch.distributed.all_reduce(n, group=cp_group)
+                scale = scale * ps.get_world_size('cp')
             safe_n = n.clamp(min=1)
             if cfg.calculate_per_token_loss:
                 hidden = MTPLossAutoScaler.apply(hidden, scale * mtp_loss * (original_tokens / safe_n))

@@ -74,7 +74,14 @@ class GPTModel(nn.Module):
                     self.output_layer.weight = self.embedding.word_embeddings.weight
                     # embedding lookup and head (and, per MTP depth, one more of each) produce a gradient for this
                     # tensor in every backward pass; the bucket waits for all of them
-                    self.output_layer.weight.grad_contributions = 2 + 2 * int(config.mtp_num_layers or 0)
+                    self.output_layer.weight.grad_contributions = 2 + 2 * (
+                        int(config.mtp_unroll_steps or config.mtp_num_layers or 0) if self.mtp is not None else 0)
+                elif self.mtp is not None:
+                    # untied, with MTP: every depth looks up the embedding and applies the head once more
+                    extra = int(config.mtp_unroll_steps or config.mtp_num_layers or 0)
+                    self.output_layer.weight.grad_contributions = 1 + extra
+                    if self.embedding is not None:
+                        self.embedding.word_embeddings.weight.grad_contributions = (1 if pre_process else 0) + extra
             elif task == 'seq_cls':
                 self.output_layer = ReplicatedLinear(config.hidden_size, config.num_labels, config, bias=False,
                                                      sequence_parallel_grad=False)

@@ -63,6 +63,22 @@ def local_chunk_layout(cu_seqlens: torch.Tensor, cp: int, rank: int) -> List[Tup
     return out
 
 
+def gather_to_stream_order(x: torch.Tensor, ctx) -> torch.Tensor:
+    """``[T_local, ...]`` on every CP rank -> ``[cp * T_local, ...]`` in the order of the original token stream
+    (differentiable: the backward reduce-scatters)."""
+    cp = ps.get_world_size('cp')
+    full = _AllGatherTokens.apply(x, 'cp')
+    index = cp_gather_index(ctx.cu_seqlens, x.shape[0] * cp, cp).to(x.device)
+    return full.index_select(0, index)
+
+
+def stream_index_of_local_tokens(ctx, device) -> torch.Tensor:
+    """Position in the original token stream of every token this CP rank holds, in local order."""
+    parts = [torch.arange(g0, g0 + c, device=device)
+             for _, g0, c in local_chunk_layout(ctx.cu_seqlens, ps.get_world_size('cp'), ps.get_rank_in('cp')) if c]
+    return torch.cat(parts)
+
+
 def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ctx, scale: Optional[float] = None,
                    window=None, sinks=None) -> torch.Tensor:
     """``q/k/v`` hold this rank's tokens ``[T_local, heads, d]``; returns ``[T_local, nq, dv]``."""

@@ -117,3 +117,24 @@ def test_gemma4_tp2_dp2_matches_single_process(tmp_path):
     """The per-layer inputs are computed identically on both tensor-parallel ranks and consumed column by column: the
     gradients of the table, the projection and its norm need the other rank's columns too."""
     _check(tmp_path, _gemma4(), tp=2)
+
+
+def _glm_dsa():
+    from transformers import GlmMoeDsaConfig, GlmMoeDsaForCausalLM
+    c = GlmMoeDsaConfig(num_hidden_layers=2, hidden_size=128, num_attention_heads=4, num_key_value_heads=4,
+                        q_lora_rank=32, kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                        n_routed_experts=4, num_experts_per_tok=2, n_group=1, topk_group=1, moe_intermediate_size=32,
+                        intermediate_size=128, mlp_layer_types=['dense', 'sparse'], n_shared_experts=1, vocab_size=256,
+                        max_position_embeddings=512, index_n_heads=4, index_head_dim=32, index_topk=16,
+                        tie_word_embeddings=False)
+    return GlmMoeDsaForCausalLM(c).float()
+
+
+def test_glm_dsa_cp2_ep2_matches_single_process(tmp_path):
+    """Sparse (top-16 keys) MLA attention with the queries of this rank's zig-zag chunks against the gathered keys of
+    the whole stream, indexer keys included."""
+    _check(tmp_path, _glm_dsa(), cp=2, ep=2)
+
+
+def test_glm_dsa_tp2_ep2_matches_single_process(tmp_path):
+    _check(tmp_path, _glm_dsa(), tp=2, ep=2)
