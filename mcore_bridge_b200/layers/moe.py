@@ -68,6 +68,12 @@ class TopKRouter(nn.Module):
         self.weight = nn.Parameter(torch.empty(self.num_experts, config.hidden_size, dtype=config.params_dtype))
         _set_tp_attrs(self.weight, False, -1)
         mark_sequence_parallel(self.weight, config)
+        if config.add_bias_linear:          # GPT-OSS: biased gate
+            self.bias = nn.Parameter(torch.zeros(self.num_experts, dtype=config.params_dtype))
+            _set_tp_attrs(self.bias, False, -1)
+            mark_sequence_parallel(self.bias, config)
+        else:
+            self.register_parameter('bias', None)
         self.enable_expert_bias = bool(config.moe_router_enable_expert_bias)
         if self.enable_expert_bias:
             self.register_buffer('expert_bias', torch.zeros(self.num_experts, dtype=torch.float32))
@@ -78,7 +84,7 @@ class TopKRouter(nn.Module):
 
     def gating(self, x: torch.Tensor) -> torch.Tensor:
         dt = {None: x.dtype, 'fp32': torch.float32, 'fp64': torch.float64}[self.config.moe_router_dtype]
-        return torch.nn.functional.linear(x.to(dt), self.weight.to(dt))
+        return torch.nn.functional.linear(x.to(dt), self.weight.to(dt), None if self.bias is None else self.bias.to(dt))
 
     def _apply_expert_bias(self, indices: torch.Tensor, padding_mask: Optional[torch.Tensor]):
         if self.enable_expert_bias and torch.is_grad_enabled():
@@ -140,7 +146,8 @@ class TopKRouter(nn.Module):
 class GroupedLinear(nn.Module):
     """``E_local`` linears as one stacked parameter; forward over an expert-sorted, padded row buffer."""
 
-    def __init__(self, num_local_experts: int, input_size: int, output_size: int, config, parallel_mode: str):
+    def __init__(self, num_local_experts: int, input_size: int, output_size: int, config, parallel_mode: str,
+                 bias: bool = False):
         super().__init__()
         n = ps.get_world_size('etp')
         self.parallel_mode = parallel_mode
@@ -153,6 +160,21 @@ class GroupedLinear(nn.Module):
         self.num_local_experts = num_local_experts
         self.weight = nn.Parameter(torch.empty(num_local_experts, output_size, input_size, dtype=config.params_dtype))
         _set_tp_attrs(self.weight, n > 1, pdim, is_expert=True)
+        if bias:
+            if n > 1:
+                raise NotImplementedError('expert biases are not supported together with expert tensor parallelism')
+            self.bias = nn.Parameter(torch.zeros(num_local_experts, output_size, dtype=config.params_dtype))
+            _set_tp_attrs(self.bias, False, -1, is_expert=True)
+        else:
+            self.register_parameter('bias', None)
+
+    def row_bias(self, offsets: torch.Tensor, rows: int, row_scale=None) -> torch.Tensor:
+        """``[rows, out]``: every row's expert bias (rows of segment ``e`` are ``offsets[e]:offsets[e+1]``; padding
+        rows get the bias of their segment, which nothing reads), optionally scaled per row."""
+        eid = torch.searchsorted(offsets[1:].to(torch.int64).contiguous(), torch.arange(rows, device=offsets.device),
+                                 right=True).clamp(max=self.num_local_experts - 1)
+        b = self.bias[eid]
+        return b if row_scale is None else b * row_scale[:, None].to(b.dtype)
 
     def __getattr__(self, name):
         m = re.fullmatch(r'weight(\d+)', name)
@@ -160,8 +182,11 @@ class GroupedLinear(nn.Module):
             return super().__getattr__('weight')[int(m.group(1))]
         return super().__getattr__(name)
 
-    def forward(self, x, offsets):
-        return _GroupedLinearFn.apply(x, self.weight, offsets)
+    def forward(self, x, offsets, bias_scale=None):
+        y = _GroupedLinearFn.apply(x, self.weight, offsets)
+        if self.bias is not None:
+            y = y + self.row_bias(offsets, y.shape[0], bias_scale)
+        return y
 
 
 class _GroupedLinearFn(torch.autograd.Function):
@@ -197,8 +222,9 @@ class GroupedMLP(nn.Module):
         self.config = config
         f = config.moe_ffn_hidden_size
         mult = 2 if config.gated_linear_unit else 1
-        self.linear_fc1 = GroupedLinear(num_local_experts, config.hidden_size, f * mult, config, 'column')
-        self.linear_fc2 = GroupedLinear(num_local_experts, f, config.hidden_size, config, 'row')
+        b = bool(config.add_bias_linear)
+        self.linear_fc1 = GroupedLinear(num_local_experts, config.hidden_size, f * mult, config, 'column', bias=b)
+        self.linear_fc2 = GroupedLinear(num_local_experts, f, config.hidden_size, config, 'row', bias=b)
         self.kind = 'swiglu' if config.swiglu else ('quick_geglu' if config.quick_geglu else 'geglu_tanh')
 
     def forward(self, x, offsets, row_probs=None):
@@ -210,7 +236,8 @@ class GroupedMLP(nn.Module):
             h = cfg.activation_func(h)
             if row_probs is not None:
                 h = h * row_probs[:, None].to(h.dtype)
-        return self.linear_fc2(h, offsets)
+        # the routing probability multiplies the expert's whole output, its output bias included
+        return self.linear_fc2(h, offsets, row_probs)
 
 
 class SharedExpertMLP(nn.Module):

@@ -62,3 +62,59 @@ register_model(ModelMeta(ModelType.hy_v3, ['hy_v3'], bridge_cls=HyV3Bridge))
 register_model(ModelMeta(ModelType.bailing_moe, ['bailing_moe'], bridge_cls=BailingMoeBridge))
 register_model(ModelMeta(ModelType.bailing_hybrid, ['bailing_hybrid'], bridge_cls=BailingHybridBridge))
 register_model(ModelMeta(ModelType.qwen3_emb, [], bridge_cls=Qwen3EmbBridge))
+
+
+# ---------------------------------------------------------------------------------------------- GPT-OSS
+class GptOssBridge(GPTBridge):
+    """Biased gate (``mlp.router.{weight,bias}``) and experts stored as fused, input-major tensors with gate and up
+    columns interleaved: ``experts.gate_up_proj [E, H, 2F]`` (+ ``gate_up_proj_bias [E, 2F]``), ``experts.down_proj
+    [E, F, H]`` (+ ``down_proj_bias [E, H]``).  Parity: reference ``src/mcore_bridge/bridge/gpt_bridge.py:696-700,
+    894-900,1061-1088``."""
+
+    def _ep_slice(self, t):
+        from ...parallel import state as ps
+        ep = ps.get_world_size('ep')
+        if ep == 1:
+            return t
+        n, r = t.shape[0] // ep, ps.get_rank_in('ep')
+        return t[r * n:(r + 1) * n]
+
+    def _set_moe(self, mlp, hf_sd, prefix: str, to_mcore: bool):
+        import torch
+        router = mlp.router if mlp is not None else None
+        self._direct(router, 'weight', hf_sd, prefix + 'router.weight', to_mcore)
+        self._direct(router, 'bias', hf_sd, prefix + 'router.bias', to_mcore)
+        ex = mlp.experts if mlp is not None else None
+        ep_ = f'{prefix}{self.hf_experts_prefix}.'
+        names = (('linear_fc1.weight', 'gate_up_proj'), ('linear_fc1.bias', 'gate_up_proj_bias'),
+                 ('linear_fc2.weight', 'down_proj'), ('linear_fc2.bias', 'down_proj_bias'))
+        for attr, key in names:
+            mod, leaf = attr.split('.')
+            param = getattr(getattr(ex, mod), leaf) if ex is not None else None
+            fused_gate_up = key.startswith('gate_up')
+            if to_mcore:
+                if param is None:
+                    continue
+                t = self._ep_slice(self._load_hf(hf_sd, ep_ + key))
+                if fused_gate_up:                                   # interleaved (gate, up) pairs -> [gate | up]
+                    t = torch.cat([t[..., ::2], t[..., 1::2]], dim=-1)
+                if leaf == 'weight':
+                    t = t.transpose(1, 2)                           # input-major -> [E, out, in]
+                with torch.no_grad():
+                    param.copy_(t.to(device=param.device, dtype=param.dtype))
+                continue
+            if not self._agree(param is not None, self._device):
+                continue
+            t = None if param is None else param.detach()
+            t = self._broadcast_pp(self._all_gather_ep(t), self._device)
+            if t is None:
+                continue
+            if leaf == 'weight':
+                t = t.transpose(1, 2)
+            if fused_gate_up:
+                g, u = t.chunk(2, dim=-1)
+                t = torch.stack([g, u], dim=-1).reshape(*t.shape)   # back to interleaved pairs
+            self._emit(hf_sd, ep_ + key, t.contiguous())
+
+
+register_model(ModelMeta(ModelType.gpt_oss, ['gpt_oss'], bridge_cls=GptOssBridge))

@@ -43,7 +43,7 @@ def _check(tmp_path, hf, tp=1, ep=1, pp=1, cp=1, over=None, atol=2e-6):
             p.normal_(0, 0.05) if p.dim() >= 2 else p.normal_(1.0 if 'norm' in n else 0.0, 0.05)
     d = str(tmp_path / 'ckpt')
     hf.save_pretrained(d)
-    key = (type(hf).__name__, repr(sorted((over or {}).items())))
+    key = (type(hf).__name__, hf.config.to_json_string(), repr(sorted((over or {}).items())))
     if key not in _BASE:
         _BASE[key] = run_ranks(_worker, 1, d, 1, 1, 1, 1, over)[0]
     base_losses, base_w, _ = _BASE[key]
@@ -57,11 +57,11 @@ def _check(tmp_path, hf, tp=1, ep=1, pp=1, cp=1, over=None, atol=2e-6):
             assert torch.allclose(weights[k], v, rtol=0, atol=atol), (k, (weights[k] - v).abs().max().item())
 
 
-def _qwen3_next():
+def _qwen3_next(k_heads=2, v_heads=4):
     from transformers import Qwen3NextConfig, Qwen3NextForCausalLM
     c = Qwen3NextConfig(num_hidden_layers=4, hidden_size=128, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                         intermediate_size=256, moe_intermediate_size=64, shared_expert_intermediate_size=64,
-                        num_experts=8, num_experts_per_tok=2, linear_num_key_heads=2, linear_num_value_heads=4,
+                        num_experts=8, num_experts_per_tok=2, linear_num_key_heads=k_heads, linear_num_value_heads=v_heads,
                         linear_key_head_dim=32, linear_value_head_dim=32, linear_conv_kernel_dim=4, vocab_size=256,
                         max_position_embeddings=512, full_attention_interval=4, partial_rotary_factor=0.25,
                         tie_word_embeddings=False, decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True)
@@ -138,3 +138,26 @@ def test_glm_dsa_cp2_ep2_matches_single_process(tmp_path):
 
 def test_glm_dsa_tp2_ep2_matches_single_process(tmp_path):
     _check(tmp_path, _glm_dsa(), tp=2, ep=2)
+
+
+def _gpt_oss():
+    from transformers import GptOssConfig, GptOssForCausalLM
+    c = GptOssConfig(num_hidden_layers=4, hidden_size=128, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                     intermediate_size=64, num_local_experts=4, num_experts_per_tok=2, vocab_size=256,
+                     max_position_embeddings=512, sliding_window=32, tie_word_embeddings=False,
+                     layer_types=['sliding_attention', 'full_attention'] * 2, rope_parameters=None)
+    return GptOssForCausalLM(c).float()
+
+
+def test_gpt_oss_tp2_dp2_matches_single_process(tmp_path):
+    """Learnable softmax sinks (sharded by head), sliding-window layers, biased expert projections."""
+    _check(tmp_path, _gpt_oss(), tp=2)
+
+
+def test_gpt_oss_cp2_ep2_matches_single_process(tmp_path):
+    _check(tmp_path, _gpt_oss(), cp=2, ep=2)
+
+
+def test_qwen3_next_tp2_cp2_matches_single_process(tmp_path):
+    # the linear-attention heads are split over tp and, inside the layer, once more over cp
+    _check(tmp_path, _qwen3_next(4, 8), tp=2, cp=2, over={'moe_aux_loss_coeff': 1e-2})
