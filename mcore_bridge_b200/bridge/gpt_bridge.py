@@ -102,6 +102,7 @@ class GPTBridge:
     hf_post_attention_layernorm_key = 'post_attention_layernorm.weight'
     hf_gate_key = 'gate.weight'
     hf_expert_bias_key = 'gate.e_score_correction_bias'
+    hf_expert_bias_2d = False                # stored as ``[1, E]`` (Ernie-4.5)
     hf_shared_expert_prefix = None           # resolved per family ('shared_expert' / 'shared_experts')
     hf_shared_expert_gate_key = 'shared_expert_gate.weight'
     hf_experts_prefix = 'experts'
@@ -606,7 +607,9 @@ class GPTBridge:
         router = mlp.router if mlp is not None else None
         self._direct(router, 'weight', hf_sd, prefix + self.hf_gate_key, to_mcore)
         if cfg.moe_router_enable_expert_bias:
-            self._direct(router, 'expert_bias', hf_sd, prefix + self.hf_expert_bias_key, to_mcore, optional=True)
+            self._direct(router, 'expert_bias', hf_sd, prefix + self.hf_expert_bias_key, to_mcore, optional=True,
+                         to_mg=lambda w: w.reshape(-1),
+                         to_hf=(lambda w: w.reshape(1, -1)) if self.hf_expert_bias_2d else None)
         self._set_experts(mlp.experts if mlp is not None else None, hf_sd, prefix, to_mcore)
         if cfg.moe_shared_expert_intermediate_size:
             sh = mlp.shared_experts if mlp is not None else None

@@ -208,6 +208,9 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
         n_shared = res.pop('n_shared_experts')
     elif llm in {'ernie4_5', 'ernie4_5_moe', 'glm4'}:
         res['rotary_interleaved'] = True
+        if llm == 'ernie4_5_moe':       # softmax probabilities plus a correction bias select the experts
+            res['moe_router_enable_expert_bias'] = True
+            res['moe_router_bias_update_rate'] = 0.0      # a checkpoint value, not moved by the balancing rule
         if llm == 'glm4':
             res['post_sublayer_layernorm'] = True
     elif hf_type in {'gemma4', 'gemma4_unified'} or llm == 'gemma4_text':
@@ -218,6 +221,8 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
         res['swiglu'] = False
         res['gated_linear_unit'] = True
         res['activation_func'] = partial(F.gelu, approximate='tanh')
+    elif llm == 'mistral':
+        res['add_qkv_bias'] = False
     elif llm == 'gpt_oss':
         res.update(add_bias_linear=True, bias_dropout_fusion=False, softmax_type='learnable', swiglu=False,
                    quick_geglu=True, activation_func_clamp_value=7, glu_linear_offset=1)

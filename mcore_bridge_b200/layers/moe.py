@@ -362,12 +362,14 @@ class MoELayer(nn.Module):
         lb = cfg.moe_router_load_balancing_type
         kernel_router = (F.router_supported(self.num_experts, r.topk, cfg.moe_router_num_groups)
                          and not (self.training and cfg.moe_aux_loss_coeff and lb == 'seq_aux_loss')
-                         and not cfg.moe_z_loss_coeff)
+                         and not cfg.moe_z_loss_coeff
+                         # softmax scores with a selection bias (Ernie-4.5) stay on the torch router
+                         and not (cfg.moe_router_score_function != 'sigmoid' and r.expert_bias is not None))
         if kernel_router:
             logits = r.gating(self._router_input(x)).float()
             valid = None if padding_mask is None else ~padding_mask.reshape(-1)
             sigmoid = cfg.moe_router_score_function == 'sigmoid'
-            renorm = (not cfg.moe_router_pre_softmax) if not sigmoid else r.topk > 1
+            renorm = (not cfg.moe_router_pre_softmax) and (not sigmoid or r.topk > 1)
             bias = r.expert_bias if (sigmoid and r.expert_bias is not None) else None
             probs, idx, score_sum, counts = self._fused.route(st, logits, bias, valid, sigmoid, renorm,
                                                               cfg.moe_router_num_groups, cfg.moe_router_group_topk,

@@ -118,3 +118,13 @@ class GptOssBridge(GPTBridge):
 
 
 register_model(ModelMeta(ModelType.gpt_oss, ['gpt_oss'], bridge_cls=GptOssBridge))
+
+
+# ---------------------------------------------------------------------------------------------- Ernie-4.5 MoE
+class Ernie45MoeBridge(GPTBridge):
+    """The selection bias lives in ``mlp.moe_statics.e_score_correction_bias`` with shape ``[1, E]``."""
+    hf_expert_bias_key = 'moe_statics.e_score_correction_bias'
+    hf_expert_bias_2d = True
+
+
+register_model(ModelMeta('ernie4_5_moe', ['ernie4_5_moe'], bridge_cls=Ernie45MoeBridge))

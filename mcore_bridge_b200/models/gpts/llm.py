@@ -8,6 +8,6 @@ from ..register import ModelMeta, register_model
 register_model(
     ModelMeta(ModelType.gpt, [
         'qwen2', 'llama', 'qwen3', 'qwen2_moe', 'qwen3_moe', 'internlm3', 'mimo', 'deepseek', 'deepseek_v2',
-        'deepseek_v3', 'deepseek_v32', 'kimi_k2', 'dots1', 'ernie4_5', 'ernie4_5_moe', 'glm4_moe', 'glm4_moe_lite',
+        'deepseek_v3', 'deepseek_v32', 'kimi_k2', 'dots1', 'ernie4_5', 'glm4_moe', 'glm4_moe_lite',
         'glm_moe_dsa', 'mistral'
     ]))

@@ -26,7 +26,7 @@ def topk_routing(logits: torch.Tensor, topk: int, score_function: str = 'softmax
     softmax + ``pre_softmax``: softmax over all experts, pick top-k, keep the raw probabilities.
     softmax otherwise: pick top-k logits, softmax over the selected k (= renormalised probabilities).
     sigmoid: scores = sigmoid(logits); selection uses ``scores + expert_bias`` when a bias is given; the
-    selected scores are normalised to sum to one (when k > 1), then scaled.
+    selected scores are normalised to sum to one (when k > 1 and not ``pre_softmax``), then scaled.
     """
     logits = logits.float()
     T, E = logits.shape
@@ -44,7 +44,15 @@ def topk_routing(logits: torch.Tensor, topk: int, score_function: str = 'softmax
         return sel_scores.topk(topk, dim=-1).indices
 
     if score_function == 'softmax':
-        if pre_softmax:
+        if expert_bias is not None:
+            # Ernie-4.5: the probabilities plus a correction bias pick the experts, the weights are the picked
+            # probabilities (renormalised unless ``pre_softmax``)
+            scores = torch.softmax(logits, dim=-1)
+            idx = select(scores + expert_bias.float())
+            probs = scores.gather(1, idx)
+            if not pre_softmax:
+                probs = probs / probs.sum(-1, keepdim=True).clamp(min=1e-12)
+        elif pre_softmax:
             scores = torch.softmax(logits, dim=-1)
             idx = select(scores)
             probs = scores.gather(1, idx)
@@ -56,7 +64,7 @@ def topk_routing(logits: torch.Tensor, topk: int, score_function: str = 'softmax
         scores = torch.sigmoid(logits)
         idx = select(scores + expert_bias.float() if expert_bias is not None else scores)
         probs = scores.gather(1, idx)
-        if topk > 1:
+        if topk > 1 and not pre_softmax:        # ``pre_softmax`` here: keep the raw scores (``norm_topk_prob=False``)
             probs = probs / (probs.sum(-1, keepdim=True) + 1e-20)
     else:
         raise ValueError(f'unknown score function {score_function}')
