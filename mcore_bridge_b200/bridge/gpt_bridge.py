@@ -109,6 +109,7 @@ class GPTBridge:
     hf_expert_proj_names = ('gate_proj', 'up_proj', 'down_proj')     # per-expert linear names (MiniMax: w1 / w3 / w2)
     hf_fused_gate_up = False                 # dense MLP exported as one ``gate_up_proj`` tensor (GLM-4)
     hf_fused_experts = False                 # routed experts exported as ``experts.gate_up_proj`` / ``experts.down_proj``
+    hf_experts_transposed = False            # layout written for fused expert tensors when no checkpoint was loaded: input-major ``[E, H, 2F]`` / ``[E, F, H]``
     hf_fused_qkv_key = None                  # e.g. 'query_key_value': one tensor laid out [all q | all k | all v]
     fp8_block_size = 128
 
@@ -554,7 +555,16 @@ class GPTBridge:
                 k2 = ep_prefix + 'down_proj' if (ep_prefix + 'down_proj') in hf_sd else ep_prefix + 'down_proj.weight'
                 w1 = self._load_hf(hf_sd, k1)[ep_rank * El:(ep_rank + 1) * El]
                 w2 = self._load_hf(hf_sd, k2)[ep_rank * El:(ep_rank + 1) * El]
-                if w1.shape[-1] != cfg.hidden_size:      # stored transposed: [E, H, 2F] / [E, F, H]
+                # Output-major ``[E, 2F, H]`` / ``[E, H, F]`` or input-major ``[E, H, 2F]`` / ``[E, F, H]`` (the layout
+                # of these families changed between Transformers releases): read it off whichever tensor is not square
+                if w1.shape[1] != w1.shape[2]:
+                    transposed = w1.shape[-1] != cfg.hidden_size
+                elif w2.shape[1] != w2.shape[2]:
+                    transposed = w2.shape[1] != cfg.hidden_size
+                else:
+                    transposed = bool(self.hf_experts_transposed)
+                self._experts_transposed_seen = transposed
+                if transposed:
                     w1, w2 = w1.transpose(1, 2), w2.transpose(1, 2)
             else:
                 l1, l2 = [], []
@@ -589,6 +599,8 @@ class GPTBridge:
             if w1 is None:
                 return
             if self.hf_fused_experts:
+                if getattr(self, '_experts_transposed_seen', self.hf_experts_transposed):
+                    w1, w2 = w1.transpose(1, 2).contiguous(), w2.transpose(1, 2).contiguous()
                 self._emit(hf_sd, ep_prefix + 'gate_up_proj', w1)
                 self._emit(hf_sd, ep_prefix + 'down_proj', w2)
                 return

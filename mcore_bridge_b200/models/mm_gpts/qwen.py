@@ -97,8 +97,14 @@ class Qwen3VLVit(HuggingFaceVit):
         return {'inputs_embeds': inputs_embeds, 'visual_pos_masks': local_mask, 'deepstack_visual_embeds': local_deep}
 
 
-register_model(ModelMeta(ModelType.qwen3_vl, ['qwen3_vl', 'qwen3_vl_moe'], bridge_cls=MultimodalGPTBridge,
-                         visual_cls=Qwen3VLVit))
+class Qwen3VLMoeBridge(MultimodalGPTBridge):
+    """Experts are stored fused (``experts.gate_up_proj`` / ``experts.down_proj``; input- or output-major depending on
+    the Transformers release that wrote the checkpoint — reference ``src/mcore_bridge/bridge/gpt_bridge.py:765-773``)."""
+    hf_fused_experts = True
+
+
+register_model(ModelMeta(ModelType.qwen3_vl, ['qwen3_vl'], bridge_cls=MultimodalGPTBridge, visual_cls=Qwen3VLVit))
+register_model(ModelMeta('qwen3_vl_moe', ['qwen3_vl_moe'], bridge_cls=Qwen3VLMoeBridge, visual_cls=Qwen3VLVit))
 
 
 # ---------------------------------------------------------------------------------------------- audio helpers

@@ -252,6 +252,7 @@ class Llama4Vit(_PixelTower):
 class Llama4Bridge(_NestedLMBridge):
     hf_mlp_prefix = 'feed_forward'
     hf_gate_key = 'router.weight'
+    hf_fused_experts = True
 
 
 register_model(ModelMeta(ModelType.llama4, ['llama4'], bridge_cls=Llama4Bridge, visual_cls=Llama4Vit))

@@ -68,6 +68,47 @@ def _qwen3_5():
     return c, Qwen3_5ForConditionalGeneration(c)
 
 
+_TEXT = dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, max_position_embeddings=512, pad_token_id=0, tie_word_embeddings=False)
+_TOKENS = dict(image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503,
+               tie_word_embeddings=False)
+
+
+def _qwen2_vl():
+    from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+    c = Qwen2VLConfig(
+        text_config=dict(_TEXT, rope_parameters=dict(rope_type='default', rope_theta=10000.0, mrope_section=[8, 4, 4])),
+        vision_config=dict(depth=2, embed_dim=64, hidden_size=128, mlp_ratio=2, num_heads=4, in_channels=3,
+                           patch_size=4, spatial_merge_size=2, temporal_patch_size=2), **_TOKENS)
+    return c, Qwen2VLForConditionalGeneration(c)
+
+
+def _qwen3_vl_moe():
+    from transformers import Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration
+    c = Qwen3VLMoeConfig(
+        text_config=dict(_TEXT, head_dim=32, moe_intermediate_size=64, num_experts=4, num_experts_per_tok=2,
+                         decoder_sparse_step=1, mlp_only_layers=[],
+                         rope_parameters=dict(rope_type='default', rope_theta=10000.0, mrope_section=[8, 4, 4],
+                                              mrope_interleaved=True)),
+        vision_config=dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=4, in_channels=3, patch_size=4,
+                           spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=128,
+                           num_position_embeddings=64, deepstack_visual_indexes=[0]), **_TOKENS)
+    return c, Qwen3VLMoeForConditionalGeneration(c)
+
+
+def _glm4v():
+    from transformers import Glm4vConfig, Glm4vForConditionalGeneration
+    c = Glm4vConfig(
+        text_config=dict(_TEXT, head_dim=32, rope_parameters=dict(rope_type='default', rope_theta=10000.0,
+                                                                  mrope_section=[4, 6, 6], partial_rotary_factor=1.0)),
+        vision_config=dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=4, in_channels=3, patch_size=4,
+                           spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=128, image_size=32),
+        image_token_id=500, video_token_id=501, image_start_token_id=502, image_end_token_id=503,
+        tie_word_embeddings=False)
+    c.vision_start_token_id, c.vision_end_token_id = 502, 503        # names the shared input helper uses
+    return c, Glm4vForConditionalGeneration(c)
+
+
 def _inputs(c):
     g = torch.Generator().manual_seed(0)
     grid = torch.tensor([[1, 8, 8]])                       # 64 patches -> 16 merged image tokens
@@ -81,7 +122,7 @@ def _inputs(c):
     return ids, pixels, grid
 
 
-@pytest.mark.parametrize('build', [_qwen3_vl, _qwen2_5_vl, _qwen3_5])
+@pytest.mark.parametrize('build', [_qwen3_vl, _qwen2_5_vl, _qwen3_5, _qwen2_vl, _qwen3_vl_moe, _glm4v])
 def test_image_prompt_logits_and_roundtrip(build, tmp_path):
     torch.manual_seed(0)
     c, hf = build()
