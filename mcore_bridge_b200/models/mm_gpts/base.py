@@ -185,11 +185,15 @@ class HFProxy:
 
     def __getattr__(self, name):
         tower = object.__getattribute__(self, '_tower')
+        if name in ('dtype', 'device'):          # properties of the Hugging Face base class: answer from the parameters
+            return getattr(next(tower.parameters()), name)
         try:
             return getattr(tower, name)
         except AttributeError:
             cls = getattr(tower, 'model_cls', None)
             if cls is not None and hasattr(cls, name):
                 attr = getattr(cls, name)
+                if isinstance(attr, property):
+                    return attr.fget(self)
                 return attr.__get__(self) if callable(attr) else attr
             raise

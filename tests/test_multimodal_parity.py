@@ -157,3 +157,49 @@ def test_image_prompt_logits_and_roundtrip(build, tmp_path):
     assert sorted(a) == sorted(b)
     for k in a:
         assert torch.equal(a[k], b[k]), k
+
+
+def test_internvl_image_prompt_logits_and_roundtrip(tmp_path):
+    """HF-native InternVL: ``pixel_values [n, 3, h, w]``, pixel-shuffle + projector borrowed from the Transformers class;
+    the checkpoint uses the published key layout (``language_model.model.*``, ``vision_tower.*``)."""
+    from safetensors.torch import save_file
+    from transformers import InternVLConfig, InternVLForConditionalGeneration
+    torch.manual_seed(0)
+    c = InternVLConfig(
+        text_config=dict(model_type='qwen2', vocab_size=512, hidden_size=128, intermediate_size=256,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=512, tie_word_embeddings=False),
+        vision_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                           image_size=[32, 32], patch_size=[8, 8], num_channels=3),
+        image_token_id=500, downsample_ratio=0.5, tie_word_embeddings=False)
+    hf = _randomise(InternVLForConditionalGeneration(c).float().eval())
+    renames = [('model.language_model.', 'language_model.model.'), ('lm_head.', 'language_model.lm_head.'),
+               ('model.vision_tower.', 'vision_tower.'), ('model.multi_modal_projector.', 'multi_modal_projector.')]
+    published = {}
+    for k, v in hf.state_dict().items():
+        for a, b in renames:
+            if k.startswith(a):
+                k = b + k[len(a):]
+                break
+        published[k] = v.contiguous()
+    d1, d2 = str(tmp_path / 'a'), str(tmp_path / 'b')
+    os.makedirs(d1)
+    save_file(published, os.path.join(d1, 'model.safetensors'))
+    c.save_pretrained(d1)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(1, 400, (1, 32), generator=g)
+    ids[0, 4:8] = 500                                      # 16 patches, pixel-shuffled to 4 image tokens
+    pixels = torch.randn(1, 3, 32, 32, generator=g)
+    with torch.no_grad():
+        ref = hf(input_ids=ids, pixel_values=pixels).logits
+    from transformers import AutoConfig
+    cfg = ModelConfig(**hf_to_mcore_config(AutoConfig.from_pretrained(d1)), params_dtype=torch.float32)
+    model = get_mcore_model(cfg)[0].eval()
+    cfg.bridge.load_weights([model], d1)
+    with torch.no_grad():
+        assert (model(ids, pixel_values=pixels) - ref).abs().max().item() < 3e-5
+    cfg.bridge.save_weights([model], d2)
+    b = load_file(os.path.join(d2, 'model.safetensors'))
+    assert sorted(b) == sorted(published)
+    for k, v in published.items():
+        assert torch.equal(b[k], v), k
