@@ -153,9 +153,13 @@ class SelfAttention(nn.Module):
             q, k, v, gate = qkv_split_norm_rope(qkv, wq, wk, cos, sin, self.ng_local, qpg, self.d, self.gate,
                                                 cfg.rotary_interleaved, cfg.layernorm_epsilon,
                                                 cfg.layernorm_zero_centered_gamma)
-        if self.qk_l2_norm:
-            from ..ops.norm import l2norm
-            q, k = l2norm(q), l2norm(k)
+        if self.qk_l2_norm and self.use_rope:
+            # Llama-4: weight-less RMS normalisation of q and k after the rotation, on the layers that rotate
+            # (``Llama4TextL2Norm`` divides by the root *mean* square)
+            def unit_rms(t):
+                tf_ = t.float()
+                return (tf_ * torch.rsqrt(tf_.pow(2).mean(-1, keepdim=True) + cfg.layernorm_epsilon)).to(t.dtype)
+            q, k = unit_rms(q), unit_rms(k)
         o = self.core_attention(q, k, v, ctx)                     # [T, nq_local, d]
         o = o.reshape(o.shape[0], -1)
         if gate is not None:

@@ -252,6 +252,7 @@ class Llama4Vit(_PixelTower):
 class Llama4Bridge(_NestedLMBridge):
     hf_mlp_prefix = 'feed_forward'
     hf_gate_key = 'router.weight'
+    hf_shared_expert_prefix = 'shared_expert'
     hf_fused_experts = True
 
 

@@ -203,3 +203,39 @@ def test_internvl_image_prompt_logits_and_roundtrip(tmp_path):
     assert sorted(b) == sorted(published)
     for k, v in published.items():
         assert torch.equal(b[k], v), k
+
+
+def test_llama4_image_prompt_logits_and_roundtrip(tmp_path):
+    """Llama-4: interleaved rope with a NoPE layer, weight-less RMS on q / k of the rotating layers, sigmoid top-1
+    routing applied on the expert input, shared expert, fused expert tensors; vision tower through pixel shuffle."""
+    from transformers import AutoConfig, Llama4Config, Llama4ForConditionalGeneration
+    torch.manual_seed(0)
+    c = Llama4Config(
+        text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=64, intermediate_size_mlp=256,
+                         num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                         num_local_experts=4, num_experts_per_tok=1, interleave_moe_layer_step=1,
+                         max_position_embeddings=512, tie_word_embeddings=False, attention_chunk_size=8192,
+                         pad_token_id=0),
+        vision_config=dict(hidden_size=64, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                           image_size=32, patch_size=8, num_channels=3, vision_output_dim=64, projector_input_dim=64,
+                           projector_output_dim=64, pixel_shuffle_ratio=0.5),
+        image_token_index=500, boi_token_index=501, eoi_token_index=502, tie_word_embeddings=False)
+    hf = _randomise(Llama4ForConditionalGeneration(c).float().eval())
+    d1, d2 = str(tmp_path / 'a'), str(tmp_path / 'b')
+    hf.save_pretrained(d1)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(1, 400, (1, 32), generator=g)
+    ids[0, 4:8] = 500
+    pixels = torch.randn(1, 3, 32, 32, generator=g)
+    with torch.no_grad():
+        ref = hf(input_ids=ids, pixel_values=pixels).logits
+    cfg = ModelConfig(**hf_to_mcore_config(AutoConfig.from_pretrained(d1)), params_dtype=torch.float32)
+    model = get_mcore_model(cfg)[0].eval()
+    cfg.bridge.load_weights([model], d1)
+    with torch.no_grad():
+        assert (model(ids, pixel_values=pixels) - ref).abs().max().item() < 3e-5
+    cfg.bridge.save_weights([model], d2)
+    a, b = load_file(os.path.join(d1, 'model.safetensors')), load_file(os.path.join(d2, 'model.safetensors'))
+    assert sorted(a) == sorted(b)
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
