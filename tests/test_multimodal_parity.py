@@ -109,6 +109,21 @@ def _glm4v():
     return c, Glm4vForConditionalGeneration(c)
 
 
+def _glm4v_moe():
+    from transformers import Glm4vMoeConfig, Glm4vMoeForConditionalGeneration
+    c = Glm4vMoeConfig(
+        text_config=dict(_TEXT, head_dim=32, moe_intermediate_size=64, n_routed_experts=4, num_experts_per_tok=2,
+                         n_shared_experts=1, first_k_dense_replace=1, n_group=1, topk_group=1,
+                         rope_parameters=dict(rope_type='default', rope_theta=10000.0, mrope_section=[2, 3, 3],
+                                              partial_rotary_factor=0.5)),
+        vision_config=dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=4, in_channels=3, patch_size=4,
+                           spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=128, image_size=32),
+        image_token_id=500, video_token_id=501, image_start_token_id=502, image_end_token_id=503,
+        tie_word_embeddings=False)
+    c.vision_start_token_id, c.vision_end_token_id = 502, 503
+    return c, Glm4vMoeForConditionalGeneration(c)
+
+
 def _inputs(c):
     g = torch.Generator().manual_seed(0)
     grid = torch.tensor([[1, 8, 8]])                       # 64 patches -> 16 merged image tokens
@@ -122,7 +137,7 @@ def _inputs(c):
     return ids, pixels, grid
 
 
-@pytest.mark.parametrize('build', [_qwen3_vl, _qwen2_5_vl, _qwen3_5, _qwen2_vl, _qwen3_vl_moe, _glm4v])
+@pytest.mark.parametrize('build', [_qwen3_vl, _qwen2_5_vl, _qwen3_5, _qwen2_vl, _qwen3_vl_moe, _glm4v, _glm4v_moe])
 def test_image_prompt_logits_and_roundtrip(build, tmp_path):
     torch.manual_seed(0)
     c, hf = build()
