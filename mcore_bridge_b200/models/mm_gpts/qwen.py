@@ -213,8 +213,11 @@ class Qwen3_5Vit(HuggingFaceVit):
     _aligner = ['visual.merger']
 
     def prepare_model(self, hf_config):
-        from transformers.models.qwen3_5 import Qwen3_5VisionModel
-        self.visual = Qwen3_5VisionModel._from_config(hf_config.vision_config)
+        if self.config.hf_model_type == 'qwen3_5_moe':      # its vision config belongs to the MoE model's own tower class
+            from transformers.models.qwen3_5_moe import Qwen3_5MoeVisionModel as VisionModel
+        else:
+            from transformers.models.qwen3_5 import Qwen3_5VisionModel as VisionModel
+        self.visual = VisionModel._from_config(hf_config.vision_config)
 
     def get_inputs_embeds(self, inputs_embeds, **inputs):
         return self.merge_media(inputs_embeds, inputs, self.visual, self.hf_config)
@@ -222,6 +225,7 @@ class Qwen3_5Vit(HuggingFaceVit):
 
 class Qwen3_5Bridge(MultimodalGPTBridge):
     split_gdn_projections = True     # in_proj_qkv / in_proj_z / in_proj_b / in_proj_a are separate tensors
+    hf_fused_experts = True          # the MoE variant stores ``experts.gate_up_proj`` / ``experts.down_proj``
 
 
 register_model(ModelMeta(ModelType.qwen3_5, ['qwen3_5', 'qwen3_5_moe'], bridge_cls=Qwen3_5Bridge,

@@ -109,6 +109,21 @@ def _glm4v():
     return c, Glm4vForConditionalGeneration(c)
 
 
+def _qwen3_5_moe():
+    from transformers import Qwen3_5MoeConfig, Qwen3_5MoeForConditionalGeneration
+    c = Qwen3_5MoeConfig(
+        text_config=dict(_TEXT, num_hidden_layers=4, head_dim=32, moe_intermediate_size=64,
+                         shared_expert_intermediate_size=64, num_experts=4, num_experts_per_tok=2,
+                         linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=16,
+                         linear_value_head_dim=16, linear_conv_kernel_dim=4, full_attention_interval=4,
+                         rope_parameters=dict(rope_type='default', rope_theta=10000.0, mrope_section=[2, 1, 1],
+                                              mrope_interleaved=True, partial_rotary_factor=0.25)),
+        vision_config=dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=4, in_channels=3, patch_size=4,
+                           spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=128,
+                           num_position_embeddings=64), **_TOKENS)
+    return c, Qwen3_5MoeForConditionalGeneration(c)
+
+
 def _glm4v_moe():
     from transformers import Glm4vMoeConfig, Glm4vMoeForConditionalGeneration
     c = Glm4vMoeConfig(
@@ -137,13 +152,13 @@ def _inputs(c):
     return ids, pixels, grid
 
 
-@pytest.mark.parametrize('build', [_qwen3_vl, _qwen2_5_vl, _qwen3_5, _qwen2_vl, _qwen3_vl_moe, _glm4v, _glm4v_moe])
+@pytest.mark.parametrize('build', [_qwen3_vl, _qwen2_5_vl, _qwen3_5, _qwen2_vl, _qwen3_vl_moe, _glm4v, _glm4v_moe, _qwen3_5_moe])
 def test_image_prompt_logits_and_roundtrip(build, tmp_path):
     torch.manual_seed(0)
     c, hf = build()
     hf = _randomise(hf.float().eval())
     d1, d2 = str(tmp_path / 'a'), str(tmp_path / 'b')
-    if build is _qwen3_5:
+    if build in (_qwen3_5, _qwen3_5_moe):
         # this Transformers version re-prefixes the language-model keys on save for this family; write the state
         # dict as it is in memory (the published layout) instead
         from safetensors.torch import save_file
