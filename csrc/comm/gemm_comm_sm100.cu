@@ -6,9 +6,9 @@
 //       consume remote blocks in arrival order, so the transfer hides behind the math tile by tile.
 //
 //   GEMM -> reduce-scatter   out[M/w, N] = sum_ranks (A . B^T)[rows of this rank]   (row-parallel fwd, column dgrad)
-//       Each epilogue stores its bf16 partial tile straight into the staging buffer of the rank that owns the
-//       rows (peer stores over NVLink) and bumps a counter there; when a CTA runs out of tiles it turns to
-//       reducing the rows this rank owns as their counters fill.
+//       Each epilogue warp pushes its part of a bf16 partial tile straight into the staging buffer of the rank
+//       that owns the rows (contiguous 4 KiB bulk copies over NVLink) and bumps a counter there; a few CTAs of the
+//       same launch sum the rows this rank owns, row block by row block, as their counters fill.
 //
 // No TMA multicast anywhere; remote data is only touched by plain bulk copies, ld/st and red.
 // Every cross-rank wait is bounded and reports through the status word.
@@ -49,16 +49,13 @@ struct CommGemmParams {
   void* out;
   long long ld_out;
   int* status;
-  int debug;  // timing experiments only (MCB200_RS_DEBUG): 1 skip reduce phase, 2 push to self, 4 skip stores
+  int reduce_ctas;  // GEMM -> RS: CTAs at the end of the grid that only sum staged partial tiles
 };
 
-// GEMM -> reduce-scatter: one TMA store descriptor per destination rank's staging buffer, viewed as
-// [world * rows_per_rank, N] bf16 with 128-byte swizzled 64-column boxes
-struct RsMaps {
-  CUtensorMap stage[MAX_WORLD];
-};
 constexpr int RS_SLAB_COLS = 64;
-constexpr int RS_SLAB_BYTES = GEMM_BM * RS_SLAB_COLS * 2;  // 16 KiB
+constexpr int RS_SLAB_BYTES = GEMM_BM * RS_SLAB_COLS * 2;  // 16 KiB: 128 rows x 64 bf16 columns
+constexpr int RS_TILE_BYTES = 4 * RS_SLAB_BYTES;           // 64 KiB: one 128 x 256 partial tile
+constexpr int RS_WARP_BYTES = 32 * RS_SLAB_COLS * 2;       // 4 KiB: the 32 rows of one epilogue warp in a slab
 
 struct CommSched {
   int tiles_m, tiles_n, total, bps, BN, world, rank, first_step;
@@ -399,226 +396,267 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_co
 // ----------------------------------------------------------------------------------------------------------
 // GEMM -> reduce-scatter
 // ----------------------------------------------------------------------------------------------------------
+// Staging layout (the owner's buffer, one half per epoch parity): tile-major, each 128x256 partial tile stored as
+// four 16 KiB slabs of 64 columns in the 128-byte-swizzled order the epilogue wrote them to shared memory,
+//     offset = ((source_rank * bps + row_block) * tiles_n + tile_n) * 64 KiB + slab * 16 KiB + row * 128 + swizzled chunk.
+// A slab quarter (the 32 rows of one epilogue warp) is 4 KiB contiguous both in shared memory and at the owner, so
+// each warp pushes it with one plain bulk copy: long contiguous NVLink writes, no tensor map, no CTA-wide barrier.
+// Because the sum over sources is element-wise, the reducer adds the staged tiles in that order and un-swizzles only
+// the output address.
+//
+// Tile order is row-block-major: for each row block, every destination rank in turn (own rows last), every column
+// tile.  A row block of the owner is therefore complete once every source is 1/bps of the way through its tiles,
+// and the last `reduce_ctas` CTAs of the grid sum finished row blocks while the others are still pushing.
+struct RsSched {
+  int tiles_n, total, bps, world, rank, BN;
+  __device__ RsSched(const CommGemmParams& p, int bn) : world(p.world), rank(p.rank), BN(bn) {
+    tiles_n = (p.N + bn - 1) / bn;
+    bps = p.rows_per_rank / GEMM_BM;
+    total = bps * world * tiles_n;
+  }
+  __device__ void get(int t, int& shard, int& blk, int& tn) const {
+    const int per_blk = world * tiles_n;
+    blk = t / per_blk;
+    const int r = t - blk * per_blk;
+    const int step = r / tiles_n;
+    tn = r - step * tiles_n;
+    shard = (rank + 1 + step) % world;
+  }
+};
+
+// Sums POS x 192 staged 16-byte positions of one row block over SRC (>= world) sources and writes bf16 rows.
+template <int SRC>
+__device__ __forceinline__ void rs_reduce_chunk(const CommGemmParams& p, const uint8_t* stage, int blk, int bps, int tiles_n,
+                                                long long pos0, long long npos_blk) {
+  constexpr int POS = 32 / SRC;
+  const long long src_stride = (long long)bps * tiles_n * RS_TILE_BYTES;
+  const uint8_t* base = stage + (long long)blk * tiles_n * RS_TILE_BYTES;
+  uint4 raw[POS][SRC];
+#pragma unroll
+  for (int u = 0; u < POS; ++u) {
+    const long long pos = pos0 + u * GEMM_THREADS + threadIdx.x;
+#pragma unroll
+    for (int s = 0; s < SRC; ++s) {
+      if (pos < npos_blk && s < p.world)
+        raw[u][s] = __ldcs(reinterpret_cast<const uint4*>(base + s * src_stride + pos * 16));
+      else
+        raw[u][s] = make_uint4(0, 0, 0, 0);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < POS; ++u) {
+    const long long pos = pos0 + u * GEMM_THREADS + threadIdx.x;
+    if (pos >= npos_blk) continue;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int s = 0; s < SRC; ++s) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][s]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    const int tn = (int)(pos >> 12);            // 4096 positions per tile
+    const int i = (int)(pos & 4095);
+    const int slab = i >> 10, w = i & 1023;     // 1024 positions per slab, 8 per row
+    const int r = w >> 3;
+    const int c = (w & 7) ^ (r & 7);            // undo the 128-byte swizzle
+    const int col = tn * 256 + slab * RS_SLAB_COLS + c * 8;
+    if (col < p.N) {
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((long long)blk * GEMM_BM + r) * p.ld_out;
+      *reinterpret_cast<uint4*>(orow + col) = o;
+    }
+  }
+}
+
 template <int BN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ RsMaps maps, const CommGemmParams p) {
+               const CommGemmParams p) {
+  static_assert(BN == 256, "the staging layout assumes 256-column tiles");
   constexpr uint32_t TMEM_COLS = 2 * BN;
   extern __shared__ uint8_t smem_raw[];
   if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;  // an earlier wait gave up: do not pile up
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint32_t* lflags = p.peer_flags[p.rank];
   const uint32_t epoch = (uint32_t)p.epoch;
-  const int bps = p.rows_per_rank / GEMM_BM;
   const int parity = p.epoch & 1;
+  RsSched sched(p, BN);
+  const int bps = sched.bps;
+  const int gemm_ctas = (int)gridDim.x - p.reduce_ctas;
   Pipe<BN> P(smem_raw);
-  if (threadIdx.x == 0) {
-    P.init();
-    prefetch_tensormap(&tmap_a);
-    prefetch_tensormap(&tmap_b);
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(P.tmem_slot), TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *P.tmem_slot;
-  CommSched sched(p, BN, 1);  // start with the rows of rank+1, finish with our own
+  const bool reducer = (int)blockIdx.x >= gemm_ctas;
 
-  if (warp == 0) {
-    if (lane == 0) {
-      uint32_t it = 0;
-      for (int t = blockIdx.x; t < sched.total; t += gridDim.x) {
-        int shard, blk, n0, step;
-        sched.get(t, shard, blk, n0, step);
-        if (!load_tile<BN, B_MN>(P, &tmap_a, &tmap_b, (shard * bps + blk) * GEMM_BM, n0, p.K, it, p.status)) break;
-      }
-      drain_loads<BN>(P, it);
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      uint32_t it = 0, lt = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x, ++lt) {
-        const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
-        if (!mbar_wait(smem_u32(&P.tempty_bar[acc]), aph ^ 1, P.abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
-        tc_fence_after();
-        issue_mma_tile<BN, B_MN>(P, tmem_base + acc * BN, p.K, it, p.status, ok);
-        if (ok) umma_commit(smem_u32(&P.tfull_bar[acc]));
-      }
-    }
-  } else {
-    // Epilogue: TMEM -> registers -> bf16 -> 128B-swizzled shared slab -> TMA store into the owner's staging
-    // buffer (coalesced NVLink writes).  A tile's counter is bumped one tile late, after the bulk stores that
-    // carried it are known to be complete, so the completion latency hides behind the next tile.
-    const int q = warp & 3;
-    const bool issuer = (warp == 2 && lane == 0);
-    uint8_t* slab_base = P.smem + GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + 1024;
-    uint32_t lt = 0;
-    uint32_t verified = 0;  // bit s: rank s has released the staging half we are about to write
-    int pend_shard = -1, pend_blk = 0;  // tile whose counter increment is still owed
-    uint32_t slab_ctr = 0;
-    for (int t = blockIdx.x; t < sched.total; t += gridDim.x, ++lt) {
-      int shard, blk, n0, step;
-      sched.get(t, shard, blk, n0, step);
-      const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
-      if (!mbar_wait(smem_u32(&P.tfull_bar[acc]), aph, P.abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
-      tc_fence_after();
-      if (!(verified & (1u << shard))) {
-        // the owner must have finished reducing the call that last used this staging half (two calls ago)
-        if (p.epoch > 2 && shard != p.rank) {
-          if (!wait_flag<SCOPE_SYS>(lflags + F_DONE + shard, epoch - 2, false, P.abort_flag, p.status)) break;
-        }
-        verified |= 1u << shard;
-      }
-      const int srow0 = p.rank * p.rows_per_rank + blk * GEMM_BM;  // row of this tile in the owner's staging view
-      const int r_local = q * 32 + lane;
-      int slabs_issued = 0;
-#pragma unroll 1
-      for (int cc = 0; cc < BN; cc += RS_SLAB_COLS, ++slab_ctr) {
-        if (n0 + cc >= p.N) break;
-        uint8_t* slab = slab_base + (slab_ctr & 1) * RS_SLAB_BYTES;
-        if (issuer) tma_store_wait_read<1>();  // the store that last used this slab has finished reading it
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-        for (int h = 0; h < RS_SLAB_COLS / 32; ++h) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + cc + h * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-            o.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            o.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-            o.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-            const int chunk = (h * 32 + j) >> 3;                 // 16-byte chunk inside the 128-byte row
-            const int sw = chunk ^ (r_local & 7);                // 128-byte swizzle
-            *reinterpret_cast<uint4*>(slab + r_local * 128 + sw * 16) = o;
-          }
-        }
-        if (cc + RS_SLAB_COLS >= BN || n0 + cc + RS_SLAB_COLS >= p.N) {
-          // last slab of the tile: the accumulator can go back to the MMA warp
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&P.tempty_bar[acc]));
-        }
-        fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (issuer) {
-          if (!(p.debug & 4)) tma_store_2d(&maps.stage[(p.debug & 2) ? p.rank : shard], smem_u32(slab), n0 + cc, srow0);
-          tma_store_commit();
-        }
-        ++slabs_issued;
-      }
-      if (issuer) {
-        if (pend_shard >= 0) {
-          // everything but this tile's stores is complete -> the previous tile may be published
-          if (slabs_issued >= 4) tma_store_wait<4>();
-          else if (slabs_issued == 3) tma_store_wait<3>();
-          else if (slabs_issued == 2) tma_store_wait<2>();
-          else tma_store_wait<1>();
-          fence_proxy_async_all();
-          fence_acq_rel_sys();
-          red_release_sys_add(p.peer_flags[pend_shard] + F_CNT + parity * F_CNT_STRIDE + pend_blk, 1u);
-        }
-        pend_shard = shard;
-        pend_blk = blk;
-      }
-    }
-    if (issuer) {
-      tma_store_wait<0>();
-      if (pend_shard >= 0) {
-        fence_proxy_async_all();
-        fence_acq_rel_sys();
-        red_release_sys_add(p.peer_flags[pend_shard] + F_CNT + parity * F_CNT_STRIDE + pend_blk, 1u);
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
-  }
-
-  // ------------------------------------------------------------------ reduce the rows this rank owns
-  if (!*P.abort_flag && !(p.debug & 1)) {
-    const uint32_t want = (uint32_t)(p.world * sched.tiles_n);
-    const int nwarps = GEMM_THREADS / 32;
-    const int segs = (p.N + 1023) / 1024;               // a warp iteration covers one row x 1024 columns
-    const long long units = (long long)p.rows_per_rank * segs;
-    const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.peer_stage[p.rank]);
+  if (reducer) {
+    // ================================================================= reducer CTA: sum the rows this rank owns
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) *P.abort_flag = 0;
+    __syncthreads();
+    const uint32_t want = (uint32_t)(p.world * sched.tiles_n * 4);  // one increment per epilogue warp per tile
+    const long long npos_blk = (long long)sched.tiles_n * (RS_TILE_BYTES / 16);
+    const int src_lanes = p.world <= 2 ? 2 : (p.world <= 4 ? 4 : 8);
+    const int chunk = GEMM_THREADS * (32 / src_lanes);
+    const int cpb = (int)((npos_blk + chunk - 1) / chunk);
+    const uint8_t* stage = reinterpret_cast<const uint8_t*>(p.peer_stage[p.rank]);
     int ready_blk = -1;
-    bool ok = true;
-    // blocks are walked in order, so early blocks (pushed first by every peer) are reduced while late ones land
-    for (long long u = (long long)blockIdx.x * nwarps + warp; u < units && ok; u += (long long)gridDim.x * nwarps) {
-      const long long row = u / segs;
-      const int seg = (int)(u - row * segs);
-      const int blk = (int)(row / GEMM_BM);
+    for (long long g = (int)blockIdx.x - gemm_ctas; g < (long long)bps * cpb; g += p.reduce_ctas) {
+      const int blk = (int)(g / cpb);
+      const long long pos0 = (g - (long long)blk * cpb) * chunk;
       if (blk != ready_blk) {
-        int good = 1;
-        if (lane == 0)
-          good = wait_flag<SCOPE_SYS>(lflags + F_CNT + parity * F_CNT_STRIDE + blk, want, true, P.abort_flag, p.status);
-        good = __shfl_sync(0xffffffffu, good, 0);
-        if (!good) {
-          ok = false;
-          break;
-        }
+        if (threadIdx.x == 0)
+          s_ok = wait_flag<SCOPE_SYS>(lflags + F_CNT + parity * F_CNT_STRIDE + blk, want, false, P.abort_flag, p.status);
+        __syncthreads();
+        const int ok = s_ok;
+        __syncthreads();
+        if (!ok) break;
         ready_blk = blk;
       }
-      float acc[4][8];
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
-      const int c0 = seg * 1024 + lane * 8;
-      for (int s0 = 0; s0 < p.world; s0 += 4) {
-        uint4 raw[4][4];
-#pragma unroll
-        for (int ss = 0; ss < 4; ++ss) {
-          const int src = s0 + ss;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int c = c0 + k * 256;
-            if (src < p.world && c < p.N)
-              raw[ss][k] = __ldcs(reinterpret_cast<const uint4*>(stage + ((long long)src * p.rows_per_rank + row) * p.N + c));
-            else
-              raw[ss][k] = make_uint4(0, 0, 0, 0);
-          }
+      if (src_lanes == 2) rs_reduce_chunk<2>(p, stage, blk, bps, sched.tiles_n, pos0, npos_blk);
+      else if (src_lanes == 4) rs_reduce_chunk<4>(p, stage, blk, bps, sched.tiles_n, pos0, npos_blk);
+      else rs_reduce_chunk<8>(p, stage, blk, bps, sched.tiles_n, pos0, npos_blk);
+    }
+  } else {
+    // ================================================================= GEMM CTA
+    if (threadIdx.x == 0) {
+      P.init();
+      prefetch_tensormap(&tmap_a);
+      prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+      tmem_alloc(smem_u32(P.tmem_slot), TMEM_COLS);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *P.tmem_slot;
+
+    if (warp == 0) {
+      if (lane == 0) {
+        uint32_t it = 0;
+        for (int t = blockIdx.x; t < sched.total; t += gemm_ctas) {
+          int shard, blk, tn;
+          sched.get(t, shard, blk, tn);
+          if (!load_tile<BN, B_MN>(P, &tmap_a, &tmap_b, (shard * bps + blk) * GEMM_BM, tn * BN, p.K, it, p.status)) break;
         }
-#pragma unroll
-        for (int ss = 0; ss < 4; ++ss)
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[ss][k]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float2 f = __bfloat1622float2(h[e]);
-              acc[k][2 * e] += f.x;
-              acc[k][2 * e + 1] += f.y;
-            }
-          }
+        drain_loads<BN>(P, it);
       }
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ld_out;
+    } else if (warp == 1) {
+      if (lane == 0) {
+        uint32_t it = 0, lt = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < sched.total && ok; t += gemm_ctas, ++lt) {
+          const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+          if (!mbar_wait(smem_u32(&P.tempty_bar[acc]), aph ^ 1, P.abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+          tc_fence_after();
+          issue_mma_tile<BN, B_MN>(P, tmem_base + acc * BN, p.K, it, p.status, ok);
+          if (ok) umma_commit(smem_u32(&P.tfull_bar[acc]));
+        }
+      }
+    } else {
+      // Epilogue, one independent pipeline per warp: TMEM -> registers -> bf16 -> this warp's 4 KiB swizzled buffer
+      // (two of them, used alternately) -> bulk copy into the owner's staging tile.  A tile's counter is bumped one
+      // tile late, once the copies that carried it are known to be complete, so that latency hides behind the
+      // next tile.
+      const int q = warp & 3;
+      uint8_t* wbuf = P.smem + GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + 1024 + q * (2 * RS_WARP_BYTES);
+      uint32_t lt = 0, sctr = 0;
+      uint32_t verified = 0;       // bit s: rank s has released the staging half we are about to write
+      uint32_t* pend_cnt = nullptr;  // counter of the tile whose increment is still owed
+      for (int t = blockIdx.x; t < sched.total; t += gemm_ctas, ++lt) {
+        int shard, blk, tn;
+        sched.get(t, shard, blk, tn);
+        const int n0 = tn * BN;
+        const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+        if (!mbar_wait(smem_u32(&P.tfull_bar[acc]), aph, P.abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+        tc_fence_after();
+        if (!(verified & (1u << shard))) {
+          // the owner must have finished reducing the call that last used this staging half (two calls ago)
+          if (p.epoch > 2 && shard != p.rank) {
+            int good = 1;
+            if (lane == 0) good = wait_flag<SCOPE_SYS>(lflags + F_DONE + shard, epoch - 2, false, P.abort_flag, p.status);
+            good = __shfl_sync(0xffffffffu, good, 0);
+            if (!good) break;
+          }
+          verified |= 1u << shard;
+        }
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer_stage[shard]) +
+                       ((long long)(p.rank * bps + blk) * sched.tiles_n + tn) * RS_TILE_BYTES + q * RS_WARP_BYTES;
+        int issued = 0;
+#pragma unroll 1
+        for (int cc = 0; cc < BN; cc += RS_SLAB_COLS, ++sctr) {
+          if (n0 + cc >= p.N) break;
+          uint8_t* buf = wbuf + (sctr & 1) * RS_WARP_BYTES;
+          if (lane == 0) tma_store_wait_read<1>();  // the copy that last used this buffer has finished reading it
+          __syncwarp();
+          uint32_t r[64];
+          tmem_ld_32x32_x64(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + cc, r);
+          tmem_ld_wait();
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int c = c0 + k * 256;
-        if (c < p.N) {
-          uint4 o;
-          o.x = pack_bf16x2(acc[k][0], acc[k][1]);
-          o.y = pack_bf16x2(acc[k][2], acc[k][3]);
-          o.z = pack_bf16x2(acc[k][4], acc[k][5]);
-          o.w = pack_bf16x2(acc[k][6], acc[k][7]);
-          *reinterpret_cast<uint4*>(orow + c) = o;
+          for (int j = 0; j < 8; ++j) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;  // 128-byte swizzle
+          }
+          if (cc + RS_SLAB_COLS >= BN || n0 + cc + RS_SLAB_COLS >= p.N) {
+            // last slab of the tile: the accumulator can go back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&P.tempty_bar[acc]));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            bulk_store_1d(dst + (cc / RS_SLAB_COLS) * RS_SLAB_BYTES, smem_u32(buf), RS_WARP_BYTES);
+            tma_store_commit();
+          }
+          ++issued;
+        }
+        if (lane == 0) {
+          if (pend_cnt) {
+            // everything but this tile's copies is complete -> the previous tile may be published
+            if (issued >= 4) tma_store_wait<4>();
+            else if (issued == 3) tma_store_wait<3>();
+            else if (issued == 2) tma_store_wait<2>();
+            else tma_store_wait<1>();
+            fence_proxy_async_all();
+            fence_acq_rel_sys();
+            red_release_sys_add(pend_cnt, 1u);
+          }
+          pend_cnt = p.peer_flags[shard] + F_CNT + parity * F_CNT_STRIDE + blk;
+        }
+      }
+      if (lane == 0) {
+        tma_store_wait<0>();  // also on the give-up paths: the buffers must outlive the copies reading them
+        if (pend_cnt && !*P.abort_flag) {
+          fence_proxy_async_all();
+          fence_acq_rel_sys();
+          red_release_sys_add(pend_cnt, 1u);
         }
       }
     }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+      tc_fence_after();
+      tmem_dealloc(tmem_base, TMEM_COLS);
+    }
   }
+
   __syncthreads();
-  // the last CTA to get here resets the counters of this parity and tells every peer we are done
+  // the last CTA to get here resets the counters of this parity and tells every peer that this rank is done reading
   if (threadIdx.x == 0) {
     __threadfence();
     const uint32_t ticket = atomicAdd(lflags + F_TICKET, 1u);
@@ -693,15 +731,35 @@ int mcb_ag_gemm_bf16(const void* const* shard_ptrs, void* const* flag_ptrs, void
   return (int)cudaGetLastError();
 }
 
+// Bytes of one staging half that a call with these sizes writes on every rank (tile-major, 64 KiB per tile).
+long long mcb_gemm_rs_stage_bytes(int M, int N) {
+  return (long long)(M / GEMM_BM) * ((N + 255) / 256) * RS_TILE_BYTES;
+}
+
 int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_inner, long long b_outer, long long ldb,
                      int b_mn, void* const* stage_ptrs, void* const* flag_ptrs, void* out, long long ld_out, int M, int N,
-                     int K, int world, int rank, int epoch, int* status, void* stream_) {
+                     int K, int world, int rank, int epoch, int reduce_ctas, int* status, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  if (world < 2 || world > MAX_WORLD || M % (world * GEMM_BM) || K % 8 || N % 8 || lda % 8) return -2;
+  if (world < 2 || world > MAX_WORLD || M % (world * GEMM_BM) || K % 8 || N % 8 || lda % 8 || ld_out % 8) return -2;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) != 0) return -2;
   const int rows = M / world;
   if (rows / GEMM_BM > F_CNT_STRIDE) return -3;
   constexpr int BN = 256;
-  int sms = device_sm_count();
+  const int sms = device_sm_count();
+  const long long tiles = (long long)(M / GEMM_BM) * ((N + BN - 1) / BN);
+  if (reduce_ctas <= 0) {
+    // balance the two roles: a reducer CTA streams ~60 GB/s of staged partials, a GEMM CTA sustains ~9.5 TFLOP/s
+    const double bytes = (double)M * N * 2.0, flops = 2.0 * M * (double)N * K;
+    double best = 1e30;
+    int best_r = 16;
+    for (int r = 8; r <= 40; r += 4) {
+      const double t_red = bytes / (60e9 * r), t_gemm = flops / (9.5e12 * (sms - r));
+      const double t = t_red > t_gemm ? t_red : t_gemm;
+      if (t < best) { best = t; best_r = r; }
+    }
+    reduce_ctas = best_r;
+  }
+  if (reduce_ctas >= sms) return -4;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, GEMM_BK, GEMM_BM);
   if (rc) return rc;
@@ -710,27 +768,24 @@ int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_in
   if (rc) return rc;
   CommGemmParams p{};
   p.M = M; p.N = N; p.K = K; p.world = world; p.rank = rank; p.epoch = epoch; p.rows_per_rank = rows;
-  RsMaps maps;
+  p.reduce_ctas = reduce_ctas;
   for (int i = 0; i < world; ++i) {
     p.peer_stage[i] = stage_ptrs[i];
     p.peer_flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
-    rc = make_tmap_2d_bf16(&maps.stage[i], stage_ptrs[i], N, (long long)M, N, RS_SLAB_COLS, GEMM_BM);
-    if (rc) return rc;
   }
-  for (int i = world; i < MAX_WORLD; ++i) maps.stage[i] = maps.stage[0];
   p.out = out; p.ld_out = ld_out; p.status = status;
-  { const char* d = getenv("MCB200_RS_DEBUG"); p.debug = d ? atoi(d) : 0; }
-  const int smem = GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + 1024 + 2 * RS_SLAB_BYTES + 1024;
-  long long tiles = (long long)(M / GEMM_BM) * ((N + BN - 1) / BN);
-  int grid = (int)(tiles < sms ? tiles : sms);
+  // pipeline stages + barriers + two 4 KiB copy buffers per epilogue warp (+ alignment slack)
+  const int smem = GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + 1024 + 4 * 2 * RS_WARP_BYTES + 1024;
+  const int gemm_ctas = (int)(tiles < sms - reduce_ctas ? tiles : sms - reduce_ctas);
+  const int grid = gemm_ctas + reduce_ctas;
   static bool cfg[2] = {false, false};
   cudaError_t e;
   if (b_mn) {
     if (!cfg[1]) { if ((e = set_smem(gemm_rs_kernel<BN, true>, smem)) != cudaSuccess) return (int)e; cfg[1] = true; }
-    gemm_rs_kernel<BN, true><<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, maps, p);
+    gemm_rs_kernel<BN, true><<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
   } else {
     if (!cfg[0]) { if ((e = set_smem(gemm_rs_kernel<BN, false>, smem)) != cudaSuccess) return (int)e; cfg[0] = true; }
-    gemm_rs_kernel<BN, false><<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, maps, p);
+    gemm_rs_kernel<BN, false><<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
   }
   return (int)cudaGetLastError();
 }

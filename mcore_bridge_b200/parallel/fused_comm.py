@@ -26,6 +26,7 @@ FLAG_BYTES = 65536
 _c_ll, _c_int = ctypes.c_longlong, ctypes.c_int
 _ptr_cache: Dict[Tuple, ctypes.Array] = {}
 COPY_CTAS = int(os.environ.get('MCB200_AG_COPY_CTAS', '0'))  # 0: the launcher balances copy vs GEMM CTAs
+REDUCE_CTAS = int(os.environ.get('MCB200_RS_REDUCE_CTAS', '0'))  # 0: the launcher balances reducer vs GEMM CTAs
 
 
 def _on() -> bool:
@@ -121,14 +122,15 @@ def _rs(a2: torch.Tensor, b: torch.Tensor, b_inner: int, b_outer: int, b_mn: boo
         group_name: str):
     M = a2.shape[0]
     n = ps.get_world_size(group_name)
-    ws, half = _workspace(group_name, 'rs', M * n_out * 2)
+    # staging is tile-major: one 64 KiB slot per 128 x 256 partial tile
+    ws, half = _workspace(group_name, 'rs', (M // 128) * ((n_out + 255) // 256) * 65536)
     epoch = ws.next_epoch()
     off = FLAG_BYTES + (epoch & 1) * half
     out = torch.empty((M // n, n_out), dtype=torch.bfloat16, device=a2.device)
     rc = _lib.lib().mcb_gemm_rs_bf16(
         _lib.ptr(a2), _c_ll(a2.stride(0)), _lib.ptr(b), _c_ll(b_inner), _c_ll(b_outer), _c_ll(b.stride(0)),
         _c_int(int(b_mn)), _ptr_array(ws, off), _ptr_array(ws, 0), _lib.ptr(out), _c_ll(out.stride(0)), _c_int(M),
-        _c_int(n_out), _c_int(k_in), _c_int(ws.world), _c_int(ws.rank), _c_int(epoch),
+        _c_int(n_out), _c_int(k_in), _c_int(ws.world), _c_int(ws.rank), _c_int(epoch), _c_int(REDUCE_CTAS),
         _lib.ptr(_lib.status_word(a2.device)), _lib.stream_ptr())
     _lib.check_rc(rc, 'mcb_gemm_rs_bf16')
     return out

@@ -24,6 +24,16 @@ def test_fused_tp_kernels_two_ranks():
     assert 'ALL OK' in res.stdout
 
 
+@pytest.mark.skipif(_ngpu() < 8, reason='needs 8 GPUs')
+def test_fused_tp_kernels_eight_ranks():
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0')
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', '8', '--master-addr',
+           '127.0.0.1', '--master-port', '29536', os.path.join(HERE, 'multi_gpu_fused_worker.py')]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert 'ALL OK' in res.stdout
+
+
 @pytest.mark.skipif(_ngpu() < 2, reason='needs 2 GPUs')
 def test_fused_moe_expert_parallel_two_ranks():
     env = dict(os.environ, NCCL_NVLS_ENABLE='0')
