@@ -424,42 +424,39 @@ struct RsSched {
   }
 };
 
-// Sums POS x 192 staged 16-byte positions of one row block over SRC (>= world) sources and writes bf16 rows.
+// Reducer pipeline: a stage of the shared-memory ring holds the same RS_PIECE-byte run of one row block from each
+// of SRC (>= world) sources; RS_RED_STAGES stages are in flight as bulk copies while four warps sum and store.
+constexpr int RS_RED_STAGE_BYTES = 32768;
+constexpr int RS_RED_STAGES = 6;
+constexpr int RS_RED_CONSUMERS = 128;  // warps 2..5
+
+// Sums one stage (piece bytes from each of SRC sources, source s at ring offset s * piece) into bf16 output rows.
+// `byte0` is the offset of the piece inside the row block's staged tiles.
 template <int SRC>
-__device__ __forceinline__ void rs_reduce_chunk(const CommGemmParams& p, const uint8_t* stage, int blk, int bps, int tiles_n,
-                                                long long pos0, long long npos_blk) {
-  constexpr int POS = 32 / SRC;
-  const long long src_stride = (long long)bps * tiles_n * RS_TILE_BYTES;
-  const uint8_t* base = stage + (long long)blk * tiles_n * RS_TILE_BYTES;
-  uint4 raw[POS][SRC];
+__device__ __forceinline__ void rs_reduce_stage(const CommGemmParams& p, const uint8_t* st, int blk, long long byte0) {
+  constexpr int PIECE = RS_RED_STAGE_BYTES / SRC;
+  constexpr int POS = PIECE / 16 / RS_RED_CONSUMERS;
+  const int t = threadIdx.x - 64;
 #pragma unroll
   for (int u = 0; u < POS; ++u) {
-    const long long pos = pos0 + u * GEMM_THREADS + threadIdx.x;
-#pragma unroll
-    for (int s = 0; s < SRC; ++s) {
-      if (pos < npos_blk && s < p.world)
-        raw[u][s] = __ldcs(reinterpret_cast<const uint4*>(base + s * src_stride + pos * 16));
-      else
-        raw[u][s] = make_uint4(0, 0, 0, 0);
-    }
-  }
-#pragma unroll
-  for (int u = 0; u < POS; ++u) {
-    const long long pos = pos0 + u * GEMM_THREADS + threadIdx.x;
-    if (pos >= npos_blk) continue;
+    const int w16 = u * RS_RED_CONSUMERS + t;      // 16-byte position inside the piece
     float acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 #pragma unroll
     for (int s = 0; s < SRC; ++s) {
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][s]);
+      if (s < p.world) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(st + s * PIECE + w16 * 16);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(h[e]);
-        acc[2 * e] += f.x;
-        acc[2 * e + 1] += f.y;
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
       }
     }
+    const long long pos = (byte0 >> 4) + w16;
     const int tn = (int)(pos >> 12);            // 4096 positions per tile
     const int i = (int)(pos & 4095);
     const int slab = i >> 10, w = i & 1023;     // 1024 positions per slab, 8 per row
@@ -498,31 +495,74 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   if (reducer) {
     // ================================================================= reducer CTA: sum the rows this rank owns
-    __shared__ int s_ok;
-    if (threadIdx.x == 0) *P.abort_flag = 0;
+    uint8_t* ring = P.smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + RS_RED_STAGES * RS_RED_STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + RS_RED_STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * RS_RED_STAGES);
+    if (threadIdx.x == 0) {
+      *abort_flag = 0;
+      for (int s = 0; s < RS_RED_STAGES; ++s) {
+        mbar_init(smem_u32(&full[s]), 1);
+        mbar_init(smem_u32(&empty[s]), 4);  // one arrive per consumer warp
+      }
+      fence_barrier_init();
+      fence_proxy_async_smem();
+    }
     __syncthreads();
     const uint32_t want = (uint32_t)(p.world * sched.tiles_n * 4);  // one increment per epilogue warp per tile
-    const long long npos_blk = (long long)sched.tiles_n * (RS_TILE_BYTES / 16);
     const int src_lanes = p.world <= 2 ? 2 : (p.world <= 4 ? 4 : 8);
-    const int chunk = GEMM_THREADS * (32 / src_lanes);
-    const int cpb = (int)((npos_blk + chunk - 1) / chunk);
+    const int piece = RS_RED_STAGE_BYTES / src_lanes;
+    const long long blk_bytes = (long long)sched.tiles_n * RS_TILE_BYTES;       // per source and row block
+    const long long src_stride = (long long)bps * blk_bytes;
+    const int upb = (int)(blk_bytes / piece);                                    // units (stages) per row block
+    const long long units = (long long)bps * upb;
     const uint8_t* stage = reinterpret_cast<const uint8_t*>(p.peer_stage[p.rank]);
-    int ready_blk = -1;
-    for (long long g = (int)blockIdx.x - gemm_ctas; g < (long long)bps * cpb; g += p.reduce_ctas) {
-      const int blk = (int)(g / cpb);
-      const long long pos0 = (g - (long long)blk * cpb) * chunk;
-      if (blk != ready_blk) {
-        if (threadIdx.x == 0)
-          s_ok = wait_flag<SCOPE_SYS>(lflags + F_CNT + parity * F_CNT_STRIDE + blk, want, false, P.abort_flag, p.status);
-        __syncthreads();
-        const int ok = s_ok;
-        __syncthreads();
-        if (!ok) break;
-        ready_blk = blk;
+    const int first = (int)blockIdx.x - gemm_ctas;
+    if (warp == 0) {
+      if (lane == 0) {
+        uint32_t it = 0;
+        int ready_blk = -1;
+        for (long long g = first; g < units; g += p.reduce_ctas, ++it) {
+          const int blk = (int)(g / upb);
+          const long long byte0 = (g - (long long)blk * upb) * piece;
+          if (blk != ready_blk) {
+            if (!wait_flag<SCOPE_SYS>(lflags + F_CNT + parity * F_CNT_STRIDE + blk, want, false, abort_flag, p.status)) break;
+            fence_proxy_async_all();  // the bulk copies below must observe what the counter published
+            ready_blk = blk;
+          }
+          const uint32_t stg = it % RS_RED_STAGES, ph = (it / RS_RED_STAGES) & 1;
+          if (!mbar_wait(smem_u32(&empty[stg]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
+          const uint32_t fb = smem_u32(&full[stg]);
+          mbar_expect_tx(fb, (uint32_t)(p.world * piece));
+          for (int s = 0; s < p.world; ++s)
+            bulk_load_1d(smem_u32(ring + stg * RS_RED_STAGE_BYTES + s * piece),
+                         stage + s * src_stride + (long long)blk * blk_bytes + byte0, (uint32_t)piece, fb);
+        }
+        // drain: copies this thread issued must land before the CTA exits
+        const uint32_t lo = it > RS_RED_STAGES ? it - RS_RED_STAGES : 0;
+        for (uint32_t j = lo; j < it; ++j) {
+          const uint32_t stg = j % RS_RED_STAGES, ph = (j / RS_RED_STAGES) & 1;
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(smem_u32(&full[stg]), ph)) {
+            if (globaltimer_ns() - t0 > 200000000ull) break;
+          }
+        }
       }
-      if (src_lanes == 2) rs_reduce_chunk<2>(p, stage, blk, bps, sched.tiles_n, pos0, npos_blk);
-      else if (src_lanes == 4) rs_reduce_chunk<4>(p, stage, blk, bps, sched.tiles_n, pos0, npos_blk);
-      else rs_reduce_chunk<8>(p, stage, blk, bps, sched.tiles_n, pos0, npos_blk);
+    } else if (warp >= 2) {
+      uint32_t it = 0;
+      for (long long g = first; g < units; g += p.reduce_ctas, ++it) {
+        const int blk = (int)(g / upb);
+        const long long byte0 = (g - (long long)blk * upb) * piece;
+        const uint32_t stg = it % RS_RED_STAGES, ph = (it / RS_RED_STAGES) & 1;
+        if (!mbar_wait(smem_u32(&full[stg]), ph, abort_flag, p.status, ST_TIMEOUT_FULL)) break;
+        const uint8_t* st = ring + stg * RS_RED_STAGE_BYTES;
+        if (src_lanes == 2) rs_reduce_stage<2>(p, st, blk, byte0);
+        else if (src_lanes == 4) rs_reduce_stage<4>(p, st, blk, byte0);
+        else rs_reduce_stage<8>(p, st, blk, byte0);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&empty[stg]));
+      }
     }
   } else {
     // ================================================================= GEMM CTA
@@ -748,12 +788,12 @@ int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_in
   const int sms = device_sm_count();
   const long long tiles = (long long)(M / GEMM_BM) * ((N + BN - 1) / BN);
   if (reduce_ctas <= 0) {
-    // balance the two roles: a reducer CTA streams ~60 GB/s of staged partials, a GEMM CTA sustains ~9.5 TFLOP/s
+    // balance the two roles: a reducer CTA streams ~100 GB/s of staged partials, a GEMM CTA sustains ~9.5 TFLOP/s
     const double bytes = (double)M * N * 2.0, flops = 2.0 * M * (double)N * K;
     double best = 1e30;
     int best_r = 16;
-    for (int r = 8; r <= 40; r += 4) {
-      const double t_red = bytes / (60e9 * r), t_gemm = flops / (9.5e12 * (sms - r));
+    for (int r = 4; r <= 40; r += 2) {
+      const double t_red = bytes / (100e9 * r), t_gemm = flops / (9.5e12 * (sms - r));
       const double t = t_red > t_gemm ? t_red : t_gemm;
       if (t < best) { best = t; best_r = r; }
     }

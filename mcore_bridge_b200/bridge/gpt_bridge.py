@@ -82,6 +82,44 @@ def unshard(parts: List[torch.Tensor], tp_dim) -> torch.Tensor:
     return torch.cat(parts, dim=tp_dim)
 
 
+def gdn_in_proj_to_hf(full: torch.Tensor, cfg, split: bool) -> Dict[str, torch.Tensor]:
+    """Rows of the fused gated-DeltaNet input projection (per key-head group ``[q | k | v | z | b | a]``) -> the
+    Hugging Face tensors: ``in_proj_qkvz`` / ``in_proj_ba`` (grouped per key head), or with ``split`` the four flat
+    ``in_proj_qkv`` (``[all q | all k | all v]``) / ``in_proj_z`` / ``in_proj_b`` / ``in_proj_a``.  Only dim 0 is
+    re-laid, so the same mapping serves the weight ``[out, H]`` and a LoRA ``lora_B`` ``[out, r]``."""
+    nk, nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    ratio = nv // nk
+    gq, gba = 2 * dk + 2 * ratio * dv, 2 * ratio
+    tail = full.shape[1:]
+    g = full.reshape(nk, gq + gba, *tail)
+    if not split:
+        return {'in_proj_qkvz': g[:, :gq].reshape(-1, *tail), 'in_proj_ba': g[:, gq:].reshape(-1, *tail)}
+    q, k, v = g[:, :dk], g[:, dk:2 * dk], g[:, 2 * dk:2 * dk + ratio * dv]
+    return {'in_proj_qkv': torch.cat([q.reshape(-1, *tail), k.reshape(-1, *tail), v.reshape(-1, *tail)], 0),
+            'in_proj_z': g[:, 2 * dk + ratio * dv:gq].reshape(-1, *tail),
+            'in_proj_b': g[:, gq:gq + ratio].reshape(-1, *tail),
+            'in_proj_a': g[:, gq + ratio:].reshape(-1, *tail)}
+
+
+def gdn_in_proj_to_mcore(parts: Dict[str, torch.Tensor], cfg, split: bool) -> torch.Tensor:
+    """Inverse of :func:`gdn_in_proj_to_hf`."""
+    nk, nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    ratio = nv // nk
+    gq, gba = 2 * dk + 2 * ratio * dv, 2 * ratio
+    if not split:
+        qkvz, ba = parts['in_proj_qkvz'], parts['in_proj_ba']
+        tail = qkvz.shape[1:]
+        return torch.cat([qkvz.reshape(nk, gq, *tail), ba.reshape(nk, gba, *tail)], dim=1).reshape(-1, *tail)
+    qkv = parts['in_proj_qkv']
+    tail = qkv.shape[1:]
+    pieces = [qkv[:nk * dk].reshape(nk, dk, *tail), qkv[nk * dk:2 * nk * dk].reshape(nk, dk, *tail),
+              qkv[2 * nk * dk:].reshape(nk, ratio * dv, *tail), parts['in_proj_z'].reshape(nk, ratio * dv, *tail),
+              parts['in_proj_b'].reshape(nk, ratio, *tail), parts['in_proj_a'].reshape(nk, ratio, *tail)]
+    return torch.cat(pieces, dim=1).reshape(-1, *tail)
+
+
 class GPTBridge:
     # ---- Hugging Face naming; families override what differs
     hf_layers_prefix = 'model.layers'
@@ -421,39 +459,16 @@ class GPTBridge:
 
         param = attn.in_proj.weight if attn is not None else None
         split = self.split_gdn_projections
+        names = ('in_proj_qkv', 'in_proj_z', 'in_proj_b', 'in_proj_a') if split else ('in_proj_qkvz', 'in_proj_ba')
         if to_mcore:
-            if param is not None and not split:
-                qkvz = self._load_hf(hf_sd, lp + 'in_proj_qkvz.weight')
-                ba = self._load_hf(hf_sd, lp + 'in_proj_ba.weight')
-                H = qkvz.shape[-1]
-                full = torch.cat([qkvz.reshape(nk, gq, H), ba.reshape(nk, gba, H)], dim=1).reshape(-1, H)
-                self._put(param, full, 0)
-            elif param is not None:
-                # Qwen3.5 stores four flat projections: qkv = [all q | all k | all v], z, b, a
-                qkv = self._load_hf(hf_sd, lp + 'in_proj_qkv.weight')
-                H = qkv.shape[-1]
-                parts = [qkv[:nk * dk].reshape(nk, dk, H), qkv[nk * dk:2 * nk * dk].reshape(nk, dk, H),
-                         qkv[2 * nk * dk:].reshape(nk, ratio * dv, H),
-                         self._load_hf(hf_sd, lp + 'in_proj_z.weight').reshape(nk, ratio * dv, H),
-                         self._load_hf(hf_sd, lp + 'in_proj_b.weight').reshape(nk, ratio, H),
-                         self._load_hf(hf_sd, lp + 'in_proj_a.weight').reshape(nk, ratio, H)]
-                self._put(param, torch.cat(parts, dim=1).reshape(-1, H), 0)
+            if param is not None:
+                parts = {n: self._load_hf(hf_sd, f'{lp}{n}.weight') for n in names}
+                self._put(param, gdn_in_proj_to_mcore(parts, cfg, split), 0)
         elif self._agree(param is not None, self._device):
             full = self._get(param, 0)
-            if full is not None and not split:
-                g = full.reshape(nk, gq + gba, full.shape[-1])
-                self._emit(hf_sd, lp + 'in_proj_qkvz.weight', g[:, :gq].reshape(-1, full.shape[-1]))
-                self._emit(hf_sd, lp + 'in_proj_ba.weight', g[:, gq:].reshape(-1, full.shape[-1]))
-            elif full is not None:
-                H = full.shape[-1]
-                g = full.reshape(nk, gq + gba, H)
-                q, k, v = g[:, :dk], g[:, dk:2 * dk], g[:, 2 * dk:2 * dk + ratio * dv]
-                z = g[:, 2 * dk + ratio * dv:gq]
-                self._emit(hf_sd, lp + 'in_proj_qkv.weight',
-                           torch.cat([q.reshape(-1, H), k.reshape(-1, H), v.reshape(-1, H)], 0))
-                self._emit(hf_sd, lp + 'in_proj_z.weight', z.reshape(-1, H))
-                self._emit(hf_sd, lp + 'in_proj_b.weight', g[:, gq:gq + ratio].reshape(-1, H))
-                self._emit(hf_sd, lp + 'in_proj_a.weight', g[:, gq + ratio:].reshape(-1, H))
+            if full is not None:
+                for n, t in gdn_in_proj_to_hf(full, cfg, split).items():
+                    self._emit(hf_sd, f'{lp}{n}.weight', t)
         self._direct(attn, 'conv1d.weight', hf_sd, lp + 'conv1d.weight', to_mcore, tp_dim=0, to_mg=conv_to_mg,
                      to_hf=conv_to_hf)
         self._direct(attn, 'A_log', hf_sd, lp + 'A_log', to_mcore, tp_dim=0)
@@ -870,15 +885,22 @@ class GPTBridge:
                                         tqdm_desc='Saving: '):
             saver.add_tensor(k, v)
         saver.finalize()
+        targets = None
+        if peft_format:
+            # the names are collected over the pipeline group: every rank takes part, only the master writes
+            from .peft_bridge import hf_target_modules
+            targets = hf_target_modules(self, mg_models if isinstance(mg_models, (list, tuple)) else [mg_models],
+                                        adapter_name)
         if is_master():
-            self._save_config(output_dir, peft_format, mg_models, adapter_name)
+            self._save_config(output_dir, peft_format, mg_models, adapter_name, targets)
         if dist.is_available() and dist.is_initialized():
             dist.barrier()
 
-    def _save_config(self, output_dir: str, peft_format: bool, mg_models, adapter_name: str):
+    def _save_config(self, output_dir: str, peft_format: bool, mg_models, adapter_name: str, target_modules=None):
         if peft_format:
             from .peft_bridge import save_adapter_config
-            save_adapter_config(self, mg_models, output_dir, adapter_name)
+            save_adapter_config(self, mg_models if isinstance(mg_models, (list, tuple)) else [mg_models], output_dir,
+                                adapter_name, target_modules)
             return
         hf_config = self.config.hf_config
         if hf_config is not None and hasattr(hf_config, 'save_pretrained'):
