@@ -23,6 +23,7 @@ enum : int {
   ST_TIMEOUT_TMEM_EMPTY = 4,
   ST_TIMEOUT_PEER_FLAG = 5,  // a flag another rank should have written never arrived
   ST_BAD_ARGUMENT = 6,
+  ST_MOE_OVERFLOW = 7,       // routing sent more rows to this rank than its receive buffer holds (largest code)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -265,7 +265,7 @@ __global__ void moe_layout_kernel(CountPtrs table, int world, int rank, int E, i
     acc += (within + PADM - 1) / PADM * PADM;
   }
   seg_off[El] = acc;
-  if (acc > capacity && status) atomicCAS(status, 0, ST_BAD_ARGUMENT);  // receive buffer too small for this routing
+  if (acc > capacity && status) atomicMax(status, ST_MOE_OVERFLOW);  // receive buffer too small for this routing
 }
 
 struct PullArgs {

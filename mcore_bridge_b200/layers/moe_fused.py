@@ -151,10 +151,30 @@ def _buffers(tag, T, H, k, E, cap, device) -> ExchangeBuffers:
     return b
 
 
+_GROWN_FACTOR: Optional[float] = None     # raised by ``grow_capacity`` after an overflow; never shrinks
+
+
+def grow_capacity() -> float:
+    """Doubles the capacity factor used for every later call (the trainer calls this on all ranks after a step in
+    which a rank received more rows than its buffer holds, then repeats the step)."""
+    global _GROWN_FACTOR
+    base = _GROWN_FACTOR or float(os.environ.get('MCB200_MOE_CAPACITY_FACTOR', 2.0))
+    _GROWN_FACTOR = base * 2.0
+    return _GROWN_FACTOR
+
+
 def capacity_rows(T: int, k: int, El: int, world: int, factor: Optional[float]) -> int:
     """Rows of the receive buffer: ``factor`` x the balanced load plus worst-case padding, capped by the true worst
-    case (every copy of every rank lands here)."""
+    case (every copy of every rank lands here).
+
+    The model config's ``moe_expert_capacity_factor`` is normally unset (dropless).  No token is ever dropped here
+    either: the buffer starts at twice the balanced load, and a routing that does not fit raises the overflow
+    status, which suppresses the optimizer update on the device; the trainer then grows the factor and repeats the
+    step (``Trainer.train_step``).  The true worst case is ``world`` x the balanced load, which at 8 ranks would
+    quadruple the activation memory of every MoE layer for a case that near-uniform routing never meets."""
     f = float(os.environ.get('MCB200_MOE_CAPACITY_FACTOR', factor or 2.0))
+    if _GROWN_FACTOR is not None:
+        f = max(f, _GROWN_FACTOR)
     worst = world * T * k
     rows = min(worst, int(f * T * k)) + El * PAD
     return (rows + PAD - 1) // PAD * PAD

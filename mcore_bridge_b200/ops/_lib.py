@@ -22,8 +22,9 @@ LAUNCHES = 0  # kernel launches issued through this library (every op reports ex
 STATUS_NAMES = {
     0: 'ok', 1: 'timeout waiting for a filled smem stage', 2: 'timeout waiting for a free smem stage',
     3: 'timeout waiting for a full TMEM accumulator', 4: 'timeout waiting for a free TMEM accumulator',
-    5: 'timeout waiting for a peer flag', 6: 'bad argument',
+    5: 'timeout waiting for a peer flag', 6: 'bad argument', 7: 'MoE receive buffer too small for this routing',
 }
+ST_MOE_OVERFLOW = 7
 
 
 class KernelError(RuntimeError):

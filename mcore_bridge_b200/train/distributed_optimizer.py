@@ -285,7 +285,9 @@ class DistributedOptimizer:
         self.device = dev
         self._scalars = {True: torch.zeros(8, dtype=torch.float32, device=dev),
                          False: torch.zeros(8, dtype=torch.float32, device=dev)}
-        self._sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        # [0] sum of squared gradients; [1] number of ranks whose kernel status word is raised (both all-reduced)
+        self._sq = torch.zeros(2, dtype=torch.float32, device=dev)
+        self._skip = torch.zeros(1, dtype=torch.int32, device=dev)   # != 0: this step's update is not applied
         self._coef = torch.ones(1, dtype=torch.float32, device=dev)
         self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.grad_norm = self._norm
@@ -305,13 +307,13 @@ class DistributedOptimizer:
         # A shard holds the *sum* of the data-parallel ranks' gradients; the averaging (and any loss scale) is folded
         # into the optimizer kernel's gradient scale.  The norm is that of the gradient the update uses, so every
         # buffer's sum of squares is scaled accordingly (buffers can have different data-parallel sizes: dense vs expert).
-        part = torch.zeros_like(self._sq)
+        part = torch.zeros(1, dtype=torch.float32, device=self._sq.device)
         cur = None
         tied_copy = ps.get_world_size('embd') > 1 and not ps.is_pipeline_first_stage()
 
         def flush():
             if cur is not None:
-                self._sq.add_(part * (self.grad_scale / cur.grad_divisor) ** 2)
+                self._sq[0:1].add_(part * (self.grad_scale / cur.grad_divisor) ** 2)
                 part.zero_()
 
         for buf, b, decay, main, m, v in self.shards:
@@ -337,14 +339,19 @@ class DistributedOptimizer:
             else:
                 part += g.float().pow(2).sum()
         flush()
+        if self._use_cuda():
+            # a raised status word (a bounded wait that gave up, an overflowing MoE receive buffer) on any rank makes
+            # every rank skip the update: the flag rides along with the norm's all-reduce, no host round trip
+            self._sq[1:2].copy_((_lib.status_word(self.device)[0:1] != 0).float())
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(self._sq)  # shards are disjoint across all ranks except the masked replicas
+        self._skip.copy_((self._sq[1:2] > 0).int())
         if self._use_cuda():
             _lib.check_rc(_lib.lib().mcb_clip_coef(_lib.ptr(self._sq), _f(float(self.clip_grad or 0.0)),
                                                    _lib.ptr(self._coef), _lib.ptr(self._norm), _lib.stream_ptr()),
                           'mcb_clip_coef')
         else:
-            self._norm.copy_(self._sq.sqrt())
+            self._norm.copy_(self._sq[0:1].sqrt())
             if self.clip_grad and self.clip_grad > 0:
                 self._coef.copy_(torch.clamp(self.clip_grad / (self._norm + 1e-6), max=1.0))
             else:
@@ -393,7 +400,8 @@ class DistributedOptimizer:
                     sc[7] *= scale_dp
                 rc = _lib.lib().mcb_adam_step(_lib.ptr(g), _lib.ptr(main), _lib.ptr(m), _lib.ptr(v), _lib.ptr(pshard),
                                               _int(int(pshard.dtype == torch.bfloat16)), _ll(main.numel()),
-                                              _lib.ptr(sc), _lib.ptr(self._coef), None, _lib.stream_ptr())
+                                              _lib.ptr(sc), _lib.ptr(self._coef), _lib.ptr(self._skip),
+                                              _lib.stream_ptr())
                 _lib.check_rc(rc, 'mcb_adam_step')
             else:
                 gf = g.float() * (self.grad_scale * scale_dp) * self._coef
@@ -418,6 +426,16 @@ class DistributedOptimizer:
                     dist.all_gather(parts, buf.param_data[s:e].clone(), group=buf.group)
                     full.copy_(torch.cat(parts))
         return self._norm
+
+    def undo_skipped_step(self):
+        """After a step whose update the device-side flag suppressed: take the step count back so the bias corrections
+        of the repeated step are the right ones."""
+        self.step_count -= 1
+
+    @property
+    def skip_flag(self) -> torch.Tensor:
+        """int32[1] on the device: non-zero when the last ``step()`` left parameters and moments untouched."""
+        return self._skip
 
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self) -> dict:

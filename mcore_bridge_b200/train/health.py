@@ -35,11 +35,24 @@ class HeartbeatMonitor:
         except (FileNotFoundError, json.JSONDecodeError):
             return None
 
-    def dead_ranks(self, now: Optional[float] = None) -> List[int]:
+    def dead_ranks(self, now: Optional[float] = None, missing_is_dead: bool = True) -> List[int]:
+        """Ranks whose heartbeat is stale or reports a failure.  A rank that has not written one yet counts as dead
+        unless ``missing_is_dead`` is False (the check at the start of a run, before everybody's first beat)."""
         now = time.time() if now is None else now
         dead = []
         for r in range(self.world):
             hb = self.read(r)
-            if hb is None or now - hb['t'] > self.timeout_s or hb.get('status') != 'ok':
+            if hb is None:
+                if missing_is_dead:
+                    dead.append(r)
+            elif now - hb['t'] > self.timeout_s or hb.get('status') != 'ok':
                 dead.append(r)
         return dead
+
+
+class RankFailure(RuntimeError):
+    """Raised on a surviving rank, on the host and before its next launch, when other ranks stopped beating."""
+
+    def __init__(self, ranks: List[int]):
+        super().__init__(f'ranks {ranks} stopped answering (stale or failed heartbeat)')
+        self.ranks = ranks

@@ -37,6 +37,8 @@ class TrainConfig:
     overlap_grad_reduce: bool = True
     init_seed: Optional[int] = 1234
     init_std: float = 0.02
+    heartbeat_dir: Optional[str] = None    # when set, every step touches this rank's heartbeat file (train/health.py)
+    heartbeat_timeout_s: float = 60.0
 
 
 @torch.no_grad()
@@ -98,6 +100,7 @@ class Trainer:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.last_metrics: Dict[str, float] = {}
+        self._hb = None
 
     # ------------------------------------------------------------------ data movement
     def _to_device(self, mb: Dict) -> Dict:
@@ -151,38 +154,73 @@ class Trainer:
         return loss.detach()
 
     # ------------------------------------------------------------------ the public step
-    def train_step(self, microbatches: Iterable[Dict]) -> float:
-        """Runs one optimizer step over the given host micro-batches and returns the mean loss (host float)."""
-        mbs = list(microbatches)
+    def _forward_backward(self, mbs: List[Dict]) -> torch.Tensor:
         n = len(mbs)
         if ps.get_world_size('pp') > 1:
             from .schedules import forward_backward_pipelining
             total = forward_backward_pipelining(self, mbs)
-        else:
-            self.optimizer.zero_grad()
-            total = torch.zeros((), dtype=torch.float32, device=self.device)
-            nxt = self._prepare(mbs[0])
-            for i in range(n):
-                cur = nxt
-                for m in self.ddp:
-                    m.is_last_microbatch = (i == n - 1)
-                if i + 1 < n:
-                    nxt = self._prepare(mbs[i + 1])  # async H2D of the next micro-batch overlaps this one's compute
-                total += self.forward_backward_microbatch(cur, n)
-        grad_norm = self.optimizer.step()
-        self._after_step()
-        # every rank holds cp x its share of its micro-batches' loss: the mean over the dp x cp group is the step's loss
-        if ps.get_world_size('dp_cp') > 1:
-            dist.all_reduce(total, group=ps.get_group('dp_cp'))
-            total = total / ps.get_world_size('dp_cp')
-        out = torch.stack([total.float(), grad_norm.float().reshape(())])
-        host = out.cpu()                       # the step's device->host read
-        self.d2h_bytes += out.numel() * out.element_size()
-        self.last_metrics = {'loss': float(host[0]), 'grad_norm': float(host[1])}
-        if self.device.type == 'cuda':
+            # only the last stage computed the loss (the others hold zero): give every stage the value
+            dist.all_reduce(total, group=ps.get_group('pp'))
+            return total
+        self.optimizer.zero_grad()
+        total = torch.zeros((), dtype=torch.float32, device=self.device)
+        nxt = self._prepare(mbs[0])
+        for i in range(n):
+            cur = nxt
+            for m in self.ddp:
+                m.is_last_microbatch = (i == n - 1)
+            if i + 1 < n:
+                nxt = self._prepare(mbs[i + 1])  # async H2D of the next micro-batch overlaps this one's compute
+            total += self.forward_backward_microbatch(cur, n)
+        return total
+
+    def train_step(self, microbatches: Iterable[Dict]) -> float:
+        """Runs one optimizer step over the given host micro-batches and returns the mean loss (host float).
+
+        A kernel that reported a problem during the step (status word raised on any rank) makes the optimizer leave
+        the parameters untouched, on the device and without a host round trip; the host learns of it with the loss.
+        An overflowing MoE receive buffer is then handled here: the buffers grow and the step is repeated.  Any other
+        status raises :class:`KernelError` with the weights still those of the previous step."""
+        mbs = list(microbatches)
+        if self.tc.heartbeat_dir:
+            # between steps, nothing of this rank in flight: publish liveness and learn of ranks that stopped, on the
+            # host, before the next launch could wait for them
+            hb = self._heartbeat()
+            hb.beat(self.optimizer.step_count)
+            dead = hb.dead_ranks(missing_is_dead=False)
+            if dead:
+                from .health import RankFailure
+                hb.beat(self.optimizer.step_count, status='peer-failure')
+                raise RankFailure(dead)
+        for attempt in range(4):
+            total = self._forward_backward(mbs)
+            grad_norm = self.optimizer.step()
+            # every rank holds cp x its share of its micro-batches' loss: the mean over the dp x cp group is the step's loss
+            if ps.get_world_size('dp_cp') > 1:
+                dist.all_reduce(total, group=ps.get_group('dp_cp'))
+                total = total / ps.get_world_size('dp_cp')
+            out = torch.stack([total.float(), grad_norm.float().reshape(()),
+                               self.optimizer.skip_flag.float().reshape(())])
+            host = out.cpu()                       # the step's device->host read
+            self.d2h_bytes += out.numel() * out.element_size()
+            if float(host[2]) == 0.0:
+                break
+            # the update was suppressed on every rank
+            self.optimizer.undo_skipped_step()
             from ..ops import _lib
-            if _lib.cuda_enabled():
-                _lib.check_status(self.device)  # a bounded in-kernel wait that gave up surfaces here, every step
+            code = int(_lib.status_word(self.device)[0].item())
+            codes = torch.tensor([code], device=self.device)
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                dist.all_reduce(codes, op=dist.ReduceOp.MAX)          # ST_MOE_OVERFLOW is the largest code
+            if int(codes.item()) != _lib.ST_MOE_OVERFLOW or attempt == 3:
+                _lib.check_status(self.device)     # raises on the rank(s) that hold the status
+                raise _lib.KernelError('another rank reported a kernel status; this step was not applied')
+            from ..layers import moe_fused
+            _lib.status_word(self.device)[0] = 0
+            factor = moe_fused.grow_capacity()
+            logger.warning(f'MoE receive buffer overflowed; capacity factor raised to {factor}, repeating the step')
+        self._after_step()
+        self.last_metrics = {'loss': float(host[0]), 'grad_norm': float(host[1])}
         from ..layers.mtp import get_mtp_losses
         for k, (sm, c) in list(get_mtp_losses().items()):
             self.last_metrics[f'mtp_{k + 1}_loss'] = float(sm) / max(c, 1)
@@ -192,6 +230,14 @@ class Trainer:
             self.last_metrics[k] = float(s) / max(c, 1)
         aux.clear()
         return self.last_metrics['loss']
+
+    def _heartbeat(self):
+        if self._hb is None:
+            from .health import HeartbeatMonitor
+            rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+            world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+            self._hb = HeartbeatMonitor(self.tc.heartbeat_dir, rank, world, self.tc.heartbeat_timeout_s)
+        return self._hb
 
     def _after_step(self):
         if self.config.moe_router_enable_expert_bias:

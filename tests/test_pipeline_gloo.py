@@ -58,6 +58,8 @@ def test_pp2_1f1b_matches_single():
     res = run_ranks(_run, 2, 2, None, 1)
     last = [r for r in res if r[2]][0]
     assert abs(last[0] - base[0]) < 1e-5
+    # every stage reports the step's loss, not only the last one
+    assert all(abs(r[0] - base[0]) < 1e-5 for r in res), [r[0] for r in res]
     merged = {}
     for r in res:
         merged.update(r[1])
