@@ -4,6 +4,7 @@
 
 #include "../common/host_utils.cuh"
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_2cta.cuh"
 
 using namespace mcb;
 
@@ -29,6 +30,37 @@ cudaError_t launch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUte
   if (!a_mn && b_mn) return launch<BN, false, true>(ta, tb, p, grid, s);
   if (a_mn && b_mn) return launch<BN, true, true>(ta, tb, p, grid, s);
   return launch<BN, true, false>(ta, tb, p, grid, s);
+}
+
+template <bool A_MN, bool B_MN>
+cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kern<<<grid, GEMM_THREADS, PAIR_SMEM, stream>>>(ta, tb, p);   // cluster of two CTAs (kernel attribute)
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pair_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                              int grid, cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch_pair<false, false>(ta, tb, p, grid, s);
+  if (!a_mn && b_mn) return launch_pair<false, true>(ta, tb, p, grid, s);
+  if (a_mn && b_mn) return launch_pair<true, true>(ta, tb, p, grid, s);
+  return launch_pair<true, false>(ta, tb, p, grid, s);
+}
+
+constexpr bool PAIR_AUTO = false;
+
+// CTA pairs (256 x 256 tiles) pay off once there are enough tiles to fill the 74 clusters a few times over; small or
+// skinny problems keep the single-CTA tiles, whose narrower variants quantise better.
+bool use_pair(int M, int N, int K, int mode, int sms) {
+  if (!PAIR_AUTO || mode != GEMM_DENSE || M < 512 || N < 256 || K < 128) return false;
+  const long long tiles = (long long)((M + PAIR_BM - 1) / PAIR_BM) * ((N + PAIR_BN - 1) / PAIR_BN);
+  return tiles >= (sms / 2);
 }
 
 int pick_bn(int M, int N, int groups, int sms) {
@@ -70,7 +102,10 @@ int mcb_gemm_bf16(const void* A, long long a_inner, long long a_outer, long long
   int sms = device_sm_count();
   if (max_sms > 0 && max_sms < sms) sms = max_sms;
   int groups = (mode == GEMM_GROUPED_K) ? num_groups : 1;
-  int bn = force_bn > 0 ? force_bn : pick_bn(M, N, groups, sms);
+  // force_bn: 0 = choose; 64 / 128 / 256 = single-CTA tile width; 512 = CTA pairs (256 x 256 per cluster)
+  const bool pair = force_bn == 512 || (force_bn == 0 && use_pair(M, N, K, mode, sms));
+  if (pair && mode != GEMM_DENSE) return -4;
+  int bn = pair ? PAIR_HALF_N : (force_bn > 0 ? force_bn : pick_bn(M, N, groups, sms));
   if (bn != 256 && bn != 128 && bn != 64) return -4;
 
   CUtensorMap ta, tb;
@@ -94,6 +129,11 @@ int mcb_gemm_bf16(const void* A, long long a_inner, long long a_outer, long long
   p.epilogue = EPI_NONE; p.aux = nullptr; p.ld_aux = 0;
   p.status = status;
 
+  if (pair) {
+    const long long ptiles = (long long)((M + PAIR_BM - 1) / PAIR_BM) * ((N + PAIR_BN - 1) / PAIR_BN);
+    const int clusters = (int)(ptiles < sms / 2 ? ptiles : sms / 2);
+    return (int)launch_pair_major(a_mn, b_mn, ta, tb, p, 2 * clusters, stream);
+  }
   long long tiles = (long long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + bn - 1) / bn) * groups;
   int grid = (int)(tiles < sms ? tiles : sms);
   cudaError_t e;

@@ -31,7 +31,7 @@ import torch.distributed as dist
 from torch import nn
 
 from ..parallel import state as ps
-from ..utils.dequantizer import Fp8Dequantizer
+from ..utils.dequantizer import Fp8Dequantizer, add_dequantized_views
 from ..utils.env import is_master
 from ..utils.logger import get_logger
 from ..utils.safetensors import LazyTensor, SafetensorLazyLoader, StreamingSafetensorSaver
@@ -819,6 +819,8 @@ class GPTBridge:
             mg_models = [mg_models]
         with SafetensorLazyLoader(hf_model_dir, peft_format=peft_format) as loader:
             sd = loader.get_state_dict()
+            if not peft_format:
+                sd = add_dequantized_views(sd, self._quantization_config(hf_model_dir), LazyTensor)
             if converter is not None:
                 sd = {k2: v2 for k, v in sd.items() for k2, v2 in self._apply_converter(converter, k, v)}
             if (self.hf_state_dict_mapping or self.hf_load_aliases) and not peft_format:
@@ -830,6 +832,21 @@ class GPTBridge:
                 for _ in self._convert(mg_models, sd, True, tqdm_desc='Loading: '):
                     pass
         self._peft_format = False
+
+    def _quantization_config(self, hf_model_dir: str) -> Optional[dict]:
+        """``quantization_config`` of the checkpoint: from the model's Hugging Face config, else from the directory."""
+        qc = getattr(self.config.hf_config, 'quantization_config', None)
+        if qc is None:
+            import json
+            import os
+            path = os.path.join(hf_model_dir, 'config.json')
+            if os.path.exists(path):
+                with open(path, 'r', encoding='utf-8') as f:
+                    cfg = json.load(f)
+                qc = cfg.get('quantization_config') or (cfg.get('text_config') or {}).get('quantization_config')
+        if qc is not None and not isinstance(qc, dict):
+            qc = qc.to_dict() if hasattr(qc, 'to_dict') else dict(qc)
+        return qc
 
     def _legacy_key(self, key: str) -> str:
         """Inverse of ``_modernise_key``: such checkpoints are written in the layout they are published in."""

@@ -3,8 +3,10 @@
 Inputs are token-major: ``q [T, nq, d]``, ``k [T, nkv, d]``, ``v [T, nkv, dv]`` plus ``cu_seqlens``
 (int32 ``[B+1]``) delimiting the packed sequences; tokens never attend across a boundary.
 
-Implementations, in order of preference on a GPU: the in-tree sm_100a kernel (``csrc/attention``) when it
-supports the shape, else the ``flash_attn`` library kernel; on CPU a masked fp32 softmax (the oracle).
+On a GPU the in-tree sm_100a kernel (``csrc/attention``) runs every configuration it covers.  A configuration it
+does not cover is handed to the ``flash_attn`` library kernel (or, for what that lacks too, the masked-softmax
+reference) with a warning logged once per kind of gap, so a model that leaves the in-tree path says so;
+``MCB200_ATTENTION_BACKEND=mcb`` turns that into an error.  On CPU the masked fp32 softmax is the oracle.
 """
 from __future__ import annotations
 
@@ -91,11 +93,16 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: Opt
     backend = os.environ.get(_BACKEND_ENV, 'auto')
     T, nq, d = q.shape
     if q.is_cuda and backend in ('auto', 'mcb'):
-        from . import attention_cuda
-        if attention_cuda.supported(q, k, v, causal, window, sinks, softcap):
+        from . import _lib, attention_cuda
+        why = attention_cuda.unsupported_reason(q, k, v, causal, window, sinks, softcap)
+        if why is None and _lib.available():
             return attention_cuda.attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start)
         if backend == 'mcb':
-            raise RuntimeError('in-tree attention kernel does not support this configuration')
+            raise RuntimeError(f'the in-tree attention kernel does not cover {why or "a run with the kernels disabled"}')
+        if why is not None and _lib.cuda_enabled():
+            from ..utils.logger import get_logger
+            get_logger().warning_once(f'attention: the in-tree sm_100a kernel does not cover {why}; '
+                                      'this call runs on a library / reference kernel')
     if q.is_cuda and backend in ('auto', 'flash_attn') and sinks is None and q.dtype in (torch.bfloat16, torch.float16) \
             and _flash_attn_available() and d <= 256:
         from flash_attn import flash_attn_varlen_func

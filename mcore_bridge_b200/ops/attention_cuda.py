@@ -2,8 +2,7 @@
 
 Forward: ``attn_fwd_sm100.cu`` (tcgen05 / TMEM, two-pass softmax, two softmax warp groups).  Backward:
 ``attn_bwd_sm100.cu`` (delta, dQ and dK/dV kernels; the dK/dV kernel can split the query heads of a GQA group over
-several CTAs when the grid would not fill the GPU).  ``MCB200_ATTENTION_BWD_KERNEL=0`` routes the backward through the
-``flash_attn`` library instead (same ``lse [heads, T]`` layout in natural log) for A/B comparisons.
+several CTAs when the grid would not fill the GPU).
 """
 from __future__ import annotations
 
@@ -19,16 +18,29 @@ from . import _lib
 _ll, _int, _f = ctypes.c_longlong, ctypes.c_int, ctypes.c_float
 
 
-def supported(q, k, v, causal, window, sinks, softcap) -> bool:
-    if os.environ.get('MCB200_ATTENTION_KERNEL', '1') == '0':
-        return False
-    if not (causal and window is None and sinks is None and not softcap):
-        return False
-    if q.dtype != torch.bfloat16 or q.shape[-1] not in (64, 128) or v.shape[-1] != q.shape[-1]:
-        return False
+def unsupported_reason(q, k, v, causal, window, sinks, softcap) -> Optional[str]:
+    """``None`` when the in-tree kernel covers the call, else what it lacks (used for the one-time warning)."""
+    if not causal:
+        return 'non-causal attention'
+    if window is not None:
+        return 'sliding-window attention'
+    if sinks is not None:
+        return 'learnable softmax sinks'
+    if softcap:
+        return 'soft-capped scores'
+    if q.dtype != torch.bfloat16:
+        return f'dtype {q.dtype}'
+    if q.shape[-1] not in (64, 128):
+        return f'head size {q.shape[-1]}'
+    if v.shape[-1] != q.shape[-1]:
+        return f'value head size {v.shape[-1]} != query head size {q.shape[-1]}'
     if q.shape[1] % k.shape[1] != 0 or q.shape[0] != k.shape[0]:
-        return False
-    return _lib.available()
+        return 'query / key token counts or head counts that do not match'
+    return None
+
+
+def supported(q, k, v, causal, window, sinks, softcap) -> bool:
+    return unsupported_reason(q, k, v, causal, window, sinks, softcap) is None and _lib.available()
 
 
 def seq_start_from_cu(cu_seqlens: Optional[torch.Tensor], T: int, device) -> torch.Tensor:
@@ -79,28 +91,19 @@ class _AttnFn(torch.autograd.Function):
         do = do.contiguous()
         T, nq, d = q.shape
         lib = _lib.lib()
-        if hasattr(lib, 'mcb_attn_bwd') and os.environ.get('MCB200_ATTENTION_BWD_KERNEL', '1') != '0':
-            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-            delta = torch.empty((nq, T), dtype=torch.float32, device=q.device)
-            nkv = k.shape[1]
-            splits = _dkv_splits(T, nq, nkv, q.device)
-            partial = None
-            if splits > 1:
-                partial = torch.empty((2, splits, T, nkv, d), dtype=torch.float32, device=q.device)
-            rc = lib.mcb_attn_bwd_split(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do),
-                                        _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(seq_start), _lib.ptr(dq),
-                                        _lib.ptr(dk), _lib.ptr(dv), _int(T), _int(nq), _int(nkv), _int(d),
-                                        _f(ctx.scale), _lib.ptr(partial) if partial is not None else None,
-                                        _int(splits), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
-            _lib.check_rc(rc, 'mcb_attn_bwd_split')
-            return dq, dk, dv, None, None, None, None
-        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        if cu is None:
-            cu = torch.tensor([0, T], dtype=torch.int32, device=q.device)
-        ms = ctx.max_seqlen or T
-        _flash_attn_varlen_backward(do, q, k, v, o, lse, dq, dk, dv, cu, cu, ms, ms, 0.0, ctx.scale, True, -1, -1, 0.0,
-                                    None, False, None)
+        delta = torch.empty((nq, T), dtype=torch.float32, device=q.device)
+        nkv = k.shape[1]
+        splits = _dkv_splits(T, nq, nkv, q.device)
+        partial = None
+        if splits > 1:
+            partial = torch.empty((2, splits, T, nkv, d), dtype=torch.float32, device=q.device)
+        rc = lib.mcb_attn_bwd_split(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do),
+                                    _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(seq_start), _lib.ptr(dq),
+                                    _lib.ptr(dk), _lib.ptr(dv), _int(T), _int(nq), _int(nkv), _int(d),
+                                    _f(ctx.scale), _lib.ptr(partial) if partial is not None else None,
+                                    _int(splits), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_attn_bwd_split')
         return dq, dk, dv, None, None, None, None
 
 
@@ -111,5 +114,5 @@ def attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start: Optional[torch.
     if seq_start is None:
         seq_start = seq_start_from_cu(cu_seqlens, T, q.device)
     if max_seqlen is None and cu_seqlens is not None:
-        max_seqlen = T  # only the library backward needs it; the bound is safe
+        max_seqlen = T
     return _AttnFn.apply(q, k, v, seq_start, cu_seqlens, max_seqlen, float(scale))

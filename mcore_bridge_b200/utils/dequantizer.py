@@ -1,6 +1,8 @@
 """Dequantisers for quantised Hugging Face checkpoints: block-scaled fp8, MXFP4, fp4(e2m1)->fp8, packed int4/int8.
 
 Semantics as in reference ``src/mcore_bridge/utils/dequantizer.py:6-152``; formulas written out here.
+``GPTBridge.load_weights`` applies them through :func:`add_dequantized_views`, so every family loader sees plain
+weight keys whatever the storage format of the checkpoint.
 """
 from __future__ import annotations
 
@@ -62,12 +64,42 @@ class MxFp4Dequantizer:
         return out.flatten(-2).to(dtype)
 
 
+def quantize_mxfp4(w: torch.Tensor):
+    """Inverse of :class:`MxFp4Dequantizer` (round to nearest e2m1 value, power-of-two scale per 32 values along the
+    last dim): returns ``(blocks uint8 [..., G, 16], scales uint8 [..., G])``.  Used to write MXFP4 checkpoints and
+    to build test fixtures."""
+    assert w.shape[-1] % 32 == 0
+    x = w.float().reshape(*w.shape[:-1], -1, 32)
+    amax = x.abs().amax(dim=-1, keepdim=True).clamp(min=2.0 ** -120)
+    exp = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)        # largest magnitude maps inside [-6, 6]
+    scaled = x / torch.exp2(exp)
+    lut = torch.tensor(_FP4_VALUES[:8], dtype=torch.float32, device=w.device)
+    mag = (scaled.abs().unsqueeze(-1) - lut).abs().argmin(dim=-1)     # nearest magnitude code 0..7
+    code = (mag + (scaled < 0).long() * 8).to(torch.uint8)
+    blocks = (code[..., 0::2] | (code[..., 1::2] << 4)).contiguous()
+    return blocks, (exp.squeeze(-1) + 127).to(torch.uint8)
+
+
 def fp4_to_fp8(packed: torch.Tensor) -> torch.Tensor:
     """Unpacks e2m1 nibbles (low first) into ``float8_e4m3fn`` values; output last dim doubles."""
     lut = torch.tensor(_FP4_VALUES, dtype=torch.float32, device=packed.device)
     b = packed.view(torch.uint8)
     lo, hi = (b & 0x0F).long(), (b >> 4).long()
     return torch.stack((lut[lo], lut[hi]), dim=-1).flatten(-2).to(torch.float8_e4m3fn)
+
+
+def pack_int_weights(w_int: torch.Tensor, num_bits: int) -> torch.Tensor:
+    """Signed integers in ``[-2^(bits-1), 2^(bits-1))`` -> offset-binary values packed into int32 words along the
+    last dim (the layout :class:`PackedDequantizer` reads)."""
+    per = 32 // num_bits
+    cols = w_int.shape[-1]
+    pad = (-cols) % per
+    u = (w_int.to(torch.int64) + (1 << (num_bits - 1)))
+    u = torch.nn.functional.pad(u, (0, pad)).reshape(*w_int.shape[:-1], -1, per)
+    shifts = torch.arange(per, dtype=torch.int64, device=w_int.device) * num_bits
+    word = (u << shifts).sum(dim=-1)
+    word = torch.where(word >= (1 << 31), word - (1 << 32), word)    # two's complement int32
+    return word.to(torch.int32)
 
 
 class PackedDequantizer:
@@ -107,3 +139,43 @@ class PackedDequantizer:
                 else weight_zero_point.float()
             q = q - zp.repeat_interleave(gs, dim=-1)[..., :cols]
         return (q * s).to(dtype)
+
+
+def add_dequantized_views(sd: dict, quantization_config: Optional[dict], lazy_cls) -> dict:
+    """Adds, next to the stored tensors of a quantised checkpoint, lazily dequantised entries under the plain keys
+    the loaders ask for (parity: reference ``src/mcore_bridge/bridge/gpt_bridge.py:874-877,930-937,1157-1187``):
+
+    * MXFP4 (GPT-OSS experts): ``X_blocks`` + ``X_scales`` -> ``X``, transposed to the input-major layout of the
+      bf16 checkpoints (``[E, in, out]``);
+    * compressed-tensors: ``M.weight_packed`` + ``M.weight_scale`` + ``M.weight_shape`` (+ ``M.weight_zero_point``)
+      -> ``M.weight``.
+
+    ``lazy_cls`` is the ``LazyTensor`` class (passed in to keep this module free of I/O imports)."""
+    out = dict(sd)
+    mx = MxFp4Dequantizer()
+    for key in sd:
+        if key.endswith('_blocks') and key[:-len('_blocks')] + '_scales' in sd:
+            base = key[:-len('_blocks')]
+            if base in sd:
+                continue
+
+            def load_mx(base=base):
+                w = mx.convert(sd[base + '_blocks'].load(), sd[base + '_scales'].load())
+                return w.transpose(-1, -2).contiguous() if w.dim() == 3 else w
+
+            out[base] = lazy_cls(loader=load_mx)
+    packed = [k for k in sd if k.endswith('.weight_packed')]
+    if packed:
+        deq = PackedDequantizer(quantization_config or {})
+        for key in packed:
+            mod = key[:-len('.weight_packed')]
+            if mod + '.weight' in sd:
+                continue
+
+            def load_packed(mod=mod):
+                zp = sd.get(mod + '.weight_zero_point')
+                return deq.convert(sd[mod + '.weight_packed'].load(), sd[mod + '.weight_scale'].load(),
+                                   sd[mod + '.weight_shape'].load(), None if zp is None else zp.load(), dtype=torch.float32)
+
+            out[mod + '.weight'] = lazy_cls(loader=load_packed)
+    return out

@@ -415,3 +415,65 @@ def test_dsa_indexer_scores_and_topk(T, H, segs, k):
     assert torch.equal(vals, want)
     # no position is selected twice
     assert (idx.sort(dim=1).values[:, 1:] != idx.sort(dim=1).values[:, :-1]).all()
+
+
+def test_bounded_wait_reports_status_and_context_survives():
+    """A device wait on a flag that nothing sets runs out after its (shortened) limit, the kernel returns with the
+    peer-flag status code, the host check raises, and the context is still usable for the next kernel."""
+    import ctypes
+
+    from mcore_bridge_b200.ops import _lib, gemm
+    dev = torch.device('cuda', torch.cuda.current_device())
+    status = _lib.status_word(dev)
+    torch.cuda.synchronize()
+    old_limit = int(status[1].item())
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)       # flag slot 0 stays 0, the wait wants 1
+    ptrs = (ctypes.c_void_p * 1)(flags.data_ptr())
+    try:
+        status[1] = 50                                            # milliseconds
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        rc = _lib.lib().mcb_flag_wait(ptrs, ctypes.c_int(1), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_uint(1),
+                                      _lib.ptr(status), _lib.stream_ptr())
+        t1.record()
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert 30.0 < t0.elapsed_time(t1) < 2000.0                # gave up near the limit, not at the 10 s default
+        assert int(status[0].item()) == 5
+        with pytest.raises(_lib.KernelError, match='peer flag'):
+            _lib.check_status(dev)
+        assert int(status[0].item()) == 0                         # cleared by the check
+    finally:
+        status[1] = old_limit
+        status[0] = 0
+    x = torch.randn(256, 128, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(256, 128, device=dev, dtype=torch.bfloat16)
+    assert rel(gemm.mm_nt(x, w), x.float() @ w.float().t()) < 5e-3
+
+
+@pytest.mark.parametrize('M,N,K', [(512, 256, 128), (1000, 776, 520), (2048, 4096, 1024), (4096, 6144, 4096),
+                                   (8192, 1024, 256)])
+def test_gemm_cta_pair(M, N, K):
+    """The 256 x 256 CTA-pair kernel (``force_bn=512``) in the three layouts of a linear layer, against fp32 matmuls
+    and against the single-CTA kernel; a wrong 128-row half or 128-column half would show in the per-row check."""
+    from mcore_bridge_b200.ops import gemm
+    torch.manual_seed(3)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    dy = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+
+    def close(a, ref, tol):
+        a, ref = a.float(), ref.float()
+        assert rel(a, ref) < tol
+        assert ((a - ref).norm(dim=-1).max() / ref.norm(dim=-1).mean()).item() < 4 * tol
+
+    ref = x.float() @ w.float().t()
+    close(gemm.mm_nt(x, w, force_bn=512), ref, 5e-3)
+    close(gemm.mm_nt(x, w, bias=b, force_bn=512), ref + b.float(), 5e-3)
+    close(gemm.mm_nt(x, w, out_dtype=torch.float32, force_bn=512), ref, 1e-5)
+    close(gemm.mm_nn(dy, w, force_bn=512), dy.float() @ w.float(), 5e-3)
+    acc = torch.randn(N, K, device=DEV, dtype=torch.float32)
+    ref_tn = acc + dy.float().t() @ x.float()
+    close(gemm.mm_tn(dy, x, out=acc, accumulate=True, force_bn=512), ref_tn, 1e-5)
