@@ -1,0 +1,30 @@
+"""The command-line trainer: a short run on a tiny preset with token-file data, saving and resuming."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_cli_trains_saves_and_resumes(tmp_path):
+    tokens = np.random.default_rng(0).integers(0, 1024, size=20000, dtype=np.int32)
+    data = str(tmp_path / 'tokens.npy')
+    np.save(data, tokens)
+    out = str(tmp_path / 'out')
+    base = [sys.executable, '-m', 'mcore_bridge_b200.train.cli', '--model', 'qwen3_tiny', '--dtype', 'fp32', '--seq-len',
+            '128', '--global-batch', '4', '--micro-batch-size', '2', '--data', data, '--lr', '1e-3', '--save', out]
+    env = dict(os.environ, PYTHONPATH=REPO, CUDA_VISIBLE_DEVICES='')
+    r = subprocess.run(base + ['--steps', '3'], env=env, capture_output=True, text=True, timeout=600, cwd=REPO)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    lines = [json.loads(l[l.index('{'):]) for l in (r.stdout + r.stderr).splitlines() if '"step"' in l]
+    assert [l['step'] for l in lines] == [1, 2, 3] and all(l['loss'] == l['loss'] for l in lines)
+    assert os.path.exists(os.path.join(out, 'model.safetensors'))
+    assert os.path.isdir(os.path.join(out, 'state'))
+    r = subprocess.run(base + ['--steps', '4', '--resume', os.path.join(out, 'state')], env=env, capture_output=True,
+                       text=True, timeout=600, cwd=REPO)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    lines = [json.loads(l[l.index('{'):]) for l in (r.stdout + r.stderr).splitlines() if '"step"' in l]
+    assert [l['step'] for l in lines] == [4]
