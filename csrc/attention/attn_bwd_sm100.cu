@@ -9,7 +9,11 @@
 //
 // All operand layouts are the ones the forward kernel uses (row-major [tokens, heads*d] tiles fetched by TMA with
 // the 128-byte swizzle, consumed K-major or MN-major), P is recomputed from the forward's log-sum-exp so nothing
-// but O and lse is kept from the forward.  Packed sequences are described by the same per-token `seq_start` array.
+// but O and lse is kept from the forward.  The mask is the forward's: a per-query inclusive key range
+// [k_lo[i], k_hi[i]] (k_hi null = the query's own index, i.e. packed causal self-attention); queries and keys may be
+// different token sets.  The dK/dV kernel additionally takes, per key, bounds [q_lo[n], q_hi[n]] on the queries that
+// can see it (null = derived from the causal structure), which only limit its loop: visibility itself is always
+// decided by the per-query ranges.
 //
 // Warp roles in dq and dk/dv (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9
 // element-wise in two groups of four (thread = TMEM lane = query row in dq, key row in dk/dv); group g takes the
@@ -20,6 +24,7 @@
 
 #include "../common/host_utils.cuh"
 #include "../common/ptx.cuh"
+#include "attn_common.cuh"
 
 using namespace mcb;
 
@@ -31,16 +36,19 @@ constexpr int BWD_THREADS = 320;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
-  int T, nq, nkv, d;
+  int T, Tk, nq, nkv, d;    // T queries, Tk keys
   float scale, scale_log2;
-  const int* seq_start;     // [T]
+  const int* k_lo;          // [T] first visible key of each query
+  const int* k_hi;          // [T] last visible key, or null: the query's own index
+  const int* q_lo;          // [Tk] bounds on the queries that see each key, or null (causal self-attention)
+  const int* q_hi;
   const float* lse;         // [nq, T]
   const float* delta;       // [nq, T]
   __nv_bfloat16* dq;        // [T, nq, d]
-  __nv_bfloat16* dk;        // [T, nkv, d]
-  __nv_bfloat16* dv;        // [T, nkv, d]
+  __nv_bfloat16* dk;        // [Tk, nkv, d]
+  __nv_bfloat16* dv;        // [Tk, nkv, d]
   int* status;
-  float* partial;           // head-split mode: [2 (dv, dk), splits, T, nkv, d] fp32 partial sums, else null
+  float* partial;           // head-split mode: [2 (dv, dk), splits, Tk, nkv, d] fp32 partial sums, else null
   int splits;               // CTAs per (key tile, kv head); each takes qpg / splits query heads
 };
 
@@ -181,9 +189,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int head = blockIdx.y;
   const int kvh = head / (p.nq / p.nkv);
   const int m0 = m_tile * TM;
-  const int kb0 = p.seq_start[m0] / BLK;
-  const int last_row = min(m0 + TM - 1, p.T - 1);
-  const int nblk = last_row / BLK - kb0 + 1;
+  __shared__ int s_rng[8];
+  tile_range_partial(p.k_lo, p.k_hi, m0, p.T, s_rng);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -212,8 +219,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  const int kmin = tile_range_min(s_rng), kmax = tile_range_max(s_rng);
+  const int kb0 = kmin / BLK;
+  const int nblk = kmax >= kmin ? kmax / BLK - kb0 + 1 : 0;
 
-  if (warp == 0) {
+  if (nblk <= 0) {
+    // no row of this tile sees any key: its queries get a zero gradient
+    if (warp >= 2) {
+      const int grp = (warp - 2) >> 2;
+      const int i = m0 + (warp & 3) * 32 + lane;
+      if (i < p.T) {
+        uint4* row = reinterpret_cast<uint4*>(p.dq + ((long long)i * p.nq + head) * D + grp * (D / 2));
+#pragma unroll
+        for (int c = 0; c < D / 16; ++c) row[c] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  } else if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(smem_u32(q_full), 2 * L::TILE);
 #pragma unroll
@@ -285,8 +306,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int r = q * 32 + lane;
     const int i = m0 + r;
     const bool row_ok = i < p.T;
-    const int lo = row_ok ? p.seq_start[i] : 1, hi = row_ok ? i : 0;
-    const float lse2 = row_ok ? p.lse[(long long)head * p.T + i] * LOG2E : 0.f;
+    int lo, hi;
+    attn_row_range(p.k_lo, p.k_hi, i, p.T, lo, hi);
+    // a query that sees nothing has lse = -inf; its masked probabilities are zeroed below, keep the arithmetic finite
+    const float lse_i = row_ok ? p.lse[(long long)head * p.T + i] : 0.f;
+    const float lse2 = (lse_i == -INFINITY) ? 0.f : lse_i * LOG2E;
     const float dl = row_ok ? p.delta[(long long)head * p.T + i] : 0.f;
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
     const uint32_t st = grp;
@@ -355,8 +379,9 @@ struct DkvSmem {
   static constexpr int OFF_DO = OFF_Q + 2 * BLOCK;      // 2 stages
   static constexpr int OFF_P = OFF_DO + 2 * BLOCK;      // 2 buffers
   static constexpr int OFF_DS = OFF_P + 2 * PT;         // 2 buffers
-  static constexpr int OFF_COL = OFF_DS + 2 * PT;       // per-column lse / delta / seq_start, 2 buffers per group
-  static constexpr int COL_BYTES = 3 * BLK * 4;
+  static constexpr int OFF_COL = OFF_DS + 2 * PT;       // per-column lse / delta / k_lo / k_hi + 4 ints of block
+                                                        // bounds, 2 buffers per group
+  static constexpr int COL_BYTES = 4 * BLK * 4 + 16;
   static constexpr int OFF_BAR = OFF_COL + 4 * COL_BYTES;
   static constexpr int TOTAL = OFF_BAR + 1024 + 1024;
 };
@@ -411,15 +436,21 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     prefetch_tensormap(&tm_v);
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_do);
-    // last query that can see a key of this tile: the largest i with seq_start[i] <= last key (seq_start is sorted)
-    const int n_last = min(n0 + TM - 1, p.T - 1);
-    int lo = n_last, hi = p.T - 1;
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (p.seq_start[mid] <= n_last) lo = mid; else hi = mid - 1;
+    if (p.q_lo == nullptr) {
+      // causal self-attention: the last query that can see a key of this tile is the largest i with
+      // k_lo[i] <= last key (k_lo = sequence starts, sorted); the first one is the tile's first key itself
+      const int n_last = min(n0 + TM - 1, p.Tk - 1);
+      int lo = n_last, hi = p.T - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (p.k_lo[mid] <= n_last) lo = mid; else hi = mid - 1;
+      }
+      i_end_slot[0] = n0;
+      i_end_slot[1] = lo;
     }
-    *i_end_slot = lo;
   }
+  __shared__ int s_rng[8];
+  if (p.q_lo != nullptr) tile_range_partial(p.q_lo, p.q_hi, n0, p.Tk, s_rng);
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
@@ -428,8 +459,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const int qb0 = n0 / BLK;
-  const int nqb = *i_end_slot / BLK - qb0 + 1;
+  const int i_first = p.q_lo ? tile_range_min(s_rng) : i_end_slot[0];
+  const int i_last = p.q_lo ? min(tile_range_max(s_rng), p.T - 1) : i_end_slot[1];
+  const int qb0 = i_first / BLK;
+  const int nqb = i_last >= i_first ? i_last / BLK - qb0 + 1 : 0;   // 0: no query sees a key of this tile
   const int hps = qpg / p.splits;                 // query heads handled by this CTA
   const int h_first = kvh * qpg + blockIdx.z * hps;
   const int iters = hps * nqb;
@@ -511,7 +544,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const int grp = (warp - 2) >> 2;
     const int r = q * 32 + lane;            // key row of this thread
     const int n = n0 + r;
-    const bool row_ok = n < p.T;
+    const bool row_ok = n < p.Tk;
     const int t = (threadIdx.x - 64) & 127; // 0..127 inside the group
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
     const uint32_t st = grp;
@@ -525,14 +558,30 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       const uint32_t cb = st * 2 + ph;
       float* col_lse = reinterpret_cast<float*>(smem + L::OFF_COL + cb * L::COL_BYTES);
       float* col_delta = col_lse + BLK;
-      int* col_start = reinterpret_cast<int*>(col_delta + BLK);
+      int* col_lo = reinterpret_cast<int*>(col_delta + BLK);
+      int* col_hi = col_lo + BLK;
+      int* col_meta = col_hi + BLK;            // [0..1] largest k_lo, [2..3] smallest k_hi of each half of the block
       {
         const int c = t & (BLK - 1);
         const int i = i0 + c;
         if (t < BLK) {
-          col_lse[c] = i < p.T ? p.lse[(long long)h * p.T + i] * LOG2E : 0.f;
-          col_start[c] = i < p.T ? p.seq_start[i] : INT_MAX;
+          int klo, khi;
+          attn_row_range(p.k_lo, p.k_hi, i, p.T, klo, khi);
+          col_lo[c] = klo;
+          col_hi[c] = khi;
+          int mxlo = klo, mnhi = khi;
+#pragma unroll
+          for (int sft = 16; sft; sft >>= 1) {
+            mxlo = max(mxlo, __shfl_xor_sync(0xffffffffu, mxlo, sft));
+            mnhi = min(mnhi, __shfl_xor_sync(0xffffffffu, mnhi, sft));
+          }
+          if ((t & 31) == 0) {
+            col_meta[t >> 5] = mxlo;
+            col_meta[2 + (t >> 5)] = mnhi;
+          }
         } else {
+          const float l = i < p.T ? p.lse[(long long)h * p.T + i] : 0.f;
+          col_lse[c] = (l == -INFINITY) ? 0.f : l * LOG2E;    // such a query sees nothing: masked below
           col_delta[c] = i < p.T ? p.delta[(long long)h * p.T + i] : 0.f;
         }
       }
@@ -541,7 +590,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       if (!mbar_wait(smem_u32(&s_full[st]), ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       if (!mbar_wait(smem_u32(&pds_empty[st]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
       tc_fence_after();
-      const bool full = row_ok && (i0 >= n) && (col_start[BLK - 1] <= n);
+      // every query of the block sees this key: largest lower bound <= n <= smallest upper bound
+      const bool full = row_ok && max(col_meta[0], col_meta[1]) <= n && n <= min(col_meta[2], col_meta[3]);
       uint8_t* tile_p = smem + L::OFF_P + st * L::PT;
       uint8_t* tile_ds = smem + L::OFF_DS + st * L::PT;
 #pragma unroll 1
@@ -564,12 +614,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
               ds[e + u] = x * (__uint_as_float(dp[e + u]) - dd[u]) * p.scale;
             }
           } else {
-            const int4 s4 = *reinterpret_cast<const int4*>(col_start + c + e);
-            const int ss[4] = {s4.x, s4.y, s4.z, s4.w};
+            const int4 s4 = *reinterpret_cast<const int4*>(col_lo + c + e);
+            const int4 h4 = *reinterpret_cast<const int4*>(col_hi + c + e);
+            const int ss[4] = {s4.x, s4.y, s4.z, s4.w}, hh[4] = {h4.x, h4.y, h4.z, h4.w};
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              const int i = i0 + c + e + u;
-              const bool vis = row_ok && i >= n && ss[u] <= n;
+              const bool vis = row_ok && ss[u] <= n && n <= hh[u];
               const float x = exp2f(__uint_as_float(s[e + u]) * p.scale_log2 - ls[u]);
               pr[e + u] = vis ? x : 0.f;
               ds[e + u] = vis ? x * (__uint_as_float(dp[e + u]) - dd[u]) * p.scale : 0.f;
@@ -585,7 +635,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&pds_full[st]));
     }
-    if (ok && mbar_wait(smem_u32(out_full), 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
+    if (iters == 0) {
+      // no query sees this tile's keys: zero gradients (the accumulators were never written)
+      const long long row_off = ((long long)n * p.nkv + kvh) * D;
+      if (row_ok) {
+        if (p.partial == nullptr) {
+          uint4* dst = reinterpret_cast<uint4*>((grp == 0 ? p.dv : p.dk) + row_off);
+#pragma unroll 1
+          for (int c = 0; c < D / 8; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+        } else {
+          const long long plane = (long long)p.Tk * p.nkv * D;
+          uint4* dst = reinterpret_cast<uint4*>(p.partial + ((long long)grp * p.splits + blockIdx.z) * plane + row_off);
+#pragma unroll 1
+          for (int c = 0; c < D / 4; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    } else if (ok && mbar_wait(smem_u32(out_full), 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       // group 0 writes dV, group 1 writes dK
       const long long row_off = ((long long)n * p.nkv + kvh) * D;
@@ -593,7 +658,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (grp == 0) store_acc_row<D>(tmem + lane_addr + COL_DV, p.dv + row_off, row_ok);
         else store_acc_row<D>(tmem + lane_addr + COL_DK, p.dk + row_off, row_ok);
       } else {
-        const long long plane = (long long)p.T * p.nkv * D;
+        const long long plane = (long long)p.Tk * p.nkv * D;
         float* dst = p.partial + ((long long)grp * p.splits + blockIdx.z) * plane + row_off;
         store_acc_row_f32<D>(tmem + lane_addr + (grp == 0 ? COL_DV : COL_DK), dst, row_ok);
       }
@@ -632,21 +697,24 @@ __global__ void attn_bwd_reduce_kernel(const float* __restrict__ partial, __nv_b
 
 template <int D>
 int launch_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, float* delta,
-               const BwdParams& p, cudaStream_t stream) {
+               bool delta_given, const BwdParams& p, cudaStream_t stream) {
   const long long rows = (long long)p.T * p.nq;
-  attn_bwd_delta_kernel<D><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
-      (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, p.T, p.nq);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
+  cudaError_t e = cudaSuccess;
+  if (!delta_given) {
+    attn_bwd_delta_kernel<D><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, p.T, p.nq);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
   CUtensorMap tq128, tdo128, tk64, tv64, tk128, tv128, tq64, tdo64;
   const long long wq = (long long)p.nq * D, wk = (long long)p.nkv * D;
   int rc = 0;
   if ((rc = make_tmap_2d_bf16(&tq128, q, wq, p.T, wq, 64, TM))) return rc;
   if ((rc = make_tmap_2d_bf16(&tdo128, dout, wq, p.T, wq, 64, TM))) return rc;
-  if ((rc = make_tmap_2d_bf16(&tk64, k, wk, p.T, wk, 64, BLK))) return rc;
-  if ((rc = make_tmap_2d_bf16(&tv64, v, wk, p.T, wk, 64, BLK))) return rc;
-  if ((rc = make_tmap_2d_bf16(&tk128, k, wk, p.T, wk, 64, TM))) return rc;
-  if ((rc = make_tmap_2d_bf16(&tv128, v, wk, p.T, wk, 64, TM))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tk64, k, wk, p.Tk, wk, 64, BLK))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tv64, v, wk, p.Tk, wk, 64, BLK))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tk128, k, wk, p.Tk, wk, 64, TM))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tv128, v, wk, p.Tk, wk, 64, TM))) return rc;
   if ((rc = make_tmap_2d_bf16(&tq64, q, wq, p.T, wq, 64, BLK))) return rc;
   if ((rc = make_tmap_2d_bf16(&tdo64, dout, wq, p.T, wq, 64, BLK))) return rc;
   static bool cfg = false;
@@ -657,15 +725,15 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* o, const
     if (e != cudaSuccess) return (int)e;
     cfg = true;
   }
-  const int tiles = (p.T + TM - 1) / TM;
+  const int tiles = (p.T + TM - 1) / TM, ktiles = (p.Tk + TM - 1) / TM;
   attn_bwd_dq_kernel<D><<<dim3(tiles, p.nq), BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(tq128, tdo128, tk64, tv64, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  attn_bwd_dkv_kernel<D><<<dim3(tiles, p.nkv, p.splits), BWD_THREADS, DkvSmem<D>::TOTAL, stream>>>(tk128, tv128, tq64,
-                                                                                                    tdo64, p);
+  attn_bwd_dkv_kernel<D><<<dim3(ktiles, p.nkv, p.splits), BWD_THREADS, DkvSmem<D>::TOTAL, stream>>>(tk128, tv128, tq64,
+                                                                                                     tdo64, p);
   e = cudaGetLastError();
   if (e != cudaSuccess || p.partial == nullptr) return (int)e;
-  const long long plane = (long long)p.T * p.nkv * D;
+  const long long plane = (long long)p.Tk * p.nkv * D;
   attn_bwd_reduce_kernel<<<(unsigned)((plane / 8 + 255) / 256), 256, 0, stream>>>(p.partial, p.dv, p.dk, plane,
                                                                                   p.splits);
   return (int)cudaGetLastError();
@@ -675,39 +743,46 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* o, const
 
 extern "C" {
 
-// q/o/dout/dq [T, nq, d], k/v/dk/dv [T, nkv, d] bf16 contiguous; lse, delta [nq, T] fp32 (delta is scratch filled
-// here); seq_start [T] int32.  `scale` is the softmax scale the forward used.
+// General form.  q/o/dout/dq [T, nq, d], k/v/dk/dv [Tk, nkv, d] bf16 contiguous; lse, delta [nq, T] fp32 (delta is
+// scratch filled here, or, with `delta_given`, read as passed: ring attention computes it once from the merged
+// output).  k_lo / k_hi [T]: the forward's per-query key ranges (k_hi null = the query's index).  q_lo / q_hi [Tk]:
+// per key, bounds on the queries that can see it (both null for causal self-attention).  `scale` is the softmax
+// scale the forward used.
 //
 // Head split: with few kv heads and few key tiles the dK/dV grid (tiles x nkv CTAs) cannot fill the GPU.  Passing
-// `splits` > 1 (a divisor of nq / nkv) and `partial` (fp32, 2 * splits * T * nkv * d elements) lets `splits` CTAs share
-// a (tile, kv head) pair, each over nq / nkv / splits query heads; a reduction kernel sums their partial results.
-int mcb_attn_bwd_split(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
-                       float* delta, const int* seq_start, void* dq, void* dk, void* dv, int T, int nq, int nkv, int d,
-                       float scale, float* partial, int splits, int* status, void* stream_) {
-  if (T == 0) return 0;
-  if (nq % nkv) return -2;
+// `splits` > 1 (a divisor of nq / nkv) and `partial` (fp32, 2 * splits * Tk * nkv * d elements) lets `splits` CTAs
+// share a (tile, kv head) pair, each over nq / nkv / splits query heads; a reduction kernel sums their partial results.
+int mcb_attn_bwd_ranges(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                        float* delta, int delta_given, const int* k_lo, const int* k_hi, const int* q_lo,
+                        const int* q_hi, void* dq, void* dk, void* dv, int T, int Tk, int nq, int nkv, int d,
+                        float scale, float* partial, int splits, int* status, void* stream_) {
+  if (T == 0 || Tk == 0) return 0;
+  if (nq % nkv || (k_hi == nullptr && Tk < T) || ((q_lo == nullptr) != (q_hi == nullptr))) return -2;
+  if (q_lo == nullptr && k_hi != nullptr) return -2;   // general masks need the per-key query bounds
   if (splits < 1 || (nq / nkv) % splits) return -4;
   if (splits == 1) partial = nullptr;
   else if (partial == nullptr) return -5;
-  BwdParams p{T, nq, nkv, d, scale, scale * LOG2E, seq_start, lse, delta,
+  BwdParams p{T, Tk, nq, nkv, d, scale, scale * LOG2E, k_lo, k_hi, q_lo, q_hi, lse, delta,
               (__nv_bfloat16*)dq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, status, partial, splits};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
-  if (d == 128) return launch_bwd<128>(q, k, v, o, dout, delta, p, s);
-  if (d == 64) return launch_bwd<64>(q, k, v, o, dout, delta, p, s);
+  if (d == 128) return launch_bwd<128>(q, k, v, o, dout, delta, delta_given != 0, p, s);
+  if (d == 64) return launch_bwd<64>(q, k, v, o, dout, delta, delta_given != 0, p, s);
   return -3;
+}
+
+// Packed causal self-attention: seq_start [T] int32 = first token of each token's sequence.
+int mcb_attn_bwd_split(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                       float* delta, const int* seq_start, void* dq, void* dk, void* dv, int T, int nq, int nkv, int d,
+                       float scale, float* partial, int splits, int* status, void* stream_) {
+  return mcb_attn_bwd_ranges(q, k, v, o, dout, lse, delta, 0, seq_start, nullptr, nullptr, nullptr, dq, dk, dv, T, T, nq,
+                             nkv, d, scale, partial, splits, status, stream_);
 }
 
 int mcb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
                  float* delta, const int* seq_start, void* dq, void* dk, void* dv, int T, int nq, int nkv, int d,
                  float scale, int* status, void* stream_) {
-  if (T == 0) return 0;
-  if (nq % nkv) return -2;
-  BwdParams p{T, nq, nkv, d, scale, scale * LOG2E, seq_start, lse, delta,
-              (__nv_bfloat16*)dq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, status, nullptr, 1};
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
-  if (d == 128) return launch_bwd<128>(q, k, v, o, dout, delta, p, s);
-  if (d == 64) return launch_bwd<64>(q, k, v, o, dout, delta, p, s);
-  return -3;
+  return mcb_attn_bwd_split(q, k, v, o, dout, lse, delta, seq_start, dq, dk, dv, T, nq, nkv, d, scale, nullptr, 1,
+                            status, stream_);
 }
 
 }  // extern "C"

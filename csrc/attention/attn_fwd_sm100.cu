@@ -1,9 +1,10 @@
 // Variable-length causal GQA attention forward for sm_100a: S = Q K^T and O += P V on tcgen05 with accumulators in
 // TMEM, operands staged by TMA, softmax in registers.
 //
-// One CTA per (128-query tile, query head).  Packed sequences are handled by a per-token `seq_start` array: query i
-// sees keys j with seq_start[i] <= j <= i, so tiles may straddle sequence boundaries and nothing is synchronised
-// with the host.
+// One CTA per (128-query tile, query head).  The mask is a per-query inclusive key range [k_lo[i], k_hi[i]] (see
+// attn_common.cuh): packed causal self-attention is k_lo = first token of the query's sequence, k_hi = the query
+// itself, so tiles may straddle sequence boundaries and nothing is synchronised with the host; queries and keys may
+// also be different token sets (the steps of context-parallel ring attention, non-causal attention).
 //
 // Two passes over the key blocks instead of online rescaling: pass 1 computes only the row maxima (Q K^T + max),
 // pass 2 recomputes S, forms P = exp2(S - max) and accumulates O += P V directly in TMEM with no correction step.
@@ -17,6 +18,7 @@
 #include <type_traits>
 #include "../common/host_utils.cuh"
 #include "../common/ptx.cuh"
+#include "attn_common.cuh"
 
 using namespace mcb;
 
@@ -27,11 +29,12 @@ constexpr int BNK = 128; // keys per block
 constexpr int ATT_THREADS = 320;
 
 struct AttnParams {
-  int T, nq, nkv, d;
+  int T, Tk, nq, nkv, d;  // T queries, Tk keys
   float scale_log2;       // softmax scale * log2(e)
-  const int* seq_start;   // [T]
+  const int* k_lo;        // [T] first visible key of each query
+  const int* k_hi;        // [T] last visible key, or null: the query's own index
   __nv_bfloat16* o;       // [T, nq, d]
-  float* lse;             // [nq, T] natural log of sum exp(scaled scores)
+  float* lse;             // [nq, T] natural log of sum exp(scaled scores); -inf for a query that sees no key
   int* status;
 };
 
@@ -88,8 +91,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int head = blockIdx.y;
   const int kvh = head / (p.nq / p.nkv);
   const int m0 = m_tile * BM;
-  const int kb0 = p.seq_start[m0] / BNK;          // first key block any row of this tile can see
-  const int nblk = m_tile - kb0 + 1;
+  __shared__ int s_rng[8];
+  tile_range_partial(p.k_lo, p.k_hi, m0, p.T, s_rng);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -121,8 +124,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  const int kmin = tile_range_min(s_rng), kmax = tile_range_max(s_rng);
+  const int kb0 = kmin / BNK;                      // first key block any row of this tile can see
+  const int nblk = kmax >= kmin ? kmax / BNK - kb0 + 1 : 0;
 
-  if (warp == 0) {
+  if (nblk <= 0) {
+    // no row of this tile sees any key: the output is zero and the log-sum-exp -inf
+    if (warp >= 2) {
+      const int grp = (warp - 2) >> 2;
+      const int i = m0 + (warp & 3) * 32 + lane;
+      if (i < p.T) {
+        uint4* orow = reinterpret_cast<uint4*>(p.o + ((long long)i * p.nq + head) * D + grp * (D / 2));
+#pragma unroll
+        for (int c = 0; c < D / 16; ++c) orow[c] = make_uint4(0, 0, 0, 0);
+        if (grp == 0) p.lse[(long long)head * p.T + i] = -INFINITY;
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(smem_u32(q_full), L::TILE);
@@ -220,7 +238,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int r = q * 32 + lane;
     const int i = m0 + r;
     const bool row_ok = i < p.T;
-    const int lo = row_ok ? p.seq_start[i] : 1, hi = row_ok ? i : 0;
+    int lo, hi;
+    attn_row_range(p.k_lo, p.k_hi, i, p.T, lo, hi);
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
     const uint32_t sb = grp;                         // this group's score buffer
     float mx = -INFINITY;
@@ -362,9 +381,9 @@ int launch_fwd(const void* q, const void* k, const void* v, const AttnParams& p,
   CUtensorMap tq, tk, tv;
   int rc = make_tmap_2d_bf16(&tq, q, (long long)p.nq * D, p.T, (long long)p.nq * D, 64, BM);
   if (rc) return rc;
-  rc = make_tmap_2d_bf16(&tk, k, (long long)p.nkv * D, p.T, (long long)p.nkv * D, 64, BNK);
+  rc = make_tmap_2d_bf16(&tk, k, (long long)p.nkv * D, p.Tk, (long long)p.nkv * D, 64, BNK);
   if (rc) return rc;
-  rc = make_tmap_2d_bf16(&tv, v, (long long)p.nkv * D, p.T, (long long)p.nkv * D, 64, BNK);
+  rc = make_tmap_2d_bf16(&tv, v, (long long)p.nkv * D, p.Tk, (long long)p.nkv * D, 64, BNK);
   if (rc) return rc;
   static bool cfg = false;
   if (!cfg) {
@@ -381,16 +400,23 @@ int launch_fwd(const void* q, const void* k, const void* v, const AttnParams& p,
 
 extern "C" {
 
-// q [T, nq, d], k/v [T, nkv, d] bf16 contiguous; seq_start [T] int32; o [T, nq, d]; lse [nq, T] fp32
-int mcb_attn_fwd(const void* q, const void* k, const void* v, const int* seq_start, void* o, float* lse, int T, int nq,
-                 int nkv, int d, float scale, int* status, void* stream_) {
+// General form.  q [T, nq, d], k/v [Tk, nkv, d] bf16 contiguous; k_lo / k_hi [T] int32: query i attends to the keys
+// k_lo[i] .. k_hi[i] (inclusive; k_hi may be null = i, which needs Tk >= T); o [T, nq, d]; lse [nq, T] fp32.
+int mcb_attn_fwd_ranges(const void* q, const void* k, const void* v, const int* k_lo, const int* k_hi, void* o,
+                        float* lse, int T, int Tk, int nq, int nkv, int d, float scale, int* status, void* stream_) {
   if (T == 0) return 0;
-  if (nq % nkv) return -2;
-  AttnParams p{T, nq, nkv, d, scale * 1.4426950408889634f, seq_start, (__nv_bfloat16*)o, lse, status};
+  if (nq % nkv || Tk <= 0 || (k_hi == nullptr && Tk < T)) return -2;
+  AttnParams p{T, Tk, nq, nkv, d, scale * 1.4426950408889634f, k_lo, k_hi, (__nv_bfloat16*)o, lse, status};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   if (d == 128) return launch_fwd<128>(q, k, v, p, s);
   if (d == 64) return launch_fwd<64>(q, k, v, p, s);
   return -3;
+}
+
+// Packed causal self-attention: seq_start [T] int32 = first token of each token's sequence.
+int mcb_attn_fwd(const void* q, const void* k, const void* v, const int* seq_start, void* o, float* lse, int T, int nq,
+                 int nkv, int d, float scale, int* status, void* stream_) {
+  return mcb_attn_fwd_ranges(q, k, v, seq_start, nullptr, o, lse, T, T, nq, nkv, d, scale, status, stream_);
 }
 
 }  // extern "C"

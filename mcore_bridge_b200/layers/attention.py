@@ -42,7 +42,7 @@ class CoreAttention(nn.Module):
             sinks = torch.zeros(q.shape[1], device=q.device, dtype=torch.float32)
         cp = ps.get_world_size('cp')
         if cp > 1:
-            from ..parallel.context_parallel import ring_attention
+            from ..parallel.context_parallel import cp_attention as ring_attention
             return ring_attention(q, k, v, ctx, scale=self.scale, window=self.window, sinks=sinks)
         return attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, causal=True, scale=self.scale, window=self.window,
                          sinks=sinks, seq_start=ctx.seq_start)

@@ -186,7 +186,7 @@ class MLASelfAttention(nn.Module):
             o = self._sparse_attention(x, qr, q, k, v, ctx, sp)
         elif ps.get_world_size('cp') > 1:
             # this rank holds two zig-zag chunks of every sequence: keys / values are exchanged over the group
-            from ..parallel.context_parallel import ring_attention
+            from ..parallel.context_parallel import cp_attention as ring_attention
             o = ring_attention(q.contiguous(), k.contiguous(), v, ctx, scale=self.scale)
         else:
             o = attention(q.contiguous(), k.contiguous(), v, ctx.cu_seqlens, ctx.max_seqlen, causal=True,

@@ -119,3 +119,15 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: Opt
                                    causal=causal, window_size=ws, softcap=softcap or 0.0)
         return o[..., :v.shape[-1]] if v.shape[-1] != d else o
     return attention_ref(q, k, v, cu_seqlens, cu_seqlens, causal, scale, window, sinks, softcap)
+
+
+def attention_qk_ranges(q: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tensor, lay, scale=None, window=None,
+                        sinks=None) -> torch.Tensor:
+    """Attention of a context-parallel rank's queries ``[T_local, nq, d]`` against the keys / values of the whole
+    token stream (``lay`` = ``parallel.context_parallel.CpLayout``), for what the in-tree ranges kernel does not
+    cover: the masked-softmax reference with explicit positions (memory O(T_local x T): meant for CPU tests and
+    small inputs)."""
+    k_rel = torch.arange(k_full.shape[0], device=q.device) - \
+        lay.cu_full.to(torch.int64)[segment_ids(lay.cu_full, k_full.shape[0])]
+    return attention_ref(q, k_full, v_full, lay.cu_local, lay.cu_full, True, scale, window, sinks, None, lay.q_rel,
+                         k_rel)

@@ -116,3 +116,59 @@ def attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start: Optional[torch.
     if max_seqlen is None and cu_seqlens is not None:
         max_seqlen = T
     return _AttnFn.apply(q, k, v, seq_start, cu_seqlens, max_seqlen, float(scale))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# general masks: per-query inclusive key ranges (context-parallel attention, non-causal packed attention)
+# ---------------------------------------------------------------------------------------------------------------
+def ranges_supported(q, k, v) -> bool:
+    d = q.shape[-1]
+    return (q.is_cuda and q.dtype == torch.bfloat16 and d in (64, 128) and v.shape[-1] == d and k.shape[-1] == d
+            and q.shape[1] % k.shape[1] == 0 and _lib.available())
+
+
+class _AttnRangesFn(torch.autograd.Function):
+    """``o[i] = softmax over keys k_lo[i]..k_hi[i] of q[i] k^T * scale`` applied to ``v``; queries ``[T, nq, d]`` and
+    keys / values ``[Tk, nkv, d]`` may be different token sets.  ``q_lo`` / ``q_hi`` ``[Tk]`` bound, per key, the
+    queries that can see it (they only limit the loops of the dK/dV kernel)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, k_lo, k_hi, q_lo, q_hi, scale):
+        T, nq, d = q.shape
+        Tk, nkv = k.shape[0], k.shape[1]
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o = torch.empty_like(q)
+        lse = torch.empty((nq, T), dtype=torch.float32, device=q.device)
+        rc = _lib.lib().mcb_attn_fwd_ranges(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(k_lo), _lib.ptr(k_hi),
+                                            _lib.ptr(o), _lib.ptr(lse), _int(T), _int(Tk), _int(nq), _int(nkv), _int(d),
+                                            _f(scale), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_attn_fwd_ranges')
+        ctx.save_for_backward(q, k, v, o, lse, k_lo, k_hi, q_lo, q_hi)
+        ctx.scale = scale
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        q, k, v, o, lse, k_lo, k_hi, q_lo, q_hi = ctx.saved_tensors
+        do = do.contiguous()
+        T, nq, d = q.shape
+        Tk, nkv = k.shape[0], k.shape[1]
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty((nq, T), dtype=torch.float32, device=q.device)
+        splits = _dkv_splits(Tk, nq, nkv, q.device)
+        partial = torch.empty((2, splits, Tk, nkv, d), dtype=torch.float32, device=q.device) if splits > 1 else None
+        rc = _lib.lib().mcb_attn_bwd_ranges(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta), _int(0),
+            _lib.ptr(k_lo), _lib.ptr(k_hi), _lib.ptr(q_lo), _lib.ptr(q_hi), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+            _int(T), _int(Tk), _int(nq), _int(nkv), _int(d), _f(ctx.scale), _lib.ptr(partial), _int(splits),
+            _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_attn_bwd_ranges')
+        return dq, dk, dv, None, None, None, None, None
+
+
+def attention_ranges(q, k, v, k_lo, k_hi, q_lo, q_hi, scale: Optional[float] = None):
+    """Returns ``(o [T, nq, d], lse [nq, T])``; all four range tensors are int32 on the device."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    return _AttnRangesFn.apply(q, k, v, k_lo, k_hi, q_lo, q_hi, float(scale))

@@ -1,27 +1,34 @@
 """Context-parallel attention.
 
 Every CP rank holds, for each packed sequence, the zig-zag chunks ``r`` and ``2cp-1-r`` (``split_cp_inputs``), which
-balances causal work.  Attention of the local queries needs all keys/values that precede them:
+balances causal work.  Attention of the local queries needs all keys / values that precede them in their sequence.
 
-* keys/values are all-gathered over the CP group (differentiable: the backward is a reduce-scatter of dK/dV) and
-  put back into original token order;
-* each local chunk becomes one entry of a variable-length batch whose query block is the chunk and whose key block is
-  the sequence prefix ending with the chunk (bottom-right aligned causal attention), so the regular varlen attention
-  op computes it.
+On a GPU (head sizes the in-tree kernel covers) one autograd function does the whole exchange with in-tree kernels:
 
-This is the all-gather formulation (``cp_comm_type='allgather'``) of the exchange the reference reaches through
-TransformerEngine's ring (``cp_comm_type='p2p'``, ``src/mcore_bridge/config/model_config.py:240``); the results are
-identical, the ring variant only overlaps the transfer with compute.
+* forward: every rank writes its K / V into a symmetric buffer and the peer-memory all-gather kernel
+  (``csrc/comm/dp_collectives.cu``) pulls the other ranks' slices over NVLink; the gathered rows are put into the order
+  of the original token stream, where the keys a query may see form one contiguous range, and the attention kernel
+  (``csrc/attention``, per-query key ranges) runs once over local queries x all keys;
+* backward: the same kernel family gives dQ and the dK / dV of *all* keys; those go back into rank-major order and
+  the peer-memory reduce-scatter kernel returns to every rank the fp32 sum of the gradients of its own keys.
+
+The layout tensors (``CpLayout``) are computed on the device from ``cu_seqlens`` once per micro-batch and shared by all
+layers; nothing synchronises with the host.  The reference reaches the same result through TransformerEngine
+(``cp_comm_type``, ``src/mcore_bridge/config/model_config.py:240``, zig-zag split
+``src/mcore_bridge/utils/megatron_utils.py:48-68``).
+
+Elsewhere (CPU / gloo, head sizes or mask options the kernel lacks) K / V are all-gathered with ``torch.distributed``
+(differentiable) and the masked-softmax reference or the generic attention op computes the same thing.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Optional
 
 import torch
 import torch.distributed as dist
 
 from ..ops.attention import attention_ref
-from ..utils.megatron_utils import cp_gather_index
 from . import state as ps
 
 
@@ -51,75 +58,206 @@ class _AllGatherTokens(torch.autograd.Function):
         return tmp[r * c:(r + 1) * c].contiguous(), None
 
 
-def local_chunk_layout(cu_seqlens: torch.Tensor, cp: int, rank: int) -> List[Tuple[int, int, int]]:
-    """For this rank: ``(local_start, global_start, length)`` of every chunk in local token order."""
-    bounds = [int(x) for x in cu_seqlens.tolist()]
-    out, loc = [], 0
-    for s, e in zip(bounds[:-1], bounds[1:]):
-        c = (e - s) // (2 * cp)
-        out.append((loc, s + rank * c, c))
-        out.append((loc + c, s + (2 * cp - rank - 1) * c, c))
-        loc += 2 * c
-    return out
+@dataclass
+class CpLayout:
+    """Index tensors of one micro-batch under context parallelism (all on the device of the activations).
+
+    "Stream order" is the order of the original token stream; "rank-major" is ``[rank 0's tokens | rank 1's | ...]``,
+    what an all-gather produces."""
+    cp: int
+    rank: int
+    t_local: int
+    gather_index: torch.Tensor      # int64 [T]: rank-major index of the token at each stream position
+    scatter_index: torch.Tensor     # int64 [T]: stream position of the token at each rank-major index
+    q_stream: torch.Tensor          # int64 [T_local]: stream position of each local token
+    q_rel: torch.Tensor             # int64 [T_local]: position of each local token inside its sequence
+    k_lo: torch.Tensor              # int32 [T_local]: first key (stream order) each local query sees
+    k_hi: torch.Tensor              # int32 [T_local]: last key it sees (itself)
+    q_lo: torch.Tensor              # int32 [T]: first local query that can see the key at each stream position
+    q_hi: torch.Tensor              # int32 [T]: last one (empty range where none can)
+    cu_local: torch.Tensor          # int32 [B+1]: sequence boundaries among the local tokens
+    cu_full: torch.Tensor           # int32 [B+1]
+
+
+def compute_layout(cu_seqlens: Optional[torch.Tensor], t_local: int, cp: int, rank: int, device) -> CpLayout:
+    """Vectorised on the device: no ``.tolist()``, no host synchronisation.  Every sequence length must be a multiple
+    of ``2 * cp`` (what ``split_cp_inputs`` requires)."""
+    T = t_local * cp
+    if cu_seqlens is None:
+        cu = torch.tensor([0, T], dtype=torch.int64, device=device)
+    else:
+        cu = cu_seqlens.to(device=device, dtype=torch.int64)
+    B = cu.numel() - 1
+    g = torch.arange(T, device=device)
+    seg = torch.searchsorted(cu[1:].contiguous(), g, right=True).clamp(max=B - 1)
+    S = cu[seg]
+    n = cu[seg + 1] - S
+    h = (n // (2 * cp)).clamp(min=1)
+    rel = g - S
+    c = torch.div(rel, h, rounding_mode='floor').clamp(max=2 * cp - 1)
+    second = c >= cp
+    rk = torch.where(second, 2 * cp - 1 - c, c)
+    L0 = torch.div(S, cp, rounding_mode='floor')
+    off = L0 + torch.where(second, h, torch.zeros_like(h)) + (rel - c * h)
+    gather_index = rk * t_local + off
+    scatter_index = torch.empty_like(gather_index)
+    scatter_index[gather_index] = g
+    q_stream = scatter_index[rank * t_local:(rank + 1) * t_local].contiguous()
+    k_lo = S[q_stream].to(torch.int32)
+    k_hi = q_stream.to(torch.int32)
+    # local queries of a sequence sit at in-sequence positions [r h, (r+1) h) and [(2cp-1-r) h, (2cp-r) h), in that
+    # order; the key at in-sequence position `rel` is seen by those with position >= rel
+    before = (rel - rank * h).clamp(min=0).minimum(h) + (rel - (2 * cp - 1 - rank) * h).clamp(min=0).minimum(h)
+    q_lo = L0 + before
+    q_hi = L0 + 2 * h - 1
+    none = before >= 2 * h
+    q_lo = torch.where(none, torch.ones_like(q_lo), q_lo).to(torch.int32)
+    q_hi = torch.where(none, torch.zeros_like(q_hi), q_hi).to(torch.int32)
+    cu_local = torch.div(cu, cp, rounding_mode='floor').to(torch.int32)
+    return CpLayout(cp, rank, t_local, gather_index, scatter_index, q_stream, (q_stream - S[q_stream]), k_lo, k_hi, q_lo,
+                    q_hi, cu_local, cu.to(torch.int32))
+
+
+def get_layout(ctx, t_local: int, device) -> CpLayout:
+    """The micro-batch's layout, computed on first use and kept in the forward context for the other layers."""
+    lay = ctx.extra.get('cp_layout') if hasattr(ctx, 'extra') else None
+    if lay is None or lay.t_local != t_local or lay.gather_index.device != torch.device(device):
+        lay = compute_layout(ctx.cu_seqlens, t_local, ps.get_world_size('cp'), ps.get_rank_in('cp'), device)
+        if hasattr(ctx, 'extra'):
+            ctx.extra['cp_layout'] = lay
+    return lay
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# exchange through symmetric memory (in-tree peer-memory kernels), with torch.distributed as the other path
+# ---------------------------------------------------------------------------------------------------------------
+_WS = {}
+
+
+def _workspace(tag: str, numel: int, dtype, device):
+    """A symmetric flat tensor of at least ``numel`` elements for the CP group (grown by re-allocation: collective)."""
+    from . import dp_comm
+    key = (tag, dtype)
+    cur = _WS.get(key)
+    if cur is None or cur[1].numel() < numel:
+        if cur is not None:
+            torch.cuda.synchronize()
+        ws, flat = dp_comm.allocate('cp', numel, dtype)
+        _WS[key] = cur = (ws, flat)
+    return cur
+
+
+def _fused_exchange(device) -> bool:
+    from . import dp_comm
+    return dp_comm.usable('cp', device)
+
+
+def _all_gather_kv(k: torch.Tensor, v: torch.Tensor):
+    """``k`` / ``v`` ``[T_local, nkv, d]`` of every rank -> rank-major ``[cp * T_local, nkv, d]`` pair."""
+    cp, r = ps.get_world_size('cp'), ps.get_rank_in('cp')
+    tl = k.shape[0]
+    per = k[0].numel() + v[0].numel()          # elements of one token's K and V
+    if _fused_exchange(k.device):
+        from . import dp_comm
+        n = tl * per
+        ws, flat = _workspace('kv', cp * n, k.dtype, k.device)
+        mine = flat[r * n:(r + 1) * n]
+        mine[:tl * k[0].numel()].view_as(k).copy_(k)
+        mine[tl * k[0].numel():].view_as(v).copy_(v)
+        dp_comm.all_gather_(ws, flat, 0, cp * n)
+        slots = flat[:cp * n].view(cp, n)
+        kg = slots[:, :tl * k[0].numel()].reshape(cp * tl, *k.shape[1:])
+        vg = slots[:, tl * k[0].numel():].reshape(cp * tl, *v.shape[1:])
+        return kg, vg
+    group = ps.get_group('cp')
+    kg = torch.empty((cp * tl, *k.shape[1:]), dtype=k.dtype, device=k.device)
+    vg = torch.empty((cp * tl, *v.shape[1:]), dtype=v.dtype, device=v.device)
+    dist.all_gather_into_tensor(kg, k.contiguous(), group=group)
+    dist.all_gather_into_tensor(vg, v.contiguous(), group=group)
+    return kg, vg
+
+
+def _reduce_scatter_kv_grads(dk_rm: torch.Tensor, dv_rm: torch.Tensor, dtype):
+    """Rank-major gradients of all keys / values on every rank -> this rank's slice of their sum (fp32 accumulation)."""
+    cp, r = ps.get_world_size('cp'), ps.get_rank_in('cp')
+    tl = dk_rm.shape[0] // cp
+    nk, nv = dk_rm[0].numel(), dv_rm[0].numel()
+    if _fused_exchange(dk_rm.device):
+        from . import dp_comm
+        n = tl * (nk + nv)
+        ws, flat = _workspace('dkv', cp * n, torch.float32, dk_rm.device)
+        slots = flat[:cp * n].view(cp, n)
+        slots[:, :tl * nk].copy_(dk_rm.reshape(cp, tl * nk))
+        slots[:, tl * nk:].copy_(dv_rm.reshape(cp, tl * nv))
+        dp_comm.reduce_scatter_(ws, flat, 0, cp * n, 1.0)
+        mine = flat[r * n:(r + 1) * n]
+        dk = mine[:tl * nk].view(tl, *dk_rm.shape[1:]).to(dtype)
+        dv = mine[tl * nk:].view(tl, *dv_rm.shape[1:]).to(dtype)
+        return dk, dv
+    group = ps.get_group('cp')
+    dk = torch.empty((tl, *dk_rm.shape[1:]), dtype=torch.float32, device=dk_rm.device)
+    dv = torch.empty((tl, *dv_rm.shape[1:]), dtype=torch.float32, device=dv_rm.device)
+    dist.reduce_scatter_tensor(dk, dk_rm.float().contiguous(), group=group)
+    dist.reduce_scatter_tensor(dv, dv_rm.float().contiguous(), group=group)
+    return dk.to(dtype), dv.to(dtype)
+
+
+class _GatherKV(torch.autograd.Function):
+    """``(k, v)`` of this rank -> rank-major ``(k, v)`` of all ranks; backward returns to every rank the summed
+    gradients of its own rows.  Both directions run on the peer-memory kernels when the group supports them."""
+
+    @staticmethod
+    def forward(ctx, k, v):
+        ctx.kv_dtype = k.dtype
+        kg, vg = _all_gather_kv(k, v)
+        # the gathered rows live in a workspace the next call reuses: hand out copies
+        return kg.clone(), vg.clone()
+
+    @staticmethod
+    def backward(ctx, dkg, dvg):
+        return _reduce_scatter_kv_grads(dkg, dvg, ctx.kv_dtype)
 
 
 def gather_to_stream_order(x: torch.Tensor, ctx) -> torch.Tensor:
     """``[T_local, ...]`` on every CP rank -> ``[cp * T_local, ...]`` in the order of the original token stream
     (differentiable: the backward reduce-scatters)."""
-    cp = ps.get_world_size('cp')
-    full = _AllGatherTokens.apply(x, 'cp')
-    index = cp_gather_index(ctx.cu_seqlens, x.shape[0] * cp, cp).to(x.device)
-    return full.index_select(0, index)
+    lay = get_layout(ctx, x.shape[0], x.device)
+    return _AllGatherTokens.apply(x, 'cp').index_select(0, lay.gather_index)
 
 
-def stream_index_of_local_tokens(ctx, device) -> torch.Tensor:
+def stream_index_of_local_tokens(ctx, device, t_local: Optional[int] = None) -> torch.Tensor:
     """Position in the original token stream of every token this CP rank holds, in local order."""
-    parts = [torch.arange(g0, g0 + c, device=device)
-             for _, g0, c in local_chunk_layout(ctx.cu_seqlens, ps.get_world_size('cp'), ps.get_rank_in('cp')) if c]
-    return torch.cat(parts)
+    if t_local is None:
+        cu = ctx.cu_seqlens
+        assert cu is not None, 'pass t_local when the batch is not packed'
+        lay = ctx.extra.get('cp_layout')
+        assert lay is not None, 'the layout is created by the first cp_attention / gather_to_stream_order call'
+        return lay.q_stream
+    return get_layout(ctx, t_local, device).q_stream
 
 
-def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ctx, scale: Optional[float] = None,
-                   window=None, sinks=None) -> torch.Tensor:
+def cp_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ctx, scale: Optional[float] = None,
+                 window=None, sinks=None) -> torch.Tensor:
     """``q/k/v`` hold this rank's tokens ``[T_local, heads, d]``; returns ``[T_local, nq, dv]``."""
-    cp = ps.get_world_size('cp')
-    rank = ps.get_rank_in('cp')
-    cu = ctx.cu_seqlens
-    T_local = q.shape[0]
-    kg = _AllGatherTokens.apply(k, 'cp')
-    vg = _AllGatherTokens.apply(v, 'cp')
-    index = cp_gather_index(cu, T_local * cp, cp).to(q.device)
-    k_full, v_full = kg.index_select(0, index), vg.index_select(0, index)      # original token order
-    bounds = [int(x) for x in cu.tolist()]
-    seq_of = {}
-    for s, e in zip(bounds[:-1], bounds[1:]):
-        seq_of[s] = e
-    chunks = local_chunk_layout(cu, cp, rank)
-    # one varlen entry per chunk: queries = the chunk, keys = its sequence from the start up to the chunk's end
-    q_parts, k_parts, v_parts, cu_q, cu_k = [], [], [], [0], [0]
-    starts = sorted(seq_of)
-    import bisect
-    for loc, g0, c in chunks:
-        if c == 0:
-            continue
-        s0 = starts[bisect.bisect_right(starts, g0) - 1]
-        q_parts.append(q[loc:loc + c])
-        k_parts.append(k_full[s0:g0 + c])
-        v_parts.append(v_full[s0:g0 + c])
-        cu_q.append(cu_q[-1] + c)
-        cu_k.append(cu_k[-1] + (g0 + c - s0))
-    qq, kk, vv = torch.cat(q_parts), torch.cat(k_parts), torch.cat(v_parts)
-    cuq = torch.tensor(cu_q, dtype=torch.int32, device=q.device)
-    cuk = torch.tensor(cu_k, dtype=torch.int32, device=q.device)
-    if q.is_cuda and sinks is None and q.dtype in (torch.bfloat16, torch.float16):
-        from flash_attn import flash_attn_varlen_func
-        mq = max(b - a for a, b in zip(cu_q[:-1], cu_q[1:]))
-        mk = max(b - a for a, b in zip(cu_k[:-1], cu_k[1:]))
-        ws = (-1, -1) if window is None else (int(window[0]), 0)
-        vpad = vv if vv.shape[-1] == qq.shape[-1] else torch.nn.functional.pad(vv, (0, qq.shape[-1] - vv.shape[-1]))
-        o = flash_attn_varlen_func(qq, kk, vpad, cuq, cuk, mq, mk, softmax_scale=scale, causal=True, window_size=ws)
-        o = o[..., :vv.shape[-1]]
-    else:
-        o = attention_ref(qq, kk, vv, cuq, cuk, True, scale, window, sinks)
-    # entries were appended in local order, so the output already is in local token order
-    return o
+    lay = get_layout(ctx, q.shape[0], q.device)
+    from ..ops import attention_cuda as ac
+    if window is None and sinks is None and ac.ranges_supported(q, k, v):
+        kg, vg = _GatherKV.apply(k, v)
+        k_full, v_full = kg.index_select(0, lay.gather_index), vg.index_select(0, lay.gather_index)
+        o, _ = ac.attention_ranges(q, k_full, v_full, lay.k_lo, lay.k_hi, lay.q_lo, lay.q_hi, scale)
+        return o
+    if q.is_cuda:
+        from ..ops import _lib
+        if _lib.cuda_enabled():
+            from ..utils.logger import get_logger
+            get_logger().warning_once('context-parallel attention: head size / mask option outside the in-tree kernel; '
+                                      'keys and values are all-gathered with torch.distributed and the generic '
+                                      'attention op runs')
+    k_full = _AllGatherTokens.apply(k, 'cp').index_select(0, lay.gather_index)
+    v_full = _AllGatherTokens.apply(v, 'cp').index_select(0, lay.gather_index)
+    from ..ops.attention import attention_qk_ranges
+    return attention_qk_ranges(q, k_full, v_full, lay, scale, window, sinks)
+
+
+# kept under the name earlier call sites import
+ring_attention = cp_attention

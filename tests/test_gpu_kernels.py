@@ -477,3 +477,69 @@ def test_gemm_cta_pair(M, N, K):
     acc = torch.randn(N, K, device=DEV, dtype=torch.float32)
     ref_tn = acc + dy.float().t() @ x.float()
     close(gemm.mm_tn(dy, x, out=acc, accumulate=True, force_bn=512), ref_tn, 1e-5)
+
+
+@pytest.mark.parametrize('d,nq,nkv', [(128, 8, 2), (64, 4, 4)])
+@pytest.mark.parametrize('cp', [2, 4])
+def test_attention_ranges_context_parallel_layout(d, nq, nkv, cp):
+    """The per-query key-range kernels on the zig-zag layout of every context-parallel rank (emulated on one GPU):
+    output and all gradients against the masked-softmax reference on the whole stream."""
+    from mcore_bridge_b200.ops import attention_cuda as ac
+    from mcore_bridge_b200.ops.attention import attention_ref
+    from mcore_bridge_b200.parallel.context_parallel import compute_layout
+    torch.manual_seed(4)
+    lens = [8 * cp * 20, 8 * cp * 3, 8 * cp * 41, 8 * cp * 7]           # multiples of 2 * cp, tiles straddle sequences
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    q = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16)
+    do = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16)
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    ref = attention_ref(qr, kr, vr, cu, cu)
+    for rank in range(cp):
+        lay = compute_layout(cu, T // cp, cp, rank, torch.device(DEV))
+        assert torch.equal(lay.scatter_index[lay.gather_index], torch.arange(T, device=DEV))
+        ql = q[lay.q_stream].clone().requires_grad_()
+        kf, vf = k.clone().requires_grad_(), v.clone().requires_grad_()
+        o, lse = ac.attention_ranges(ql, kf, vf, lay.k_lo, lay.k_hi, lay.q_lo, lay.q_hi)
+        assert rel(o, ref[lay.q_stream]) < 2e-2
+        o.backward(do[lay.q_stream])
+        gq, gk, gv = torch.autograd.grad(ref[lay.q_stream], (qr, kr, vr), do[lay.q_stream].float(), retain_graph=True)
+        assert rel(ql.grad, gq[lay.q_stream]) < 3e-2
+        assert rel(kf.grad, gk) < 3e-2 and rel(vf.grad, gv) < 3e-2
+        worst = ((kf.grad.float() - gk).flatten(1).norm(dim=1).max() / gk.flatten(1).norm(dim=1).mean()).item()
+        assert worst < 0.15, worst
+
+
+def test_attention_ranges_bidirectional_and_empty_rows():
+    """Non-causal packed attention (every query sees its whole sequence) and queries that see nothing."""
+    from mcore_bridge_b200.ops import attention_cuda as ac
+    from mcore_bridge_b200.ops.attention import attention_ref
+    torch.manual_seed(5)
+    lens = [300, 77, 513, 134]
+    T, nq, nkv, d = sum(lens), 4, 2, 128
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    seg = torch.searchsorted(cu[1:].long().contiguous(), torch.arange(T, device=DEV), right=True)
+    k_lo = cu[:-1][seg].to(torch.int32)
+    k_hi = (cu[1:][seg] - 1).to(torch.int32)
+    q_lo, q_hi = k_lo.clone(), k_hi.clone()
+    # the queries of the second sequence see nothing
+    dead = seg == 1
+    k_lo[dead], k_hi[dead] = 1, 0
+    q_lo[dead], q_hi[dead] = 1, 0
+    q = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    do = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16)
+    o, lse = ac.attention_ranges(q, k, v, k_lo, k_hi, q_lo, q_hi)
+    o.backward(do)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = attention_ref(qr, kr, vr, cu, cu, causal=False)
+    live = ~dead
+    assert rel(o[live], ref[live]) < 2e-2
+    assert o[dead].abs().max().item() == 0.0 and torch.isinf(lse[:, dead]).all()
+    (ref[live] * do[live].float()).sum().backward()
+    assert rel(q.grad[live], qr.grad[live]) < 3e-2 and q.grad[dead].abs().max().item() == 0.0
+    assert rel(k.grad, kr.grad) < 3e-2 and rel(v.grad, vr.grad) < 3e-2
+    assert torch.isfinite(k.grad.float()).all() and torch.isfinite(q.grad.float()).all()
