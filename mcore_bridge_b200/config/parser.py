@@ -188,7 +188,11 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
         res['moe_router_load_balancing_type'] = 'seq_aux_loss'
         if llm == 'dots1':
             res['moe_router_score_function'] = 'sigmoid'
-        elif llm == 'deepseek_v32':
+        if llm in ('deepseek_v3', 'kimi_k2', 'deepseek_v32'):
+            # these architectures always route with sigmoid scores; a config that leaves `scoring_func` out (the
+            # Transformers config class has no such field) must not fall back to softmax
+            res.setdefault('moe_router_score_function', 'sigmoid')
+        if llm == 'deepseek_v32':
             res['experimental_attention_variant'] = 'dsa'
         elif llm == 'deepseek_v4':
             res.setdefault('v_head_dim', res.get('kv_channels'))

@@ -126,3 +126,44 @@ def test_generic_family_logits_and_roundtrip(name, tmp_path):
     assert set(exported) == set(disk), set(exported) ^ set(disk)
     for k, v in disk.items():
         assert torch.equal(exported[k], v), k
+
+
+@pytest.mark.parametrize('alias,base', [('kimi_k2', 'deepseek_v3'), ('mimo', 'qwen2'), ('internlm3', 'llama'),
+                                        ('deepseek_v3', 'deepseek_v3')])
+def test_alias_families_match_their_architecture(alias, base, tmp_path):
+    """Model types that reuse another family's architecture (Kimi-K2 = DeepSeek-V3, MiMo = Qwen2 plus MTP layers that
+    a plain checkpoint lacks, InternLM3 = Llama): the config parser has to give them the same model, checked by logits
+    against the architecture's Transformers class and a byte-exact round trip."""
+    import transformers as tf
+    common, cases = _sweep_cases()
+    cases['deepseek_v3'] = ('DeepseekV3Config', 'DeepseekV3ForCausalLM',
+                            dict(q_lora_rank=32, kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                                 intermediate_size=256, moe_intermediate_size=64, n_routed_experts=8,
+                                 num_experts_per_tok=2, n_shared_experts=1, first_k_dense_replace=1, n_group=2,
+                                 topk_group=1, num_key_value_heads=4, routed_scaling_factor=2.5, norm_topk_prob=True))
+    cname, mname, kw = cases[base]
+    torch.manual_seed(0)
+    c = getattr(tf, cname)(**{**common, **kw})
+    hf = getattr(tf, mname)(c).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            p.normal_(0, 0.05) if p.dim() >= 2 else p.normal_(1.0 if 'norm' in n else 0.0, 0.05)
+        for n, b in hf.named_buffers():
+            if n.endswith('e_score_correction_bias'):
+                b.normal_(0, 0.1)
+    d = str(tmp_path / 'ckpt')
+    hf.save_pretrained(d)
+    c.model_type = alias                                   # what the published config of the alias family says
+    kw_mcore = hf_to_mcore_config(c)
+    assert kw_mcore.get('hf_model_type', alias) == alias or kw_mcore.get('llm_model_type') == alias
+    cfg = ModelConfig(**kw_mcore, params_dtype=torch.float32)
+    model = get_mcore_model(cfg)[0].eval()
+    cfg.bridge.load_weights([model], d)
+    ids = torch.randint(0, 256, (2, 64), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        assert torch.allclose(model(ids), hf(ids).logits, atol=3e-5)
+    disk = load_file(os.path.join(d, 'model.safetensors'))
+    exported = dict(cfg.bridge.export_weights([model]))
+    assert set(exported) == set(disk), set(exported) ^ set(disk)
+    for k, v in disk.items():
+        assert torch.equal(exported[k], v), k
