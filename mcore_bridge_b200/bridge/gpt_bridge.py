@@ -322,6 +322,9 @@ class GPTBridge:
         has = model is not None and getattr(model, 'post_process', False)
         dec = model.decoder if has else None
         self._direct(dec, 'final_layernorm.weight', hf_sd, self.hf_final_layernorm_key, to_mcore)
+        if cfg.enable_hyper_connections:
+            head_prefix = self.hf_final_layernorm_key.rsplit('norm.weight', 1)[0]
+            self._set_hyper_connection(dec.hc_head if has else None, hf_sd, head_prefix, 'head', to_mcore)
         if cfg.task_type == 'seq_cls':
             self._direct(model if has else None, 'output_layer.weight', hf_sd, self.hf_score_key, to_mcore)
             return
@@ -633,6 +636,10 @@ class GPTBridge:
         cfg = self.config
         router = mlp.router if mlp is not None else None
         self._direct(router, 'weight', hf_sd, prefix + self.hf_gate_key, to_mcore)
+        if cfg.moe_n_hash_layers:
+            # hash-routed layers carry the token-id -> experts table next to the gate
+            hashed = router if (router is not None and getattr(router, 'is_hash_layer', False)) else None
+            self._direct(hashed, 'tid2eid', hf_sd, prefix + self.hf_gate_key.rsplit('.', 1)[0] + '.tid2eid', to_mcore)
         if cfg.moe_router_enable_expert_bias:
             self._direct(router, 'expert_bias', hf_sd, prefix + self.hf_expert_bias_key, to_mcore, optional=True,
                          to_mg=lambda w: w.reshape(-1),
@@ -660,9 +667,35 @@ class GPTBridge:
                          to_mcore)
             self._set_dense_mlp(mlp, hf_sd, mp, to_mcore)
 
+    def _set_hyper_connection(self, hc, hf_sd, prefix: str, name: str, to_mcore: bool):
+        """One hyper-connection module <-> ``hc_{name}_fn`` (projection), ``hc_{name}_base`` (bias) and
+        ``hc_{name}_scale`` (the scales stacked ``[pre, post, res]``; the block's output contraction has only the
+        first).  Parity: reference ``src/mcore_bridge/bridge/gpt_bridge.py:1653-1673``."""
+        self._direct(hc, 'mapping_proj.weight', hf_sd, f'{prefix}hc_{name}_fn', to_mcore)
+        self._direct(hc, 'bias', hf_sd, f'{prefix}hc_{name}_base', to_mcore)
+        alphas = ['alpha_pre', 'alpha_post', 'alpha_res'] if name != 'head' else ['alpha_pre']
+        key = f'{prefix}hc_{name}_scale'
+        if to_mcore:
+            if hc is None:
+                return
+            scale = self._load_hf(hf_sd, key).reshape(-1)
+            with torch.no_grad():
+                for i, a in enumerate(alphas):
+                    getattr(hc, a).copy_(scale[i:i + 1].to(getattr(hc, a).dtype))
+            return
+        if not self._agree(hc is not None, self._device):
+            return
+        local = None if hc is None else torch.cat([getattr(hc, a).detach().reshape(1) for a in alphas])
+        self._emit(hf_sd, key, self._broadcast_pp(local, self._device))
+
     def _set_layer_state(self, layer, hf_sd, prefix: str, layer_idx: int, to_mcore: bool):
         self._set_layer_attn(layer, hf_sd, prefix, to_mcore)
         self._set_layer_mlp(layer, hf_sd, prefix, layer_idx, to_mcore)
+        if self.config.enable_hyper_connections:
+            self._set_hyper_connection(getattr(layer, 'self_attention_hyper_connection', None) if layer is not None
+                                       else None, hf_sd, prefix, 'attn', to_mcore)
+            self._set_hyper_connection(getattr(layer, 'mlp_hyper_connection', None) if layer is not None else None,
+                                       hf_sd, prefix, 'ffn', to_mcore)
 
     # ------------------------------------------------------------------ walker
     def _find_layer(self, mg_models: List[nn.Module], layer_idx: int):

@@ -213,8 +213,9 @@ class ModelConfig:
     recompute_method: Optional[Literal['uniform', 'block']] = None
     recompute_num_layers: Optional[int] = None
     recompute_modules: Optional[List[str]] = None
-    cpu_offloading: bool = False
-    fine_grained_activation_offloading: bool = False
+    cpu_offloading: bool = False                      # saved activations of the first layers live in pinned host memory
+    cpu_offloading_num_layers: Optional[int] = None   # how many leading layers of a stage offload (default: all)
+    fine_grained_activation_offloading: bool = False  # per-module offload lists: not implemented (rejected below)
 
     # initialisation
     perform_initialization: bool = False
@@ -242,6 +243,16 @@ class ModelConfig:
         from ..models.register import get_mcore_model_type, get_model_meta
         from ..parallel import state as ps
         self._format_config()
+        # options that exist in the reference's config but have no implementation here are refused instead of being
+        # silently ignored
+        if self.fine_grained_activation_offloading:
+            raise NotImplementedError('fine_grained_activation_offloading is not implemented; use cpu_offloading '
+                                      '(whole-layer activation offload) or activation recompute')
+        if self.experimental_attention_variant == 'dsv4_hybrid' or any(self.csa_compress_ratios or []):
+            raise NotImplementedError(
+                'compressed sparse attention (DeepSeek-V4 hybrid attention) is not implemented: the reference takes it '
+                'from a Megatron-Core development branch that is not part of its own source tree.  The other '
+                'DeepSeek-V4 pieces (hyper-connections, hash-routed MoE layers) are available on their own.')
         if isinstance(self.moe_router_dtype, str) and self.moe_router_dtype.lower() == 'none':
             self.moe_router_dtype = None
         if self.moe_shared_expert_intermediate_size == 0:

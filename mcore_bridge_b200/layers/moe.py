@@ -60,7 +60,7 @@ class TopKRouter(nn.Module):
     ``src/mcore_bridge/model/modules/topk_router.py:7-21``).
     """
 
-    def __init__(self, config):
+    def __init__(self, config, is_hash_layer: bool = False):
         super().__init__()
         self.config = config
         self.num_experts = config.num_moe_experts
@@ -74,6 +74,11 @@ class TopKRouter(nn.Module):
             mark_sequence_parallel(self.bias, config)
         else:
             self.register_parameter('bias', None)
+        # hash-routed layers (the first ``moe_n_hash_layers`` MoE layers of DeepSeek-V4): the experts of a token are a
+        # fixed function of its id, read from the table ``tid2eid``; the gate still provides the mixing weights
+        self.is_hash_layer = bool(is_hash_layer)
+        if self.is_hash_layer:
+            self.register_buffer('tid2eid', torch.zeros(config.padded_vocab_size, self.topk, dtype=torch.int64))
         self.enable_expert_bias = bool(config.moe_router_enable_expert_bias)
         if self.enable_expert_bias:
             self.register_buffer('expert_bias', torch.zeros(self.num_experts, dtype=torch.float32))
@@ -103,9 +108,37 @@ class TopKRouter(nn.Module):
         self.expert_bias += self.config.moe_router_bias_update_rate * torch.sign(load.mean() - load)
         self.local_tokens_per_expert.zero_()
 
-    def forward(self, x: torch.Tensor, padding_mask: Optional[torch.Tensor] = None, seg_ids=None, num_seqs=None):
+    def _hash_route(self, logits: torch.Tensor, input_ids: torch.Tensor):
+        """Experts from the id table, weights from the gate's scores of those experts (normalised over the ``k``
+        experts unless the scores are pre-softmax probabilities, then scaled like the learned routing)."""
+        cfg = self.config
+        if input_ids is None:
+            raise ValueError('hash-routed MoE layers need the token ids (ForwardContext.input_ids)')
+        ids = input_ids.reshape(-1)
+        tp = ps.get_world_size('tp')
+        if ids.numel() == logits.shape[0] * tp and cfg.sequence_parallel and tp > 1:
+            ids = ids.chunk(tp)[ps.get_rank_in('tp')]         # sequence parallelism: this rank's slice of the tokens
+        if ids.numel() != logits.shape[0]:
+            raise ValueError(f'hash routing: {ids.numel()} token ids for {logits.shape[0]} tokens (under sequence '
+                             'parallelism pass the ids of this rank\'s tokens)')
+        idx = self.tid2eid[ids.clamp(min=0)]
+        scores = torch.sigmoid(logits.float()) if cfg.moe_router_score_function == 'sigmoid' else \
+            torch.softmax(logits.float(), dim=-1)
+        probs = scores.gather(1, idx)
+        if self.topk > 1 and cfg.moe_router_score_function == 'sigmoid':
+            probs = probs / probs.sum(-1, keepdim=True).clamp_min(1e-20)
+        if cfg.moe_router_topk_scaling_factor:
+            probs = probs * cfg.moe_router_topk_scaling_factor
+        return probs.to(logits.dtype), idx, scores
+
+    def forward(self, x: torch.Tensor, padding_mask: Optional[torch.Tensor] = None, seg_ids=None, num_seqs=None,
+                input_ids: Optional[torch.Tensor] = None):
         cfg = self.config
         logits = self.gating(x)
+        if self.is_hash_layer:
+            probs, idx, _ = self._hash_route(logits, input_ids)
+            self._apply_expert_bias(idx, padding_mask)
+            return probs, idx
         if cfg.moe_z_loss_coeff:
             z = moe_ops.z_loss(logits, cfg.moe_z_loss_coeff)
             logits = moe_ops.MoEAuxLossAutoScaler.apply(logits, z)
@@ -282,7 +315,9 @@ class MoELayer(nn.Module):
         self.num_experts = config.num_moe_experts
         assert self.num_experts % self.ep == 0
         self.num_local_experts = self.num_experts // self.ep
-        self.router = TopKRouter(config)
+        # the first ``moe_n_hash_layers`` MoE layers of the model route by token id
+        moe_before = sum(config.moe_layer_pattern()[:max(0, min(layer_number, config.num_layers) - 1)])
+        self.router = TopKRouter(config, is_hash_layer=moe_before < (config.moe_n_hash_layers or 0))
         self.experts = GroupedMLP(config, self.num_local_experts)
         if config.moe_shared_expert_intermediate_size:
             self.shared_experts = SharedExpertMLP(config, config.moe_shared_expert_intermediate_size)
@@ -350,7 +385,7 @@ class MoELayer(nn.Module):
         ret = M.all_to_all(back, in_splits, out_splits, 'ep')    # rows in `order`
         return moe_ops.unpermute(ret, src_token[order], torch.arange(ret.shape[0], device=x.device), T, None)
 
-    def _forward_fused(self, x, padding_mask, seg_ids, num_seqs):
+    def _forward_fused(self, x, padding_mask, seg_ids, num_seqs, input_ids=None):
         """Router, exchange and combine on the in-tree kernels (``layers/moe_fused.py``)."""
         from . import moe_fused as F
         cfg = self.config
@@ -361,6 +396,7 @@ class MoELayer(nn.Module):
         st = self._fused.begin(T, H, x.device)
         lb = cfg.moe_router_load_balancing_type
         kernel_router = (F.router_supported(self.num_experts, r.topk, cfg.moe_router_num_groups)
+                         and not r.is_hash_layer
                          and not (self.training and cfg.moe_aux_loss_coeff and lb == 'seq_aux_loss')
                          and not cfg.moe_z_loss_coeff
                          # softmax scores with a selection bias (Ernie-4.5) stay on the torch router
@@ -394,7 +430,7 @@ class MoELayer(nn.Module):
                 probs = moe_ops.MoEAuxLossAutoScaler.apply(probs, aux)
                 _track('load_balancing_loss', aux / coeff)
         else:
-            probs, idx = r(self._router_input(x), padding_mask, seg_ids, num_seqs)
+            probs, idx = r(self._router_input(x), padding_mask, seg_ids, num_seqs, input_ids)
             self._fused.publish_routing(st, idx)
             idx = idx.to(torch.int32)
         probs = self._post_route(probs, idx)
@@ -408,14 +444,16 @@ class MoELayer(nn.Module):
             y = y + self.shared_experts(x)
         return y
 
-    def forward(self, x: torch.Tensor, padding_mask: Optional[torch.Tensor] = None, seg_ids=None, num_seqs=None):
-        """``x [T_local, H]`` -> ``[T_local, H]``."""
+    def forward(self, x: torch.Tensor, padding_mask: Optional[torch.Tensor] = None, seg_ids=None, num_seqs=None,
+                input_ids: Optional[torch.Tensor] = None):
+        """``x [T_local, H]`` -> ``[T_local, H]``.  ``input_ids`` (this rank's token ids) is only read by hash-routed
+        layers."""
         cfg = self.config
         T, H = x.shape
         from . import moe_fused
         if moe_fused.available(x) and ps.get_world_size('etp') == 1 and H % 8 == 0:
-            return self._forward_fused(x, padding_mask, seg_ids, num_seqs)
-        probs, idx = self.router(self._router_input(x), padding_mask, seg_ids, num_seqs)
+            return self._forward_fused(x, padding_mask, seg_ids, num_seqs, input_ids)
+        probs, idx = self.router(self._router_input(x), padding_mask, seg_ids, num_seqs, input_ids)
         probs = self._post_route(probs, idx)
         etp = ps.get_world_size('etp')
         x_in = x

@@ -87,6 +87,12 @@ class TransformerBlock(nn.Module):
         self.layers = nn.ModuleList([self.layer_cls(config, self.layer_offset + i + 1) for i in range(n)])
         self.final_layernorm = Norm(config, config.hidden_size) if post_process else None
         self.input_tensor = None
+        # hyper-connections: the streams are contracted where the final norm lives (the last stage); earlier stages
+        # pass all n streams on (the activation sent to the next stage is n x as wide)
+        self.hc_head = None
+        if config.enable_hyper_connections and post_process:
+            from ..layers.hyper_connection import HyperConnection
+            self.hc_head = HyperConnection(config, kind='head')
 
     def set_input_tensor(self, t):
         self.input_tensor = t
@@ -109,6 +115,24 @@ class TransformerBlock(nn.Module):
         rows = mask.reshape(-1).nonzero(as_tuple=True)[0].to(h.device)
         return h.index_add(0, rows, ds[layer_index].to(device=h.device, dtype=h.dtype))
 
+    def _offload_context(self):
+        """``cpu_offloading``: the tensors the first ``cpu_offloading_num_layers`` layers save for backward are
+        moved to pinned host memory and brought back when their backward runs (parity: the offload hooks of
+        reference ``src/mcore_bridge/model/modules/transformer_block.py:468-470``).  Layers under full recompute
+        save only their input, so offloading applies to the layers that keep their activations."""
+        import contextlib
+        cfg = self.config
+        if not (cfg.cpu_offloading and self.training and torch.is_grad_enabled()):
+            return lambda i: contextlib.nullcontext()
+        n_off = cfg.cpu_offloading_num_layers if cfg.cpu_offloading_num_layers is not None else len(self.layers)
+        pin = torch.cuda.is_available()
+
+        def ctx_for(i):
+            if i < n_off:
+                return torch.autograd.graph.save_on_cpu(pin_memory=pin)
+            return contextlib.nullcontext()
+        return ctx_for
+
     def _run(self, start: int, end: int):
         def fn(h, ctx):
             for i in range(start, end):
@@ -120,6 +144,10 @@ class TransformerBlock(nn.Module):
         cfg = self.config
         if not self.pre_process:
             hidden = self.input_tensor  # activation received from the previous pipeline stage
+        elif cfg.enable_hyper_connections:
+            from ..layers.hyper_connection import input_expand
+            hidden = input_expand(hidden, cfg.num_residual_streams)      # [T, C] -> [T, n * C]
+        offload = self._offload_context()
         taps: List[torch.Tensor] = []
         want = set(cfg.extract_layer_indices or [])
         n = len(self.layers)
@@ -138,11 +166,15 @@ class TransformerBlock(nn.Module):
                 hidden = checkpoint(self._run(i, j), hidden, ctx, use_reentrant=False)
             else:
                 j = i + 1
-                hidden = self._after_layer(self.layers[i](hidden, ctx), ctx, i)
+                with offload(i):
+                    hidden = self._after_layer(self.layers[i](hidden, ctx), ctx, i)
             for g in range(i, j):
                 if (self.layer_offset + g) in want:
                     taps.append(hidden)
             i = j
+        if self.hc_head is not None:
+            ctx.extra['mhc_multistream'] = hidden                        # the MTP layers read the uncontracted streams
+            hidden = self.hc_head.contract(hidden)
         if self.final_layernorm is not None:
             hidden = self.final_layernorm(hidden)
         if want:

@@ -64,27 +64,44 @@ class TransformerLayer(nn.Module):
         else:
             self.pre_mlp_layernorm = None
             self.mlp = MLP(config, fuse_input_norm=True)
+        self.self_attention_hyper_connection = self.mlp_hyper_connection = None
+        if config.enable_hyper_connections:
+            from ..layers.hyper_connection import HyperConnection
+            self.self_attention_hyper_connection = HyperConnection(config)
+            self.mlp_hyper_connection = HyperConnection(config)
         if config.post_sublayer_layernorm:
             # sandwich norms live on the sub-modules so their names match the checkpoint layout
             self.self_attention.post_self_attn_layernorm = Norm(config, config.hidden_size)
             self.mlp.post_mlp_layernorm = Norm(config, config.hidden_size)
 
     def _attention(self, hidden, ctx):
+        hc = self.self_attention_hyper_connection
+        if hc is not None:
+            streams = hidden                                 # [T, n * C]: the sub-layer reads a mix of the streams
+            hidden, post, res = hc.pre(streams)
         x = hidden if self.input_layernorm is None else self.input_layernorm(hidden)
         out = self.self_attention(x, ctx)
         if self.config.post_sublayer_layernorm:
             out = self.self_attention.post_self_attn_layernorm(out)
+        if hc is not None:
+            return hc.post(out, streams, post, res)
         return hidden + out
 
     def _mlp(self, hidden, ctx: ForwardContext):
         cfg = self.config
+        hc = self.mlp_hyper_connection
+        if hc is not None:
+            streams = hidden
+            hidden, post, res = hc.pre(streams)
         x = hidden if self.pre_mlp_layernorm is None else self.pre_mlp_layernorm(hidden)
         if self.is_moe:
-            out = self.mlp(x, ctx.padding_mask, ctx.seg_ids, ctx.num_seqs)
+            out = self.mlp(x, ctx.padding_mask, ctx.seg_ids, ctx.num_seqs, ctx.input_ids)
         else:
             out = self.mlp(x)
         if cfg.post_sublayer_layernorm:
             out = self.mlp.post_mlp_layernorm(out)
+        if hc is not None:
+            return hc.post(out, streams, post, res)
         return hidden + out
 
     def _mlp_padding_free(self, hidden, ctx: ForwardContext):
