@@ -126,7 +126,7 @@ int mcb_gemm_bf16(const void* A, long long a_inner, long long a_outer, long long
   p.C = C; p.ldc = ldc; p.c_group_stride = c_group_stride;
   p.bias = bias; p.c_fp32 = c_fp32; p.accumulate = accumulate; p.alpha = alpha;
   p.mode = mode; p.num_groups = num_groups; p.offsets = offsets; p.b_group_rows = b_group_rows;
-  p.epilogue = EPI_NONE; p.aux = nullptr; p.ld_aux = 0;
+  p.epilogue = EPI_NONE;
   p.status = status;
 
   if (pair) {
@@ -141,6 +141,55 @@ int mcb_gemm_bf16(const void* A, long long a_inner, long long a_outer, long long
   else if (bn == 128) e = launch_major<128>(a_mn, b_mn, ta, tb, p, grid, stream);
   else e = launch_major<64>(a_mn, b_mn, ta, tb, p, grid, stream);
   return (int)e;
+}
+
+// Fused language-model head on the GEMM engine: logits = A[M,K] . B[N,K]^T (both K-major) are consumed by the
+// epilogue and never stored.
+//   grad == 0: `part` [M, ceil(N/256), 2] receives per row and 256-column tile (max, sum exp(logit - max)); `tgt` [M]
+//              the logit of the row's label when its column is in [col0, col0 + N) (untouched otherwise: zero it first)
+//   grad != 0: C [M, N] bf16 = (exp(logit - lse[row]) - [col0 + column == label]) * g[row]
+int mcb_gemm_ce_bf16(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K,
+                     const long long* labels, int col0, float* part, float* tgt, const float* lse, const float* g,
+                     void* C, long long ldc, int grad, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (labels == nullptr || (grad ? (C == nullptr || lse == nullptr || g == nullptr) : (part == nullptr || tgt == nullptr)))
+    return -2;
+  constexpr int BN = 256;
+  const int sms = device_sm_count();
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, GEMM_BK, GEMM_BM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, GEMM_BK, BN);
+  if (rc) return rc;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.alpha = 1.f; p.mode = GEMM_DENSE;
+  p.epilogue = grad ? EPI_CE_GRAD : EPI_CE_STATS;
+  p.ce_labels = labels; p.ce_col0 = col0; p.ce_part = part; p.ce_tgt = tgt; p.ce_lse = lse; p.ce_g = g;
+  p.status = status;
+  const long long tiles = (long long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  static bool cfg[2] = {false, false};
+  cudaError_t e;
+  if (grad) {
+    auto kern = gemm_bf16_sm100_kernel<BN, false, false, EPI_CE_GRAD>;
+    if (!cfg[1]) {
+      if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL)) != cudaSuccess)
+        return (int)e;
+      cfg[1] = true;
+    }
+    kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(ta, tb, p);
+  } else {
+    auto kern = gemm_bf16_sm100_kernel<BN, false, false, EPI_CE_STATS>;
+    if (!cfg[0]) {
+      if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL)) != cudaSuccess)
+        return (int)e;
+      cfg[0] = true;
+    }
+    kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(ta, tb, p);
+  }
+  return (int)cudaGetLastError();
 }
 
 }  // extern "C"

@@ -24,7 +24,11 @@ constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_MAX_GROUPS = 512;
 
 enum GemmMode : int { GEMM_DENSE = 0, GEMM_GROUPED_M = 1, GEMM_GROUPED_K = 2 };
-enum GemmEpilogue : int { EPI_NONE = 0, EPI_SWIGLU = 1 };
+// Epilogues.  The cross-entropy ones belong to the fused language-model head (logits = h . W^T are never stored):
+//   EPI_CE_STATS  per row and column tile, the running maximum and sum of exp(logit - max) over the tile's columns go
+//                 to `ce_part`, and the logit of the row's label (when its column lies in the tile) to `ce_tgt`
+//   EPI_CE_GRAD   C = (exp(logit - lse[row]) - [column == label]) * g[row] in bf16: the gradient w.r.t. the logits
+enum GemmEpilogue : int { EPI_NONE = 0, EPI_CE_STATS = 2, EPI_CE_GRAD = 3 };
 
 struct GemmParams {
   int M, N, K;          // dense: the problem.  grouped-M: M = upper bound on padded rows.
@@ -41,8 +45,12 @@ struct GemmParams {
   const int* offsets;   // [G+1] device ints; multiples of 128
   int b_group_rows;     // grouped-M: rows between consecutive groups in the 2-D view of B
   int epilogue;         // EPI_*
-  void* aux;            // EPI_SWIGLU: optional bf16 [M, N] pre-activation copy (gate|up) for backward
-  long long ld_aux;
+  const long long* ce_labels;  // [M] global label of each row (cross-entropy epilogues)
+  int ce_col0;                 // global index of this shard's column 0 (vocab-parallel head)
+  float* ce_part;              // EPI_CE_STATS: [M, tiles_n, 2] (max, sum exp) per row and column tile
+  float* ce_tgt;               // EPI_CE_STATS: [M] label logit, written by the tile that holds the label's column
+  const float* ce_lse;         // EPI_CE_GRAD: [M] log-sum-exp over the whole vocabulary
+  const float* ce_g;           // EPI_CE_GRAD: [M] upstream gradient of each row's loss
   int* status;          // device status word, 0 = ok
 };
 
@@ -125,7 +133,7 @@ struct TileScheduler {
   }
 };
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int EPI = EPI_NONE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const GemmParams p) {
@@ -282,6 +290,75 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           p.bias ? reinterpret_cast<const __nv_bfloat16*>(p.bias) + (p.mode == GEMM_GROUPED_M ? (long long)c.group * p.N : 0)
                  : nullptr;
       const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+      if constexpr (EPI == EPI_CE_STATS || EPI == EPI_CE_GRAD) {
+        // fused language-model head: one thread owns one row of the tile
+        constexpr float LOG2E = 1.4426950408889634f;
+        const int label_col = row_ok ? (int)(p.ce_labels[row] - p.ce_col0) - c.n0 : -1;   // column inside this tile
+        float run_m = -INFINITY, run_s = 0.f, tgt = 0.f;
+        const float lse2 = (EPI == EPI_CE_GRAD && row_ok) ? p.ce_lse[row] * LOG2E : 0.f;
+        const float g = (EPI == EPI_CE_GRAD && row_ok) ? p.ce_g[row] : 0.f;
+#pragma unroll 1
+        for (int cc = 0; cc < BN; cc += 32) {
+          if (c.n0 + cc >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + cc, r);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          const int valid = min(32, p.N - (c.n0 + cc));
+          if constexpr (EPI == EPI_CE_STATS) {
+            float cm = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) cm = fmaxf(cm, __uint_as_float(r[j]) * p.alpha);
+            const float nm = fmaxf(run_m, cm);
+            float add = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) add += exp2f((__uint_as_float(r[j]) * p.alpha - nm) * LOG2E);
+            run_s = run_s * exp2f((run_m - nm) * LOG2E) + add;
+            run_m = nm;
+            const int lj = label_col - cc;
+            if (lj >= 0 && lj < valid) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j == lj) tgt = __uint_as_float(r[j]) * p.alpha;
+            }
+          } else {
+            const int lj = label_col - cc;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = (exp2f(__uint_as_float(r[j]) * p.alpha * LOG2E - lse2) - (j == lj ? 1.f : 0.f)) * g;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + c.n0 + cc;
+            if (vec_ok && valid == 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o;
+                o.x = pack_bf16x2(v[j], v[j + 1]);
+                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(dst + j) = o;
+              }
+            } else {
+              for (int j = 0; j < valid; ++j) dst[j] = __float2bfloat16(v[j]);
+            }
+          }
+        }
+        if constexpr (EPI == EPI_CE_STATS) {
+          if (row_ok) {
+            float* part = p.ce_part + ((long long)row * sched.tiles_n + c.n0 / BN) * 2;
+            part[0] = run_m;
+            part[1] = run_s;
+            if (label_col >= 0 && label_col < BN && c.n0 + label_col < p.N) p.ce_tgt[row] = tgt;
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+        ++lt;
+        continue;
+      }
 #pragma unroll 1
       for (int cc = 0; cc < BN; cc += 32) {
         if (c.n0 + cc >= p.N) break;  // whole chunk out of range (uniform across the warp)

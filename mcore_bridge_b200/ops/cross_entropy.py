@@ -3,10 +3,13 @@
 * :func:`vocab_parallel_cross_entropy` — logits sharded on the vocab dim; max / sum-exp / target-logit
   reduced over the tensor-parallel group (parity: the ``compute_language_model_loss`` call at reference
   ``src/mcore_bridge/model/gpt_model.py:577``).
-* :func:`fused_linear_cross_entropy` — never materialises ``[T, V]``: the head GEMM runs per token chunk,
-  the softmax statistics come from a one-pass kernel over the chunk, and backward recomputes the chunk's
-  logits, turns them into ``dlogits`` in place and feeds the two gradient GEMMs.  Only ``[T]`` statistics are
-  kept between forward and backward.
+* :func:`fused_linear_cross_entropy` — never materialises the logits.  On a GPU the head GEMM's epilogue reduces
+  every 128 x 256 accumulator tile to per-row (max, sum-exp) partials and picks out the label's logit
+  (``csrc/gemm``, ``EPI_CE_STATS``); the partials of a row are combined, the tensor-parallel ranks exchange their
+  ``[T]`` statistics through peer memory (``parallel/dp_comm.py`` all-gather kernel; ``torch.distributed`` elsewhere)
+  and the loss follows.  Backward runs the head GEMM again per token chunk with an epilogue that writes the
+  gradient of the logits directly in bf16 (``EPI_CE_GRAD``) and feeds it to the two gradient GEMMs.  Only ``[T]``
+  statistics are kept between forward and backward.  On CPU the same chunked algorithm runs on torch ops.
 
 Both return the per-token loss ``[T]`` in fp32 (the caller masks and averages).
 """
@@ -88,6 +91,77 @@ def _dlogits(logits, labels, vocab_start, lse, g, out_dtype):
     return (p * g[:, None]).to(out_dtype)
 
 
+_STATS_WS = {}
+
+
+def _reduce_stats_peer(m, s, tgt, group_name):
+    """Same combination as :func:`_reduce_stats`, with the ranks' ``[3, T]`` statistics exchanged by the in-tree
+    peer-memory all-gather kernel instead of two NCCL all-reduces."""
+    from ..parallel import dp_comm
+    n, r = ps.get_world_size(group_name), ps.get_rank_in(group_name)
+    T = m.numel()
+    per = 3 * T
+    per_al = (per + 3) // 4 * 4                     # 16-byte multiples per rank
+    cur = _STATS_WS.get(group_name)
+    if cur is None or cur[1].numel() < n * per_al:
+        if cur is not None:
+            torch.cuda.synchronize()
+        cur = _STATS_WS[group_name] = dp_comm.allocate(group_name, n * max(per_al, 1 << 16), torch.float32)
+    ws, flat = cur
+    mine = flat[r * per_al:r * per_al + per].view(3, T)
+    mine[0].copy_(m)
+    mine[1].copy_(s)
+    mine[2].copy_(tgt)
+    dp_comm.all_gather_(ws, flat, 0, n * per_al)
+    allr = flat[:n * per_al].view(n, per_al)[:, :per].view(n, 3, T)
+    gm = allr[:, 0].max(dim=0).values
+    ssum = (allr[:, 1] * torch.exp(allr[:, 0] - gm)).sum(0)
+    return gm + torch.log(ssum), allr[:, 2].sum(0)
+
+
+def _combine(m, s, tgt, group_name, group):
+    if group is not None and m.is_cuda:
+        from ..parallel import dp_comm
+        if dp_comm.usable(group_name, m.device):
+            return _reduce_stats_peer(m, s, tgt, group_name)
+    return _reduce_stats(m, s, tgt, group)
+
+
+def _head_kernel_ok(h2, weight) -> bool:
+    return (h2.is_cuda and h2.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _lib.available()
+            and h2.shape[1] % 8 == 0 and weight.is_contiguous())
+
+
+def _head_stats(h2, weight, lab, vocab_start):
+    """(max, sum exp, label logit) of every row over the local vocabulary shard, from the GEMM epilogue."""
+    T, H = h2.shape
+    vl = weight.shape[0]
+    tiles_n = (vl + 255) // 256
+    part = torch.empty((T, tiles_n, 2), dtype=torch.float32, device=h2.device)
+    tgt = torch.zeros(T, dtype=torch.float32, device=h2.device)
+    rc = _lib.lib().mcb_gemm_ce_bf16(_lib.ptr(h2), _ll(h2.stride(0)), _lib.ptr(weight), _ll(weight.stride(0)), _int(T),
+                                     _int(vl), _int(H), _lib.ptr(lab), _int(vocab_start), _lib.ptr(part), _lib.ptr(tgt),
+                                     None, None, None, _ll(0), _int(0), _lib.ptr(_lib.status_word(h2.device)),
+                                     _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_gemm_ce_bf16')
+    m_t, s_t = part[..., 0], part[..., 1]
+    m = m_t.max(dim=1).values
+    s = (s_t * torch.exp(m_t - m[:, None])).sum(1)
+    return m, s, tgt
+
+
+def _head_dlogits(h2, weight, lab, vocab_start, lse, g):
+    T, H = h2.shape
+    vl = weight.shape[0]
+    d = torch.empty((T, vl), dtype=torch.bfloat16, device=h2.device)
+    rc = _lib.lib().mcb_gemm_ce_bf16(_lib.ptr(h2), _ll(h2.stride(0)), _lib.ptr(weight), _ll(weight.stride(0)), _int(T),
+                                     _int(vl), _int(H), _lib.ptr(lab), _int(vocab_start), None, None, _lib.ptr(lse),
+                                     _lib.ptr(g), _lib.ptr(d), _ll(d.stride(0)), _int(1),
+                                     _lib.ptr(_lib.status_word(h2.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_gemm_ce_bf16')
+    return d
+
+
 class _VocabParallelCE(torch.autograd.Function):
 
     @staticmethod
@@ -123,6 +197,14 @@ class _FusedLinearCE(torch.autograd.Function):
         h2 = h.reshape(-1, H)
         lab = labels.reshape(-1).to(torch.int64)
         T = h2.shape[0]
+        if h2.stride(1) != 1 or h2.stride(0) % 8:
+            h2 = h2.contiguous()
+        if _head_kernel_ok(h2, weight):
+            m, s, tgt = _head_stats(h2, weight, lab, r * vl)
+            lse_all, tgt = _combine(m, s, tgt, group_name, group)
+            ctx.save_for_backward(h2, weight, lab, lse_all)
+            ctx.meta = (group_name, chunk, r * vl, h.shape, labels.shape)
+            return (lse_all - tgt).view(labels.shape)
         loss = torch.empty(T, dtype=torch.float32, device=h.device)
         lse_all = torch.empty(T, dtype=torch.float32, device=h.device)
         ldt = torch.float32
@@ -152,11 +234,15 @@ class _FusedLinearCE(torch.autograd.Function):
         if need_dw and mg is None:
             dw = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
         ddt = h2.dtype if h2.dtype == torch.bfloat16 else torch.float32
+        fused = _head_kernel_ok(h2, weight)
         for s0 in range(0, T, chunk):
             s1 = min(T, s0 + chunk)
-            logits = gemm.mm_nt(h2[s0:s1], weight, out_dtype=torch.float32)
-            d = _dlogits(logits, lab[s0:s1], vstart, lse[s0:s1], g[s0:s1], ddt)
-            del logits
+            if fused:
+                d = _head_dlogits(h2[s0:s1], weight, lab[s0:s1], vstart, lse[s0:s1], g[s0:s1])
+            else:
+                logits = gemm.mm_nt(h2[s0:s1], weight, out_dtype=torch.float32)
+                d = _dlogits(logits, lab[s0:s1], vstart, lse[s0:s1], g[s0:s1], ddt)
+                del logits
             gemm.mm_nn(d, weight, out=dh[s0:s1])
             if need_dw:
                 gemm.mm_tn(d, h2[s0:s1], out=mg if mg is not None else dw, accumulate=True)

@@ -139,7 +139,7 @@ def test_qkv_split_norm_rope(ng, qpg, d, gate, rotf, inter, nrm):
         assert rel(wq.grad, wqr.grad) < 1e-2 and rel(wk.grad, wkr.grad) < 1e-2
 
 
-@pytest.mark.parametrize('V', [1024, 32000])
+@pytest.mark.parametrize('V', [1000, 1024, 32000])
 def test_fused_linear_cross_entropy(V):
     from mcore_bridge_b200.ops import cross_entropy
     torch.manual_seed(6)
@@ -154,6 +154,12 @@ def test_fused_linear_cross_entropy(V):
     lr_ = torch.nn.functional.cross_entropy(hr @ wr.t(), lab, reduction='none')
     lr_.backward(gl)
     assert rel(loss, lr_) < 1e-3 and rel(h.grad, hr.grad) < 1e-2 and rel(w.grad, wr.grad) < 1e-2
+    # a vocabulary shard that starts at a non-zero column: the epilogue statistics against the torch ones
+    start = 512
+    glob = lab + start - (V // 2)                      # some labels fall outside this shard on either side
+    m, s, t = cross_entropy._head_stats(h.detach(), w.detach(), glob, start)
+    mr, sr, tr = cross_entropy._stats_torch(h.detach().float() @ w.detach().float().t(), glob, start)
+    assert rel(m, mr) < 1e-3 and rel(m + torch.log(s), mr + torch.log(sr)) < 1e-3 and (t - tr).abs().max() < 2e-2
 
 
 def test_fused_adam_matches_torch():
