@@ -33,6 +33,7 @@ struct AttnParams {
   float scale_log2;       // softmax scale * log2(e)
   const int* k_lo;        // [T] first visible key of each query
   const int* k_hi;        // [T] last visible key, or null: the query's own index
+  const float* sinks;     // [nq] or null: a per-head logit that joins every row's softmax with a zero value vector
   __nv_bfloat16* o;       // [T, nq, d]
   float* lse;             // [nq, T] natural log of sum exp(scaled scores); -inf for a query that sees no key
   int* status;
@@ -137,7 +138,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint4* orow = reinterpret_cast<uint4*>(p.o + ((long long)i * p.nq + head) * D + grp * (D / 2));
 #pragma unroll
         for (int c = 0; c < D / 16; ++c) orow[c] = make_uint4(0, 0, 0, 0);
-        if (grp == 0) p.lse[(long long)head * p.T + i] = -INFINITY;
+        if (grp == 0) p.lse[(long long)head * p.T + i] = p.sinks ? p.sinks[head] : -INFINITY;
       }
     }
   } else if (warp == 0) {
@@ -282,8 +283,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (ok && !mbar_wait(smem_u32(&xchg[0]), 0, abort_flag, p.status, ST_TIMEOUT_FULL)) ok = false;
       if (ok) mx = fmaxf(mx, reinterpret_cast<const float*>(smem + L::OFF_P + pb_mine * L::P_BYTES)[r]);
     }
-    const float m2 = (mx == -INFINITY) ? 0.f : mx * p.scale_log2;
-    float sum = 0.f;
+    // learnable softmax sink: an extra logit (already in softmax units, no scale) in the row's maximum and sum
+    const float sink2 = p.sinks ? p.sinks[head] * 1.4426950408889634f : -INFINITY;
+    const float m_tot = fmaxf((mx == -INFINITY) ? -INFINITY : mx * p.scale_log2, sink2);
+    const float m2 = (m_tot == -INFINITY) ? 0.f : m_tot;
+    float sum = (p.sinks && grp == 0) ? exp2f(sink2 - m2) : 0.f;
     // pass 2: score iterations sit = nblk + j; this group takes the j with (nblk + j) & 1 == grp, which all share
     // one P buffer
     const int j0 = (grp + nblk) & 1;
@@ -401,12 +405,14 @@ int launch_fwd(const void* q, const void* k, const void* v, const AttnParams& p,
 extern "C" {
 
 // General form.  q [T, nq, d], k/v [Tk, nkv, d] bf16 contiguous; k_lo / k_hi [T] int32: query i attends to the keys
-// k_lo[i] .. k_hi[i] (inclusive; k_hi may be null = i, which needs Tk >= T); o [T, nq, d]; lse [nq, T] fp32.
-int mcb_attn_fwd_ranges(const void* q, const void* k, const void* v, const int* k_lo, const int* k_hi, void* o,
-                        float* lse, int T, int Tk, int nq, int nkv, int d, float scale, int* status, void* stream_) {
+// k_lo[i] .. k_hi[i] (inclusive; k_hi may be null = i, which needs Tk >= T); sinks [nq] fp32 or null; o [T, nq, d];
+// lse [nq, T] fp32 (it includes the sink, which is what the backward kernels need to recompute the probabilities).
+int mcb_attn_fwd_ranges(const void* q, const void* k, const void* v, const int* k_lo, const int* k_hi,
+                        const float* sinks, void* o, float* lse, int T, int Tk, int nq, int nkv, int d, float scale,
+                        int* status, void* stream_) {
   if (T == 0) return 0;
   if (nq % nkv || Tk <= 0 || (k_hi == nullptr && Tk < T)) return -2;
-  AttnParams p{T, Tk, nq, nkv, d, scale * 1.4426950408889634f, k_lo, k_hi, (__nv_bfloat16*)o, lse, status};
+  AttnParams p{T, Tk, nq, nkv, d, scale * 1.4426950408889634f, k_lo, k_hi, sinks, (__nv_bfloat16*)o, lse, status};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   if (d == 128) return launch_fwd<128>(q, k, v, p, s);
   if (d == 64) return launch_fwd<64>(q, k, v, p, s);
@@ -416,7 +422,7 @@ int mcb_attn_fwd_ranges(const void* q, const void* k, const void* v, const int* 
 // Packed causal self-attention: seq_start [T] int32 = first token of each token's sequence.
 int mcb_attn_fwd(const void* q, const void* k, const void* v, const int* seq_start, void* o, float* lse, int T, int nq,
                  int nkv, int d, float scale, int* status, void* stream_) {
-  return mcb_attn_fwd_ranges(q, k, v, seq_start, nullptr, o, lse, T, T, nq, nkv, d, scale, status, stream_);
+  return mcb_attn_fwd_ranges(q, k, v, seq_start, nullptr, nullptr, o, lse, T, T, nq, nkv, d, scale, status, stream_);
 }
 
 }  // extern "C"

@@ -96,7 +96,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: Opt
         from . import _lib, attention_cuda
         why = attention_cuda.unsupported_reason(q, k, v, causal, window, sinks, softcap)
         if why is None and _lib.available():
-            return attention_cuda.attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start)
+            return attention_cuda.attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start, window, sinks)
         if backend == 'mcb':
             raise RuntimeError(f'the in-tree attention kernel does not cover {why or "a run with the kernels disabled"}')
         if why is not None and _lib.cuda_enabled():

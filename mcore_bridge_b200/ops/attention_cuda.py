@@ -22,10 +22,8 @@ def unsupported_reason(q, k, v, causal, window, sinks, softcap) -> Optional[str]
     """``None`` when the in-tree kernel covers the call, else what it lacks (used for the one-time warning)."""
     if not causal:
         return 'non-causal attention'
-    if window is not None:
-        return 'sliding-window attention'
-    if sinks is not None:
-        return 'learnable softmax sinks'
+    if window is not None and (window[0] is None or int(window[0]) < 0):
+        window = None
     if softcap:
         return 'soft-capped scores'
     if q.dtype != torch.bfloat16:
@@ -107,7 +105,10 @@ class _AttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None
 
 
-def attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start: Optional[torch.Tensor] = None):
+def attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start: Optional[torch.Tensor] = None, window=None,
+              sinks: Optional[torch.Tensor] = None):
+    """Packed causal self-attention.  ``window = (left, _)`` limits every query to its ``left`` most recent
+    predecessors (plus itself); ``sinks [nq]`` adds a learnable per-head logit to every row's softmax."""
     T, nq, d = q.shape
     if scale is None:
         scale = 1.0 / math.sqrt(d)
@@ -115,7 +116,15 @@ def attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start: Optional[torch.
         seq_start = seq_start_from_cu(cu_seqlens, T, q.device)
     if max_seqlen is None and cu_seqlens is not None:
         max_seqlen = T
-    return _AttnFn.apply(q, k, v, seq_start, cu_seqlens, max_seqlen, float(scale))
+    left = None if window is None or window[0] is None or int(window[0]) < 0 else int(window[0])
+    if left is None and sinks is None:
+        return _AttnFn.apply(q, k, v, seq_start, cu_seqlens, max_seqlen, float(scale))
+    k_lo = seq_start
+    if left is not None:
+        # still non-decreasing, so the kernels' causal fast paths (k_hi = the query itself) apply unchanged
+        k_lo = torch.maximum(seq_start, (torch.arange(T, device=q.device, dtype=torch.int32) - left))
+    o, _ = attention_ranges(q, k, v, k_lo.contiguous(), None, None, None, scale, sinks)
+    return o
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -133,24 +142,27 @@ class _AttnRangesFn(torch.autograd.Function):
     queries that can see it (they only limit the loops of the dK/dV kernel)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, k_lo, k_hi, q_lo, q_hi, scale):
+    def forward(ctx, q, k, v, k_lo, k_hi, q_lo, q_hi, scale, sinks=None):
         T, nq, d = q.shape
         Tk, nkv = k.shape[0], k.shape[1]
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         o = torch.empty_like(q)
         lse = torch.empty((nq, T), dtype=torch.float32, device=q.device)
+        sk = None if sinks is None else sinks.detach().float().contiguous()
         rc = _lib.lib().mcb_attn_fwd_ranges(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(k_lo), _lib.ptr(k_hi),
-                                            _lib.ptr(o), _lib.ptr(lse), _int(T), _int(Tk), _int(nq), _int(nkv), _int(d),
-                                            _f(scale), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+                                            _lib.ptr(sk), _lib.ptr(o), _lib.ptr(lse), _int(T), _int(Tk), _int(nq),
+                                            _int(nkv), _int(d), _f(scale), _lib.ptr(_lib.status_word(q.device)),
+                                            _lib.stream_ptr())
         _lib.check_rc(rc, 'mcb_attn_fwd_ranges')
-        ctx.save_for_backward(q, k, v, o, lse, k_lo, k_hi, q_lo, q_hi)
+        ctx.save_for_backward(q, k, v, o, lse, k_lo, k_hi, q_lo, q_hi, sk)
         ctx.scale = scale
+        ctx.sink_dtype = None if sinks is None else sinks.dtype
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, do, _dlse):
-        q, k, v, o, lse, k_lo, k_hi, q_lo, q_hi = ctx.saved_tensors
+        q, k, v, o, lse, k_lo, k_hi, q_lo, q_hi, sk = ctx.saved_tensors
         do = do.contiguous()
         T, nq, d = q.shape
         Tk, nkv = k.shape[0], k.shape[1]
@@ -164,11 +176,17 @@ class _AttnRangesFn(torch.autograd.Function):
             _int(T), _int(Tk), _int(nq), _int(nkv), _int(d), _f(ctx.scale), _lib.ptr(partial), _int(splits),
             _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
         _lib.check_rc(rc, 'mcb_attn_bwd_ranges')
-        return dq, dk, dv, None, None, None, None, None
+        dsinks = None
+        if sk is not None:
+            # the sink is one more softmax column with a zero value vector: d sink_h = -sum_i p_sink(i, h) * delta(i, h)
+            dsinks = -(torch.exp(sk[:, None] - lse) * delta).sum(1).to(ctx.sink_dtype)
+        return dq, dk, dv, None, None, None, None, None, dsinks
 
 
-def attention_ranges(q, k, v, k_lo, k_hi, q_lo, q_hi, scale: Optional[float] = None):
-    """Returns ``(o [T, nq, d], lse [nq, T])``; all four range tensors are int32 on the device."""
+def attention_ranges(q, k, v, k_lo, k_hi, q_lo, q_hi, scale: Optional[float] = None,
+                     sinks: Optional[torch.Tensor] = None):
+    """Returns ``(o [T, nq, d], lse [nq, T])``; all four range tensors are int32 on the device (``k_hi`` / ``q_lo`` /
+    ``q_hi`` may all be ``None`` for masks of the causal family: ``k_hi[i] = i`` and a non-decreasing ``k_lo``)."""
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
-    return _AttnRangesFn.apply(q, k, v, k_lo, k_hi, q_lo, q_hi, float(scale))
+    return _AttnRangesFn.apply(q, k, v, k_lo, k_hi, q_lo, q_hi, float(scale), sinks)

@@ -549,3 +549,31 @@ def test_attention_ranges_bidirectional_and_empty_rows():
     assert rel(q.grad[live], qr.grad[live]) < 3e-2 and q.grad[dead].abs().max().item() == 0.0
     assert rel(k.grad, kr.grad) < 3e-2 and rel(v.grad, vr.grad) < 3e-2
     assert torch.isfinite(k.grad.float()).all() and torch.isfinite(q.grad.float()).all()
+
+
+@pytest.mark.parametrize('d,nq,nkv', [(64, 8, 2), (128, 4, 4)])
+@pytest.mark.parametrize('window,use_sinks', [(96, False), (None, True), (200, True)])
+def test_attention_window_and_sinks(d, nq, nkv, window, use_sinks):
+    """Sliding-window attention and learnable softmax sinks on the in-tree kernels (the GPT-OSS configuration), packed
+    sequences, output and every gradient (the sinks' included) against the masked-softmax reference."""
+    from mcore_bridge_b200.ops.attention import attention, attention_ref
+    torch.manual_seed(8)
+    lens = [333, 40, 700, 129]
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    q = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    sinks = (torch.randn(nq, device=DEV) * 2).requires_grad_() if use_sinks else None
+    do = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16)
+    w = None if window is None else (window, 0)
+    o = attention(q, k, v, cu, max(lens), True, None, w, sinks)
+    o.backward(do)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    sr = sinks.detach().clone().requires_grad_() if use_sinks else None
+    ref = attention_ref(qr, kr, vr, cu, cu, True, None, w, sr)
+    ref.backward(do.float())
+    assert rel(o, ref) < 2e-2
+    assert rel(q.grad, qr.grad) < 3e-2 and rel(k.grad, kr.grad) < 3e-2 and rel(v.grad, vr.grad) < 3e-2
+    if use_sinks:
+        assert rel(sinks.grad, sr.grad) < 3e-2
