@@ -1,0 +1,466 @@
+// MoE token dispatch fused with the grouped expert GEMM (one launch):
+//
+//   source side   mcb_moe_sort: the routing of a rank's tokens, sorted by expert (stable), so that the entries that go
+//                 to one expert are one contiguous, deterministically ordered run of the published `order` table
+//   owner side    mcb_moe_pull_gemm: a few "pull CTAs" gather the routed rows from the sources' published activations
+//                 over NVLink (one bulk copy per row, through a shared-memory ring) into the expert-sorted, 128-row
+//                 padded GEMM input and publish a flag per 128-row block; the other CTAs run the grouped expert GEMM
+//                 C[rows of expert e] = X[rows of e] . W_e^T on tcgen05 and consume the blocks in arrival order, so
+//                 the exchange hides behind the math block by block.
+//
+// Rows are assigned without atomics: expert segment -> source rank -> position in that source's sorted run, which
+// makes the row order (and therefore every fp32 weight-gradient sum over rows) reproducible.  The same kernel replays
+// a recorded assignment (`row_src`) for the backward pass, where the rows are output gradients and the GEMM is the
+// data gradient of the second expert layer.
+//
+// No TMA multicast; remote memory is read by plain bulk copies and 4-byte loads and written by 4-byte stores.  Every
+// wait is bounded and reports through the status word.
+#include "../common/host_utils.cuh"
+#include "../gemm/gemm_pipe.cuh"
+
+using namespace mcb;
+
+namespace {
+
+constexpr int MAX_WORLD = 8;
+constexpr int PADM = 128;
+constexpr int MAX_EL = 64;            // local experts per rank the fused kernel supports
+constexpr int PULL_STORES_IN_FLIGHT = 4;
+
+// ---------------------------------------------------------------------------------------------------------------
+// source side: stable counting sort of the routing entries by expert
+// ---------------------------------------------------------------------------------------------------------------
+// One CTA of 32 warps per expert.  Warp w owns a contiguous slice of the entries; pass 1 counts its matches, pass 2
+// writes them behind the matches of the warps before it, so entries keep their order inside an expert's run.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, const int* __restrict__ counts,
+                                                        int n_entries, int E, int* __restrict__ eoff,
+                                                        int* __restrict__ order) {
+  const int e = blockIdx.x;
+  __shared__ int s_base;
+  __shared__ int s_warp[32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    int b = 0;
+    for (int i = 0; i < e; ++i) b += counts[i];
+    s_base = b;
+    eoff[e] = b;
+    if (e == E - 1) eoff[E] = b + counts[e];
+  }
+  const int per_warp = ((n_entries + 31) / 32 + 31) / 32 * 32;   // a multiple of 32 so that slices stay aligned
+  const int lo = warp * per_warp, hi = min(n_entries, lo + per_warp);
+  int cnt = 0;
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const bool m = i < hi && idx[i] == e;
+    cnt += __popc(__ballot_sync(0xffffffffu, m));
+  }
+  if (lane == 0) s_warp[warp] = cnt;
+  __syncthreads();
+  int running = s_base;
+  for (int w = 0; w < warp; ++w) running += s_warp[w];
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const bool m = i < hi && idx[i] == e;
+    const unsigned b = __ballot_sync(0xffffffffu, m);
+    if (m) order[running + __popc(b & ((1u << lane) - 1u))] = i;
+    running += __popc(b);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// owner side: pull + grouped GEMM
+// ---------------------------------------------------------------------------------------------------------------
+struct MoeFusedParams {
+  int world, rank, T, k, E, El;
+  int H;                  // width of the pulled rows = contraction size of the GEMM
+  int N;                  // output width of the GEMM (per expert)
+  int capacity;           // rows of xp / C (a multiple of 128)
+  int pull_ctas;
+  int mode;               // 0: assign rows from the sources' sorted tables; 1: replay the assignment in row_src
+  const void* x_ptrs[MAX_WORLD];      // published rows [T, H] bf16
+  const int* order_ptrs[MAX_WORLD];   // mode 0: entries sorted by expert [T * k]
+  const int* eoff_ptrs[MAX_WORLD];    // mode 0: start of every expert's run [E + 1]
+  const float* prob_ptrs[MAX_WORLD];  // mode 0: routing probabilities [T, k] (may be null)
+  int* sent_row_ptrs[MAX_WORLD];      // mode 0: [T, k] row of each entry on its owner (written here)
+  int* seg_off;                       // [El + 1] first row of every local expert (written in mode 0, read in mode 1)
+  int* row_src;                       // [capacity] source entry of every row or -1 (written in mode 0)
+  float* row_probs;                   // [capacity] routing probability of every row (mode 0, may be null)
+  __nv_bfloat16* xp;                  // [capacity, H] gathered rows
+  uint32_t* blk_flags;                // [capacity / 128] "block landed" flags in local memory (epoch stamped)
+  uint32_t epoch;
+  void* C;                            // [capacity, N] bf16
+  long long ldc;
+  int b_group_rows;                   // rows between consecutive experts in the 2-D view of B
+  int* status;
+};
+
+struct Layout {
+  int seg_off[MAX_EL + 1];
+  int src_off[(MAX_WORLD + 1) * MAX_EL];   // [s][el]: rows of expert el that come from sources < s
+  int eoff_base[MAX_WORLD * MAX_EL];       // [s][el]: start of expert (rank * El + el) in source s's sorted table
+};
+
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const MoeFusedParams p) {
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ Layout L;
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;  // an earlier wait gave up: do not pile up
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int El = p.El;
+
+  // ------------------------------------------------------------------ row layout (every CTA computes it itself)
+  if (p.mode == 0) {
+    for (int el = threadIdx.x; el < El; el += blockDim.x) {
+      int run = 0;
+      for (int s = 0; s < p.world; ++s) {
+        const int* eo = p.eoff_ptrs[s] + p.rank * El + el;
+        const int b = eo[0], c = eo[1] - b;
+        L.src_off[s * MAX_EL + el] = run;
+        L.eoff_base[s * MAX_EL + el] = b;
+        run += c;
+      }
+      L.src_off[p.world * MAX_EL + el] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      for (int el = 0; el < El; ++el) {
+        L.seg_off[el] = acc;
+        acc += (L.src_off[p.world * MAX_EL + el] + PADM - 1) / PADM * PADM;
+      }
+      L.seg_off[El] = acc;
+      if (blockIdx.x == 0) {
+        for (int el = 0; el <= El; ++el) p.seg_off[el] = L.seg_off[el];
+        if (acc > p.capacity && p.status) atomicMax(p.status, ST_MOE_OVERFLOW);  // routing does not fit the buffer
+      }
+    }
+  } else {
+    for (int el = threadIdx.x; el <= El; el += blockDim.x) L.seg_off[el] = p.seg_off[el];
+  }
+  __syncthreads();
+  const int valid_rows = min(L.seg_off[El], p.capacity);
+  const int nblocks = valid_rows / PADM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+
+  if ((int)blockIdx.x < p.pull_ctas) {
+    // ================================================================= pull CTA
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t row_bytes = (uint32_t)p.H * 2u;
+    const int ring_bytes = GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES - 8192;   // the rest: barriers + row tables
+    int rstages = ring_bytes / (int)row_bytes;
+    if (rstages > 32) rstages = 32;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + ring_bytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + 32;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 64);
+    const uint8_t** meta = reinterpret_cast<const uint8_t**>(bars + 72);   // [2][128] source address of every row
+    if (threadIdx.x == 0) {
+      *abort_flag = 0;
+      for (int s = 0; s < rstages; ++s) {
+        mbar_init(smem_u32(&full[s]), 1);
+        mbar_init(smem_u32(&empty[s]), 1);
+      }
+      fence_barrier_init();
+      fence_proxy_async_smem();
+    }
+    __syncthreads();
+    const long long per_src = (long long)p.T * p.k;
+
+    // source row of every row of block `b` -> meta[buf]; the side tables of the block are written on the way
+    auto describe = [&](int b, int buf) {
+      const int t = threadIdx.x - 64;               // warps 2..5: one thread per row
+      if (t < 0 || t >= PADM) return;
+      const int R = b * PADM + t;
+      const uint8_t* src = nullptr;
+      if (p.mode == 0) {
+        int el = 0;
+        while (el + 1 < El && L.seg_off[el + 1] <= R) ++el;
+        const int i = R - L.seg_off[el];
+        int s = -1;
+        if (i < L.src_off[p.world * MAX_EL + el]) {
+          s = 0;
+          while (s + 1 < p.world && L.src_off[(s + 1) * MAX_EL + el] <= i) ++s;
+        }
+        int id = -1;
+        float prob = 0.f;
+        if (s >= 0) {
+          const int j = i - L.src_off[s * MAX_EL + el];
+          const int ent = p.order_ptrs[s][L.eoff_base[s * MAX_EL + el] + j];
+          if (ent >= 0 && ent < per_src) {          // a torn table would otherwise turn into a wild address
+            src = reinterpret_cast<const uint8_t*>(p.x_ptrs[s]) + (long long)(ent / p.k) * row_bytes;
+            id = s * (int)per_src + ent;
+            prob = p.prob_ptrs[s] ? p.prob_ptrs[s][ent] : 1.f;
+            p.sent_row_ptrs[s][ent] = R;
+          }
+        }
+        p.row_src[R] = id;
+        if (p.row_probs) p.row_probs[R] = prob;
+      } else {
+        const int id = p.row_src[R];
+        if (id >= 0) {
+          const int s = id / (int)per_src;
+          const int ent = id - s * (int)per_src;
+          if (s < p.world) src = reinterpret_cast<const uint8_t*>(p.x_ptrs[s]) + (long long)(ent / p.k) * row_bytes;
+        }
+      }
+      meta[buf * PADM + t] = src;
+    };
+
+    int nmine = 0;
+    for (int b = blockIdx.x; b < nblocks; b += p.pull_ctas) ++nmine;
+    if (nmine > 0) describe(blockIdx.x, 0);
+    __syncthreads();
+    uint32_t it_load = 0, it_store = 0;
+    bool ok = true;
+    for (int i = 0; i < nmine; ++i) {
+      const int b = blockIdx.x + i * p.pull_ctas;
+      const int buf = i & 1;
+      if (warp == 0) {
+        if (lane == 0 && ok) {
+          for (int r = 0; r < PADM; ++r) {
+            const uint8_t* src = meta[buf * PADM + r];
+            if (!src) continue;
+            const uint32_t st = it_load % rstages, ph = (it_load / rstages) & 1;
+            if (!mbar_wait(smem_u32(&empty[st]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+            mbar_expect_tx(smem_u32(&full[st]), row_bytes);
+            bulk_load_1d(smem_u32(ring + (size_t)st * row_bytes), src, row_bytes, smem_u32(&full[st]));
+            ++it_load;
+          }
+        }
+      } else if (warp == 1) {
+        if (lane == 0 && ok) {
+          const uint32_t first = it_store;
+          for (int r = 0; r < PADM; ++r) {
+            if (!meta[buf * PADM + r]) continue;
+            const uint32_t st = it_store % rstages, ph = (it_store / rstages) & 1;
+            if (!mbar_wait(smem_u32(&full[st]), ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+            bulk_store_1d(reinterpret_cast<uint8_t*>(p.xp) + (long long)(b * PADM + r) * row_bytes,
+                          smem_u32(ring + (size_t)st * row_bytes), row_bytes);
+            tma_store_commit();
+            tma_store_wait_read<PULL_STORES_IN_FLIGHT>();   // older stores have read their stage: hand it back
+            if (it_store >= first + PULL_STORES_IN_FLIGHT)
+              mbar_arrive(smem_u32(&empty[(it_store - PULL_STORES_IN_FLIGHT) % rstages]));
+            ++it_store;
+          }
+          tma_store_wait<0>();                               // the whole block is in global memory
+          const uint32_t from = it_store >= first + PULL_STORES_IN_FLIGHT ? it_store - PULL_STORES_IN_FLIGHT : first;
+          for (uint32_t j = from; j < it_store; ++j) mbar_arrive(smem_u32(&empty[j % rstages]));
+        }
+      } else {
+        // warps 2..5: zero the padding rows of this block, then describe the next block
+        const int t = threadIdx.x - 64;
+        if (!meta[buf * PADM + t]) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.xp) + (long long)(b * PADM + t) * row_bytes);
+          for (uint32_t c = 0; c < row_bytes / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+        }
+        if (i + 1 < nmine) describe(b + p.pull_ctas, buf ^ 1);
+      }
+      __syncthreads();
+      if (*abort_flag) break;
+      if (threadIdx.x == 0) {
+        fence_proxy_async_all();
+        __threadfence();
+        st_release_gpu(p.blk_flags + b, p.epoch);
+      }
+    }
+    if (warp == 0 && lane == 0) {
+      // drain: loads that were issued but never stored (give-up paths) must land before the CTA exits
+      const uint32_t lo = it_load > (uint32_t)rstages ? it_load - rstages : 0;
+      for (uint32_t j = lo; j < it_load; ++j) {
+        const uint32_t st = j % rstages, ph = (j / rstages) & 1;
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(smem_u32(&full[st]), ph)) {
+          if (globaltimer_ns() - t0 > 200000000ull) break;
+        }
+      }
+    }
+    if (warp == 1 && lane == 0) tma_store_wait<0>();
+    return;
+  }
+
+  // ===================================================================== GEMM CTA
+  Pipe<BN> P(smem_raw);
+  if (threadIdx.x == 0) {
+    P.init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(P.tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *P.tmem_slot;
+  const int g0 = blockIdx.x - p.pull_ctas, gs = gridDim.x - p.pull_ctas;
+  const int total = nblocks * tiles_n;      // row-block major: the tiles of a block wait for the same flag
+  auto expert_of = [&](int mb) {
+    int el = 0;
+    while (el + 1 < El && L.seg_off[el + 1] <= mb * PADM) ++el;
+    return el;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      int seen = -1;
+      for (int t = g0; t < total; t += gs) {
+        const int mb = t / tiles_n, tn = t - mb * tiles_n;
+        const int el = expert_of(mb);
+        if (mb != seen) {
+          if (!wait_flag<SCOPE_GPU>(p.blk_flags + mb, p.epoch, false, P.abort_flag, p.status)) break;
+          fence_proxy_async_all();
+          seen = mb;
+        }
+        const int n0 = B_MN ? tn * BN : el * p.b_group_rows + tn * BN;
+        if (!load_tile<BN, B_MN>(P, &tmap_a, &tmap_b, mb * PADM, n0, p.H, it, p.status, B_MN ? el * p.b_group_rows : 0))
+          break;
+      }
+      drain_loads<BN>(P, it);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int t = g0; t < total && ok; t += gs, ++lt) {
+        const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+        if (!mbar_wait(smem_u32(&P.tempty_bar[acc]), aph ^ 1, P.abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        issue_mma_tile<BN, B_MN>(P, tmem_base + acc * BN, p.H, it, p.status, ok);
+        if (ok) umma_commit(smem_u32(&P.tfull_bar[acc]));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t lt = 0;
+    for (int t = g0; t < total; t += gs, ++lt) {
+      const int mb = t / tiles_n, tn = t - mb * tiles_n;
+      const int n0 = tn * BN;
+      const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+      if (!mbar_wait(smem_u32(&P.tfull_bar[acc]), aph, P.abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      const long long row = (long long)mb * PADM + q * 32 + lane;
+      __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc;
+#pragma unroll 1
+      for (int cc = 0; cc < BN; cc += 32) {
+        if (n0 + cc >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + cc, r);
+        tmem_ld_wait();
+        const int col0 = n0 + cc;
+        if (col0 + 32 <= p.N) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+            *reinterpret_cast<uint4*>(crow + col0 + j) = o;
+          }
+        } else {
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) crow[col0 + j] = __float2bfloat16(__uint_as_float(r[j]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&P.tempty_bar[acc]));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// idx [n_entries] expert of every routing entry (entry = token * k + choice), counts [E] entries per expert ->
+// eoff [E + 1] start of every expert's run, order [n_entries] entries sorted by expert, ties in entry order.
+int mcb_moe_sort(const int* idx, const int* counts, int n_entries, int E, int* eoff, int* order, void* stream_) {
+  if (E < 1 || n_entries < 0) return -1;
+  moe_sort_kernel<<<E, 1024, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(idx, counts, n_entries, E, eoff, order);
+  return (int)cudaGetLastError();
+}
+
+// Pointer arrays hold `world` device pointers (index = rank in the expert-parallel group).  B is the stacked expert
+// weight: K-major `[El * N, H]` (b_mn = 0, forward of the first expert layer) or MN-major `[El * H, N]` (b_mn = 1,
+// data gradient of the second expert layer: rows are contraction indices).  `blk_flags` holds capacity / 128 words
+// that carry the epoch of the call that last filled each block (monotonically increasing, never cleared).
+int mcb_moe_pull_gemm(const void* const* x_ptrs, const int* const* order_ptrs, const int* const* eoff_ptrs,
+                      const float* const* prob_ptrs, int* const* sent_row_ptrs, int world, int rank, int T, int k, int E,
+                      int El, int H, int N, int capacity, int mode, int* seg_off, int* row_src, float* row_probs, void* xp,
+                      unsigned* blk_flags, unsigned epoch, const void* B, long long b_inner, long long b_outer,
+                      long long ldb, int b_mn, int b_group_rows, void* C, long long ldc, int pull_ctas, int* status,
+                      void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (world < 1 || world > MAX_WORLD || El < 1 || El > MAX_EL || H % 8 || N % 8 || capacity % PADM || ldc % 8) return -2;
+  if (H * 2 > 32768) return -3;                      // a row has to fit a stage of the pull ring comfortably
+  if ((long long)world * T * k >= (1ll << 31)) return -3;
+  constexpr int BN = 256;
+  const int sms = device_sm_count();
+  if (pull_ctas <= 0) {
+    // balance the two roles: a pull CTA sustains ~25 GB/s of row gathers, a GEMM CTA ~9.5 TFLOP/s
+    const double rows = (double)T * k;               // balanced load
+    const double bytes = rows * H * 2.0, flops = 2.0 * rows * (double)N * H;
+    double best = 1e30;
+    int best_c = 16;
+    for (int c = 8; c <= 56; c += 4) {
+      const double t_pull = bytes / (25e9 * c), t_gemm = flops / (9.5e12 * (sms - c));
+      const double t = t_pull > t_gemm ? t_pull : t_gemm;
+      if (t < best) { best = t; best_c = c; }
+    }
+    pull_ctas = best_c;
+  }
+  if (pull_ctas >= sms) return -4;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, xp, H, capacity, H, GEMM_BK, GEMM_BM);
+  if (rc) return rc;
+  rc = b_mn ? make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, 64, GEMM_BK)
+            : make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, GEMM_BK, BN);
+  if (rc) return rc;
+  MoeFusedParams p{};
+  p.world = world; p.rank = rank; p.T = T; p.k = k; p.E = E; p.El = El; p.H = H; p.N = N; p.capacity = capacity;
+  p.pull_ctas = pull_ctas; p.mode = mode;
+  for (int i = 0; i < world; ++i) {
+    p.x_ptrs[i] = x_ptrs[i];
+    p.order_ptrs[i] = order_ptrs ? order_ptrs[i] : nullptr;
+    p.eoff_ptrs[i] = eoff_ptrs ? eoff_ptrs[i] : nullptr;
+    p.prob_ptrs[i] = prob_ptrs ? prob_ptrs[i] : nullptr;
+    p.sent_row_ptrs[i] = sent_row_ptrs ? sent_row_ptrs[i] : nullptr;
+  }
+  if (mode == 0 && (!order_ptrs || !eoff_ptrs || !sent_row_ptrs || !row_src || !seg_off)) return -2;
+  if (mode == 1 && (!row_src || !seg_off)) return -2;
+  p.seg_off = seg_off; p.row_src = row_src; p.row_probs = row_probs; p.xp = reinterpret_cast<__nv_bfloat16*>(xp);
+  p.blk_flags = blk_flags; p.epoch = epoch; p.C = C; p.ldc = ldc; p.b_group_rows = b_group_rows; p.status = status;
+  const int smem = GemmSmem<BN>::TOTAL;
+  static bool cfg[2] = {false, false};
+  cudaError_t e;
+  if (b_mn) {
+    auto kern = moe_pull_gemm_kernel<BN, true>;
+    if (!cfg[1]) {
+      if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
+      cfg[1] = true;
+    }
+    kern<<<sms, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+  } else {
+    auto kern = moe_pull_gemm_kernel<BN, false>;
+    if (!cfg[0]) {
+      if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
+      cfg[0] = true;
+    }
+    kern<<<sms, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

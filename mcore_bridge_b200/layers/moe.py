@@ -434,6 +434,11 @@ class MoELayer(nn.Module):
             self._fused.publish_routing(st, idx)
             idx = idx.to(torch.int32)
         probs = self._post_route(probs, idx)
+        if F.pull_gemm_supported(self.experts, cfg, self.num_local_experts, H):
+            y = self._fused.experts_fused(st, x, probs, idx, self.experts)
+            if self.shared_experts is not None:
+                y = y + self.shared_experts(x)
+            return y
         xp, row_probs = self._fused.dispatch(st, x, probs, idx)
         if self.apply_probs_on_input:
             xp = (xp.float() * row_probs[:, None]).to(xp.dtype)

@@ -77,7 +77,8 @@ class ExchangeBuffers:
         o = 0
         offs = {}
         for name, nbytes in (('x', T * H * 2), ('idx', T * k * 4), ('probs', T * k * 4), ('counts', E * 4),
-                             ('sent', T * k * 4), ('out', capacity * H * 2), ('scalar', capacity * 4)):
+                             ('sent', T * k * 4), ('out', capacity * H * 2), ('scalar', capacity * 4),
+                             ('order', T * k * 4), ('eoff', (E + 1) * 4)):
             offs[name] = o
             o += al(nbytes)
         self.half = o
@@ -93,10 +94,28 @@ class ExchangeBuffers:
             self.base_ptrs = [self.buf.data_ptr()]
         self.epoch = 0
         self._ptr_cache: Dict[Tuple[str, int], ctypes.Array] = {}
+        # "block landed" flags of the fused pull + GEMM kernel (local memory; they carry the epoch of the launch that
+        # filled the block, so they are never cleared)
+        self.blk_flags = torch.zeros(max(1, capacity // PAD), dtype=torch.int32, device=device)
+        self.pull_epoch = 0
 
     def next_epoch(self) -> int:
         self.epoch += 1
         return self.epoch
+
+    def next_pull_epoch(self) -> int:
+        self.pull_epoch += 1
+        return self.pull_epoch
+
+    def sort_routing(self, parity: int):
+        """Sorts the published routing of this rank by expert (``order`` / ``eoff`` regions) for the fused
+        pull + GEMM kernel of the owners."""
+        T, k, E = self.T, self.k, self.E
+        rc = _lib.lib().mcb_moe_sort(_lib.ptr(self.view('idx', parity, (T * k,), torch.int32)),
+                                     _lib.ptr(self.view('counts', parity, (E,), torch.int32)), _int(T * k), _int(E),
+                                     _lib.ptr(self.view('eoff', parity, (E + 1,), torch.int32)),
+                                     _lib.ptr(self.view('order', parity, (T * k,), torch.int32)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_moe_sort')
 
     def off(self, name: str, parity: int) -> int:
         return FLAG_BYTES + parity * self.half + self.offs[name]
@@ -345,6 +364,155 @@ class _CombineFn(torch.autograd.Function):
         return dy, None, None
 
 
+def _weight_grad_grouped(weight, dy, x, offsets):
+    """dW of a stacked expert weight: straight into ``main_grad`` when the optimizer provides it."""
+    from ..ops import gemm
+    mg = getattr(weight, 'main_grad', None)
+    if mg is not None:
+        gemm.grouped_mm_tn(dy, x, offsets, out=mg, accumulate=True)
+        hook = getattr(weight, 'grad_ready_hook', None)
+        if hook is not None:
+            hook()
+        return None
+    return gemm.grouped_mm_tn(dy, x, offsets, out_dtype=weight.dtype)
+
+
+def _pull_gemm(b: ExchangeBuffers, par: int, mode: int, st: 'DispatchState', El: int, rows_region: str, weight,
+               b_mn: bool, xp, row_probs, out):
+    """Launches the fused pull + grouped GEMM kernel on ``b``'s published regions of parity ``par``."""
+    T, H, k, E = b.T, b.H, b.k, b.E
+    G, d1, d2 = weight.shape
+    w2 = weight.view(G * d1, d2)
+    if b_mn:            # weight [El, H(contraction), N]: rows of the 2-D view are contraction indices
+        N, b_inner, b_outer, group_rows = d2, d2, G * d1, d1
+    else:               # weight [El, N, H]
+        N, b_inner, b_outer, group_rows = d1, d2, G * d1, d1
+    fwd = mode == 0
+    rc = _lib.lib().mcb_moe_pull_gemm(
+        b.ptrs(rows_region, par), b.ptrs('order', par) if fwd else None, b.ptrs('eoff', par) if fwd else None,
+        b.ptrs('probs', par) if fwd else None, b.ptrs('sent', par) if fwd else None, _int(b.world), _int(b.rank),
+        _int(T), _int(k), _int(E), _int(El), _int(H), _int(N), _int(b.cap), _int(mode), _lib.ptr(st.seg_off),
+        _lib.ptr(st.row_src), _lib.ptr(row_probs), _lib.ptr(xp), _lib.ptr(b.blk_flags), _u(b.next_pull_epoch()),
+        _lib.ptr(w2), ctypes.c_longlong(b_inner), ctypes.c_longlong(b_outer), ctypes.c_longlong(w2.stride(0)),
+        _int(int(b_mn)), _int(group_rows), _lib.ptr(out), ctypes.c_longlong(out.stride(0)), _int(PULL_CTAS),
+        _lib.ptr(_lib.status_word(xp.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_moe_pull_gemm')
+
+
+PULL_CTAS = int(os.environ.get('MCB200_MOE_PULL_CTAS', '0'))   # 0: the launcher balances pull vs GEMM CTAs
+
+
+def pull_gemm_supported(experts, config, El: int, H: int) -> bool:
+    """The fused dispatch + expert GEMM applies to plain stacked bf16 expert weights without biases, probabilities
+    applied after the first layer, at most 64 local experts and rows of at most 32 KiB."""
+    from .moe import GroupedLinear, GroupedMLP
+    if os.environ.get('MCB200_MOE_FUSED_GEMM', '1') == '0':
+        return False
+    if type(experts) is not GroupedMLP or config.moe_apply_probs_on_input:
+        return False
+    for lin in (experts.linear_fc1, experts.linear_fc2):
+        if type(lin) is not GroupedLinear or lin.bias is not None or lin.weight.dtype != torch.bfloat16:
+            return False
+    f = experts.linear_fc2.weight.shape[2]
+    return El <= 64 and H * 2 <= 32768 and H % 8 == 0 and f % 64 == 0 and experts.linear_fc1.weight.shape[1] % 8 == 0
+
+
+class _DispatchFc1Fn(torch.autograd.Function):
+    """(x [T,H], probs [T,k], w1 [El,N,H]) -> (h [cap,N], row_probs [cap]): the owners pull their routed rows and
+    run the first expert layer in one launch; the exchange hides behind the GEMM block by block."""
+
+    @staticmethod
+    def forward(ctx, x, probs, idx, w1, st: 'DispatchState', El: int):
+        b = st.fwd
+        T, H, k = b.T, b.H, b.k
+        par, epoch = st.parity, b.epoch
+        b.view('x', par, (T, H), torch.bfloat16).copy_(x)
+        b.view('probs', par, (T, k), torch.float32).copy_(probs.float())
+        b.sort_routing(par)                   # idx and counts were published by the router
+        b.signal(F_READY, epoch)
+        b.wait(F_READY, epoch)
+        dev = x.device
+        xp = torch.empty((b.cap, H), dtype=torch.bfloat16, device=dev)
+        h = torch.empty((b.cap, w1.shape[1]), dtype=torch.bfloat16, device=dev)
+        row_probs = torch.empty(b.cap, dtype=torch.float32, device=dev)
+        _pull_gemm(b, par, 0, st, El, 'x', w1, False, xp, row_probs, h)
+        ctx.save_for_backward(xp, w1)
+        ctx.st, ctx.El, ctx.pdtype = st, El, probs.dtype
+        return h, row_probs
+
+    @staticmethod
+    def backward(ctx, dh, drow_probs):
+        from ..ops import gemm
+        xp, w1 = ctx.saved_tensors
+        st, El = ctx.st, ctx.El
+        b = st.bwd
+        T, H, k = b.T, b.H, b.k
+        dh = dh.contiguous()
+        par, epoch = b.epoch & 1, b.epoch     # same call whose first half ran in _Fc2CombineFn.backward
+        # owners publish their input-gradient rows (written by the GEMM straight into the symmetric region) and the
+        # probability gradients, sources pull them back
+        gemm.grouped_mm_nn(dh, w1, st.seg_off, out=b.view('out', par, (b.cap, H), torch.bfloat16))
+        dw1 = _weight_grad_grouped(w1, dh, xp, st.seg_off) if ctx.needs_input_grad[3] else None
+        sc = b.view('scalar', par, (b.cap,), torch.float32)
+        if drow_probs is not None:
+            sc.copy_(drow_probs.float())
+        else:
+            sc.zero_()
+        b.signal(F_DONE, epoch)
+        b.wait(F_DONE, epoch)
+        dx = torch.empty((T, H), dtype=torch.bfloat16, device=dh.device)
+        dprobs = torch.empty((T, k), dtype=torch.float32, device=dh.device)
+        rc = _lib.lib().mcb_moe_combine(b.ptrs('out', par), b.ptrs('scalar', par), _int(b.world), _int(T), _int(k),
+                                        _int(El), _int(H), _lib.ptr(st.idx), _lib.ptr(st.sent_row), _lib.ptr(dx),
+                                        _lib.ptr(dprobs), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_moe_combine')
+        return dx, dprobs.to(ctx.pdtype), None, dw1, None, None
+
+
+class _Fc2CombineFn(torch.autograd.Function):
+    """(a [cap,F], w2 [El,H,F]) -> out [T,H]: second expert layer into the symmetric output buffer, then the sources
+    pull and sum their k rows.  Backward: the owners pull the output-gradient rows and run the data-gradient GEMM of
+    the second layer in one launch."""
+
+    @staticmethod
+    def forward(ctx, a, w2, st: 'DispatchState', El: int):
+        from ..ops import gemm
+        b = st.fwd
+        T, H, k = b.T, b.H, b.k
+        par, epoch = st.parity, b.epoch
+        gemm.grouped_mm_nt(a, w2, st.seg_off, out=b.view('out', par, (b.cap, H), torch.bfloat16))
+        b.signal(F_DONE, epoch)
+        b.wait(F_DONE, epoch)
+        idx = b.view('idx', par, (T, k), torch.int32)
+        sent = b.view('sent', par, (T, k), torch.int32)
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=a.device)
+        rc = _lib.lib().mcb_moe_combine(b.ptrs('out', par), None, _int(b.world), _int(T), _int(k), _int(El), _int(H),
+                                        _lib.ptr(idx), _lib.ptr(sent), _lib.ptr(out), None, _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_moe_combine')
+        st.sent_row = sent.clone()   # the published tables are reused two calls later
+        st.idx = idx.clone()
+        ctx.save_for_backward(a, w2)
+        ctx.st, ctx.El = st, El
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        a, w2 = ctx.saved_tensors
+        st, El = ctx.st, ctx.El
+        b = st.bwd
+        T, H = b.T, b.H
+        epoch = b.next_epoch()
+        par = epoch & 1
+        b.view('x', par, (T, H), torch.bfloat16).copy_(dout)
+        b.signal(F_READY, epoch)
+        b.wait(F_READY, epoch)
+        dy = torch.empty((b.cap, H), dtype=torch.bfloat16, device=dout.device)
+        da = torch.empty_like(a)
+        _pull_gemm(b, par, 1, st, El, 'x', w2, True, dy, None, da)
+        dw2 = _weight_grad_grouped(w2, dy, a, st.seg_off) if ctx.needs_input_grad[1] else None
+        return da, dw2, None, None
+
+
 class FusedMoEDispatcher:
     """Per-layer helper owned by ``MoELayer``; holds no parameters."""
 
@@ -384,6 +552,18 @@ class FusedMoEDispatcher:
 
     def dispatch(self, st: DispatchState, x, probs, idx):
         return _DispatchFn.apply(x, probs, idx, st, self.El)
+
+    def experts_fused(self, st: DispatchState, x, probs, idx, experts):
+        """Dispatch + both expert layers + combine with the exchange fused into the expert GEMMs
+        (``pull_gemm_supported`` decides whether this path applies)."""
+        from ..ops.activation import glu
+        cfg = self.config
+        h, row_probs = _DispatchFc1Fn.apply(x, probs, idx, experts.linear_fc1.weight, st, self.El)
+        if cfg.gated_linear_unit:
+            a = glu(h, experts.kind, row_probs, cfg.activation_func_clamp_value or 0.0, cfg.glu_linear_offset)
+        else:
+            a = cfg.activation_func(h) * row_probs[:, None].to(h.dtype)
+        return _Fc2CombineFn.apply(a, experts.linear_fc2.weight, st, self.El)
 
     def out_buffer(self, st: DispatchState) -> torch.Tensor:
         """Where the last expert GEMM should write so that the combine needs no copy."""

@@ -40,8 +40,10 @@ for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None
     gx = torch.Generator(device=dev).manual_seed(100+rank)
     x = (torch.randn(T, H, device=dev, generator=gx)).to(torch.bfloat16)
     outs = {}
-    for fused in ('1','0'):
-        os.environ['MCB200_FUSED_MOE'] = fused
+    # '1': exchange fused into the expert GEMMs; 'k': the separate dispatch / combine kernels; '0': torch.distributed
+    for fused in ('1','k','0'):
+        os.environ['MCB200_FUSED_MOE'] = '0' if fused == '0' else '1'
+        os.environ['MCB200_MOE_FUSED_GEMM'] = '0' if fused == 'k' else '1' 
         layer.zero_grad()
         xx = x.clone().requires_grad_()
         y = layer(xx)
@@ -51,12 +53,22 @@ for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None
         outs[fused] = (y.detach().clone(), xx.grad.clone(), layer.router.weight.grad.clone(), layer.experts.linear_fc1.weight.grad.clone(), layer.experts.linear_fc2.weight.grad.clone())
         torch.cuda.synchronize(); _lib.check_status()
     names = ['y','dx','drouter','dfc1','dfc2']
-    for n_, a_, b_ in zip(names, outs['1'], outs['0']):
-        r = rel(a_, b_); good = r < 3e-2
-        t = torch.tensor([0 if good else 1], device=dev)
+    for tag in ('1', 'k'):
+        for n_, a_, b_ in zip(names, outs[tag], outs['0']):
+            r = rel(a_, b_); good = r < 3e-2
+            t = torch.tensor([0 if good else 1], device=dev)
+            if world>1: dist.all_reduce(t)
+            ok &= t.item()==0
+            if rank==0: print(f'E{E} k{k} H{H} sig{sig} mode {tag}: {n_} rel={r:.3e} {"OK" if t.item()==0 else "FAIL"}', flush=True)
+    # the row assignment of the fused path has no atomics: a second run gives the same bits
+    if True:
+        os.environ['MCB200_FUSED_MOE'] = '1'; os.environ['MCB200_MOE_FUSED_GEMM'] = '1'
+        layer.zero_grad(); xx = x.clone().requires_grad_(); y2 = layer(xx); y2.backward(dy)
+        same = torch.equal(y2, outs['1'][0]) and torch.equal(layer.experts.linear_fc1.weight.grad, outs['1'][3])
+        t = torch.tensor([0 if same else 1], device=dev)
         if world>1: dist.all_reduce(t)
         ok &= t.item()==0
-        if rank==0: print(f'E{E} k{k} H{H} sig{sig}: {n_} rel={r:.3e} {"OK" if t.item()==0 else "FAIL"}', flush=True)
+        if rank==0: print(f'E{E} k{k} H{H} sig{sig}: fused path reproducible {"OK" if t.item()==0 else "FAIL"}', flush=True)
 if rank==0: print('ALL OK' if ok else 'SOME FAILED', flush=True)
 if world>1:
     dist.barrier(); dist.destroy_process_group()
