@@ -53,12 +53,10 @@ cudaError_t launch_pair_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const
   return launch_pair<true, false>(ta, tb, p, grid, s);
 }
 
-constexpr bool PAIR_AUTO = false;
-
 // CTA pairs (256 x 256 tiles) pay off once there are enough tiles to fill the 74 clusters a few times over; small or
 // skinny problems keep the single-CTA tiles, whose narrower variants quantise better.
 bool use_pair(int M, int N, int K, int mode, int sms) {
-  if (!PAIR_AUTO || mode != GEMM_DENSE || M < 512 || N < 256 || K < 128) return false;
+  if (mode != GEMM_DENSE || M < 512 || N < 256 || K < 128) return false;
   const long long tiles = (long long)((M + PAIR_BM - 1) / PAIR_BM) * ((N + PAIR_BN - 1) / PAIR_BN);
   return tiles >= (sms / 2);
 }

@@ -39,9 +39,52 @@ def _time(fn, iters, flush=None):
     return total / iters * 1e-3
 
 
+def step_profile(a):
+    """Per-kernel device time of one ``Trainer.train_step`` (torch.profiler / kineto, CUDA activity) on a model of
+    reduced depth, after three warm-up steps: the table the step-breakdown summaries under ``profiles/`` are made of.
+    Single GPU; per-layer figures carry over to the full model."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from .train.data import SyntheticPackedDataset
+    from .train.presets import model_config
+    from .train.trainer import TrainConfig, Trainer
+    torch.cuda.set_device(0)
+    cfg = model_config(a.model, {'num_hidden_layers': a.layers}, bf16=True)
+    tr = Trainer(cfg, TrainConfig())
+    ds = SyntheticPackedDataset(cfg.padded_vocab_size, a.seq_len, micro_batch_size=1, seed=1)
+
+    def batch():
+        return [ds.next_microbatch() for _ in range(a.micro_batches)]
+
+    for _ in range(3):
+        tr.train_step(batch())
+    torch.cuda.synchronize()
+    mbs = batch()
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        tr.train_step(mbs)
+        torch.cuda.synchronize()
+    rows = {}
+    total = 0.0
+    for ev in prof.events():
+        if ev.device_type.name != 'CUDA':
+            continue
+        t = ev.device_time if hasattr(ev, 'device_time') else ev.cuda_time
+        name = ev.name.split('<')[0].split('(')[0][:70]
+        r = rows.setdefault(name, [0.0, 0])
+        r[0] += t
+        r[1] += 1
+        total += t
+    out = {'op': 'step-profile', 'model': a.model, 'layers': a.layers, 'micro_batches': a.micro_batches,
+           'seq_len': a.seq_len, 'gpu_ms': round(total / 1e3, 2), 'kernels': []}
+    for name, (t, n) in sorted(rows.items(), key=lambda kv: -kv[1][0])[:30]:
+        out['kernels'].append({'name': name, 'ms': round(t / 1e3, 3), 'share': round(t / total, 4), 'launches': n})
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('op', choices=['gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'rmsnorm_bwd', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention', 'attention_bwd',
+    ap.add_argument('op', choices=['step-profile', 'gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'rmsnorm_bwd', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention', 'attention_bwd',
                                   'gemm_fp8', 'quant_fp8', 'dsa_index', 'topk', 'simple_gla', 'conv1d'])
     ap.add_argument('--m', type=int, default=8192)
     ap.add_argument('--n', type=int, default=4096)
@@ -49,7 +92,13 @@ def main():
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--bn', type=int, default=0)
     ap.add_argument('--no-flush', action='store_true')
+    ap.add_argument('--model', default='qwen3_8b', help='step-profile: preset name')
+    ap.add_argument('--layers', type=int, default=6, help='step-profile: layers of the reduced model')
+    ap.add_argument('--micro-batches', type=int, default=2)
+    ap.add_argument('--seq-len', type=int, default=8192)
     a = ap.parse_args()
+    if a.op == 'step-profile':
+        return step_profile(a)
     from .ops import _lib, activation, cross_entropy, gemm, norm, rope
     dev = 'cuda'
     burst, sustained, hbm, src = _peaks()

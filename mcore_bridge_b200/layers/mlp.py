@@ -18,6 +18,11 @@ class MLP(nn.Module):
         cls = LayerNormColumnParallelLinear if fuse_input_norm else ColumnParallelLinear
         self.linear_fc1 = cls(config.hidden_size, f * mult, config, bias=config.add_bias_linear)
         self.linear_fc2 = RowParallelLinear(f, config.hidden_size, config, bias=config.add_bias_linear)
+        if config.gated_linear_unit:
+            # the local shard is [gate shard; up shard]: two interleaved partitions of the output dim
+            for prm in (self.linear_fc1.weight, self.linear_fc1.bias):
+                if prm is not None:
+                    prm.partition_stride = 2
         self.kind = 'swiglu' if config.swiglu else ('quick_geglu' if config.quick_geglu else 'geglu_tanh')
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

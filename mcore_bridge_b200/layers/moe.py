@@ -257,6 +257,10 @@ class GroupedMLP(nn.Module):
         mult = 2 if config.gated_linear_unit else 1
         b = bool(config.add_bias_linear)
         self.linear_fc1 = GroupedLinear(num_local_experts, config.hidden_size, f * mult, config, 'column', bias=b)
+        if config.gated_linear_unit:
+            for prm in (self.linear_fc1.weight, self.linear_fc1.bias):
+                if prm is not None:
+                    prm.partition_stride = 2          # [gate shard; up shard] on the output dim
         self.linear_fc2 = GroupedLinear(num_local_experts, f, config.hidden_size, config, 'row', bias=b)
         self.kind = 'swiglu' if config.swiglu else ('quick_geglu' if config.quick_geglu else 'geglu_tanh')
 
@@ -283,6 +287,10 @@ class SharedExpertMLP(nn.Module):
         self.linear_fc1 = ColumnParallelLinear(config.hidden_size, intermediate_size * mult, config,
                                                bias=config.add_bias_linear)
         self.linear_fc2 = RowParallelLinear(intermediate_size, config.hidden_size, config, bias=config.add_bias_linear)
+        if config.gated_linear_unit:
+            for prm in (self.linear_fc1.weight, self.linear_fc1.bias):
+                if prm is not None:
+                    prm.partition_stride = 2
         if config.moe_shared_expert_gate:
             self.gate_weight = nn.Parameter(torch.empty(1, config.hidden_size, dtype=config.params_dtype))
             mark_sequence_parallel(self.gate_weight, config)

@@ -1,22 +1,16 @@
-"""State-dict helpers for adapter-wrapped models (parity: reference ``src/mcore_bridge/tuners/utils.py:8-28``)."""
+"""Sharded-checkpoint description of adapter-wrapped models (parity: reference
+``src/mcore_bridge/tuners/utils.py:8-28``, ``src/mcore_bridge/tuners/lora.py:448-474``)."""
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, List
 
 from torch import nn
 
 
-def tuners_sharded_state_dict(module: nn.Module, prefix: str = '', sharded_offsets=(), metadata=None) -> Dict[str, dict]:
-    """Describes every trainable adapter tensor with its sharding so a sharded checkpoint writer can place it:
-    ``{key: {'tensor', 'tp_parallel', 'partition_dim', 'is_expert'}}``."""
-    out = {}
-    for name, p in module.named_parameters():
-        if 'lora_' not in name and 'modules_to_save' not in name:
-            continue
-        out[prefix + name] = {
-            'tensor': p,
-            'tp_parallel': bool(getattr(p, 'tensor_model_parallel', False)),
-            'partition_dim': int(getattr(p, 'partition_dim', -1)),
-            'is_expert': bool(getattr(p, 'is_expert', False)),
-        }
-    return out
+def tuners_sharded_state_dict(module: nn.Module, prefix: str = '', sharded_offsets=(), metadata=None) -> Dict[str, List]:
+    """The trainable adapter tensors (LoRA factors, ``modules_to_save`` copies) of ``module`` as sharded-checkpoint
+    pieces: ``{key: [ShardedTensor, ...]}`` with global shape, this rank's offset and the writer flag, ready for
+    ``train.dist_checkpoint.save`` / ``load`` (``trainable_only=True`` does the same for a whole model)."""
+    from ..train.dist_checkpoint import sharded_state_dict
+    full = sharded_state_dict([module], prefix)
+    return {k: v for k, v in full.items() if 'lora_' in k or 'modules_to_save' in k}
