@@ -1,14 +1,18 @@
 // Tensor-parallel GEMMs fused with their collective over NVLink peer memory (one kernel each):
 //
+// Every CTA runs the GEMM roles (TMA producer, MMA issuer, four epilogue warps) plus four communication warps, so no
+// SM is taken away from the tensor cores and all 148 SMs contribute loads in flight to the exchange (a single SM
+// sustains only a few tens of GB/s of peer or staged reads; the link needs several hundred).
+//
 //   all-gather -> GEMM   C[M,N] = gather(A_shards)[M,K] . B^T       (column-parallel fwd, row-parallel dgrad)
-//       A few "copy CTAs" pull the peers' shards with bulk (TMA) copies through shared memory into a local
-//       gathered buffer and publish a flag per 128-row block; the GEMM CTAs start on the local shard and
-//       consume remote blocks in arrival order, so the transfer hides behind the math tile by tile.
+//       The communication warps pull the peers' shards with vector loads over NVLink into a local gathered buffer,
+//       16 KiB units in ring order, and publish a flag per 128-row block once its units are all in; the GEMM roles
+//       start on the local shard and consume remote blocks in arrival order, so the transfer hides behind the math.
 //
 //   GEMM -> reduce-scatter   out[M/w, N] = sum_ranks (A . B^T)[rows of this rank]   (row-parallel fwd, column dgrad)
 //       Each epilogue warp pushes its part of a bf16 partial tile straight into the staging buffer of the rank
-//       that owns the rows (contiguous 4 KiB bulk copies over NVLink) and bumps a counter there; a few CTAs of the
-//       same launch sum the rows this rank owns, row block by row block, as their counters fill.
+//       that owns the rows (contiguous 4 KiB bulk copies over NVLink) and bumps a counter there; the communication
+//       warps sum the rows this rank owns, row block by row block, as their counters fill.
 //
 // No TMA multicast anywhere; remote data is only touched by plain bulk copies, ld/st and red.
 // Every cross-rank wait is bounded and reports through the status word.
@@ -31,15 +35,17 @@ constexpr int F_TICKET = 32;      // RS: CTA completion ticket
 constexpr int F_CNT = 64;         // [2][2048] RS: tiles pushed per row block, per epoch parity
 constexpr int F_CNT_STRIDE = 2048;
 
-constexpr int COPY_STAGES = 12;
-constexpr int COPY_CHUNK = 16384;
-constexpr int COPY_STORES_IN_FLIGHT = 3;
+constexpr int F_BLKCNT = 4160;    // [<=4096]  AG: copy units finished per gathered block (the finisher resets it)
+
+constexpr int COMM_WARPS = 4;                                  // communication warps per CTA (warps 6..9)
+constexpr int COMM_THREADS = GEMM_THREADS + COMM_WARPS * 32;   // 320
+constexpr int AG_UNIT_BYTES = 16384;                           // what one warp copies between two flag updates
+constexpr int AG_LOADS = 8;                                    // 16-byte loads a lane keeps in flight
 
 struct CommGemmParams {
   int M, N, K;
   int world, rank, epoch;
   int rows_per_rank;
-  int copy_ctas;
   const void* peer_shard[MAX_WORLD];
   void* gathered;
   uint32_t* peer_flags[MAX_WORLD];
@@ -50,7 +56,6 @@ struct CommGemmParams {
   void* out;
   long long ld_out;
   int* status;
-  int reduce_ctas;  // GEMM -> RS: CTAs at the end of the grid that only sum staged partial tiles
 };
 
 constexpr int RS_SLAB_COLS = 64;
@@ -86,7 +91,7 @@ struct CommSched {
 // all-gather -> GEMM
 // ----------------------------------------------------------------------------------------------------------
 template <int BN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(COMM_THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_constant__ CUtensorMap tmap_a_gath,
                const __grid_constant__ CUtensorMap tmap_b, const CommGemmParams p) {
   using L = GemmSmem<BN>;
@@ -98,99 +103,6 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_co
   const uint32_t epoch = (uint32_t)p.epoch;
   const int bps = p.rows_per_rank / GEMM_BM;
 
-  if ((int)blockIdx.x < p.copy_ctas) {
-    // =================================================================== copy CTA
-    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + COPY_STAGES * COPY_CHUNK);
-    uint64_t* full = bars;
-    uint64_t* empty = bars + COPY_STAGES;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * COPY_STAGES);
-    if (threadIdx.x == 0) {
-      *abort_flag = 0;
-      for (int s = 0; s < COPY_STAGES; ++s) {
-        mbar_init(smem_u32(&full[s]), 1);
-        mbar_init(smem_u32(&empty[s]), 1);
-      }
-      fence_barrier_init();
-      fence_proxy_async_smem();
-    }
-    __syncthreads();
-    // announce that this rank's shard (written by the preceding kernel in stream order) may be read
-    if (blockIdx.x == 0 && (int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
-      fence_acq_rel_sys();
-      st_release_sys(p.peer_flags[threadIdx.x] + F_READY + p.rank, epoch);
-    }
-    const long long block_bytes = (long long)GEMM_BM * p.K * 2;
-    const int chunks_per_block = (int)((block_bytes + COPY_CHUNK - 1) / COPY_CHUNK);
-    const int nblocks = p.world * bps;  // remote shards in ring order, then the local shard
-    if (warp == 0 && lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int i = blockIdx.x; i < nblocks && ok; i += p.copy_ctas) {
-        const int step = i / bps, blk = i - step * bps;
-        const int s = step < p.world - 1 ? (p.rank + 1 + step) % p.world : p.rank;
-        if (s != p.rank && !wait_flag<SCOPE_SYS>(lflags + F_READY + s, epoch, false, abort_flag, p.status)) break;
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.peer_shard[s]) + (long long)blk * block_bytes;
-        for (int c = 0; c < chunks_per_block; ++c, ++it) {
-          const uint32_t st = it % COPY_STAGES, ph = (it / COPY_STAGES) & 1;
-          if (!mbar_wait(smem_u32(&empty[st]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
-            ok = false;
-            break;
-          }
-          const long long off = (long long)c * COPY_CHUNK;
-          const uint32_t bytes = (uint32_t)min((long long)COPY_CHUNK, block_bytes - off);
-          mbar_expect_tx(smem_u32(&full[st]), bytes);
-          bulk_load_1d(smem_u32(ring + st * COPY_CHUNK), src + off, bytes, smem_u32(&full[st]));
-        }
-      }
-      // drain: loads this thread issued must land before the CTA exits
-      uint32_t first = it > COPY_STAGES ? it - COPY_STAGES : 0;
-      for (uint32_t j = first; j < it; ++j) {
-        const uint32_t st = j % COPY_STAGES, ph = (j / COPY_STAGES) & 1;
-        uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(smem_u32(&full[st]), ph)) {
-          if (globaltimer_ns() - t0 > 200000000ull) break;
-        }
-      }
-    } else if (warp == 1 && lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int i = blockIdx.x; i < nblocks && ok; i += p.copy_ctas) {
-        const int step = i / bps, blk = i - step * bps;
-        const int s = step < p.world - 1 ? (p.rank + 1 + step) % p.world : p.rank;
-        const int gblock = s * bps + blk;
-        uint8_t* dst = reinterpret_cast<uint8_t*>(p.gathered) + (long long)gblock * block_bytes;
-        const uint32_t block_first = it;
-        for (int c = 0; c < chunks_per_block; ++c, ++it) {
-          const uint32_t st = it % COPY_STAGES, ph = (it / COPY_STAGES) & 1;
-          if (!mbar_wait(smem_u32(&full[st]), ph, abort_flag, p.status, ST_TIMEOUT_FULL)) {
-            ok = false;
-            break;
-          }
-          const long long off = (long long)c * COPY_CHUNK;
-          const uint32_t bytes = (uint32_t)min((long long)COPY_CHUNK, block_bytes - off);
-          bulk_store_1d(dst + off, smem_u32(ring + st * COPY_CHUNK), bytes);
-          tma_store_commit();
-          // stores older than the most recent few have finished reading their stage: hand it back
-          tma_store_wait_read<COPY_STORES_IN_FLIGHT>();
-          if (it >= block_first + COPY_STORES_IN_FLIGHT)
-            mbar_arrive(smem_u32(&empty[(it - COPY_STORES_IN_FLIGHT) % COPY_STAGES]));
-        }
-        tma_store_wait<0>();  // the whole block is in global memory
-        if (ok) {
-          const uint32_t done = it;
-          const uint32_t from = done >= block_first + COPY_STORES_IN_FLIGHT ? done - COPY_STORES_IN_FLIGHT : block_first;
-          for (uint32_t j = from; j < done; ++j) mbar_arrive(smem_u32(&empty[j % COPY_STAGES]));
-          fence_proxy_async_all();
-          st_release_gpu(lflags + F_BLOCK + gblock, epoch);
-        }
-      }
-      tma_store_wait<0>();
-    }
-    return;
-  }
-
-  // ===================================================================== GEMM CTA
   Pipe<BN> P(smem_raw);
   if (threadIdx.x == 0) {
     P.init();
@@ -202,12 +114,70 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_co
     tmem_alloc(smem_u32(P.tmem_slot), TMEM_COLS);
     tmem_relinquish();
   }
+  // announce that this rank's shard (written by the preceding kernel in stream order) may be read
+  if (blockIdx.x == 0 && warp == 2 && lane < p.world && lane != p.rank) {
+    fence_acq_rel_sys();
+    st_release_sys(p.peer_flags[lane] + F_READY + p.rank, epoch);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *P.tmem_slot;
   CommSched sched(p, BN, 0);
-  const int g0 = blockIdx.x - p.copy_ctas, gs = gridDim.x - p.copy_ctas;
+  const int g0 = blockIdx.x, gs = gridDim.x;
+
+  if (warp >= GEMM_THREADS / 32) {
+    // =================================================================== communication warps: gather the shards
+    const long long block_bytes = (long long)GEMM_BM * p.K * 2;
+    const int upb = (int)((block_bytes + AG_UNIT_BYTES - 1) / AG_UNIT_BYTES);   // units per 128-row block
+    const long long units = (long long)p.world * bps * upb;     // remote shards in ring order, then the local one
+    const long long cw = (long long)blockIdx.x * COMM_WARPS + (warp - GEMM_THREADS / 32);
+    const long long ncw = (long long)gridDim.x * COMM_WARPS;
+    int ready_src = -1;
+    for (long long u = cw; u < units; u += ncw) {
+      const int i = (int)(u / upb), c = (int)(u - (long long)i * upb);
+      const int step = i / bps, blk = i - step * bps;
+      const int s = step < p.world - 1 ? (p.rank + 1 + step) % p.world : p.rank;
+      if (s != p.rank && s != ready_src) {
+        int good = 1;
+        if (lane == 0) good = wait_flag<SCOPE_SYS>(lflags + F_READY + s, epoch, false, P.abort_flag, p.status);
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) break;
+        ready_src = s;
+      }
+      const int gblock = s * bps + blk;
+      const long long off = (long long)c * AG_UNIT_BYTES;
+      const int n16 = (int)(min((long long)AG_UNIT_BYTES, block_bytes - off) / 16);
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.peer_shard[s]) +
+                                                        (long long)blk * block_bytes + off);
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.gathered) + (long long)gblock * block_bytes + off);
+      for (int base = 0; base < n16; base += 32 * AG_LOADS) {
+        uint4 v[AG_LOADS];
+#pragma unroll
+        for (int j = 0; j < AG_LOADS; ++j) {
+          const int idx = base + j * 32 + lane;
+          if (idx < n16) v[j] = src[idx];               // every load is issued before the first store
+        }
+#pragma unroll
+        for (int j = 0; j < AG_LOADS; ++j) {
+          const int idx = base + j * 32 + lane;
+          if (idx < n16) dst[idx] = v[j];
+        }
+      }
+      __syncwarp();
+      if (lane == 0 && s != p.rank) {
+        // the warp that completes a block publishes it: its own fence orders its stores before the count, the
+        // fence after the count orders the other warps' (already counted, hence fenced) stores before the flag
+        __threadfence();
+        const uint32_t done = atomicAdd(lflags + F_BLKCNT + gblock, 1u) + 1u;
+        if (done == (uint32_t)upb) {
+          __threadfence();
+          lflags[F_BLKCNT + gblock] = 0;
+          st_release_gpu(lflags + F_BLOCK + gblock, epoch);
+        }
+      }
+    }
+  } else
 
   if (warp == 0) {
     if (lane == 0) {
@@ -312,7 +282,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_co
 //
 // Tile order is row-block-major: for each row block, every destination rank in turn (own rows last), every column
 // tile.  A row block of the owner is therefore complete once every source is 1/bps of the way through its tiles,
-// and the last `reduce_ctas` CTAs of the grid sum finished row blocks while the others are still pushing.
+// and the communication warps of all CTAs sum finished row blocks while the GEMM roles are still pushing.
 struct RsSched {
   int tiles_n, total, bps, world, rank, BN;
   __device__ RsSched(const CommGemmParams& p, int bn) : world(p.world), rank(p.rank), BN(bn) {
@@ -330,30 +300,37 @@ struct RsSched {
   }
 };
 
-// Reducer pipeline: a stage of the shared-memory ring holds the same RS_PIECE-byte run of one row block from each
-// of SRC (>= world) sources; RS_RED_STAGES stages are in flight as bulk copies while four warps sum and store.
-constexpr int RS_RED_STAGE_BYTES = 32768;
-constexpr int RS_RED_STAGES = 6;
-constexpr int RS_RED_CONSUMERS = 128;  // warps 2..5
+// One warp sums RS_UNIT_POS consecutive 16-byte positions of one row block over SRC (>= world) staged sources and
+// writes bf16 output rows.  A lane keeps 16 loads in flight (16 / SRC positions x SRC sources).
+constexpr int RS_UNIT_POS = 1024;     // 16 KiB per source between two counter checks
 
-// Sums one stage (piece bytes from each of SRC sources, source s at ring offset s * piece) into bf16 output rows.
-// `byte0` is the offset of the piece inside the row block's staged tiles.
 template <int SRC>
-__device__ __forceinline__ void rs_reduce_stage(const CommGemmParams& p, const uint8_t* st, int blk, long long byte0) {
-  constexpr int PIECE = RS_RED_STAGE_BYTES / SRC;
-  constexpr int POS = PIECE / 16 / RS_RED_CONSUMERS;
-  const int t = threadIdx.x - 64;
+__device__ __forceinline__ void rs_reduce_unit(const CommGemmParams& p, const uint8_t* stage, int blk, int bps, int tiles_n,
+                                               long long pos0, int lane) {
+  constexpr int POS = 16 / SRC;
+  const long long src_stride = (long long)bps * tiles_n * RS_TILE_BYTES;
+  const uint8_t* base = stage + (long long)blk * tiles_n * RS_TILE_BYTES;
+#pragma unroll 1
+  for (int r0 = 0; r0 < RS_UNIT_POS; r0 += 32 * POS) {
+    uint4 raw[POS][SRC];
 #pragma unroll
-  for (int u = 0; u < POS; ++u) {
-    const int w16 = u * RS_RED_CONSUMERS + t;      // 16-byte position inside the piece
-    float acc[8];
+    for (int u = 0; u < POS; ++u) {
+      const long long pos = pos0 + r0 + u * 32 + lane;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int s = 0; s < SRC; ++s) {
+        if (s < p.world) raw[u][s] = __ldcs(reinterpret_cast<const uint4*>(base + s * src_stride + pos * 16));
+        else raw[u][s] = make_uint4(0, 0, 0, 0);
+      }
+    }
 #pragma unroll
-    for (int s = 0; s < SRC; ++s) {
-      if (s < p.world) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(st + s * PIECE + w16 * 16);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    for (int u = 0; u < POS; ++u) {
+      const long long pos = pos0 + r0 + u * 32 + lane;
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+      for (int s = 0; s < SRC; ++s) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][s]);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 f = __bfloat1622float2(h[e]);
@@ -361,28 +338,27 @@ __device__ __forceinline__ void rs_reduce_stage(const CommGemmParams& p, const u
           acc[2 * e + 1] += f.y;
         }
       }
-    }
-    const long long pos = (byte0 >> 4) + w16;
-    const int tn = (int)(pos >> 12);            // 4096 positions per tile
-    const int i = (int)(pos & 4095);
-    const int slab = i >> 10, w = i & 1023;     // 1024 positions per slab, 8 per row
-    const int r = w >> 3;
-    const int c = (w & 7) ^ (r & 7);            // undo the 128-byte swizzle
-    const int col = tn * 256 + slab * RS_SLAB_COLS + c * 8;
-    if (col < p.N) {
-      uint4 o;
-      o.x = pack_bf16x2(acc[0], acc[1]);
-      o.y = pack_bf16x2(acc[2], acc[3]);
-      o.z = pack_bf16x2(acc[4], acc[5]);
-      o.w = pack_bf16x2(acc[6], acc[7]);
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((long long)blk * GEMM_BM + r) * p.ld_out;
-      *reinterpret_cast<uint4*>(orow + col) = o;
+      const int tn = (int)(pos >> 12);            // 4096 positions per tile
+      const int i = (int)(pos & 4095);
+      const int slab = i >> 10, w = i & 1023;     // 1024 positions per slab, 8 per row
+      const int r = w >> 3;
+      const int c = (w & 7) ^ (r & 7);            // undo the 128-byte swizzle
+      const int col = tn * 256 + slab * RS_SLAB_COLS + c * 8;
+      if (col < p.N) {
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((long long)blk * GEMM_BM + r) * p.ld_out;
+        *reinterpret_cast<uint4*>(orow + col) = o;
+      }
     }
   }
 }
 
 template <int BN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(COMM_THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const CommGemmParams p) {
   static_assert(BN == 256, "the staging layout assumes 256-column tiles");
@@ -395,82 +371,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int parity = p.epoch & 1;
   RsSched sched(p, BN);
   const int bps = sched.bps;
-  const int gemm_ctas = (int)gridDim.x - p.reduce_ctas;
+  const int gemm_ctas = (int)gridDim.x;
   Pipe<BN> P(smem_raw);
-  const bool reducer = (int)blockIdx.x >= gemm_ctas;
 
-  if (reducer) {
-    // ================================================================= reducer CTA: sum the rows this rank owns
-    uint8_t* ring = P.smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + RS_RED_STAGES * RS_RED_STAGE_BYTES);
-    uint64_t* full = bars;
-    uint64_t* empty = bars + RS_RED_STAGES;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * RS_RED_STAGES);
-    if (threadIdx.x == 0) {
-      *abort_flag = 0;
-      for (int s = 0; s < RS_RED_STAGES; ++s) {
-        mbar_init(smem_u32(&full[s]), 1);
-        mbar_init(smem_u32(&empty[s]), 4);  // one arrive per consumer warp
-      }
-      fence_barrier_init();
-      fence_proxy_async_smem();
-    }
-    __syncthreads();
-    const uint32_t want = (uint32_t)(p.world * sched.tiles_n * 4);  // one increment per epilogue warp per tile
-    const int src_lanes = p.world <= 2 ? 2 : (p.world <= 4 ? 4 : 8);
-    const int piece = RS_RED_STAGE_BYTES / src_lanes;
-    const long long blk_bytes = (long long)sched.tiles_n * RS_TILE_BYTES;       // per source and row block
-    const long long src_stride = (long long)bps * blk_bytes;
-    const int upb = (int)(blk_bytes / piece);                                    // units (stages) per row block
-    const long long units = (long long)bps * upb;
-    const uint8_t* stage = reinterpret_cast<const uint8_t*>(p.peer_stage[p.rank]);
-    const int first = (int)blockIdx.x - gemm_ctas;
-    if (warp == 0) {
-      if (lane == 0) {
-        uint32_t it = 0;
-        int ready_blk = -1;
-        for (long long g = first; g < units; g += p.reduce_ctas, ++it) {
-          const int blk = (int)(g / upb);
-          const long long byte0 = (g - (long long)blk * upb) * piece;
-          if (blk != ready_blk) {
-            if (!wait_flag<SCOPE_SYS>(lflags + F_CNT + parity * F_CNT_STRIDE + blk, want, false, abort_flag, p.status)) break;
-            fence_proxy_async_all();  // the bulk copies below must observe what the counter published
-            ready_blk = blk;
-          }
-          const uint32_t stg = it % RS_RED_STAGES, ph = (it / RS_RED_STAGES) & 1;
-          if (!mbar_wait(smem_u32(&empty[stg]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
-          const uint32_t fb = smem_u32(&full[stg]);
-          mbar_expect_tx(fb, (uint32_t)(p.world * piece));
-          for (int s = 0; s < p.world; ++s)
-            bulk_load_1d(smem_u32(ring + stg * RS_RED_STAGE_BYTES + s * piece),
-                         stage + s * src_stride + (long long)blk * blk_bytes + byte0, (uint32_t)piece, fb);
-        }
-        // drain: copies this thread issued must land before the CTA exits
-        const uint32_t lo = it > RS_RED_STAGES ? it - RS_RED_STAGES : 0;
-        for (uint32_t j = lo; j < it; ++j) {
-          const uint32_t stg = j % RS_RED_STAGES, ph = (j / RS_RED_STAGES) & 1;
-          const uint64_t t0 = globaltimer_ns();
-          while (!mbar_try_wait(smem_u32(&full[stg]), ph)) {
-            if (globaltimer_ns() - t0 > 200000000ull) break;
-          }
-        }
-      }
-    } else if (warp >= 2) {
-      uint32_t it = 0;
-      for (long long g = first; g < units; g += p.reduce_ctas, ++it) {
-        const int blk = (int)(g / upb);
-        const long long byte0 = (g - (long long)blk * upb) * piece;
-        const uint32_t stg = it % RS_RED_STAGES, ph = (it / RS_RED_STAGES) & 1;
-        if (!mbar_wait(smem_u32(&full[stg]), ph, abort_flag, p.status, ST_TIMEOUT_FULL)) break;
-        const uint8_t* st = ring + stg * RS_RED_STAGE_BYTES;
-        if (src_lanes == 2) rs_reduce_stage<2>(p, st, blk, byte0);
-        else if (src_lanes == 4) rs_reduce_stage<4>(p, st, blk, byte0);
-        else rs_reduce_stage<8>(p, st, blk, byte0);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&empty[stg]));
-      }
-    }
-  } else {
+  {
     // ================================================================= GEMM CTA
     if (threadIdx.x == 0) {
       P.init();
@@ -486,7 +390,33 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = *P.tmem_slot;
 
-    if (warp == 0) {
+    if (warp >= GEMM_THREADS / 32) {
+      // ================================================================= communication warps: sum the rows this
+      // rank owns, row block by row block, as the counters say that every source has pushed its tiles
+      const uint32_t want = (uint32_t)(p.world * sched.tiles_n * 4);  // one increment per epilogue warp per tile
+      const long long npos_blk = (long long)sched.tiles_n * (RS_TILE_BYTES / 16);
+      const int upb = (int)(npos_blk / RS_UNIT_POS);
+      const long long units = (long long)bps * upb;
+      const uint8_t* stage = reinterpret_cast<const uint8_t*>(p.peer_stage[p.rank]);
+      const long long cw = (long long)blockIdx.x * COMM_WARPS + (warp - GEMM_THREADS / 32);
+      const long long ncw = (long long)gridDim.x * COMM_WARPS;
+      int ready_blk = -1;
+      for (long long u = cw; u < units; u += ncw) {
+        const int blk = (int)(u / upb);
+        const long long pos0 = (u - (long long)blk * upb) * RS_UNIT_POS;
+        if (blk != ready_blk) {
+          int good = 1;
+          if (lane == 0)
+            good = wait_flag<SCOPE_SYS>(lflags + F_CNT + parity * F_CNT_STRIDE + blk, want, false, P.abort_flag, p.status);
+          good = __shfl_sync(0xffffffffu, good, 0);
+          if (!good) break;
+          ready_blk = blk;
+        }
+        if (p.world <= 2) rs_reduce_unit<2>(p, stage, blk, bps, sched.tiles_n, pos0, lane);
+        else if (p.world <= 4) rs_reduce_unit<4>(p, stage, blk, bps, sched.tiles_n, pos0, lane);
+        else rs_reduce_unit<8>(p, stage, blk, bps, sched.tiles_n, pos0, lane);
+      }
+    } else if (warp == 0) {
       if (lane == 0) {
         uint32_t it = 0;
         for (int t = blockIdx.x; t < sched.total; t += gemm_ctas) {
@@ -628,26 +558,13 @@ extern "C" {
 // flags_ptrs / shard_ptrs / stage_ptrs: host arrays of `world` device pointers (index = group rank)
 int mcb_ag_gemm_bf16(const void* const* shard_ptrs, void* const* flag_ptrs, void* gathered, const void* B, long long b_inner,
                      long long b_outer, long long ldb, int b_mn, void* C, long long ldc, const void* bias, int M, int N,
-                     int K, int world, int rank, int epoch, int copy_ctas, int* status, void* stream_) {
+                     int K, int world, int rank, int epoch, int* status, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (world < 2 || world > MAX_WORLD || M % (world * GEMM_BM) || K % 8 || N % 8) return -2;
   const int rows = M / world;
-  if (M / GEMM_BM > 4096 - F_BLOCK) return -3;
+  if (M / GEMM_BM > 4096) return -3;
   constexpr int BN = 256;
-  int sms = device_sm_count();
-  if (copy_ctas <= 0) {
-    // balance the two roles: copy CTAs each sustain ~27 GB/s of NVLink pulls (measured), a GEMM CTA ~9.5 TFLOP/s.
-    const double bytes = (double)(world - 1) * rows * K * 2.0, flops = 2.0 * M * (double)N * K;
-    double best = 1e30;
-    int best_c = 12;
-    for (int c = 8; c <= 48; c += 4) {
-      const double t_copy = bytes / (27e9 * c), t_gemm = flops / (9.5e12 * (sms - c));
-      const double t = t_copy > t_gemm ? t_copy : t_gemm;
-      if (t < best) { best = t; best_c = c; }
-    }
-    copy_ctas = best_c;
-  }
-  if (copy_ctas >= sms) return -4;
+  const int sms = device_sm_count();
   CUtensorMap ta_l, ta_g, tb;
   int rc = make_tmap_2d_bf16(&ta_l, shard_ptrs[rank], K, rows, K, GEMM_BK, GEMM_BM);
   if (rc) return rc;
@@ -658,21 +575,22 @@ int mcb_ag_gemm_bf16(const void* const* shard_ptrs, void* const* flag_ptrs, void
   if (rc) return rc;
   CommGemmParams p{};
   p.M = M; p.N = N; p.K = K; p.world = world; p.rank = rank; p.epoch = epoch; p.rows_per_rank = rows;
-  p.copy_ctas = copy_ctas;
   for (int i = 0; i < world; ++i) {
     p.peer_shard[i] = shard_ptrs[i];
     p.peer_flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
   }
   p.gathered = gathered; p.C = C; p.ldc = ldc; p.bias = bias; p.status = status;
   const int smem = GemmSmem<BN>::TOTAL;
+  // every CTA also carries communication warps, so the whole GPU takes part even when there are few tiles
+  const int grid = sms;
   static bool cfg[2] = {false, false};
   cudaError_t e;
   if (b_mn) {
     if (!cfg[1]) { if ((e = set_smem(ag_gemm_kernel<BN, true>, smem)) != cudaSuccess) return (int)e; cfg[1] = true; }
-    ag_gemm_kernel<BN, true><<<sms, GEMM_THREADS, smem, stream>>>(ta_l, ta_g, tb, p);
+    ag_gemm_kernel<BN, true><<<grid, COMM_THREADS, smem, stream>>>(ta_l, ta_g, tb, p);
   } else {
     if (!cfg[0]) { if ((e = set_smem(ag_gemm_kernel<BN, false>, smem)) != cudaSuccess) return (int)e; cfg[0] = true; }
-    ag_gemm_kernel<BN, false><<<sms, GEMM_THREADS, smem, stream>>>(ta_l, ta_g, tb, p);
+    ag_gemm_kernel<BN, false><<<grid, COMM_THREADS, smem, stream>>>(ta_l, ta_g, tb, p);
   }
   return (int)cudaGetLastError();
 }
@@ -684,7 +602,7 @@ long long mcb_gemm_rs_stage_bytes(int M, int N) {
 
 int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_inner, long long b_outer, long long ldb,
                      int b_mn, void* const* stage_ptrs, void* const* flag_ptrs, void* out, long long ld_out, int M, int N,
-                     int K, int world, int rank, int epoch, int reduce_ctas, int* status, void* stream_) {
+                     int K, int world, int rank, int epoch, int* status, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (world < 2 || world > MAX_WORLD || M % (world * GEMM_BM) || K % 8 || N % 8 || lda % 8 || ld_out % 8) return -2;
   if ((reinterpret_cast<uintptr_t>(out) & 15) != 0) return -2;
@@ -693,19 +611,6 @@ int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_in
   constexpr int BN = 256;
   const int sms = device_sm_count();
   const long long tiles = (long long)(M / GEMM_BM) * ((N + BN - 1) / BN);
-  if (reduce_ctas <= 0) {
-    // balance the two roles: a reducer CTA streams ~100 GB/s of staged partials, a GEMM CTA sustains ~9.5 TFLOP/s
-    const double bytes = (double)M * N * 2.0, flops = 2.0 * M * (double)N * K;
-    double best = 1e30;
-    int best_r = 16;
-    for (int r = 4; r <= 40; r += 2) {
-      const double t_red = bytes / (100e9 * r), t_gemm = flops / (9.5e12 * (sms - r));
-      const double t = t_red > t_gemm ? t_red : t_gemm;
-      if (t < best) { best = t; best_r = r; }
-    }
-    reduce_ctas = best_r;
-  }
-  if (reduce_ctas >= sms) return -4;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, GEMM_BK, GEMM_BM);
   if (rc) return rc;
@@ -714,7 +619,6 @@ int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_in
   if (rc) return rc;
   CommGemmParams p{};
   p.M = M; p.N = N; p.K = K; p.world = world; p.rank = rank; p.epoch = epoch; p.rows_per_rank = rows;
-  p.reduce_ctas = reduce_ctas;
   for (int i = 0; i < world; ++i) {
     p.peer_stage[i] = stage_ptrs[i];
     p.peer_flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
@@ -722,16 +626,16 @@ int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_in
   p.out = out; p.ld_out = ld_out; p.status = status;
   // pipeline stages + barriers + two 4 KiB copy buffers per epilogue warp (+ alignment slack)
   const int smem = GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + 1024 + 4 * 2 * RS_WARP_BYTES + 1024;
-  const int gemm_ctas = (int)(tiles < sms - reduce_ctas ? tiles : sms - reduce_ctas);
-  const int grid = gemm_ctas + reduce_ctas;
+  (void)tiles;
+  const int grid = sms;      // every CTA also carries reducer warps
   static bool cfg[2] = {false, false};
   cudaError_t e;
   if (b_mn) {
     if (!cfg[1]) { if ((e = set_smem(gemm_rs_kernel<BN, true>, smem)) != cudaSuccess) return (int)e; cfg[1] = true; }
-    gemm_rs_kernel<BN, true><<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+    gemm_rs_kernel<BN, true><<<grid, COMM_THREADS, smem, stream>>>(ta, tb, p);
   } else {
     if (!cfg[0]) { if ((e = set_smem(gemm_rs_kernel<BN, false>, smem)) != cudaSuccess) return (int)e; cfg[0] = true; }
-    gemm_rs_kernel<BN, false><<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+    gemm_rs_kernel<BN, false><<<grid, COMM_THREADS, smem, stream>>>(ta, tb, p);
   }
   return (int)cudaGetLastError();
 }

@@ -26,8 +26,6 @@ def main():
     ap.add_argument('--qkv', type=int, default=6144)
     ap.add_argument('--ffn', type=int, default=12288)
     ap.add_argument('--iters', type=int, default=20)
-    ap.add_argument('--sweep', action='store_true',
-                    help='also time each fused kernel over a range of copy-CTA / reducer-CTA counts')
     a = ap.parse_args()
     from .ops import _lib, gemm
     from .parallel import fused_comm as fc
@@ -67,13 +65,6 @@ def main():
         comp = 2.0 * T * N * K / (GEMM_TFLOPS * 1e6)
         out.append(dict(op=f'ag_gemm {name}', fused_us=t_f, nccl_plus_gemm_us=t_n, link_us=link, compute_us=comp,
                         roofline_frac=max(link, comp) / t_f))
-        if a.sweep:
-            sw = {}
-            for c in (4, 8, 12, 16, 24, 32, 40, 48):
-                fc.COPY_CTAS = c
-                sw[c] = round(bench(lambda: fc.all_gather_gemm(x, w, None, 'tp')), 1)
-            fc.COPY_CTAS = 0
-            out[-1]['copy_ctas_us'] = sw
     for name, K, N in (('oproj', H // world, H), ('fc2', a.ffn // world, H)):
         xf = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
         w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
@@ -83,14 +74,7 @@ def main():
         comp = 2.0 * T * N * K / (GEMM_TFLOPS * 1e6)
         out.append(dict(op=f'gemm_rs {name}', fused_us=t_f, nccl_plus_gemm_us=t_n, link_us=link, compute_us=comp,
                         roofline_frac=max(link, comp) / t_f))
-        if a.sweep:
-            sw = {}
-            for c in (2, 4, 6, 8, 12, 16, 24, 32):
-                fc.REDUCE_CTAS = c
-                sw[c] = round(bench(lambda: fc.gemm_reduce_scatter(xf, w, 'tp')), 1)
-            fc.REDUCE_CTAS = 0
-            out[-1]['reduce_ctas_us'] = sw
-            out[-1]['gemm_only_us'] = round(bench(lambda: gemm.mm_nt(xf, w)), 1)
+        out[-1]['gemm_only_us'] = round(bench(lambda: gemm.mm_nt(xf, w)), 1)
     torch.cuda.synchronize()
     _lib.check_status()
     if rank == 0:

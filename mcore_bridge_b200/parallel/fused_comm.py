@@ -25,8 +25,6 @@ from . import symm
 FLAG_BYTES = 65536
 _c_ll, _c_int = ctypes.c_longlong, ctypes.c_int
 _ptr_cache: Dict[Tuple, ctypes.Array] = {}
-COPY_CTAS = int(os.environ.get('MCB200_AG_COPY_CTAS', '0'))  # 0: the launcher balances copy vs GEMM CTAs
-REDUCE_CTAS = int(os.environ.get('MCB200_RS_REDUCE_CTAS', '0'))  # 0: the launcher balances reducer vs GEMM CTAs
 
 
 def _on() -> bool:
@@ -93,7 +91,7 @@ def _ag(x2: torch.Tensor, b: torch.Tensor, b_inner: int, b_outer: int, b_mn: boo
     rc = _lib.lib().mcb_ag_gemm_bf16(
         _ptr_array(ws, off), _ptr_array(ws, 0), _lib.ptr(gathered), _lib.ptr(b), _c_ll(b_inner), _c_ll(b_outer),
         _c_ll(b.stride(0)), _c_int(int(b_mn)), _lib.ptr(out), _c_ll(out.stride(0)), _lib.ptr(bias), _c_int(M),
-        _c_int(n_out), _c_int(k_in), _c_int(ws.world), _c_int(ws.rank), _c_int(epoch), _c_int(COPY_CTAS),
+        _c_int(n_out), _c_int(k_in), _c_int(ws.world), _c_int(ws.rank), _c_int(epoch),
         _lib.ptr(_lib.status_word(x2.device)), _lib.stream_ptr())
     _lib.check_rc(rc, 'mcb_ag_gemm_bf16')
     return out, gathered
@@ -130,7 +128,7 @@ def _rs(a2: torch.Tensor, b: torch.Tensor, b_inner: int, b_outer: int, b_mn: boo
     rc = _lib.lib().mcb_gemm_rs_bf16(
         _lib.ptr(a2), _c_ll(a2.stride(0)), _lib.ptr(b), _c_ll(b_inner), _c_ll(b_outer), _c_ll(b.stride(0)),
         _c_int(int(b_mn)), _ptr_array(ws, off), _ptr_array(ws, 0), _lib.ptr(out), _c_ll(out.stride(0)), _c_int(M),
-        _c_int(n_out), _c_int(k_in), _c_int(ws.world), _c_int(ws.rank), _c_int(epoch), _c_int(REDUCE_CTAS),
+        _c_int(n_out), _c_int(k_in), _c_int(ws.world), _c_int(ws.rank), _c_int(epoch),
         _lib.ptr(_lib.status_word(a2.device)), _lib.stream_ptr())
     _lib.check_rc(rc, 'mcb_gemm_rs_bf16')
     return out
