@@ -61,7 +61,6 @@ struct CommGemmParams {
 constexpr int RS_SLAB_COLS = 64;
 constexpr int RS_SLAB_BYTES = GEMM_BM * RS_SLAB_COLS * 2;  // 16 KiB: 128 rows x 64 bf16 columns
 constexpr int RS_TILE_BYTES = 4 * RS_SLAB_BYTES;           // 64 KiB: one 128 x 256 partial tile
-constexpr int RS_WARP_BYTES = 32 * RS_SLAB_COLS * 2;       // 4 KiB: the 32 rows of one epilogue warp in a slab
 
 struct CommSched {
   int tiles_m, tiles_n, total, bps, BN, world, rank, first_step;
@@ -273,12 +272,11 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_local, const __grid_co
 // GEMM -> reduce-scatter
 // ----------------------------------------------------------------------------------------------------------
 // Staging layout (the owner's buffer, one half per epoch parity): tile-major, each 128x256 partial tile stored as
-// four 16 KiB slabs of 64 columns in the 128-byte-swizzled order the epilogue wrote them to shared memory,
-//     offset = ((source_rank * bps + row_block) * tiles_n + tile_n) * 64 KiB + slab * 16 KiB + row * 128 + swizzled chunk.
-// A slab quarter (the 32 rows of one epilogue warp) is 4 KiB contiguous both in shared memory and at the owner, so
-// each warp pushes it with one plain bulk copy: long contiguous NVLink writes, no tensor map, no CTA-wide barrier.
-// Because the sum over sources is element-wise, the reducer adds the staged tiles in that order and un-swizzles only
-// the output address.
+// four 16 KiB slabs of 64 columns, a slab as [8 column chunks of 16 bytes][128 rows],
+//     offset = ((source_rank * bps + row_block) * tiles_n + tile_n) * 64 KiB + slab * 16 KiB + (chunk * 128 + row) * 16.
+// An epilogue thread owns one row of the accumulator, so the 32 lanes of a warp hold 32 consecutive rows and each of
+// their store instructions covers 512 contiguous bytes of a chunk.  Because the sum over sources is element-wise, the
+// reducer adds the staged tiles in that order and only the output address undoes the layout.
 //
 // Tile order is row-block-major: for each row block, every destination rank in turn (own rows last), every column
 // tile.  A row block of the owner is therefore complete once every source is 1/bps of the way through its tiles,
@@ -340,10 +338,9 @@ __device__ __forceinline__ void rs_reduce_unit(const CommGemmParams& p, const ui
       }
       const int tn = (int)(pos >> 12);            // 4096 positions per tile
       const int i = (int)(pos & 4095);
-      const int slab = i >> 10, w = i & 1023;     // 1024 positions per slab, 8 per row
-      const int r = w >> 3;
-      const int c = (w & 7) ^ (r & 7);            // undo the 128-byte swizzle
-      const int col = tn * 256 + slab * RS_SLAB_COLS + c * 8;
+      const int slab = i >> 10, w = i & 1023;     // 1024 positions per slab: [8 column chunks][128 rows]
+      const int r = w & (GEMM_BM - 1);
+      const int col = tn * 256 + slab * RS_SLAB_COLS + (w >> 7) * 8;
       if (col < p.N) {
         uint4 o;
         o.x = pack_bf16x2(acc[0], acc[1]);
@@ -439,15 +436,15 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
     } else {
-      // Epilogue, one independent pipeline per warp: TMEM -> registers -> bf16 -> this warp's 4 KiB swizzled buffer
-      // (two of them, used alternately) -> bulk copy into the owner's staging tile.  A tile's counter is bumped one
-      // tile late, once the copies that carried it are known to be complete, so that latency hides behind the
-      // next tile.
+      // Epilogue: TMEM -> registers -> bf16 -> vector stores straight into the owner's staging tile (peer memory for
+      // the other ranks' rows).  The staging layout puts the 32 rows of a warp next to each other for every 16-byte
+      // column chunk, so each store instruction of a warp writes 512 contiguous bytes: full NVLink write packets
+      // without a shared-memory detour.  After a tile's stores a system-scope fence per lane, then one counter
+      // increment per warp publishes them.
       const int q = warp & 3;
-      uint8_t* wbuf = P.smem + GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + 1024 + q * (2 * RS_WARP_BYTES);
-      uint32_t lt = 0, sctr = 0;
+      const int r_local = q * 32 + lane;
+      uint32_t lt = 0;
       uint32_t verified = 0;       // bit s: rank s has released the staging half we are about to write
-      uint32_t* pend_cnt = nullptr;  // counter of the tile whose increment is still owed
       for (int t = blockIdx.x; t < sched.total; t += gemm_ctas, ++lt) {
         int shard, blk, tn;
         sched.get(t, shard, blk, tn);
@@ -465,18 +462,16 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           verified |= 1u << shard;
         }
-        uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer_stage[shard]) +
-                       ((long long)(p.rank * bps + blk) * sched.tiles_n + tn) * RS_TILE_BYTES + q * RS_WARP_BYTES;
-        int issued = 0;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peer_stage[shard]) +
+                                              ((long long)(p.rank * bps + blk) * sched.tiles_n + tn) * RS_TILE_BYTES) +
+                     r_local;
 #pragma unroll 1
-        for (int cc = 0; cc < BN; cc += RS_SLAB_COLS, ++sctr) {
+        for (int cc = 0; cc < BN; cc += RS_SLAB_COLS) {
           if (n0 + cc >= p.N) break;
-          uint8_t* buf = wbuf + (sctr & 1) * RS_WARP_BYTES;
-          if (lane == 0) tma_store_wait_read<1>();  // the copy that last used this buffer has finished reading it
-          __syncwarp();
           uint32_t r[64];
           tmem_ld_32x32_x64(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + cc, r);
           tmem_ld_wait();
+          uint4* slab = dst + (cc / RS_SLAB_COLS) * (RS_SLAB_BYTES / 16);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             uint4 o;
@@ -484,43 +479,16 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             o.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
             o.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
             o.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;  // 128-byte swizzle
+            slab[j * GEMM_BM] = o;     // chunk j of row r_local: unit (j * 128 + r_local) of the slab
           }
-          if (cc + RS_SLAB_COLS >= BN || n0 + cc + RS_SLAB_COLS >= p.N) {
-            // last slab of the tile: the accumulator can go back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&P.tempty_bar[acc]));
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            bulk_store_1d(dst + (cc / RS_SLAB_COLS) * RS_SLAB_BYTES, smem_u32(buf), RS_WARP_BYTES);
-            tma_store_commit();
-          }
-          ++issued;
         }
-        if (lane == 0) {
-          if (pend_cnt) {
-            // everything but this tile's copies is complete -> the previous tile may be published
-            if (issued >= 4) tma_store_wait<4>();
-            else if (issued == 3) tma_store_wait<3>();
-            else if (issued == 2) tma_store_wait<2>();
-            else tma_store_wait<1>();
-            fence_proxy_async_all();
-            fence_acq_rel_sys();
-            red_release_sys_add(pend_cnt, 1u);
-          }
-          pend_cnt = p.peer_flags[shard] + F_CNT + parity * F_CNT_STRIDE + blk;
-        }
-      }
-      if (lane == 0) {
-        tma_store_wait<0>();  // also on the give-up paths: the buffers must outlive the copies reading them
-        if (pend_cnt && !*P.abort_flag) {
-          fence_proxy_async_all();
-          fence_acq_rel_sys();
-          red_release_sys_add(pend_cnt, 1u);
-        }
+        // the accumulator can go back to the MMA warp before the stores are known to have landed
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&P.tempty_bar[acc]));
+        fence_acq_rel_sys();           // every lane: its stores are performed before the count below
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(p.peer_flags[shard] + F_CNT + parity * F_CNT_STRIDE + blk, 1u);
       }
     }
     tc_fence_before();
@@ -624,8 +592,7 @@ int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_in
     p.peer_flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
   }
   p.out = out; p.ld_out = ld_out; p.status = status;
-  // pipeline stages + barriers + two 4 KiB copy buffers per epilogue warp (+ alignment slack)
-  const int smem = GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + 1024 + 4 * 2 * RS_WARP_BYTES + 1024;
+  const int smem = GemmSmem<BN>::TOTAL;
   (void)tiles;
   const int grid = sms;      // every CTA also carries reducer warps
   static bool cfg[2] = {false, false};

@@ -463,6 +463,8 @@ __global__ void dw_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* 
 
 // Device address of the scratch array on the current device; resolved once per device.
 // In host code `g_rmsnorm_dw_scratch` itself is only a handle for the runtime, never a pointer a kernel may use.
+// The cache is filled without a lock: two host threads that race on a device's first call both resolve the same
+// address and store the same value (an aligned pointer store), so the race is benign.
 int noalloc_scratch_ptr(float** out) {
   static float* per_device[64] = {nullptr};
   int dev = 0;

@@ -4,6 +4,12 @@ shapes of a Qwen3-8B layer.  One process per GPU:
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29500 \\
         -m mcore_bridge_b200.bench_comm --tokens 32768
 
+    python -m torch.distributed.run ... -m mcore_bridge_b200.bench_comm --moe --tokens 16384   # expert parallel
+
+``--moe`` times one Qwen3-30B-A3B MoE layer (128 experts, top-8, hidden 2048, expert FFN 768), forward + backward,
+expert parallel over all ranks with ``--tokens`` tokens per rank: the exchange fused into the expert GEMMs, the
+separate pull dispatch / combine kernels, and the torch.distributed all-to-all path.
+
 Every number is device time (CUDA events) per call, max over ranks.  The roofline of a fused kernel is the slower of
 its FLOPs at the measured GEMM peak and the bytes that must cross NVLink at the measured peer bandwidth.
 """
@@ -19,6 +25,65 @@ LINK_GBS = 770.0          # measured peer copy bandwidth per direction per GPU o
 GEMM_TFLOPS = 1400.0      # sustained measured cuBLAS bf16
 
 
+def moe_main(a):
+    import os
+    from . import ModelConfig
+    from .config import hf_to_mcore_config
+    from .layers.moe import MoELayer
+    from .ops import _lib
+    from .parallel import state as ps
+    from .train.presets import hf_config
+    ps.init_distributed()
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    ps.initialize_model_parallel(expert_model_parallel_size=world)
+    dev = torch.device('cuda', torch.cuda.current_device())
+    kw = hf_to_mcore_config(hf_config('qwen3_30b_a3b'))
+    cfg = ModelConfig(**kw, bf16=True, expert_model_parallel_size=world)
+    torch.manual_seed(7)
+    with torch.device(dev):
+        layer = MoELayer(cfg).train()
+    T, H = a.tokens, cfg.hidden_size
+    torch.manual_seed(100 + rank)
+    x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+    dy = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+
+    def step():
+        layer.zero_grad(set_to_none=True)
+        xx = x.detach().requires_grad_()
+        layer(xx).backward(dy)
+
+    res = {}
+    for tag, fused, fgemm in (('fused_exchange_gemm', '1', '1'), ('pull_kernels', '1', '0'), ('all_to_all', '0', '0')):
+        os.environ['MCB200_FUSED_MOE'] = fused
+        os.environ['MCB200_MOE_FUSED_GEMM'] = fgemm
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(a.iters):
+            step()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / a.iters], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res[tag + '_us'] = round(t.item() * 1e3, 1)
+        _lib.check_status()
+    k, F = cfg.moe_router_topk, cfg.moe_ffn_hidden_size
+    flops = 3 * 2.0 * T * k * H * 3 * F          # fc1 (2F wide) + fc2, forward + two backward GEMMs each
+    res['compute_us'] = round(flops / (GEMM_TFLOPS * 1e6), 1)
+    res['link_us'] = round(4 * T * k * H * 2 * (world - 1) / world / (LINK_GBS * 1e3), 1)   # dispatch + combine, fwd + bwd
+    if rank == 0:
+        print(json.dumps({'op': 'moe_layer fwd+bwd', 'ep': world, 'tokens_per_rank': T} | res))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--tokens', type=int, default=8192, help='tokens of the full (gathered) micro-batch')
@@ -26,7 +91,10 @@ def main():
     ap.add_argument('--qkv', type=int, default=6144)
     ap.add_argument('--ffn', type=int, default=12288)
     ap.add_argument('--iters', type=int, default=20)
+    ap.add_argument('--moe', action='store_true', help='time the expert-parallel MoE layer instead of the TP kernels')
     a = ap.parse_args()
+    if a.moe:
+        return moe_main(a)
     from .ops import _lib, gemm
     from .parallel import fused_comm as fc
     from .parallel import mappings as M

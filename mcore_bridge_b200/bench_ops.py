@@ -69,7 +69,8 @@ def step_profile(a):
         if ev.device_type.name != 'CUDA':
             continue
         t = ev.device_time if hasattr(ev, 'device_time') else ev.cuda_time
-        name = ev.name.split('<')[0].split('(')[0][:70]
+        name = ev.name.replace('void ', '').replace('(anonymous namespace)::', '').replace('mcb::', '')
+        name = name.split('<')[0].split('(')[0][:70] or ev.name[:70]
         r = rows.setdefault(name, [0.0, 0])
         r[0] += t
         r[1] += 1

@@ -60,8 +60,9 @@ for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None
             if world>1: dist.all_reduce(t)
             ok &= t.item()==0
             if rank==0: print(f'E{E} k{k} H{H} sig{sig} mode {tag}: {n_} rel={r:.3e} {"OK" if t.item()==0 else "FAIL"}', flush=True)
-    # the row assignment of the fused path has no atomics: a second run gives the same bits
-    if True:
+    # the row assignment of the fused dispatch+GEMM path has no atomics: a second run gives the same bits
+    from mcore_bridge_b200.layers import moe_fused
+    if moe_fused.pull_gemm_supported(layer.experts, layer.config, E // world, H):
         os.environ['MCB200_FUSED_MOE'] = '1'; os.environ['MCB200_MOE_FUSED_GEMM'] = '1'
         layer.zero_grad(); xx = x.clone().requires_grad_(); y2 = layer(xx); y2.backward(dy)
         same = torch.equal(y2, outs['1'][0]) and torch.equal(layer.experts.linear_fc1.weight.grad, outs['1'][3])
