@@ -39,6 +39,7 @@ constexpr int F_BLKCNT = 4160;    // [<=4096]  AG: copy units finished per gathe
 
 constexpr int COMM_WARPS = 4;                                  // communication warps per CTA (warps 6..9)
 constexpr int COMM_THREADS = GEMM_THREADS + COMM_WARPS * 32;   // 320
+constexpr int RS_THREADS = COMM_THREADS + 32;                  // + the warp that publishes finished tiles (warp 10)
 constexpr int AG_UNIT_BYTES = 16384;                           // what one warp copies between two flag updates
 constexpr int AG_LOADS = 8;                                    // 16-byte loads a lane keeps in flight
 
@@ -355,7 +356,7 @@ __device__ __forceinline__ void rs_reduce_unit(const CommGemmParams& p, const ui
 }
 
 template <int BN, bool B_MN>
-__global__ void __launch_bounds__(COMM_THREADS, 1)
+__global__ void __launch_bounds__(RS_THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const CommGemmParams p) {
   static_assert(BN == 256, "the staging layout assumes 256-column tiles");
@@ -370,11 +371,13 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int bps = sched.bps;
   const int gemm_ctas = (int)gridDim.x;
   Pipe<BN> P(smem_raw);
+  uint32_t* pushed = P.tmem_slot + 2;     // [4]: tiles whose stores each epilogue warp has issued
 
   {
     // ================================================================= GEMM CTA
     if (threadIdx.x == 0) {
       P.init();
+      for (int i = 0; i < 4; ++i) pushed[i] = 0;
       prefetch_tensormap(&tmap_a);
       prefetch_tensormap(&tmap_b);
     }
@@ -387,10 +390,54 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = *P.tmem_slot;
 
-    if (warp >= GEMM_THREADS / 32) {
+    if (warp == COMM_THREADS / 32) {
+      // ================================================================= publisher: a system-scope fence costs a
+      // round trip to the peers, so it is kept off the epilogue warps.  This thread watches how many tiles all four
+      // epilogue warps have stored, fences once for everything new (the stores reach it through the warps'
+      // release / acquire on `pushed`), then bumps the owners' row-block counters.
+      if (lane == 0) {
+        const uint32_t my_tiles =
+            (int)blockIdx.x < sched.total ? (uint32_t)((sched.total - 1 - (int)blockIdx.x) / gemm_ctas + 1) : 0u;
+        uint32_t done = 0;
+        while (done < my_tiles) {
+          uint32_t n = done;
+          uint64_t t0 = 0;
+          bool good = false;
+          for (uint32_t it = 0; it < 0x7fffffffu; ++it) {
+            uint32_t lo = 0xffffffffu;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) lo = min(lo, ld_acquire_cta_shared(smem_u32(pushed + i)));
+            if (lo > done) {
+              n = lo;
+              good = true;
+              break;
+            }
+            if ((it & 0x3fu) == 0x3fu) {
+              if (*P.abort_flag) break;
+              const uint64_t now = globaltimer_ns();
+              if (t0 == 0) t0 = now;
+              if (now - t0 > wait_limit_ns(p.status)) {
+                *P.abort_flag = 1;
+                if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_TMEM_FULL);
+                break;
+              }
+            }
+            __nanosleep(32);
+          }
+          if (!good) break;
+          fence_acq_rel_sys();
+          for (uint32_t i = done; i < n; ++i) {
+            int shard, blk, tn;
+            sched.get((int)blockIdx.x + (int)i * gemm_ctas, shard, blk, tn);
+            red_relaxed_sys_add(p.peer_flags[shard] + F_CNT + parity * F_CNT_STRIDE + blk, 4u);
+          }
+          done = n;
+        }
+      }
+    } else if (warp >= GEMM_THREADS / 32) {
       // ================================================================= communication warps: sum the rows this
       // rank owns, row block by row block, as the counters say that every source has pushed its tiles
-      const uint32_t want = (uint32_t)(p.world * sched.tiles_n * 4);  // one increment per epilogue warp per tile
+      const uint32_t want = (uint32_t)(p.world * sched.tiles_n * 4);  // the publisher adds 4 per tile
       const long long npos_blk = (long long)sched.tiles_n * (RS_TILE_BYTES / 16);
       const int upb = (int)(npos_blk / RS_UNIT_POS);
       const long long units = (long long)bps * upb;
@@ -439,8 +486,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // Epilogue: TMEM -> registers -> bf16 -> vector stores straight into the owner's staging tile (peer memory for
       // the other ranks' rows).  The staging layout puts the 32 rows of a warp next to each other for every 16-byte
       // column chunk, so each store instruction of a warp writes 512 contiguous bytes: full NVLink write packets
-      // without a shared-memory detour.  After a tile's stores a system-scope fence per lane, then one counter
-      // increment per warp publishes them.
+      // without a shared-memory detour.  The warp then only notes the tile in shared memory; the publisher warp
+      // makes it visible to the owner.
       const int q = warp & 3;
       const int r_local = q * 32 + lane;
       uint32_t lt = 0;
@@ -482,13 +529,12 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             slab[j * GEMM_BM] = o;     // chunk j of row r_local: unit (j * 128 + r_local) of the slab
           }
         }
-        // the accumulator can go back to the MMA warp before the stores are known to have landed
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&P.tempty_bar[acc]));
-        fence_acq_rel_sys();           // every lane: its stores are performed before the count below
-        __syncwarp();
-        if (lane == 0) red_release_sys_add(p.peer_flags[shard] + F_CNT + parity * F_CNT_STRIDE + blk, 1u);
+        __syncwarp();                  // orders every lane's stores before lane 0's release below
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&P.tempty_bar[acc]));
+          st_release_cta_shared(smem_u32(pushed + q), lt + 1);
+        }
       }
     }
     tc_fence_before();
@@ -599,10 +645,10 @@ int mcb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long b_in
   cudaError_t e;
   if (b_mn) {
     if (!cfg[1]) { if ((e = set_smem(gemm_rs_kernel<BN, true>, smem)) != cudaSuccess) return (int)e; cfg[1] = true; }
-    gemm_rs_kernel<BN, true><<<grid, COMM_THREADS, smem, stream>>>(ta, tb, p);
+    gemm_rs_kernel<BN, true><<<grid, RS_THREADS, smem, stream>>>(ta, tb, p);
   } else {
     if (!cfg[0]) { if ((e = set_smem(gemm_rs_kernel<BN, false>, smem)) != cudaSuccess) return (int)e; cfg[0] = true; }
-    gemm_rs_kernel<BN, false><<<grid, COMM_THREADS, smem, stream>>>(ta, tb, p);
+    gemm_rs_kernel<BN, false><<<grid, RS_THREADS, smem, stream>>>(ta, tb, p);
   }
   return (int)cudaGetLastError();
 }

@@ -140,8 +140,8 @@ template <int VPT>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
-                                   float* __restrict__ dw, long long rows, int H, long long ldx, float eps,
-                                   int zero_centered) {
+                                   float* __restrict__ dw, float* __restrict__ partials, long long rows, int H,
+                                   long long ldx, float eps, int zero_centered) {
   __shared__ float red[66];
   const int nvec = H / 8;
   float dwacc[VPT][8];
@@ -241,7 +241,18 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
       }
     }
   }
-  if (dw) {
+  if (partials) {
+    // one row of partial sums per CTA; rmsnorm_dw_reduce_kernel adds the rows in a fixed order
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        float4* o = reinterpret_cast<float4*>(partials + (long long)blockIdx.x * H + vi * 8);
+        o[0] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+        o[1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+      }
+    }
+  } else if (dw) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = threadIdx.x + i * blockDim.x;
@@ -251,6 +262,16 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
       }
     }
   }
+}
+
+// dw[h] += sum over the CTAs' partial rows, always in row order: the weight gradient repeats bit for bit
+__global__ void __launch_bounds__(256) rmsnorm_dw_reduce_kernel(const float* __restrict__ partials, int nparts, int H,
+                                                                float* __restrict__ dw) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  float acc = 0.f;
+  for (int b = 0; b < nparts; ++b) acc += partials[(long long)b * H + h];
+  dw[h] += acc;
 }
 
 // ------------------------------------------------------------------ gated activations
@@ -390,12 +411,11 @@ int mcb_rmsnorm_fwd(const void* x, const void* res_in, const void* w, void* y, v
   return (int)cudaGetLastError();
 }
 
-// dw (fp32, [H]) is accumulated into; pass nullptr to skip.  dres (optional) is added to dx (residual branch).
-int mcb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
-                    float* dw, long long rows, int H, long long ldx, float eps, int zero_centered, void* stream_) {
+static int rmsnorm_bwd_launch(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                              float* dw, float* partials, long long rows, int H, long long ldx, float eps,
+                              int zero_centered, cudaStream_t s) {
   if (rows == 0) return 0;
   if (H % 8 || ldx % 8) return -1;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   // the two-rows-per-iteration kernel needs up to ~160 registers: blocks stay at <= 256 threads
   const int nvec = H / 8;
   int threads = nvec <= 128 ? 128 : 256;
@@ -404,17 +424,47 @@ int mcb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   long long cap = (long long)device_sm_count() * (vpt <= 2 ? 2 : 1);
   long long pairs = (rows + 1) / 2;
   long long grid = pairs < cap ? pairs : cap;
+  if (!dw) partials = nullptr;
 #define LAUNCH(V)                                                                                                    \
   rmsnorm_bwd_kernel<V><<<(int)grid, threads, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,              \
                                                       (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,      \
-                                                      (__nv_bfloat16*)dx, dw, rows, H, ldx, eps, zero_centered)
+                                                      (__nv_bfloat16*)dx, dw, partials, rows, H, ldx, eps,            \
+                                                      zero_centered)
   if (vpt <= 1) LAUNCH(1);
   else if (vpt <= 2) LAUNCH(2);
   else if (vpt <= 4) LAUNCH(4);
   else if (vpt <= 8) LAUNCH(8);
   else return -2;
 #undef LAUNCH
+  if (partials) rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(partials, (int)grid, H, dw);
   return (int)cudaGetLastError();
+}
+
+// dw (fp32, [H]) is accumulated into (with atomics: the sum order varies from run to run); pass nullptr to skip.
+// dres (optional) is added to dx (residual branch).
+int mcb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                    float* dw, long long rows, int H, long long ldx, float eps, int zero_centered, void* stream_) {
+  return rmsnorm_bwd_launch(dy, x, w, rstd, dres, dx, dw, nullptr, rows, H, ldx, eps, zero_centered,
+                            reinterpret_cast<cudaStream_t>(stream_));
+}
+
+// Rows of fp32 scratch the deterministic variant needs for `rows` rows of width H (each H floats wide).
+int mcb_rmsnorm_bwd_partial_rows(long long rows, int H) {
+  const int nvec = H / 8;
+  const int threads = nvec <= 128 ? 128 : 256;
+  const int vpt = (nvec + threads - 1) / threads;
+  const long long cap = (long long)device_sm_count() * (vpt <= 2 ? 2 : 1);
+  const long long pairs = (rows + 1) / 2;
+  return (int)(pairs < cap ? pairs : cap);
+}
+
+// Same as mcb_rmsnorm_bwd, but the weight gradient is summed in a fixed order through `partials`
+// ([mcb_rmsnorm_bwd_partial_rows(rows, H), H] fp32 scratch), so it repeats bit for bit.
+int mcb_rmsnorm_bwd_det(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                        float* dw, float* partials, long long rows, int H, long long ldx, float eps, int zero_centered,
+                        void* stream_) {
+  return rmsnorm_bwd_launch(dy, x, w, rstd, dres, dx, dw, partials, rows, H, ldx, eps, zero_centered,
+                            reinterpret_cast<cudaStream_t>(stream_));
 }
 
 int mcb_glu_fwd(const void* in, const float* probs, void* out, long long rows, int F, long long ld_in, int kind,

@@ -130,15 +130,16 @@ qkv_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __res
                const __nv_bfloat16* __restrict__ wk, const float* __restrict__ cosb, const float* __restrict__ sinb,
                const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
                const __nv_bfloat16* __restrict__ dv, const __nv_bfloat16* __restrict__ dgate,
-               __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dwq, float* __restrict__ dwk, long long T,
+               __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dwq, float* __restrict__ dwk,
+               float* __restrict__ partials, long long T,
                QkvLayout L) {
   __shared__ float sx[WARPS][MAX_D];   // raw input head
   __shared__ float sg[WARPS][MAX_D];   // gradient after inverse rotation
-  __shared__ float sdw[2][MAX_D];
+  __shared__ float sdw[WARPS][2][MAX_D];   // one slot per warp: summed in warp order below, no atomics
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slots = L.ng * (L.qpg * (1 + L.gate) + 2);
   const int nq = L.ng * L.qpg, d = L.d, half = L.rot / 2;
-  for (int i = threadIdx.x; i < 2 * MAX_D; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
+  for (int i = threadIdx.x; i < WARPS * 2 * MAX_D; i += blockDim.x) (&sdw[0][0][0])[i] = 0.f;
   __syncthreads();
   // every lane always touches the same head positions, so the norm-weight gradients are summed in registers over all
   // the heads a warp visits and meet in shared memory once, after the loop
@@ -249,16 +250,26 @@ qkv_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __res
       for (int e = 0; e < 2; ++e) {
         const int idx = lane * 2 + j * 64 + e;
         if (idx < d) {
-          atomicAdd(&sdw[0][idx], dw_acc[0][2 * j + e]);
-          atomicAdd(&sdw[1][idx], dw_acc[1][2 * j + e]);
+          sdw[warp][0][idx] = dw_acc[0][2 * j + e];
+          sdw[warp][1][idx] = dw_acc[1][2 * j + e];
         }
       }
   }
   __syncthreads();
   if (L.norm) {
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      if (dwq) atomicAdd(dwq + i, sdw[0][i]);
-      if (dwk) atomicAdd(dwk + i, sdw[1][i]);
+      float a = 0.f, b = 0.f;
+      for (int w = 0; w < WARPS; ++w) {
+        a += sdw[w][0][i];
+        b += sdw[w][1][i];
+      }
+      if (partials) {                       // fixed-order sum over CTAs in qkv_dw_reduce_kernel
+        partials[((long long)blockIdx.x * 2) * d + i] = a;
+        partials[((long long)blockIdx.x * 2 + 1) * d + i] = b;
+      } else {
+        if (dwq) atomicAdd(dwq + i, a);
+        if (dwk) atomicAdd(dwk + i, b);
+      }
     }
   }
 }
@@ -321,13 +332,14 @@ qkv_bwd_fast_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* 
                     const float* __restrict__ sinb, const __nv_bfloat16* __restrict__ dq,
                     const __nv_bfloat16* __restrict__ dk, const __nv_bfloat16* __restrict__ dv,
                     const __nv_bfloat16* __restrict__ dgate, __nv_bfloat16* __restrict__ dqkv,
-                    float* __restrict__ dwq, float* __restrict__ dwk, long long T, QkvLayout L) {
+                    float* __restrict__ dwq, float* __restrict__ dwk, float* __restrict__ partials, long long T,
+                    QkvLayout L) {
   constexpr int D = 128;
-  __shared__ float sdw[2][D];
+  __shared__ float sdw[WARPS][2][D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slots = L.ng * (L.qpg * (1 + L.gate) + 2);
   const int nq = L.ng * L.qpg;
-  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
+  for (int i = threadIdx.x; i < WARPS * 2 * D; i += blockDim.x) (&sdw[0][0][0])[i] = 0.f;
   __syncthreads();
   const float wbase = L.zero_centered ? 1.f : 0.f;
   float2 wqa = make_float2(1.f, 1.f), wqb = wqa, wka = wqa, wkb = wqa;
@@ -381,17 +393,39 @@ qkv_bwd_fast_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* 
   if (L.norm) {
 #pragma unroll
     for (int a = 0; a < 2; ++a) {
-      atomicAdd(&sdw[a][2 * lane], acc[a][0]);
-      atomicAdd(&sdw[a][2 * lane + 1], acc[a][1]);
-      atomicAdd(&sdw[a][64 + 2 * lane], acc[a][2]);
-      atomicAdd(&sdw[a][65 + 2 * lane], acc[a][3]);
+      sdw[warp][a][2 * lane] = acc[a][0];
+      sdw[warp][a][2 * lane + 1] = acc[a][1];
+      sdw[warp][a][64 + 2 * lane] = acc[a][2];
+      sdw[warp][a][65 + 2 * lane] = acc[a][3];
     }
     __syncthreads();
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
-      if (dwq) atomicAdd(dwq + i, sdw[0][i]);
-      if (dwk) atomicAdd(dwk + i, sdw[1][i]);
+      float a = 0.f, b = 0.f;
+      for (int w = 0; w < WARPS; ++w) {
+        a += sdw[w][0][i];
+        b += sdw[w][1][i];
+      }
+      if (partials) {
+        partials[((long long)blockIdx.x * 2) * D + i] = a;
+        partials[((long long)blockIdx.x * 2 + 1) * D + i] = b;
+      } else {
+        if (dwq) atomicAdd(dwq + i, a);
+        if (dwk) atomicAdd(dwk + i, b);
+      }
     }
   }
+}
+
+// dwq[i] += sum over the CTAs' partial rows, in row order
+__global__ void qkv_dw_reduce_kernel(const float* __restrict__ partials, int nparts, int d, float* __restrict__ dwq,
+                                     float* __restrict__ dwk) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 2 * d) return;
+  const int which = i / d, c = i - which * d;
+  float acc = 0.f;
+  for (int b = 0; b < nparts; ++b) acc += partials[((long long)b * 2 + which) * d + c];
+  float* dst = which == 0 ? dwq : dwk;
+  if (dst) dst[c] += acc;
 }
 
 }  // namespace
@@ -419,27 +453,37 @@ int mcb_qkv_split_norm_rope_fwd(const void* qkv, const void* wq, const void* wk,
   return (int)cudaGetLastError();
 }
 
-// dwq / dwk: fp32 [d], accumulated into (caller zeroes or carries them across micro-batches)
+// CTAs the backward kernels launch for T tokens = rows of `partials` ([rows, 2, d] fp32) the caller provides
+int mcb_qkv_bwd_partial_rows(long long T) {
+  const long long cap = (long long)device_sm_count() * 8;
+  return (int)(T < cap ? T : cap);
+}
+
+// dwq / dwk: fp32 [d], accumulated into (caller zeroes or carries them across micro-batches).  With `partials` the
+// norm-weight gradients are summed in a fixed order (bit-reproducible); without, with atomics.
 int mcb_qkv_split_norm_rope_bwd(const void* qkv, const void* wq, const void* wk, const float* cosb, const float* sinb,
                                 const void* dq, const void* dk, const void* dv, const void* dgate, void* dqkv,
-                                float* dwq, float* dwk, long long T, int ng, int qpg, int d, int has_gate, int rot,
-                                int interleaved, int norm, int zero_centered, float eps, long long ld, void* stream_) {
+                                float* dwq, float* dwk, float* partials, long long T, int ng, int qpg, int d, int has_gate,
+                                int rot, int interleaved, int norm, int zero_centered, float eps, long long ld,
+                                void* stream_) {
   if (T == 0) return 0;
   if (d > MAX_D || d % 8 || rot > d || (rot & 1) || ld % 8) return -1;
   QkvLayout L{ng, qpg, d, has_gate, rot, interleaved, norm, zero_centered, eps, ld};
-  long long blocks = T;
-  long long cap = (long long)device_sm_count() * 8;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const int grid = mcb_qkv_bwd_partial_rows(T);
+  if (!norm) partials = nullptr;
   if (d == 128 && rot == 128 && !interleaved) {
-    qkv_bwd_fast_kernel<<<(int)(blocks < cap ? blocks : cap), WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+    qkv_bwd_fast_kernel<<<grid, WARPS * 32, 0, s>>>(
         (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cosb, sinb,
         (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv, (const __nv_bfloat16*)dgate,
-        (__nv_bfloat16*)dqkv, dwq, dwk, T, L);
-    return (int)cudaGetLastError();
+        (__nv_bfloat16*)dqkv, dwq, dwk, partials, T, L);
+  } else {
+    qkv_bwd_kernel<<<grid, WARPS * 32, 0, s>>>(
+        (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cosb, sinb,
+        (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv, (const __nv_bfloat16*)dgate,
+        (__nv_bfloat16*)dqkv, dwq, dwk, partials, T, L);
   }
-  qkv_bwd_kernel<<<(int)(blocks < cap ? blocks : cap), WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
-      (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, cosb, sinb,
-      (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv, (const __nv_bfloat16*)dgate,
-      (__nv_bfloat16*)dqkv, dwq, dwk, T, L);
+  if (partials) qkv_dw_reduce_kernel<<<(2 * d + 255) / 256, 256, 0, s>>>(partials, grid, d, dwq, dwk);
   return (int)cudaGetLastError();
 }
 

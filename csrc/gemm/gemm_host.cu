@@ -122,7 +122,9 @@ int mcb_gemm_bf16(const void* A, long long a_inner, long long a_outer, long long
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.c_group_stride = c_group_stride;
-  p.bias = bias; p.c_fp32 = c_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  p.bias = bias; p.c_fp32 = c_fp32; p.alpha = alpha;
+  // grouped-K (expert weight gradients): many output tiles per unit of math, where reductions would queue at the L2
+  p.accumulate = accumulate ? (mode == GEMM_GROUPED_K && c_fp32 ? 2 : 1) : 0;
   p.mode = mode; p.num_groups = num_groups; p.offsets = offsets; p.b_group_rows = b_group_rows;
   p.epilogue = EPI_NONE;
   p.status = status;

@@ -38,7 +38,7 @@ struct GemmParams {
   long long c_group_stride;  // grouped-K: elements between consecutive group outputs
   const void* bias;     // optional, bf16 [N] (grouped-M: [G,N])
   int c_fp32;           // 0: bf16 output, 1: fp32 output
-  int accumulate;       // C += ...
+  int accumulate;       // C += ...  (1: as reductions at the L2; 2: read-add-write with prefetched old values)
   float alpha;
   int mode;
   int num_groups;
@@ -63,6 +63,50 @@ struct GemmSmem {
   static constexpr int BAR_BYTES = 1024;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
 };
+
+// C[row, n0 .. n0 + BN) += alpha * accumulator row, fp32, for tiles whose valid columns are a multiple of 32.  The old
+// values of two 32-column chunks ahead are already on their way while the current chunk is added and stored, which
+// keeps about 32 KiB of reads in flight per SM: short-K problems (expert weight gradients) have many output tiles per
+// unit of math, and an epilogue that waits for each chunk's read, or 16-byte reductions that queue at the L2's
+// atomic units, would bound them.
+template <int BN>
+__device__ __forceinline__ void epilogue_accumulate_fp32(uint32_t tmem_row, float* crow, int chunks, bool row_ok,
+                                                         float alpha) {
+  float4 nxt[2][8];
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+    if (row_ok && a < chunks) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) nxt[a][j] = *reinterpret_cast<const float4*>(crow + a * 32 + j * 4);
+    }
+#pragma unroll 1
+  for (int ch = 0; ch < chunks; ch += 2) {
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      if (ch + a >= chunks) break;
+      float4 cur[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) cur[j] = nxt[a][j];
+      if (row_ok && ch + a + 2 < chunks) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) nxt[a][j] = *reinterpret_cast<const float4*>(crow + (ch + a + 2) * 32 + j * 4);
+      }
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_row + (ch + a) * 32, r);
+      tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          cur[j].x += __uint_as_float(r[4 * j]) * alpha;
+          cur[j].y += __uint_as_float(r[4 * j + 1]) * alpha;
+          cur[j].z += __uint_as_float(r[4 * j + 2]) * alpha;
+          cur[j].w += __uint_as_float(r[4 * j + 3]) * alpha;
+          *reinterpret_cast<float4*>(crow + (ch + a) * 32 + j * 4) = cur[j];
+        }
+      }
+    }
+  }
+}
 
 struct TileCoord {
   int m0, n0;        // output tile origin (row within C / group output)
@@ -359,6 +403,16 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         ++lt;
         continue;
       }
+      const int cols_valid = min(BN, p.N - c.n0);
+      if (p.accumulate == 2 && p.c_fp32 && vec_ok && has_acc && !bias && cols_valid % 32 == 0) {
+        epilogue_accumulate_fp32<BN>(tmem_base + (uint32_t(q * 32) << 16) + acc * BN,
+                                     reinterpret_cast<float*>(p.C) + cbase + c.n0, cols_valid / 32, row_ok, p.alpha);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+        ++lt;
+        continue;
+      }
 #pragma unroll 1
       for (int cc = 0; cc < BN; cc += 32) {
         if (c.n0 + cc >= p.N) break;  // whole chunk out of range (uniform across the warp)
@@ -383,14 +437,15 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           if (p.c_fp32) {
             float* dst = reinterpret_cast<float*>(p.C) + cbase + col0;
             if (vec_ok && col0 + 32 <= p.N) {
+              if (p.accumulate) {
+                // C += tile as vector reductions performed at the L2: nothing is read back, so the epilogue does not
+                // wait on memory latency (every output element belongs to exactly one tile: no ordering to respect)
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                if (p.accumulate) {
-                  float4 old = *reinterpret_cast<float4*>(dst + j);
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(dst + j) = o;
+                for (int j = 0; j < 32; j += 4) red_add_v4_f32(dst + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
               }
             } else {
               for (int j = 0; j < 32; ++j)

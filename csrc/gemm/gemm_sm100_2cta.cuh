@@ -211,14 +211,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (p.c_fp32) {
             float* dst = reinterpret_cast<float*>(p.C) + cbase + col0;
             if (vec_ok && col0 + 32 <= p.N) {
+              if (p.accumulate) {   // vector reductions at the L2: no read-back latency in the epilogue
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                if (p.accumulate) {
-                  const float4 old = *reinterpret_cast<float4*>(dst + j);
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(dst + j) = o;
+                for (int j = 0; j < 32; j += 4) red_add_v4_f32(dst + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
               }
             } else {
               for (int j = 0; j < 32; ++j)

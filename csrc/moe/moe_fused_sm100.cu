@@ -2,18 +2,19 @@
 //
 //   source side   mcb_moe_sort: the routing of a rank's tokens, sorted by expert (stable), so that the entries that go
 //                 to one expert are one contiguous, deterministically ordered run of the published `order` table
-//   owner side    mcb_moe_pull_gemm: a few "pull CTAs" gather the routed rows from the sources' published activations
-//                 over NVLink (one bulk copy per row, through a shared-memory ring) into the expert-sorted, 128-row
-//                 padded GEMM input and publish a flag per 128-row block; the other CTAs run the grouped expert GEMM
-//                 C[rows of expert e] = X[rows of e] . W_e^T on tcgen05 and consume the blocks in arrival order, so
-//                 the exchange hides behind the math block by block.
+//   owner side    mcb_moe_pull_gemm: every CTA of a persistent grid carries the GEMM roles plus four communication
+//                 warps.  The communication warps of all CTAs gather the routed rows from the sources' published
+//                 activations over NVLink (vector loads, eight in flight per lane: one SM alone keeps too few bytes
+//                 in flight to feed the GEMM) into the expert-sorted, 128-row padded GEMM input and publish a flag
+//                 per 128-row block; the GEMM roles run the grouped expert GEMM C[rows of expert e] = X[rows of e] .
+//                 W_e^T on tcgen05 and consume the blocks in arrival order, so the exchange hides behind the math.
 //
 // Rows are assigned without atomics: expert segment -> source rank -> position in that source's sorted run, which
 // makes the row order (and therefore every fp32 weight-gradient sum over rows) reproducible.  The same kernel replays
 // a recorded assignment (`row_src`) for the backward pass, where the rows are output gradients and the GEMM is the
 // data gradient of the second expert layer.
 //
-// No TMA multicast; remote memory is read by plain bulk copies and 4-byte loads and written by 4-byte stores.  Every
+// No TMA multicast; remote memory is read by plain vector loads and written by 4-byte stores.  Every
 // wait is bounded and reports through the status word.
 #include "../common/host_utils.cuh"
 #include "../gemm/gemm_pipe.cuh"
@@ -25,7 +26,9 @@ namespace {
 constexpr int MAX_WORLD = 8;
 constexpr int PADM = 128;
 constexpr int MAX_EL = 64;            // local experts per rank the fused kernel supports
-constexpr int PULL_STORES_IN_FLIGHT = 4;
+constexpr int PULL_WARPS = 4;         // communication warps per CTA (warps 6..9)
+constexpr int PULL_LOADS = 8;         // 16-byte loads a lane keeps in flight
+constexpr int MOE_THREADS = GEMM_THREADS + PULL_WARPS * 32;
 
 // ---------------------------------------------------------------------------------------------------------------
 // source side: stable counting sort of the routing entries by expert
@@ -75,7 +78,6 @@ struct MoeFusedParams {
   int H;                  // width of the pulled rows = contraction size of the GEMM
   int N;                  // output width of the GEMM (per expert)
   int capacity;           // rows of xp / C (a multiple of 128)
-  int pull_ctas;
   int mode;               // 0: assign rows from the sources' sorted tables; 1: replay the assignment in row_src
   const void* x_ptrs[MAX_WORLD];      // published rows [T, H] bf16
   const int* order_ptrs[MAX_WORLD];   // mode 0: entries sorted by expert [T * k]
@@ -86,7 +88,8 @@ struct MoeFusedParams {
   int* row_src;                       // [capacity] source entry of every row or -1 (written in mode 0)
   float* row_probs;                   // [capacity] routing probability of every row (mode 0, may be null)
   __nv_bfloat16* xp;                  // [capacity, H] gathered rows
-  uint32_t* blk_flags;                // [capacity / 128] "block landed" flags in local memory (epoch stamped)
+  uint32_t* blk_flags;                // [2 * capacity / 128]: "block landed" flags (epoch stamped), then the quarter
+                                      // counters of every block (zero between calls)
   uint32_t epoch;
   void* C;                            // [capacity, N] bf16
   long long ldc;
@@ -101,7 +104,7 @@ struct Layout {
 };
 
 template <int BN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(MOE_THREADS, 1)
 moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const MoeFusedParams p) {
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -145,142 +148,6 @@ moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int nblocks = valid_rows / PADM;
   const int tiles_n = (p.N + BN - 1) / BN;
 
-  if ((int)blockIdx.x < p.pull_ctas) {
-    // ================================================================= pull CTA
-    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t row_bytes = (uint32_t)p.H * 2u;
-    const int ring_bytes = GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES - 8192;   // the rest: barriers + row tables
-    int rstages = ring_bytes / (int)row_bytes;
-    if (rstages > 32) rstages = 32;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + ring_bytes);
-    uint64_t* full = bars;
-    uint64_t* empty = bars + 32;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 64);
-    const uint8_t** meta = reinterpret_cast<const uint8_t**>(bars + 72);   // [2][128] source address of every row
-    if (threadIdx.x == 0) {
-      *abort_flag = 0;
-      for (int s = 0; s < rstages; ++s) {
-        mbar_init(smem_u32(&full[s]), 1);
-        mbar_init(smem_u32(&empty[s]), 1);
-      }
-      fence_barrier_init();
-      fence_proxy_async_smem();
-    }
-    __syncthreads();
-    const long long per_src = (long long)p.T * p.k;
-
-    // source row of every row of block `b` -> meta[buf]; the side tables of the block are written on the way
-    auto describe = [&](int b, int buf) {
-      const int t = threadIdx.x - 64;               // warps 2..5: one thread per row
-      if (t < 0 || t >= PADM) return;
-      const int R = b * PADM + t;
-      const uint8_t* src = nullptr;
-      if (p.mode == 0) {
-        int el = 0;
-        while (el + 1 < El && L.seg_off[el + 1] <= R) ++el;
-        const int i = R - L.seg_off[el];
-        int s = -1;
-        if (i < L.src_off[p.world * MAX_EL + el]) {
-          s = 0;
-          while (s + 1 < p.world && L.src_off[(s + 1) * MAX_EL + el] <= i) ++s;
-        }
-        int id = -1;
-        float prob = 0.f;
-        if (s >= 0) {
-          const int j = i - L.src_off[s * MAX_EL + el];
-          const int ent = p.order_ptrs[s][L.eoff_base[s * MAX_EL + el] + j];
-          if (ent >= 0 && ent < per_src) {          // a torn table would otherwise turn into a wild address
-            src = reinterpret_cast<const uint8_t*>(p.x_ptrs[s]) + (long long)(ent / p.k) * row_bytes;
-            id = s * (int)per_src + ent;
-            prob = p.prob_ptrs[s] ? p.prob_ptrs[s][ent] : 1.f;
-            p.sent_row_ptrs[s][ent] = R;
-          }
-        }
-        p.row_src[R] = id;
-        if (p.row_probs) p.row_probs[R] = prob;
-      } else {
-        const int id = p.row_src[R];
-        if (id >= 0) {
-          const int s = id / (int)per_src;
-          const int ent = id - s * (int)per_src;
-          if (s < p.world) src = reinterpret_cast<const uint8_t*>(p.x_ptrs[s]) + (long long)(ent / p.k) * row_bytes;
-        }
-      }
-      meta[buf * PADM + t] = src;
-    };
-
-    int nmine = 0;
-    for (int b = blockIdx.x; b < nblocks; b += p.pull_ctas) ++nmine;
-    if (nmine > 0) describe(blockIdx.x, 0);
-    __syncthreads();
-    uint32_t it_load = 0, it_store = 0;
-    bool ok = true;
-    for (int i = 0; i < nmine; ++i) {
-      const int b = blockIdx.x + i * p.pull_ctas;
-      const int buf = i & 1;
-      if (warp == 0) {
-        if (lane == 0 && ok) {
-          for (int r = 0; r < PADM; ++r) {
-            const uint8_t* src = meta[buf * PADM + r];
-            if (!src) continue;
-            const uint32_t st = it_load % rstages, ph = (it_load / rstages) & 1;
-            if (!mbar_wait(smem_u32(&empty[st]), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
-            mbar_expect_tx(smem_u32(&full[st]), row_bytes);
-            bulk_load_1d(smem_u32(ring + (size_t)st * row_bytes), src, row_bytes, smem_u32(&full[st]));
-            ++it_load;
-          }
-        }
-      } else if (warp == 1) {
-        if (lane == 0 && ok) {
-          const uint32_t first = it_store;
-          for (int r = 0; r < PADM; ++r) {
-            if (!meta[buf * PADM + r]) continue;
-            const uint32_t st = it_store % rstages, ph = (it_store / rstages) & 1;
-            if (!mbar_wait(smem_u32(&full[st]), ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
-            bulk_store_1d(reinterpret_cast<uint8_t*>(p.xp) + (long long)(b * PADM + r) * row_bytes,
-                          smem_u32(ring + (size_t)st * row_bytes), row_bytes);
-            tma_store_commit();
-            tma_store_wait_read<PULL_STORES_IN_FLIGHT>();   // older stores have read their stage: hand it back
-            if (it_store >= first + PULL_STORES_IN_FLIGHT)
-              mbar_arrive(smem_u32(&empty[(it_store - PULL_STORES_IN_FLIGHT) % rstages]));
-            ++it_store;
-          }
-          tma_store_wait<0>();                               // the whole block is in global memory
-          const uint32_t from = it_store >= first + PULL_STORES_IN_FLIGHT ? it_store - PULL_STORES_IN_FLIGHT : first;
-          for (uint32_t j = from; j < it_store; ++j) mbar_arrive(smem_u32(&empty[j % rstages]));
-        }
-      } else {
-        // warps 2..5: zero the padding rows of this block, then describe the next block
-        const int t = threadIdx.x - 64;
-        if (!meta[buf * PADM + t]) {
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.xp) + (long long)(b * PADM + t) * row_bytes);
-          for (uint32_t c = 0; c < row_bytes / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
-        }
-        if (i + 1 < nmine) describe(b + p.pull_ctas, buf ^ 1);
-      }
-      __syncthreads();
-      if (*abort_flag) break;
-      if (threadIdx.x == 0) {
-        fence_proxy_async_all();
-        __threadfence();
-        st_release_gpu(p.blk_flags + b, p.epoch);
-      }
-    }
-    if (warp == 0 && lane == 0) {
-      // drain: loads that were issued but never stored (give-up paths) must land before the CTA exits
-      const uint32_t lo = it_load > (uint32_t)rstages ? it_load - rstages : 0;
-      for (uint32_t j = lo; j < it_load; ++j) {
-        const uint32_t st = j % rstages, ph = (j / rstages) & 1;
-        const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(smem_u32(&full[st]), ph)) {
-          if (globaltimer_ns() - t0 > 200000000ull) break;
-        }
-      }
-    }
-    if (warp == 1 && lane == 0) tma_store_wait<0>();
-    return;
-  }
-
   // ===================================================================== GEMM CTA
   Pipe<BN> P(smem_raw);
   if (threadIdx.x == 0) {
@@ -296,7 +163,7 @@ moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *P.tmem_slot;
-  const int g0 = blockIdx.x - p.pull_ctas, gs = gridDim.x - p.pull_ctas;
+  const int g0 = blockIdx.x, gs = gridDim.x;
   const int total = nblocks * tiles_n;      // row-block major: the tiles of a block wait for the same flag
   auto expert_of = [&](int mb) {
     int el = 0;
@@ -304,7 +171,88 @@ moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     return el;
   };
 
-  if (warp == 0) {
+  if (warp >= GEMM_THREADS / 32) {
+    // =================================================================== communication warps: gather the rows.
+    // A unit is a quarter (32 rows) of a 128-row block; lane l works out where row l of the unit comes from, then the
+    // warp copies the rows one after the other with every lane keeping up to eight 16-byte loads in flight.  The
+    // warp that completes a block's fourth quarter publishes the block.
+    const uint32_t row_bytes = (uint32_t)p.H * 2u;
+    const int n16 = (int)(row_bytes / 16);
+    const long long per_src = (long long)p.T * p.k;
+    uint32_t* blk_cnt = p.blk_flags + p.capacity / PADM;
+    const int cw = (int)blockIdx.x * PULL_WARPS + (warp - GEMM_THREADS / 32);
+    const int ncw = (int)gridDim.x * PULL_WARPS;
+    for (int u = cw; u < nblocks * 4; u += ncw) {
+      const int b = u >> 2;
+      const int R = u * 32 + lane;
+      const uint8_t* src = nullptr;
+      if (p.mode == 0) {
+        int el = 0;
+        while (el + 1 < El && L.seg_off[el + 1] <= R) ++el;
+        const int i = R - L.seg_off[el];
+        int sr = -1;
+        if (i < L.src_off[p.world * MAX_EL + el]) {
+          sr = 0;
+          while (sr + 1 < p.world && L.src_off[(sr + 1) * MAX_EL + el] <= i) ++sr;
+        }
+        int id = -1;
+        float prob = 0.f;
+        if (sr >= 0) {
+          const int j = i - L.src_off[sr * MAX_EL + el];
+          const int ent = p.order_ptrs[sr][L.eoff_base[sr * MAX_EL + el] + j];
+          if (ent >= 0 && ent < per_src) {          // a torn table would otherwise turn into a wild address
+            src = reinterpret_cast<const uint8_t*>(p.x_ptrs[sr]) + (long long)(ent / p.k) * row_bytes;
+            id = sr * (int)per_src + ent;
+            prob = p.prob_ptrs[sr] ? p.prob_ptrs[sr][ent] : 1.f;
+            p.sent_row_ptrs[sr][ent] = R;
+          }
+        }
+        p.row_src[R] = id;
+        if (p.row_probs) p.row_probs[R] = prob;
+      } else {
+        const int id = p.row_src[R];
+        if (id >= 0) {
+          const int sr = id / (int)per_src;
+          const int ent = id - sr * (int)per_src;
+          if (sr < p.world) src = reinterpret_cast<const uint8_t*>(p.x_ptrs[sr]) + (long long)(ent / p.k) * row_bytes;
+        }
+      }
+      uint4* dst_row = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.xp) + (long long)(u * 32) * row_bytes);
+#pragma unroll 1
+      for (int r = 0; r < 32; ++r, dst_row += n16) {
+        const uint4* s16 = reinterpret_cast<const uint4*>(__shfl_sync(0xffffffffu, reinterpret_cast<uintptr_t>(src), r));
+        if (s16 == nullptr) {
+          for (int c = lane; c < n16; c += 32) dst_row[c] = make_uint4(0, 0, 0, 0);   // padding row
+          continue;
+        }
+        for (int base = 0; base < n16; base += 32 * PULL_LOADS) {
+          uint4 v[PULL_LOADS];
+#pragma unroll
+          for (int j = 0; j < PULL_LOADS; ++j) {
+            const int c = base + j * 32 + lane;
+            if (c < n16) v[j] = s16[c];                 // every load is issued before the first store
+          }
+#pragma unroll
+          for (int j = 0; j < PULL_LOADS; ++j) {
+            const int c = base + j * 32 + lane;
+            if (c < n16) dst_row[c] = v[j];
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        // the fence orders this warp's stores before its count; the fence after the fourth count orders the other
+        // warps' (counted, hence fenced) stores before the flag
+        __threadfence();
+        const uint32_t done = atomicAdd(blk_cnt + b, 1u) + 1u;
+        if (done == 4u) {
+          __threadfence();
+          blk_cnt[b] = 0;
+          st_release_gpu(p.blk_flags + b, p.epoch);
+        }
+      }
+    }
+  } else if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;
       int seen = -1;
@@ -394,34 +342,20 @@ int mcb_moe_sort(const int* idx, const int* counts, int n_entries, int E, int* e
 
 // Pointer arrays hold `world` device pointers (index = rank in the expert-parallel group).  B is the stacked expert
 // weight: K-major `[El * N, H]` (b_mn = 0, forward of the first expert layer) or MN-major `[El * H, N]` (b_mn = 1,
-// data gradient of the second expert layer: rows are contraction indices).  `blk_flags` holds capacity / 128 words
-// that carry the epoch of the call that last filled each block (monotonically increasing, never cleared).
+// data gradient of the second expert layer: rows are contraction indices).  `blk_flags` holds 2 * capacity / 128
+// words: first the epoch of the call that last filled each block (monotonically increasing, never cleared), then the
+// per-block counters of landed quarters (zero when allocated, zero again after every call).
 int mcb_moe_pull_gemm(const void* const* x_ptrs, const int* const* order_ptrs, const int* const* eoff_ptrs,
                       const float* const* prob_ptrs, int* const* sent_row_ptrs, int world, int rank, int T, int k, int E,
                       int El, int H, int N, int capacity, int mode, int* seg_off, int* row_src, float* row_probs, void* xp,
                       unsigned* blk_flags, unsigned epoch, const void* B, long long b_inner, long long b_outer,
-                      long long ldb, int b_mn, int b_group_rows, void* C, long long ldc, int pull_ctas, int* status,
+                      long long ldb, int b_mn, int b_group_rows, void* C, long long ldc, int* status,
                       void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (world < 1 || world > MAX_WORLD || El < 1 || El > MAX_EL || H % 8 || N % 8 || capacity % PADM || ldc % 8) return -2;
-  if (H * 2 > 32768) return -3;                      // a row has to fit a stage of the pull ring comfortably
   if ((long long)world * T * k >= (1ll << 31)) return -3;
   constexpr int BN = 256;
   const int sms = device_sm_count();
-  if (pull_ctas <= 0) {
-    // balance the two roles: a pull CTA sustains ~25 GB/s of row gathers, a GEMM CTA ~9.5 TFLOP/s
-    const double rows = (double)T * k;               // balanced load
-    const double bytes = rows * H * 2.0, flops = 2.0 * rows * (double)N * H;
-    double best = 1e30;
-    int best_c = 16;
-    for (int c = 8; c <= 56; c += 4) {
-      const double t_pull = bytes / (25e9 * c), t_gemm = flops / (9.5e12 * (sms - c));
-      const double t = t_pull > t_gemm ? t_pull : t_gemm;
-      if (t < best) { best = t; best_c = c; }
-    }
-    pull_ctas = best_c;
-  }
-  if (pull_ctas >= sms) return -4;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d_bf16(&ta, xp, H, capacity, H, GEMM_BK, GEMM_BM);
   if (rc) return rc;
@@ -430,7 +364,7 @@ int mcb_moe_pull_gemm(const void* const* x_ptrs, const int* const* order_ptrs, c
   if (rc) return rc;
   MoeFusedParams p{};
   p.world = world; p.rank = rank; p.T = T; p.k = k; p.E = E; p.El = El; p.H = H; p.N = N; p.capacity = capacity;
-  p.pull_ctas = pull_ctas; p.mode = mode;
+  p.mode = mode;
   for (int i = 0; i < world; ++i) {
     p.x_ptrs[i] = x_ptrs[i];
     p.order_ptrs[i] = order_ptrs ? order_ptrs[i] : nullptr;
@@ -451,14 +385,14 @@ int mcb_moe_pull_gemm(const void* const* x_ptrs, const int* const* order_ptrs, c
       if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
       cfg[1] = true;
     }
-    kern<<<sms, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+    kern<<<sms, MOE_THREADS, smem, stream>>>(ta, tb, p);
   } else {
     auto kern = moe_pull_gemm_kernel<BN, false>;
     if (!cfg[0]) {
       if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
       cfg[0] = true;
     }
-    kern<<<sms, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+    kern<<<sms, MOE_THREADS, smem, stream>>>(ta, tb, p);
   }
   return (int)cudaGetLastError();
 }

@@ -69,7 +69,13 @@ __global__ void adam_kernel(const float* __restrict__ grad, float* __restrict__ 
   }
 }
 
-__global__ void sqnorm_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
+// Sum of squares.  With `scratch` every CTA writes its partial sum there and the last CTA to finish (a ticket counter
+// at scratch[SQ_MAX_CTAS]) adds the partials in CTA order, so the result repeats bit for bit; without, CTAs add to
+// `out` with atomics.
+constexpr int SQ_MAX_CTAS = 1024;
+
+__global__ void sqnorm_kernel(const float* __restrict__ x, long long n, float* __restrict__ out,
+                              float* __restrict__ scratch) {
   float acc = 0.f;
   const long long stride = (long long)gridDim.x * blockDim.x * 4;
   for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
@@ -90,7 +96,22 @@ __global__ void sqnorm_kernel(const float* __restrict__ x, long long n, float* _
     acc = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) atomicAdd(out, acc);
+    if (lane == 0) {
+      if (!scratch) {
+        atomicAdd(out, acc);
+      } else {
+        scratch[blockIdx.x] = acc;
+        __threadfence();
+        unsigned* ticket = reinterpret_cast<unsigned*>(scratch + SQ_MAX_CTAS);
+        if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+          __threadfence();
+          float total = 0.f;
+          for (unsigned b = 0; b < gridDim.x; ++b) total += *reinterpret_cast<volatile float*>(scratch + b);
+          *out += total;
+          *ticket = 0;
+        }
+      }
+    }
   }
 }
 
@@ -121,14 +142,16 @@ int mcb_adam_step(const float* grad, float* main, float* m, float* v, void* para
   return (int)cudaGetLastError();
 }
 
-// out (1 float) is accumulated into: zero it before the first call of a step
-int mcb_sqnorm_accum(const float* x, long long n, float* out, void* stream_) {
+// out (1 float) is accumulated into: zero it before the first call of a step.  `scratch` (optional, 1025 floats, zero
+// when allocated, owned by one stream of calls) makes the sum order fixed.
+int mcb_sqnorm_accum(const float* x, long long n, float* out, float* scratch, void* stream_) {
   if (n == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   long long blocks = (n / 4 + 255) / 256;
   long long cap = (long long)device_sm_count() * 4;
+  if (cap > SQ_MAX_CTAS) cap = SQ_MAX_CTAS;
   int grid = (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
-  sqnorm_kernel<<<grid, 256, 0, s>>>(x, n, out);
+  sqnorm_kernel<<<grid, 256, 0, s>>>(x, n, out, scratch);
   return (int)cudaGetLastError();
 }
 

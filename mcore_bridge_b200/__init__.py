@@ -3,10 +3,7 @@
 Names are resolved lazily so ``import mcore_bridge_b200`` stays cheap (parity: reference
 ``src/mcore_bridge/__init__.py:18-33``).
 """
-import sys
 from typing import TYPE_CHECKING
-
-from .utils.import_utils import _LazyModule
 
 if TYPE_CHECKING:
     from .bridge import GPTBridge
@@ -25,5 +22,5 @@ else:
         'parallel': ['initialize_model_parallel', 'destroy_model_parallel'],
         'version': ['__release_datetime__', '__version__'],
     }
-    sys.modules[__name__] = _LazyModule(__name__, globals()['__file__'], _import_structure, module_spec=__spec__,
-                                        extra_objects={})
+    from .utils.import_utils import lazy_exports
+    __getattr__, __dir__, __all__ = lazy_exports(__name__, _import_structure)

@@ -52,6 +52,45 @@ def _track(name: str, value: torch.Tensor):
     _AUX_TRACKER[name] = (s + value.detach().float(), c + 1)
 
 
+def _gate_on_engine(x: torch.Tensor, w: torch.Tensor) -> bool:
+    from ..ops import _lib
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[0] % 8 == 0
+            and w.shape[1] % 8 == 0 and _lib.available())
+
+
+class _RouterGateFn(torch.autograd.Function):
+    """Router logits ``x @ w^T`` on the tensor-core GEMM.  bf16 operands with fp32 accumulation give the products and
+    sums of the fp32 GEMM the router's ``moe_router_dtype='fp32'`` asks for (a bf16 value is exact in fp32).  The
+    fp32 logit gradient enters the backward GEMMs as two bf16 terms (value rounded to bf16 + the rounding error), which
+    keeps 16 mantissa bits; both terms ride in one GEMM by doubling the contraction dimension."""
+
+    @staticmethod
+    def forward(ctx, x, w, out_dtype):
+        from ..ops import gemm
+        ctx.save_for_backward(x, w)
+        return gemm.mm_nt(x, w, out_dtype=out_dtype)
+
+    @staticmethod
+    def backward(ctx, dl):
+        from ..ops import gemm
+        x, w = ctx.saved_tensors
+        E = w.shape[0]
+        if dl.dtype == torch.float32:
+            hi = dl.to(torch.bfloat16)
+            d2 = torch.cat([hi, (dl - hi.float()).to(torch.bfloat16)], dim=1)      # [T, 2E]
+            w2 = torch.cat([w, w], dim=0)                                          # [2E, H]
+        else:
+            d2, w2 = dl.contiguous(), w
+        dx = gemm.mm_nn(d2, w2) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = gemm.mm_tn(d2, x, out_dtype=torch.float32)                         # [2E or E, H]
+            if dw.shape[0] != E:
+                dw = dw[:E] + dw[E:]
+            dw = dw.to(w.dtype)
+        return dx, dw, None
+
+
 class TopKRouter(nn.Module):
     """Gate ``[E, H]`` in fp32 math + top-k selection + load-balancing losses + expert-bias bookkeeping.
 
@@ -89,6 +128,9 @@ class TopKRouter(nn.Module):
 
     def gating(self, x: torch.Tensor) -> torch.Tensor:
         dt = {None: x.dtype, 'fp32': torch.float32, 'fp64': torch.float64}[self.config.moe_router_dtype]
+        if dt != torch.float64 and x.dim() == 2 and _gate_on_engine(x, self.weight):
+            logits = _RouterGateFn.apply(x, self.weight, dt)
+            return logits if self.bias is None else logits + self.bias.to(dt)
         return torch.nn.functional.linear(x.to(dt), self.weight.to(dt), None if self.bias is None else self.bias.to(dt))
 
     def _apply_expert_bias(self, indices: torch.Tensor, padding_mask: Optional[torch.Tensor]):

@@ -96,7 +96,7 @@ class ExchangeBuffers:
         self._ptr_cache: Dict[Tuple[str, int], ctypes.Array] = {}
         # "block landed" flags of the fused pull + GEMM kernel (local memory; they carry the epoch of the launch that
         # filled the block, so they are never cleared)
-        self.blk_flags = torch.zeros(max(1, capacity // PAD), dtype=torch.int32, device=device)
+        self.blk_flags = torch.zeros(2 * max(1, capacity // PAD), dtype=torch.int32, device=device)   # flags, then counters
         self.pull_epoch = 0
 
     def next_epoch(self) -> int:
@@ -394,17 +394,16 @@ def _pull_gemm(b: ExchangeBuffers, par: int, mode: int, st: 'DispatchState', El:
         _int(T), _int(k), _int(E), _int(El), _int(H), _int(N), _int(b.cap), _int(mode), _lib.ptr(st.seg_off),
         _lib.ptr(st.row_src), _lib.ptr(row_probs), _lib.ptr(xp), _lib.ptr(b.blk_flags), _u(b.next_pull_epoch()),
         _lib.ptr(w2), ctypes.c_longlong(b_inner), ctypes.c_longlong(b_outer), ctypes.c_longlong(w2.stride(0)),
-        _int(int(b_mn)), _int(group_rows), _lib.ptr(out), ctypes.c_longlong(out.stride(0)), _int(PULL_CTAS),
+        _int(int(b_mn)), _int(group_rows), _lib.ptr(out), ctypes.c_longlong(out.stride(0)),
         _lib.ptr(_lib.status_word(xp.device)), _lib.stream_ptr())
     _lib.check_rc(rc, 'mcb_moe_pull_gemm')
 
 
-PULL_CTAS = int(os.environ.get('MCB200_MOE_PULL_CTAS', '0'))   # 0: the launcher balances pull vs GEMM CTAs
 
 
 def pull_gemm_supported(experts, config, El: int, H: int) -> bool:
     """The fused dispatch + expert GEMM applies to plain stacked bf16 expert weights without biases, probabilities
-    applied after the first layer, at most 64 local experts and rows of at most 32 KiB."""
+    applied after the first layer and at most 64 local experts."""
     from .moe import GroupedLinear, GroupedMLP
     if os.environ.get('MCB200_MOE_FUSED_GEMM', '1') == '0':
         return False
@@ -414,7 +413,7 @@ def pull_gemm_supported(experts, config, El: int, H: int) -> bool:
         if type(lin) is not GroupedLinear or lin.bias is not None or lin.weight.dtype != torch.bfloat16:
             return False
     f = experts.linear_fc2.weight.shape[2]
-    return El <= 64 and H * 2 <= 32768 and H % 8 == 0 and f % 64 == 0 and experts.linear_fc1.weight.shape[1] % 8 == 0
+    return El <= 64 and H % 8 == 0 and f % 64 == 0 and experts.linear_fc1.weight.shape[1] % 8 == 0
 
 
 class _DispatchFc1Fn(torch.autograd.Function):

@@ -70,10 +70,12 @@ class _NormLinearFn(torch.autograd.Function):
         dxn = gemm.mm_nn(dy2, weight)
         dx = torch.empty((rows, H), dtype=x2.dtype, device=x2.device)
         dlw = torch.zeros(H, dtype=torch.float32, device=x2.device)
-        rc = _lib.lib().mcb_rmsnorm_bwd(_lib.ptr(dxn), _lib.ptr(x2), _lib.ptr(ln_w), _lib.ptr(rstd), None, _lib.ptr(dx),
-                                        _lib.ptr(dlw), _ll(rows), _int(H), _ll(x2.stride(0)), _f(ctx.eps),
-                                        _int(int(ctx.zc)), _lib.stream_ptr())
-        _lib.check_rc(rc, 'mcb_rmsnorm_bwd')
+        part = torch.empty((_lib.lib().mcb_rmsnorm_bwd_partial_rows(_ll(rows), _int(H)), H), dtype=torch.float32,
+                           device=x2.device)
+        rc = _lib.lib().mcb_rmsnorm_bwd_det(_lib.ptr(dxn), _lib.ptr(x2), _lib.ptr(ln_w), _lib.ptr(rstd), None,
+                                            _lib.ptr(dx), _lib.ptr(dlw), _lib.ptr(part), _ll(rows), _int(H),
+                                            _ll(x2.stride(0)), _f(ctx.eps), _int(int(ctx.zc)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_rmsnorm_bwd_det')
         return dx.view(ctx.shape), dlw.to(ln_w.dtype), dw, None, None
 
 

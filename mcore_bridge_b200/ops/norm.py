@@ -48,11 +48,16 @@ class _RMSNormCuda(torch.autograd.Function):
         rows = x2.shape[0]
         dy2 = dy.reshape(rows, H).contiguous()
         dx = torch.empty((rows, H), dtype=x2.dtype, device=x2.device)
-        dw = torch.zeros(H, dtype=torch.float32, device=x2.device) if ctx.needs_input_grad[1] else None
-        rc = _lib.lib().mcb_rmsnorm_bwd(_lib.ptr(dy2), _lib.ptr(x2), _lib.ptr(w), _lib.ptr(rstd), None, _lib.ptr(dx),
-                                        _lib.ptr(dw), _ll(rows), _int(H), _ll(x2.stride(0)), _f(ctx.eps),
-                                        _int(int(ctx.zc)), _lib.stream_ptr())
-        _lib.check_rc(rc, 'mcb_rmsnorm_bwd')
+        dw = part = None
+        if ctx.needs_input_grad[1]:
+            # per-CTA partial rows summed in a fixed order: the weight gradient repeats bit for bit
+            dw = torch.zeros(H, dtype=torch.float32, device=x2.device)
+            part = torch.empty((_lib.lib().mcb_rmsnorm_bwd_partial_rows(_ll(rows), _int(H)), H), dtype=torch.float32,
+                               device=x2.device)
+        rc = _lib.lib().mcb_rmsnorm_bwd_det(_lib.ptr(dy2), _lib.ptr(x2), _lib.ptr(w), _lib.ptr(rstd), None,
+                                            _lib.ptr(dx), _lib.ptr(dw), _lib.ptr(part), _ll(rows), _int(H),
+                                            _ll(x2.stride(0)), _f(ctx.eps), _int(int(ctx.zc)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_rmsnorm_bwd_det')
         return dx.view(ctx.shape), (dw.to(w.dtype) if dw is not None else None), None, None
 
 

@@ -112,9 +112,13 @@ class _QkvCuda(torch.autograd.Function):
         dqkv = torch.empty_like(qkv)
         dwq = torch.zeros(d, dtype=torch.float32, device=dev) if norm else None
         dwk = torch.zeros(d, dtype=torch.float32, device=dev) if norm else None
+        # per-CTA partial sums of the norm-weight gradients, added in a fixed order (bit-reproducible)
+        part = torch.empty((_lib.lib().mcb_qkv_bwd_partial_rows(_ll(T)), 2, d), dtype=torch.float32,
+                           device=dev) if norm else None
         rc = _lib.lib().mcb_qkv_split_norm_rope_bwd(
             _lib.ptr(qkv), _lib.ptr(wq), _lib.ptr(wk), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(dq), _lib.ptr(dk),
-            _lib.ptr(dv), _lib.ptr(dgate if has_gate else None), _lib.ptr(dqkv), _lib.ptr(dwq), _lib.ptr(dwk), _ll(T),
+            _lib.ptr(dv), _lib.ptr(dgate if has_gate else None), _lib.ptr(dqkv), _lib.ptr(dwq), _lib.ptr(dwk),
+            _lib.ptr(part), _ll(T),
             _int(ng), _int(qpg), _int(d), _int(int(has_gate)), _int(rot), _int(int(interleaved)), _int(int(norm)),
             _int(int(zc)), _f(eps), _ll(qkv.stride(0)), _lib.stream_ptr())
         _lib.check_rc(rc, 'mcb_qkv_split_norm_rope_bwd')

@@ -287,6 +287,7 @@ class DistributedOptimizer:
                          False: torch.zeros(8, dtype=torch.float32, device=dev)}
         # [0] sum of squared gradients; [1] number of ranks whose kernel status word is raised (both all-reduced)
         self._sq = torch.zeros(2, dtype=torch.float32, device=dev)
+        self._sq_scratch = None
         self._skip = torch.zeros(1, dtype=torch.int32, device=dev)   # != 0: this step's update is not applied
         self._coef = torch.ones(1, dtype=torch.float32, device=dev)
         self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -334,8 +335,11 @@ class DistributedOptimizer:
                 if dup is not None:
                     g = g * dup
             if self._use_cuda() and g.dtype == torch.float32:
+                if self._sq_scratch is None:     # per-CTA partials + ticket: fixed summation order
+                    self._sq_scratch = torch.zeros(1025, dtype=torch.float32, device=g.device)
                 _lib.check_rc(_lib.lib().mcb_sqnorm_accum(_lib.ptr(g), _ll(g.numel()), _lib.ptr(part),
-                                                          _lib.stream_ptr()), 'mcb_sqnorm_accum')
+                                                          _lib.ptr(self._sq_scratch), _lib.stream_ptr()),
+                              'mcb_sqnorm_accum')
             else:
                 part += g.float().pow(2).sum()
         flush()

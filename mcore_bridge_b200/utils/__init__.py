@@ -1,6 +1,6 @@
 from .dequantizer import Fp8Dequantizer, MxFp4Dequantizer, PackedDequantizer, fp4_to_fp8, quantize_fp8_blockwise
 from .env import get_dist_setting, get_node_setting, is_dist, is_last_rank, is_local_master, is_master
-from .import_utils import _LazyModule, is_flash_attn_3_available
+from .import_utils import is_flash_attn_3_available, lazy_exports
 from .logger import get_logger
 from .safetensors import LazyTensor, SafetensorLazyLoader, StreamingSafetensorSaver
 from .torch_utils import gc_collect, get_current_device, safe_ddp_context, to_device

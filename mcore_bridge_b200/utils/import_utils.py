@@ -1,56 +1,36 @@
-"""Lazy module used by the package façade so ``import mcore_bridge_b200`` stays cheap.
-
-Parity: reference ``src/mcore_bridge/utils/import_utils.py:11-67``.
-"""
+"""Lazy name resolution for the package façade, so ``import mcore_bridge_b200`` stays cheap (same purpose as the lazy
+module of reference ``src/mcore_bridge/utils/import_utils.py:11-67``, done with module-level ``__getattr__``)."""
 from __future__ import annotations
 
 import importlib
-import os
-from itertools import chain
-from types import ModuleType
 from typing import Any
 
 
-class _LazyModule(ModuleType):
-    """Resolves ``package.Name`` on first access from an ``{submodule: [names]}`` table."""
+def lazy_exports(package: str, table: dict[str, list[str]]):
+    """PEP 562 hooks (``__getattr__``, ``__dir__``) for a package whose public names live in submodules.
 
-    def __init__(self, name, module_file, import_structure, module_spec=None, extra_objects=None):
-        super().__init__(name)
-        self._modules = set(import_structure.keys())
-        self._class_to_module = {}
-        for key, values in import_structure.items():
-            for value in values:
-                self._class_to_module[value] = key
-        self.__all__ = list(import_structure.keys()) + list(chain(*import_structure.values()))
-        self.__file__ = module_file
-        self.__spec__ = module_spec
-        self.__path__ = [os.path.dirname(module_file)]
-        self._objects = {} if extra_objects is None else extra_objects
-        self._name = name
-        self._import_structure = import_structure
+    ``table`` maps a submodule to the names it exports; the submodule is imported the first time one of its names
+    (or the submodule itself) is asked for, and the result is cached in the package's namespace.
+    """
+    owner = {name: sub for sub, names in table.items() for name in names}
+    public = sorted(set(table) | set(owner))
 
-    def __dir__(self):
-        result = list(super().__dir__())
-        result.extend(a for a in self.__all__ if a not in result)
-        return result
-
-    def __getattr__(self, name: str) -> Any:
-        if name in self._objects:
-            return self._objects[name]
-        if name in self._modules:
-            value = self._get_module(name)
-        elif name in self._class_to_module:
-            value = getattr(self._get_module(self._class_to_module[name]), name)
+    def __getattr__(name: str) -> Any:
+        import sys
+        if name in table:
+            value = importlib.import_module(f'{package}.{name}')
+        elif name in owner:
+            value = getattr(importlib.import_module(f'{package}.{owner[name]}'), name)
         else:
-            raise AttributeError(f'module {self.__name__} has no attribute {name}')
-        setattr(self, name, value)
+            raise AttributeError(f'module {package} has no attribute {name}')
+        setattr(sys.modules[package], name, value)
         return value
 
-    def _get_module(self, module_name: str):
-        return importlib.import_module('.' + module_name, self.__name__)
+    def __dir__():
+        import sys
+        return sorted(set(vars(sys.modules[package])) | set(public))
 
-    def __reduce__(self):
-        return self.__class__, (self._name, self.__file__, self._import_structure)
+    return __getattr__, __dir__, public
 
 
 def is_flash_attn_3_available() -> bool:

@@ -107,3 +107,28 @@ def test_gemma4_gpu_matches_cpu_reference():
                     attn.k_layernorm.weight.mul_(0.35)
 
     _compare(c, 256, T=256, tol=8e-2, prep=condition)
+
+
+def _two_steps(name, seed, **kw):
+    from mcore_bridge_b200.train.data import SyntheticPackedDataset
+    from mcore_bridge_b200.train.presets import model_config
+    from mcore_bridge_b200.train.trainer import TrainConfig, Trainer
+    cfg = model_config(name, None, params_dtype=torch.bfloat16, bf16=True, **kw)
+    tr = Trainer(cfg, TrainConfig(lr=1e-3, init_seed=seed, clip_grad=1.0))
+    ds = SyntheticPackedDataset(1024, 1024, seg_lo=96, seg_hi=512, seed=3, pin=False)
+    losses = [float(tr.train_step([ds.next_microbatch() for _ in range(2)])) for _ in range(2)]
+    torch.cuda.synchronize()
+    weights = {n: p.detach().clone() for m in tr.models for n, p in m.named_parameters()}
+    return losses, weights
+
+
+@pytest.mark.parametrize('name,kw', [('qwen3_tiny', {}), ('qwen3_moe_tiny', {'moe_aux_loss_coeff': 1e-2})])
+def test_training_steps_repeat_bit_for_bit(name, kw):
+    """Two optimizer steps from the same seed and data, run twice in one process: losses and every weight must be
+    identical bits.  A kernel whose result depends on the order in which CTAs or warps finish (atomics on floats, a
+    race on a buffer) shows up here as a differing parameter."""
+    l1, w1 = _two_steps(name, 11, **kw)
+    l2, w2 = _two_steps(name, 11, **kw)
+    assert l1 == l2, (l1, l2)
+    bad = [n for n in w1 if not torch.equal(w1[n], w2[n])]
+    assert not bad, bad[:8]

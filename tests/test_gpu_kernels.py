@@ -577,3 +577,31 @@ def test_attention_window_and_sinks(d, nq, nkv, window, use_sinks):
     assert rel(q.grad, qr.grad) < 3e-2 and rel(k.grad, kr.grad) < 3e-2 and rel(v.grad, vr.grad) < 3e-2
     if use_sinks:
         assert rel(sinks.grad, sr.grad) < 3e-2
+
+
+def test_router_gate_on_tensor_cores_matches_fp32_linear():
+    """Router logits and their gradients from the bf16 tensor-core GEMM (fp32 accumulate, two-term split of the fp32
+    logit gradient) against the fp32 ``F.linear`` the router's fp32 mode describes."""
+    from mcore_bridge_b200.layers.moe import _RouterGateFn
+    torch.manual_seed(3)
+    T, H, E = 1000, 512, 128
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(E, H, device=DEV) * 0.1).to(torch.bfloat16).requires_grad_()
+    dl = torch.randn(T, E, device=DEV, dtype=torch.float32)
+    y = _RouterGateFn.apply(x, w, torch.float32)
+    y.backward(dl)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(dl)
+    assert y.dtype == torch.float32
+    assert (y - yr).abs().max().item() < 1e-3 * yr.abs().max().item()
+    assert rel(x.grad, xr.grad) < 5e-3            # bf16 rounding of the result only
+    assert rel(w.grad, wr.grad) < 5e-3
+    # the split keeps the fp32 gradient's low bits: much closer than rounding dl to bf16 would be
+    dx_fp32 = (dl.double() @ w.detach().double())
+    hi_only = (dl.to(torch.bfloat16).double() @ w.detach().double())
+    from mcore_bridge_b200.ops import gemm
+    hi = dl.to(torch.bfloat16)
+    d2 = torch.cat([hi, (dl - hi.float()).to(torch.bfloat16)], dim=1)
+    dx_split = gemm.mm_nn(d2, torch.cat([w.detach(), w.detach()], 0), out_dtype=torch.float32)
+    assert (dx_split.double() - dx_fp32).norm() < 0.05 * (hi_only - dx_fp32).norm()

@@ -1,4 +1,5 @@
-"""Fused compute+collective kernels against the torch.distributed path, on 2 GPUs (skipped on a 1-GPU box)."""
+"""Fused compute+collective kernels against the torch.distributed path and the parallel layouts of the trainer, on 2 or
+more GPUs (skipped on a 1-GPU box)."""
 import os
 import subprocess
 import sys
@@ -50,6 +51,20 @@ def test_peer_memory_dp_collectives_two_ranks():
     cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', '2', '--master-addr',
            '127.0.0.1', '--master-port', '29535', os.path.join(HERE, 'dp_comm_worker.py')]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert 'ALL OK' in res.stdout, res.stdout[-3000:]
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason='needs 2 GPUs')
+def test_parallel_layouts_train_like_data_parallel_on_gpus():
+    """TP2 (+SP), PP2 (1F1B over NCCL send / recv), CP2 (peer-memory K/V exchange) and EP2 (fused MoE exchange) train a
+    tiny model on real GPUs to the same losses as plain data parallelism; with 4 GPUs also TP2 x PP2, TP2 x CP2 and
+    TP2 x EP2."""
+    n = 4 if _ngpu() >= 4 else 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0')
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', str(n), '--master-addr',
+           '127.0.0.1', '--master-port', '29541', os.path.join(HERE, 'gpu_layouts_worker.py')]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert 'ALL OK' in res.stdout, res.stdout[-3000:]
 
