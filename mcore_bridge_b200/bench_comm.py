@@ -38,7 +38,7 @@ def moe_main(a):
     rank = dist.get_rank() if dist.is_initialized() else 0
     ps.initialize_model_parallel(expert_model_parallel_size=world)
     dev = torch.device('cuda', torch.cuda.current_device())
-    kw = hf_to_mcore_config(hf_config('qwen3_30b_a3b'))
+    kw = hf_to_mcore_config(hf_config('qwen3_30b_a3b', num_experts=a.experts))
     cfg = ModelConfig(**kw, bf16=True, expert_model_parallel_size=world)
     torch.manual_seed(7)
     with torch.device(dev):
@@ -47,6 +47,9 @@ def moe_main(a):
     torch.manual_seed(100 + rank)
     x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
     dy = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+
+    for p in layer.parameters():            # weight gradients accumulate into fp32 buffers, as under the trainer
+        p.main_grad = torch.zeros_like(p, dtype=torch.float32)
 
     def step():
         layer.zero_grad(set_to_none=True)
@@ -73,6 +76,15 @@ def moe_main(a):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         res[tag + '_us'] = round(t.item() * 1e3, 1)
         _lib.check_status()
+        if a.profile:
+            from torch.profiler import ProfilerActivity, profile
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for _ in range(3):
+                    step()
+                torch.cuda.synchronize()
+            if rank == 0:
+                print(f'===== {tag}: device time of three iterations')
+                print(prof.key_averages().table(sort_by='cuda_time_total', row_limit=20, max_name_column_width=90))
     k, F = cfg.moe_router_topk, cfg.moe_ffn_hidden_size
     flops = 3 * 2.0 * T * k * H * 3 * F          # fc1 (2F wide) + fc2, forward + two backward GEMMs each
     res['compute_us'] = round(flops / (GEMM_TFLOPS * 1e6), 1)
@@ -92,6 +104,10 @@ def main():
     ap.add_argument('--ffn', type=int, default=12288)
     ap.add_argument('--iters', type=int, default=20)
     ap.add_argument('--moe', action='store_true', help='time the expert-parallel MoE layer instead of the TP kernels')
+    ap.add_argument('--experts', type=int, default=128, help='--moe: number of experts (the fused dispatch + GEMM kernel '
+                    'takes at most 64 per rank, so a single-GPU run of it needs --experts 64)')
+    ap.add_argument('--profile', action='store_true',
+                    help='--moe: also print the per-kernel device times of three iterations (torch.profiler)')
     a = ap.parse_args()
     if a.moe:
         return moe_main(a)

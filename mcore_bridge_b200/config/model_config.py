@@ -253,6 +253,13 @@ class ModelConfig:
                 'compressed sparse attention (DeepSeek-V4 hybrid attention) is not implemented: the reference takes it '
                 'from a Megatron-Core development branch that is not part of its own source tree.  The other '
                 'DeepSeek-V4 pieces (hyper-connections, hash-routed MoE layers) are available on their own.')
+        if self.fp8_param:
+            # weights stay bf16 views of the optimizer's flat buffers; their fp8 copies (and transposes) are cached and
+            # re-quantised only when an optimizer step changes the weight (ops/fp8.py: quantized_weight), which gives
+            # fp8_param's run-time effect (no per-micro-batch weight quantisation) but not its memory saving
+            from ..utils.logger import get_logger
+            get_logger().warning_once('fp8_param: parameters are kept in bf16 with cached fp8 copies; the memory '
+                                      'saving of fp8-only parameters is not implemented')
         if isinstance(self.moe_router_dtype, str) and self.moe_router_dtype.lower() == 'none':
             self.moe_router_dtype = None
         if self.moe_shared_expert_intermediate_size == 0:
