@@ -41,7 +41,7 @@ constexpr int COMM_WARPS = 4;                                  // communication 
 constexpr int COMM_THREADS = GEMM_THREADS + COMM_WARPS * 32;   // 320
 constexpr int RS_THREADS = COMM_THREADS + 32;                  // + the warp that publishes finished tiles (warp 10)
 constexpr int AG_UNIT_BYTES = 16384;                           // what one warp copies between two flag updates
-constexpr int AG_LOADS = 8;                                    // 16-byte loads a lane keeps in flight
+constexpr int AG_LOADS = 16;                                   // 16-byte loads a lane keeps in flight
 
 struct CommGemmParams {
   int M, N, K;

@@ -1,5 +1,6 @@
 // RMSNorm (plain / zero-centred gamma) forward + backward and SwiGLU-family forward + backward.
 // Memory-bound kernels: 16-byte vector accesses, fp32 math, persistent grids sized to the SM count.
+#include "../common/partials.cuh"
 #include "../common/host_utils.cuh"
 #include "../common/ptx.cuh"
 
@@ -242,7 +243,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
     }
   }
   if (partials) {
-    // one row of partial sums per CTA; rmsnorm_dw_reduce_kernel adds the rows in a fixed order
+    // one row of partial sums per CTA; reduce_partials_kernel adds the rows in a fixed order
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = threadIdx.x + i * blockDim.x;
@@ -262,16 +263,6 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
       }
     }
   }
-}
-
-// dw[h] += sum over the CTAs' partial rows, always in row order: the weight gradient repeats bit for bit
-__global__ void __launch_bounds__(256) rmsnorm_dw_reduce_kernel(const float* __restrict__ partials, int nparts, int H,
-                                                                float* __restrict__ dw) {
-  const int h = blockIdx.x * blockDim.x + threadIdx.x;
-  if (h >= H) return;
-  float acc = 0.f;
-  for (int b = 0; b < nparts; ++b) acc += partials[(long long)b * H + h];
-  dw[h] += acc;
 }
 
 // ------------------------------------------------------------------ gated activations
@@ -436,7 +427,7 @@ static int rmsnorm_bwd_launch(const void* dy, const void* x, const void* w, cons
   else if (vpt <= 8) LAUNCH(8);
   else return -2;
 #undef LAUNCH
-  if (partials) rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(partials, (int)grid, H, dw);
+  if (partials) launch_reduce_partials(partials, (int)grid, H, dw, nullptr, H, s);
   return (int)cudaGetLastError();
 }
 

@@ -8,6 +8,7 @@
 //   for each of `ng` groups: [ qpg query heads (each optionally followed by its gate head) | k | v ], head size d.
 // cos/sin are per-token tables [T, rot/2] fp32, so positions, packing, context-parallel chunking,
 // MRoPE sections and attention scaling are all decided by whoever builds the table.
+#include "../common/partials.cuh"
 #include "../common/host_utils.cuh"
 #include "../common/ptx.cuh"
 
@@ -416,18 +417,6 @@ qkv_bwd_fast_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* 
   }
 }
 
-// dwq[i] += sum over the CTAs' partial rows, in row order
-__global__ void qkv_dw_reduce_kernel(const float* __restrict__ partials, int nparts, int d, float* __restrict__ dwq,
-                                     float* __restrict__ dwk) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= 2 * d) return;
-  const int which = i / d, c = i - which * d;
-  float acc = 0.f;
-  for (int b = 0; b < nparts; ++b) acc += partials[((long long)b * 2 + which) * d + c];
-  float* dst = which == 0 ? dwq : dwk;
-  if (dst) dst[c] += acc;
-}
-
 }  // namespace
 
 extern "C" {
@@ -483,7 +472,7 @@ int mcb_qkv_split_norm_rope_bwd(const void* qkv, const void* wq, const void* wk,
         (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv, (const __nv_bfloat16*)dgate,
         (__nv_bfloat16*)dqkv, dwq, dwk, partials, T, L);
   }
-  if (partials) qkv_dw_reduce_kernel<<<(2 * d + 255) / 256, 256, 0, s>>>(partials, grid, d, dwq, dwk);
+  if (partials) launch_reduce_partials(partials, grid, 2 * d, dwq, dwk, d, s);   // rows are [dwq | dwk]
   return (int)cudaGetLastError();
 }
 

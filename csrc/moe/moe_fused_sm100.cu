@@ -218,12 +218,10 @@ moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
       }
       uint4* dst_row = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.xp) + (long long)(u * 32) * row_bytes);
-#pragma unroll 1
-      for (int r = 0; r < 32; ++r, dst_row += n16) {
-        const uint4* s16 = reinterpret_cast<const uint4*>(__shfl_sync(0xffffffffu, reinterpret_cast<uintptr_t>(src), r));
+      auto copy_row = [&](const uint4* s16, uint4* d16) {
         if (s16 == nullptr) {
-          for (int c = lane; c < n16; c += 32) dst_row[c] = make_uint4(0, 0, 0, 0);   // padding row
-          continue;
+          for (int c = lane; c < n16; c += 32) d16[c] = make_uint4(0, 0, 0, 0);   // padding row
+          return;
         }
         for (int base = 0; base < n16; base += 32 * PULL_LOADS) {
           uint4 v[PULL_LOADS];
@@ -235,8 +233,37 @@ moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
           for (int j = 0; j < PULL_LOADS; ++j) {
             const int c = base + j * 32 + lane;
-            if (c < n16) dst_row[c] = v[j];
+            if (c < n16) d16[c] = v[j];
           }
+        }
+      };
+#pragma unroll 1
+      for (int r = 0; r < 32; r += 2, dst_row += 2 * n16) {
+        const uint4* sa = reinterpret_cast<const uint4*>(__shfl_sync(0xffffffffu, reinterpret_cast<uintptr_t>(src), r));
+        const uint4* sb =
+            reinterpret_cast<const uint4*>(__shfl_sync(0xffffffffu, reinterpret_cast<uintptr_t>(src), r + 1));
+        if (sa != nullptr && sb != nullptr && n16 <= 32 * PULL_LOADS) {
+          // two rows of at most 4 KiB at once: 2 x PULL_LOADS loads in flight per lane
+          uint4 va[PULL_LOADS], vb[PULL_LOADS];
+#pragma unroll
+          for (int j = 0; j < PULL_LOADS; ++j) {
+            const int c = j * 32 + lane;
+            if (c < n16) {
+              va[j] = sa[c];
+              vb[j] = sb[c];
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < PULL_LOADS; ++j) {
+            const int c = j * 32 + lane;
+            if (c < n16) {
+              dst_row[c] = va[j];
+              dst_row[n16 + c] = vb[j];
+            }
+          }
+        } else {
+          copy_row(sa, dst_row);
+          copy_row(sb, dst_row + n16);
         }
       }
       __syncwarp();

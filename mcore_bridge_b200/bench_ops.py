@@ -42,16 +42,30 @@ def _time(fn, iters, flush=None):
 def step_profile(a):
     """Per-kernel device time of one ``Trainer.train_step`` (torch.profiler / kineto, CUDA activity) on a model of
     reduced depth, after three warm-up steps: the table the step-breakdown summaries under ``profiles/`` are made of.
-    Single GPU; per-layer figures carry over to the full model."""
+    One GPU, or under ``torch.distributed.run`` with ``--parallelism tp`` / ``ep`` over all ranks (rank 0 reports);
+    per-layer figures carry over to the full model."""
     from torch.profiler import ProfilerActivity, profile
 
     from .train.data import SyntheticPackedDataset
     from .train.presets import model_config
     from .train.trainer import TrainConfig, Trainer
-    torch.cuda.set_device(0)
-    cfg = model_config(a.model, {'num_hidden_layers': a.layers}, bf16=True)
+    import os
+
+    import torch.distributed as dist
+
+    from .parallel import state as ps
+    world, rank = int(os.environ.get('WORLD_SIZE', '1')), int(os.environ.get('RANK', '0'))
+    torch.cuda.set_device(int(os.environ.get('LOCAL_RANK', '0')))
+    extra = {}
+    if world > 1:                      # torchrun: tensor parallel (+ sequence parallel) or expert parallel over all ranks
+        ps.init_distributed()
+        tp = world if a.parallelism == 'tp' else 1
+        ep = world if a.parallelism == 'ep' else 1
+        ps.initialize_model_parallel(tensor_model_parallel_size=tp, expert_model_parallel_size=ep)
+        extra = dict(tensor_model_parallel_size=tp, sequence_parallel=tp > 1, expert_model_parallel_size=ep)
+    cfg = model_config(a.model, {'num_hidden_layers': a.layers}, bf16=True, **extra)
     tr = Trainer(cfg, TrainConfig())
-    ds = SyntheticPackedDataset(cfg.padded_vocab_size, a.seq_len, micro_batch_size=1, seed=1)
+    ds = SyntheticPackedDataset(cfg.padded_vocab_size, a.seq_len, micro_batch_size=1, seed=1 + rank)
 
     def batch():
         return [ds.next_microbatch() for _ in range(a.micro_batches)]
@@ -75,11 +89,16 @@ def step_profile(a):
         r[0] += t
         r[1] += 1
         total += t
-    out = {'op': 'step-profile', 'model': a.model, 'layers': a.layers, 'micro_batches': a.micro_batches,
+    out = {'op': 'step-profile', 'model': a.model, 'layers': a.layers, 'world': world,
+           'parallelism': a.parallelism if world > 1 else 'none', 'micro_batches': a.micro_batches,
            'seq_len': a.seq_len, 'gpu_ms': round(total / 1e3, 2), 'kernels': []}
     for name, (t, n) in sorted(rows.items(), key=lambda kv: -kv[1][0])[:30]:
         out['kernels'].append({'name': name, 'ms': round(t / 1e3, 3), 'share': round(t / total, 4), 'launches': n})
-    print(json.dumps(out))
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     return 0
 
 
@@ -96,6 +115,7 @@ def main():
     ap.add_argument('--model', default='qwen3_8b', help='step-profile: preset name')
     ap.add_argument('--layers', type=int, default=6, help='step-profile: layers of the reduced model')
     ap.add_argument('--micro-batches', type=int, default=2)
+    ap.add_argument('--parallelism', default='tp', choices=['tp', 'ep'], help='step-profile under torchrun')
     ap.add_argument('--seq-len', type=int, default=8192)
     a = ap.parse_args()
     if a.op == 'step-profile':

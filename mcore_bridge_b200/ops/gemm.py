@@ -39,6 +39,15 @@ def _launch(a, a_inner, a_outer, lda, a_mn, b, b_inner, b_outer, ldb, b_mn, c, l
     _lib.check_rc(rc, 'mcb_gemm_bf16')
 
 
+def _lib_mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a @ b`` for the paths without the in-tree kernels, returned in fp32.  On the CPU (the oracle of the tests) the
+    product is formed in fp32; on a GPU with the kernels switched off it is the library's GEMM in the operands' own
+    dtype (bf16 inputs, fp32 accumulation), which is what a stack built on cuBLAS would run."""
+    if a.is_cuda and a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16):
+        return torch.matmul(a, b).float()
+    return torch.matmul(a.float(), b.float())
+
+
 def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
     """Returns a 2-D view whose last dim is contiguous and whose row stride is TMA-compatible."""
     if t.dim() != 2:
@@ -65,7 +74,7 @@ def mm_nt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
     N = w.shape[0]
     assert w.shape[1] == K
     if not _use_cuda(x, w, bias):
-        y = torch.matmul(x.reshape(-1, K).float(), w.float().t()) * alpha
+        y = _lib_mm(x.reshape(-1, K), w.t()) * alpha
         if bias is not None:
             y = y + bias.float()
         y = y.to(out_dtype or x.dtype)
@@ -97,7 +106,7 @@ def mm_nn(dy: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
     K = w.shape[1]
     assert w.shape[0] == N
     if not _use_cuda(dy, w):
-        y = (torch.matmul(dy.reshape(-1, N).float(), w.float()) * alpha).to(out_dtype or dy.dtype)
+        y = (_lib_mm(dy.reshape(-1, N), w) * alpha).to(out_dtype or dy.dtype)
         if out is not None:
             if accumulate:
                 out.add_(y.view(out.shape))
@@ -123,7 +132,7 @@ def mm_tn(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None,
     N = dy.shape[-1]
     K = x.shape[-1]
     if not _use_cuda(dy, x):
-        y = (torch.matmul(dy.reshape(-1, N).float().t(), x.reshape(-1, K).float()) * alpha)
+        y = (_lib_mm(dy.reshape(-1, N).t(), x.reshape(-1, K)) * alpha)
         if out is not None:
             if accumulate:
                 out.add_(y.to(out.dtype))
@@ -161,7 +170,7 @@ def grouped_mm_nt(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, bias:
         for g in range(G):
             s, e = off[g], off[g + 1]
             if e > s:
-                r = x[s:e].float() @ w[g].float().t()
+                r = _lib_mm(x[s:e], w[g].t())
                 if bias is not None:
                     r = r + bias[g].float()
                 y[s:e] = r.to(y.dtype)
@@ -186,7 +195,7 @@ def grouped_mm_nn(dy: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor,
         for g in range(G):
             s, e = off[g], off[g + 1]
             if e > s:
-                y[s:e] = (dy[s:e].float() @ w[g].float()).to(y.dtype)
+                y[s:e] = _lib_mm(dy[s:e], w[g]).to(y.dtype)
         return y
     assert N % 64 == 0, 'grouped dgrad needs the contraction (N) to be a multiple of 64'
     d2 = _row_major_2d(dy)
@@ -209,7 +218,7 @@ def grouped_mm_tn(dy: torch.Tensor, x: torch.Tensor, offsets: torch.Tensor, out:
         for g in range(G):
             s, e = off[g], off[g + 1]
             if e > s:
-                y[g] = dy[s:e].float().t() @ x[s:e].float()
+                y[g] = _lib_mm(dy[s:e].t(), x[s:e])
         if out is not None:
             if accumulate:
                 out.add_(y.to(out.dtype))
