@@ -56,6 +56,7 @@ def parse_args():
     ap.add_argument('--no-secondary', action='store_true', help='skip the MoE run that follows the dense run at 8 GPUs')
     ap.add_argument('--secondary-steps', type=int, default=10)
     ap.add_argument('--no-selfcheck', action='store_true')
+    ap.add_argument('--stage2', default=None, help=argparse.SUPPRESS)   # set by the script itself (see main)
     ap.add_argument('--lora-rank', type=int, default=0,
                     help='train LoRA adapters (alpha = 2 * rank) on all linear layers with the base weights frozen')
     ap.add_argument('--recompute-layers', type=int, default=-1,
@@ -441,6 +442,8 @@ def main():
     args = parse_args()
     if args.impl == 'reference':
         return reference_arm()
+    if args.stage2:
+        return stage2(args)
     if args.impl == 'torchlib':
         os.environ.update(TORCHLIB_ENV)
     os.environ.setdefault('PYTORCH_CUDA_ALLOC_CONF', 'expandable_segments:True')
@@ -470,20 +473,77 @@ def main():
     failed = list(out.get('selfcheck_failed') or [])
     if not moe_primary and args.model == 'qwen3_8b' and not args.no_secondary and args.lora_rank == 0:
         if world >= 8:
-            sec = run_config(args, model='qwen3_30b_a3b', parallelism='ep', steps=args.secondary_steps,
-                             warmup=min(3, max(args.warmup, 3)), seq_len=4096, seqs_per_gpu=16, mbs=2, packed=False,
-                             tol=3e-2)
-            failed += list(sec.get('selfcheck_failed') or [])
-            out['secondary'] = sec
-        else:
-            out['secondary'] = {'model': 'qwen3_30b_a3b', 'unavailable': (
-                f'does not fit on {world} GPU(s): 30.5 B parameters need 16 bytes each for bf16 weights, fp32 '
-                'gradients, master weights and Adam moments (488 GB) before activations; measured at 8 GPUs (EP = 8)')}
+            # The second model runs in a fresh process image: every rank parks the dense result, leaves the process
+            # group and re-executes this script with --stage2.  A new image starts with empty device memory, which no
+            # amount of reference dropping guarantees for 16 GB of model state plus peer-mapped workspaces per rank.
+            path = _stage_path()
+            if rank == 0:
+                import socket
+                with socket.socket() as sk:     # a free port for the second rendezvous (all ranks are on this node)
+                    sk.bind(('127.0.0.1', 0))
+                    port = sk.getsockname()[1]
+                with open(path, 'w') as f:
+                    json.dump({'port': port, 'result': out}, f)
+            dist.barrier()
+            dist.destroy_process_group()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os.execv(sys.executable, [sys.executable, os.path.abspath(__file__)] + sys.argv[1:] + ['--stage2', path])
+        out['secondary'] = {'model': 'qwen3_30b_a3b', 'unavailable': (
+            f'does not fit on {world} GPU(s): 30.5 B parameters need 16 bytes each for bf16 weights, fp32 '
+            'gradients, master weights and Adam moments (488 GB) before activations; measured at 8 GPUs (EP = 8)')}
     if rank == 0:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return 1 if failed else 0
+
+
+def _stage_path() -> str:
+    return os.path.join(tempfile.gettempdir(), f"mcb200_bench_{os.environ.get('MASTER_PORT', '0')}_stage1.json")
+
+
+def stage2(args) -> int:
+    """Second half of the 8-GPU run, in the re-executed processes: the Qwen3-30B-A3B EP = 8 configuration.  Rank 0
+    merges it into the dense result written by the first half and prints the one JSON line."""
+    os.environ.setdefault('PYTORCH_CUDA_ALLOC_CONF', 'expandable_segments:True')
+    from datetime import timedelta
+
+    import torch
+    import torch.distributed as dist
+
+    from mcore_bridge_b200.parallel import state as ps
+    world, rank = int(os.environ['WORLD_SIZE']), int(os.environ['RANK'])
+    torch.cuda.set_device(int(os.environ.get('LOCAL_RANK', '0')))
+    # a rendezvous store of its own (rank 0 hosts it on the port chosen by the first half): the launcher's store still
+    # holds the keys of the first initialisation
+    with open(args.stage2) as f:
+        stage1 = json.load(f)
+    store = dist.TCPStore(os.environ.get('MASTER_ADDR', '127.0.0.1'), int(stage1['port']), world,
+                          is_master=(rank == 0), timeout=timedelta(seconds=600))
+    ps.init_distributed(store=store)
+    error = False
+    try:
+        sec = run_config(args, model='qwen3_30b_a3b', parallelism='ep', steps=args.secondary_steps,
+                         warmup=min(3, max(args.warmup, 3)), seq_len=4096, seqs_per_gpu=16, mbs=2, packed=False,
+                         tol=3e-2)
+    except Exception as e:      # the dense result must not be lost with the second model's run
+        sec = {'model': 'qwen3_30b_a3b', 'error': f'{type(e).__name__}: {str(e)[:300]}'}
+        error = True
+    failed = []
+    if rank == 0:
+        out = stage1['result']
+        os.unlink(args.stage2)
+        failed = list(out.get('selfcheck_failed') or []) + list(sec.get('selfcheck_failed') or [])
+        out['secondary'] = sec
+        print(json.dumps(out), flush=True)
+    if error:
+        # the failed run may have left collectives or the CUDA context unusable: leave without the usual teardown
+        sys.stderr.flush()
+        os._exit(1 if failed else 0)
+    dist.barrier()
+    dist.destroy_process_group()
     return 1 if failed else 0
 
 

@@ -110,7 +110,13 @@ moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   constexpr uint32_t TMEM_COLS = 2 * BN;
   extern __shared__ uint8_t smem_raw[];
   __shared__ Layout L;
-  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;  // an earlier wait gave up: do not pile up
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) {
+    // an earlier kernel gave up (or a receive buffer overflowed): do not pile up, and leave offsets behind that keep
+    // the kernels that follow in this step inside their buffers (the step's update is skipped anyway)
+    if (p.mode == 0 && blockIdx.x == 0)
+      for (int el = threadIdx.x; el <= p.El; el += blockDim.x) p.seg_off[el] = 0;
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int El = p.El;
 
@@ -136,8 +142,9 @@ moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
       L.seg_off[El] = acc;
       if (blockIdx.x == 0) {
-        for (int el = 0; el <= El; ++el) p.seg_off[el] = L.seg_off[el];
-        if (acc > p.capacity && p.status) atomicMax(p.status, ST_MOE_OVERFLOW);  // routing does not fit the buffer
+        // published offsets never point past the buffer, also when the routing does not fit it
+        for (int el = 0; el <= El; ++el) p.seg_off[el] = min(L.seg_off[el], p.capacity);
+        if (acc > p.capacity && p.status) atomicMax(p.status, ST_MOE_OVERFLOW);
       }
     }
   } else {
@@ -355,6 +362,194 @@ moe_pull_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// owner side: grouped GEMM whose epilogue scatters every output row to the rank and slot it came from
+// ---------------------------------------------------------------------------------------------------------------
+// Second expert layer (forward) and data gradient of the first (backward).  Row R of the expert-sorted operand
+// belongs to routing entry `ent` of source rank `s` (row_src[R] = s * T * k + ent, recorded by the dispatch); its
+// result goes straight from the accumulator to slot `ent` of that rank's [T * k, N] buffer, over NVLink for remote
+// sources, while later tiles are still being multiplied.  The source then adds the k slots of each token in a fixed
+// order (moe_sum_slots_kernel): the combine needs no second pass over the owners' memory and no atomics.
+struct MoeScatterParams {
+  int world, T, k, El;
+  int K;                  // contraction size
+  int N;                  // output width = slot width (a multiple of 64)
+  int capacity;
+  const int* seg_off;     // [El + 1]
+  const int* row_src;     // [capacity]
+  void* slot_ptrs[MAX_WORLD];         // [T * k, N] bf16 on every source
+  float* sslot_ptrs[MAX_WORLD];       // optional [T * k] fp32: per-entry scalar (gradient of the routing probability)
+  const float* scalar;                // optional [capacity]: the scalar of every row
+  int b_group_rows;
+  int* status;
+};
+
+constexpr int SC_STAGE_BYTES = 32 * 128;   // per epilogue warp: 32 rows x 64 bf16 columns
+
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+moe_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const MoeScatterParams p) {
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_seg[MAX_EL + 1];
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int El = p.El;
+  for (int el = threadIdx.x; el <= El; el += blockDim.x) s_seg[el] = p.seg_off[el];
+  Pipe<BN> P(smem_raw);
+  if (threadIdx.x == 0) {
+    P.init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(P.tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *P.tmem_slot;
+  const int valid_rows = min(s_seg[El], p.capacity);
+  const int nblocks = valid_rows / PADM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int total = nblocks * tiles_n;
+  const int g0 = blockIdx.x, gs = gridDim.x;
+  const long long per_src = (long long)p.T * p.k;
+  auto expert_of = [&](int mb) {
+    int el = 0;
+    while (el + 1 < El && s_seg[el + 1] <= mb * PADM) ++el;
+    return el;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = g0; t < total; t += gs) {
+        const int mb = t / tiles_n, tn = t - mb * tiles_n;
+        const int el = expert_of(mb);
+        const int n0 = B_MN ? tn * BN : el * p.b_group_rows + tn * BN;
+        if (!load_tile<BN, B_MN>(P, &tmap_a, &tmap_b, mb * PADM, n0, p.K, it, p.status, B_MN ? el * p.b_group_rows : 0))
+          break;
+      }
+      drain_loads<BN>(P, it);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int t = g0; t < total && ok; t += gs, ++lt) {
+        const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+        if (!mbar_wait(smem_u32(&P.tempty_bar[acc]), aph ^ 1, P.abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        issue_mma_tile<BN, B_MN>(P, tmem_base + acc * BN, p.K, it, p.status, ok);
+        if (ok) umma_commit(smem_u32(&P.tfull_bar[acc]));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    // this warp's transposition buffer: rows go in one per lane, come out 128 contiguous bytes per quarter-warp
+    uint8_t* stage = P.smem + GemmSmem<BN>::STAGES * GemmSmem<BN>::STAGE_BYTES + GemmSmem<BN>::BAR_BYTES + q * SC_STAGE_BYTES;
+    uint32_t lt = 0;
+    for (int t = g0; t < total; t += gs, ++lt) {
+      const int mb = t / tiles_n, tn = t - mb * tiles_n;
+      const int n0 = tn * BN;
+      const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+      // destination of this lane's row (null: padding row, nothing to send)
+      const int R = mb * PADM + q * 32 + lane;
+      uint8_t* dst_row = nullptr;
+      const int id = p.row_src[R];
+      if (id >= 0) {
+        const int sr = id / (int)per_src;
+        const int ent = id - sr * (int)per_src;
+        if (sr < p.world) dst_row = reinterpret_cast<uint8_t*>(p.slot_ptrs[sr]) + ((long long)ent * p.N + n0) * 2;
+        else if (p.status) atomicCAS(p.status, 0, ST_BAD_ARGUMENT);      // a torn table: report, send nothing
+      }
+      if (!mbar_wait(smem_u32(&P.tfull_bar[acc]), aph, P.abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int cc = 0; cc < BN; cc += 64) {
+        if (n0 + cc >= p.N) break;
+        uint32_t r[64];
+        tmem_ld_32x32_x64(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + cc, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(r[8 * u]), __uint_as_float(r[8 * u + 1]));
+          o.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
+          o.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
+          o.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((u ^ (lane & 7)) << 4)) = o;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = i * 4 + (lane >> 3), u = lane & 7;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 128 + ((u ^ (row & 7)) << 4));
+          uint8_t* base = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<uintptr_t>(dst_row), row));
+          if (base) *reinterpret_cast<uint4*>(base + cc * 2 + u * 16) = v;
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&P.tempty_bar[acc]));
+    }
+    // per-entry scalars (backward: gradient of each routing probability) ride along
+    if (p.scalar) {
+      const int tid = (int)blockIdx.x * 128 + (int)threadIdx.x - 64, nthr = (int)gridDim.x * 128;
+      for (int R = tid; R < valid_rows; R += nthr) {
+        const int id = p.row_src[R];
+        if (id < 0) continue;
+        const int sr = id / (int)per_src;
+        const int ent = id - sr * (int)per_src;
+        if (sr < p.world && p.sslot_ptrs[sr]) p.sslot_ptrs[sr][ent] = p.scalar[R];
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// out[t] = sum over the k slots of token t whose entry was delivered (sent_row >= 0), in slot order
+__global__ void __launch_bounds__(256) moe_sum_slots_kernel(const __nv_bfloat16* __restrict__ slots,
+                                                            const int* __restrict__ sent_row, int T, int k, int N,
+                                                            __nv_bfloat16* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int nvec = N / 8;
+  for (long long t = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += nwarps) {
+    const int mine = lane < k ? sent_row[t * k + lane] : -1;
+    const unsigned have = __ballot_sync(0xffffffffu, mine >= 0);
+    for (int v0 = lane; v0 < nvec; v0 += 32) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int kk = 0; kk < k; ++kk) {
+        if (!((have >> kk) & 1u)) continue;
+        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(slots + ((long long)t * k + kk) * N) + v0);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      reinterpret_cast<uint4*>(out + t * N)[v0] = o;
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -421,6 +616,65 @@ int mcb_moe_pull_gemm(const void* const* x_ptrs, const int* const* order_ptrs, c
     }
     kern<<<sms, MOE_THREADS, smem, stream>>>(ta, tb, p);
   }
+  return (int)cudaGetLastError();
+}
+
+// Grouped GEMM C[rows of expert e] = A[rows of e] . B_e with the result rows scattered to their sources:
+// A [capacity, K] bf16 (expert-sorted rows, segments `seg_off`), B stacked expert weights K-major `[El * N, K]`
+// (b_mn = 0) or MN-major `[El * K, N]` (b_mn = 1), row_src [capacity] from the dispatch, slot_ptrs[s] = rank s's
+// [T * k, N] bf16 slot buffer, sslot_ptrs / scalar optional (per-entry fp32 values pushed the same way).
+int mcb_moe_gemm_scatter(const void* A, const void* B, long long b_inner, long long b_outer, long long ldb, int b_mn,
+                         int b_group_rows, void* const* slot_ptrs, void* const* sslot_ptrs, const float* scalar,
+                         const int* seg_off, const int* row_src, int world, int T, int k, int El, int K, int N,
+                         int capacity, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (world < 1 || world > MAX_WORLD || El < 1 || El > MAX_EL || K % 8 || N % 64 || capacity % PADM) return -2;
+  if ((long long)world * T * k >= (1ll << 31)) return -3;
+  constexpr int BN = 256;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, capacity, K, GEMM_BK, GEMM_BM);
+  if (rc) return rc;
+  rc = b_mn ? make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, 64, GEMM_BK)
+            : make_tmap_2d_bf16(&tb, B, b_inner, b_outer, ldb, GEMM_BK, BN);
+  if (rc) return rc;
+  MoeScatterParams p{};
+  p.world = world; p.T = T; p.k = k; p.El = El; p.K = K; p.N = N; p.capacity = capacity;
+  p.seg_off = seg_off; p.row_src = row_src; p.scalar = scalar; p.b_group_rows = b_group_rows; p.status = status;
+  for (int i = 0; i < world; ++i) {
+    p.slot_ptrs[i] = slot_ptrs[i];
+    p.sslot_ptrs[i] = sslot_ptrs ? reinterpret_cast<float*>(sslot_ptrs[i]) : nullptr;
+  }
+  const int smem = GemmSmem<BN>::TOTAL + 4 * SC_STAGE_BYTES;
+  const int sms = device_sm_count();
+  static bool cfg[2] = {false, false};
+  cudaError_t e;
+  if (b_mn) {
+    auto kern = moe_gemm_scatter_kernel<BN, true>;
+    if (!cfg[1]) {
+      if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
+      cfg[1] = true;
+    }
+    kern<<<sms, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+  } else {
+    auto kern = moe_gemm_scatter_kernel<BN, false>;
+    if (!cfg[0]) {
+      if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
+      cfg[0] = true;
+    }
+    kern<<<sms, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+  }
+  return (int)cudaGetLastError();
+}
+
+// out [T, N] = per token, the sum of its delivered slots (slots [T * k, N] bf16, sent_row [T, k]: < 0 = not delivered)
+int mcb_moe_sum_slots(const void* slots, const int* sent_row, int T, int k, int N, void* out, void* stream_) {
+  if (N % 8 || k < 1 || k > 32) return -1;
+  if (T == 0) return 0;
+  long long blocks = ((long long)T * 32 + 255) / 256;
+  const long long cap = (long long)device_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  moe_sum_slots_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(slots), sent_row, T, k, N, reinterpret_cast<__nv_bfloat16*>(out));
   return (int)cudaGetLastError();
 }
 

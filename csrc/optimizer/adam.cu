@@ -78,7 +78,16 @@ __global__ void sqnorm_kernel(const float* __restrict__ x, long long n, float* _
                               float* __restrict__ scratch) {
   float acc = 0.f;
   const long long stride = (long long)gridDim.x * blockDim.x * 4;
-  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+  long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  // four independent 16-byte loads in flight per thread while whole strides remain
+  for (; i + 3 * stride + 4 <= n; i += 4 * stride) {
+    float4 g[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) g[u] = __ldcs(reinterpret_cast<const float4*>(x + i + u * stride));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc += g[u].x * g[u].x + g[u].y * g[u].y + g[u].z * g[u].z + g[u].w * g[u].w;
+  }
+  for (; i < n; i += stride) {
     if (i + 4 <= n) {
       float4 g = *reinterpret_cast<const float4*>(x + i);
       acc += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;

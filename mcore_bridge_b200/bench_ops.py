@@ -105,7 +105,7 @@ def step_profile(a):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('op', choices=['step-profile', 'gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'rmsnorm_bwd', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention', 'attention_bwd',
-                                  'gemm_fp8', 'quant_fp8', 'dsa_index', 'topk', 'simple_gla', 'conv1d'])
+                                  'gemm_fp8', 'quant_fp8', 'dsa_index', 'topk', 'simple_gla', 'conv1d', 'lora'])
     ap.add_argument('--m', type=int, default=8192)
     ap.add_argument('--n', type=int, default=4096)
     ap.add_argument('--k', type=int, default=4096)
@@ -135,6 +135,34 @@ def main():
         t = _time(fn, a.iters, flush)
         tf = 2.0 * M * N * K / t / 1e12
         res.update(seconds=t, tflops=tf, frac_of_burst_peak=tf / burst, peak_source=src)
+    elif a.op == 'lora':
+        # the adapter GEMMs of one LoRA linear (rank --bn or 16) next to its frozen base GEMMs, forward + backward
+        r = a.bn or 16
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        la = torch.randn(r, K, device=dev, dtype=torch.bfloat16) * 0.02
+        lb = torch.randn(N, r, device=dev, dtype=torch.bfloat16) * 0.02
+        dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+        y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        dx = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+
+        def base():
+            gemm.mm_nt(x, w, out=y)
+            gemm.mm_nn(dy, w, out=dx)
+
+        def adapter():
+            t = gemm.mm_nt(x, la)                               # [M, r]
+            gemm.mm_nt(t, lb, out=y, accumulate=True, alpha=2.0)
+            dt = gemm.mm_nn(dy, lb, alpha=2.0)                  # [M, r]
+            gemm.mm_tn(dy, t, out_dtype=torch.bfloat16)         # dB [N, r]
+            gemm.mm_tn(dt, x, out_dtype=torch.bfloat16)         # dA [r, K]
+            gemm.mm_nn(dt, la, out=dx, accumulate=True)
+
+        tb = _time(base, a.iters, flush)
+        ta = _time(adapter, a.iters, flush)
+        moved = (2 * M * K + 3 * M * N + 2 * M * K) * 2          # x, y (r+w), dy x2, x, dx (r+w)
+        res.update(rank=r, seconds_base_fwd_dgrad=tb, seconds_adapter_6_gemms=ta, adapter_over_base=ta / tb,
+                   adapter_gbs=moved / ta / 1e9, frac_of_hbm_peak=moved / ta / 1e9 / hbm, peak_source=src)
     elif a.op == 'rmsnorm':
         x = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
         w = torch.ones(N, device=dev, dtype=torch.bfloat16)

@@ -83,11 +83,14 @@ def build(verbose: bool = True, force: bool = False) -> Path:
     newest = max(o.stat().st_mtime for o in objs)
     if out.exists() and out.stat().st_mtime >= newest and not force:
         return out
-    cmd = [_nvcc(), '-shared', '-o', str(out), *map(str, objs), '-gencode', 'arch=compute_100a,code=sm_100a',
-           ]
+    # link next to the target and rename: a process (or a copy of the tree) never sees a half-written library
+    tmp = out.with_name(out.name + f'.tmp{os.getpid()}')
+    cmd = [_nvcc(), '-shared', '-o', str(tmp), *map(str, objs), '-gencode', 'arch=compute_100a,code=sm_100a']
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
+        tmp.unlink(missing_ok=True)
         raise RuntimeError(f'link failed:\n{res.stdout}\n{res.stderr}')
+    os.replace(tmp, out)
     if verbose:
         sys.stderr.write(f'[build_ext] linked {out}\n')
     return out

@@ -78,7 +78,10 @@ class ExchangeBuffers:
         offs = {}
         for name, nbytes in (('x', T * H * 2), ('idx', T * k * 4), ('probs', T * k * 4), ('counts', E * 4),
                              ('sent', T * k * 4), ('out', capacity * H * 2), ('scalar', capacity * 4),
-                             ('order', T * k * 4), ('eoff', (E + 1) * 4)):
+                             ('order', T * k * 4), ('eoff', (E + 1) * 4),
+                             # one slot per routing entry: the owners' last GEMM of a direction writes result rows
+                             # (and per-entry scalars) straight into them
+                             ('slots', T * k * H * 2), ('sslots', T * k * 4)):
             offs[name] = o
             o += al(nbytes)
         self.half = o
@@ -401,6 +404,42 @@ def _pull_gemm(b: ExchangeBuffers, par: int, mode: int, st: 'DispatchState', El:
 
 
 
+def _gemm_scatter(b: ExchangeBuffers, par: int, st: 'DispatchState', El: int, a2: torch.Tensor, weight: torch.Tensor,
+                  b_mn: bool, scalar: Optional[torch.Tensor]):
+    """Grouped expert GEMM over the expert-sorted rows ``a2 [cap, K]`` whose epilogue sends every result row to the
+    slot of the routing entry it belongs to on the entry's source rank (``slots`` region, over NVLink for remote
+    sources); ``scalar [cap]`` (fp32, optional) travels the same way into ``sslots``."""
+    G, d1, d2 = weight.shape
+    w2 = weight.view(G * d1, d2)
+    if b_mn:            # weight [El, K(contraction), N]
+        K, N, b_inner, b_outer, group_rows = d1, d2, d2, G * d1, d1
+    else:               # weight [El, N, K]
+        K, N, b_inner, b_outer, group_rows = d2, d1, d2, G * d1, d1
+    assert a2.shape == (b.cap, K) and a2.is_contiguous() and N == b.H
+    rc = _lib.lib().mcb_moe_gemm_scatter(
+        _lib.ptr(a2), _lib.ptr(w2), ctypes.c_longlong(b_inner), ctypes.c_longlong(b_outer),
+        ctypes.c_longlong(w2.stride(0)), _int(int(b_mn)), _int(group_rows), b.ptrs('slots', par),
+        b.ptrs('sslots', par) if scalar is not None else None, _lib.ptr(scalar), _lib.ptr(st.seg_off),
+        _lib.ptr(st.row_src), _int(b.world), _int(b.T), _int(b.k), _int(El), _int(K), _int(N), _int(b.cap),
+        _lib.ptr(_lib.status_word(a2.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_moe_gemm_scatter')
+
+
+def scatter_enabled() -> bool:
+    """The last GEMM of each direction pushes its rows to the sources' slots (``MCB200_MOE_SCATTER=0``: it writes the
+    owner's buffer and the sources pull and sum with ``moe_combine``)."""
+    return os.environ.get('MCB200_MOE_SCATTER', '0') != '0'
+
+
+def _sum_slots(b: ExchangeBuffers, par: int, sent: torch.Tensor) -> torch.Tensor:
+    """Per token, the fixed-order sum of the ``k`` result rows the owners wrote into this rank's slots."""
+    out = torch.empty((b.T, b.H), dtype=torch.bfloat16, device=sent.device)
+    rc = _lib.lib().mcb_moe_sum_slots(_lib.ptr(b.view('slots', par, (b.T * b.k, b.H), torch.bfloat16)), _lib.ptr(sent),
+                                      _int(b.T), _int(b.k), _int(b.H), _lib.ptr(out), _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_moe_sum_slots')
+    return out
+
+
 def pull_gemm_supported(experts, config, El: int, H: int) -> bool:
     """The fused dispatch + expert GEMM applies to plain stacked bf16 expert weights without biases, probabilities
     applied after the first layer and at most 64 local experts."""
@@ -413,7 +452,7 @@ def pull_gemm_supported(experts, config, El: int, H: int) -> bool:
         if type(lin) is not GroupedLinear or lin.bias is not None or lin.weight.dtype != torch.bfloat16:
             return False
     f = experts.linear_fc2.weight.shape[2]
-    return El <= 64 and H % 8 == 0 and f % 64 == 0 and experts.linear_fc1.weight.shape[1] % 8 == 0
+    return El <= 64 and H % 64 == 0 and f % 64 == 0 and experts.linear_fc1.weight.shape[1] % 8 == 0
 
 
 class _DispatchFc1Fn(torch.autograd.Function):
@@ -448,6 +487,20 @@ class _DispatchFc1Fn(torch.autograd.Function):
         T, H, k = b.T, b.H, b.k
         dh = dh.contiguous()
         par, epoch = b.epoch & 1, b.epoch     # same call whose first half ran in _Fc2CombineFn.backward
+        # the data-gradient GEMM of the first layer sends every input-gradient row (and the gradient of its routing
+        # probability) straight to the slot of its entry on the source rank; the sources then add their k slots
+        if scatter_enabled():
+            sc = drow_probs.float().contiguous() if drow_probs is not None else None
+            _gemm_scatter(b, par, st, El, dh, w1, True, sc)
+            dw1 = _weight_grad_grouped(w1, dh, xp, st.seg_off) if ctx.needs_input_grad[3] else None
+            b.signal(F_DONE, epoch)
+            b.wait(F_DONE, epoch)
+            dx = _sum_slots(b, par, st.sent_row)
+            if sc is not None:
+                dprobs = torch.where(st.sent_row >= 0, b.view('sslots', par, (T, k), torch.float32), 0.0)
+            else:
+                dprobs = torch.zeros((T, k), dtype=torch.float32, device=dh.device)
+            return dx, dprobs.to(ctx.pdtype), None, dw1, None, None
         # owners publish their input-gradient rows (written by the GEMM straight into the symmetric region) and the
         # probability gradients, sources pull them back
         gemm.grouped_mm_nn(dh, w1, st.seg_off, out=b.view('out', par, (b.cap, H), torch.bfloat16))
@@ -469,9 +522,9 @@ class _DispatchFc1Fn(torch.autograd.Function):
 
 
 class _Fc2CombineFn(torch.autograd.Function):
-    """(a [cap,F], w2 [El,H,F]) -> out [T,H]: second expert layer into the symmetric output buffer, then the sources
-    pull and sum their k rows.  Backward: the owners pull the output-gradient rows and run the data-gradient GEMM of
-    the second layer in one launch."""
+    """(a [cap,F], w2 [El,H,F]) -> out [T,H]: the second expert layer's epilogue sends every result row to its entry's
+    slot on the source rank, then the sources add their k slots.  Backward: the owners pull the output-gradient rows and
+    run the data-gradient GEMM of the second layer in one launch."""
 
     @staticmethod
     def forward(ctx, a, w2, st: 'DispatchState', El: int):
@@ -479,15 +532,23 @@ class _Fc2CombineFn(torch.autograd.Function):
         b = st.fwd
         T, H, k = b.T, b.H, b.k
         par, epoch = st.parity, b.epoch
-        gemm.grouped_mm_nt(a, w2, st.seg_off, out=b.view('out', par, (b.cap, H), torch.bfloat16))
+        scatter = scatter_enabled()
+        if scatter:
+            _gemm_scatter(b, par, st, El, a.contiguous(), w2, False, None)
+        else:
+            gemm.grouped_mm_nt(a, w2, st.seg_off, out=b.view('out', par, (b.cap, H), torch.bfloat16))
         b.signal(F_DONE, epoch)
         b.wait(F_DONE, epoch)
         idx = b.view('idx', par, (T, k), torch.int32)
         sent = b.view('sent', par, (T, k), torch.int32)
-        out = torch.empty((T, H), dtype=torch.bfloat16, device=a.device)
-        rc = _lib.lib().mcb_moe_combine(b.ptrs('out', par), None, _int(b.world), _int(T), _int(k), _int(El), _int(H),
-                                        _lib.ptr(idx), _lib.ptr(sent), _lib.ptr(out), None, _lib.stream_ptr())
-        _lib.check_rc(rc, 'mcb_moe_combine')
+        if scatter:
+            out = _sum_slots(b, par, sent)
+        else:
+            out = torch.empty((T, H), dtype=torch.bfloat16, device=a.device)
+            rc = _lib.lib().mcb_moe_combine(b.ptrs('out', par), None, _int(b.world), _int(T), _int(k), _int(El),
+                                            _int(H), _lib.ptr(idx), _lib.ptr(sent), _lib.ptr(out), None,
+                                            _lib.stream_ptr())
+            _lib.check_rc(rc, 'mcb_moe_combine')
         st.sent_row = sent.clone()   # the published tables are reused two calls later
         st.idx = idx.clone()
         ctx.save_for_backward(a, w2)

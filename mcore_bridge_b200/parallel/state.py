@@ -343,8 +343,9 @@ def get_model_parallel_group():
     return get_group('mp')
 
 
-def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) -> None:
-    """Initialises ``torch.distributed`` from the torchrun environment (no-op for a single process)."""
+def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0, store=None) -> None:
+    """Initialises ``torch.distributed`` from the torchrun environment (no-op for a single process).  ``store``: an
+    explicit rendezvous store instead of the environment's (for a second initialisation after ``exec``)."""
     if dist.is_initialized():
         return
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -357,4 +358,6 @@ def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) ->
     kw = {}
     if backend == 'nccl':
         kw['device_id'] = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
+    if store is not None:
+        kw.update(store=store, rank=int(os.environ['RANK']), world_size=world)
     dist.init_process_group(backend=backend, timeout=timedelta(seconds=timeout_s), **kw)

@@ -40,10 +40,13 @@ for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None
     gx = torch.Generator(device=dev).manual_seed(100+rank)
     x = (torch.randn(T, H, device=dev, generator=gx)).to(torch.bfloat16)
     outs = {}
-    # '1': exchange fused into the expert GEMMs; 'k': the separate dispatch / combine kernels; '0': torch.distributed
-    for fused in ('1','k','0'):
+    # 's': exchange fused into the expert GEMMs in both directions (gather before the first, scatter after the last);
+    # '1': gather fused, results pulled by the combine kernel; 'k': the separate dispatch / combine kernels;
+    # '0': torch.distributed
+    for fused in ('s','1','k','0'):
         os.environ['MCB200_FUSED_MOE'] = '0' if fused == '0' else '1'
-        os.environ['MCB200_MOE_FUSED_GEMM'] = '0' if fused == 'k' else '1' 
+        os.environ['MCB200_MOE_FUSED_GEMM'] = '0' if fused == 'k' else '1'
+        os.environ['MCB200_MOE_SCATTER'] = '1' if fused == 's' else '0'
         layer.zero_grad()
         xx = x.clone().requires_grad_()
         y = layer(xx)
@@ -53,7 +56,7 @@ for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None
         outs[fused] = (y.detach().clone(), xx.grad.clone(), layer.router.weight.grad.clone(), layer.experts.linear_fc1.weight.grad.clone(), layer.experts.linear_fc2.weight.grad.clone())
         torch.cuda.synchronize(); _lib.check_status()
     names = ['y','dx','drouter','dfc1','dfc2']
-    for tag in ('1', 'k'):
+    for tag in ('s', '1', 'k'):
         for n_, a_, b_ in zip(names, outs[tag], outs['0']):
             r = rel(a_, b_); good = r < 3e-2
             t = torch.tensor([0 if good else 1], device=dev)
@@ -63,7 +66,7 @@ for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None
     # the row assignment of the fused dispatch+GEMM path has no atomics: a second run gives the same bits
     from mcore_bridge_b200.layers import moe_fused
     if moe_fused.pull_gemm_supported(layer.experts, layer.config, E // world, H):
-        os.environ['MCB200_FUSED_MOE'] = '1'; os.environ['MCB200_MOE_FUSED_GEMM'] = '1'
+        os.environ['MCB200_FUSED_MOE'] = '1'; os.environ['MCB200_MOE_FUSED_GEMM'] = '1'; os.environ['MCB200_MOE_SCATTER'] = '0'
         layer.zero_grad(); xx = x.clone().requires_grad_(); y2 = layer(xx); y2.backward(dy)
         same = torch.equal(y2, outs['1'][0]) and torch.equal(layer.experts.linear_fc1.weight.grad, outs['1'][3])
         t = torch.tensor([0 if same else 1], device=dev)
