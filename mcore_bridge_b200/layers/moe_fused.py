@@ -597,10 +597,18 @@ class FusedMoEDispatcher:
         probs_out = torch.empty((b.T, b.k), dtype=torch.float32, device=logits.device)
         idx_out = b.view('idx', st.parity, (b.T, b.k), torch.int32)
         counts_out = b.view('counts', st.parity, (b.E,), torch.int32)
-        v8 = None if valid is None else valid.to(torch.uint8).contiguous()
-        probs, idx, score_sum = _RouterFn.apply(logits, bias, v8, b.k, sigmoid, renorm, groups, group_topk,
-                                                float(scaling or 1.0), probs_out, idx_out, counts_out)
-        return probs, idx, score_sum, counts_out
+        if valid is None:
+            probs, idx, score_sum = _RouterFn.apply(logits, bias, None, b.k, sigmoid, renorm, groups, group_topk,
+                                                    float(scaling or 1.0), probs_out, idx_out, counts_out)
+            return probs, idx, score_sum, counts_out
+        # Padded tokens are routed like any other token but do not enter the load statistics: the kernel's counts
+        # (valid tokens only) go to the caller, the published counts, which size the exchange, cover every entry.
+        stat_counts = torch.empty(b.E, dtype=torch.int32, device=logits.device)
+        probs, idx, score_sum = _RouterFn.apply(logits, bias, valid.to(torch.uint8).contiguous(), b.k, sigmoid, renorm,
+                                                groups, group_topk, float(scaling or 1.0), probs_out, idx_out,
+                                                stat_counts)
+        counts_out.copy_(torch.bincount(idx_out.reshape(-1).long(), minlength=b.E).to(torch.int32))
+        return probs, idx, score_sum, stat_counts
 
     def publish_routing(self, st: DispatchState, idx: torch.Tensor):
         """Routing decided elsewhere (torch router): publish indices and per-expert counts for the exchange."""

@@ -20,7 +20,8 @@ from mcore_bridge_b200.config import hf_to_mcore_config
 from mcore_bridge_b200.layers.moe import MoELayer
 def rel(a,b): return ((a.float()-b.float()).norm()/(b.float().norm()+1e-9)).item()
 ok = True
-for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None),(64,6,1024,256,True,8)]:
+for (E,k,H,F,sig,groups,use_mask) in [(8,2,256,128,False,None,False),(128,8,2048,768,False,None,False),(64,6,1024,256,True,8,False),
+                                      (8,2,256,128,False,None,True),(64,6,1024,256,True,8,True)]:
     kw = hf_to_mcore_config(hf_config('qwen3_moe_tiny', num_experts=E, num_experts_per_tok=k, hidden_size=H, moe_intermediate_size=F))
     if sig: kw.update(moe_router_score_function='sigmoid', moe_router_enable_expert_bias=True, moe_router_num_groups=groups, moe_router_group_topk=4, moe_router_topk_scaling_factor=2.5)
     cfg = ModelConfig(**kw, bf16=True, expert_model_parallel_size=world, moe_aux_loss_coeff=1e-2)
@@ -39,6 +40,8 @@ for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None
     T = 1024
     gx = torch.Generator(device=dev).manual_seed(100+rank)
     x = (torch.randn(T, H, device=dev, generator=gx)).to(torch.bfloat16)
+    # padded tokens are routed like the others but stay out of the load statistics
+    mask = (torch.rand(T, device=dev, generator=gx) < 0.1) if use_mask else None
     outs = {}
     # 's': exchange fused into the expert GEMMs in both directions (gather before the first, scatter after the last);
     # '1': gather fused, results pulled by the combine kernel; 'k': the separate dispatch / combine kernels;
@@ -49,7 +52,7 @@ for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None
         os.environ['MCB200_MOE_SCATTER'] = '1' if fused == 's' else '0'
         layer.zero_grad()
         xx = x.clone().requires_grad_()
-        y = layer(xx)
+        y = layer(xx, padding_mask=mask)
         gy = torch.Generator(device=dev).manual_seed(200+rank)
         dy = torch.randn(y.shape, device=dev, generator=gy).to(torch.bfloat16)
         y.backward(dy)
@@ -62,12 +65,12 @@ for (E,k,H,F,sig,groups) in [(8,2,256,128,False,None),(128,8,2048,768,False,None
             t = torch.tensor([0 if good else 1], device=dev)
             if world>1: dist.all_reduce(t)
             ok &= t.item()==0
-            if rank==0: print(f'E{E} k{k} H{H} sig{sig} mode {tag}: {n_} rel={r:.3e} {"OK" if t.item()==0 else "FAIL"}', flush=True)
+            if rank==0: print(f'E{E} k{k} H{H} sig{sig} mask{int(use_mask)} mode {tag}: {n_} rel={r:.3e} {"OK" if t.item()==0 else "FAIL"}', flush=True)
     # the row assignment of the fused dispatch+GEMM path has no atomics: a second run gives the same bits
     from mcore_bridge_b200.layers import moe_fused
     if moe_fused.pull_gemm_supported(layer.experts, layer.config, E // world, H):
         os.environ['MCB200_FUSED_MOE'] = '1'; os.environ['MCB200_MOE_FUSED_GEMM'] = '1'; os.environ['MCB200_MOE_SCATTER'] = '0'
-        layer.zero_grad(); xx = x.clone().requires_grad_(); y2 = layer(xx); y2.backward(dy)
+        layer.zero_grad(); xx = x.clone().requires_grad_(); y2 = layer(xx, padding_mask=mask); y2.backward(dy)
         same = torch.equal(y2, outs['1'][0]) and torch.equal(layer.experts.linear_fc1.weight.grad, outs['1'][3])
         t = torch.tensor([0 if same else 1], device=dev)
         if world>1: dist.all_reduce(t)

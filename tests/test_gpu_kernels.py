@@ -33,7 +33,7 @@ def test_gemm_nt(M, N, K, bn):
     assert rel(gemm.mm_nt(x, w, out_dtype=torch.float32, force_bn=bn), ref) < 1e-5
 
 
-@pytest.mark.parametrize('M,N,K', [(128, 256, 64), (1000, 776, 520), (2048, 1024, 4096)])
+@pytest.mark.parametrize('M,N,K', [(128, 256, 64), (1000, 776, 520), (2048, 1024, 4096), (264, 136, 1096)])
 def test_gemm_nn_tn(M, N, K):
     from mcore_bridge_b200.ops import gemm
     torch.manual_seed(1)
@@ -227,7 +227,9 @@ def test_bf16_model_matches_fp32_reference_model():
 
 @pytest.mark.parametrize('T,nq,nkv,d,segs', [(256, 2, 1, 128, [256]), (300, 4, 2, 128, [100, 200]),
                                              (1000, 4, 4, 64, [77, 500, 423]), (1536, 4, 1, 128, [512, 1, 1023]),
-                                             (2048, 8, 2, 128, [700, 1348])])
+                                             (2048, 8, 2, 128, [700, 1348]),
+                                             # T not a multiple of the 128-row tile together with 8 query heads per kv head
+                                             (1100, 8, 1, 128, [333, 767])])
 def test_attention_kernels(T, nq, nkv, d, segs):
     """Forward (two-pass softmax) and backward (delta, dQ, dK/dV kernels) against fp32 masked-softmax attention."""
     from mcore_bridge_b200.ops import attention as A
@@ -605,3 +607,26 @@ def test_router_gate_on_tensor_cores_matches_fp32_linear():
     d2 = torch.cat([hi, (dl - hi.float()).to(torch.bfloat16)], dim=1)
     dx_split = gemm.mm_nn(d2, torch.cat([w.detach(), w.detach()], 0), out_dtype=torch.float32)
     assert (dx_split.double() - dx_fp32).norm() < 0.05 * (hi_only - dx_fp32).norm()
+
+
+def test_router_kernel_padding_mask_keeps_padded_tokens_out_of_the_statistics():
+    """Padded tokens are routed like the others (probabilities and indices unchanged) but are not counted: the
+    per-expert token counts and score sums cover the valid tokens only."""
+    from mcore_bridge_b200.layers import moe_fused as F
+    torch.manual_seed(10)
+    T, E, k = 600, 64, 4
+    logits = torch.randn(T, E, device=DEV) * 2
+    valid = (torch.rand(T, device=DEV) > 0.2)
+    out = {}
+    for name, v in (('all', None), ('masked', valid.to(torch.uint8))):
+        probs_out = torch.empty(T, k, device=DEV)
+        idx_out = torch.empty(T, k, dtype=torch.int32, device=DEV)
+        counts = torch.empty(E, dtype=torch.int32, device=DEV)
+        probs, idx, ssum = F._RouterFn.apply(logits.clone(), None, v, k, False, True, None, None, 1.0, probs_out, idx_out,
+                                             counts)
+        out[name] = (probs.clone(), idx.clone(), ssum.clone(), counts.clone())
+    assert torch.equal(out['all'][1], out['masked'][1]) and torch.equal(out['all'][0], out['masked'][0])
+    ref_counts = torch.bincount(out['all'][1][valid].reshape(-1).long(), minlength=E)
+    assert torch.equal(out['masked'][3].long(), ref_counts)
+    ref_sum = torch.softmax(logits, dim=-1)[valid].sum(0)
+    assert rel(out['masked'][2], ref_sum) < 1e-4
