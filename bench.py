@@ -515,16 +515,16 @@ def stage2(args) -> int:
 
     from mcore_bridge_b200.parallel import state as ps
     world, rank = int(os.environ['WORLD_SIZE']), int(os.environ['RANK'])
-    torch.cuda.set_device(int(os.environ.get('LOCAL_RANK', '0')))
-    # a rendezvous store of its own (rank 0 hosts it on the port chosen by the first half): the launcher's store still
-    # holds the keys of the first initialisation
     with open(args.stage2) as f:
         stage1 = json.load(f)
-    store = dist.TCPStore(os.environ.get('MASTER_ADDR', '127.0.0.1'), int(stage1['port']), world,
-                          is_master=(rank == 0), timeout=timedelta(seconds=600))
-    ps.init_distributed(store=store)
     error = False
     try:
+        torch.cuda.set_device(int(os.environ.get('LOCAL_RANK', '0')))
+        # a rendezvous store of its own (rank 0 hosts it on the port chosen by the first half): the launcher's store
+        # still holds the keys of the first initialisation
+        store = dist.TCPStore(os.environ.get('MASTER_ADDR', '127.0.0.1'), int(stage1['port']), world,
+                              is_master=(rank == 0), timeout=timedelta(seconds=600))
+        ps.init_distributed(store=store)
         sec = run_config(args, model='qwen3_30b_a3b', parallelism='ep', steps=args.secondary_steps,
                          warmup=min(3, max(args.warmup, 3)), seq_len=4096, seqs_per_gpu=16, mbs=2, packed=False,
                          tol=3e-2)

@@ -16,7 +16,7 @@ from torch import nn
 from ..ops.attention import attention
 from ..ops.rope import qkv_split_norm_rope
 from ..parallel import state as ps
-from .context import ForwardContext
+from .context import ForwardContext, layer_cp_comm_type
 from .linear import ColumnParallelLinear, LayerNormColumnParallelLinear, RowParallelLinear
 from .norm import Norm
 
@@ -28,6 +28,7 @@ class CoreAttention(nn.Module):
         self.config = config
         self.window = window
         self.scale = scale
+        self.cp_comm_type = layer_cp_comm_type(config, layer_number)
         if config.softmax_type == 'learnable':
             self.softmax_offset = nn.Parameter(torch.zeros(num_heads_local, dtype=config.params_dtype))
             self.softmax_offset.tensor_model_parallel = ps.get_world_size('tp') > 1
@@ -43,7 +44,8 @@ class CoreAttention(nn.Module):
         cp = ps.get_world_size('cp')
         if cp > 1:
             from ..parallel.context_parallel import cp_attention as ring_attention
-            return ring_attention(q, k, v, ctx, scale=self.scale, window=self.window, sinks=sinks)
+            return ring_attention(q, k, v, ctx, scale=self.scale, window=self.window, sinks=sinks,
+                                  comm_type=self.cp_comm_type)
         return attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, causal=True, scale=self.scale, window=self.window,
                          sinks=sinks, seq_start=ctx.seq_start)
 

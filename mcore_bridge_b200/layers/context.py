@@ -34,3 +34,12 @@ class ForwardContext:
     input_ids: Optional[torch.Tensor] = None       # hash-routed MoE layers look at the ids
     extra: Dict[str, Any] = field(default_factory=dict)
     rope_tables: Dict[str, Any] = field(default_factory=dict)  # alternative tables (sliding / compressed / indexer)
+
+
+def layer_cp_comm_type(config, layer_number: int) -> str:
+    """``cp_comm_type`` of one layer (1-based ``layer_number``): a string applies to every layer, a list gives one
+    entry per layer (parity: reference ``src/mcore_bridge/model/modules/transformer_layer.py:90-96``)."""
+    t = getattr(config, 'cp_comm_type', 'p2p') or 'p2p'
+    if isinstance(t, (list, tuple)):
+        t = t[min(max(layer_number, 1), len(t)) - 1] if t else 'p2p'
+    return str(t)

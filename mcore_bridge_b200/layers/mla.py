@@ -116,6 +116,8 @@ class MLASelfAttention(nn.Module):
         super().__init__()
         self.config = config
         self.layer_number = layer_number
+        from .context import layer_cp_comm_type
+        self.cp_comm_type = layer_cp_comm_type(config, layer_number)
         cfg = config
         tp = ps.get_world_size('tp')
         self.nh = cfg.num_attention_heads
@@ -187,7 +189,8 @@ class MLASelfAttention(nn.Module):
         elif ps.get_world_size('cp') > 1:
             # this rank holds two zig-zag chunks of every sequence: keys / values are exchanged over the group
             from ..parallel.context_parallel import cp_attention as ring_attention
-            o = ring_attention(q.contiguous(), k.contiguous(), v, ctx, scale=self.scale)
+            o = ring_attention(q.contiguous(), k.contiguous(), v, ctx, scale=self.scale,
+                               comm_type=self.cp_comm_type)
         else:
             o = attention(q.contiguous(), k.contiguous(), v, ctx.cu_seqlens, ctx.max_seqlen, causal=True,
                           scale=self.scale)

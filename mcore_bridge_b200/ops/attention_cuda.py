@@ -183,6 +183,37 @@ class _AttnRangesFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None, dsinks
 
 
+def fwd_ranges_raw(q, k, v, k_lo, k_hi, scale: float):
+    """One forward launch without autograd: ``(o [T, nq, d], lse [nq, T])`` of the queries over their key ranges in
+    ``k`` / ``v`` (rows with an empty range: ``o = 0``, ``lse = -inf``).  Building block of ring attention."""
+    T, nq, d = q.shape
+    o = torch.empty_like(q)
+    lse = torch.empty((nq, T), dtype=torch.float32, device=q.device)
+    rc = _lib.lib().mcb_attn_fwd_ranges(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(k_lo), _lib.ptr(k_hi), None,
+                                        _lib.ptr(o), _lib.ptr(lse), _int(T), _int(k.shape[0]), _int(nq),
+                                        _int(k.shape[1]), _int(d), _f(scale), _lib.ptr(_lib.status_word(q.device)),
+                                        _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_attn_fwd_ranges')
+    return o, lse
+
+
+def bwd_ranges_raw(q, k, v, o, do, lse, delta, k_lo, k_hi, q_lo, q_hi, scale: float):
+    """One backward launch without autograd, with the log-sum-exp and ``delta = rowsum(o * do)`` of the *whole*
+    attention given (``[nq, T]`` fp32): ``(dq, dk, dv)`` of this block of keys."""
+    T, nq, d = q.shape
+    Tk, nkv = k.shape[0], k.shape[1]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    splits = _dkv_splits(Tk, nq, nkv, q.device)
+    partial = torch.empty((2, splits, Tk, nkv, d), dtype=torch.float32, device=q.device) if splits > 1 else None
+    rc = _lib.lib().mcb_attn_bwd_ranges(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta), _int(1),
+        _lib.ptr(k_lo), _lib.ptr(k_hi), _lib.ptr(q_lo), _lib.ptr(q_hi), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+        _int(T), _int(Tk), _int(nq), _int(nkv), _int(d), _f(scale), _lib.ptr(partial), _int(splits),
+        _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, 'mcb_attn_bwd_ranges')
+    return dq, dk, dv
+
+
 def attention_ranges(q, k, v, k_lo, k_hi, q_lo, q_hi, scale: Optional[float] = None,
                      sinks: Optional[torch.Tensor] = None):
     """Returns ``(o [T, nq, d], lse [nq, T])``; all four range tensors are int32 on the device (``k_hi`` / ``q_lo`` /

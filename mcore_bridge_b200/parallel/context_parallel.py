@@ -77,6 +77,8 @@ class CpLayout:
     q_hi: torch.Tensor              # int32 [T]: last one (empty range where none can)
     cu_local: torch.Tensor          # int32 [B+1]: sequence boundaries among the local tokens
     cu_full: torch.Tensor           # int32 [B+1]
+    ring_lo: torch.Tensor           # int32 [cp, T_local]: first key, in rank j's local order, local query i sees
+    ring_hi: torch.Tensor           # int32 [cp, T_local]: last one (lo > hi: none)
 
 
 def compute_layout(cu_seqlens: Optional[torch.Tensor], t_local: int, cp: int, rank: int, device) -> CpLayout:
@@ -114,8 +116,19 @@ def compute_layout(cu_seqlens: Optional[torch.Tensor], t_local: int, cp: int, ra
     q_lo = torch.where(none, torch.ones_like(q_lo), q_lo).to(torch.int32)
     q_hi = torch.where(none, torch.zeros_like(q_hi), q_hi).to(torch.int32)
     cu_local = torch.div(cu, cp, rounding_mode='floor').to(torch.int32)
-    return CpLayout(cp, rank, t_local, gather_index, scatter_index, q_stream, (q_stream - S[q_stream]), k_lo, k_hi, q_lo,
-                    q_hi, cu_local, cu.to(torch.int32))
+    # Ring steps: rank j holds, per sequence, the chunks j and 2cp-1-j back to back (h tokens each, starting at local
+    # index L0).  A query at in-sequence position rho sees a prefix of chunk j, and, only once chunk j is wholly
+    # visible, a prefix of chunk 2cp-1-j: one contiguous range of rank j's local tokens.
+    q_rel = q_stream - S[q_stream]
+    hq, lq = h[q_stream], L0[q_stream]
+    j = torch.arange(cp, device=device)[:, None]
+    n1 = (q_rel[None, :] - j * hq[None, :] + 1).clamp(min=0).minimum(hq[None, :])
+    n2 = (q_rel[None, :] - (2 * cp - 1 - j) * hq[None, :] + 1).clamp(min=0).minimum(hq[None, :])
+    cnt = n1 + n2
+    ring_lo = torch.where(cnt > 0, lq[None, :].expand(cp, -1), torch.ones_like(cnt)).to(torch.int32).contiguous()
+    ring_hi = torch.where(cnt > 0, lq[None, :] + cnt - 1, torch.zeros_like(cnt)).to(torch.int32).contiguous()
+    return CpLayout(cp, rank, t_local, gather_index, scatter_index, q_stream, q_rel, k_lo, k_hi, q_lo, q_hi, cu_local,
+                    cu.to(torch.int32), ring_lo, ring_hi)
 
 
 def get_layout(ctx, t_local: int, device) -> CpLayout:
@@ -236,11 +249,196 @@ def stream_index_of_local_tokens(ctx, device, t_local: Optional[int] = None) -> 
     return get_layout(ctx, t_local, device).q_stream
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# ring form (cp_comm_type = 'p2p'): one chunk of keys / values per step, the next chunk fetched behind the kernel
+# ---------------------------------------------------------------------------------------------------------------
+def _range_mask(lo: torch.Tensor, hi: torch.Tensor, tk: int) -> torch.Tensor:
+    pos = torch.arange(tk, device=lo.device)[None, :]
+    return (pos >= lo[:, None].long()) & (pos <= hi[:, None].long())        # [T, Tk]
+
+
+def _partial_fwd_ref(q, k, v, lo, hi, scale):
+    """fp32 attention of every query over its key range in this chunk -> (o [T, nq, d] un-normalised by nothing:
+    softmax within the chunk, lse [nq, T]); rows with an empty range give o = 0, lse = -inf."""
+    nq, nkv = q.shape[1], k.shape[1]
+    kf = k.float().repeat_interleave(nq // nkv, dim=1)
+    vf = v.float().repeat_interleave(nq // nkv, dim=1)
+    sc = torch.einsum('ihd,jhd->hij', q.float(), kf) * scale
+    sc = sc.masked_fill(~_range_mask(lo, hi, k.shape[0])[None], float('-inf'))
+    lse = torch.logsumexp(sc, dim=-1)
+    p = torch.exp(sc - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[..., None])
+    p = torch.where(torch.isinf(lse)[..., None], torch.zeros_like(p), p)
+    return torch.einsum('hij,jhd->ihd', p, vf), lse
+
+
+def _partial_bwd_ref(q, k, v, do, lse, delta, lo, hi, scale):
+    """Gradients of one chunk given the final log-sum-exp and delta = rowsum(o * do): (dq, dk, dv) in fp32."""
+    nq, nkv = q.shape[1], k.shape[1]
+    g = nq // nkv
+    kf = k.float().repeat_interleave(g, dim=1)
+    vf = v.float().repeat_interleave(g, dim=1)
+    sc = torch.einsum('ihd,jhd->hij', q.float(), kf) * scale
+    p = torch.exp(sc - lse[..., None]).masked_fill(~_range_mask(lo, hi, k.shape[0])[None], 0.0)
+    dof = do.float()
+    dv = torch.einsum('hij,ihd->jhd', p, dof)
+    ds = p * (torch.einsum('ihd,jhd->hij', dof, vf) - delta[..., None]) * scale
+    dq = torch.einsum('hij,jhd->ihd', ds, kf)
+    dk = torch.einsum('hij,ihd->jhd', ds, q.float())
+    tk = k.shape[0]
+    return dq, dk.view(tk, nkv, g, -1).sum(2), dv.view(tk, nkv, g, -1).sum(2)
+
+
+class _ChunkFetcher:
+    """Hands out the keys / values of the CP ranks one chunk at a time.  On a GPU with peer-mapped memory every rank
+    publishes its K / V in a symmetric buffer and the copy engine pulls the next rank's chunk on a side stream while
+    the attention kernel works on the current one; elsewhere the chunks come from one ``torch.distributed``
+    all-gather."""
+
+    _side = {}
+    _epoch = 0
+
+    def __init__(self, k: torch.Tensor, v: torch.Tensor):
+        self.cp, self.rank = ps.get_world_size('cp'), ps.get_rank_in('cp')
+        self.k, self.v = k.contiguous(), v.contiguous()
+        self.nk, self.nv = self.k.numel(), self.v.numel()
+        self.peer = _fused_exchange(k.device)
+        self.pending = None
+        if self.peer:
+            n = self.nk + self.nv
+            _ChunkFetcher._epoch += 1
+            self.base = (_ChunkFetcher._epoch & 1) * n        # two halves: a rank republishes only two calls later
+            self.ws, flat = _workspace('ring_kv', 2 * n, k.dtype, k.device)
+            mine = flat[self.base:self.base + n]
+            mine[:self.nk].view_as(self.k).copy_(self.k)
+            mine[self.nk:].view_as(self.v).copy_(self.v)
+            self.ws.handle.barrier(channel=0)                  # every rank's chunk is in place (stream-ordered)
+            dev = k.device.index
+            if dev not in _ChunkFetcher._side:
+                _ChunkFetcher._side[dev] = torch.cuda.Stream(device=k.device)
+            self.side = _ChunkFetcher._side[dev]
+            self.published = torch.cuda.Event()
+            self.published.record()
+        else:
+            group = ps.get_group('cp')
+            self.kg = torch.empty((self.cp, *self.k.shape), dtype=k.dtype, device=k.device)
+            self.vg = torch.empty((self.cp, *self.v.shape), dtype=v.dtype, device=v.device)
+            dist.all_gather_into_tensor(self.kg.view(-1, *self.k.shape[1:]), self.k, group=group)
+            dist.all_gather_into_tensor(self.vg.view(-1, *self.v.shape[1:]), self.v, group=group)
+
+    def prefetch(self, j: int):
+        """Starts bringing rank ``j``'s chunk into local memory (no-op for the own chunk and off the peer path)."""
+        if not self.peer or j == self.rank:
+            return
+        from .dp_comm import FLAG_BYTES
+        n = self.nk + self.nv
+        es = self.k.element_size()
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(self.published)
+            buf = torch.empty(n, dtype=self.k.dtype, device=self.k.device)
+            src = self.ws.handle.get_buffer(j, (n,), self.k.dtype, FLAG_BYTES // es + self.base)
+            buf.copy_(src, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        buf.record_stream(main)
+        self.pending = (j, buf, ev)
+
+    def get(self, j: int):
+        if j == self.rank:
+            return self.k, self.v
+        if not self.peer:
+            return self.kg[j], self.vg[j]
+        if self.pending is None or self.pending[0] != j:
+            self.prefetch(j)
+        _, buf, ev = self.pending
+        self.pending = None
+        torch.cuda.current_stream().wait_event(ev)
+        return buf[:self.nk].view_as(self.k), buf[self.nk:].view_as(self.v)
+
+
+class _RingAttnFn(torch.autograd.Function):
+    """Context-parallel attention one source rank at a time: step ``s`` attends to the keys / values of rank
+    ``(r - s) mod cp`` (a contiguous range of that rank's tokens per query, ``CpLayout.ring_lo / ring_hi``) while the
+    next rank's chunk is on its way; the partial results are merged through their log-sum-exp.  Only the local K / V
+    are kept for the backward pass, which fetches the chunks again, recomputes the probabilities from the final
+    log-sum-exp and returns the key / value gradients through the reduce-scatter of the all-gather form."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, lay: CpLayout, scale: float, use_kernel: bool):
+        cp, r = lay.cp, lay.rank
+        T, nq, d = q.shape
+        fetch = _ChunkFetcher(k, v)
+        o_acc = torch.zeros((T, nq, v.shape[-1]), dtype=torch.float32, device=q.device)
+        lse_acc = torch.full((nq, T), float('-inf'), dtype=torch.float32, device=q.device)
+        qc = q.contiguous()
+        for s in range(cp):
+            j = (r - s) % cp
+            if s + 1 < cp:
+                fetch.prefetch((r - s - 1) % cp)
+            kj, vj = fetch.get(j) if s else (fetch.k, fetch.v)
+            if use_kernel:
+                from ..ops import attention_cuda as ac
+                o_s, lse_s = ac.fwd_ranges_raw(qc, kj, vj, lay.ring_lo[j], lay.ring_hi[j], scale)
+                o_s = o_s.float()
+            else:
+                o_s, lse_s = _partial_fwd_ref(qc, kj, vj, lay.ring_lo[j], lay.ring_hi[j], scale)
+            new = torch.logaddexp(lse_acc, lse_s)
+            safe = torch.where(torch.isinf(new), torch.zeros_like(new), new)
+            w_old = torch.exp(lse_acc - safe).t()[..., None]       # exp(-inf) = 0 for rows that had nothing yet
+            w_new = torch.exp(lse_s - safe).t()[..., None]
+            o_acc = o_acc * w_old + o_s * w_new
+            lse_acc = new
+        o = o_acc.to(q.dtype)
+        ctx.save_for_backward(qc, fetch.k, fetch.v, o, lse_acc)
+        ctx.lay, ctx.scale, ctx.use_kernel = lay, scale, use_kernel
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        lay, scale = ctx.lay, ctx.scale
+        cp, r = lay.cp, lay.rank
+        T = q.shape[0]
+        do = do.contiguous()
+        delta = (o.float() * do.float()).sum(-1).t().contiguous()              # [nq, T]
+        fetch = _ChunkFetcher(k, v)
+        dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        dk_rm = torch.empty((cp, *k.shape), dtype=torch.float32, device=q.device)
+        dv_rm = torch.empty((cp, *v.shape), dtype=torch.float32, device=q.device)
+        if ctx.use_kernel:
+            all_lo = torch.zeros(k.shape[0], dtype=torch.int32, device=q.device)
+            all_hi = torch.full((k.shape[0],), T - 1, dtype=torch.int32, device=q.device)
+        for s in range(cp):
+            j = (r - s) % cp
+            if s + 1 < cp:
+                fetch.prefetch((r - s - 1) % cp)
+            kj, vj = fetch.get(j) if s else (fetch.k, fetch.v)
+            if ctx.use_kernel:
+                from ..ops import attention_cuda as ac
+                dq_s, dk_s, dv_s = ac.bwd_ranges_raw(q, kj, vj, o, do, lse, delta, lay.ring_lo[j], lay.ring_hi[j],
+                                                     all_lo, all_hi, scale)
+            else:
+                dq_s, dk_s, dv_s = _partial_bwd_ref(q, kj, vj, do, lse, delta, lay.ring_lo[j], lay.ring_hi[j], scale)
+            dq += dq_s.float()
+            dk_rm[j].copy_(dk_s)
+            dv_rm[j].copy_(dv_s)
+        dk, dv = _reduce_scatter_kv_grads(dk_rm.view(-1, *k.shape[1:]), dv_rm.view(-1, *v.shape[1:]), k.dtype)
+        return dq.to(q.dtype), dk, dv, None, None, None
+
+
 def cp_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ctx, scale: Optional[float] = None,
-                 window=None, sinks=None) -> torch.Tensor:
-    """``q/k/v`` hold this rank's tokens ``[T_local, heads, d]``; returns ``[T_local, nq, dv]``."""
+                 window=None, sinks=None, comm_type: Optional[str] = None) -> torch.Tensor:
+    """``q/k/v`` hold this rank's tokens ``[T_local, heads, d]``; returns ``[T_local, nq, dv]``.  ``comm_type`` is the
+    layer's ``cp_comm_type``: ``'p2p'`` (the reference's default) runs the ring form, anything else (``'allgather'``,
+    ``'a2a'``, ...) the all-gather form; masks the ring does not cover (window, sinks) use the all-gather form."""
     lay = get_layout(ctx, q.shape[0], q.device)
     from ..ops import attention_cuda as ac
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    if (comm_type or 'p2p') == 'p2p' and window is None and sinks is None and k.shape[-1] == v.shape[-1]:
+        kernel = ac.ranges_supported(q, k, v)
+        if kernel or not q.is_cuda:
+            return _RingAttnFn.apply(q, k, v, lay, float(scale), kernel)
     if window is None and sinks is None and ac.ranges_supported(q, k, v):
         kg, vg = _GatherKV.apply(k, v)
         k_full, v_full = kg.index_select(0, lay.gather_index), vg.index_select(0, lay.gather_index)

@@ -630,3 +630,58 @@ def test_router_kernel_padding_mask_keeps_padded_tokens_out_of_the_statistics():
     assert torch.equal(out['masked'][3].long(), ref_counts)
     ref_sum = torch.softmax(logits, dim=-1)[valid].sum(0)
     assert rel(out['masked'][2], ref_sum) < 1e-4
+
+
+@pytest.mark.parametrize('cp', [2, 4])
+def test_ring_attention_steps_on_the_kernels(cp):
+    """The ring form of context-parallel attention with the ranks emulated on one GPU: per source rank one forward
+    launch over a contiguous key range of that rank's tokens, partial results merged through their log-sum-exp; the
+    backward launches get the final log-sum-exp and delta.  Output, dQ and the summed dK / dV against the reference."""
+    from mcore_bridge_b200.ops import attention_cuda as ac
+    from mcore_bridge_b200.ops.attention import attention_ref
+    from mcore_bridge_b200.parallel.context_parallel import compute_layout
+    torch.manual_seed(6)
+    nq, nkv, d = 4, 2, 128
+    lens = [8 * cp * 20, 8 * cp * 3, 8 * cp * 33]
+    T = sum(lens)
+    tl = T // cp
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    q = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(T, nkv, d, device=DEV, dtype=torch.bfloat16)
+    do = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16)
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    ref = attention_ref(qr, kr, vr, cu, cu)
+    gq, gk, gv = torch.autograd.grad(ref, (qr, kr, vr), do.float())
+    lays = [compute_layout(cu, tl, cp, r, torch.device(DEV)) for r in range(cp)]
+    k_loc = [k[lay.q_stream].contiguous() for lay in lays]          # what each rank holds, in its local order
+    v_loc = [v[lay.q_stream].contiguous() for lay in lays]
+    dk_sum = [torch.zeros(tl, nkv, d, device=DEV) for _ in range(cp)]
+    dv_sum = [torch.zeros(tl, nkv, d, device=DEV) for _ in range(cp)]
+    scale = d ** -0.5
+    all_lo = torch.zeros(tl, dtype=torch.int32, device=DEV)
+    all_hi = torch.full((tl,), tl - 1, dtype=torch.int32, device=DEV)
+    for r, lay in enumerate(lays):
+        ql, dol = q[lay.q_stream].contiguous(), do[lay.q_stream].contiguous()
+        o_acc = torch.zeros(tl, nq, d, device=DEV)
+        lse_acc = torch.full((nq, tl), float('-inf'), device=DEV)
+        for s in range(cp):
+            j = (r - s) % cp
+            o_s, lse_s = ac.fwd_ranges_raw(ql, k_loc[j], v_loc[j], lay.ring_lo[j], lay.ring_hi[j], scale)
+            new = torch.logaddexp(lse_acc, lse_s)
+            o_acc = o_acc * torch.exp(lse_acc - new).t()[..., None] + o_s.float() * torch.exp(lse_s - new).t()[..., None]
+            lse_acc = new
+        o = o_acc.to(torch.bfloat16)
+        assert rel(o, ref[lay.q_stream]) < 2e-2
+        delta = (o.float() * dol.float()).sum(-1).t().contiguous()
+        dq = torch.zeros(tl, nq, d, device=DEV)
+        for s in range(cp):
+            j = (r - s) % cp
+            dq_s, dk_s, dv_s = ac.bwd_ranges_raw(ql, k_loc[j], v_loc[j], o, dol, lse_acc, delta, lay.ring_lo[j],
+                                                 lay.ring_hi[j], all_lo, all_hi, scale)
+            dq += dq_s.float()
+            dk_sum[j] += dk_s.float()
+            dv_sum[j] += dv_s.float()
+        assert rel(dq, gq[lay.q_stream]) < 3e-2
+    for j, lay in enumerate(lays):
+        assert rel(dk_sum[j], gk[lay.q_stream]) < 3e-2 and rel(dv_sum[j], gv[lay.q_stream]) < 3e-2
