@@ -215,7 +215,8 @@ class ModelConfig:
     recompute_modules: Optional[List[str]] = None
     cpu_offloading: bool = False                      # saved activations of the first layers live in pinned host memory
     cpu_offloading_num_layers: Optional[int] = None   # how many leading layers of a stage offload (default: all)
-    fine_grained_activation_offloading: bool = False  # per-module offload lists: not implemented (rejected below)
+    fine_grained_activation_offloading: bool = False  # offload the saved tensors of the sub-blocks in offload_modules
+    offload_modules: Optional[List[str]] = None       # attn_norm / core_attn / attn_proj / mlp_norm / moe_act / expert_fc1 ...
 
     # initialisation
     perform_initialization: bool = False
@@ -245,9 +246,6 @@ class ModelConfig:
         self._format_config()
         # options that exist in the reference's config but have no implementation here are refused instead of being
         # silently ignored
-        if self.fine_grained_activation_offloading:
-            raise NotImplementedError('fine_grained_activation_offloading is not implemented; use cpu_offloading '
-                                      '(whole-layer activation offload) or activation recompute')
         if self.experimental_attention_variant == 'dsv4_hybrid' or any(self.csa_compress_ratios or []):
             raise NotImplementedError(
                 'compressed sparse attention (DeepSeek-V4 hybrid attention) is not implemented: the reference takes it '

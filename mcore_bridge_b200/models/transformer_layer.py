@@ -145,14 +145,33 @@ class TransformerLayer(nn.Module):
         return (self.training and cfg.recompute_granularity == 'selective' and name in (cfg.recompute_modules or ())
                 and torch.is_grad_enabled())
 
+    # names of ``offload_modules`` that belong to the attention block and to the feed-forward block
+    _ATTN_OFFLOAD = frozenset({'attn_norm', 'qkv_linear', 'core_attn', 'attn_proj', 'self_attn'})
+    _MLP_OFFLOAD = frozenset({'mlp_norm', 'mlp', 'moe', 'moe_act', 'expert_fc1', 'expert_fc2', 'shared_expert', 'dense_mlp'})
+
+    def _offload(self, names):
+        """``fine_grained_activation_offloading``: while a sub-block named in ``offload_modules`` runs, the tensors it
+        saves for backward go to (pinned) host memory and come back when its backward runs.  The granularity is the
+        sub-block (attention incl. its norm and projections / feed-forward incl. its norm), the finest at which this
+        layer keeps activations: the fused norm-linear and gated-activation blocks save one tensor each (reference
+        ``src/mcore_bridge/model/modules/transformer_layer.py:197-209``)."""
+        import contextlib
+        cfg = self.config
+        if (cfg.fine_grained_activation_offloading and self.training and torch.is_grad_enabled()
+                and names & set(cfg.offload_modules or ())):
+            return torch.autograd.graph.save_on_cpu(pin_memory=torch.cuda.is_available())
+        return contextlib.nullcontext()
+
     def forward(self, hidden: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
         from torch.utils.checkpoint import checkpoint
         if self._selective('self_attn'):
             hidden = checkpoint(self._attention, hidden, ctx, use_reentrant=False)
         else:
-            hidden = self._attention(hidden, ctx)
+            with self._offload(self._ATTN_OFFLOAD):
+                hidden = self._attention(hidden, ctx)
         if self.config.mlp_padding_free and ctx.extra.get('full_padding_mask') is not None:
             return self._mlp_padding_free(hidden, ctx)
         if self._selective('moe' if self.is_moe else 'mlp'):
             return checkpoint(self._mlp, hidden, ctx, use_reentrant=False)
-        return self._mlp(hidden, ctx)
+        with self._offload(self._MLP_OFFLOAD):
+            return self._mlp(hidden, ctx)

@@ -116,9 +116,40 @@ def test_cpu_offloading_gives_the_same_gradients():
         assert torch.equal(grads[0][n], grads[1][n]), n
 
 
+def test_fine_grained_offloading_moves_saved_tensors_and_keeps_gradients():
+    """``offload_modules`` names sub-blocks whose saved tensors live on the host between forward and backward: the
+    pack hook runs only while a named sub-block runs, and gradients do not change."""
+    from mcore_bridge_b200 import get_mcore_model
+    from mcore_bridge_b200.train.trainer import init_weights
+    ids = torch.randint(0, 1024, (2, 48), generator=torch.Generator().manual_seed(0))
+    grads, packed = [], []
+    for mods in (None, ['mlp_norm', 'moe_act'], ['core_attn']):
+        cfg = _cfg(fine_grained_activation_offloading=mods is not None, offload_modules=mods)
+        model = get_mcore_model(cfg)[0].train()
+        init_weights(model, 0.05, 1)
+        seen = []
+        orig = torch.autograd.graph.save_on_cpu
+
+        class Spy(orig):
+            def __init__(self, *a, **k):
+                seen.append(1)
+                super().__init__(*a, **k)
+        torch.autograd.graph.save_on_cpu = Spy
+        try:
+            model(ids, labels=ids).mean().backward()
+        finally:
+            torch.autograd.graph.save_on_cpu = orig
+        packed.append(len(seen))
+        grads.append({n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None})
+    n_layers = _cfg().num_layers
+    assert packed == [0, n_layers, n_layers]          # one sub-block per layer each time
+    for g in grads[1:]:
+        assert g.keys() == grads[0].keys()
+        for n in g:
+            assert torch.equal(g[n], grads[0][n]), n
+
+
 def test_unbuilt_options_are_refused():
     import pytest
-    with pytest.raises(NotImplementedError, match='fine_grained'):
-        _cfg(fine_grained_activation_offloading=True)
     with pytest.raises(NotImplementedError, match='compressed sparse attention'):
         _cfg(experimental_attention_variant='dsv4_hybrid')
