@@ -49,7 +49,8 @@ def parse_args():
     ap.add_argument('--seq-len', type=int, default=0, help='0: the model\'s benchmark length (8192 dense, 4096 MoE)')
     ap.add_argument('--seqs-per-gpu', type=int, default=0,
                     help='sequences per GPU per step, weak scaling (0: 8 for the dense model, 16 for the MoE model)')
-    ap.add_argument('--layers', type=int, default=None, help='debug only: override the layer count (marks the run invalid)')
+    ap.add_argument('--layers', type=int, default=None,
+                    help='debug only: override the layer count (marks the run invalid)')
     ap.add_argument('--parallelism', default='tp', choices=['tp', 'dp', 'ep'],
                     help="'ep': expert parallel over all GPUs with data parallel dense parameters (MoE models)")
     ap.add_argument('--no-e2e', action='store_true')
@@ -425,7 +426,8 @@ def run_config(args, *, model: str, parallelism: str, steps: int, warmup: int, s
                    'optimizer': 'AdamW, fp32 master weights and moments, fp32 gradient accumulation',
                    'lora': (f'rank {args.lora_rank}, alpha {2 * args.lora_rank}, all linear layers'
                             if args.lora_rank > 0 else None),
-                   'l2': 'working set per step (parameters, gradients, optimizer state: > 100 GB) exceeds the 126 MB L2; no flush needed',
+                   'l2': ('working set per step (parameters, gradients, optimizer state: > 100 GB) exceeds the 126 MB '
+                          'L2; no flush needed'),
                    'loss': trainer.last_metrics.get('loss')},
         'clocks': clocks, 'e2e': e2e, 'gpu_launches': launches,
     }

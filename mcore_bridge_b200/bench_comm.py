@@ -88,7 +88,8 @@ def moe_main(a):
     k, F = cfg.moe_router_topk, cfg.moe_ffn_hidden_size
     flops = 3 * 2.0 * T * k * H * 3 * F          # fc1 (2F wide) + fc2, forward + two backward GEMMs each
     res['compute_us'] = round(flops / (GEMM_TFLOPS * 1e6), 1)
-    res['link_us'] = round(4 * T * k * H * 2 * (world - 1) / world / (LINK_GBS * 1e3), 1)   # dispatch + combine, fwd + bwd
+    # dispatch + combine, forward + backward
+    res['link_us'] = round(4 * T * k * H * 2 * (world - 1) / world / (LINK_GBS * 1e3), 1)
     if rank == 0:
         print(json.dumps({'op': 'moe_layer fwd+bwd', 'ep': world, 'tokens_per_rank': T} | res))
     if world > 1:
@@ -104,7 +105,8 @@ def main():
     ap.add_argument('--ffn', type=int, default=12288)
     ap.add_argument('--iters', type=int, default=20)
     ap.add_argument('--moe', action='store_true', help='time the expert-parallel MoE layer instead of the TP kernels')
-    ap.add_argument('--experts', type=int, default=128, help='--moe: number of experts (the fused dispatch + GEMM kernel '
+    ap.add_argument('--experts', type=int, default=128,
+                    help='--moe: number of experts (the fused dispatch + GEMM kernel '
                     'takes at most 64 per rank, so a single-GPU run of it needs --experts 64)')
     ap.add_argument('--profile', action='store_true',
                     help='--moe: also print the per-kernel device times of three iterations (torch.profiler)')

@@ -18,7 +18,8 @@ def _peaks():
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 'MEASURED_PEAKS.json')
     if os.path.exists(p):
         d = json.load(open(p))
-        return d.get('bf16_tflops', 1590.0), d.get('bf16_tflops_sustained', 1400.0), d.get('hbm_gbs', 6650.0), 'measured'
+        return (d.get('bf16_tflops', 1590.0), d.get('bf16_tflops_sustained', 1400.0), d.get('hbm_gbs', 6650.0),
+                'measured')
     return 1590.0, 1400.0, 6650.0, 'fallback'
 
 
@@ -57,7 +58,7 @@ def step_profile(a):
     world, rank = int(os.environ.get('WORLD_SIZE', '1')), int(os.environ.get('RANK', '0'))
     torch.cuda.set_device(int(os.environ.get('LOCAL_RANK', '0')))
     extra = {}
-    if world > 1:                      # torchrun: tensor parallel (+ sequence parallel) or expert parallel over all ranks
+    if world > 1:      # torchrun: tensor parallel (+ sequence parallel) or expert parallel over all ranks
         ps.init_distributed()
         tp = world if a.parallelism == 'tp' else 1
         ep = world if a.parallelism == 'ep' else 1
@@ -104,8 +105,9 @@ def step_profile(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('op', choices=['step-profile', 'gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'rmsnorm_bwd', 'swiglu', 'qkv_rope', 'ce', 'adam', 'attention', 'attention_bwd',
-                                  'gemm_fp8', 'quant_fp8', 'dsa_index', 'topk', 'simple_gla', 'conv1d', 'lora'])
+    ap.add_argument('op', choices=['step-profile', 'gemm', 'gemm_nn', 'gemm_tn', 'rmsnorm', 'rmsnorm_bwd', 'swiglu',
+                                  'qkv_rope', 'ce', 'adam', 'attention', 'attention_bwd', 'gemm_fp8', 'quant_fp8',
+                                  'dsa_index', 'topk', 'simple_gla', 'conv1d', 'lora'])
     ap.add_argument('--m', type=int, default=8192)
     ap.add_argument('--n', type=int, default=4096)
     ap.add_argument('--k', type=int, default=4096)

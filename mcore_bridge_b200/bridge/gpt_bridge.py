@@ -146,8 +146,10 @@ class GPTBridge:
     hf_experts_prefix = 'experts'
     hf_expert_proj_names = ('gate_proj', 'up_proj', 'down_proj')     # per-expert linear names (MiniMax: w1 / w3 / w2)
     hf_fused_gate_up = False                 # dense MLP exported as one ``gate_up_proj`` tensor (GLM-4)
-    hf_fused_experts = False                 # routed experts exported as ``experts.gate_up_proj`` / ``experts.down_proj``
-    hf_experts_transposed = False            # layout written for fused expert tensors when no checkpoint was loaded: input-major ``[E, H, 2F]`` / ``[E, F, H]``
+    # routed experts exported as ``experts.gate_up_proj`` / ``experts.down_proj``
+    hf_fused_experts = False
+    # layout written for fused expert tensors when no checkpoint was loaded: input-major ``[E, H, 2F]`` / ``[E, F, H]``
+    hf_experts_transposed = False
     hf_fused_qkv_key = None                  # e.g. 'query_key_value': one tensor laid out [all q | all k | all v]
     fp8_block_size = 128
 
@@ -904,7 +906,8 @@ class GPTBridge:
         return list(res)
 
     def export_weights(self, mg_models, target_device=None, only_master_rank: bool = False, peft_format: bool = False,
-                       adapter_name: str = 'default', converter: Optional[Callable] = None, tqdm_desc: str = 'Exporting: '):
+                       adapter_name: str = 'default', converter: Optional[Callable] = None,
+                       tqdm_desc: str = 'Exporting: '):
         self._target_device, self._only_master_rank = target_device, only_master_rank
         self._peft_format, self._adapter_name = peft_format, adapter_name
         if not isinstance(mg_models, (list, tuple)):

@@ -101,7 +101,8 @@ class ModelConfig:
     kv_channels: Optional[int] = None
     qk_layernorm: bool = False
     qk_l2_norm: bool = False
-    lean_activations: bool = True            # single-rank dense path: recompute norm / gated activation in backward instead of storing them
+    # single-rank dense path: recompute norm / gated activation in backward instead of storing them
+    lean_activations: bool = True
     qk_layernorm_full: bool = False          # q/k RMSNorm over all heads' channels at once (OLMoE, MiniMax-M2)
     post_sublayer_layernorm: bool = False    # sandwich norms after attention and MLP outputs (GLM-4)
     no_rope_freq: Optional[Union[int, str, List[int]]] = None
@@ -200,7 +201,8 @@ class ModelConfig:
     fp16: bool = False
     pipeline_dtype: Optional[torch.dtype] = None
     fp8: Optional[str] = None  # None | 'e4m3' | 'hybrid'
-    fp8_recipe: Optional[str] = None  # 'blockwise' (128x128 weights, 1x128 activations) | 'delayed' | 'tensorwise' | 'mxfp8'
+    # 'blockwise' (128x128 weights, 1x128 activations) | 'delayed' | 'tensorwise' | 'mxfp8'
+    fp8_recipe: Optional[str] = None
     fp8_param: bool = False
     fp4: Optional[str] = None
     attention_softmax_in_fp32: bool = True
@@ -216,7 +218,8 @@ class ModelConfig:
     cpu_offloading: bool = False                      # saved activations of the first layers live in pinned host memory
     cpu_offloading_num_layers: Optional[int] = None   # how many leading layers of a stage offload (default: all)
     fine_grained_activation_offloading: bool = False  # offload the saved tensors of the sub-blocks in offload_modules
-    offload_modules: Optional[List[str]] = None       # attn_norm / core_attn / attn_proj / mlp_norm / moe_act / expert_fc1 ...
+    # attn_norm / core_attn / attn_proj / mlp_norm / moe_act / expert_fc1 ...
+    offload_modules: Optional[List[str]] = None
 
     # initialisation
     perform_initialization: bool = False
@@ -321,7 +324,8 @@ class ModelConfig:
             for cfg_name, have in (('tensor_model_parallel_size', st.tp), ('pipeline_model_parallel_size', st.pp),
                                    ('context_parallel_size', st.cp), ('expert_model_parallel_size', st.ep)):
                 if getattr(self, cfg_name) != have:
-                    raise ValueError(f'{cfg_name}={getattr(self, cfg_name)} but the process groups were built with {have}')
+                    raise ValueError(f'{cfg_name}={getattr(self, cfg_name)} but the process groups were built with '
+                                     f'{have}')
         self._validate()
         if self.mcore_model_type is None:
             self.mcore_model_type = get_mcore_model_type(self.hf_model_type)

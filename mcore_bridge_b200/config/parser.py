@@ -147,7 +147,8 @@ def _window_pattern(layer_types) -> str:
 
 _DEEPSEEK_LIKE = {'deepseek', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'deepseek_v32', 'dots1', 'deepseek_v4'}
 _QK_NORM_LLM = {'qwen3', 'qwen3_moe', 'qwen3_next'}
-_QK_NORM_HF = {'qwen3_omni_moe', 'qwen3_omni', 'qwen3_vl', 'qwen3_vl_moe', 'qwen3_5', 'qwen3_5_moe', 'llavaonevision1_5'}
+_QK_NORM_HF = {'qwen3_omni_moe', 'qwen3_omni', 'qwen3_vl', 'qwen3_vl_moe', 'qwen3_5', 'qwen3_5_moe',
+               'llavaonevision1_5'}
 
 
 def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
@@ -288,7 +289,8 @@ def hf_to_mcore_config(hf_config) -> Dict[str, Any]:
     if rope_scaling.get('mrope_section') is not None:
         res['position_embedding_type'] = 'mrope'
         res['mrope_section'] = rope_scaling['mrope_section']
-        res['mrope_interleaved'] = bool(rope_scaling.get('mrope_interleaved', False) or rope_scaling.get('interleaved', False))
+        res['mrope_interleaved'] = bool(rope_scaling.get('mrope_interleaved', False)
+                                        or rope_scaling.get('interleaved', False))
     if rope_scaling and set(rope_scaling.keys()) <= {'rope_theta', 'rope_type', 'type', 'partial_rotary_factor',
                                                      'mrope_section', 'mrope_interleaved', 'interleaved'} \
             and rope_scaling.get('rope_type', rope_scaling.get('type', 'default')) == 'default':

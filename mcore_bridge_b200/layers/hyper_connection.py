@@ -11,8 +11,8 @@ a ``HyperConnection`` computes, per token and from the token's own streams, thre
   ``s'_i = post[i] * f(x) + sum_j res[i, j] * s_j``
 
 The maps come from one linear layer on the RMS-normalised, flattened streams (``mapping_proj``: ``n C -> 2 n + n^2``),
-three learnable scales (``alpha_pre``, ``alpha_post``, ``alpha_res``) and a bias.  ``pre`` uses a sigmoid, ``post`` twice
-a sigmoid (so its initial value can be 1), ``res`` a row softmax followed by the Sinkhorn iterations.
+three learnable scales (``alpha_pre``, ``alpha_post``, ``alpha_res``) and a bias.  ``pre`` uses a sigmoid, ``post``
+twice a sigmoid (so its initial value can be 1), ``res`` a row softmax followed by the Sinkhorn iterations.
 
 Checkpoint keys (reference ``src/mcore_bridge/bridge/gpt_bridge.py:1653-1673``): ``hc_{attn,ffn}_fn`` (the projection),
 ``hc_{attn,ffn}_base`` (the bias), ``hc_{attn,ffn}_scale`` (the three scales); the block's output contraction uses

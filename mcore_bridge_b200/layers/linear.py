@@ -71,7 +71,8 @@ class ColumnParallelLinear(_LinearBase):
         return linear(x, self.weight, self.bias, self.spec)
 
     def extra_repr(self):
-        return f'in={self.input_size}, out={self.output_size_per_partition} (of {self.output_size}), bias={self.bias is not None}, sp={self.sequence_parallel}'
+        return (f'in={self.input_size}, out={self.output_size_per_partition} (of {self.output_size}), '
+                f'bias={self.bias is not None}, sp={self.sequence_parallel}')
 
 
 class LayerNormColumnParallelLinear(ColumnParallelLinear):
@@ -159,7 +160,8 @@ class RowParallelLinear(_LinearBase):
         return linear(x, self.weight, self.bias, self.spec)
 
     def extra_repr(self):
-        return f'in={self.input_size_per_partition} (of {self.input_size}), out={self.output_size}, bias={self.bias is not None}, sp={self.sequence_parallel}'
+        return (f'in={self.input_size_per_partition} (of {self.input_size}), out={self.output_size}, '
+                f'bias={self.bias is not None}, sp={self.sequence_parallel}')
 
 
 class ReplicatedLinear(nn.Module):

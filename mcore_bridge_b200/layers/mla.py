@@ -69,7 +69,8 @@ class DSAIndexer(nn.Module):
         return torch.cat([pe, nope], dim=-1)
 
     def forward_before_topk(self, x: torch.Tensor, qr: torch.Tensor, ctx: ForwardContext):
-        """``x [T, H]``, ``qr [T, q_lora]`` (both already gathered over SP) -> ``q [T, h, d]``, ``k [T, d]``, ``w [T, h]``."""
+        """``x [T, H]``, ``qr [T, q_lora]`` (both already gathered over SP) -> ``q [T, h, d]``, ``k [T, d]``,
+        ``w [T, h]``."""
         T = x.shape[0]
         q = self.linear_wq_b(qr).view(T, self.n_heads, self.head_dim)
         q = self._rope(q, ctx.cos, ctx.sin)
@@ -130,8 +131,8 @@ class MLASelfAttention(nn.Module):
             self.linear_q_proj = ColumnParallelLinear(cfg.hidden_size, self.nh * self.q_dim, cfg, bias=False)
         else:
             self.linear_q_down_proj = ReplicatedLinear(cfg.hidden_size, cfg.q_lora_rank, cfg)
-            self.linear_q_up_proj = LayerNormColumnParallelLinear(cfg.q_lora_rank, self.nh * self.q_dim, cfg, bias=False,
-                                                                  sequence_parallel=False)
+            self.linear_q_up_proj = LayerNormColumnParallelLinear(cfg.q_lora_rank, self.nh * self.q_dim, cfg,
+                                                                  bias=False, sequence_parallel=False)
             self.linear_q_up_proj.layer_norm_weight.sequence_parallel = False  # sees all tokens, full gradient
         self.linear_kv_down_proj = ReplicatedLinear(cfg.hidden_size, self.kv_lora + self.qk_rope, cfg)
         self.linear_kv_up_proj = LayerNormColumnParallelLinear(self.kv_lora, self.nh * (self.qk_nope + self.v_dim), cfg,
@@ -263,7 +264,8 @@ class MLASelfAttention(nn.Module):
         from ..ops import dsa
         o, attn_probs = dsa.sparse_attention(q, k, v, idx, mask, self.scale, need_probs=train_indexer)
         if train_indexer:
-            loss = dsa.indexer_kl_loss(scores, attn_probs.detach(), mask, idx if cfg.dsa_indexer_use_sparse_loss else None)
+            loss = dsa.indexer_kl_loss(scores, attn_probs.detach(), mask,
+                                       idx if cfg.dsa_indexer_use_sparse_loss else None)
             from ..ops.moe import MoEAuxLossAutoScaler
             o = MoEAuxLossAutoScaler.apply(o, loss * cfg.dsa_indexer_loss_coeff)
             self.indexer_loss = loss.detach()

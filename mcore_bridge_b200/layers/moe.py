@@ -209,8 +209,8 @@ class TopKRouter(nn.Module):
                     dist.all_reduce(packed, group=ps.get_group(group))
                     n = ps.get_world_size(group)
                     counts, ntok_all = packed[:-1], packed[-1]
-                    aux = coeff * self.num_experts * ((counts / (ntok_all * self.topk)) *
-                                                      (sc.sum(0) / _micro_batch_tokens(cfg, ntok, ntok_all, group))).sum()
+                    ntok_mb = _micro_batch_tokens(cfg, ntok, ntok_all, group)
+                    aux = coeff * self.num_experts * ((counts / (ntok_all * self.topk)) * (sc.sum(0) / ntok_mb)).sum()
                 else:
                     aux = moe_ops.aux_loss(sc, counts, self.topk, coeff, ntok)
             probs = moe_ops.MoEAuxLossAutoScaler.apply(probs, aux)

@@ -63,10 +63,32 @@ class _Region:
 
 
 class ExchangeBuffers:
-    """Published/received buffers of one direction (forward or backward) for a fixed problem size."""
+    """The exchange buffers of one direction as one layer call sees them: the shared allocation plus this call's token
+    count ``T`` (calls of different sizes share an allocation laid out for the largest)."""
+
+    def __init__(self, alloc: '_ExchangeAllocation', T: int):
+        self._alloc = alloc
+        self.T = T
+
+    def __getattr__(self, name):
+        return getattr(self._alloc, name)
+
+    def sort_routing(self, parity: int):
+        """Sorts the published routing of this rank by expert (``order`` / ``eoff`` regions) for the fused
+        pull + GEMM kernel of the owners."""
+        T, k, E = self.T, self.k, self.E
+        rc = _lib.lib().mcb_moe_sort(_lib.ptr(self.view('idx', parity, (T * k,), torch.int32)),
+                                     _lib.ptr(self.view('counts', parity, (E,), torch.int32)), _int(T * k), _int(E),
+                                     _lib.ptr(self.view('eoff', parity, (E + 1,), torch.int32)),
+                                     _lib.ptr(self.view('order', parity, (T * k,), torch.int32)), _lib.stream_ptr())
+        _lib.check_rc(rc, 'mcb_moe_sort')
+
+
+class _ExchangeAllocation:
+    """Published/received buffers of one direction (forward or backward), laid out for up to ``T_alloc`` tokens."""
 
     def __init__(self, tag: str, T: int, H: int, k: int, E: int, capacity: int, device):
-        self.tag, self.T, self.H, self.k, self.E, self.cap = tag, T, H, k, E, capacity
+        self.tag, self.T_alloc, self.H, self.k, self.E, self.cap = tag, T, H, k, E, capacity
         self.world = ps.get_world_size('ep')
         self.rank = ps.get_rank_in('ep') if self.world > 1 else 0
         self.device = device
@@ -88,7 +110,8 @@ class ExchangeBuffers:
         self.offs = offs
         total = FLAG_BYTES + 2 * self.half
         if self.world > 1:
-            self.ws = symm.get_workspace('ep', total, f'moe_{tag}_{T}_{H}_{k}_{E}_{capacity}')
+            self.ws_tag = f'moe_{tag}_{T}_{H}_{k}_{E}_{capacity}'
+            self.ws = symm.get_workspace('ep', total, self.ws_tag)
             self.base_ptrs = self.ws.peer_ptrs
             self.buf = self.ws.buffer
         else:
@@ -99,7 +122,8 @@ class ExchangeBuffers:
         self._ptr_cache: Dict[Tuple[str, int], ctypes.Array] = {}
         # "block landed" flags of the fused pull + GEMM kernel (local memory; they carry the epoch of the launch that
         # filled the block, so they are never cleared)
-        self.blk_flags = torch.zeros(2 * max(1, capacity // PAD), dtype=torch.int32, device=device)   # flags, then counters
+        # per block: the flag, then (second half) the counter of landed quarters
+        self.blk_flags = torch.zeros(2 * max(1, capacity // PAD), dtype=torch.int32, device=device)
         self.pull_epoch = 0
 
     def next_epoch(self) -> int:
@@ -109,16 +133,6 @@ class ExchangeBuffers:
     def next_pull_epoch(self) -> int:
         self.pull_epoch += 1
         return self.pull_epoch
-
-    def sort_routing(self, parity: int):
-        """Sorts the published routing of this rank by expert (``order`` / ``eoff`` regions) for the fused
-        pull + GEMM kernel of the owners."""
-        T, k, E = self.T, self.k, self.E
-        rc = _lib.lib().mcb_moe_sort(_lib.ptr(self.view('idx', parity, (T * k,), torch.int32)),
-                                     _lib.ptr(self.view('counts', parity, (E,), torch.int32)), _int(T * k), _int(E),
-                                     _lib.ptr(self.view('eoff', parity, (E + 1,), torch.int32)),
-                                     _lib.ptr(self.view('order', parity, (T * k,), torch.int32)), _lib.stream_ptr())
-        _lib.check_rc(rc, 'mcb_moe_sort')
 
     def off(self, name: str, parity: int) -> int:
         return FLAG_BYTES + parity * self.half + self.offs[name]
@@ -161,16 +175,25 @@ class ExchangeBuffers:
                                                _lib.stream_ptr()), 'mcb_flag_wait')
 
 
-_BUFFERS: Dict[Tuple, ExchangeBuffers] = {}
+_BUFFERS: Dict[Tuple, _ExchangeAllocation] = {}
 
 
 def _buffers(tag, T, H, k, E, cap, device) -> ExchangeBuffers:
-    key = (tag, T, H, k, E, cap, device.index)
-    b = _BUFFERS.get(key)
-    if b is None:
-        b = ExchangeBuffers(tag, T, H, k, E, cap, device)
-        _BUFFERS[key] = b
-    return b
+    """One set of exchange buffers per (direction, layer shape), laid out for the largest token count and capacity
+    seen so far: a larger micro-batch re-allocates (a collective call: every rank of the group sees the same sizes),
+    smaller ones reuse the regions, so variable-length micro-batches do not pile up peer-mapped workspaces.  Calls
+    still in flight (saved for a later backward) keep the buffers they started with."""
+    key = (tag, H, k, E, device.index)
+    a = _BUFFERS.get(key)
+    if a is None or T > a.T_alloc or cap > a.cap:
+        t_new, cap_new = T, cap
+        if a is not None:
+            t_new, cap_new = max(T, a.T_alloc), max(cap, a.cap)
+            if a.ws is not None:
+                symm.release_workspace('ep', a.ws_tag)
+        a = _ExchangeAllocation(tag, t_new, H, k, E, cap_new, device)
+        _BUFFERS[key] = a
+    return ExchangeBuffers(a, T)
 
 
 _GROWN_FACTOR: Optional[float] = None     # raised by ``grow_capacity`` after an overflow; never shrinks
@@ -590,7 +613,7 @@ class FusedMoEDispatcher:
         epoch = fwd.next_epoch()
         return DispatchState(fwd=fwd, bwd=bwd, parity=epoch & 1,
                              seg_off=torch.empty(self.El + 1, dtype=torch.int32, device=device),
-                             row_src=torch.empty(cap, dtype=torch.int32, device=device))
+                             row_src=torch.empty(fwd.cap, dtype=torch.int32, device=device))
 
     def route(self, st: DispatchState, logits: torch.Tensor, bias, valid, sigmoid, renorm, groups, group_topk, scaling):
         b = st.fwd

@@ -88,7 +88,8 @@ class MultimodalGPTModel(nn.Module):
             position_ids.shape[-1] * cp == input_ids.shape[-1]
         extras = {}
         if decoder_input is None and self.pre_process and input_ids is not None:
-            full_ids = input_ids if (cp == 1 or ids_are_full) else reconstruct_tensor_cp(input_ids, packed_seq_params, 1)
+            full_ids = input_ids if (cp == 1 or ids_are_full) else \
+                reconstruct_tensor_cp(input_ids, packed_seq_params, 1)
             decoder_input, extras = self.embed_full_stream(full_ids, packed_seq_params, kwargs)
             if cp > 1:
                 decoder_input = split_cp_inputs(decoder_input, cu, 1)

@@ -43,7 +43,8 @@ def scatter_embeds(inputs_embeds: torch.Tensor, input_ids: torch.Tensor, token_i
     flat = inputs_embeds.reshape(-1, inputs_embeds.shape[-1])
     idx = mask.reshape(-1).nonzero(as_tuple=True)[0]
     if idx.numel() != media_embeds.shape[0]:
-        raise ValueError(f'{idx.numel()} placeholder tokens (id {token_id}) but {media_embeds.shape[0]} media embeddings')
+        raise ValueError(f'{idx.numel()} placeholder tokens (id {token_id}) but {media_embeds.shape[0]} media '
+                         'embeddings')
     flat = flat.index_copy(0, idx, media_embeds.to(flat.dtype).to(flat.device))
     return flat.view_as(inputs_embeds), mask
 

@@ -128,7 +128,8 @@ class Gemma4Attention(nn.Module):
             raise NotImplementedError(f'Gemma-4 attention needs query heads ({self.nq}) divisible by TP {tp}')
         # More TP ranks than KV heads: the row split of ``linear_qkv`` cuts through a group, so the projection output is
         # all-gathered on the last dim and every rank takes its group and, inside it, its share of the query heads;
-        # ``kv_rep`` ranks then share one KV head (reference ``src/mcore_bridge/model/mm_gpts/gemma4.py:305-309,343-346``)
+        # ``kv_rep`` ranks then share one KV head (reference
+        # ``src/mcore_bridge/model/mm_gpts/gemma4.py:305-309,343-346``)
         self.kv_rep = 1
         if self.ng % tp:
             if tp % self.ng:
@@ -358,7 +359,8 @@ class Gemma4TextModel(GPTModel):
         got, at = {}, H
         if self.per_layer_dim:
             w = tokens * self.config.num_layers * (self.per_layer_dim // tp) // rows
-            got[PER_LAYER] = input_tensor[:, at:at + w].reshape(tokens, self.config.num_layers, self.per_layer_dim // tp)
+            got[PER_LAYER] = input_tensor[:, at:at + w].reshape(tokens, self.config.num_layers,
+                                                                self.per_layer_dim // tp)
             at += w
         kv = {}
         for lt, h, d in self._kv_slots():

@@ -99,7 +99,8 @@ class Qwen3VLVit(HuggingFaceVit):
 
 class Qwen3VLMoeBridge(MultimodalGPTBridge):
     """Experts are stored fused (``experts.gate_up_proj`` / ``experts.down_proj``; input- or output-major depending on
-    the Transformers release that wrote the checkpoint — reference ``src/mcore_bridge/bridge/gpt_bridge.py:765-773``)."""
+    the Transformers release that wrote the checkpoint — reference
+    ``src/mcore_bridge/bridge/gpt_bridge.py:765-773``)."""
     hf_fused_experts = True
 
 
@@ -213,7 +214,7 @@ class Qwen3_5Vit(HuggingFaceVit):
     _aligner = ['visual.merger']
 
     def prepare_model(self, hf_config):
-        if self.config.hf_model_type == 'qwen3_5_moe':      # its vision config belongs to the MoE model's own tower class
+        if self.config.hf_model_type == 'qwen3_5_moe':      # its vision config belongs to the MoE model's tower class
             from transformers.models.qwen3_5_moe import Qwen3_5MoeVisionModel as VisionModel
         else:
             from transformers.models.qwen3_5 import Qwen3_5VisionModel as VisionModel

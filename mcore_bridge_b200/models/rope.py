@@ -152,16 +152,17 @@ class RotaryEmbedding(torch.nn.Module):
         cfg = self.config
         if self.rope_type == 'dynamic':
             if seq_len > self._cached_seq_len or (seq_len <= cfg.max_position_embeddings < self._cached_seq_len):
-                inv, _ = compute_inv_freq('dynamic', self.base, self.dim, self.rope_scaling, cfg.max_position_embeddings,
-                                          seq_len)
+                inv, _ = compute_inv_freq('dynamic', self.base, self.dim, self.rope_scaling,
+                                          cfg.max_position_embeddings, seq_len)
                 self.inv_freq.copy_(inv.to(self.inv_freq.device))
                 self._cached_seq_len = max(seq_len, cfg.max_position_embeddings)
         elif self.rope_type == 'longrope':
             orig = cfg.original_max_position_embeddings or cfg.max_position_embeddings
             want_long = seq_len > orig
             if want_long != self._uses_long:
-                inv, _ = compute_inv_freq('longrope', self.base, self.dim, self.rope_scaling, cfg.max_position_embeddings,
-                                          seq_len if want_long else None, cfg.original_max_position_embeddings)
+                inv, _ = compute_inv_freq('longrope', self.base, self.dim, self.rope_scaling,
+                                          cfg.max_position_embeddings, seq_len if want_long else None,
+                                          cfg.original_max_position_embeddings)
                 self.inv_freq.copy_(inv.to(self.inv_freq.device))
                 self._uses_long = want_long
 

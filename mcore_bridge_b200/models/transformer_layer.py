@@ -147,7 +147,8 @@ class TransformerLayer(nn.Module):
 
     # names of ``offload_modules`` that belong to the attention block and to the feed-forward block
     _ATTN_OFFLOAD = frozenset({'attn_norm', 'qkv_linear', 'core_attn', 'attn_proj', 'self_attn'})
-    _MLP_OFFLOAD = frozenset({'mlp_norm', 'mlp', 'moe', 'moe_act', 'expert_fc1', 'expert_fc2', 'shared_expert', 'dense_mlp'})
+    _MLP_OFFLOAD = frozenset({'mlp_norm', 'mlp', 'moe', 'moe_act', 'expert_fc1', 'expert_fc2', 'shared_expert',
+                              'dense_mlp'})
 
     def _offload(self, names):
         """``fine_grained_activation_offloading``: while a sub-block named in ``offload_modules`` runs, the tensors it

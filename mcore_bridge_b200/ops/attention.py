@@ -98,13 +98,14 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: Opt
         if why is None and _lib.available():
             return attention_cuda.attention(q, k, v, cu_seqlens, max_seqlen, scale, seq_start, window, sinks)
         if backend == 'mcb':
-            raise RuntimeError(f'the in-tree attention kernel does not cover {why or "a run with the kernels disabled"}')
+            raise RuntimeError('the in-tree attention kernel does not cover '
+                               f'{why or "a run with the kernels disabled"}')
         if why is not None and _lib.cuda_enabled():
             from ..utils.logger import get_logger
             get_logger().warning_once(f'attention: the in-tree sm_100a kernel does not cover {why}; '
                                       'this call runs on a library / reference kernel')
-    if q.is_cuda and backend in ('auto', 'flash_attn') and sinks is None and q.dtype in (torch.bfloat16, torch.float16) \
-            and _flash_attn_available() and d <= 256:
+    if q.is_cuda and backend in ('auto', 'flash_attn') and sinks is None \
+            and q.dtype in (torch.bfloat16, torch.float16) and _flash_attn_available() and d <= 256:
         from flash_attn import flash_attn_varlen_func
         if cu_seqlens is None:
             cu_seqlens = torch.tensor([0, T], dtype=torch.int32, device=q.device)

@@ -16,7 +16,8 @@ from typing import Optional, Tuple
 import torch
 
 
-def index_scores(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, mask: torch.Tensor, chunk: int = 2048) -> torch.Tensor:
+def index_scores(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, mask: torch.Tensor,
+                 chunk: int = 2048) -> torch.Tensor:
     """``q [T, h, d]``, ``k [Tk, d]``, ``w [T, h]`` (scales folded in), ``mask [T, Tk]`` bool -> ``[T, Tk]`` fp32."""
     T = q.shape[0]
     out = torch.empty(T, k.shape[0], dtype=torch.float32, device=q.device)
@@ -109,7 +110,8 @@ def sparse_mla_attention_absorbed(q_nope: torch.Tensor, q_pe: torch.Tensor, kv_l
     """Top-k sparse MLA attention in the weight-absorbed (latent, multi-query) form, one block of queries at a time.
 
     ``q_nope [T, h, dn]``, ``q_pe [T, h, dr]`` (rotated), ``kv_lat [T, dl]`` (normalised latent), ``k_pe [T, dr]``
-    (rotated, shared by the heads), ``w_uk [h, dn, dl]`` / ``w_uv [h, dv, dl]`` (the two halves of the kv up-projection),
+    (rotated, shared by the heads), ``w_uk [h, dn, dl]`` / ``w_uv [h, dv, dl]`` (the two halves of the kv
+    up-projection),
     ``idx [T, topk]`` selected key positions, ``seq_start [T]``.  Scores are ``(q_nope W_uk) . c_kv + q_pe . k_pe`` over
     the selected keys only, so memory is ``O(chunk * topk)`` instead of ``O(T^2)`` and the work is the sparse work.  A
     selected position that the query may not see (later than the query or in another sequence: rows with fewer than

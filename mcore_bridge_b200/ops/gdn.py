@@ -79,7 +79,8 @@ def _chunk_one_sequence(q, k, v, g, beta, chunk: int):
         o = (q[:, i] * gc[:, i].exp()[..., None]) @ S + qk[:, i] @ v_new
         outs.append(o)
         g_last = gc[:, i, -1]
-        S = S * g_last.exp()[:, None, None] + (k[:, i] * (g_last[:, None] - gc[:, i]).exp()[..., None]).transpose(-1, -2) @ v_new
+        k_dec = k[:, i] * (g_last[:, None] - gc[:, i]).exp()[..., None]
+        S = S * g_last.exp()[:, None, None] + k_dec.transpose(-1, -2) @ v_new
     return torch.stack(outs, dim=1).reshape(h, n * chunk, dv)[:, :L]
 
 

@@ -132,8 +132,8 @@ class _LinearFn(torch.autograd.Function):
             x_full = x2  # saved gathered input
             if need_dx:
                 fc = _fused()
-                dx = fc.gemm_reduce_scatter_nn(dy2, weight, spec.group) if (not f8 and fc.enabled(dy2, weight, spec.group)) \
-                    else None
+                fused = not f8 and fc.enabled(dy2, weight, spec.group)
+                dx = fc.gemm_reduce_scatter_nn(dy2, weight, spec.group) if fused else None
                 if dx is None:
                     dx = M.reduce_scatter_dim0(_mm_nn(dy2, weight, f8), spec.group)
             if need_dw:

@@ -28,7 +28,6 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-from ..ops.attention import attention_ref
 from . import state as ps
 
 
@@ -79,6 +78,8 @@ class CpLayout:
     cu_full: torch.Tensor           # int32 [B+1]
     ring_lo: torch.Tensor           # int32 [cp, T_local]: first key, in rank j's local order, local query i sees
     ring_hi: torch.Tensor           # int32 [cp, T_local]: last one (lo > hi: none)
+    ring_qlo: torch.Tensor          # int32 [cp, T_local]: first local query that can see token t of rank j
+    ring_qhi: torch.Tensor          # int32 [cp, T_local]: last one (they bound the loops of the dK/dV kernel)
 
 
 def compute_layout(cu_seqlens: Optional[torch.Tensor], t_local: int, cp: int, rank: int, device) -> CpLayout:
@@ -127,8 +128,11 @@ def compute_layout(cu_seqlens: Optional[torch.Tensor], t_local: int, cp: int, ra
     cnt = n1 + n2
     ring_lo = torch.where(cnt > 0, lq[None, :].expand(cp, -1), torch.ones_like(cnt)).to(torch.int32).contiguous()
     ring_hi = torch.where(cnt > 0, lq[None, :] + cnt - 1, torch.zeros_like(cnt)).to(torch.int32).contiguous()
+    # q_lo / q_hi are indexed by stream position; rank j's token t sits at stream position scatter_index[j * tl + t]
+    ring_qlo = q_lo[scatter_index].view(cp, t_local).contiguous()
+    ring_qhi = q_hi[scatter_index].view(cp, t_local).contiguous()
     return CpLayout(cp, rank, t_local, gather_index, scatter_index, q_stream, q_rel, k_lo, k_hi, q_lo, q_hi, cu_local,
-                    cu.to(torch.int32), ring_lo, ring_hi)
+                    cu.to(torch.int32), ring_lo, ring_hi, ring_qlo, ring_qhi)
 
 
 def get_layout(ctx, t_local: int, device) -> CpLayout:
@@ -398,16 +402,12 @@ class _RingAttnFn(torch.autograd.Function):
         q, k, v, o, lse = ctx.saved_tensors
         lay, scale = ctx.lay, ctx.scale
         cp, r = lay.cp, lay.rank
-        T = q.shape[0]
         do = do.contiguous()
         delta = (o.float() * do.float()).sum(-1).t().contiguous()              # [nq, T]
         fetch = _ChunkFetcher(k, v)
         dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
         dk_rm = torch.empty((cp, *k.shape), dtype=torch.float32, device=q.device)
         dv_rm = torch.empty((cp, *v.shape), dtype=torch.float32, device=q.device)
-        if ctx.use_kernel:
-            all_lo = torch.zeros(k.shape[0], dtype=torch.int32, device=q.device)
-            all_hi = torch.full((k.shape[0],), T - 1, dtype=torch.int32, device=q.device)
         for s in range(cp):
             j = (r - s) % cp
             if s + 1 < cp:
@@ -416,7 +416,7 @@ class _RingAttnFn(torch.autograd.Function):
             if ctx.use_kernel:
                 from ..ops import attention_cuda as ac
                 dq_s, dk_s, dv_s = ac.bwd_ranges_raw(q, kj, vj, o, do, lse, delta, lay.ring_lo[j], lay.ring_hi[j],
-                                                     all_lo, all_hi, scale)
+                                                     lay.ring_qlo[j], lay.ring_qhi[j], scale)
             else:
                 dq_s, dk_s, dv_s = _partial_bwd_ref(q, kj, vj, do, lse, delta, lay.ring_lo[j], lay.ring_hi[j], scale)
             dq += dq_s.float()

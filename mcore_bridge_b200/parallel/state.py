@@ -138,8 +138,8 @@ def initialize_model_parallel(tensor_model_parallel_size: int = 1, pipeline_mode
     if world % (etp * ep * pp) != 0:
         raise ValueError(f'world size {world} is not divisible by etp*ep*pp = {etp * ep * pp}')
     edp = world // (etp * ep * pp)
-    st = ParallelState(world_size=world, rank=rank, tp=tp, cp=cp, dp=dp, pp=pp, vpp=virtual_pipeline_model_parallel_size,
-                       ep=ep, etp=etp, edp=edp)
+    st = ParallelState(world_size=world, rank=rank, tp=tp, cp=cp, dp=dp, pp=pp,
+                       vpp=virtual_pipeline_model_parallel_size, ep=ep, etp=etp, edp=edp)
     if virtual_pipeline_model_parallel_size is not None:
         st.vp_rank = 0
     kw = {}

@@ -88,5 +88,10 @@ def get_workspace(group_name: str, nbytes: int, tag: str = 'default') -> SymmWor
     return ws
 
 
+def release_workspace(group_name: str, tag: str) -> None:
+    """Forgets a workspace; its memory goes back once the last tensor viewing it is gone (on every rank)."""
+    _WORKSPACES.pop(f'{group_name}:{tag}', None)
+
+
 def free_all():
     _WORKSPACES.clear()

@@ -71,7 +71,8 @@ class TokenFileDataset:
 
     def __init__(self, path: str, dtype: str, seq_len: int, micro_batch_size: int, dp_rank: int, dp_size: int):
         import numpy as np
-        arr = np.load(path, mmap_mode='r') if path.endswith('.npy') else np.memmap(path, dtype=np.dtype(dtype), mode='r')
+        arr = np.load(path, mmap_mode='r') if path.endswith('.npy') else \
+            np.memmap(path, dtype=np.dtype(dtype), mode='r')
         self.tokens = arr.reshape(-1)
         self.seq_len, self.mbs = seq_len, micro_batch_size
         self.n_windows = (len(self.tokens) - 1) // seq_len

@@ -10,7 +10,8 @@ manifest of all pieces; ``load`` fills each local shard from whatever saved piec
 under one TP / PP / EP layout loads under any other.
 
 Parity: the reference's modules take part in Megatron's distributed checkpointing through ``sharded_state_dict``
-overrides (``src/mcore_bridge/model/gpt_model.py:584-621``, ``src/mcore_bridge/model/modules/gated_delta_net.py:381-425``,
+overrides (``src/mcore_bridge/model/gpt_model.py:584-621``,
+``src/mcore_bridge/model/modules/gated_delta_net.py:381-425``,
 ``src/mcore_bridge/tuners/lora.py:448-474``, ``src/mcore_bridge/tuners/utils.py:8-28``); this module is that
 checkpoint format's counterpart here.  (Model exchange with Transformers stays on the Hugging Face bridge; the
 optimizer state has its own per-rank format in ``train/checkpoint.py``.)
@@ -101,7 +102,8 @@ def sharded_state_dict(models: Iterable[torch.nn.Module], prefix: str = '', trai
                 for j in range(stride):
                     off = list(goff)
                     off[pdim] = j * (gshape[pdim] // stride) + loc * tp_rank
-                    pieces.append(ShardedTensor(key, data.narrow(pdim, j * loc, loc), tuple(gshape), tuple(off), writer))
+                    pieces.append(ShardedTensor(key, data.narrow(pdim, j * loc, loc), tuple(gshape), tuple(off),
+                                                writer))
                 out[key] = pieces
             else:
                 out[key] = [ShardedTensor(key, data, tuple(gshape), tuple(goff), writer)]

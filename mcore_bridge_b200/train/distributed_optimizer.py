@@ -127,8 +127,8 @@ class DistributedDataParallel(nn.Module):
             dev, dt = params[0].device, params[0].dtype
             same = [p for p in params if p.dtype == dt]
             assert len(same) == len(params), 'all parameters of a buffer must share a dtype'
-            self.buffers[key] = ParamAndGradBuffer(params, 'edp' if key[0] else 'dp_cp', int(bucket_mb * 2**20), dev, dt,
-                                                   grad_dtype)
+            self.buffers[key] = ParamAndGradBuffer(params, 'edp' if key[0] else 'dp_cp', int(bucket_mb * 2**20), dev,
+                                                   dt, grad_dtype)
         self.is_last_microbatch = True
         self._comm_stream = torch.cuda.Stream() if torch.cuda.is_available() else None
         self._hooks = []
@@ -307,7 +307,8 @@ class DistributedOptimizer:
         tp_rank0 = ps.get_rank_in('tp') == 0 if ps.get_world_size('tp') > 1 else True
         # A shard holds the *sum* of the data-parallel ranks' gradients; the averaging (and any loss scale) is folded
         # into the optimizer kernel's gradient scale.  The norm is that of the gradient the update uses, so every
-        # buffer's sum of squares is scaled accordingly (buffers can have different data-parallel sizes: dense vs expert).
+        # buffer's sum of squares is scaled accordingly (buffers can have different data-parallel sizes: dense vs
+        # expert).
         part = torch.zeros(1, dtype=torch.float32, device=self._sq.device)
         cur = None
         tied_copy = ps.get_world_size('embd') > 1 and not ps.is_pipeline_first_stage()

@@ -67,8 +67,8 @@ class _P2P:
 def _psp(d: Dict):
     if d.get('cu_seqlens') is None:
         return None
-    return PackedSeqParams(cu_seqlens_q=d['cu_seqlens'], cu_seqlens_kv=d['cu_seqlens'], max_seqlen_q=d.get('max_seqlen'),
-                           max_seqlen_kv=d.get('max_seqlen'))
+    return PackedSeqParams(cu_seqlens_q=d['cu_seqlens'], cu_seqlens_kv=d['cu_seqlens'],
+                           max_seqlen_q=d.get('max_seqlen'), max_seqlen_kv=d.get('max_seqlen'))
 
 
 def _local_rows(d: Dict, cfg) -> int:
@@ -94,7 +94,8 @@ def _forward(trainer, model, d: Dict, input_tensor: Optional[torch.Tensor], n_mi
         if ps.get_world_size('cp') > 1:
             ntok = ntok.clone()
             dist.all_reduce(ntok, group=ps.get_group('cp'))
-        # a context-parallel rank's share of the micro-batch loss, scaled by cp (see Trainer.forward_backward_microbatch)
+        # a context-parallel rank's share of the micro-batch loss, scaled by cp (see
+        # Trainer.forward_backward_microbatch)
         out = (out * mask).sum() / ntok.clamp(min=1.0) * (float(ps.get_world_size('cp')) / n_micro)
     return out
 

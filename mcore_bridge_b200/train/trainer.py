@@ -54,7 +54,8 @@ def init_weights(model: torch.nn.Module, std: float = 0.02, seed: Optional[int] 
                    'q_norm' in name or 'k_norm' in name)
         if p.dim() < 2 and (is_norm or name.endswith('bias')):
             if is_norm and name.endswith('weight'):
-                zero_centered = getattr(model, 'config', None) is not None and model.config.layernorm_zero_centered_gamma
+                zero_centered = (getattr(model, 'config', None) is not None
+                                 and model.config.layernorm_zero_centered_gamma)
                 p.fill_(0.0 if zero_centered else 1.0)
             else:
                 p.zero_()
@@ -195,7 +196,8 @@ class Trainer:
         for attempt in range(4):
             total = self._forward_backward(mbs)
             grad_norm = self.optimizer.step()
-            # every rank holds cp x its share of its micro-batches' loss: the mean over the dp x cp group is the step's loss
+            # every rank holds cp x its share of its micro-batches' loss: the mean over the dp x cp group is the step's
+            # loss
             if ps.get_world_size('dp_cp') > 1:
                 dist.all_reduce(total, group=ps.get_group('dp_cp'))
                 total = total / ps.get_world_size('dp_cp')

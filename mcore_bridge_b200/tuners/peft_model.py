@@ -112,7 +112,8 @@ class LoraModel(nn.Module):
                 continue
             if isinstance(module, LoraParallelLinear) or '.lora_' in name or '.base_layer' in name:
                 continue
-            if cfg.modules_to_save and _matches(name, cfg.modules_to_save) and not isinstance(module, ModulesToSaveWrapper):
+            if cfg.modules_to_save and _matches(name, cfg.modules_to_save) \
+                    and not isinstance(module, ModulesToSaveWrapper):
                 setattr(parent, child, ModulesToSaveWrapper(module, adapter_name))
                 continue
             if not isinstance(module, LORA_TARGET_TYPES):

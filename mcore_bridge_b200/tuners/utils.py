@@ -7,7 +7,8 @@ from typing import Dict, List
 from torch import nn
 
 
-def tuners_sharded_state_dict(module: nn.Module, prefix: str = '', sharded_offsets=(), metadata=None) -> Dict[str, List]:
+def tuners_sharded_state_dict(module: nn.Module, prefix: str = '', sharded_offsets=(),
+                              metadata=None) -> Dict[str, List]:
     """The trainable adapter tensors (LoRA factors, ``modules_to_save`` copies) of ``module`` as sharded-checkpoint
     pieces: ``{key: [ShardedTensor, ...]}`` with global shape, this rank's offset and the writer flag, ready for
     ``train.dist_checkpoint.save`` / ``load`` (``trainable_only=True`` does the same for a whole model)."""

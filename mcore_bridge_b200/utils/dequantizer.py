@@ -135,7 +135,8 @@ class PackedDequantizer:
         gs = self.group_size if self.group_size and self.group_size > 0 else cols
         s = scale.repeat_interleave(gs, dim=-1)[..., :cols] if scale.shape[-1] != cols else scale
         if weight_zero_point is not None and not self.symmetric:
-            zp = self.unpack(weight_zero_point, [rows, scale.shape[-1]]).float() if weight_zero_point.dtype == torch.int32 \
+            packed_zp = weight_zero_point.dtype == torch.int32
+            zp = self.unpack(weight_zero_point, [rows, scale.shape[-1]]).float() if packed_zp \
                 else weight_zero_point.float()
             q = q - zp.repeat_interleave(gs, dim=-1)[..., :cols]
         return (q * s).to(dtype)
@@ -175,7 +176,8 @@ def add_dequantized_views(sd: dict, quantization_config: Optional[dict], lazy_cl
             def load_packed(mod=mod):
                 zp = sd.get(mod + '.weight_zero_point')
                 return deq.convert(sd[mod + '.weight_packed'].load(), sd[mod + '.weight_scale'].load(),
-                                   sd[mod + '.weight_shape'].load(), None if zp is None else zp.load(), dtype=torch.float32)
+                                   sd[mod + '.weight_shape'].load(), None if zp is None else zp.load(),
+                                   dtype=torch.float32)
 
             out[mod + '.weight'] = lazy_cls(loader=load_packed)
     return out

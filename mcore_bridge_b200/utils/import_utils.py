@@ -34,4 +34,5 @@ def lazy_exports(package: str, table: dict[str, list[str]]):
 
 
 def is_flash_attn_3_available() -> bool:
-    return importlib.util.find_spec('flash_attn_3') is not None or importlib.util.find_spec('flash_attn_interface') is not None
+    return (importlib.util.find_spec('flash_attn_3') is not None
+            or importlib.util.find_spec('flash_attn_interface') is not None)

@@ -1,6 +1,7 @@
 """Tracing helpers: NVTX ranges (no-ops without CUDA) and device-side timers built on CUDA events.
 
-The reference only wraps a few ops in ``nvtx_range_push/pop`` (``src/mcore_bridge/model/modules/gated_delta_net.py:190-377``);
+The reference only wraps a few ops in ``nvtx_range_push/pop``
+(``src/mcore_bridge/model/modules/gated_delta_net.py:190-377``);
 here every layer-level op can be wrapped with :func:`nvtx_range`, and :class:`DeviceTimers` accumulates per-name
 device time (events are resolved lazily at ``summary()`` so measuring does not synchronise the step).
 """

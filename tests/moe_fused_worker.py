@@ -76,6 +76,30 @@ for (E,k,H,F,sig,groups,use_mask) in [(8,2,256,128,False,None,False),(128,8,2048
         if world>1: dist.all_reduce(t)
         ok &= t.item()==0
         if rank==0: print(f'E{E} k{k} H{H} sig{sig}: fused path reproducible {"OK" if t.item()==0 else "FAIL"}', flush=True)
+# micro-batches of different lengths reuse (and, when larger, grow) one allocation per layer shape
+from mcore_bridge_b200.layers import moe_fused as _mf
+kw = hf_to_mcore_config(hf_config('qwen3_moe_tiny', num_experts=8, num_experts_per_tok=2, hidden_size=256, moe_intermediate_size=128))
+cfg = ModelConfig(**kw, bf16=True, expert_model_parallel_size=world)
+torch.manual_seed(5)
+with torch.device(dev):
+    layer = MoELayer(cfg).train()
+_mf._BUFFERS.clear()
+for T in (512, 256, 768, 384):
+    gx = torch.Generator(device=dev).manual_seed(300 + rank + T)
+    x = torch.randn(T, 256, device=dev, generator=gx).to(torch.bfloat16)
+    dy = torch.randn(T, 256, device=dev, generator=gx).to(torch.bfloat16)
+    res = {}
+    for fused in ('1', '0'):
+        os.environ['MCB200_FUSED_MOE'] = fused; os.environ['MCB200_MOE_FUSED_GEMM'] = '1'; os.environ['MCB200_MOE_SCATTER'] = '0'
+        layer.zero_grad(); xx = x.clone().requires_grad_(); y = layer(xx); y.backward(dy)
+        res[fused] = (y.detach().clone(), xx.grad.clone())
+    torch.cuda.synchronize(); _lib.check_status()
+    r = max(rel(res['1'][0], res['0'][0]), rel(res['1'][1], res['0'][1]))
+    t = torch.tensor([0 if r < 3e-2 else 1], device=dev)
+    if world>1: dist.all_reduce(t)
+    ok &= t.item()==0
+    if rank==0: print(f'varying T={T}: rel={r:.3e} allocations={len(_mf._BUFFERS)} {"OK" if t.item()==0 else "FAIL"}', flush=True)
+ok &= len(_mf._BUFFERS) == 2        # one forward and one backward allocation for the layer shape
 if rank==0: print('ALL OK' if ok else 'SOME FAILED', flush=True)
 if world>1:
     dist.barrier(); dist.destroy_process_group()

@@ -659,8 +659,6 @@ def test_ring_attention_steps_on_the_kernels(cp):
     dk_sum = [torch.zeros(tl, nkv, d, device=DEV) for _ in range(cp)]
     dv_sum = [torch.zeros(tl, nkv, d, device=DEV) for _ in range(cp)]
     scale = d ** -0.5
-    all_lo = torch.zeros(tl, dtype=torch.int32, device=DEV)
-    all_hi = torch.full((tl,), tl - 1, dtype=torch.int32, device=DEV)
     for r, lay in enumerate(lays):
         ql, dol = q[lay.q_stream].contiguous(), do[lay.q_stream].contiguous()
         o_acc = torch.zeros(tl, nq, d, device=DEV)
@@ -678,7 +676,7 @@ def test_ring_attention_steps_on_the_kernels(cp):
         for s in range(cp):
             j = (r - s) % cp
             dq_s, dk_s, dv_s = ac.bwd_ranges_raw(ql, k_loc[j], v_loc[j], o, dol, lse_acc, delta, lay.ring_lo[j],
-                                                 lay.ring_hi[j], all_lo, all_hi, scale)
+                                                 lay.ring_hi[j], lay.ring_qlo[j], lay.ring_qhi[j], scale)
             dq += dq_s.float()
             dk_sum[j] += dk_s.float()
             dv_sum[j] += dv_s.float()
