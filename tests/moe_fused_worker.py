@@ -83,6 +83,11 @@ cfg = ModelConfig(**kw, bf16=True, expert_model_parallel_size=world)
 torch.manual_seed(5)
 with torch.device(dev):
     layer = MoELayer(cfg).train()
+g = torch.Generator(device=dev).manual_seed(12)
+with torch.no_grad():
+    layer.router.weight.copy_(torch.randn(layer.router.weight.shape, device=dev, generator=g) * 0.3)
+    for w in (layer.experts.linear_fc1.weight, layer.experts.linear_fc2.weight):
+        w.copy_(torch.randn(w.shape, device=dev, generator=g) * 0.05)
 _mf._BUFFERS.clear()
 for T in (512, 256, 768, 384):
     gx = torch.Generator(device=dev).manual_seed(300 + rank + T)
