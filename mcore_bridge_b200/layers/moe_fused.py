@@ -183,7 +183,8 @@ def _buffers(tag, T, H, k, E, cap, device) -> ExchangeBuffers:
     seen so far: a larger micro-batch re-allocates (a collective call: every rank of the group sees the same sizes),
     smaller ones reuse the regions, so variable-length micro-batches do not pile up peer-mapped workspaces.  Calls
     still in flight (saved for a later backward) keep the buffers they started with."""
-    key = (tag, H, k, E, device.index)
+    # the expert-parallel group is part of the identity: an allocation holds that group's peer mappings
+    key = (tag, H, k, E, device.index, tuple(ps.get_group_ranks('ep')))
     a = _BUFFERS.get(key)
     if a is None or T > a.T_alloc or cap > a.cap:
         t_new, cap_new = T, cap

@@ -60,7 +60,7 @@ def _ptr_array(ws: symm.SymmWorkspace, offset: int):
 
 def _workspace(group_name: str, tag: str, half_bytes: int) -> Tuple[symm.SymmWorkspace, int]:
     """Workspace with two halves of at least ``half_bytes``; returns (workspace, actual half size)."""
-    key = f'{group_name}:{tag}'
+    key = symm._key(group_name, tag)
     ws = symm._WORKSPACES.get(key)
     if ws is not None:
         half = (ws.nbytes - FLAG_BYTES) // 2 // 1024 * 1024

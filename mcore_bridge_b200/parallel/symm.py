@@ -62,9 +62,15 @@ def is_supported() -> bool:
         return False
 
 
+def _key(group_name: str, tag: str) -> str:
+    # the member ranks are part of the identity: after the parallel state is rebuilt with other groups of the same
+    # name, an old workspace (mapped to other peers) must not be handed out
+    return f"{group_name}:{','.join(map(str, ps.get_group_ranks(group_name)))}:{tag}"
+
+
 def get_workspace(group_name: str, nbytes: int, tag: str = 'default') -> SymmWorkspace:
     """Returns (allocating or growing on first use — a collective call over the group) the named workspace."""
-    key = f'{group_name}:{tag}'
+    key = _key(group_name, tag)
     ws = _WORKSPACES.get(key)
     if ws is not None and ws.nbytes >= nbytes:
         return ws
@@ -90,7 +96,7 @@ def get_workspace(group_name: str, nbytes: int, tag: str = 'default') -> SymmWor
 
 def release_workspace(group_name: str, tag: str) -> None:
     """Forgets a workspace; its memory goes back once the last tensor viewing it is gone (on every rank)."""
-    _WORKSPACES.pop(f'{group_name}:{tag}', None)
+    _WORKSPACES.pop(_key(group_name, tag), None)
 
 
 def free_all():
