@@ -54,7 +54,32 @@ def parse_args(argv=None):
     ap.add_argument('--resume', default=None)
     ap.add_argument('--log-interval', type=int, default=1)
     ap.add_argument('--heartbeat-dir', default=None)
+    ap.add_argument('--set', dest='overrides', action='append', default=[], metavar='FIELD=VALUE',
+                    help='any other ModelConfig field, value in Python / JSON syntax (repeatable), e.g. '
+                    "--set cp_comm_type=allgather --set cpu_offloading=true --set offload_modules='[\"core_attn\"]'")
     return ap.parse_args(argv)
+
+
+def parse_overrides(items) -> Dict[str, object]:
+    """``FIELD=VALUE`` strings -> dict; values are read as JSON (``true``, ``3``, ``[1, 2]``, ``"text"``), then as a
+    Python literal, and kept as plain text when they are neither."""
+    import ast
+    import json
+    out = {}
+    for item in items or []:
+        if '=' not in item:
+            raise ValueError(f'--set expects FIELD=VALUE, got {item!r}')
+        key, text = item.split('=', 1)
+        key = key.strip().replace('-', '_')
+        try:
+            val = json.loads(text)
+        except ValueError:
+            try:
+                val = ast.literal_eval(text)
+            except (ValueError, SyntaxError):
+                val = text
+        out[key] = val
+    return out
 
 
 def _hf_config(model: str):
@@ -126,6 +151,11 @@ def main(argv=None) -> int:
         kw['params_dtype'] = torch.float32
     if args.recompute_layers > 0:
         kw.update(recompute_granularity='full', recompute_method='block', recompute_num_layers=args.recompute_layers)
+    extra = parse_overrides(args.overrides)
+    unknown = [k for k in extra if k not in ModelConfig.__dataclass_fields__]
+    if unknown:
+        raise SystemExit(f'--set: unknown ModelConfig field(s) {unknown}')
+    kw.update(extra)
     cfg = ModelConfig(**kw)
     tc = TrainConfig(lr=args.lr, weight_decay=args.weight_decay, clip_grad=args.clip_grad, init_seed=args.seed,
                      heartbeat_dir=args.heartbeat_dir)

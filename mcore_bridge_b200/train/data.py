@@ -33,7 +33,8 @@ class SyntheticPackedDataset:
                  packed: bool = True, seg_lo: int = 256, seg_hi: int = 4096, segment_multiple: int = 1,
                  pin: Optional[bool] = None):
         self.vocab_size, self.seq_len, self.mbs = vocab_size, seq_len, micro_batch_size
-        self.packed, self.seg_lo, self.seg_hi = packed, seg_lo, min(seg_hi, seq_len)
+        self.packed, self.seg_hi = packed, min(seg_hi, seq_len)
+        self.seg_lo = min(seg_lo, self.seg_hi)         # sequences shorter than the smallest segment: one segment
         self.segment_multiple = segment_multiple
         self.gen = torch.Generator().manual_seed(seed)
         self.pin = torch.cuda.is_available() if pin is None else pin

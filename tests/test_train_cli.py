@@ -28,3 +28,20 @@ def test_cli_trains_saves_and_resumes(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     lines = [json.loads(l[l.index('{'):]) for l in (r.stdout + r.stderr).splitlines() if '"step"' in l]
     assert [l['step'] for l in lines] == [4]
+
+
+def test_cli_overrides_reach_the_model_config(tmp_path):
+    from mcore_bridge_b200.train.cli import parse_overrides
+    got = parse_overrides(['cp_comm_type=allgather', 'cpu-offloading=true', 'offload_modules=["core_attn", "mlp_norm"]',
+                           'recompute_num_layers=2', "moe_router_dtype='fp32'"])
+    assert got == {'cp_comm_type': 'allgather', 'cpu_offloading': True, 'offload_modules': ['core_attn', 'mlp_norm'],
+                   'recompute_num_layers': 2, 'moe_router_dtype': 'fp32'}
+    env = dict(os.environ, PYTHONPATH=REPO, CUDA_VISIBLE_DEVICES='')
+    base = [sys.executable, '-m', 'mcore_bridge_b200.train.cli', '--model', 'qwen3_tiny', '--dtype', 'fp32', '--seq-len',
+            '64', '--global-batch', '2', '--micro-batch-size', '1', '--steps', '1']
+    r = subprocess.run(base + ['--set', 'fine_grained_activation_offloading=true', '--set',
+                               'offload_modules=["core_attn"]'], env=env, capture_output=True, text=True, timeout=600,
+                       cwd=REPO)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    r = subprocess.run(base + ['--set', 'no_such_field=1'], env=env, capture_output=True, text=True, timeout=600, cwd=REPO)
+    assert r.returncode != 0 and 'no_such_field' in (r.stdout + r.stderr)
