@@ -154,7 +154,7 @@ _WS = {}
 def _workspace(tag: str, numel: int, dtype, device):
     """A symmetric flat tensor of at least ``numel`` elements for the CP group (grown by re-allocation: collective)."""
     from . import dp_comm
-    key = (tag, dtype)
+    key = (tag, dtype, tuple(ps.get_group_ranks('cp')))      # a workspace belongs to one set of peers
     cur = _WS.get(key)
     if cur is None or cur[1].numel() < numel:
         if cur is not None:
