@@ -57,10 +57,10 @@ def test_peer_memory_dp_collectives_two_ranks():
 
 @pytest.mark.skipif(_ngpu() < 2, reason='needs 2 GPUs')
 def test_parallel_layouts_train_like_data_parallel_on_gpus():
-    """TP2 (+SP), PP2 (1F1B over NCCL send / recv), CP2 (peer-memory K/V exchange) and EP2 (fused MoE exchange) train a
-    tiny model on real GPUs to the same losses as plain data parallelism; with 4 GPUs also TP2 x PP2, TP2 x CP2 and
-    TP2 x EP2."""
-    n = 4 if _ngpu() >= 4 else 2
+    """TP2 (+SP), PP2 (1F1B over NCCL send / recv), CP2 (ring attention with the peer-memory K/V exchange) and EP2 (fused
+    MoE exchange) train a tiny model on two real GPUs to the same losses as plain data parallelism.  (Launched with four
+    ranks the worker adds TP2 x PP2, TP2 x CP2 and TP2 x EP2.)"""
+    n = 2
     env = dict(os.environ, NCCL_NVLS_ENABLE='0')
     cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', str(n), '--master-addr',
            '127.0.0.1', '--master-port', '29541', os.path.join(HERE, 'gpu_layouts_worker.py')]
