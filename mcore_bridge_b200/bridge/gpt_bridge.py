@@ -862,6 +862,7 @@ class GPTBridge:
                 sd = {self._modernise_key(k): v for k, v in sd.items()}
             if peft_format:
                 from .peft_bridge import load_adapter
+                sd = {self._peft_key(k, True): v for k, v in sd.items()}
                 load_adapter(self, mg_models, sd, adapter_name)
             else:
                 for _ in self._convert(mg_models, sd, True, tqdm_desc='Loading: '):
@@ -896,6 +897,15 @@ class GPTBridge:
                 return new + key[len(old):]
         return key
 
+    def _peft_key(self, key: str, to_mcore: bool) -> str:
+        """Adapter key as stored on disk <-> the name used internally; families whose checkpoint names differ from
+        the internal ones override it."""
+        return key
+
+    def _peft_module_name(self, name: str) -> str:
+        """Internal linear name -> the name ``adapter_config.json`` lists under ``target_modules``."""
+        return name
+
     @staticmethod
     def _apply_converter(converter, key, value):
         res = converter(key, value)
@@ -922,6 +932,8 @@ class GPTBridge:
                 for k, v in gen:
                     if self.hf_state_dict_mapping and not peft_format:
                         k = self._legacy_key(k)
+                    elif peft_format:
+                        k = self._peft_key(k, False)
                     if converter is not None:
                         for k2, v2 in self._apply_converter(converter, k, v):
                             yield k2, v2
@@ -944,6 +956,7 @@ class GPTBridge:
             from .peft_bridge import hf_target_modules
             targets = hf_target_modules(self, mg_models if isinstance(mg_models, (list, tuple)) else [mg_models],
                                         adapter_name)
+            targets = sorted({self._peft_module_name(t) for t in targets})
         if is_master():
             self._save_config(output_dir, peft_format, mg_models, adapter_name, targets)
         if dist.is_available() and dist.is_initialized():

@@ -46,6 +46,11 @@ def _layer_slots(bridge, layer_idx: int, hf_idx: Optional[int] = None) -> List[T
         slots.append(('self_attention.linear_qkv', 'qkv', ap, ['q_proj', 'k_proj', 'v_proj']))
         slots.append(('self_attention.g_proj', 'column', ap, ['g_proj']))
         slots.append(('self_attention.linear_proj', 'row', ap, ['o_proj']))
+    elif cfg.experimental_attention_variant == 'dsv4_hybrid':
+        slots.append(('self_attention.linear_q_down_proj', 'replicated', ap, ['wq_a']))
+        slots.append(('self_attention.linear_q_up_proj', 'column', ap, ['wq_b']))
+        slots.append(('self_attention.linear_kv_proj', 'replicated', ap, ['wkv']))
+        slots.append(('self_attention.linear_proj', 'row', ap, ['wo_b']))
     elif cfg.multi_latent_attention:
         if cfg.q_lora_rank is None:
             slots.append(('self_attention.linear_q_proj', 'column', ap, ['q_proj']))

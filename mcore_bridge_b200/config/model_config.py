@@ -249,11 +249,16 @@ class ModelConfig:
         self._format_config()
         # options that exist in the reference's config but have no implementation here are refused instead of being
         # silently ignored
-        if self.experimental_attention_variant == 'dsv4_hybrid' or any(self.csa_compress_ratios or []):
+        if any(self.csa_compress_ratios or []):
             raise NotImplementedError(
-                'compressed sparse attention (DeepSeek-V4 hybrid attention) is not implemented: the reference takes it '
-                'from a Megatron-Core development branch that is not part of its own source tree.  The other '
-                'DeepSeek-V4 pieces (hyper-connections, hash-routed MoE layers) are available on their own.')
+                'compressed attention layers (non-zero csa_compress_ratios: the compressed-sparse and heavily-'
+                'compressed layers of DeepSeek-V4) are not implemented: the reference takes their core attention from '
+                'a '
+                'Megatron-Core development branch that is not part of its own source tree.  Sliding-window layers '
+                '(ratio 0), hyper-connections and hash-routed MoE layers of the family are available.')
+        if self.experimental_attention_variant == 'dsv4_hybrid' and self.mtp_num_layers:
+            raise NotImplementedError('DeepSeek-V4: multi-token-prediction layers over hyper-connection streams are '
+                                      'not implemented; build the model with mtp_num_layers=None')
         if self.fp8_param:
             # weights stay bf16 views of the optimizer's flat buffers; their fp8 copies (and transposes) are cached and
             # re-quantised only when an optimizer step changes the weight (ops/fp8.py: quantized_weight), which gives

@@ -1,1 +1,1 @@
-from . import families, llm, qwen3_next  # noqa: F401
+from . import deepseek_v4, families, llm, qwen3_next  # noqa: F401

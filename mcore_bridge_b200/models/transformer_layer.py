@@ -51,6 +51,10 @@ class TransformerLayer(nn.Module):
             from ..layers.lightning_attention import LightningAttention
             self.input_layernorm = Norm(config, config.hidden_size)
             self.self_attention = LightningAttention(config, layer_number)
+        elif variant == 'dsv4_hybrid':
+            from ..layers.dsv4_attention import DSv4SelfAttention
+            self.input_layernorm = Norm(config, config.hidden_size)
+            self.self_attention = DSv4SelfAttention(config, layer_number)
         elif config.multi_latent_attention:
             from ..layers.mla import MLASelfAttention
             self.input_layernorm = Norm(config, config.hidden_size)

@@ -64,6 +64,14 @@ class MxFp4Dequantizer:
         return out.flatten(-2).to(dtype)
 
 
+def fp4_e2m1_to_float(packed: torch.Tensor) -> torch.Tensor:
+    """``[..., n]`` bytes (int8 / uint8) holding two e2m1 values each, low nibble first -> fp32 ``[..., 2 n]``
+    (unscaled; parity: reference ``src/mcore_bridge/utils/dequantizer.py:67-79``)."""
+    lut = torch.tensor(_FP4_VALUES, dtype=torch.float32, device=packed.device)
+    b = packed.contiguous().view(torch.uint8)
+    return torch.stack((lut[(b & 0x0F).long()], lut[(b >> 4).long()]), dim=-1).flatten(-2)
+
+
 def quantize_mxfp4(w: torch.Tensor):
     """Inverse of :class:`MxFp4Dequantizer` (round to nearest e2m1 value, power-of-two scale per 32 values along the
     last dim): returns ``(blocks uint8 [..., G, 16], scales uint8 [..., G])``.  Used to write MXFP4 checkpoints and

@@ -151,5 +151,7 @@ def test_fine_grained_offloading_moves_saved_tensors_and_keeps_gradients():
 
 def test_unbuilt_options_are_refused():
     import pytest
-    with pytest.raises(NotImplementedError, match='compressed sparse attention'):
-        _cfg(experimental_attention_variant='dsv4_hybrid')
+    with pytest.raises(NotImplementedError, match='compressed attention layers'):
+        _cfg(csa_compress_ratios=[0, 4])
+    with pytest.raises(NotImplementedError, match='multi-token-prediction'):
+        _cfg(experimental_attention_variant='dsv4_hybrid', mtp_num_layers=1)
