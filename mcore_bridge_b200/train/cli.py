@@ -54,6 +54,8 @@ def parse_args(argv=None):
     ap.add_argument('--resume', default=None)
     ap.add_argument('--log-interval', type=int, default=1)
     ap.add_argument('--heartbeat-dir', default=None)
+    ap.add_argument('--overlap-param-gather', action='store_true',
+                    help='overlap the parameter all-gather of a step with the forward pass of the next one')
     ap.add_argument('--set', dest='overrides', action='append', default=[], metavar='FIELD=VALUE',
                     help='any other ModelConfig field, value in Python / JSON syntax (repeatable), e.g. '
                     "--set cp_comm_type=allgather --set cpu_offloading=true --set offload_modules='[\"core_attn\"]'")
@@ -158,7 +160,7 @@ def main(argv=None) -> int:
     kw.update(extra)
     cfg = ModelConfig(**kw)
     tc = TrainConfig(lr=args.lr, weight_decay=args.weight_decay, clip_grad=args.clip_grad, init_seed=args.seed,
-                     heartbeat_dir=args.heartbeat_dir)
+                     heartbeat_dir=args.heartbeat_dir, overlap_param_gather=args.overlap_param_gather)
     models = get_mcore_model(cfg)
     if os.path.isdir(args.model) and not args.random_init:
         cfg.bridge.load_weights(models, args.model)
@@ -196,6 +198,7 @@ def main(argv=None) -> int:
             logger.info(json.dumps(rec))
         if args.save and args.save_interval and (step + 1) % args.save_interval == 0 and step + 1 < args.steps:
             save_training_state(trainer, os.path.join(args.save, 'state'), step + 1)
+    trainer.optimizer.finish_param_gather()
     if args.save:
         cfg.bridge.save_weights(trainer.models, args.save, peft_format=args.lora_rank > 0)
         save_training_state(trainer, os.path.join(args.save, 'state'), args.steps)

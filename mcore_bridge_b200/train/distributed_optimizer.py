@@ -270,7 +270,8 @@ class DistributedOptimizer:
     """AdamW on the rank's slice of every bucket; fp32 master weights + moments are allocated only for it."""
 
     def __init__(self, ddp_models: Iterable[DistributedDataParallel], lr: float = 1e-4, betas=(0.9, 0.95),
-                 eps: float = 1e-8, weight_decay: float = 0.1, clip_grad: float = 1.0):
+                 eps: float = 1e-8, weight_decay: float = 0.1, clip_grad: float = 1.0,
+                 overlap_param_gather: bool = False):
         self.models = list(ddp_models)
         self.lr, self.betas, self.eps, self.weight_decay, self.clip_grad = lr, betas, eps, weight_decay, clip_grad
         self.step_count = 0
@@ -293,6 +294,15 @@ class DistributedOptimizer:
         self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.grad_norm = self._norm
         self.grad_scale = 1.0
+        # overlap_param_gather: the all-gather of the updated parameters is issued bucket by bucket in the order the
+        # next forward pass needs them (on a side stream on a GPU, as asynchronous collectives elsewhere) and every
+        # transformer layer waits only for its own buckets
+        self.overlap_param_gather = bool(overlap_param_gather)
+        self._pending: Dict[int, tuple] = {}
+        self._gather_order: List[Tuple[ParamAndGradBuffer, Bucket]] = []
+        self._ag_stream = None
+        if self.overlap_param_gather:
+            self._install_gather_hooks()
 
     def zero_grad(self):
         for m in self.models:
@@ -417,20 +427,109 @@ class DistributedOptimizer:
                 main.addcdiv_(m / (1 - b1**t), denom, value=-self.lr)
                 pshard.copy_(main.to(pshard.dtype))
         # parameter all-gather, bucket by bucket (in place: every rank's slice sits at its final position)
+        if self.overlap_param_gather:
+            self._start_param_gather()
+            return self._norm
         for buf, b, *_ in self.shards:
             if buf.dp > 1:
-                full = buf.param_data[b.start:b.end]
-                s, e = buf.shard_range(b)
-                if full.is_cuda and buf.fused:
-                    from ..parallel import dp_comm
-                    dp_comm.all_gather_(buf.param_ws, buf.param_data, b.start, b.end)
-                elif full.is_cuda:
-                    dist.all_gather_into_tensor(full, buf.param_data[s:e], group=buf.group)
-                else:
-                    parts = [torch.empty_like(buf.param_data[s:e]) for _ in range(buf.dp)]
-                    dist.all_gather(parts, buf.param_data[s:e].clone(), group=buf.group)
-                    full.copy_(torch.cat(parts))
+                self._gather_bucket(buf, b)
         return self._norm
+
+    @staticmethod
+    def _gather_bucket(buf: ParamAndGradBuffer, b: Bucket, async_op: bool = False):
+        full = buf.param_data[b.start:b.end]
+        s, e = buf.shard_range(b)
+        if full.is_cuda and buf.fused:
+            from ..parallel import dp_comm
+            dp_comm.all_gather_(buf.param_ws, buf.param_data, b.start, b.end)
+        elif full.is_cuda:
+            dist.all_gather_into_tensor(full, buf.param_data[s:e], group=buf.group)
+        else:
+            parts = [torch.empty_like(buf.param_data[s:e]) for _ in range(buf.dp)]
+            work = dist.all_gather(parts, buf.param_data[s:e].clone(), group=buf.group, async_op=async_op)
+            if async_op:
+                return work, parts, full
+            full.copy_(torch.cat(parts))
+        return None
+
+    # ------------------------------------------------------------------ overlapped parameter all-gather
+    def _install_gather_hooks(self):
+        """Forward pre-hooks: the model waits for the buckets that hold parameters outside the transformer layers
+        (embedding, head, final norm, towers), each transformer layer for the buckets that hold its own.  The issue
+        order follows the same sequence, so on a GPU a layer's wait never covers a later layer's bucket."""
+        from ..models.transformer_layer import TransformerLayer
+        for model in self.models:
+            p2b = {}
+            for buf in model.buffers.values():
+                if buf.dp > 1:
+                    for p, b in buf.param_to_bucket.items():
+                        p2b[p] = (buf, b)
+            layers = [m for m in model.module.modules() if isinstance(m, TransformerLayer)]
+            in_layer = set()
+            per_layer = []
+            for lay in layers:
+                own = []
+                for p in lay.parameters():
+                    in_layer.add(p)
+                    if p in p2b and p2b[p] not in own:
+                        own.append(p2b[p])
+                per_layer.append(own)
+            root = []
+            for p, bb in p2b.items():
+                if p not in in_layer and bb not in root:
+                    root.append(bb)
+            for bb in root + [bb for own in per_layer for bb in own]:
+                if bb not in self._gather_order:
+                    self._gather_order.append(bb)
+
+            def make_hook(buckets):
+                ids = [id(b) for _, b in buckets]
+
+                def hook(module, args):
+                    if self._pending:
+                        self._wait_buckets(ids)
+                return hook
+
+            model.module.register_forward_pre_hook(make_hook(root))
+            for lay, own in zip(layers, per_layer):
+                lay.register_forward_pre_hook(make_hook(own))
+
+    def _start_param_gather(self):
+        self.finish_param_gather()
+        on_gpu = self.device.type == 'cuda'
+        if on_gpu:
+            if self._ag_stream is None:
+                self._ag_stream = torch.cuda.Stream()
+            self._ag_stream.wait_stream(torch.cuda.current_stream())
+        for buf, b in self._gather_order:
+            if on_gpu:
+                with torch.cuda.stream(self._ag_stream):
+                    self._gather_bucket(buf, b)
+                    ev = torch.cuda.Event()
+                    ev.record(self._ag_stream)
+                self._pending[id(b)] = ('event', ev)
+            else:
+                self._pending[id(b)] = ('work',) + self._gather_bucket(buf, b, async_op=True)
+
+    def _wait_buckets(self, ids):
+        for i in ids:
+            item = self._pending.pop(i, None)
+            if item is None:
+                continue
+            if item[0] == 'event':
+                torch.cuda.current_stream().wait_event(item[1])
+            else:
+                _, work, parts, full = item
+                work.wait()
+                with torch.no_grad():
+                    full.copy_(torch.cat(parts))
+
+    def finish_param_gather(self):
+        """Waits for every parameter all-gather still in flight.  Anything that reads parameters without running the
+        model's forward pass (checkpoint export, a hand-written evaluation loop over ``model.parameters()``) calls this
+        first; ``state_dict`` and the next ``step`` do it themselves."""
+        if self._pending:
+            self._wait_buckets(list(self._pending))
 
     def undo_skipped_step(self):
         """After a step whose update the device-side flag suppressed: take the step count back so the bias corrections
@@ -444,6 +543,7 @@ class DistributedOptimizer:
 
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self) -> dict:
+        self.finish_param_gather()
         return {
             'step': self.step_count,
             'shards': [{'main': main, 'exp_avg': m, 'exp_avg_sq': v} for (_, _, _, main, m, v) in self.shards],

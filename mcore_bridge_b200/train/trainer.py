@@ -35,6 +35,7 @@ class TrainConfig:
     clip_grad: float = 1.0
     bucket_mb: float = 256.0
     overlap_grad_reduce: bool = True
+    overlap_param_gather: bool = False     # parameter all-gather of step N overlaps the forward pass of step N + 1
     init_seed: Optional[int] = 1234
     init_std: float = 0.02
     heartbeat_dir: Optional[str] = None    # when set, every step touches this rank's heartbeat file (train/health.py)
@@ -95,7 +96,7 @@ class Trainer:
         sync_shared_embeddings(self.models)
         self.ddp = [DistributedDataParallel(m, self.tc.bucket_mb, self.tc.overlap_grad_reduce) for m in self.models]
         self.optimizer = DistributedOptimizer(self.ddp, self.tc.lr, self.tc.betas, self.tc.eps, self.tc.weight_decay,
-                                              self.tc.clip_grad)
+                                              self.tc.clip_grad, overlap_param_gather=self.tc.overlap_param_gather)
         self.device = next(self.models[0].parameters()).device
         self._copy_stream = torch.cuda.Stream() if self.device.type == 'cuda' else None
         self.h2d_bytes = 0

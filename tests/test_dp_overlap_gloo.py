@@ -46,3 +46,38 @@ def test_overlapped_reduction_equals_reduction_after_backward(tied):
         assert loss_a == loss_b
         assert same, 'overlapped and deferred gradient reduction gave different parameters after one step'
     assert torch.equal(res[0][4], res[1][4]), 'data-parallel ranks hold different parameters after one step'
+
+
+def _gather_worker(rank, world):
+    """Three steps with the parameter all-gather overlapped with the next forward pass against three steps with the
+    all-gather inside ``step``; small buckets so that every layer waits for buckets of its own."""
+    from mcore_bridge_b200.parallel import state as ps
+    from mcore_bridge_b200.train.data import SyntheticPackedDataset
+    from mcore_bridge_b200.train.presets import model_config
+    from mcore_bridge_b200.train.trainer import TrainConfig, Trainer
+    ps.initialize_model_parallel()
+    out = {}
+    for overlap in (True, False):
+        torch.manual_seed(0)
+        cfg = model_config('qwen3_moe_tiny')
+        tr = Trainer(cfg, TrainConfig(lr=1e-3, bucket_mb=0.05, overlap_param_gather=overlap))
+        ds = SyntheticPackedDataset(cfg.padded_vocab_size, 256, seg_lo=32, seg_hi=128, seed=11 + rank, pin=False)
+        losses, in_flight = [], []
+        for _ in range(3):
+            losses.append(tr.train_step([ds.next_microbatch() for _ in range(2)]))
+            in_flight.append(len(tr.optimizer._pending))
+        n_buckets = sum(len(buf.buckets) for m in tr.ddp for buf in m.buffers.values())
+        sd = tr.optimizer.state_dict()                       # waits for what is in flight
+        assert not tr.optimizer._pending and sd['step'] == 3
+        flat = torch.cat([p.detach().float().reshape(-1) for m in tr.models for p in m.parameters()])
+        out[overlap] = (losses, flat, in_flight, n_buckets)
+    return out
+
+
+def test_overlapped_parameter_gather_equals_gather_inside_the_step():
+    res = run_ranks(_gather_worker, 2)
+    for out in res:
+        (la, pa, fa, nb), (lb, pb, fb, _) = out[True], out[False]
+        assert la == lb and torch.equal(pa, pb)
+        assert fb == [0, 0, 0] and fa == [nb, nb, nb] and nb > 4       # every bucket was left in flight by the step
+    assert torch.equal(res[0][True][1], res[1][True][1]), 'data-parallel ranks hold different parameters'
