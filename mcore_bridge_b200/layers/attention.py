@@ -16,6 +16,7 @@ from torch import nn
 from ..ops.attention import attention
 from ..ops.rope import qkv_split_norm_rope
 from ..parallel import state as ps
+from ..utils.profiling import nvtx_range
 from .context import ForwardContext, layer_cp_comm_type
 from .linear import ColumnParallelLinear, LayerNormColumnParallelLinear, RowParallelLinear
 from .norm import Norm
@@ -124,7 +125,8 @@ class SelfAttention(nn.Module):
 
     def forward(self, x: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
         cfg = self.config
-        qkv = self.linear_qkv(x)                                  # [T, local packed qkv]
+        with nvtx_range('qkv'):
+            qkv = self.linear_qkv(x)                              # [T, local packed qkv]
         qpg = self.qpg
         if self.kv_rep > 1:
             from ..parallel import mappings as M
@@ -162,8 +164,10 @@ class SelfAttention(nn.Module):
                 tf_ = t.float()
                 return (tf_ * torch.rsqrt(tf_.pow(2).mean(-1, keepdim=True) + cfg.layernorm_epsilon)).to(t.dtype)
             q, k = unit_rms(q), unit_rms(k)
-        o = self.core_attention(q, k, v, ctx)                     # [T, nq_local, d]
+        with nvtx_range('core_attention'):
+            o = self.core_attention(q, k, v, ctx)                 # [T, nq_local, d]
         o = o.reshape(o.shape[0], -1)
         if gate is not None:
             o = o * torch.sigmoid(gate.reshape(o.shape[0], -1).float()).to(o.dtype)
-        return self.linear_proj(o)
+        with nvtx_range('linear_proj'):
+            return self.linear_proj(o)

@@ -17,6 +17,7 @@ from torch import nn
 from ..ops import gdn as G
 from ..parallel import mappings as M
 from ..parallel import state as ps
+from ..utils.profiling import nvtx_range
 from .context import ForwardContext
 from .linear import LayerNormColumnParallelLinear, RowParallelLinear
 
@@ -66,7 +67,8 @@ class GatedDeltaNet(nn.Module):
 
     def forward(self, x: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
         cp = ps.get_world_size('cp')
-        proj = self.in_proj(x)                                     # [T, nk_local * group_all]
+        with nvtx_range('in_proj'):
+            proj = self.in_proj(x)                                 # [T, nk_local * group_all]
         cu = ctx.cu_seqlens
         if cp > 1:
             proj = M.all_to_all_cp2hp(proj, 'cp')                  # [T * cp (rank-major), cols / cp]
@@ -82,7 +84,8 @@ class GatedDeltaNet(nn.Module):
         b = g[..., self.group_qkvz:self.group_qkvz + self.ratio].reshape(T, nvh)
         a = g[..., self.group_qkvz + self.ratio:].reshape(T, nvh)
         w = self._cp_slice(self.conv1d.weight.squeeze(1), self.group_conv)
-        qkv = G.causal_conv1d_silu(qkv.contiguous(), w, None, cu)
+        with nvtx_range('conv1d'):
+            qkv = G.causal_conv1d_silu(qkv.contiguous(), w, None, cu)
         qkv = qkv.view(T, nk, self.group_conv)
         q = qkv[..., :self.dk]
         k = qkv[..., self.dk:2 * self.dk]
@@ -92,14 +95,18 @@ class GatedDeltaNet(nn.Module):
             q = q.repeat_interleave(self.ratio, dim=1)
             k = k.repeat_interleave(self.ratio, dim=1)
         A_log, dt_bias = self._cp_slice(self.A_log, 1), self._cp_slice(self.dt_bias, 1)
-        gdecay = -A_log.float().exp() * F.softplus(a.float() + dt_bias.float())
-        beta = torch.sigmoid(b.float())
-        o = G.chunk_gated_delta_rule(q.contiguous(), k.contiguous(), v.contiguous(), gdecay, beta, cu)
-        o = G.gated_rmsnorm(o, z, self.out_norm.weight, self.eps).reshape(T, nvh * self.dv)
+        with nvtx_range('g_and_beta'):
+            gdecay = -A_log.float().exp() * F.softplus(a.float() + dt_bias.float())
+            beta = torch.sigmoid(b.float())
+        with nvtx_range('gated_delta_rule'):
+            o = G.chunk_gated_delta_rule(q.contiguous(), k.contiguous(), v.contiguous(), gdecay, beta, cu)
+        with nvtx_range('gated_norm'):
+            o = G.gated_rmsnorm(o, z, self.out_norm.weight, self.eps).reshape(T, nvh * self.dv)
         if cp > 1:
             from ..utils.megatron_utils import cp_gather_index
             inv = torch.empty_like(index)
             inv[index] = torch.arange(index.numel(), device=index.device)
             o = o.index_select(0, inv)                              # back to rank-major order
             o = M.all_to_all_hp2cp(o, 'cp')
-        return self.out_proj(o)
+        with nvtx_range('out_proj'):
+            return self.out_proj(o)

@@ -25,6 +25,7 @@ from ..layers.moe import MoELayer
 from ..layers.norm import Norm
 from ..parallel import mappings as M
 from ..parallel import state as ps
+from ..utils.profiling import nvtx_range
 
 
 def _identity(x):
@@ -84,7 +85,8 @@ class TransformerLayer(nn.Module):
             streams = hidden                                 # [T, n * C]: the sub-layer reads a mix of the streams
             hidden, post, res = hc.pre(streams)
         x = hidden if self.input_layernorm is None else self.input_layernorm(hidden)
-        out = self.self_attention(x, ctx)
+        with nvtx_range('attention'):
+            out = self.self_attention(x, ctx)
         if self.config.post_sublayer_layernorm:
             out = self.self_attention.post_self_attn_layernorm(out)
         if hc is not None:
@@ -98,10 +100,11 @@ class TransformerLayer(nn.Module):
             streams = hidden
             hidden, post, res = hc.pre(streams)
         x = hidden if self.pre_mlp_layernorm is None else self.pre_mlp_layernorm(hidden)
-        if self.is_moe:
-            out = self.mlp(x, ctx.padding_mask, ctx.seg_ids, ctx.num_seqs, ctx.input_ids)
-        else:
-            out = self.mlp(x)
+        with nvtx_range('moe' if self.is_moe else 'mlp'):
+            if self.is_moe:
+                out = self.mlp(x, ctx.padding_mask, ctx.seg_ids, ctx.num_seqs, ctx.input_ids)
+            else:
+                out = self.mlp(x)
         if cfg.post_sublayer_layernorm:
             out = self.mlp.post_mlp_layernorm(out)
         if hc is not None:

@@ -21,6 +21,7 @@ from ..ops.moe import MoEAuxLossAutoScaler
 from ..parallel import state as ps
 from ..utils.logger import get_logger
 from ..utils.megatron_utils import split_cp_inputs
+from ..utils.profiling import _NO_RANGE, DeviceTimers, nvtx_range
 from .distributed_optimizer import DistributedDataParallel, DistributedOptimizer
 
 logger = get_logger()
@@ -38,6 +39,7 @@ class TrainConfig:
     overlap_param_gather: bool = False     # parameter all-gather of step N overlaps the forward pass of step N + 1
     init_seed: Optional[int] = 1234
     init_std: float = 0.02
+    device_timers: bool = False            # CUDA-event time of forward+backward and of the optimizer in last_metrics
     heartbeat_dir: Optional[str] = None    # when set, every step touches this rank's heartbeat file (train/health.py)
     heartbeat_timeout_s: float = 60.0
 
@@ -98,6 +100,7 @@ class Trainer:
         self.optimizer = DistributedOptimizer(self.ddp, self.tc.lr, self.tc.betas, self.tc.eps, self.tc.weight_decay,
                                               self.tc.clip_grad, overlap_param_gather=self.tc.overlap_param_gather)
         self.device = next(self.models[0].parameters()).device
+        self.timers = DeviceTimers() if self.tc.device_timers else None
         self._copy_stream = torch.cuda.Stream() if self.device.type == 'cuda' else None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -195,8 +198,10 @@ class Trainer:
                 hb.beat(self.optimizer.step_count, status='peer-failure')
                 raise RankFailure(dead)
         for attempt in range(4):
-            total = self._forward_backward(mbs)
-            grad_norm = self.optimizer.step()
+            with nvtx_range('forward_backward'), self._timed('forward_backward'):
+                total = self._forward_backward(mbs)
+            with nvtx_range('optimizer'), self._timed('optimizer'):
+                grad_norm = self.optimizer.step()
             # every rank holds cp x its share of its micro-batches' loss: the mean over the dp x cp group is the step's
             # loss
             if ps.get_world_size('dp_cp') > 1:
@@ -224,6 +229,9 @@ class Trainer:
             logger.warning(f'MoE receive buffer overflowed; capacity factor raised to {factor}, repeating the step')
         self._after_step()
         self.last_metrics = {'loss': float(host[0]), 'grad_norm': float(host[1])}
+        if self.timers is not None:             # device time of the two phases of this step (CUDA events)
+            for name, rec in self.timers.summary().items():
+                self.last_metrics[f'{name}_ms'] = rec['total_ms']
         from ..layers.mtp import get_mtp_losses
         for k, (sm, c) in list(get_mtp_losses().items()):
             self.last_metrics[f'mtp_{k + 1}_loss'] = float(sm) / max(c, 1)
@@ -233,6 +241,9 @@ class Trainer:
             self.last_metrics[k] = float(s) / max(c, 1)
         aux.clear()
         return self.last_metrics['loss']
+
+    def _timed(self, name: str):
+        return self.timers.time(name) if self.timers is not None else _NO_RANGE
 
     def _heartbeat(self):
         if self._hb is None:

@@ -2,8 +2,10 @@
 
 The reference only wraps a few ops in ``nvtx_range_push/pop``
 (``src/mcore_bridge/model/modules/gated_delta_net.py:190-377``);
-here every layer-level op can be wrapped with :func:`nvtx_range`, and :class:`DeviceTimers` accumulates per-name
-device time (events are resolved lazily at ``summary()`` so measuring does not synchronise the step).
+here the layer-level ops (attention block: ``qkv`` / ``qk_norm_rope`` / ``core_attention`` / ``linear_proj``; the
+gated-DeltaNet stages; ``mlp`` / ``moe``; the trainer's ``forward_backward`` / ``optimizer``) sit inside
+:func:`nvtx_range`, and :class:`DeviceTimers` accumulates per-name device time (events are resolved lazily at
+``summary()`` so measuring does not synchronise the step).
 """
 from __future__ import annotations
 
@@ -22,16 +24,41 @@ def set_nvtx(enabled: bool):
     _ENABLED = bool(enabled)
 
 
-@contextmanager
+class _NoRange:
+    """What :func:`nvtx_range` returns while tracing is off: entering and leaving it does nothing."""
+    __slots__ = ()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+class _Range:
+    __slots__ = ('name',)
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
+_NO_RANGE = _NoRange()
+
+
 def nvtx_range(name: str):
+    """``with nvtx_range('core_attention'): ...`` — an NVTX range when tracing is on (``MCB200_NVTX=1`` or
+    :func:`set_nvtx`) and CUDA is present, otherwise a shared do-nothing object (no allocation on the hot path)."""
     if _ENABLED and torch.cuda.is_available():
-        torch.cuda.nvtx.range_push(name)
-        try:
-            yield
-        finally:
-            torch.cuda.nvtx.range_pop()
-    else:
-        yield
+        return _Range(name)
+    return _NO_RANGE
 
 
 class DeviceTimers:
