@@ -101,6 +101,12 @@ class Trainer:
                                               self.tc.clip_grad, overlap_param_gather=self.tc.overlap_param_gather)
         self.device = next(self.models[0].parameters()).device
         self.timers = DeviceTimers() if self.tc.device_timers else None
+        # MCB200_CHECK_COLLECTIVES=1: every collective is compared across its group on the host before it is launched
+        self._collective_checker = None
+        from ..parallel import collective_check
+        if collective_check.enabled_by_env() and dist.is_available() and dist.is_initialized() \
+                and dist.get_world_size() > 1:
+            self._collective_checker = collective_check.CollectiveOrderChecker().install()
         self._copy_stream = torch.cuda.Stream() if self.device.type == 'cuda' else None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
