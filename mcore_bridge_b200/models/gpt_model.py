@@ -118,7 +118,16 @@ class GPTModel(nn.Module):
         cp = ps.get_world_size('cp')
         T = batch * seq
         if packed_seq_params is not None and packed_seq_params.cu_seqlens_q is not None:
-            cu = packed_seq_params.cu_seqlens_q.to(device=device, dtype=torch.int32)
+            src = packed_seq_params.cu_seqlens_q
+            cu = src.to(device=device, dtype=torch.int32)
+            if cu is not src:
+                # keep the boundaries readable on the host: from the caller's host copy if it is one, else from the
+                # values a previous copy already carries
+                if src.device.type == 'cpu':
+                    from ..utils.torch_utils import attach_host_list
+                    attach_host_list(cu, src)
+                elif getattr(src, '_host_list', None) is not None:
+                    cu._host_list = src._host_list
             max_len = packed_seq_params.max_seqlen_q
         else:
             cu = torch.arange(0, (batch + 1) * seq * cp, seq * cp, dtype=torch.int32, device=device)

@@ -16,6 +16,7 @@ Transformers' ``torch_chunk_gated_delta_rule`` (``modeling_qwen3_next.py``) and 
 """
 from __future__ import annotations
 
+import functools
 from typing import List, Optional, Tuple
 
 import torch
@@ -30,7 +31,8 @@ def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
 def _bounds(cu_seqlens: Optional[torch.Tensor], T: int) -> List[Tuple[int, int]]:
     if cu_seqlens is None:
         return [(0, T)]
-    b = [int(x) for x in cu_seqlens.tolist()]
+    from ..utils.torch_utils import host_list
+    b = host_list(cu_seqlens)
     return [(s, e) for s, e in zip(b[:-1], b[1:]) if e > s]
 
 
@@ -84,35 +86,59 @@ def _chunk_one_sequence(q, k, v, g, beta, chunk: int):
     return torch.stack(outs, dim=1).reshape(h, n * chunk, dv)[:, :L]
 
 
+class _ChunkPlan:
+    """Host-side layout of a packed batch for the chunked rule, with its index tensors on the device."""
+    __slots__ = ('total', 'n_seq', 'tok_idx', 'slot_idx', 'first', 'alive', 'identity')
+
+
+@functools.lru_cache(maxsize=16)
+def _chunk_plan(bounds: Tuple[Tuple[int, int], ...], T: int, chunk: int, device: str) -> _ChunkPlan:
+    """Sequences sorted by length (longest first) and padded to whole chunks: token -> slot indices, first chunk of
+    every sequence, and how many sequences are still running at every chunk position.  Sorting makes "the sequences
+    still running" a prefix, so the recurrence slices instead of asking the device which ones are left; the plan is
+    cached because every layer of a step sees the same batch."""
+    dev = torch.device(device)
+    order = sorted(range(len(bounds)), key=lambda j: -(bounds[j][1] - bounds[j][0]))
+    tok, slot, first, counts, off = [], [], [], [], 0
+    for j in order:
+        s, e = bounds[j]
+        n = -(-(e - s) // chunk)
+        tok.append(torch.arange(s, e))
+        slot.append(torch.arange(off * chunk, off * chunk + (e - s)))
+        first.append(off)
+        counts.append(n)
+        off += n
+    p = _ChunkPlan()
+    p.total, p.n_seq = off, len(order)
+    tok_idx = torch.cat(tok) if tok else torch.zeros(0, dtype=torch.int64)
+    slot_idx = torch.cat(slot) if slot else torch.zeros(0, dtype=torch.int64)
+    p.identity = tok_idx.numel() == T == off * chunk and bool((tok_idx == slot_idx).all())
+    p.tok_idx, p.slot_idx = tok_idx.to(dev), slot_idx.to(dev)
+    p.first = torch.tensor(first, dtype=torch.int64).to(dev)
+    p.alive = tuple(sum(1 for n in counts if n > i) for i in range(max(counts) if counts else 0))
+    return p
+
+
 def chunk_gated_delta_rule(q, k, v, g, beta, cu_seqlens=None, scale: Optional[float] = None, chunk: int = 64):
     """Chunked evaluation; same signature and result as :func:`recurrent_gated_delta_rule`.
 
     All sequences are processed together: every sequence is padded to a whole number of chunks, the intra-chunk
     quantities (decay matrix, WY solve, intra-chunk attention) are one batched computation over all chunks, and the
     state recurrence runs over the chunk *position inside its sequence*, i.e. ``max_len / chunk`` steps of batched
-    matmuls over the sequences still alive, rather than one step per chunk of the packed stream."""
+    matmuls over the sequences still running, rather than one step per chunk of the packed stream.  Apart from reading
+    the sequence boundaries, nothing in here waits for the device."""
     T, h, dk = q.shape
     dv = v.shape[-1]
     dev = q.device
     scale = dk**-0.5 if scale is None else scale
-    bounds = _bounds(cu_seqlens, T)
-    n_chunks = [-(-(e - s) // chunk) for s, e in bounds]
-    total = sum(n_chunks)
-    # token -> slot in the chunk-padded layout
-    slot = torch.empty(T, dtype=torch.int64, device=dev)
-    first_chunk, off = [], 0
-    for (s, e), n in zip(bounds, n_chunks):
-        slot[s:e] = torch.arange(off * chunk, off * chunk + (e - s), device=dev)
-        first_chunk.append(off)
-        off += n
-    covered = torch.zeros(T, dtype=torch.bool, device=dev)
-    for s, e in bounds:
-        covered[s:e] = True
+    plan = _chunk_plan(tuple(_bounds(cu_seqlens, T)), T, chunk, str(dev))
+    total = plan.total
 
-    def pad(x, fill=0.0):
-        out = x.new_full((total * chunk, *x.shape[1:]), fill, dtype=torch.float32)
-        out[slot[covered]] = x[covered].float()
-        return out
+    def pad(x):
+        if plan.identity:
+            return x.float()
+        out = x.new_zeros((total * chunk, *x.shape[1:]), dtype=torch.float32)
+        return out.index_copy(0, plan.slot_idx, x.float().index_select(0, plan.tok_idx))
 
     qp = (pad(q) * scale).view(total, chunk, h, dk).permute(0, 2, 1, 3)          # [N, h, C, dk]
     kp = pad(k).view(total, chunk, h, dk).permute(0, 2, 1, 3)
@@ -130,22 +156,23 @@ def chunk_gated_delta_rule(q, k, v, g, beta, cu_seqlens=None, scale: Optional[fl
     q_dec = qp * gc.exp()[..., None]
     g_last = gc[..., -1]                                                          # [N, h]
     k_dec = kp * (g_last[..., None] - gc).exp()[..., None]
-    out = torch.empty(total, h, chunk, dv, dtype=torch.float32, device=dev)
-    n_seq = len(bounds)
-    S = torch.zeros(n_seq, h, dk, dv, dtype=torch.float32, device=dev)
-    first = torch.tensor(first_chunk, dtype=torch.int64, device=dev)
-    counts = torch.tensor(n_chunks, dtype=torch.int64, device=dev)
-    for i in range(max(n_chunks) if n_chunks else 0):
-        alive = (counts > i).nonzero(as_tuple=True)[0]
-        ci = first[alive] + i                                                     # chunk ids processed this step
-        Si = S[alive]
+    S = torch.zeros(plan.n_seq, h, dk, dv, dtype=torch.float32, device=dev)
+    outs, ids = [], []
+    for i, m in enumerate(plan.alive):
+        ci = plan.first[:m] + i                                                   # chunk ids processed this step
+        Si = S[:m]
         v_new = u[ci] - w[ci] @ Si
-        out[ci] = q_dec[ci] @ Si + qk[ci] @ v_new
-        S = S.index_copy(0, alive, Si * g_last[ci].exp()[..., None, None] + k_dec[ci].transpose(-1, -2) @ v_new)
+        outs.append(q_dec[ci] @ Si + qk[ci] @ v_new)
+        ids.append(ci)
+        S = Si * g_last[ci].exp()[..., None, None] + k_dec[ci].transpose(-1, -2) @ v_new
+    out = torch.zeros(total, h, chunk, dv, dtype=torch.float32, device=dev)
+    if outs:
+        out = out.index_copy(0, torch.cat(ids), torch.cat(outs))
     o_flat = out.permute(0, 2, 1, 3).reshape(total * chunk, h, dv)
+    if plan.identity:
+        return o_flat.to(v.dtype)
     res = torch.zeros(T, h, dv, dtype=torch.float32, device=dev)
-    res[covered] = o_flat[slot[covered]]
-    return res.to(v.dtype)
+    return res.index_copy(0, plan.tok_idx, o_flat.index_select(0, plan.slot_idx)).to(v.dtype)
 
 
 def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,

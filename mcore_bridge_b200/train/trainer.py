@@ -22,6 +22,7 @@ from ..parallel import state as ps
 from ..utils.logger import get_logger
 from ..utils.megatron_utils import split_cp_inputs
 from ..utils.profiling import _NO_RANGE, DeviceTimers, nvtx_range
+from ..utils.torch_utils import attach_host_list
 from .distributed_optimizer import DistributedDataParallel, DistributedOptimizer
 
 logger = get_logger()
@@ -120,6 +121,8 @@ class Trainer:
             if isinstance(v, torch.Tensor):
                 self.h2d_bytes += v.numel() * v.element_size() if v.device.type == 'cpu' else 0
                 out[k] = v.to(self.device, non_blocking=True)
+                if k == 'cu_seqlens':      # the layers that walk the boundaries on the host read them from here
+                    attach_host_list(out[k], v)
             else:
                 out[k] = v
         return out

@@ -18,6 +18,7 @@ import torch
 import torch.distributed as dist
 
 from ..parallel import state as ps
+from .torch_utils import host_list
 
 
 def unwrap_model(models, module_instances=None):
@@ -62,7 +63,7 @@ def split_cp_inputs(inputs: torch.Tensor, cu_seqlens: Optional[torch.Tensor], di
         return inputs
     if dim < 0:
         dim += inputs.ndim
-    bounds = [0, inputs.shape[dim]] if cu_seqlens is None else [int(x) for x in cu_seqlens.tolist()]
+    bounds = [0, inputs.shape[dim]] if cu_seqlens is None else host_list(cu_seqlens)
     idx = []
     for s, e in zip(bounds[:-1], bounds[1:]):
         n = e - s
@@ -77,7 +78,7 @@ def split_cp_inputs(inputs: torch.Tensor, cu_seqlens: Optional[torch.Tensor], di
 def cp_gather_index(cu_seqlens: Optional[torch.Tensor], total: int, cp_size: int) -> torch.Tensor:
     """``index[j]`` = position in the rank-major concatenation ``[rank0 tokens | rank1 tokens | ...]`` of the
     ``j``-th token of the original stream (used to undo the zig-zag after an all-gather)."""
-    bounds = [0, total] if cu_seqlens is None else [int(x) for x in cu_seqlens.tolist()]
+    bounds = [0, total] if cu_seqlens is None else host_list(cu_seqlens)
     local_total = total // cp_size
     out = torch.empty(total, dtype=torch.int64)
     local_off = 0
@@ -158,7 +159,7 @@ def roll_tensor(tensor: torch.Tensor, shifts: int = -1, dims: int = -1, cp_group
         return rolled, rolled.sum()
     rank = dist.get_rank(cp_group)
     # local layout per sequence: [front chunk r | tail chunk 2cp-1-r], each of length c_i
-    bounds = [0, T * cp_size] if cu is None else [int(x) for x in cu.tolist()]
+    bounds = [0, T * cp_size] if cu is None else host_list(cu)
     starts, lens = [], []
     off = 0
     for s, e in zip(bounds[:-1], bounds[1:]):

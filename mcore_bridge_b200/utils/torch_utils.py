@@ -105,3 +105,21 @@ def to_device(data: Any, device, non_blocking: bool = False) -> Any:
     if isinstance(data, torch.Tensor):
         return data.to(device=device, non_blocking=non_blocking)
     return data
+
+
+def host_list(t: torch.Tensor):
+    """Values of a small integer tensor (sequence boundaries) as a Python list.  A device tensor that was copied from
+    host memory can carry the host values in ``_host_list`` (:func:`attach_host_list`); reading them from there does
+    not wait for the device, ``tolist()`` on a device tensor does."""
+    cached = getattr(t, '_host_list', None)
+    if cached is not None:
+        return list(cached)
+    return [int(x) for x in t.tolist()]
+
+
+def attach_host_list(device_tensor: torch.Tensor, host_tensor: torch.Tensor) -> torch.Tensor:
+    """Remember the values of ``host_tensor`` on its device copy (see :func:`host_list`)."""
+    if host_tensor.device.type == 'cpu' and host_tensor.numel() <= 1 << 16:
+        device_tensor._host_list = tuple(int(x) for x in host_tensor.tolist())
+    return device_tensor
+
