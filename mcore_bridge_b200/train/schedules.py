@@ -102,11 +102,17 @@ def _forward(trainer, model, d: Dict, input_tensor: Optional[torch.Tensor], n_mi
 
 def _pipeline_width(trainer) -> int:
     """Columns of the tensor sent between stages: the hidden size, or what the model declares when it sends more than
-    the hidden states (Gemma-4 packs its per-layer inputs and shared keys / values behind them)."""
+    the hidden states (Gemma-4 packs its per-layer inputs and shared keys / values behind them; with hyper-connections
+    the residual streams travel side by side)."""
     m = trainer.models[0]
     m = getattr(m, 'language_model', m)
     fn = getattr(m, 'pipeline_width', None)
-    return int(fn()) if fn is not None else trainer.config.hidden_size
+    if fn is not None:
+        return int(fn())
+    cfg = trainer.config
+    if cfg.enable_hyper_connections:          # all residual streams cross the boundary side by side
+        return cfg.hidden_size * int(cfg.num_residual_streams)
+    return cfg.hidden_size
 
 
 def _backward(output: torch.Tensor, grad: Optional[torch.Tensor], input_tensor: Optional[torch.Tensor]):

@@ -200,16 +200,17 @@ def test_fp4_and_fp8_expert_weights_are_dequantised_on_load(tmp_path):
 
 
 # ------------------------------------------------------------------ parallel layouts against one process (gloo)
-def _train_worker(rank, world, ckpt, tp, ep, cp):
+def _train_worker(rank, world, ckpt, tp, ep, cp, pp=1):
     from mcore_bridge_b200 import ModelConfig, hf_to_mcore_config
     from mcore_bridge_b200.parallel import state as ps
     from mcore_bridge_b200.train.data import SyntheticPackedDataset
     from mcore_bridge_b200.train.trainer import TrainConfig, Trainer
     ps.initialize_model_parallel(tensor_model_parallel_size=tp, expert_model_parallel_size=ep,
-                                 expert_tensor_parallel_size=1, context_parallel_size=cp)
+                                 expert_tensor_parallel_size=1, context_parallel_size=cp,
+                                 pipeline_model_parallel_size=pp)
     cfg = ModelConfig(**hf_to_mcore_config(_hf_config()), params_dtype=torch.float32, tensor_model_parallel_size=tp,
                       expert_model_parallel_size=ep, expert_tensor_parallel_size=1, context_parallel_size=cp,
-                      sequence_parallel=tp > 1, moe_aux_loss_coeff=1e-2)
+                      pipeline_model_parallel_size=pp, sequence_parallel=tp > 1, moe_aux_loss_coeff=1e-2)
     tr = Trainer(cfg, TrainConfig(lr=1e-3, init_seed=None, clip_grad=1.0))
     cfg.bridge.load_weights(tr.models, ckpt)
     tr.optimizer = type(tr.optimizer)(tr.ddp, 1e-3, eps=1e-3, clip_grad=1.0)
@@ -225,7 +226,7 @@ def _train_worker(rank, world, ckpt, tp, ep, cp):
 _SINGLE = {}
 
 
-def _check_layout(tmp_path, tp=1, ep=1, cp=1):
+def _check_layout(tmp_path, tp=1, ep=1, cp=1, pp=1):
     from dist_utils import run_ranks
     cfg, model = _model()
     d = str(tmp_path / 'ckpt')
@@ -233,7 +234,7 @@ def _check_layout(tmp_path, tp=1, ep=1, cp=1):
     if 'base' not in _SINGLE:
         _SINGLE['base'] = run_ranks(_train_worker, 1, d, 1, 1, 1)[0]
     base_losses, base_w = _SINGLE['base']
-    for losses, weights in run_ranks(_train_worker, 4, d, tp, ep, cp):
+    for losses, weights in run_ranks(_train_worker, 4, d, tp, ep, cp, pp):
         for a, b in zip(losses, base_losses):
             assert abs(a - b) < 3e-5, (losses, base_losses)
         assert set(weights) == set(base_w)
@@ -286,3 +287,10 @@ def test_lora_adapter_round_trip_uses_disk_names(tmp_path):
     ids = torch.randint(0, 512, (1, 24), generator=torch.Generator().manual_seed(1))
     with torch.no_grad():
         assert torch.equal(peft.eval()(ids), peft2.eval()(ids))
+
+
+def test_pp2_tp2_matches_single_process(tmp_path):
+    """The streams of the hyper-connections cross the stage boundary; the hash-routed layer sits on the first stage, the
+    streams' output contraction on the last; the checkpoint walk agrees across stages on which layers route by hash."""
+    _check_layout(tmp_path, tp=2, pp=2)
+
