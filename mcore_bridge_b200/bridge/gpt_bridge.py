@@ -832,6 +832,13 @@ class GPTBridge:
         ``enorm`` / ``hnorm`` / ``eh_proj`` and an ordinary transformer layer (DeepSeek-V3 convention)."""
         cfg = self.config
         mtp = model.mtp if (model is not None and getattr(model, 'mtp', None) is not None) else None
+        if to_mcore and mtp is not None and not getattr(model, 'pre_process', False) \
+                and getattr(model, 'embedding', None) is not None:
+            # under pipeline parallelism the last stage looks the MTP depths' tokens up in an embedding of its own:
+            # a second copy of the first stage's matrix
+            rows = self._vocab_rows()
+            self._direct(model.embedding.word_embeddings, 'weight', hf_sd, self.hf_embed_key, True, tp_dim=0,
+                         to_mg=lambda w: self._pad_vocab(w, rows))
         for k in range(cfg.mtp_num_layers):
             prefix = f'{self.hf_layers_prefix}.{cfg.num_layers + k}.'
             lay = mtp.layers[k] if mtp is not None else None
@@ -922,6 +929,8 @@ class GPTBridge:
         self._peft_format, self._adapter_name = peft_format, adapter_name
         if not isinstance(mg_models, (list, tuple)):
             mg_models = [mg_models]
+        from ..train.distributed_optimizer import finish_all_param_gathers
+        finish_all_param_gathers()        # an overlapped parameter all-gather may still be writing the weights
         try:
             if peft_format:
                 from .peft_bridge import export_adapter

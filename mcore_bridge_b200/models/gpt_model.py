@@ -70,28 +70,36 @@ class GPTModel(nn.Module):
             if task == 'causal_lm' or task == 'generative_reranker':
                 self.output_layer = ColumnParallelLinear(config.hidden_size, self.vocab_size, config, bias=False,
                                                          sequence_parallel=False, fp8=False)
-                if self.share_embeddings_and_output_weights and pre_process:
+                extra = int(config.mtp_unroll_steps or config.mtp_num_layers or 0) if self.mtp is not None else 0
+                # the last pipeline stage of a model with MTP holds an embedding of its own (the MTP depths look their
+                # tokens up): with tied weights it is the head's matrix there too
+                tie_here = self.share_embeddings_and_output_weights and self.embedding is not None
+                if tie_here:
                     self.output_layer.weight = self.embedding.word_embeddings.weight
                     # embedding lookup and head (and, per MTP depth, one more of each) produce a gradient for this
                     # tensor in every backward pass; the bucket waits for all of them
-                    self.output_layer.weight.grad_contributions = 2 + 2 * (
-                        int(config.mtp_unroll_steps or config.mtp_num_layers or 0) if self.mtp is not None else 0)
+                    self.output_layer.weight.grad_contributions = (1 if pre_process else 0) + 1 + 2 * extra
                 elif self.mtp is not None:
                     # untied, with MTP: every depth looks up the embedding and applies the head once more
-                    extra = int(config.mtp_unroll_steps or config.mtp_num_layers or 0)
                     self.output_layer.weight.grad_contributions = 1 + extra
                     if self.embedding is not None:
                         self.embedding.word_embeddings.weight.grad_contributions = (1 if pre_process else 0) + extra
             elif task == 'seq_cls':
                 self.output_layer = ReplicatedLinear(config.hidden_size, config.num_labels, config, bias=False,
                                                      sequence_parallel_grad=False)
-        if self.share_embeddings_and_output_weights and ps.get_pipeline_model_parallel_world_size() > 1:
-            # the stages at the two ends of the pipeline each hold a copy of the tied matrix
-            if pre_process and self.embedding is not None:
+        if ps.get_pipeline_model_parallel_world_size() > 1:
+            lm_head = post_process and self.output_layer is not None and \
+                config.task_type in ('causal_lm', 'generative_reranker')
+            if self.share_embeddings_and_output_weights:
+                # the stages at the two ends of the pipeline each hold a copy of the tied matrix
+                if pre_process and self.embedding is not None:
+                    self.embedding.word_embeddings.weight.shared_embedding = True
+                if post_process and not pre_process and lm_head:
+                    self.output_layer.weight.shared_embedding = True
+            elif config.mtp_num_layers and self.embedding is not None and (pre_process or post_process):
+                # untied, with MTP: the embedding exists on the first stage and, for the MTP depths, on the last one;
+                # the two copies sum their gradients like a tied pair
                 self.embedding.word_embeddings.weight.shared_embedding = True
-            if post_process and not pre_process and self.output_layer is not None and \
-                    config.task_type in ('causal_lm', 'generative_reranker'):
-                self.output_layer.weight.shared_embedding = True
         self._extra_tables: Dict[str, RotaryEmbedding] = {}
 
     # ------------------------------------------------------------------ pipeline plumbing

@@ -266,6 +266,17 @@ class DistributedDataParallel(nn.Module):
         return self.module.load_state_dict(*a, **k)
 
 
+_WITH_PENDING_GATHERS = None      # weak set of optimizers created with overlap_param_gather
+
+
+def finish_all_param_gathers() -> None:
+    """Waits for the overlapped parameter all-gathers of every live optimizer; the checkpoint bridge calls it before
+    it reads parameters.  A no-op unless an optimizer was built with ``overlap_param_gather``."""
+    if _WITH_PENDING_GATHERS:
+        for opt in list(_WITH_PENDING_GATHERS):
+            opt.finish_param_gather()
+
+
 class DistributedOptimizer:
     """AdamW on the rank's slice of every bucket; fp32 master weights + moments are allocated only for it."""
 
@@ -303,6 +314,11 @@ class DistributedOptimizer:
         self._ag_stream = None
         if self.overlap_param_gather:
             self._install_gather_hooks()
+            global _WITH_PENDING_GATHERS
+            if _WITH_PENDING_GATHERS is None:
+                import weakref
+                _WITH_PENDING_GATHERS = weakref.WeakSet()
+            _WITH_PENDING_GATHERS.add(self)
 
     def zero_grad(self):
         for m in self.models:
@@ -526,8 +542,8 @@ class DistributedOptimizer:
 
     def finish_param_gather(self):
         """Waits for every parameter all-gather still in flight.  Anything that reads parameters without running the
-        model's forward pass (checkpoint export, a hand-written evaluation loop over ``model.parameters()``) calls this
-        first; ``state_dict`` and the next ``step`` do it themselves."""
+        model's forward pass (a hand-written loop over ``model.parameters()``) calls this first; ``state_dict``, the
+        next ``step`` and the checkpoint bridge's export do it themselves."""
         if self._pending:
             self._wait_buckets(list(self._pending))
 

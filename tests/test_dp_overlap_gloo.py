@@ -81,3 +81,30 @@ def test_overlapped_parameter_gather_equals_gather_inside_the_step():
         assert la == lb and torch.equal(pa, pb)
         assert fb == [0, 0, 0] and fa == [nb, nb, nb] and nb > 4       # every bucket was left in flight by the step
     assert torch.equal(res[0][True][1], res[1][True][1]), 'data-parallel ranks hold different parameters'
+
+
+def _export_worker(rank, world):
+    """The checkpoint bridge reads parameters without running the model: with the all-gather still in flight it has to
+    wait for it itself."""
+    from mcore_bridge_b200.parallel import state as ps
+    from mcore_bridge_b200.train.data import SyntheticPackedDataset
+    from mcore_bridge_b200.train.presets import model_config
+    from mcore_bridge_b200.train.trainer import TrainConfig, Trainer
+    ps.initialize_model_parallel()
+    out = {}
+    for overlap in (True, False):
+        torch.manual_seed(0)
+        cfg = model_config('qwen3_tiny')
+        tr = Trainer(cfg, TrainConfig(lr=1e-3, bucket_mb=0.05, overlap_param_gather=overlap))
+        ds = SyntheticPackedDataset(cfg.padded_vocab_size, 256, seg_lo=32, seg_hi=128, seed=11 + rank, pin=False)
+        tr.train_step([ds.next_microbatch() for _ in range(2)])
+        pending = len(tr.optimizer._pending)
+        out[overlap] = ({k: v.clone() for k, v in cfg.bridge.export_weights(tr.models)}, pending)
+    return out
+
+
+def test_export_waits_for_the_overlapped_gather():
+    for out in run_ranks(_export_worker, 2):
+        (wa, pa), (wb, pb) = out[True], out[False]
+        assert pa > 0 and pb == 0
+        assert wa.keys() == wb.keys() and all(torch.equal(wa[k], wb[k]) for k in wa)

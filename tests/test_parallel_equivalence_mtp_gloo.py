@@ -18,17 +18,21 @@ def _config():
                             tie_word_embeddings=False, num_nextn_predict_layers=1)
 
 
-def _worker(rank, world, ckpt, tp, ep, cp, make):
+def _worker(rank, world, ckpt, tp, ep, cp, make, pp=1, tied=False):
     from mcore_bridge_b200 import ModelConfig, hf_to_mcore_config
     from mcore_bridge_b200.parallel import state as ps
     from mcore_bridge_b200.train.data import SyntheticPackedDataset
     from mcore_bridge_b200.train.trainer import TrainConfig, Trainer
     ps.initialize_model_parallel(tensor_model_parallel_size=tp, expert_model_parallel_size=ep,
-                                 expert_tensor_parallel_size=1, context_parallel_size=cp)
+                                 expert_tensor_parallel_size=1, context_parallel_size=cp,
+                                 pipeline_model_parallel_size=pp)
     kw = hf_to_mcore_config(_config())
     kw.update(mtp_num_layers=1, moe_aux_loss_coeff=1e-2)
+    if tied:
+        kw['untie_embeddings_and_output_weights'] = False
     cfg = ModelConfig(**kw, params_dtype=torch.float32, tensor_model_parallel_size=tp, expert_model_parallel_size=ep,
-                      expert_tensor_parallel_size=1, context_parallel_size=cp, sequence_parallel=tp > 1)
+                      expert_tensor_parallel_size=1, context_parallel_size=cp, pipeline_model_parallel_size=pp,
+                      sequence_parallel=tp > 1)
     tr = Trainer(cfg, TrainConfig(lr=1e-3, init_seed=7, clip_grad=1.0))
     if make:
         cfg.bridge.save_weights(tr.models, ckpt)
@@ -45,19 +49,34 @@ def _worker(rank, world, ckpt, tp, ep, cp, make):
     return losses, weights
 
 
-def _check(tmp_path, layouts):
+def _check(tmp_path, layouts, tied=False):
     d = str(tmp_path / 'ckpt')
-    run_ranks(_worker, 1, d, 1, 1, 1, True)
-    base_losses, base_w = run_ranks(_worker, 1, d, 1, 1, 1, False)[0]
+    run_ranks(_worker, 1, d, 1, 1, 1, True, 1, tied)
+    base_losses, base_w = run_ranks(_worker, 1, d, 1, 1, 1, False, 1, tied)[0]
     assert base_losses[0][1] is not None and any('layers.2.' in k for k in base_w)      # the MTP layer is exported
-    for tp, ep, cp in layouts:
-        for losses, weights in run_ranks(_worker, 4, d, tp, ep, cp, False):
+    for layout in layouts:
+        tp, ep, cp = layout[:3]
+        pp = layout[3] if len(layout) > 3 else 1
+        for losses, weights in run_ranks(_worker, 4, d, tp, ep, cp, False, pp, tied):
             for (a, _), (b, _) in zip(losses, base_losses):
-                assert abs(a - b) < 3e-5, (tp, ep, cp, losses, base_losses)
+                assert abs(a - b) < 3e-5, (layout, losses, base_losses)
+            assert set(weights) == set(base_w)
             for k, v in base_w.items():
-                assert torch.allclose(weights[k], v, rtol=0, atol=2e-6), (tp, ep, cp, k,
+                assert torch.allclose(weights[k], v, rtol=0, atol=2e-6), (layout, k,
                                                                           (weights[k] - v).abs().max().item())
 
 
 def test_mtp_tp2_ep2_and_cp2_match_single_process(tmp_path):
     _check(tmp_path, [(2, 2, 1), (1, 2, 2)])
+
+
+def test_mtp_pp2_tp2_matches_single_process(tmp_path):
+    """The last stage holds an embedding of its own for the MTP depths: a second copy of the first stage's matrix, which
+    the checkpoint load has to fill (tensor-parallel shards: a random init would not match) and whose gradient is
+    summed with the first stage's."""
+    _check(tmp_path, [(2, 1, 1, 2)])
+
+
+def test_mtp_tied_embeddings_pp2_tp2_matches_single_process(tmp_path):
+    """Tied weights: on the last stage the MTP embedding and the head are one tensor, paired with the first stage's."""
+    _check(tmp_path, [(2, 1, 1, 2)], tied=True)
