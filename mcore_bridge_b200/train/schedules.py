@@ -84,8 +84,10 @@ def _forward(trainer, model, d: Dict, input_tensor: Optional[torch.Tensor], n_mi
         input_tensor.requires_grad_(True)
         inner = model.module if hasattr(model, 'module') else model
         inner.set_input_tensor(input_tensor)
+    from .trainer import model_extras
     out = model(input_ids=d['input_ids'], position_ids=d.get('position_ids'), attention_mask=d.get('attention_mask'),
-                labels=d['labels'] if is_last else None, packed_seq_params=_psp(d), loss_mask=d.get('loss_mask'))
+                labels=d['labels'] if is_last else None, packed_seq_params=_psp(d), loss_mask=d.get('loss_mask'),
+                **model_extras(d))
     if is_last:
         mask = d.get('loss_mask')
         if mask is None:

@@ -45,6 +45,16 @@ class TrainConfig:
     heartbeat_timeout_s: float = 60.0
 
 
+_BATCH_KEYS = frozenset({'input_ids', 'labels', 'position_ids', 'attention_mask', 'loss_mask', 'cu_seqlens',
+                         'max_seqlen'})
+
+
+def model_extras(d: Dict) -> Dict:
+    """What a micro-batch holds beyond the text fields (``pixel_values``, ``image_grid_thw``, ``input_features`` ...):
+    passed to the model as keyword arguments, for the multimodal wrappers."""
+    return {k: v for k, v in d.items() if k not in _BATCH_KEYS}
+
+
 @torch.no_grad()
 def init_weights(model: torch.nn.Module, std: float = 0.02, seed: Optional[int] = None):
     """Random init: N(0, std) for matrices (tensor-parallel shards draw from the TP stream, replicated tensors
@@ -147,7 +157,7 @@ class Trainer:
                                   max_seqlen_q=d.get('max_seqlen'), max_seqlen_kv=d.get('max_seqlen'))
         loss_tok = model(input_ids=d['input_ids'], position_ids=d.get('position_ids'),
                          attention_mask=d.get('attention_mask'), labels=d['labels'], packed_seq_params=psp,
-                         loss_mask=d.get('loss_mask'))
+                         loss_mask=d.get('loss_mask'), **model_extras(d))
         mask = d.get('loss_mask')
         if mask is None:
             mask = torch.ones_like(loss_tok)
