@@ -213,10 +213,14 @@ class MLASelfAttention(nn.Module):
         from ..ops import dsa
         T = q.shape[0]
         up = self.linear_kv_up_proj
+        # with a LoRA adapter on this projection the slot holds the wrapper: norm from the wrapped layer, matrix with
+        # the adapter's low-rank update added
+        weight = up.effective_weight() if hasattr(up, 'effective_weight') else up.weight
+        up = getattr(up, 'base_layer', up)
         lat_n = up.norm(kv_lat.contiguous())                                    # normalised latent [T, kv_lora]
         if ps.get_world_size('tp') > 1:       # feeds this rank's heads only: the gradient is a per-rank partial sum
             lat_n = M.copy_to_tensor_model_parallel_region(lat_n, 'tp')
-        W = up.weight.view(self.nh_local, self.qk_nope + self.v_dim, self.kv_lora)
+        W = weight.view(self.nh_local, self.qk_nope + self.v_dim, self.kv_lora)
         q = q.view(T, self.nh_local, self.q_dim)
         q_nope, q_pe = q[..., :self.qk_nope], q[..., self.qk_nope:]
         rope = rope_interleaved_to_half if cfg.mla_rope_interleaved else apply_rope_ref

@@ -23,7 +23,7 @@ from typing import Any, Dict, List, Optional
 import torch
 from torch import nn
 
-from ..layers.linear import LayerNormColumnParallelLinear, RowParallelLinear, _set_tp_attrs
+from ..layers.linear import LayerNormColumnParallelLinear, ReplicatedLinear, RowParallelLinear, _set_tp_attrs
 from ..layers.moe import GroupedLinear, TopKRouter, _GroupedLinearFn
 from ..ops.linear import LinearSpec, linear
 from ..parallel import mappings as M
@@ -99,6 +99,9 @@ class LoraParallelLinear(nn.Module):
         self.is_parallel_a = isinstance(base_layer, RowParallelLinear) or (
             self.is_grouped and base_layer.parallel_mode == 'row')
         self.is_expert = is_expert_layer(base_layer)
+        # a linear replicated over the TP group (MLA down projections, DSA indexer linears): the adapter is replicated
+        # too and runs on whatever tokens the layer sees, without any collective
+        self.is_replicated = isinstance(base_layer, ReplicatedLinear)
         self.sequence_parallel = bool(getattr(base_layer, 'sequence_parallel', False))
         self.group = 'etp' if self.is_expert else 'tp'
         self.tp_size = ps.get_world_size(self.group)
@@ -178,6 +181,12 @@ class LoraParallelLinear(nn.Module):
             # A/B stacked per expert.  Row base: A sees the sharded input; column base: B produces the sharded output.
             a = _LoraFactor((self.num_gemms, r, self.in_features), dt, dev, False, -1, True, False)
             b = _LoraFactor((self.num_gemms, self.out_features, r), dt, dev, False, -1, True, False)
+        elif self.is_replicated:
+            # gradients follow the base weight: summed over the TP group where every rank sees its own tokens
+            # (sequence parallelism), otherwise identical on every rank
+            sum_tp = bool(getattr(w, 'sequence_parallel', False))
+            a = _LoraFactor((r, self.in_features), dt, dev, False, -1, False, sum_tp)
+            b = _LoraFactor((self.out_features, r), dt, dev, False, -1, False, sum_tp)
         elif self.is_parallel_a:
             a = _LoraFactor((r, self.in_features), dt, dev, tp > 1, 1, self.is_expert, False)
             b = _LoraFactor((self.out_features, r), dt, dev, False, -1, self.is_expert, sp)
@@ -225,6 +234,8 @@ class LoraParallelLinear(nn.Module):
         x = self.lora_dropout[name](x).to(a.dtype)
         tp, sp = self.tp_size, self.sequence_parallel
         h = linear(x, a, None, LinearSpec())
+        if self.is_replicated:
+            return h
         if tp > 1 and self.is_parallel_a:                          # partial sums over the input shards
             return M.reduce_scatter_to_sequence_parallel_region(h, self.group) if sp else \
                 M.reduce_from_tensor_model_parallel_region(h, self.group)
@@ -263,8 +274,12 @@ class LoraParallelLinear(nn.Module):
         base = self.base_layer
         if self.is_router:
             return base(x, *args, **kwargs) if not use else self._router_forward(x, *args, **kwargs)
+        # a caller that also wants the normalised input of a fused norm + linear (MLA hands it to the DSA indexer) sets
+        # ``return_layernorm_output`` on whatever module sits in the slot: honoured here like on the bare layer
+        want_norm = bool(self.__dict__.get('return_layernorm_output', False)) and \
+            isinstance(base, LayerNormColumnParallelLinear)
         if isinstance(base, LayerNormColumnParallelLinear):
-            if not use:
+            if not use and not want_norm:
                 base.return_layernorm_output = False
                 return base(x)
             base.return_layernorm_output = True
@@ -275,7 +290,7 @@ class LoraParallelLinear(nn.Module):
         else:
             result = base(x, *args, **kwargs)
         if not use:
-            return result
+            return (result, x) if want_norm else result
         for name in self.active_adapters:
             if name not in self.lora_A:
                 continue
@@ -288,7 +303,19 @@ class LoraParallelLinear(nn.Module):
                     continue
                 delta = linear(h, b, None, LinearSpec())
             result = result + delta * self.scaling[name]
-        return result.to(x.dtype) if result.dtype != x.dtype and x.is_floating_point() else result
+        result = result.to(x.dtype) if result.dtype != x.dtype and x.is_floating_point() else result
+        return (result, x) if want_norm else result
+
+    def effective_weight(self) -> torch.Tensor:
+        """Base weight plus the active adapters' ``scaling * B @ A`` (differentiable in the factors): for callers that
+        use the matrix itself instead of calling the layer (weight-absorbed MLA)."""
+        w = self.base_layer.weight
+        if self.disable_adapters or self.merged:
+            return w
+        for name in self.active_adapters:
+            if name in self.lora_A:
+                w = w + self.get_delta_weight(name)
+        return w
 
     def _router_forward(self, x, *args, **kwargs):
         """Adds the adapter to the gate logits by swapping ``gating`` for the duration of the call

@@ -115,3 +115,45 @@ def test_dsa_gather_path_equals_dense_path(monkeypatch):
     assert abs(res[0][0].item() - res[1][0].item()) < 1e-5
     for a, b in zip(res[0][1:], res[1][1:]):
         assert torch.allclose(a, b, atol=2e-5), (a - b).abs().max()
+
+
+def test_dsa_gather_path_with_lora_equals_dense_path(monkeypatch):
+    """With LoRA adapters on every linear the weight-absorbed path uses base weight + the adapter's low-rank update of
+    the key / value up projection, and the indexer still receives the normalised query latent: same loss and same
+    adapter gradients as the dense-masked formulation."""
+    from transformers import GlmMoeDsaConfig
+
+    from mcore_bridge_b200.layers.context import PackedSeqParams
+    from mcore_bridge_b200.train.trainer import init_weights
+    from mcore_bridge_b200.tuners import LoraConfig, get_peft_model
+    c = GlmMoeDsaConfig(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=4,
+                        q_lora_rank=16, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                        n_routed_experts=4, num_experts_per_tok=2, n_group=1, topk_group=1, moe_intermediate_size=16,
+                        intermediate_size=32, mlp_layer_types=['dense', 'dense'], n_shared_experts=1, vocab_size=64,
+                        max_position_embeddings=128, index_n_heads=2, index_head_dim=16, index_topk=6)
+    ids = torch.randint(0, 64, (1, 48), generator=torch.Generator().manual_seed(2))
+    cu = torch.tensor([0, 20, 48], dtype=torch.int32)
+    pos = torch.cat([torch.arange(20), torch.arange(28)]).reshape(1, -1)
+    psp = PackedSeqParams(cu_seqlens_q=cu, cu_seqlens_kv=cu, max_seqlen_q=28, max_seqlen_kv=28)
+    res = []
+    for min_t in ('100000', '0'):
+        monkeypatch.setenv('MCB200_DSA_GATHER_MIN_T', min_t)
+        cfg = ModelConfig(**hf_to_mcore_config(c), params_dtype=torch.float32)
+        model = get_mcore_model(cfg)[0]
+        init_weights(model, 0.1, 3)
+        peft = get_peft_model(model, LoraConfig(r=4, lora_alpha=8, target_modules='all-linear')).train()
+        g = torch.Generator().manual_seed(9)
+        with torch.no_grad():
+            for n, p in sorted(peft.named_parameters(), key=lambda kv: kv[0]):
+                if 'lora_' in n:
+                    p.copy_(torch.randn(p.shape, generator=g) * 0.1)
+        loss = peft(ids, position_ids=pos, labels=ids, packed_seq_params=psp).mean()
+        loss.backward()
+        # the indexer is not trained through this loss: its adapters get no gradient
+        grads = {n: p.grad.clone() for n, p in peft.named_parameters()
+                 if 'lora_' in n and 'layers.0.self_attention' in n and p.grad is not None}
+        assert any('linear_kv_up_proj.lora_B' in n for n in grads) and all(g_.abs().sum() > 0 for g_ in grads.values())
+        res.append((loss.detach(), grads))
+    assert abs(res[0][0].item() - res[1][0].item()) < 1e-5
+    for n, g_ in res[0][1].items():
+        assert torch.allclose(g_, res[1][1][n], atol=2e-5), (n, (g_ - res[1][1][n]).abs().max())

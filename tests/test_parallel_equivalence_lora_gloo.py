@@ -72,3 +72,64 @@ def test_lora_dense_tp2_dp2_matches_single_process(tmp_path):
 def test_lora_moe_tp2_ep2_matches_single_process(tmp_path):
     from transformers import Qwen3MoeForCausalLM
     _check(tmp_path, 'qwen3_moe_tiny', Qwen3MoeForCausalLM, tp=2, ep=2)
+
+
+# ------------------------------------------------------------------ MLA families: adapters on replicated projections
+def _family_worker(rank, world, ckpt, adapter, tp, ep, save_to=None):
+    from transformers import AutoConfig
+
+    from mcore_bridge_b200 import ModelConfig, get_mcore_model, hf_to_mcore_config
+    from mcore_bridge_b200.parallel import state as ps
+    from mcore_bridge_b200.train.data import SyntheticPackedDataset
+    from mcore_bridge_b200.train.trainer import TrainConfig, Trainer
+    from mcore_bridge_b200.tuners import LoraConfig, get_peft_model
+    ps.initialize_model_parallel(tensor_model_parallel_size=tp, expert_model_parallel_size=ep,
+                                 expert_tensor_parallel_size=1)
+    cfg = ModelConfig(**hf_to_mcore_config(AutoConfig.from_pretrained(ckpt)), params_dtype=torch.float32,
+                      tensor_model_parallel_size=tp, expert_model_parallel_size=ep, expert_tensor_parallel_size=1,
+                      sequence_parallel=tp > 1)
+    models = get_mcore_model(cfg)
+    cfg.bridge.load_weights(models, ckpt)
+    models = [get_peft_model(m, LoraConfig(r=4, lora_alpha=8, target_modules='all-linear')) for m in models]
+    if adapter is None:
+        g = torch.Generator().manual_seed(3)
+        with torch.no_grad():
+            for m in models:
+                for n, p in sorted(m.named_parameters(), key=lambda kv: kv[0]):
+                    if 'lora_' in n:
+                        p.copy_(torch.randn(p.shape, generator=g) * 0.05)
+        cfg.bridge.save_weights(models, save_to, peft_format=True)
+        return None
+    cfg.bridge.load_weights(models, adapter, peft_format=True)
+    tr = Trainer(cfg, TrainConfig(lr=1e-3, init_seed=None, clip_grad=1.0), models=models)
+    tr.optimizer = type(tr.optimizer)(tr.ddp, 1e-3, eps=1e-3, clip_grad=1.0)
+    dp, dp_rank = ps.get_world_size('dp'), ps.get_rank_in('dp') if ps.get_world_size('dp') > 1 else 0
+    ds = SyntheticPackedDataset(256, 256, seg_lo=32, seg_hi=128, seed=3, pin=False, segment_multiple=4)
+    losses = []
+    for _ in range(STEPS):
+        mbs = [ds.next_microbatch() for _ in range(GLOBAL_MB)]
+        losses.append(tr.train_step(mbs[dp_rank::dp]))
+    return losses, {k: v.clone() for k, v in cfg.bridge.export_weights(tr.models, peft_format=True)}
+
+
+def test_lora_glm_dsa_tp2_ep2_matches_single_process(tmp_path):
+    """MLA with a query low-rank path and the DSA indexer: adapters on the replicated down projections (run on this
+    rank's tokens under sequence parallelism, no collective of their own), on the fused norm + up projections (whose
+    normalised input also feeds the indexer) and on the indexer's linears."""
+    import test_parallel_equivalence_families_gloo as Fm
+    hf = Fm._glm_dsa()
+    torch.manual_seed(0)
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            p.normal_(0, 0.05) if p.dim() >= 2 else p.normal_(1.0 if 'norm' in n else 0.0, 0.05)
+    d, a = str(tmp_path / 'ckpt'), str(tmp_path / 'adapter')
+    hf.save_pretrained(d)
+    run_ranks(_family_worker, 1, d, None, 1, 1, a)
+    base_losses, base_w = run_ranks(_family_worker, 1, d, a, 1, 1)[0]
+    assert any('q_a_proj.lora_B' in k for k in base_w) and any('indexer.wq_b.lora_A' in k for k in base_w)
+    for losses, weights in run_ranks(_family_worker, 4, d, a, 2, 2):
+        for x, y in zip(losses, base_losses):
+            assert abs(x - y) < 3e-5, (losses, base_losses)
+        assert set(weights) == set(base_w)
+        for k, v in base_w.items():
+            assert torch.allclose(weights[k], v, rtol=0, atol=2e-6), (k, (weights[k] - v).abs().max().item())
