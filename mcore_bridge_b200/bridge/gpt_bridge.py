@@ -909,6 +909,23 @@ class GPTBridge:
         the internal ones override it."""
         return key
 
+    def _peft_layer_slots(self, layer_idx: int):
+        """Adapter slot table of one layer for families whose layers differ from the generic ones (``None``: the generic
+        table of ``peft_bridge._layer_slots``).  Entries: (path inside the layer, kind, Hugging Face prefix relative to
+        the layer, Hugging Face module names); kind ``custom_col`` re-lays ``lora_B`` through ``_peft_split`` /
+        ``_peft_join``."""
+        return None
+
+    def _peft_model_slots(self):
+        """``(slots, Hugging Face prefix)`` of wrapped linears that belong to the model, not to a layer."""
+        return None
+
+    def _peft_split(self, layer_prefix: str, path: str, B: torch.Tensor, names):
+        raise NotImplementedError
+
+    def _peft_join(self, layer_prefix: str, path: str, parts, names) -> torch.Tensor:
+        raise NotImplementedError
+
     def _peft_module_name(self, name: str) -> str:
         """Internal linear name -> the name ``adapter_config.json`` lists under ``target_modules``."""
         return name

@@ -39,6 +39,9 @@ def _layer_slots(bridge, layer_idx: int, hf_idx: Optional[int] = None) -> List[T
     the layer, hf module names).  ``layer_idx`` selects the layer's structure (MoE or dense, linear or softmax
     attention); ``hf_idx`` is the index the layer has in the checkpoint (MTP layers sit after the decoder)."""
     cfg = bridge.config
+    custom = bridge._peft_layer_slots(layer_idx)
+    if custom is not None:          # families whose layers are laid out differently give their own table
+        return custom
     ap, mp = bridge.hf_attn_prefix + '.', bridge.hf_mlp_prefix + '.'
     lprefix = f'{bridge.hf_layers_prefix}.{layer_idx if hf_idx is None else hf_idx}.'
     slots = []
@@ -144,6 +147,11 @@ def _iter_layers(bridge, mg_models):
     for k in range(bridge.config.mtp_num_layers or 0):
         slots, lp = _mtp_slots(bridge, k)
         yield (mtp.layers[k] if mtp is not None else None), slots, lp
+    # linears that belong to the model rather than to a layer (family-specific), addressed from the first stage
+    extra = bridge._peft_model_slots()
+    if extra:
+        first = next((m for m in models if getattr(m, 'pre_process', False)), None)
+        yield first, extra[0], PREFIX + extra[1]
 
 
 def _check_all_visited(bridge, mg_models, visited: set, adapter_name: str, what: str) -> None:
@@ -184,7 +192,7 @@ def export_adapter(bridge, mg_models, adapter_name: str = 'default') -> Iterator
                 continue
             a = mod.lora_A[adapter_name].weight if is_lora else None
             b = mod.lora_B[adapter_name].weight if is_lora else None
-            if kind in ('column', 'replicated', 'qkv', 'qkv_fused', 'glu', 'gdn_in'):
+            if kind in ('column', 'replicated', 'qkv', 'qkv_fused', 'glu', 'gdn_in', 'custom_col'):
                 A = _gather(bridge, None if a is None else a.detach(), None)
                 B = _gather(bridge, None if b is None else b.detach(), None if kind == 'replicated' else
                             ('glu' if kind == 'glu' else 0))
@@ -200,6 +208,8 @@ def export_adapter(bridge, mg_models, adapter_name: str = 'default') -> Iterator
                     from .gpt_bridge import gdn_in_proj_to_hf
                     by_name = gdn_in_proj_to_hf(B, cfg, bridge.split_gdn_projections)
                     parts = [by_name[n] for n in names]
+                elif kind == 'custom_col':
+                    parts = bridge._peft_split(lp, path, B, names)
                 else:
                     parts = [B]
                 for n, bp in zip(names, parts):
@@ -263,7 +273,7 @@ def load_adapter(bridge, mg_models, sd: Dict[str, LazyTensor], adapter_name: str
             a, b = mod.lora_A[adapter_name].weight, mod.lora_B[adapter_name].weight
             is_expert = mod.is_expert
             _, n, r = _tp(bridge, is_expert)
-            if kind in ('column', 'replicated', 'qkv', 'qkv_fused', 'glu', 'gdn_in'):
+            if kind in ('column', 'replicated', 'qkv', 'qkv_fused', 'glu', 'gdn_in', 'custom_col'):
                 As = [get(f'{lp}{hp}{nm}.lora_A.weight') for nm in names]
                 for other in As[1:]:
                     assert torch.equal(As[0], other), f'{path}: the fused projections need identical lora_A matrices'
@@ -280,6 +290,8 @@ def load_adapter(bridge, mg_models, sd: Dict[str, LazyTensor], adapter_name: str
                 elif kind == 'gdn_in':
                     from .gpt_bridge import gdn_in_proj_to_mcore
                     B, tp_dim = gdn_in_proj_to_mcore(dict(zip(names, Bs)), cfg, bridge.split_gdn_projections), 0
+                elif kind == 'custom_col':
+                    B, tp_dim = bridge._peft_join(lp, path, Bs, names), 0
                 else:
                     B, tp_dim = Bs[0], (None if kind == 'replicated' else 0)
                 with torch.no_grad():

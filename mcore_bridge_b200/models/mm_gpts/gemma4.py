@@ -480,6 +480,52 @@ class Gemma4Bridge(MultimodalGPTBridge):
         for j, n in enumerate(names[1:]):
             self._emit(hf_sd, f'{ap}{n}.weight', g[:, (qpg + j) * d:(qpg + j + 1) * d].reshape(-1, h))
 
+    # ------------------------------------------------------------------ LoRA adapters (PEFT format)
+    def _qkv_names(self, kind):
+        _, _, _, k_eq_v, shared, _ = kind
+        return ['q_proj'] + ([] if shared else (['k_proj'] if k_eq_v else ['k_proj', 'v_proj']))
+
+    def _peft_layer_slots(self, layer_idx: int):
+        kind = self.kinds[layer_idx]
+        slots = [('self_attention.linear_qkv', 'custom_col', 'self_attn.', self._qkv_names(kind)),
+                 ('self_attention.linear_proj', 'row', 'self_attn.', ['o_proj']),
+                 ('mlp.linear_fc1', 'glu', 'mlp.', ['gate_proj', 'up_proj']),
+                 ('mlp.linear_fc2', 'row', 'mlp.', ['down_proj'])]
+        if getattr(self.tc, 'hidden_size_per_layer_input', 0):
+            slots.append(('per_layer_input_gate', 'column', '', ['per_layer_input_gate']))
+            slots.append(('per_layer_projection', 'row', '', ['per_layer_projection']))
+        if getattr(self.tc, 'enable_moe_block', False):
+            slots.append(('experts_mlp.router', 'replicated', 'router.', ['proj']))
+            slots.append(('experts_mlp.experts.linear_fc1', 'grouped_glu', 'experts.', ['gate_proj', 'up_proj']))
+            slots.append(('experts_mlp.experts.linear_fc2', 'grouped_row', 'experts.', ['down_proj']))
+        return slots
+
+    def _peft_model_slots(self):
+        if not getattr(self.tc, 'hidden_size_per_layer_input', 0):
+            return None
+        return [('per_layer_model_projection', 'column', '', ['per_layer_model_projection'])], self.lm_prefix
+
+    def _kind_of(self, layer_prefix: str):
+        return self.kinds[int(layer_prefix.rstrip('.').rsplit('.', 1)[1])]
+
+    def _peft_split(self, layer_prefix: str, path: str, B, names):
+        """``lora_B`` of the packed q / k / v projection (rows grouped per KV head) -> one matrix per projection."""
+        _, d, ng, _, shared, _ = self._kind_of(layer_prefix)
+        if shared:
+            return [B]
+        qpg, r = self.config.num_attention_heads // ng, B.shape[1]
+        g = B.view(ng, (qpg + len(names) - 1) * d, r)
+        return [g[:, :qpg * d].reshape(-1, r)] + [g[:, (qpg + j) * d:(qpg + j + 1) * d].reshape(-1, r)
+                                                  for j in range(len(names) - 1)]
+
+    def _peft_join(self, layer_prefix: str, path: str, parts, names):
+        _, d, ng, _, shared, _ = self._kind_of(layer_prefix)
+        if shared:
+            return parts[0]
+        qpg, r = self.config.num_attention_heads // ng, parts[0].shape[1]
+        grouped = [parts[0].view(ng, qpg * d, r)] + [p_.view(ng, d, r) for p_ in parts[1:]]
+        return torch.cat(grouped, dim=1).reshape(-1, r)
+
     def _set_layer_state(self, layer, hf_sd, prefix: str, layer_idx: int, to_mcore: bool):
         kind = self.kinds[layer_idx]
         attn = layer.self_attention if layer is not None else None

@@ -298,10 +298,14 @@ class LoraParallelLinear(nn.Module):
                 delta = self._lora_grouped(x, args[0] if args else kwargs['offsets'], name)
             else:
                 h, b = self._lora_dense_a(x, name), self.lora_B[name].weight
-                if self._can_accumulate(result, h, b):
+                # a column-parallel base that hands out its gathered output: the adapter's local columns are gathered too
+                gathered = self.tp_size > 1 and bool(getattr(base, 'gather_output', False))
+                if not gathered and self._can_accumulate(result, h, b):
                     result = _AccumulateLoraB.apply(result, h, b, float(self.scaling[name]))
                     continue
                 delta = linear(h, b, None, LinearSpec())
+                if gathered:
+                    delta = M.gather_from_tensor_model_parallel_region(delta, self.group)
             result = result + delta * self.scaling[name]
         result = result.to(x.dtype) if result.dtype != x.dtype and x.is_floating_point() else result
         return (result, x) if want_norm else result

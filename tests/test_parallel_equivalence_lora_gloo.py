@@ -112,12 +112,7 @@ def _family_worker(rank, world, ckpt, adapter, tp, ep, save_to=None):
     return losses, {k: v.clone() for k, v in cfg.bridge.export_weights(tr.models, peft_format=True)}
 
 
-def test_lora_glm_dsa_tp2_ep2_matches_single_process(tmp_path):
-    """MLA with a query low-rank path and the DSA indexer: adapters on the replicated down projections (run on this
-    rank's tokens under sequence parallelism, no collective of their own), on the fused norm + up projections (whose
-    normalised input also feeds the indexer) and on the indexer's linears."""
-    import test_parallel_equivalence_families_gloo as Fm
-    hf = Fm._glm_dsa()
+def _check_family(tmp_path, hf, tp, ep, expect_keys):
     torch.manual_seed(0)
     with torch.no_grad():
         for n, p in hf.named_parameters():
@@ -126,10 +121,33 @@ def test_lora_glm_dsa_tp2_ep2_matches_single_process(tmp_path):
     hf.save_pretrained(d)
     run_ranks(_family_worker, 1, d, None, 1, 1, a)
     base_losses, base_w = run_ranks(_family_worker, 1, d, a, 1, 1)[0]
-    assert any('q_a_proj.lora_B' in k for k in base_w) and any('indexer.wq_b.lora_A' in k for k in base_w)
-    for losses, weights in run_ranks(_family_worker, 4, d, a, 2, 2):
+    for frag in expect_keys:
+        assert any(frag in k for k in base_w), frag
+    for losses, weights in run_ranks(_family_worker, 4, d, a, tp, ep):
         for x, y in zip(losses, base_losses):
             assert abs(x - y) < 3e-5, (losses, base_losses)
         assert set(weights) == set(base_w)
         for k, v in base_w.items():
             assert torch.allclose(weights[k], v, rtol=0, atol=2e-6), (k, (weights[k] - v).abs().max().item())
+    return base_w
+
+
+def test_lora_glm_dsa_tp2_ep2_matches_single_process(tmp_path):
+    """MLA with a query low-rank path and the DSA indexer: adapters on the replicated down projections (run on this
+    rank's tokens under sequence parallelism, no collective of their own), on the fused norm + up projections (whose
+    normalised input also feeds the indexer) and on the indexer's linears."""
+    import test_parallel_equivalence_families_gloo as Fm
+    _check_family(tmp_path, Fm._glm_dsa(), 2, 2, ['q_a_proj.lora_B', 'indexer.wq_b.lora_A'])
+
+
+def test_lora_gemma4_tp2_dp2_matches_single_process(tmp_path):
+    """Gemma-4: per-layer-type head sizes and KV head counts in the packed q / k / v adapter, layers without a value
+    projection (k = v) or without keys and values of their own (shared KV), the per-layer-input projections (one of
+    them a model-level column-parallel linear that hands out its gathered output) and the MoE branch."""
+    import test_parallel_equivalence_families_gloo as Fm
+    w = _check_family(tmp_path, Fm._gemma4(), 2, 1,
+                      ['layers.0.self_attn.v_proj.lora_B', 'layers.2.self_attn.k_proj.lora_B',
+                       'per_layer_model_projection.lora_A', 'layers.0.per_layer_input_gate.lora_B',
+                       'layers.0.experts.1.gate_proj.lora_B'])
+    assert not any('layers.2.self_attn.v_proj' in k for k in w)         # full-attention layers: k = v
+    assert not any('layers.5.self_attn.k_proj' in k for k in w)         # shared-KV tail layers project queries only
