@@ -107,6 +107,10 @@ class TokenFileDataset:
             raise ValueError(f'{path} holds fewer than {seq_len + 1} tokens')
         self.cursor, self.stride = dp_rank, dp_size
 
+    def skip(self, n_microbatches: int) -> None:
+        """Moves past ``n_microbatches`` micro-batches without reading them (resume)."""
+        self.cursor += n_microbatches * self.mbs * self.stride
+
     def next_microbatch(self) -> Dict[str, torch.Tensor]:
         import numpy as np
         rows = []
@@ -186,6 +190,13 @@ def main(argv=None) -> int:
     else:
         ds = SyntheticPackedDataset(cfg.padded_vocab_size, args.seq_len, micro_batch_size=args.micro_batch_size,
                                     seed=args.seed + dp_rank, segment_multiple=max(1, args.tp * 2 * args.cp))
+    if start_step:
+        # continue the data stream where the interrupted run stopped
+        if hasattr(ds, 'skip'):
+            ds.skip(start_step * n_micro)
+        else:
+            for _ in range(start_step * n_micro):
+                ds.next_microbatch()
     tokens_per_step = args.global_batch * args.seq_len
     t_last = time.perf_counter()
     for step in range(start_step, args.steps):

@@ -28,6 +28,12 @@ def test_cli_trains_saves_and_resumes(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     lines = [json.loads(l[l.index('{'):]) for l in (r.stdout + r.stderr).splitlines() if '"step"' in l]
     assert [l['step'] for l in lines] == [4]
+    resumed = lines[0]
+    # the resumed run continues the data stream: its step 4 is the step 4 of an uninterrupted run
+    r = subprocess.run(base[:-2] + ['--steps', '4'], env=env, capture_output=True, text=True, timeout=600, cwd=REPO)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    lines = [json.loads(l[l.index('{'):]) for l in (r.stdout + r.stderr).splitlines() if '"step"' in l]
+    assert lines[-1]['step'] == 4 and abs(lines[-1]['loss'] - resumed['loss']) < 1e-5, (lines[-1], resumed)
 
 
 def test_cli_overrides_reach_the_model_config(tmp_path):
