@@ -193,6 +193,9 @@ class LoraParallelLinear(nn.Module):
         else:
             a = _LoraFactor((r, self.in_features), dt, dev, False, -1, self.is_expert, sp)
             b = _LoraFactor((self.out_features, r), dt, dev, tp > 1, 0, self.is_expert, False)
+            # rows laid out like the base weight's (a gated MLP keeps [gate shard; up shard] on every rank): sharded
+            # checkpoints re-partition the factor with the same stride
+            b.weight.partition_stride = int(getattr(w, 'partition_stride', 1))
         self.lora_A[adapter_name] = a
         self.lora_B[adapter_name] = b
         self.scaling[adapter_name] = lora_alpha / math.sqrt(r) if use_rslora else lora_alpha / r
