@@ -301,7 +301,7 @@ class LoraParallelLinear(nn.Module):
                 delta = self._lora_grouped(x, args[0] if args else kwargs['offsets'], name)
             else:
                 h, b = self._lora_dense_a(x, name), self.lora_B[name].weight
-                # a column-parallel base that hands out its gathered output: the adapter's local columns are gathered too
+                # a column-parallel base that hands out its gathered output: the adapter's columns are gathered too
                 gathered = self.tp_size > 1 and bool(getattr(base, 'gather_output', False))
                 if not gathered and self._can_accumulate(result, h, b):
                     result = _AccumulateLoraB.apply(result, h, b, float(self.scaling[name]))
