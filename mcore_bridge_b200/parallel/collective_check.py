@@ -2,12 +2,12 @@
 into an exception that names the group, the position in the sequence and what each rank tried to do.
 
 While installed (``with CollectiveOrderChecker(): ...``, or ``MCB200_CHECK_COLLECTIVES=1`` in the trainer), every
-``torch.distributed`` collective first publishes a signature (operation, element count, dtype) under a key made of
-the group's member ranks and a per-group sequence number in the job's rendezvous store, then reads the signatures of
-the other members with a time limit.  A different signature raises :class:`CollectiveMismatch` on every rank that
-sees it; a member that never arrives raises :class:`CollectiveTimeout` on the ones waiting.  Nothing runs on a device:
-the comparison happens on the host before the collective is launched, so a diverged rank never leaves a kernel waiting for
-its peers.  It costs a store round trip per collective and is meant for reproducing a hang, not for production steps.
+``torch.distributed`` collective first publishes a signature (operation, element count, dtype) under a key made of the
+group's member ranks and a per-group sequence number in the job's rendezvous store, then reads the signatures of the
+other members with a time limit. A different signature raises :class:`CollectiveMismatch` on every rank that sees it;
+a member that never arrives raises :class:`CollectiveTimeout` on the ones waiting. Nothing runs on a device: the
+comparison happens on the host before the collective is launched, so a diverged rank never leaves a kernel waiting for
+its peers. It costs a store round trip per collective and is meant for reproducing a hang, not for production steps.
 
 The reference has no such facility: its lock-step weight export relies on flag all-reduces to keep ranks on the same
 branch (``src/mcore_bridge/bridge/gpt_bridge.py:358-382,469-472``).
