@@ -268,8 +268,11 @@ class MLASelfAttention(nn.Module):
         from ..ops import dsa
         o, attn_probs = dsa.sparse_attention(q, k, v, idx, mask, self.scale, need_probs=train_indexer)
         if train_indexer:
+            # the target distribution sums the heads of every tensor-parallel rank; under context parallelism the
+            # queries here are this rank's part of the stream and the loss its share of the stream's mean
             loss = dsa.indexer_kl_loss(scores, attn_probs.detach(), mask,
-                                       idx if cfg.dsa_indexer_use_sparse_loss else None)
+                                       idx if cfg.dsa_indexer_use_sparse_loss else None, head_group='tp',
+                                       token_share=ps.get_world_size('cp'))
             from ..ops.moe import MoEAuxLossAutoScaler
             o = MoEAuxLossAutoScaler.apply(o, loss * cfg.dsa_indexer_loss_coeff)
             self.indexer_loss = loss.detach()

@@ -52,16 +52,28 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, idx: tor
 
 
 def indexer_kl_loss(scores: torch.Tensor, attn_probs: torch.Tensor, mask: torch.Tensor,
-                    idx: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``scores [T, Tk]`` (with ``-inf`` outside the mask), ``attn_probs [h, T, Tk]`` -> scalar KL."""
+                    idx: Optional[torch.Tensor] = None, head_group: Optional[str] = None,
+                    token_share: int = 1) -> torch.Tensor:
+    """``scores [T, Tk]`` (with ``-inf`` outside the mask), ``attn_probs [h, T, Tk]`` -> scalar KL.
+
+    ``head_group``: the heads are split over this process group (tensor parallelism): the target distribution is the
+    sum over all of them.  ``token_share``: the queries are 1 / ``token_share`` of the token stream (context
+    parallelism): the result is this rank's share of the mean over the whole stream, like the other auxiliary losses."""
     target = attn_probs.sum(0)
+    if head_group is not None:
+        import torch.distributed as dist
+
+        from ..parallel import state as ps
+        if ps.get_world_size(head_group) > 1:
+            target = target.clone()
+            dist.all_reduce(target, group=ps.get_group(head_group))
     keep = mask if idx is None else (topk_mask(idx, scores.shape[1]) & mask)
     target = target.masked_fill(~keep, 0.0)
     target = target / target.sum(-1, keepdim=True).clamp(min=1e-20)
     logp = torch.log_softmax(scores.masked_fill(~keep, float('-inf')), dim=-1)
     logp = torch.where(keep, logp, torch.zeros_like(logp))
     kl = (target * (torch.log(target.clamp(min=1e-20)) - logp)).sum(-1)
-    return kl.mean()
+    return kl.mean() / token_share
 
 
 # ------------------------------------------------------------------------------------------------ CUDA kernels

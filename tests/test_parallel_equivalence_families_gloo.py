@@ -161,3 +161,9 @@ def test_gpt_oss_cp2_ep2_matches_single_process(tmp_path):
 def test_qwen3_next_tp2_cp2_matches_single_process(tmp_path):
     # the linear-attention heads are split over tp and, inside the layer, once more over cp
     _check(tmp_path, _qwen3_next(4, 8), tp=2, cp=2, over={'moe_aux_loss_coeff': 1e-2})
+
+
+def test_glm_dsa_indexer_loss_tp2_ep2_matches_single_process(tmp_path):
+    """Training the DSA indexer (KL towards the attention distribution): the target sums the heads of both
+    tensor-parallel ranks, so every rank computes the same loss for the replicated indexer."""
+    _check(tmp_path, _glm_dsa(), tp=2, ep=2, over={'dsa_indexer_loss_coeff': 0.1})
