@@ -183,7 +183,11 @@ class TopKRouter(nn.Module):
             return probs, idx
         if cfg.moe_z_loss_coeff:
             z = moe_ops.z_loss(logits, cfg.moe_z_loss_coeff)
-            logits = moe_ops.MoEAuxLossAutoScaler.apply(logits, z)
+            # the mean is over this rank's tokens: where the tokens are split over ranks (sequence and context
+            # parallelism) the term added to the graph is this rank's share of the mean over all of them
+            tp = ps.get_world_size('tp')
+            share = (tp if (cfg.sequence_parallel and tp > 1) else 1) * ps.get_world_size('cp')
+            logits = moe_ops.MoEAuxLossAutoScaler.apply(logits, z / share if share > 1 else z)
             _track('z_loss', z / cfg.moe_z_loss_coeff)
         probs, idx, scores = moe_ops.topk_routing(
             logits, self.topk, cfg.moe_router_score_function, cfg.moe_router_pre_softmax, cfg.moe_router_num_groups,

@@ -114,3 +114,10 @@ def test_dense_tied_embeddings_pp2_dp2_matches_single_process(tmp_path):
     clipping norm once."""
     from transformers import Qwen3ForCausalLM
     _check(tmp_path, 'qwen3_tiny', Qwen3ForCausalLM, tp=1, ep=1, pp=2, hf_over={'tie_word_embeddings': True})
+
+
+def test_moe_z_loss_tp2_ep2_matches_single_process(tmp_path):
+    """The router z-loss is a mean over tokens: with the tokens split over the tensor-parallel ranks (sequence
+    parallelism) every rank adds its share of it."""
+    from transformers import Qwen3MoeForCausalLM
+    _check(tmp_path, 'qwen3_moe_tiny', Qwen3MoeForCausalLM, tp=2, ep=2, aux=1e-2, over={'moe_z_loss_coeff': 1e-2})
